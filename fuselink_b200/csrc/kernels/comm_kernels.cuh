@@ -1,0 +1,61 @@
+// Device-initiated data movement over NVLink / NVSwitch peer mappings: chunked multi-segment put
+// (p2p, striped relay send, relay forward, all-to-all), flag waits and a flag barrier.
+//
+// Synchronisation model (shared by every kernel of this library):
+//   * every rank owns a "signal pad" (uint32 words) inside its symmetric region, mapped by all peers;
+//   * words are monotone: a producer either stores a sequence number (st.release.sys) or adds 1
+//     (red.release.sys) after its data stores; a consumer polls with ld.acquire.sys until the word is
+//     >= the value it expects.  Nothing is ever reset, so no reset/reuse races exist;
+//   * every poll is bounded (2 s); on expiry the kernel records a code in `status` and returns.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define FL_MAX_SEGS 8
+
+enum FlFlagMode : int {
+  FL_FLAG_NONE = 0,
+  FL_FLAG_SEQ_PER_CHUNK = 1,  // flags[chunk] = seq          (relay staging: one word per chunk)
+  FL_FLAG_COUNT = 2,          // flags[0]   += 1 per chunk   (final destination: arrival counter)
+};
+
+struct FlSeg {
+  const void* src;            // local or peer address
+  void* dst;                  // local or peer address
+  unsigned long long bytes;
+  uint32_t* flags;            // see FlFlagMode (address in the consumer's signal pad)
+  int flag_mode;
+  const uint32_t* wait_flags; // if set: chunk c is copied only after wait_flags[c] >= seq (relay forward)
+};
+
+struct FlPutArgs {
+  FlSeg seg[FL_MAX_SEGS];
+  int nseg;
+  unsigned int chunk_bytes;   // multiple of 16
+  unsigned int seq;
+  int use_bulk;               // 1: cp.async.bulk global->smem->global engine, 0: ld/st vectors
+  int* status;
+};
+
+struct FlWaitArgs {
+  const uint32_t* flag[16];
+  unsigned int want[16];
+  int n;
+  int* status;
+};
+
+struct FlSignalPtrs {
+  uint32_t* p[8];             // p[r] = base of rank r's signal pad as mapped in THIS process
+};
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+int fl_put_chunks(const FlPutArgs* args, int num_ctas, int threads, cudaStream_t stream);
+int fl_wait_flags(const FlWaitArgs* args, cudaStream_t stream);
+// every rank: pads.p[r][slot0 + rank] = seq for all r, then wait pads.p[rank][slot0 + r] >= seq for all r
+int fl_barrier(FlSignalPtrs pads, int slot0, int rank, int world, unsigned int seq, int do_signal, int do_wait,
+               int* status, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,140 @@
+// DLRM sparse side, table-wise sharded: embedding-bag sum pooling fused with the pooled-embedding
+// all-to-all (forward) and its mirror fused with the sparse SGD update (backward).
+//
+//   forward : the GPU that owns table t pools the rows of every sample b of the GLOBAL batch and stores
+//             the pooled vector straight into the sample owner's [B_local, T_total, D] buffer over NVLink.
+//             No [B_global, T_local, D] send buffer and no separate all-to-all exist.
+//   backward: the table owner reads d(pooled)[b, t, :] from the sample owner's gradient buffer over
+//             NVLink and applies  W[idx] -= lr * g  for every index of the bag with vector reductions.
+//
+// One warp handles one (table, sample) bag; D = 32 * 4 * VEC floats (D = 128 -> one float4 per lane).
+// Reference parity: the reference runs this workload through an external DLRM checkout
+// (.gitmodules:5-7) that uses a framework EmbeddingBag followed by an NCCL all-to-all.
+#include "embbag.cuh"
+#include "../common/fl_ptx.cuh"
+
+namespace fl {
+
+__device__ __forceinline__ float4 ld_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float4 ld_f4_coherent(const float* p) {
+  float4 v;
+  asm volatile("ld.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_f4(float* p, float4 v) {
+  asm volatile("st.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void red_add_f4(float* p, float4 v) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+               : "memory");
+}
+
+// grid: persistent; each warp walks bags  w, w + nwarps, ...   bag id = t_local * B_global + b
+template <int MAXL>
+__global__ void __launch_bounds__(256) embbag_fwd_kernel(const FlEmbBagArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long nbags = (long long)a.t_local * a.b_global;
+  const int vec_per_lane = a.dim / 128;  // float4 per lane
+  for (long long bag = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); bag < nbags; bag += nwarps) {
+    const int t = (int)(bag / a.b_global);
+    const int b = (int)(bag - (long long)t * a.b_global);
+    const long long* idx = a.indices + bag * a.pooling;
+    // lanes load the bag's indices once, then broadcast
+    long long my_idx = 0;
+    if (lane < a.pooling) {
+      my_idx = idx[lane];
+      if (my_idx < 0 || my_idx >= a.rows) {  // bounds check: skip the access, record it
+        report(a.status, kBadIndex, 900);
+        my_idx = -1;
+      }
+    }
+    const float* table = a.weights + (long long)t * a.rows * a.dim;
+    const int owner = b / a.b_local;
+    const int bl = b - owner * a.b_local;
+    float* out = reinterpret_cast<float*>(a.out_peers.p[owner]) +
+                 ((long long)bl * a.t_total + (a.t_first + t)) * a.dim;
+    for (int v = 0; v < vec_per_lane; ++v) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 r[MAXL];
+#pragma unroll
+      for (int j = 0; j < MAXL; ++j) {
+        const long long ij = __shfl_sync(0xffffffffu, my_idx, j);
+        r[j] = (j < a.pooling && ij >= 0) ? ld_f4(table + ij * a.dim + v * 128 + lane * 4)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < MAXL; ++j) {
+        acc.x += r[j].x; acc.y += r[j].y; acc.z += r[j].z; acc.w += r[j].w;
+      }
+      st_f4(out + v * 128 + lane * 4, acc);
+    }
+  }
+}
+
+template <int MAXL>
+__global__ void __launch_bounds__(256) embbag_bwd_kernel(const FlEmbBagArgs a) {
+  const int lane = threadIdx.x & 31;
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long nbags = (long long)a.t_local * a.b_global;
+  const int vec_per_lane = a.dim / 128;
+  for (long long bag = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); bag < nbags; bag += nwarps) {
+    const int t = (int)(bag / a.b_global);
+    const int b = (int)(bag - (long long)t * a.b_global);
+    const long long* idx = a.indices + bag * a.pooling;
+    long long my_idx = -1;
+    if (lane < a.pooling) {
+      my_idx = idx[lane];
+      if (my_idx < 0 || my_idx >= a.rows) {
+        report(a.status, kBadIndex, 901);
+        my_idx = -1;
+      }
+    }
+    float* table = a.weights_rw + (long long)t * a.rows * a.dim;
+    const int owner = b / a.b_local;
+    const int bl = b - owner * a.b_local;
+    const float* g = reinterpret_cast<const float*>(a.out_peers.p[owner]) +
+                     ((long long)bl * a.t_total + (a.t_first + t)) * a.dim;
+    for (int v = 0; v < vec_per_lane; ++v) {
+      float4 gv = ld_f4_coherent(g + v * 128 + lane * 4);  // peer memory written this step: no .nc
+      gv.x *= -a.lr; gv.y *= -a.lr; gv.z *= -a.lr; gv.w *= -a.lr;
+#pragma unroll
+      for (int j = 0; j < MAXL; ++j) {
+        const long long ij = __shfl_sync(0xffffffffu, my_idx, j);
+        if (j < a.pooling && ij >= 0) red_add_f4(table + ij * a.dim + v * 128 + lane * 4, gv);
+      }
+    }
+  }
+}
+
+}  // namespace fl
+
+static int check(const FlEmbBagArgs* a) {
+  if (a->dim <= 0 || a->dim % 128) return -1;   // one float4 per lane per 128 columns
+  if (a->pooling < 1 || a->pooling > 32) return -2;
+  if (a->b_local <= 0 || a->b_global % a->b_local) return -3;
+  if (a->b_global / a->b_local > 8) return -4;
+  return 0;
+}
+
+extern "C" int fl_embbag_a2a_fwd(const FlEmbBagArgs* a, int num_ctas, cudaStream_t stream) {
+  int rc = check(a);
+  if (rc) return rc;
+  if (num_ctas <= 0) num_ctas = 148 * 8;
+  if (a->pooling <= 20) fl::embbag_fwd_kernel<20><<<num_ctas, 256, 0, stream>>>(*a);
+  else fl::embbag_fwd_kernel<32><<<num_ctas, 256, 0, stream>>>(*a);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fl_embbag_a2a_bwd_sgd(const FlEmbBagArgs* a, int num_ctas, cudaStream_t stream) {
+  int rc = check(a);
+  if (rc) return rc;
+  if (num_ctas <= 0) num_ctas = 148 * 8;
+  if (a->pooling <= 20) fl::embbag_bwd_kernel<20><<<num_ctas, 256, 0, stream>>>(*a);
+  else fl::embbag_bwd_kernel<32><<<num_ctas, 256, 0, stream>>>(*a);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,521 @@
+// Persistent, warp-specialised grouped GEMM for sm_100a.
+//
+//   warp 0      : TMA producer  (cp.async.bulk.tensor, never multicast; operands are always local memory)
+//   warp 1      : MMA issuer    (tcgen05.mma kind::f16, one elected thread), owns the TMEM allocation
+//   warps 2..5  : epilogue      (tcgen05.ld -> registers -> fused epilogue -> global / peer stores)
+//
+// One CTA per SM walks a tile list that is derived on the device from the per-expert row counts, so the
+// host never has to read the routing result back.  Tile = 128 x 256 fp32 accumulator in TMEM, two
+// accumulators (512 columns) so the epilogue of tile i overlaps the main loop of tile i+1.  Operand
+// tiles are 128-byte-swizzled, 4 stages of (16 KiB A + 32 KiB B).
+//
+// The fused epilogues are what make this the MoE hot path rather than a library GEMM:
+//   SWIGLU  : gate/up interleaved weight -> act = silu(g)*u written once, g/u saved for backward
+//   SCATTER : every output row is stored straight into the home GPU's combine buffer over NVLink
+//   DSWIGLU : backward of the activation applied on the dAct accumulator
+//   WGRAD   : contraction over the routed tokens (both operands MN-major), optional in-place SGD
+//
+// Reference parity: the reference ships no GPU kernels; its MoE workload is an external
+// Megatron-DeepSpeed checkout (.gitmodules:11-13) whose expert FFN is a framework GEMM between two NCCL
+// all-to-alls.  This file is the replacement for that GEMM + the second all-to-all.
+#include "grouped_gemm.cuh"
+#include "../common/fl_ptx.cuh"
+#include <cuda.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace fl {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int ROW_BYTES = 128;            // one swizzle row: 64 bf16 along the contiguous dimension
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * ROW_BYTES;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * ROW_BYTES;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers, counts*/;
+
+struct KParams {
+  int group_mode, num_groups, cap, M, N, K;
+  const int* counts;
+  int a_mn, b_mn;
+  int epilogue;
+  __nv_bfloat16* C; long long ldc, gsc;
+  __nv_bfloat16* gu; long long ldgu;
+  __nv_bfloat16* dgu;
+  const int* row_info;
+  FlPeerPtrs peers;
+  float sgd_lr;
+  int zero_tail;
+  int group_m;
+  int* status;
+};
+
+struct Tile {
+  int g, m0, n0, kblocks, rows;  // rows: valid rows of this tile (M-grouped), BM otherwise
+};
+
+struct Shared {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int counts[FL_GEMM_MAX_GROUPS];
+};
+
+// Map a linear tile id to a tile.  Every role of the CTA calls this with the same id and gets the same
+// answer; the list ends at the first id that maps to nothing.
+__device__ __forceinline__ bool map_tile(const KParams& p, const int* counts, int id, Tile& t) {
+  const int NT = (p.N + BN - 1) / BN;
+  if (p.group_mode == 0) {
+    const int kblocks = (p.K * 2 /*bytes*/ + ROW_BYTES - 1) / ROW_BYTES;
+    int acc = 0;
+    for (int g = 0; g < p.num_groups; ++g) {
+      const int cnt = counts[g];
+      const int mt = (cnt + BM - 1) / BM;
+      const int tiles = mt * NT;
+      if (id < acc + tiles) {
+        const int l = id - acc;
+        const int per_sg = p.group_m * NT;
+        const int sg = l / per_sg;
+        const int first_m = sg * p.group_m;
+        const int gsz = min(p.group_m, mt - first_m);
+        const int r = l - sg * per_sg;
+        const int m = first_m + r % gsz;
+        const int n = r / gsz;
+        t.g = g; t.m0 = m * BM; t.n0 = n * BN; t.kblocks = kblocks;
+        t.rows = min(BM, cnt - t.m0);
+        return true;
+      }
+      acc += tiles;
+    }
+    return false;
+  } else {
+    const int MT = (p.M + BM - 1) / BM;
+    const int per_group = MT * NT;
+    const int g = id / per_group;
+    if (g >= p.num_groups) return false;
+    const int l = id - g * per_group;
+    const int per_sg = p.group_m * NT;
+    const int sg = l / per_sg;
+    const int first_m = sg * p.group_m;
+    const int gsz = min(p.group_m, MT - first_m);
+    const int r = l - sg * per_sg;
+    t.g = g; t.m0 = (first_m + r % gsz) * BM; t.n0 = (r / gsz) * BN;
+    t.kblocks = (counts[g] + 63) / 64;
+    t.rows = BM;
+    return true;
+  }
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void unpack_bf16(uint32_t u, float& a, float& b) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
+  a = __bfloat162float(v.x);
+  b = __bfloat162float(v.y);
+}
+// store 32 fp32 values as 32 bf16 (64 B) to a 16-byte aligned address
+__device__ __forceinline__ void store32_bf16(__nv_bfloat16* dst, const float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 o;
+    o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+    o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+    o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+    o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+    st_v4(dst + 8 * i, o);
+  }
+}
+__device__ __forceinline__ void load32_bf16(const __nv_bfloat16* src, float* v) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 o = ld_v4(src + 8 * i);
+    unpack_bf16(o.x, v[8 * i + 0], v[8 * i + 1]);
+    unpack_bf16(o.y, v[8 * i + 2], v[8 * i + 3]);
+    unpack_bf16(o.z, v[8 * i + 4], v[8 * i + 5]);
+    unpack_bf16(o.w, v[8 * i + 6], v[8 * i + 7]);
+  }
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // operand stages need 1024-byte alignment for the 128-byte swizzle pattern
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Shared* sh = reinterpret_cast<Shared*>(smem + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sh->tmem_full[a], 1);
+      mbar_init(&sh->tmem_empty[a], 4);  // one arrival per epilogue warp
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  for (int g = threadIdx.x; g < p.num_groups; g += NUM_THREADS)
+    sh->counts[g] = p.counts ? min(p.counts[g], p.cap) : p.cap;
+  if (warp == 1) {
+    tmem_alloc(&sh->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+  const int* counts = sh->counts;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;  // global k-block counter -> stage and phase
+      bool ok = true;
+      Tile t;
+      for (int id = blockIdx.x; ok && map_tile(p, counts, id, t); id += gridDim.x) {
+        for (int kb = 0; kb < t.kblocks && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&sh->empty[s], ph ^ 1, abort_flag, p.status, kTimeoutMbarEmpty, 100 + s);
+          if (!ok) break;
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          uint8_t* b_dst = a_dst + A_STAGE_BYTES;
+          mbar_arrive_expect_tx(&sh->full[s], STAGE_BYTES);
+          const int k0 = kb * 64;
+          if (p.group_mode == 0) {
+            // A rows of group g, K-major: box {64 k, 128 rows}
+            tma_load_3d(a_dst, &tmA, &sh->full[s], k0, t.m0, t.g);
+            if (!p.b_mn) {
+              tma_load_3d(b_dst, &tmB, &sh->full[s], k0, t.n0, t.g);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(b_dst + j * (64 * ROW_BYTES), &tmB, &sh->full[s], t.n0 + 64 * j, k0, t.g);
+            }
+          } else {
+            // both operands MN-major, contraction over the rows of group g: boxes {64 mn, 64 rows}
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j)
+              tma_load_3d(a_dst + j * (64 * ROW_BYTES), &tmA, &sh->full[s], t.m0 + 64 * j, k0, t.g);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(b_dst + j * (64 * ROW_BYTES), &tmB, &sh->full[s], t.n0 + 64 * j, k0, t.g);
+          }
+        }
+      }
+      if (!ok) {
+        // give copies that are still in flight time to land before the CTA (and its shared memory) goes away
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(1, 1, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u, BM, BN);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      Tile t;
+      for (int id = blockIdx.x; ok && map_tile(p, counts, id, t); id += gridDim.x, ++tile_i) {
+        const int acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        ok = mbar_wait(&sh->tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, 200 + acc);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.kblocks && ok; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&sh->full[s], ph, abort_flag, p.status, kTimeoutMbarFull, 300 + s);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t b_base = a_base + A_STAGE_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {  // 4 x (K = 16) per 64-wide k-block
+            const uint64_t da = p.a_mn ? make_smem_desc(a_base + kk * 2048, 64 * ROW_BYTES, 1024)
+                                       : make_smem_desc(a_base + kk * 32, 16, 1024);
+            const uint64_t db = p.b_mn ? make_smem_desc(b_base + kk * 2048, 64 * ROW_BYTES, 1024)
+                                       : make_smem_desc(b_base + kk * 32, 16, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&sh->empty[s]);  // frees the stage once these MMAs have read it
+        }
+        if (!ok) break;
+        if (t.kblocks > 0) umma_commit(&sh->tmem_full[acc]);
+        else mbar_arrive(&sh->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t tile_i = 0;
+    bool ok = true;
+    Tile t;
+    for (int id = blockIdx.x; ok && map_tile(p, counts, id, t); id += gridDim.x, ++tile_i) {
+      const int acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      ok = mbar_wait(&sh->tmem_full[acc], acc_ph, abort_flag, p.status, kTimeoutTmemFull, 400 + acc);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int r_in_tile = q * 32 + lane;
+      const int row = t.m0 + r_in_tile;            // row inside the group (M-grouped) / output row (K-grouped)
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      const bool have_acc = t.kblocks > 0;
+
+      if (p.epilogue == FL_EPI_STORE || p.epilogue == FL_EPI_SCATTER || p.epilogue == FL_EPI_WGRAD) {
+        bool valid, zero_row = false;
+        __nv_bfloat16* dst = nullptr;
+        if (p.epilogue == FL_EPI_STORE) {
+          valid = r_in_tile < t.rows;
+          zero_row = !valid && p.zero_tail && row < p.cap;
+          dst = p.C + (long long)t.g * p.gsc + (long long)row * p.ldc;
+        } else if (p.epilogue == FL_EPI_SCATTER) {
+          valid = r_in_tile < t.rows;
+          if (valid) {
+            const int info = p.row_info[(long long)t.g * p.cap + row];
+            const int rk = (info >> 28) & 0xF;
+            const long long slot = info & 0x0FFFFFFF;
+            dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
+          }
+        } else {
+          valid = row < p.M;
+          dst = p.C + (long long)t.g * p.gsc + (long long)row * p.ldc;
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          float v[32];
+          if (have_acc) {
+            tmem_ld_32x32(t_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+          }
+          const int col = t.n0 + c * 32;
+          if (col >= p.N) continue;
+          if (valid) {
+            if (p.epilogue == FL_EPI_WGRAD && p.sgd_lr != 0.f) {
+              float w[32];
+              load32_bf16(dst + col, w);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = w[i] - p.sgd_lr * v[i];
+            }
+            store32_bf16(dst + col, v);
+          } else if (zero_row) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            store32_bf16(dst + col, v);
+          }
+        }
+      } else if (p.epilogue == FL_EPI_SWIGLU) {
+        const bool valid = r_in_tile < t.rows;
+        const bool zero_row = !valid && p.zero_tail && row < p.cap;
+        const long long grow = (long long)t.g * p.cap + row;
+        __nv_bfloat16* act = p.C + grow * p.ldc + t.n0 / 2;
+        __nv_bfloat16* gu = p.gu ? p.gu + grow * p.ldgu + t.n0 : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_addr + c * 32, rg);
+          tmem_ld_32x32(t_addr + 128 + c * 32, ru);
+          tmem_ld_wait();
+          float g[32], u[32], a[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            g[i] = valid ? __uint_as_float(rg[i]) : 0.f;
+            u[i] = valid ? __uint_as_float(ru[i]) : 0.f;
+            a[i] = silu_f(g[i]) * u[i];
+          }
+          if (valid || zero_row) {
+            store32_bf16(act + c * 32, a);
+            if (gu) {
+              store32_bf16(gu + c * 32, g);
+              store32_bf16(gu + 128 + c * 32, u);
+            }
+          }
+        }
+      } else {  // FL_EPI_DSWIGLU
+        const bool valid = r_in_tile < t.rows;
+        const bool zero_row = !valid && p.zero_tail && row < p.cap;
+        const long long grow = (long long)t.g * p.cap + row;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int a_col = t.n0 + c * 32;                        // column of dAct
+          const int blk = a_col >> 7, within = a_col & 127;       // 128-wide gate/up block
+          const long long gcol = (long long)blk * 256 + within;   // gate position; up is +128
+          if (valid) {
+            float g[32], u[32], dg[32], du[32];
+            load32_bf16(p.gu + grow * p.ldgu + gcol, g);
+            load32_bf16(p.gu + grow * p.ldgu + gcol + 128, u);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float da = __uint_as_float(r[i]);
+              const float sg = 1.f / (1.f + __expf(-g[i]));
+              const float sl = g[i] * sg;
+              dg[i] = da * u[i] * (sg * (1.f + g[i] * (1.f - sg)));
+              du[i] = da * sl;
+            }
+            store32_bf16(p.dgu + grow * p.ldgu + gcol, dg);
+            store32_bf16(p.dgu + grow * p.ldgu + gcol + 128, du);
+          } else if (zero_row) {
+            float z[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) z[i] = 0.f;
+            store32_bf16(p.dgu + grow * p.ldgu + gcol, z);
+            store32_bf16(p.dgu + grow * p.ldgu + gcol + 128, z);
+          }
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+    }
+    if (p.epilogue == FL_EPI_SCATTER) fence_sys();  // peer stores visible before the kernel's completion is signalled
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------
+// host side
+// --------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static thread_local char g_err[256] = "";
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+// 3-D bf16 view {inner, outer, groups}; box {box_inner, box_outer, 1}; 128-byte swizzle; zero fill.
+static int make_map(CUtensorMap* m, const void* base, long long inner, long long outer, long long groups,
+                    long long ld_elems, long long gs_elems, int box_inner, int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not available");
+    return -10;
+  }
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)groups};
+  if (gs_elems <= 0) gs_elems = ld_elems * outer;
+  cuuint64_t strides[2] = {(cuuint64_t)ld_elems * 2, (cuuint64_t)gs_elems * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (strides[0] & 15) || (strides[1] & 15)) {
+    snprintf(g_err, sizeof g_err, "operand base/strides must be 16-byte aligned");
+    return -11;
+  }
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return -12;
+  }
+  return 0;
+}
+
+}  // namespace fl
+
+extern "C" const char* fl_gemm_last_error(void) { return fl::g_err; }
+
+extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
+  using namespace fl;
+  g_err[0] = 0;
+  auto bad = [](const char* why) {
+    snprintf(g_err, sizeof g_err, "%s", why);
+    return -1;
+  };
+  if (d->elem_bytes != 2) return bad("only bf16 operands are handled by this kernel (fp8 has its own entry point)");
+  if (d->num_groups < 1 || d->num_groups > FL_GEMM_MAX_GROUPS) return bad("num_groups out of range");
+  if (d->cap <= 0 || d->cap % 128) return bad("cap must be a positive multiple of 128");
+  if (d->N % 32) return bad("N must be a multiple of 32");
+  KParams p;
+  memset(&p, 0, sizeof p);
+  p.group_mode = d->group_mode; p.num_groups = d->num_groups; p.cap = d->cap;
+  p.M = d->M; p.N = d->N; p.K = d->K; p.counts = d->counts;
+  p.a_mn = d->a_mn_major; p.b_mn = d->b_mn_major; p.epilogue = d->epilogue;
+  p.C = (__nv_bfloat16*)d->C; p.ldc = d->ldc; p.gsc = d->gsc;
+  p.gu = (__nv_bfloat16*)d->gu; p.ldgu = d->ldgu; p.dgu = (__nv_bfloat16*)d->dgu;
+  p.row_info = d->row_info; p.peers = d->peers; p.sgd_lr = d->sgd_lr; p.zero_tail = d->zero_tail;
+  p.group_m = d->group_m > 0 ? d->group_m : 16;
+  p.status = d->status;
+
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (d->group_mode == 0) {
+    if (d->a_mn_major) return bad("M-grouped GEMM takes a K-major A (token rows)");
+    if (d->K % 8) return bad("K must be a multiple of 8");
+    if (d->epilogue == FL_EPI_WGRAD) return bad("WGRAD epilogue needs group_mode 1");
+    if ((d->epilogue == FL_EPI_SWIGLU) && (d->N % 256)) return bad("SWIGLU needs N % 256 == 0");
+    if ((d->epilogue == FL_EPI_DSWIGLU) && (d->N % 128)) return bad("DSWIGLU needs N % 128 == 0");
+    rc = make_map(&tmA, d->A, d->K, d->cap, d->num_groups, d->lda, d->gsa, 64, BM);
+    if (rc) return rc;
+    if (!d->b_mn_major) rc = make_map(&tmB, d->B, d->K, d->N, d->num_groups, d->ldb, d->gsb, 64, BN);
+    else rc = make_map(&tmB, d->B, d->N, d->K, d->num_groups, d->ldb, d->gsb, 64, 64);
+    if (rc) return rc;
+  } else {
+    if (!d->a_mn_major || !d->b_mn_major) return bad("K-grouped GEMM takes MN-major A and B (token-major buffers)");
+    if (d->epilogue != FL_EPI_WGRAD) return bad("K-grouped GEMM supports the WGRAD epilogue only");
+    if (d->M % 8) return bad("M must be a multiple of 8");
+    rc = make_map(&tmA, d->A, d->M, d->cap, d->num_groups, d->lda, d->gsa, 64, 64);
+    if (rc) return rc;
+    rc = make_map(&tmB, d->B, d->N, d->cap, d->num_groups, d->ldb, d->gsb, 64, 64);
+    if (rc) return rc;
+  }
+
+  static int num_sms = 0;
+  static bool attr_set = false;
+  if (!attr_set) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  int grid = num_sms;
+  if (d->max_ctas > 0 && d->max_ctas < grid) grid = d->max_ctas;
+  grouped_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return (int)cudaGetLastError();
+}

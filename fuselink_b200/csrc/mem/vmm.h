@@ -1,0 +1,64 @@
+// cuMem (CUDA virtual memory management) layer: regions made of physical slabs that can be exported to
+// other processes, mapped by every peer GPU, aliased, and re-homed onto another GPU without changing
+// their virtual address.
+//
+// What it answers in the reference:
+//   * FuseLinkMemRegionInit (src/fuselink.cc:4-59): per-GPU physical allocations + alias VAs, then the
+//     ORIGINAL VA of a buffer is re-mapped onto memory of a relay GPU        -> fl_vmm_adopt + fl_vmm_remap_slab
+//   * MemRemap / CreateMem with its "Remap time" log (src/plugin.cc:1106-1165) -> fl_vmm_remap_slab(usec)
+//   * the 2 MiB slab pool of src/cumem.cu (register/remap/free/ptr2dev/usage)  -> slabs of a region, fl_vmm_ptr2dev,
+//     fl_vmm_usage
+// and what it adds: export/import of the slabs as POSIX fds so that every rank's buffers are addressable
+// from every GPU of the box (the symmetric heap the device kernels store into).
+//
+// The driver is reached through a function table loaded with dlopen, so this file builds and loads on a
+// machine without a GPU.  A second table backed by memfd + mmap ("fake driver") gives the same aliasing
+// semantics on the CPU and is what the CPU tests run against.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct FlVmmRegion FlVmmRegion;
+
+// backend: 0 = CUDA driver, 1 = fake (memfd/mmap).  Returns 0 on success.
+int fl_vmm_init(int backend);
+int fl_vmm_backend(void);
+const char* fl_vmm_last_error(void);
+
+int fl_vmm_granularity(int device, size_t* out);
+// `size` is rounded up to a whole number of slabs; slab_bytes == 0 means one slab; slab_bytes is rounded up
+// to the allocation granularity.  The region is mapped read/write for `device`.
+FlVmmRegion* fl_vmm_create(int device, size_t size, size_t slab_bytes);
+// Take over an existing VMM allocation (for instance a staging buffer another library allocated with
+// cuMemCreate): the handle behind `ptr` is retained and the region can then be re-homed.
+FlVmmRegion* fl_vmm_adopt(void* ptr, size_t size, int owner_device);
+// Map slabs exported by another process (or another region) into a fresh VA range, RW for `device`.
+FlVmmRegion* fl_vmm_import(int device, const int* fds, int nslabs, size_t slab_bytes);
+// A second VA range over the same physical slabs (the reference's per-GPU alias addresses).
+FlVmmRegion* fl_vmm_alias(FlVmmRegion* r, int device);
+void fl_vmm_destroy(FlVmmRegion* r);
+
+void* fl_vmm_ptr(const FlVmmRegion* r);
+size_t fl_vmm_size(const FlVmmRegion* r);
+size_t fl_vmm_slab_bytes(const FlVmmRegion* r);
+int fl_vmm_num_slabs(const FlVmmRegion* r);
+int fl_vmm_slab_device(const FlVmmRegion* r, int slab);
+int fl_vmm_export_fd(FlVmmRegion* r, int slab, int* fd_out);
+int fl_vmm_grant(FlVmmRegion* r, int device);
+// Back slab `slab` with new physical memory on `target_device`, keeping the virtual address.  With
+// `keep_contents` the bytes are carried over.  `access_devices`/`n_access` list the GPUs that get RW access
+// to the new mapping (the reference opens it to the source GPU only, src/fuselink.cc:52-56).
+int fl_vmm_remap_slab(FlVmmRegion* r, int slab, int target_device, int keep_contents, const int* access_devices,
+                      int n_access, long* usec_out);
+// Which device backs the slab that contains ptr (-1 if ptr is not inside a known region).
+int fl_vmm_ptr2dev(const void* ptr);
+// Bytes of physical memory this layer currently holds on `device`.
+size_t fl_vmm_usage(int device);
+
+#ifdef __cplusplus
+}
+#endif

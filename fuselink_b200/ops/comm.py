@@ -1,0 +1,208 @@
+"""Point-to-point, striped-relay and all-to-all transfers over the symmetric heap.
+
+All transfers are one launch of the chunked put kernel (csrc/kernels/comm_kernels.cu) on the sender plus,
+where the receiver has to know, one launch of the flag-wait kernel on the receiver.  Nothing here calls
+NCCL; NCCL is what these are benchmarked against (bench/p2p_sweep.py, bench/a2a_sweep.py).
+
+Completion accounting uses monotone arrival counters: the sender adds 1 per chunk to a word in the
+receiver's signal pad, both sides derive the number of chunks from the byte count with ``chunking()``, and
+the receiver waits for its running total.  No word is ever reset.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from .._ext import require_native
+from ..parallel.symm import SymmetricHeap, SymTensor
+from ..utils.env import knobs
+
+FLAG_NONE, FLAG_SEQ_PER_CHUNK, FLAG_COUNT = 0, 1, 2
+_NUM_SMS = 148
+
+
+def chunking(nbytes: int, chunk_bytes: Optional[int] = None) -> Tuple[int, int]:
+    """(chunk_bytes, number_of_chunks) both sides of a transfer agree on.
+
+    Large messages use the configured chunk (512 KiB, the reference's NCCL_P2P_NET_CHUNKSIZE setting); small
+    ones are cut so that a few hundred CTAs still share the work, never below 16 KiB.
+    """
+    cfg = chunk_bytes or knobs().chunk_bytes
+    if nbytes <= 0:
+        return cfg, 0
+    c = cfg
+    while c > 16 * 1024 and nbytes // c < 2 * _NUM_SMS:
+        c //= 2
+    c = max(16, (c + 15) // 16 * 16)
+    return c, (nbytes + c - 1) // c
+
+
+def _launch_shape(total_chunks: int, engine: str) -> Tuple[int, int]:
+    k = knobs()
+    if engine == "bulk":
+        ctas = k.copy_ctas or min(max(total_chunks, 1), 3 * _NUM_SMS)
+        return ctas, 32
+    ctas = k.copy_ctas or min(max(total_chunks, 1), 2 * _NUM_SMS)
+    return ctas, 512
+
+
+class Channel:
+    """A set of arrival counters (one per source rank) plus the running totals both sides keep."""
+
+    def __init__(self, heap: SymmetricHeap, name: str, engine: Optional[str] = None):
+        self.heap, self.name = heap, name
+        self.C = require_native()
+        self.slot0 = heap.signal_slots(f"chan:{name}", heap.world)
+        self.expected = [0] * heap.world
+        self.engine = engine or knobs().copy_engine
+
+    # -- sender ------------------------------------------------------------------------------------
+    def put(self, src: torch.Tensor, dst_rank: int, dst_offset: int, nbytes: Optional[int] = None,
+            chunk_bytes: Optional[int] = None) -> int:
+        """Copy ``nbytes`` of the local tensor ``src`` to byte ``dst_offset`` of rank ``dst_rank``'s region and
+        bump that rank's arrival counter for this source.  Returns the number of chunks signalled."""
+        nbytes = src.numel() * src.element_size() if nbytes is None else nbytes
+        cb, n = chunking(nbytes, chunk_bytes)
+        if n == 0:
+            return 0
+        seg = (src.data_ptr(), self.heap.addr(dst_offset, dst_rank), nbytes,
+               self.heap.sig_addr(self.slot0 + self.heap.rank, dst_rank), FLAG_COUNT, 0)
+        ctas, threads = _launch_shape(n, self.engine)
+        self.C.put_chunks([seg], cb, 0, self.engine == "bulk", ctas, threads, self.heap.status_addr)
+        return n
+
+    def put_many(self, items: Sequence[Tuple[int, int, int, int]], chunk_bytes: int) -> None:
+        """items: (src_addr, dst_rank, dst_offset, nbytes); one launch, at most 8 items."""
+        segs = []
+        total = 0
+        for src_addr, dst_rank, dst_off, nbytes in items:
+            if nbytes <= 0:
+                continue
+            segs.append((src_addr, self.heap.addr(dst_off, dst_rank), nbytes,
+                         self.heap.sig_addr(self.slot0 + self.heap.rank, dst_rank), FLAG_COUNT, 0))
+            total += (nbytes + chunk_bytes - 1) // chunk_bytes
+        if not segs:
+            return
+        ctas, threads = _launch_shape(total, self.engine)
+        self.C.put_chunks(segs, chunk_bytes, 0, self.engine == "bulk", ctas, threads, self.heap.status_addr)
+
+    # -- receiver ----------------------------------------------------------------------------------
+    def expect(self, src_rank: int, nbytes: int, chunk_bytes: Optional[int] = None) -> None:
+        _, n = chunking(nbytes, chunk_bytes)
+        self.expected[src_rank] += n
+
+    def expect_chunks(self, src_rank: int, n: int) -> None:
+        self.expected[src_rank] += n
+
+    def wait(self, src_ranks: Optional[Sequence[int]] = None) -> None:
+        """Enqueue a wait (on the current stream) until everything announced with expect() has arrived."""
+        ranks = range(self.heap.world) if src_ranks is None else src_ranks
+        flags = [(self.heap.sig_addr(self.slot0 + r), self.expected[r] & 0xFFFFFFFF) for r in ranks if self.expected[r] > 0]
+        for i in range(0, len(flags), 16):
+            self.C.wait_flags(flags[i:i + 16], self.heap.status_addr)
+
+
+def barrier(heap: SymmetricHeap, name: str = "barrier", signal: bool = True, wait: bool = True) -> None:
+    """Device-side barrier over all ranks of the heap (one tiny kernel on the current stream)."""
+    C = require_native()
+    slot0 = heap.signal_slots(f"bar:{name}", heap.world)
+    if signal:
+        heap._state.setdefault("barseq", {})
+        key = (name, heap.rank)
+        heap._state["barseq"][key] = heap._state["barseq"].get(key, 0) + 1
+    seq = heap._state.get("barseq", {}).get((name, heap.rank), 0)
+    C.barrier(heap.pads(), slot0, heap.rank, heap.world, seq, signal, wait, heap.status_addr)
+
+
+def all_to_all(chan: Channel, send: torch.Tensor, recv: SymTensor, wait: bool = True) -> None:
+    """Uniform all-to-all: ``send`` is [world, n] on this rank, block p goes to rank p's ``recv[rank]``.
+
+    One launch pushes all blocks (segment p -> peer p); with ``wait`` the call also enqueues the wait for the
+    blocks of every other rank.
+    """
+    heap = chan.heap
+    W = heap.world
+    assert send.shape[0] == W and send.is_contiguous()
+    per = send[0].numel() * send.element_size()
+    cb, n = chunking(per)
+    items = []
+    for k in range(W):
+        p = (heap.rank + k) % W   # start with the own block, then walk the ring so peers are hit evenly
+        items.append((send[p].data_ptr(), p, recv.offset + heap.rank * per, per))
+    chan.put_many(items, cb)
+    for r in range(W):
+        chan.expect_chunks(r, n)
+    if wait:
+        chan.wait()
+
+
+def all_to_all_v(chan: Channel, send: torch.Tensor, send_offsets: Sequence[int], send_bytes: Sequence[int],
+                 recv: SymTensor, dst_offsets: Sequence[int], recv_bytes: Sequence[int], wait: bool = True) -> None:
+    """Variable all-to-all in bytes.  ``dst_offsets[p]`` is where this rank's block lands inside rank p's ``recv``;
+    ``recv_bytes[r]`` is what rank r sends here (both known from a prior size exchange)."""
+    heap = chan.heap
+    cb = knobs().chunk_bytes
+    base = send.data_ptr()
+    items = [(base + send_offsets[p], p, recv.offset + dst_offsets[p], send_bytes[p]) for p in range(heap.world)]
+    chan.put_many(items, cb)
+    for r in range(heap.world):
+        chan.expect_chunks(r, (recv_bytes[r] + cb - 1) // cb)
+    if wait:
+        chan.wait()
+
+
+class StripedP2P:
+    """One logical src -> dst transfer striped over the direct path and idle relay GPUs.
+
+    Collective over the heap: every rank calls ``transfer`` with the same arguments; the source pushes each
+    stripe (stripe 0 straight to the destination, stripe i into relay i's staging buffer, one flag per
+    chunk), each relay forwards its stripe chunk by chunk as the flags appear, the destination waits for its
+    arrival counter.  This is the reference's multi-path idea (a channel's buffer lives on a relay GPU,
+    src/plugin.cc:1201, src/fuselink.cc:43-56) with explicit stripes instead of per-channel VA remaps.
+    """
+
+    def __init__(self, heap: SymmetricHeap, name: str, staging_bytes: int, engine: Optional[str] = None):
+        self.heap = heap
+        self.C = require_native()
+        self.engine = engine or knobs().copy_engine
+        self.chunk = knobs().chunk_bytes
+        self.staging = heap.alloc_tensor([staging_bytes], torch.uint8)
+        self.max_chunks = (staging_bytes + self.chunk - 1) // self.chunk
+        self.chunk_flags = heap.signal_slots(f"relay:{name}:chunks", self.max_chunks)
+        self.arrive = heap.signal_slots(f"relay:{name}:arrive", 1)
+        self.seq = 0
+        self.arrived_expected = 0
+
+    def transfer(self, src_rank: int, dst_rank: int, src: Optional[torch.Tensor], dst: SymTensor, nbytes: int,
+                 stripes: Sequence[Tuple[int, int, int]]) -> None:
+        """stripes: (path, offset, bytes) as produced by the selector; path == dst_rank is the direct stripe."""
+        heap = self.heap
+        self.seq += 1
+        cb = self.chunk
+        me = heap.rank
+        total_chunks = sum((b + cb - 1) // cb for _, _, b in stripes if b > 0)
+        if me == src_rank:
+            segs = []
+            for path, off, b in stripes:
+                if b <= 0:
+                    continue
+                if path == dst_rank:
+                    segs.append((src.data_ptr() + off, dst.addr(dst_rank) + off, b,
+                                 heap.sig_addr(self.arrive, dst_rank), FLAG_COUNT, 0))
+                else:
+                    assert b <= self.staging.shape[0], "stripe larger than the relay staging buffer"
+                    segs.append((src.data_ptr() + off, self.staging.addr(path), b,
+                                 heap.sig_addr(self.chunk_flags, path), FLAG_SEQ_PER_CHUNK, 0))
+            ctas, threads = _launch_shape(total_chunks, self.engine)
+            self.C.put_chunks(segs, cb, self.seq, self.engine == "bulk", ctas, threads, heap.status_addr)
+        for path, off, b in stripes:
+            if path == me and me != dst_rank and me != src_rank and b > 0:
+                seg = (self.staging.addr(), dst.addr(dst_rank) + off, b, heap.sig_addr(self.arrive, dst_rank),
+                       FLAG_COUNT, heap.sig_addr(self.chunk_flags))
+                n = (b + cb - 1) // cb
+                ctas, threads = _launch_shape(n, self.engine)
+                self.C.put_chunks([seg], cb, self.seq, self.engine == "bulk", ctas, threads, heap.status_addr)
+        if me == dst_rank:
+            self.arrived_expected += total_chunks
+            self.C.wait_flags([(heap.sig_addr(self.arrive), self.arrived_expected & 0xFFFFFFFF)], heap.status_addr)

@@ -1,0 +1,78 @@
+"""Python entry points of the tcgen05 grouped GEMM (csrc/kernels/grouped_gemm.cu)."""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .._ext import require_native
+
+EPI_STORE, EPI_SWIGLU, EPI_SCATTER, EPI_DSWIGLU, EPI_WGRAD = 0, 1, 2, 3, 4
+
+
+def _status_tensor(status):
+    return status
+
+
+def grouped_gemm_rows(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.Tensor], cap: int, *,
+                      b_mn_major: bool = False, epilogue: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+                      gu: Optional[torch.Tensor] = None, dgu: Optional[torch.Tensor] = None,
+                      row_info: Optional[torch.Tensor] = None, peers: Optional[List[int]] = None, ldc: Optional[int] = None,
+                      zero_tail: bool = False, group_m: int = 16, max_ctas: int = 0,
+                      status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """M-grouped GEMM: for each group g, ``C_g = A_g @ B_g^T`` over the first counts[g] rows of A_g.
+
+    a: [G*cap, K] bf16 token buffer (group g owns rows [g*cap, (g+1)*cap)).
+    b: [G, N, K] (K-major, the nn.Linear layout) or, with ``b_mn_major``, [G, K, N].
+    """
+    C = require_native()
+    G = b.shape[0]
+    K = a.shape[1]
+    N = b.shape[2] if b_mn_major else b.shape[1]
+    assert a.shape[0] == G * cap and a.is_contiguous() and b.is_contiguous()
+    assert (b.shape[1] if b_mn_major else b.shape[2]) == K
+    if epilogue == EPI_STORE and out is None:
+        out = torch.empty(G * cap, N, dtype=torch.bfloat16, device=a.device)
+    if epilogue == EPI_SWIGLU and out is None:
+        out = torch.empty(G * cap, N // 2, dtype=torch.bfloat16, device=a.device)
+    if ldc is None:
+        ldc = out.shape[1] if out is not None else N
+    gsc = cap * ldc
+    ldb = N if b_mn_major else K
+    C.grouped_gemm(0, G, cap, 0, N, K, counts, a, False, K, cap * K, b, b_mn_major, ldb, b.shape[1] * b.shape[2],
+                   epilogue, out, ldc, gsc, gu if gu is not None else None, gu.shape[1] if gu is not None else 0, dgu,
+                   row_info, peers or [], 0.0, zero_tail, group_m, max_ctas, status)
+    return out
+
+
+def grouped_gemm_wgrad(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.Tensor], cap: int, G: int, *,
+                       out: Optional[torch.Tensor] = None, sgd_lr: float = 0.0, group_m: int = 16, max_ctas: int = 0,
+                       status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """K-grouped GEMM: ``C_g[M, N] = A_g^T @ B_g`` with A_g, B_g the first counts[g] rows of group g in the
+    token-major buffers a: [G*cap, M], b: [G*cap, N].  With ``sgd_lr`` the result is applied to ``out`` in place
+    (``out -= lr * C``) instead of being stored."""
+    C = require_native()
+    M, N = a.shape[1], b.shape[1]
+    assert a.shape[0] == G * cap and b.shape[0] == G * cap and a.is_contiguous() and b.is_contiguous()
+    if out is None:
+        assert sgd_lr == 0.0
+        out = torch.empty(G, M, N, dtype=torch.bfloat16, device=a.device)
+    C.grouped_gemm(1, G, cap, M, N, 0, counts, a, True, M, cap * M, b, True, N, cap * N, EPI_WGRAD, out, N, M * N,
+                   None, 0, None, None, [], sgd_lr, False, group_m, max_ctas, status)
+    return out
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """[.., F, H] gate and up projections -> [.., 2F, H] with rows in blocks [128 gate | 128 up], the layout
+    the SWIGLU epilogue expects (one 256-wide accumulator tile holds matching gate and up columns)."""
+    *lead, F, H = w_gate.shape
+    assert F % block == 0
+    g = w_gate.reshape(*lead, F // block, 1, block, H)
+    u = w_up.reshape(*lead, F // block, 1, block, H)
+    return torch.cat([g, u], dim=-3).reshape(*lead, 2 * F, H).contiguous()
+
+
+def deinterleave_gate_up(w13: torch.Tensor, block: int = 128):
+    *lead, F2, H = w13.shape
+    v = w13.reshape(*lead, F2 // (2 * block), 2, block, H)
+    return v[..., 0, :, :].reshape(*lead, F2 // 2, H), v[..., 1, :, :].reshape(*lead, F2 // 2, H)

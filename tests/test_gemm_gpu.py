@@ -1,0 +1,197 @@
+"""tcgen05 grouped GEMM against a plain fp32 PyTorch restatement (small shapes, every operand layout and
+every fused epilogue)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _status():
+    return torch.zeros(8, dtype=torch.int32, device="cuda")
+
+
+def _check_status(st):
+    v = st.cpu().tolist()
+    assert v[0] == 0, f"kernel reported status {v}"
+
+
+def _close(got, ref, tol=2e-2):
+    err = (got.float() - ref).abs().max().item()
+    den = ref.abs().max().item() + 1e-6
+    assert err / den < tol, f"max abs err {err} vs ref max {den}"
+
+
+@pytest.mark.parametrize("K", [64, 192, 136, 1024])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_rows_store(K, b_mn):
+    from fuselink_b200.ops import gemm
+    G, cap, N = 3, 256, 512
+    counts = torch.tensor([200, 0, 129], dtype=torch.int32, device="cuda")
+    a = _mk([G * cap, K], seed=1)
+    w = _mk([G, N, K], 0.1, seed=2)            # logical B_g[N, K]
+    b = w.transpose(1, 2).contiguous() if b_mn else w
+    st = _status()
+    out = torch.full((G * cap, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    gemm.grouped_gemm_rows(a, b, counts, cap, b_mn_major=b_mn, out=out, zero_tail=True, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    for g in range(G):
+        c = int(counts[g])
+        ref = a[g * cap:g * cap + c].float() @ w[g].float().t()
+        _close(out[g * cap:g * cap + c], ref)
+        tail_end = min((c + 127) // 128 * 128, cap)
+        assert (out[g * cap + c:g * cap + tail_end] == 0).all(), "tail rows must be zeroed"
+        assert (out[g * cap + tail_end:(g + 1) * cap] == 7.0).all(), "rows past the tail must be untouched"
+
+
+def test_rows_many_tiles_multi_cta_order():
+    from fuselink_b200.ops import gemm
+    G, cap, N, K = 2, 1024, 1024, 512
+    counts = torch.tensor([1024, 700], dtype=torch.int32, device="cuda")
+    a = _mk([G * cap, K], seed=3)
+    w = _mk([G, N, K], 0.05, seed=4)
+    st = _status()
+    out = gemm.grouped_gemm_rows(a, w, counts, cap, status=st, group_m=4)
+    torch.cuda.synchronize()
+    _check_status(st)
+    for g in range(G):
+        c = int(counts[g])
+        _close(out[g * cap:g * cap + c], a[g * cap:g * cap + c].float() @ w[g].float().t())
+
+
+def test_wgrad_and_fused_sgd():
+    from fuselink_b200.ops import gemm
+    G, cap, M, N = 3, 256, 256, 512
+    counts_l = [200, 0, 129]
+    counts = torch.tensor(counts_l, dtype=torch.int32, device="cuda")
+    a = _mk([G * cap, M], seed=5)
+    b = _mk([G * cap, N], seed=6)
+    for g, c in enumerate(counts_l):           # rows past the count are zero up to the 128-row tile edge
+        a[g * cap + c:(g + 1) * cap] = 0
+        b[g * cap + c:g * cap + (c + 127) // 128 * 128] = 0
+    st = _status()
+    dw = gemm.grouped_gemm_wgrad(a, b, counts, cap, G, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    refs = []
+    for g, c in enumerate(counts_l):
+        ref = a[g * cap:g * cap + c].float().t() @ b[g * cap:g * cap + c].float()
+        refs.append(ref)
+        if c == 0:
+            assert (dw[g] == 0).all()
+        else:
+            _close(dw[g], ref)
+    w = _mk([G, M, N], seed=7)
+    w0 = w.clone()
+    gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=w, sgd_lr=0.01, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    for g in range(G):
+        _close(w[g], w0[g].float() - 0.01 * refs[g], tol=1e-2)
+
+
+def test_swiglu_and_backward_epilogues():
+    from fuselink_b200.ops import gemm
+    import torch.nn.functional as F
+    G, cap, H, Fd = 2, 256, 256, 512
+    counts_l = [256, 77]
+    counts = torch.tensor(counts_l, dtype=torch.int32, device="cuda")
+    x = _mk([G * cap, H], seed=8)
+    wg = _mk([G, Fd, H], 0.1, seed=9)
+    wu = _mk([G, Fd, H], 0.1, seed=10)
+    w13 = gemm.interleave_gate_up(wg, wu)
+    g2, u2 = gemm.deinterleave_gate_up(w13)
+    assert torch.equal(g2, wg) and torch.equal(u2, wu)
+    st = _status()
+    gu = torch.empty(G * cap, 2 * Fd, dtype=torch.bfloat16, device="cuda")
+    act = gemm.grouped_gemm_rows(x, w13, counts, cap, epilogue=gemm.EPI_SWIGLU, gu=gu, zero_tail=True, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    dact = _mk([G * cap, Fd], seed=11)
+    for g, c in enumerate(counts_l):
+        xs = x[g * cap:g * cap + c].float()
+        gate, up = xs @ wg[g].float().t(), xs @ wu[g].float().t()
+        _close(act[g * cap:g * cap + c], F.silu(gate) * up)
+        gg, uu = gemm.deinterleave_gate_up(gu[g * cap:g * cap + c].t().contiguous().unsqueeze(0))
+        _close(gg[0].t(), gate)
+        _close(uu[0].t(), up)
+    # DSWIGLU: accumulator = dAct = dY @ W2 with W2 given as [G, K=H2, N=Fd] (MN-major B)
+    H2 = 128
+    dy = _mk([G * cap, H2], seed=12)
+    w2 = _mk([G, H2, Fd], 0.1, seed=13)        # nn.Linear layout of the down projection: [out=H2, in=Fd]
+    dgu = torch.zeros_like(gu)
+    gemm.grouped_gemm_rows(dy, w2, counts, cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=gu, dgu=dgu,
+                           zero_tail=True, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    for g, c in enumerate(counts_l):
+        da = dy[g * cap:g * cap + c].float() @ w2[g].float()
+        gsl = gu[g * cap:g * cap + c].float()
+        gate, up = gemm.deinterleave_gate_up(gsl.t().contiguous().unsqueeze(0))
+        gate, up = gate[0].t(), up[0].t()
+        sg = torch.sigmoid(gate)
+        ref_dg = da * up * (sg * (1 + gate * (1 - sg)))
+        ref_du = da * gate * sg
+        dg, du = gemm.deinterleave_gate_up(dgu[g * cap:g * cap + c].t().contiguous().unsqueeze(0))
+        _close(dg[0].t(), ref_dg)
+        _close(du[0].t(), ref_du)
+
+
+def test_scatter_epilogue_to_peer_slots():
+    from fuselink_b200.ops import gemm
+    G, cap, N, K, world = 2, 128, 256, 128, 3
+    counts_l = [128, 50]
+    counts = torch.tensor(counts_l, dtype=torch.int32, device="cuda")
+    a = _mk([G * cap, K], seed=14)
+    w = _mk([G, N, K], 0.1, seed=15)
+    nslots = 200
+    bufs = [torch.zeros(nslots, N, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    gen = torch.Generator().manual_seed(0)
+    perm = torch.randperm(world * nslots, generator=gen)[:G * cap]
+    rank, slot = (perm // nslots).int(), (perm % nslots).int()
+    info = ((rank << 28) | slot).int().cuda()
+    st = _status()
+    gemm.grouped_gemm_rows(a, w, counts, cap, epilogue=gemm.EPI_SCATTER, row_info=info,
+                           peers=[b.data_ptr() for b in bufs], ldc=N, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    touched = torch.zeros(world, nslots, dtype=torch.bool)
+    for g, c in enumerate(counts_l):
+        ref = a[g * cap:g * cap + c].float() @ w[g].float().t()
+        for i in range(c):
+            r, s = int(rank[g * cap + i]), int(slot[g * cap + i])
+            touched[r, s] = True
+            _close(bufs[r][s], ref[i])
+    for r in range(world):
+        assert (bufs[r][~touched[r].cuda()] == 0).all(), "rows that were not routed must stay untouched"
+
+
+def test_throughput_smoke():
+    """Not a benchmark: checks that a production-sized launch completes and reports its rate."""
+    from fuselink_b200.ops import gemm
+    G, cap, N, K = 1, 8192, 4096, 4096
+    a = _mk([G * cap, K], seed=16)
+    w = _mk([G, N, K], 0.02, seed=17)
+    st = _status()
+    out = gemm.grouped_gemm_rows(a, w, None, cap, status=st)
+    torch.cuda.synchronize()
+    _check_status(st)
+    ref = a[:256].float() @ w[0].float().t()
+    _close(out[:256], ref)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        gemm.grouped_gemm_rows(a, w, None, cap, out=out, status=st)
+    e0.record()
+    for _ in range(10):
+        gemm.grouped_gemm_rows(a, w, None, cap, out=out, status=st)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 10
+    tf = 2.0 * cap * N * K / ms / 1e9
+    print(f"\n[gemm smoke] 8192x4096x4096 bf16: {ms:.3f} ms  {tf:.0f} TFLOP/s")
+    assert tf > 50, "tensor-core path is not being used"
