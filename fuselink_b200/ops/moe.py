@@ -1,0 +1,198 @@
+"""Expert-parallel MoE forward/backward built from the fused kernels.
+
+Per step and rank (E experts over W ranks, top-k routing, SwiGLU experts):
+
+forward   dispatch (permute + scatter into the expert owners' buffers over NVLink)  -> flag barrier ->
+          GEMM1 (tcgen05, SWIGLU epilogue) -> GEMM2 (tcgen05, SCATTER epilogue: rows return to the token's home
+          rank inside the GEMM) -> flag barrier -> weighted combine
+backward  dw = <dOut, y_k>; dispatch(w_k * dOut) to the slots chosen in forward -> barrier ->
+          dAct GEMM (B MN-major, DSWIGLU epilogue) -> wgrad W2, wgrad W13 (K-grouped, both operands MN-major)
+          -> dX GEMM (B MN-major, SCATTER epilogue) -> barrier -> sum over k
+
+There is no stand-alone all-to-all and no framework permute in either direction; NCCL is not called.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .._ext import require_native
+from ..parallel.symm import SymmetricHeap
+from . import gemm
+from .comm import barrier
+
+
+@dataclass
+class MoEConfig:
+    hidden: int = 4096
+    ffn: int = 14336
+    num_experts: int = 8
+    topk: int = 2
+    tokens: int = 8192          # tokens per rank and step
+
+
+class MoEWorkspace:
+    """Symmetric and local buffers of one MoE layer on one rank.  Sized for the worst case: every token of
+    every rank may choose the same expert, so each expert buffer holds tokens*world rows."""
+
+    def __init__(self, heap: SymmetricHeap, cfg: MoEConfig, name: str = "moe"):
+        self.heap, self.cfg, self.name = heap, cfg, name
+        W = heap.world
+        assert cfg.num_experts % W == 0, "experts must divide evenly over ranks"
+        self.epr = cfg.num_experts // W
+        self.cap = (cfg.tokens * W + 127) // 128 * 128
+        rows = self.epr * self.cap
+        H, F, T, k = cfg.hidden, cfg.ffn, cfg.tokens, cfg.topk
+        bf = torch.bfloat16
+        # symmetric (peers write into these)
+        self.xd = heap.alloc_tensor([rows, H], bf)        # dispatched tokens
+        self.dyd = heap.alloc_tensor([rows, H], bf)       # dispatched output gradients
+        self.info = heap.alloc_tensor([rows], torch.int32)
+        self.counts = heap.alloc_tensor([2, self.epr], torch.int32)
+        self.comb = heap.alloc_tensor([T * k, H], bf)     # expert outputs y_k returned to the home rank
+        self.dxs = heap.alloc_tensor([T * k, H], bf)      # input gradients returned to the home rank
+        dev = self.xd.local.device
+        # local
+        self.act = torch.empty(rows, F, dtype=bf, device=dev)
+        self.gu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
+        self.dgu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
+        self.local_count = torch.zeros(cfg.num_experts, dtype=torch.int32, device=dev)
+        self.base = torch.zeros(cfg.num_experts, dtype=torch.int32, device=dev)
+        self.pos = torch.zeros(T, k, dtype=torch.int32, device=dev)
+        self.slot = torch.zeros(T, k, dtype=torch.int32, device=dev)
+        self.parity = 0
+        self.step_parity = 0
+        self.launches = 0   # kernels of this library launched through this workspace (bench accounting)
+
+    def counts_now(self) -> torch.Tensor:
+        return self.counts.local[self.step_parity]
+
+
+def _dispatch(ws: MoEWorkspace, x: torch.Tensor, idx: torch.Tensor, scale: Optional[torch.Tensor], dst, reuse: bool):
+    C = require_native()
+    h, cfg = ws.heap, ws.cfg
+    C.moe_dispatch(x, idx, scale, cfg.num_experts, ws.epr, ws.cap, h.rank, h.world, ws.local_count, ws.base, ws.pos,
+                   ws.slot, ws.counts.peers(), ws.step_parity, dst.peers(), ws.info.peers(), reuse, h.status_addr)
+    ws.launches += 1 if reuse else 3
+
+
+def moe_forward_dispatch(ws: MoEWorkspace, x: torch.Tensor, topk_idx: torch.Tensor) -> None:
+    ws.step_parity = ws.parity
+    ws.parity ^= 1
+    _dispatch(ws, x, topk_idx, None, ws.xd, reuse=False)
+    barrier(ws.heap, ws.name + ":d", signal=True, wait=False)
+    ws.launches += 1
+
+
+def moe_forward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor) -> None:
+    C = require_native()
+    h = ws.heap
+    barrier(h, ws.name + ":d", signal=False, wait=True)
+    counts = ws.counts_now()
+    C.moe_zero_tail(ws.xd.addr(), counts.data_ptr(), ws.epr, ws.cap, ws.cfg.hidden)
+    st = h.status()
+    gemm.grouped_gemm_rows(ws.xd.local, w13, counts, ws.cap, epilogue=gemm.EPI_SWIGLU, out=ws.act, gu=ws.gu,
+                           zero_tail=True, status=st)
+    gemm.grouped_gemm_rows(ws.act, w2, counts, ws.cap, epilogue=gemm.EPI_SCATTER, row_info=ws.info.local,
+                           peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st)
+    barrier(h, ws.name + ":c", signal=True, wait=False)
+    ws.launches += 5
+
+
+def moe_forward_combine(ws: MoEWorkspace, topk_w: torch.Tensor) -> torch.Tensor:
+    C = require_native()
+    barrier(ws.heap, ws.name + ":c", signal=False, wait=True)
+    out = torch.empty(ws.cfg.tokens, ws.cfg.hidden, dtype=torch.bfloat16, device=topk_w.device)
+    C.moe_combine(ws.comb.local, topk_w, out, ws.cfg.topk)
+    ws.launches += 2
+    return out
+
+
+def moe_backward_dispatch(ws: MoEWorkspace, dout: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> torch.Tensor:
+    """Phase 1 of backward: gate-weight gradient and dispatch of w_k * dOut to the slots chosen in forward."""
+    C = require_native()
+    cfg = ws.cfg
+    dw = torch.empty(cfg.tokens, cfg.topk, dtype=torch.float32, device=dout.device)
+    C.moe_combine_dw(dout, ws.comb.local, dw, cfg.topk)
+    _dispatch(ws, dout, topk_idx, topk_w, ws.dyd, reuse=True)
+    barrier(ws.heap, ws.name + ":bd", signal=True, wait=False)
+    ws.launches += 2
+    return dw
+
+
+def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, sgd_lr: float = 0.0,
+                         need_dx: bool = True):
+    """Phase 2: expert-side GEMMs.  Returns (dw13, dw2), both None when ``sgd_lr`` fuses the update."""
+    C = require_native()
+    h, cfg = ws.heap, ws.cfg
+    barrier(h, ws.name + ":bd", signal=False, wait=True)
+    counts = ws.counts_now()
+    C.moe_zero_tail(ws.dyd.addr(), counts.data_ptr(), ws.epr, ws.cap, cfg.hidden)
+    st = h.status()
+    # dAct = dY @ W2 ; the epilogue turns it into dGate/dUp using the saved gate/up
+    gemm.grouped_gemm_rows(ws.dyd.local, w2, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=ws.gu,
+                           dgu=ws.dgu, zero_tail=True, status=st)
+    # dX rows go home first (needs the pre-update W13), then the weight gradients
+    if need_dx:
+        gemm.grouped_gemm_rows(ws.dgu, w13, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER,
+                               row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st)
+    if sgd_lr:
+        gemm.grouped_gemm_wgrad(ws.dyd.local, ws.act, counts, ws.cap, ws.epr, out=w2, sgd_lr=sgd_lr, status=st)
+        gemm.grouped_gemm_wgrad(ws.dgu, ws.xd.local, counts, ws.cap, ws.epr, out=w13, sgd_lr=sgd_lr, status=st)
+        dw2 = dw13 = None
+    else:
+        dw2 = gemm.grouped_gemm_wgrad(ws.dyd.local, ws.act, counts, ws.cap, ws.epr, status=st)
+        dw13 = gemm.grouped_gemm_wgrad(ws.dgu, ws.xd.local, counts, ws.cap, ws.epr, status=st)
+    # every read of the buffers peers will overwrite next step is enqueued before this signal
+    barrier(h, ws.name + ":bx", signal=True, wait=False)
+    ws.launches += 6 + (1 if need_dx else 0)
+    return dw13, dw2
+
+
+def moe_backward_finish(ws: MoEWorkspace, need_dx: bool = True) -> Optional[torch.Tensor]:
+    """Phase 3: wait for the returned input-gradient rows and sum them over k."""
+    C = require_native()
+    cfg = ws.cfg
+    barrier(ws.heap, ws.name + ":bx", signal=False, wait=True)
+    ws.launches += 1
+    if not need_dx:
+        return None
+    dx = torch.empty(cfg.tokens, cfg.hidden, dtype=torch.bfloat16, device=ws.dxs.local.device)
+    C.moe_combine(ws.dxs.local, None, dx, cfg.topk)
+    ws.launches += 1
+    return dx
+
+
+def moe_backward(ws: MoEWorkspace, dout: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
+                 w13: torch.Tensor, w2: torch.Tensor, sgd_lr: float = 0.0, need_dx: bool = True):
+    """Returns (dx, dtopk_w, dw13, dw2).  With ``sgd_lr`` the expert weights are updated in place by the wgrad
+    kernels' epilogue and dw13/dw2 are None."""
+    dw = moe_backward_dispatch(ws, dout.contiguous(), topk_idx, topk_w)
+    dw13, dw2 = moe_backward_experts(ws, w13, w2, sgd_lr, need_dx)
+    dx = moe_backward_finish(ws, need_dx)
+    return dx, dw, dw13, dw2
+
+
+class MoEFunction(torch.autograd.Function):
+    """autograd node: (x, topk_w) are differentiable inputs, (w13, w2) differentiable parameters."""
+
+    @staticmethod
+    def forward(ctx, x, topk_w, topk_idx, w13, w2, ws: MoEWorkspace, sgd_lr: float):
+        x = x.contiguous()
+        topk_w = topk_w.contiguous().float()
+        topk_idx = topk_idx.contiguous().int()
+        moe_forward_dispatch(ws, x, topk_idx)
+        moe_forward_experts(ws, w13, w2)
+        out = moe_forward_combine(ws, topk_w)
+        ctx.ws, ctx.sgd_lr = ws, sgd_lr
+        ctx.save_for_backward(topk_w, topk_idx, w13, w2)
+        ctx.need_dx = x.requires_grad
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        topk_w, topk_idx, w13, w2 = ctx.saved_tensors
+        dx, dw, dw13, dw2 = moe_backward(ctx.ws, dout, topk_idx, topk_w, w13, w2, ctx.sgd_lr, need_dx=True)
+        return dx, dw, None, dw13, dw2, None, None
