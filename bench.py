@@ -1,0 +1,254 @@
+#!/usr/bin/env python
+"""Headline benchmark: MoE expert-parallel layer, forward + backward + SGD update, tokens/s.
+
+Config (the MoE row of the baseline configs): hidden 4096, 8 experts (SwiGLU 4096 -> 14336 -> 4096), top-2
+routing, 8192 tokens per GPU, bf16, Zipf(1.2) router bias, random-init N(0, 0.02) weights, synthetic
+N(0, 1) activations.  Weak scaling: tokens per GPU fixed, the 8 experts are spread over the N GPUs.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 10 --warmup 3
+
+Prints ONE JSON line on rank 0.  ``value`` is device-timed (CUDA events, max over ranks) with inputs resident
+on the device; ``e2e`` is the same step driven through ``MoELayer`` with the host->device copy of each step's
+activations from pinned memory and the device->host read of the loss inside the timed region.
+
+``--impl reference`` reports that the reference cannot be run here; ``--impl nccl`` runs the stock
+PyTorch + NCCL formulation of the same step (framework permute, all_to_all_single, library GEMMs).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+REFERENCE_UNAVAILABLE = (
+    "reference is not installable (no setup.py/pyproject; Makefile needs the absent nccl/ submodule sources) "
+    "and its plugin refuses to initialise without RDMA verbs devices"
+)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thr = threading.Thread(target=self._read, daemon=True)
+            self.thr.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        rows = [s for t, s in self.samples if t0 <= t <= t1 + 0.1] or [s for _, s in self.samples[-3:]]
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            p = [x.strip() for x in r.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0])); mx.append(float(p[1])); power.append(float(p[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, p[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="fuselink", choices=["fuselink", "reference", "nccl"])
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=14336)
+    ap.add_argument("--experts", type=int, default=8)
+    ap.add_argument("--topk", type=int, default=2)
+    ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--zipf", type=float, default=1.2)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops.moe import MoEConfig
+
+    cfg = MoEConfig(hidden=args.hidden, ffn=args.ffn, num_experts=args.experts, topk=args.topk, tokens=args.tokens)
+    T, H = cfg.tokens, cfg.hidden
+
+    if args.impl == "fuselink":
+        from fuselink_b200.parallel.symm import SymmetricHeap
+
+        W = world
+        cap = (T * W + 127) // 128 * 128
+        rows = (cfg.num_experts // W) * cap
+        heap_bytes = 2 * rows * H * 2 + rows * 4 + 2 * T * cfg.topk * H * 2 + (64 << 20)
+        heap = SymmetricHeap.create(heap_bytes, device=local_rank)
+        layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr)
+        expert_params = []          # updated inside the wgrad kernels' epilogue
+    else:
+        from fuselink_b200.models.moe_baseline import BaselineMoELayer
+
+        heap = None
+        layer = BaselineMoELayer(cfg, rank, world, device=dev, zipf_s=args.zipf, seed=0)
+        expert_params = [layer.w13, layer.w2]
+    opt = torch.optim.SGD([layer.router] + expert_params, lr=args.lr)
+
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    n_inputs = 4
+    xs = [torch.randn(T, H, generator=gen, device=dev).to(torch.bfloat16) for _ in range(n_inputs)]
+
+    def step(x):
+        x = x.detach().requires_grad_(True)
+        out = layer(x)
+        loss = out.float().pow(2).mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def launches():
+        return layer.ws.launches if getattr(layer, "ws", None) is not None else 0
+
+    # ---------------------------------------------------------------- device-timed region
+    for i in range(args.warmup):
+        step(xs[i % n_inputs])
+    sync_all()
+    if heap is not None:
+        heap.check_status("warmup")
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    sync_all()
+    l0 = launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    e0.record()
+    for i in range(args.steps):
+        step(xs[i % n_inputs])
+    e1.record()
+    sync_all()
+    t_wall1 = time.time()
+    ms = e0.elapsed_time(e1)
+    n_launch = launches() - l0
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    if heap is not None:
+        heap.check_status("timed region")
+    tms = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    ms_per_step = ms / args.steps
+    value = world * T * args.steps / (ms / 1e3)
+
+    # ---------------------------------------------------------------- end-to-end region (public API)
+    e2e = None
+    if not args.no_e2e:
+        host = [torch.randn(T, H).to(torch.bfloat16).pin_memory() for _ in range(2)]
+        dbuf = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        for i in range(2):
+            dbuf.copy_(host[i % 2], non_blocking=True)
+            float(step(dbuf).item())
+        sync_all()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for i in range(args.steps):
+            dbuf.copy_(host[i % 2], non_blocking=True)     # this step's activations, pinned host -> device
+            loss_host = float(step(dbuf).item())            # the step's result, device -> host
+        f1.record()
+        sync_all()
+        ems = torch.tensor([f0.elapsed_time(f1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ems, op=dist.ReduceOp.MAX)
+        e2e = {"value": world * T * args.steps / (float(ems.item()) / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": 4, "last_loss": loss_host}
+        if heap is not None:
+            heap.check_status("e2e region")
+
+    if rank == 0:
+        flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
+        line = {
+            "metric": "MoE-EP tokens/s (fwd+bwd+SGD)", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": "MoE-EP layer: hidden 4096, 8 experts SwiGLU 4096-14336-4096, top-2, Zipf(1.2) router bias"
+                       if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else
+                       f"MoE-EP layer h{args.hidden} f{args.ffn} e{args.experts} k{args.topk}",
+                       "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T, "parallelism": f"ep{world}",
+                       "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
+                       "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
+            "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch,
+        }
+        print(json.dumps(line))
+    if heap is not None:
+        heap.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,113 @@
+"""MoE expert-parallel layer (the workload the reference runs through Megatron-DeepSpeed, .gitmodules:11-13).
+
+``MoELayer`` owns a router and this rank's experts.  On CUDA tensors the forward/backward are the fused
+kernels of ``ops/moe.py`` over the symmetric heap; on CPU tensors (multi-process tests over gloo) the same
+math runs as plain PyTorch with an all-gather of the tokens and a reduce-scatter of the outputs.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from ..ops import gemm, ref
+from ..ops.moe import MoEConfig, MoEFunction, MoEWorkspace
+from ..parallel.symm import SymmetricHeap
+
+
+def zipf_log_bias(num_experts: int, s: float = 1.2) -> torch.Tensor:
+    """log of the Zipf(s) pmf over expert ranks 1..E; added to the router logits it skews the load."""
+    p = torch.arange(1, num_experts + 1, dtype=torch.float32).pow(-s)
+    return (p / p.sum()).log()
+
+
+class MoELayer(nn.Module):
+    def __init__(self, cfg: MoEConfig, heap: Optional[SymmetricHeap] = None, rank: int = 0, world: int = 1,
+                 device="cuda", zipf_s: Optional[float] = 1.2, seed: int = 0, fused_sgd_lr: float = 0.0,
+                 name: str = "moe"):
+        super().__init__()
+        self.cfg, self.rank, self.world = cfg, rank, world
+        assert cfg.num_experts % world == 0
+        self.epr = cfg.num_experts // world
+        self.fused_sgd_lr = fused_sgd_lr
+        g = torch.Generator().manual_seed(seed)
+        H, F, E = cfg.hidden, cfg.ffn, cfg.num_experts
+        self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16).to(device))
+        bias = zipf_log_bias(E, zipf_s) if zipf_s else torch.zeros(E)
+        self.register_buffer("router_bias", bias.to(device))
+        # this rank's experts only; every expert's init depends on (seed, global expert id), not on the layout
+        w13, w2 = [], []
+        for le in range(self.epr):
+            ge = torch.Generator().manual_seed(seed * 1000 + 17 + rank * self.epr + le)
+            wg = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
+            wu = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
+            wd = (torch.randn(H, F, generator=ge) * 0.02).to(torch.bfloat16)
+            w13.append(gemm.interleave_gate_up(wg, wu))
+            w2.append(wd)
+        self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr, 2F, H], gate/up interleaved by 128
+        self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr, H, F]
+        self.ws = MoEWorkspace(heap, cfg, name) if heap is not None else None
+
+    # -- routing ------------------------------------------------------------------------------------------
+    def route(self, x: torch.Tensor):
+        logits = (x @ self.router.t()).float() + self.router_bias
+        probs = torch.softmax(logits, dim=-1)
+        w, idx = torch.topk(probs, self.cfg.topk, dim=-1)
+        w = w / w.sum(dim=-1, keepdim=True)
+        return w, idx.int()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w, idx = self.route(x)
+        if x.is_cuda:
+            if self.ws is None:
+                raise RuntimeError("MoELayer on CUDA needs a SymmetricHeap (the fused kernels write peer memory)")
+            return MoEFunction.apply(x, w, idx, self.w13, self.w2, self.ws, self.fused_sgd_lr)
+        return self._forward_reference(x, w, idx)
+
+    # -- CPU / gloo path ----------------------------------------------------------------------------------
+    def _forward_reference(self, x, w, idx):
+        import torch.distributed as dist
+
+        wg, wu = gemm.deinterleave_gate_up(self.w13)
+        if self.world == 1:
+            return ref.moe_forward(x, idx, w, wg, wu, self.w2).to(x.dtype)
+        T = x.shape[0]
+        xs = [torch.empty_like(x) for _ in range(self.world)]
+        ws_ = [torch.empty_like(w) for _ in range(self.world)]
+        ids = [torch.empty_like(idx) for _ in range(self.world)]
+        dist.all_gather(xs, x.detach()); dist.all_gather(ws_, w.detach()); dist.all_gather(ids, idx)
+        xs[self.rank], ws_[self.rank] = x, w    # keep the autograd edge of the local shard
+        xa, wa, ia = torch.cat(xs), torch.cat(ws_), torch.cat(ids)
+        local = ia - self.rank * self.epr
+        local = torch.where((local >= 0) & (local < self.epr), local, torch.full_like(local, -1))
+        part = ref.moe_forward(xa, local, wa, wg, wu, self.w2)
+        parts = list(part.split(T))
+        out = torch.empty_like(parts[0])
+        dist.reduce_scatter(out, [p.detach().contiguous() for p in parts]) if dist.get_backend() != "gloo" else None
+        if dist.get_backend() == "gloo":
+            tot = part.detach().clone()
+            dist.all_reduce(tot)
+            out = tot.split(T)[self.rank]
+        return out.to(x.dtype)
+
+
+def smoke_step(device: str = "cuda:0", tokens: int = 512, hidden: int = 512, ffn: int = 1024) -> float:
+    """One tiny forward + backward + update of the MoE layer on one GPU (all experts local)."""
+    torch.cuda.set_device(device)
+    cfg = MoEConfig(hidden=hidden, ffn=ffn, num_experts=8, topk=2, tokens=tokens)
+    heap = SymmetricHeap.create(64 << 20, device=torch.cuda.current_device())
+    try:
+        layer = MoELayer(cfg, heap, 0, 1, device=device, fused_sgd_lr=0.01)
+        x = torch.randn(tokens, hidden, device=device).to(torch.bfloat16).requires_grad_(True)
+        out = layer(x)
+        loss = out.float().pow(2).mean()
+        loss.backward()
+        torch.cuda.synchronize()
+        heap.check_status("smoke")
+        assert x.grad is not None and torch.isfinite(x.grad.float()).all()
+        assert layer.router.grad is not None
+        return float(loss)
+    finally:
+        heap.close()

@@ -1,0 +1,83 @@
+"""The stock formulation of the MoE expert-parallel step, used as the measured baseline:
+framework permute (sort by expert) + ``all_to_all_single`` over NCCL + library GEMMs per expert + the mirror
+all-to-all, with autograd doing the backward and ``torch.optim.SGD`` the update.  None of this library's
+kernels run on this path."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops.moe import MoEConfig
+from .moe import zipf_log_bias
+
+
+class BaselineMoELayer(nn.Module):
+    def __init__(self, cfg: MoEConfig, rank: int = 0, world: int = 1, device="cuda", zipf_s=1.2, seed: int = 0):
+        super().__init__()
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self.epr = cfg.num_experts // world
+        g = torch.Generator().manual_seed(seed)
+        H, Fd, E = cfg.hidden, cfg.ffn, cfg.num_experts
+        self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16).to(device))
+        bias = zipf_log_bias(E, zipf_s) if zipf_s else torch.zeros(E)
+        self.register_buffer("router_bias", bias.to(device))
+        w13, w2 = [], []
+        for le in range(self.epr):
+            ge = torch.Generator().manual_seed(seed * 1000 + 17 + rank * self.epr + le)
+            wg = (torch.randn(Fd, H, generator=ge) * 0.02).to(torch.bfloat16)
+            wu = (torch.randn(Fd, H, generator=ge) * 0.02).to(torch.bfloat16)
+            wd = (torch.randn(H, Fd, generator=ge) * 0.02).to(torch.bfloat16)
+            w13.append(torch.cat([wg, wu], 0))
+            w2.append(wd)
+        self.w13 = nn.Parameter(torch.stack(w13).to(device))
+        self.w2 = nn.Parameter(torch.stack(w2).to(device))
+
+    def forward(self, x):
+        cfg, W = self.cfg, self.world
+        T, k, E = x.shape[0], cfg.topk, cfg.num_experts
+        logits = (x @ self.router.t()).float() + self.router_bias
+        probs = torch.softmax(logits, -1)
+        w, idx = torch.topk(probs, k, -1)
+        w = w / w.sum(-1, keepdim=True)
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        tok = order // k
+        xp = x[tok]                                                # permute
+        cnt = torch.bincount(flat, minlength=E)
+        if W > 1:
+            import torch.distributed as dist
+            from torch.distributed.nn.functional import all_to_all_single
+
+            recv_cnt = torch.empty_like(cnt)
+            dist.all_to_all_single(recv_cnt, cnt)                  # [W, epr] counts from every rank
+            send_sizes = cnt.view(W, self.epr).sum(1).tolist()
+            recv_sizes = recv_cnt.view(W, self.epr).sum(1).tolist()
+            xr = all_to_all_single(torch.empty(sum(recv_sizes), x.shape[1], dtype=x.dtype, device=x.device), xp,
+                                   recv_sizes, send_sizes)
+            # received rows are grouped (src rank, local expert): regroup by expert
+            rc = recv_cnt.view(W, self.epr)
+            eid = torch.repeat_interleave(torch.arange(self.epr, device=x.device).repeat(W), rc.reshape(-1))
+            eorder = torch.argsort(eid, stable=True)
+            xe = xr[eorder]
+            ecnt = rc.sum(0).tolist()
+        else:
+            xe, ecnt = xp, cnt.tolist()
+        outs, o = [], 0
+        Fd = cfg.ffn
+        for e in range(self.epr):
+            xs = xe[o:o + ecnt[e]]
+            o += ecnt[e]
+            h = xs @ self.w13[e].t()
+            outs.append((F.silu(h[:, :Fd].float()) * h[:, Fd:].float()).to(x.dtype) @ self.w2[e].t())
+        ye = torch.cat(outs)
+        if W > 1:
+            inv = torch.empty_like(eorder)
+            inv[eorder] = torch.arange(eorder.numel(), device=x.device)
+            yr = ye[inv]
+            yp = all_to_all_single(torch.empty_like(xp), yr, send_sizes, recv_sizes)
+        else:
+            yp = ye
+        wflat = w.reshape(-1)[order].to(yp.dtype).unsqueeze(1)
+        out = torch.zeros_like(x).index_add_(0, tok, yp * wflat)   # un-permute + weighted combine
+        return out
