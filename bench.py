@@ -89,7 +89,7 @@ class ClockSampler:
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="fuselink", choices=["fuselink", "reference", "nccl"])
     ap.add_argument("--tokens", type=int, default=8192)

@@ -1,0 +1,49 @@
+// Path / NIC selection for the plugin: which device carries the next message of a channel.
+//
+// Reference: class FuseLinkConnManager (src/fuselink.h:68-314).  Intended behaviour there (most of it is
+// stubbed in the shipped code): the receiver periodically asks the idleness monitor for an idle NIC of
+// another group (refreshRxComm, :190-244), tells the sender through the receive descriptor, and the
+// sender "bids" for that NIC, falling back to its own when the bid fails (bidTxChannel, :153-161,
+// src/plugin.cc:1538-1547); the sender's availability mask travels back with the data
+// (src/plugin.cc:1441-1451).  The only rule live in the shipped code is dev = channelId % nNics.
+// This class implements the intended rules on top of the lock-free monitor, and keeps the channel-modulo
+// rule as the fallback when the monitor is off.
+#pragma once
+#include <stdint.h>
+#include "../monitor/monitor.h"
+
+namespace flnet {
+
+class ConnManager {
+ public:
+  ConnManager(int ndev, int priority_dev, bool use_monitor, const char* shm_name, int timeout_us);
+  ~ConnManager();
+  int ndev() const { return ndev_; }
+  int priority_dev() const { return priority_dev_; }
+  FlMonitor* monitor() { return mon_; }
+
+  // Receiver side: device that should carry the next message of `channel`.  `current` is the device in
+  // use (or -1); `tx_mask` is the sender's last advertised availability mask.  A new device is looked for
+  // only when `quiescent` (nothing posted is still incomplete), as the reference does every 8 completions
+  // when received == done (src/plugin.cc:1700-1716).
+  int refresh_rx(int channel, int own_dev, int current, uint64_t tx_mask, bool quiescent);
+  // Sender side: accept the receiver's proposal if that device is usable for tx, else fall back to own_dev.
+  int bid_tx(int channel, int own_dev, int proposed);
+  // Activity stamps (the "todo: update nic activities" of src/plugin.cc:1812).
+  void mark_tx(int dev, uint64_t bytes_posted);
+  void done_tx(int dev, uint64_t bytes);
+  void mark_rx(int dev, uint64_t bytes_posted);
+  void done_rx(int dev, uint64_t bytes);
+  // 64-bit mask of devices this process considers available for tx (bit set = idle or own)
+  uint64_t tx_mask(int own_dev);
+  void set_dead(int dev, bool dead);
+  uint64_t decisions() const { return decisions_; }
+  uint64_t fallbacks() const { return fallbacks_; }
+
+ private:
+  int ndev_, priority_dev_;
+  FlMonitor* mon_ = nullptr;
+  uint64_t decisions_ = 0, fallbacks_ = 0;
+};
+
+}  // namespace flnet

@@ -1,0 +1,215 @@
+// fl_net_harness: drives a ncclNet plugin the way NCCL's proxy thread does, without NCCL and without GPUs.
+//
+//   fl_net_harness <plugin.so> recv <handle-file> [options] <size> [<size> ...]
+//   fl_net_harness <plugin.so> send <handle-file> [options] <size> [<size> ...]
+//
+// The receiver listens, writes the 128-byte handle to <handle-file>, accepts, and receives every message
+// in chunks (--chunk, default 512 KiB) with at most --inflight (default 8) requests outstanding; the
+// sender mirrors it.  Payloads are fp32 uniform[-1,1] generated from --seed on both sides, so the receiver
+// can compare bit for bit without a side channel.  Exit code 0 = all messages identical.
+//
+// Options: --chunk N  --inflight N  --seed N  --dev N  --abi 6|7|8  --die-after-chunks N (sender exits
+// abruptly after N chunks: peer-failure test)  --expect-error (receiver: a transfer error is the
+// expected outcome; exit 0 if it is reported within the timeout, 3 if the transfer hangs or succeeds).
+#include <dlfcn.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <time.h>
+#include <unistd.h>
+
+#include <deque>
+#include <string>
+#include <vector>
+
+#include "nccl_net_abi.h"
+
+static uint64_t rng_state;
+static inline uint64_t next_u64() {  // xorshift64*
+  rng_state ^= rng_state >> 12;
+  rng_state ^= rng_state << 25;
+  rng_state ^= rng_state >> 27;
+  return rng_state * 2685821657736338717ull;
+}
+static void fill(std::vector<float>& v, uint64_t seed, size_t msg_index) {
+  rng_state = seed * 0x9E3779B97F4A7C15ull + msg_index * 0xD1B54A32D192ED03ull + 1;
+  for (auto& x : v) x = (float)((double)(next_u64() >> 11) / (double)(1ull << 53) * 2.0 - 1.0);
+}
+static double now_s() {
+  timespec ts;
+  clock_gettime(CLOCK_MONOTONIC, &ts);
+  return ts.tv_sec + ts.tv_nsec * 1e-9;
+}
+static void logger(ncclDebugLogLevel lvl, unsigned long, const char*, int, const char* fmt, ...) {
+  if (lvl != NCCL_LOG_WARN && !getenv("FL_HARNESS_VERBOSE")) return;
+  va_list ap;
+  va_start(ap, fmt);
+  vfprintf(stderr, fmt, ap);
+  va_end(ap);
+  fputc('\n', stderr);
+}
+
+// one calling convention over the three ABI versions
+struct Api {
+  int abi = 7;
+  ncclNet_v6_t* v6 = nullptr;
+  ncclNet_v7_t* v7 = nullptr;
+  ncclNet_v8_t* v8 = nullptr;
+#define PICK(f) (abi == 6 ? v6->f : abi == 7 ? v7->f : v8->f)
+  ncclResult_t init() { return PICK(init)(logger); }
+  ncclResult_t devices(int* n) { return PICK(devices)(n); }
+  ncclResult_t listen(int dev, void* h, void** lc) { return PICK(listen)(dev, h, lc); }
+  ncclResult_t connect(int dev, void* h, void** sc) {
+    if (abi == 6) return v6->connect(dev, h, sc);
+    ncclNetDeviceHandle_v7_t* dh = nullptr;
+    return abi == 7 ? v7->connect(dev, h, sc, &dh) : v8->connect(dev, h, sc, &dh);
+  }
+  ncclResult_t accept(void* lc, void** rc) {
+    if (abi == 6) return v6->accept(lc, rc);
+    ncclNetDeviceHandle_v7_t* dh = nullptr;
+    return abi == 7 ? v7->accept(lc, rc, &dh) : v8->accept(lc, rc, &dh);
+  }
+  ncclResult_t regMr(void* c, void* d, size_t s, void** mh) {
+    if (abi == 8) return v8->regMr(c, d, s, NCCL_PTR_HOST, mh);
+    return abi == 6 ? v6->regMr(c, d, (int)s, NCCL_PTR_HOST, mh) : v7->regMr(c, d, (int)s, NCCL_PTR_HOST, mh);
+  }
+  ncclResult_t deregMr(void* c, void* mh) { return PICK(deregMr)(c, mh); }
+  ncclResult_t isend(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(isend)(c, d, s, tag, mh, r); }
+  ncclResult_t irecv(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(irecv)(c, 1, &d, &s, &tag, &mh, r); }
+  ncclResult_t test(void* r, int* done, int* sz) { return PICK(test)(r, done, sz); }
+  ncclResult_t closeSend(void* c) { return PICK(closeSend)(c); }
+  ncclResult_t closeRecv(void* c) { return PICK(closeRecv)(c); }
+  ncclResult_t closeListen(void* c) { return PICK(closeListen)(c); }
+#undef PICK
+};
+
+int main(int argc, char** argv) {
+  if (argc < 5) {
+    fprintf(stderr, "usage: %s <plugin.so> send|recv <handle-file> [options] <size>...\n", argv[0]);
+    return 2;
+  }
+  const char* so = argv[1];
+  const bool is_send = !strcmp(argv[2], "send");
+  const std::string hfile = argv[3];
+  size_t chunk = 512 * 1024;
+  int inflight = 8, dev = 0, die_after = -1;
+  uint64_t seed = 0;
+  bool expect_error = false;
+  Api api;
+  std::vector<size_t> sizes;
+  for (int i = 4; i < argc; ++i) {
+    std::string a = argv[i];
+    auto val = [&]() { return strtoull(argv[++i], nullptr, 0); };
+    if (a == "--chunk") chunk = val();
+    else if (a == "--inflight") inflight = (int)val();
+    else if (a == "--seed") seed = val();
+    else if (a == "--dev") dev = (int)val();
+    else if (a == "--abi") api.abi = (int)val();
+    else if (a == "--die-after-chunks") die_after = (int)val();
+    else if (a == "--expect-error") expect_error = true;
+    else sizes.push_back(strtoull(a.c_str(), nullptr, 0));
+  }
+  void* lib = dlopen(so, RTLD_NOW);
+  if (!lib) { fprintf(stderr, "dlopen: %s\n", dlerror()); return 2; }
+  api.v6 = (ncclNet_v6_t*)dlsym(lib, "ncclNetPlugin_v6");
+  api.v7 = (ncclNet_v7_t*)dlsym(lib, "ncclNetPlugin_v7");
+  api.v8 = (ncclNet_v8_t*)dlsym(lib, "ncclNetPlugin_v8");
+  if (!api.v6 || !api.v7 || !api.v8) { fprintf(stderr, "plugin symbols missing\n"); return 2; }
+  if (strcmp(api.v7->name, "FuseLink")) { fprintf(stderr, "unexpected plugin name %s\n", api.v7->name); return 2; }
+  if (api.init() != ncclSuccess) { fprintf(stderr, "init failed\n"); return 2; }
+  int ndev = 0;
+  api.devices(&ndev);
+  if (dev >= ndev) { fprintf(stderr, "device %d of %d\n", dev, ndev); return 2; }
+
+  char handle[NCCL_NET_HANDLE_MAXSIZE];
+  void *lcomm = nullptr, *comm = nullptr;
+  const double t_limit = now_s() + 120.0;
+  if (!is_send) {
+    if (api.listen(dev, handle, &lcomm) != ncclSuccess) { fprintf(stderr, "listen failed\n"); return 2; }
+    std::string tmp = hfile + ".tmp";
+    FILE* f = fopen(tmp.c_str(), "wb");
+    fwrite(handle, 1, sizeof handle, f);
+    fclose(f);
+    rename(tmp.c_str(), hfile.c_str());
+    while (!comm) {
+      if (api.accept(lcomm, &comm) != ncclSuccess) { fprintf(stderr, "accept failed\n"); return 2; }
+      if (now_s() > t_limit) { fprintf(stderr, "accept timed out\n"); return 3; }
+      if (!comm) usleep(200);
+    }
+  } else {
+    FILE* f = nullptr;
+    while (!(f = fopen(hfile.c_str(), "rb"))) {
+      if (now_s() > t_limit) { fprintf(stderr, "no handle file\n"); return 3; }
+      usleep(1000);
+    }
+    if (fread(handle, 1, sizeof handle, f) != sizeof handle) { fprintf(stderr, "short handle\n"); return 2; }
+    fclose(f);
+    while (!comm) {
+      if (api.connect(dev, handle, &comm) != ncclSuccess) { fprintf(stderr, "connect failed\n"); return 2; }
+      if (now_s() > t_limit) { fprintf(stderr, "connect timed out\n"); return 3; }
+      if (!comm) usleep(200);
+    }
+  }
+
+  int rc = 0;
+  size_t total_bytes = 0;
+  const double t0 = now_s();
+  int chunks_done_total = 0;
+  for (size_t mi = 0; mi < sizes.size() && rc == 0; ++mi) {
+    const size_t bytes = sizes[mi];
+    std::vector<float> buf((bytes + 3) / 4), expect;
+    if (is_send) fill(buf, seed, mi);
+    else { expect.resize(buf.size()); fill(expect, seed, mi); memset(buf.data(), 0xA5, buf.size() * 4); }
+    void* mh = nullptr;
+    if (api.regMr(comm, buf.data(), buf.size() * 4, &mh) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
+    const size_t nchunks = bytes == 0 ? 1 : (bytes + chunk - 1) / chunk;
+    size_t next = 0, done_chunks = 0;
+    std::deque<void*> reqs;
+    const double msg_limit = now_s() + 90.0;
+    while (done_chunks < nchunks && rc == 0) {
+      while (next < nchunks && (int)reqs.size() < inflight) {
+        const size_t off = next * chunk;
+        const int len = (int)(bytes - off < chunk ? bytes - off : chunk);
+        void* r = nullptr;
+        ncclResult_t e = is_send ? api.isend(comm, (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mh, &r)
+                                 : api.irecv(comm, (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mh, &r);
+        if (e != ncclSuccess) { fprintf(stderr, "%s failed with %d\n", is_send ? "isend" : "irecv", (int)e); rc = 4; break; }
+        if (!r) break;   // would block
+        reqs.push_back(r);
+        ++next;
+      }
+      if (rc) break;
+      if (!reqs.empty()) {
+        int done = 0, sz = 0;
+        ncclResult_t e = api.test(reqs.front(), &done, &sz);
+        if (e != ncclSuccess) { fprintf(stderr, "test failed with %d\n", (int)e); rc = 4; break; }
+        if (done) {
+          reqs.pop_front();
+          ++done_chunks;
+          ++chunks_done_total;
+          if (is_send && die_after >= 0 && chunks_done_total >= die_after) _exit(9);   // abrupt death: no close, no flush
+        }
+      }
+      if (now_s() > msg_limit) { fprintf(stderr, "message %zu timed out\n", mi); rc = 3; }
+    }
+    if (rc == 0 && !is_send && memcmp(buf.data(), expect.data(), bytes) != 0) {
+      size_t bad = 0;
+      while (bad < bytes && ((char*)buf.data())[bad] == ((char*)expect.data())[bad]) ++bad;
+      fprintf(stderr, "message %zu (%zu bytes) differs at byte %zu\n", mi, bytes, bad);
+      rc = 5;
+    }
+    api.deregMr(comm, mh);
+    total_bytes += bytes;
+  }
+  const double dt = now_s() - t0;
+  if (expect_error) {
+    if (rc == 4) { printf("EXPECTED-ERROR after %.3f s\n", dt); rc = 0; }
+    else if (rc == 0) { fprintf(stderr, "transfer succeeded but an error was expected\n"); rc = 3; }
+  } else if (rc == 0) {
+    printf("OK %s %zu bytes in %.4f s (%.3f GB/s) abi v%d\n", is_send ? "sent" : "received", total_bytes, dt, total_bytes / dt / 1e9, api.abi);
+  }
+  if (is_send) api.closeSend(comm);
+  else { api.closeRecv(comm); api.closeListen(lcomm); }
+  return rc;
+}

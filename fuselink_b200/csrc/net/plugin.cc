@@ -1,0 +1,544 @@
+// ncclNet plugin entry points: `libnccl-net-fuselink.so`, loaded by NCCL with NCCL_NET_PLUGIN=fuselink.
+//
+// Surface kept from the reference (src/plugin.cc:1997-2018): the table is named "FuseLink" and is exported
+// as ncclNetPlugin_v7 with a v6 alias; getDeviceMr / irecvConsumed are NULL; multi-receive (n > 1) is
+// rejected (src/plugin.cc:1449-1450,1879-1880).  A v8 table (size_t registration sizes) is exported too so
+// that current NCCL releases find a version they probe for.
+//
+// What differs: devices are the virtual NICs of a transport.  The TCP transport (tcp_transport.*) works on
+// any machine and is what the CPU tests drive; the verbs transport (ib_transport.*) is compiled in and
+// used only where libibverbs and RDMA devices exist.  Path selection goes through ConnManager and the
+// lock-free monitor instead of peeking into NCCL's private proxy structures (src/fuselink.h:18-37): the
+// plugin counts its own posted / completed requests to know when a connection is quiescent.
+#include <arpa/inet.h>
+#include <errno.h>
+#include <poll.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <mutex>
+#include <random>
+
+#include "conn_manager.h"
+#include "ib_transport.h"
+#include "logging.h"
+#include "nccl_net_abi.h"
+#include "params.h"
+#include "tcp_transport.h"
+#include "../mem/vmm.h"
+
+using namespace flnet;
+
+namespace {
+
+constexpr uint64_t kHelloMagic = 0x464c4e4b48454c4full;  // "FLNKHELO"
+constexpr uint32_t kDescMagic = 0x464c4453u;
+constexpr uint32_t kFrameMagic = 0x464c4652u;
+
+std::mutex g_mu;
+ConnManager* g_cm = nullptr;
+int g_ndev = 0;
+std::atomic<int> g_channel_counter{0};
+char g_names[kMaxDev][32];
+char g_pci[kMaxDev][64];
+
+struct MemHandle {
+  void* data;
+  size_t size;
+  int type;
+  FlVmmRegion* region;   // CUDA registrations made through the cuMem layer, else null
+};
+
+uint64_t random_u64() {
+  static std::mt19937_64 rng{std::random_device{}()};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> l(mu);
+  return rng();
+}
+
+// ---------------------------------------------------------------------------------------------------
+ncclResult_t fl_init(ncclDebugLogger_t logger) {
+  std::lock_guard<std::mutex> l(g_mu);
+  log_set(logger);
+  if (g_cm) return ncclSuccess;
+  params_reload();
+  const Params& p = params();
+  int n_ib = 0;
+  if (!p.ib_disable) n_ib = ib_discover();   // 0 on a machine without verbs devices
+  g_ndev = (int)p.tcp_ndev;
+  for (int d = 0; d < g_ndev; ++d) {
+    snprintf(g_names[d], sizeof g_names[d], "fuselink-tcp%d", d);
+    snprintf(g_pci[d], sizeof g_pci[d], "/sys/devices/virtual/net/fuselink%d", d);
+  }
+  int prio = (int)p.priority_dev;
+  if (prio < 0 || prio >= g_ndev) prio = 0;
+  g_cm = new ConnManager(g_ndev, prio, p.monitor_enable != 0, p.monitor_shm.c_str(), (int)p.monitor_timeout_us);
+  FL_INFO("FuseLink plugin: %d virtual NIC(s) over TCP, %d verbs device(s) found, degree %ld step %ld, monitor %s", g_ndev, n_ib,
+          (long)p.degree, (long)p.step, g_cm->monitor() ? "on" : "off");
+  return ncclSuccess;
+}
+
+ncclResult_t fl_devices(int* ndev) {
+  *ndev = g_ndev;
+  return ncclSuccess;
+}
+
+template <class P>
+void fill_props_common(int dev, P* props) {
+  props->name = g_names[dev];
+  props->pciPath = g_pci[dev];
+  props->guid = 0x464c0000ull + (uint64_t)dev;
+  props->ptrSupport = NCCL_PTR_HOST;      // the TCP transport reads/writes host memory; NCCL stages GPU data
+  props->speed = 100000;                  // Mbps, nominal
+  props->port = 0;
+  props->latency = 0;
+  props->maxComms = 65536;
+  props->maxRecvs = 1;                    // grouped receives are not supported (as in the reference)
+}
+ncclResult_t fl_props_v6(int dev, ncclNetProperties_v6_t* props) {
+  if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
+  fill_props_common(dev, props);
+  return ncclSuccess;
+}
+ncclResult_t fl_props_v7(int dev, ncclNetProperties_v7_t* props) {
+  if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
+  fill_props_common(dev, props);
+  props->netDeviceType = NCCL_NET_DEVICE_HOST;
+  props->netDeviceVersion = 0;
+  return ncclSuccess;
+}
+ncclResult_t fl_props_v8(int dev, ncclNetProperties_v8_t* props) {
+  if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
+  fill_props_common(dev, props);
+  props->regIsGlobal = 0;
+  props->netDeviceType = NCCL_NET_DEVICE_HOST;
+  props->netDeviceVersion = 0;
+  return ncclSuccess;
+}
+
+// ---------------------------------------------------------------------------------------------------
+ncclResult_t fl_listen(int dev, void* opaque, void** listen_comm) {
+  if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
+  Handle* h = reinterpret_cast<Handle*>(opaque);
+  memset(h, 0, NCCL_NET_HANDLE_MAXSIZE);
+  sockaddr_in6 addr;
+  pick_listen_addr(&addr);
+  addr.sin6_port = 0;
+  int fd = socket(AF_INET6, SOCK_STREAM, 0);
+  if (fd < 0) return ncclSystemError;
+  int zero = 0, one = 1;
+  setsockopt(fd, IPPROTO_IPV6, IPV6_V6ONLY, &zero, sizeof zero);
+  setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
+  if (bind(fd, reinterpret_cast<sockaddr*>(&addr), sizeof addr) != 0 || listen(fd, 256) != 0) {
+    FL_WARN("listen: bind/listen failed: %s", strerror(errno));
+    close(fd);
+    return ncclSystemError;
+  }
+  socklen_t len = sizeof addr;
+  getsockname(fd, reinterpret_cast<sockaddr*>(&addr), &len);
+  set_nonblock_nodelay(fd);
+  ListenComm* lc = new ListenComm();
+  lc->fd = fd;
+  lc->dev = dev;
+  lc->channel_id = g_channel_counter.fetch_add(1);   // global channel id, carried in the handle (src/plugin.cc:690-698)
+  h->magic = kHandleMagic;
+  h->addr = addr;
+  h->channel_id = lc->channel_id;
+  h->ndev = g_ndev;
+  h->listen_dev = dev;
+  *listen_comm = lc;
+  return ncclSuccess;
+}
+
+// connect(): re-entered until *send_comm != NULL.  Stage 0 starts one control and ndev data connections,
+// stage 1 finishes the TCP handshakes and sends the hellos.  All data sockets are set up eagerly (the
+// reference builds its per-NIC side comms eagerly too, src/plugin.cc:727-753) so switching device later costs
+// nothing.
+ncclResult_t fl_connect_impl(int dev, void* opaque, void** send_comm) {
+  *send_comm = nullptr;
+  Handle* h = reinterpret_cast<Handle*>(opaque);
+  if (h->magic != kHandleMagic) return ncclInvalidArgument;
+  if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
+  Comm* c = reinterpret_cast<Comm*>(h->connect_state);
+  if (!c) {
+    c = new Comm();
+    c->is_send = true;
+    c->own_dev = dev;
+    c->peer_dev = h->listen_dev;
+    c->ndev = h->ndev < g_ndev ? h->ndev : g_ndev;
+    c->channel_id = h->channel_id;
+    c->uid = random_u64();
+    const int nsock = 1 + c->ndev;
+    for (int i = 0; i < nsock; ++i) {
+      int fd = socket(AF_INET6, SOCK_STREAM, 0);
+      if (fd < 0) { comm_close(c); return ncclSystemError; }
+      set_nonblock_nodelay(fd);
+      int rc = connect(fd, reinterpret_cast<sockaddr*>(&h->addr), sizeof h->addr);
+      if (rc != 0 && errno != EINPROGRESS) {
+        FL_WARN("connect: %s", strerror(errno));
+        close(fd);
+        comm_close(c);
+        return ncclSystemError;
+      }
+      c->pending_fds.push_back(fd);
+      c->hello_sent.push_back(0);
+    }
+    h->connect_state = c;
+  }
+  bool all = true;
+  for (size_t i = 0; i < c->pending_fds.size(); ++i) {
+    if (c->hello_sent[i] == sizeof(Hello)) continue;
+    const int fd = c->pending_fds[i];
+    pollfd pfd{fd, POLLOUT, 0};
+    if (poll(&pfd, 1, 0) <= 0 || !(pfd.revents & (POLLOUT | POLLERR | POLLHUP))) { all = false; continue; }
+    int err = 0;
+    socklen_t el = sizeof err;
+    getsockopt(fd, SOL_SOCKET, SO_ERROR, &err, &el);
+    if (err) {
+      FL_WARN("connect to listener failed: %s", strerror(err));
+      h->connect_state = nullptr;
+      comm_close(c);
+      return ncclSystemError;
+    }
+    Hello hello;
+    memset(&hello, 0, sizeof hello);
+    hello.magic = kHelloMagic;
+    hello.comm_uid = c->uid;
+    hello.kind = i == 0 ? 0 : 1;
+    hello.dev = i == 0 ? -1 : (int)i - 1;
+    hello.sender_dev = c->own_dev;
+    hello.ndev = c->ndev;
+    ssize_t r = send(fd, reinterpret_cast<uint8_t*>(&hello) + c->hello_sent[i], sizeof hello - c->hello_sent[i], MSG_DONTWAIT | MSG_NOSIGNAL);
+    if (r > 0) c->hello_sent[i] += (size_t)r;
+    if (c->hello_sent[i] < sizeof(Hello)) all = false;
+  }
+  if (!all) return ncclSuccess;
+  c->ctrl_fd = c->pending_fds[0];
+  for (int d = 0; d < c->ndev; ++d) c->data[d].fd = c->pending_fds[1 + d];
+  c->pending_fds.clear();
+  h->connect_state = nullptr;
+  *send_comm = c;
+  return ncclSuccess;
+}
+
+ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
+  *recv_comm = nullptr;
+  ListenComm* lc = reinterpret_cast<ListenComm*>(listen_comm);
+  for (;;) {
+    int fd = accept(lc->fd, nullptr, nullptr);
+    if (fd < 0) break;
+    set_nonblock_nodelay(fd);
+    PendingSock ps;
+    ps.fd = fd;
+    ps.got = 0;
+    lc->pending.push_back(ps);
+  }
+  for (size_t i = 0; i < lc->pending.size();) {
+    PendingSock& ps = lc->pending[i];
+    ssize_t r = recv(ps.fd, reinterpret_cast<uint8_t*>(&ps.hello) + ps.got, sizeof(Hello) - ps.got, MSG_DONTWAIT);
+    if (r > 0) ps.got += (size_t)r;
+    else if (r == 0 || (errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) {
+      close(ps.fd);                                    // stray or broken connection: drop it (socket.cc:431-437)
+      lc->pending.erase(lc->pending.begin() + i);
+      continue;
+    }
+    if (ps.got < sizeof(Hello)) { ++i; continue; }
+    if (ps.hello.magic != kHelloMagic || ps.hello.ndev < 1 || ps.hello.ndev > kMaxDev ||
+        (ps.hello.kind == 1 && (ps.hello.dev < 0 || ps.hello.dev >= ps.hello.ndev))) {
+      FL_WARN("accept: dropping a connection with a bad hello");
+      close(ps.fd);
+      lc->pending.erase(lc->pending.begin() + i);
+      continue;
+    }
+    ListenComm::Partial* part = nullptr;
+    for (auto& p : lc->partials) if (p.uid == ps.hello.comm_uid) part = &p;
+    if (!part) {
+      Comm* c = new Comm();
+      c->is_send = false;
+      c->own_dev = lc->dev;
+      c->peer_dev = ps.hello.sender_dev;
+      c->ndev = ps.hello.ndev;
+      c->channel_id = lc->channel_id;
+      c->uid = ps.hello.comm_uid;
+      lc->partials.push_back({ps.hello.comm_uid, c, 0});
+      part = &lc->partials.back();
+    }
+    if (ps.hello.kind == 0) part->comm->ctrl_fd = ps.fd;
+    else part->comm->data[ps.hello.dev].fd = ps.fd;
+    part->have++;
+    lc->pending.erase(lc->pending.begin() + i);
+  }
+  for (size_t i = 0; i < lc->partials.size(); ++i) {
+    if (lc->partials[i].have == 1 + lc->partials[i].comm->ndev) {
+      Comm* c = lc->partials[i].comm;
+      lc->partials.erase(lc->partials.begin() + i);
+      c->cur_dev = -1;
+      *recv_comm = c;
+      return ncclSuccess;
+    }
+  }
+  return ncclSuccess;
+}
+
+ncclResult_t fl_connect_v6(int dev, void* handle, void** send_comm) { return fl_connect_impl(dev, handle, send_comm); }
+ncclResult_t fl_accept_v6(void* listen_comm, void** recv_comm) { return fl_accept_impl(listen_comm, recv_comm); }
+ncclResult_t fl_connect_v7(int dev, void* handle, void** send_comm, ncclNetDeviceHandle_v7_t** dev_comm) {
+  if (dev_comm) *dev_comm = nullptr;    // no device offload
+  return fl_connect_impl(dev, handle, send_comm);
+}
+ncclResult_t fl_accept_v7(void* listen_comm, void** recv_comm, ncclNetDeviceHandle_v7_t** dev_comm) {
+  if (dev_comm) *dev_comm = nullptr;
+  return fl_accept_impl(listen_comm, recv_comm);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Registration.  Host memory needs nothing.  A CUDA pointer is accepted when the cuMem layer can adopt it
+// (a VMM allocation, NCCL_CUMEM_ENABLE=1): the region handle is kept so the buffer can be re-homed onto a
+// relay GPU, which is what the reference's regMr does (src/plugin.cc:1168-1330).  The TCP data path itself
+// only touches host memory, so a CUDA registration is refused unless the device transport is active.
+ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
+  (void)comm;
+  if (type != NCCL_PTR_HOST) {
+    FL_WARN("regMr: pointer type %d is not supported by the TCP transport (ptrSupport is HOST)", type);
+    return ncclInvalidUsage;
+  }
+  MemHandle* m = new MemHandle{data, size, type, nullptr};
+  *mhandle = m;
+  return ncclSuccess;
+}
+ncclResult_t fl_reg_mr(void* comm, void* data, int size, int type, void** mhandle) {
+  return fl_reg_mr_sz(comm, data, (size_t)size, type, mhandle);
+}
+ncclResult_t fl_reg_mr_dmabuf(void* comm, void* data, size_t size, int type, uint64_t offset, int fd, void** mhandle) {
+  (void)offset; (void)fd;
+  return fl_reg_mr_sz(comm, data, size, type, mhandle);
+}
+ncclResult_t fl_dereg_mr(void* comm, void* mhandle) {
+  (void)comm;
+  MemHandle* m = reinterpret_cast<MemHandle*>(mhandle);
+  if (m && m->region) fl_vmm_destroy(m->region);
+  delete m;
+  return ncclSuccess;
+}
+
+// ---------------------------------------------------------------------------------------------------
+Request* get_request(Comm* c) {
+  // slots are handed out round-robin so a slot is not reused while frames of its previous use may be in flight
+  static thread_local int hint = 0;
+  for (int i = 0; i < kMaxRequests; ++i) {
+    const int s = (hint + i) % kMaxRequests;
+    if (!c->reqs[s].used) {
+      hint = s + 1;
+      Request& r = c->reqs[s];
+      r = Request();
+      r.used = true;
+      r.comm = c;
+      r.slot = (uint32_t)s;
+      r.last_progress_ns = now_ns();
+      return &r;
+    }
+  }
+  return nullptr;
+}
+
+ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhandle, void** request) {
+  (void)mhandle;
+  Comm* c = reinterpret_cast<Comm*>(send_comm);
+  *request = nullptr;
+  ScopedTimer tm(&c->timers, T_ISEND, params().timers != 0);
+  if (c->error) return (ncclResult_t)c->error;
+  if (size < 0) return ncclInvalidArgument;
+  comm_progress(c, g_cm);
+  if (c->error) return (ncclResult_t)c->error;
+  if (c->fifo.empty()) return ncclSuccess;          // the receiver has not posted yet: try again later
+  const RecvDesc d = c->fifo.front();
+  if (d.tag != tag) {
+    FL_WARN("isend: tag mismatch (posted %d, sending %d)", d.tag, tag);
+    return ncclInternalError;
+  }
+  if ((uint64_t)size > d.size) {
+    FL_WARN("isend: message of %d bytes does not fit the posted receive of %llu bytes", size, (unsigned long long)d.size);
+    return ncclInvalidUsage;
+  }
+  Request* r = get_request(c);
+  if (!r) {
+    FL_WARN("isend: out of request slots");        // src/plugin.cc:1082-1084
+    return ncclInternalError;
+  }
+  c->fifo.pop_front();
+  r->is_send = true;
+  r->data = reinterpret_cast<uint8_t*>(data);
+  r->size = (uint64_t)size;
+  r->tag = tag;
+  // path: the device the receiver proposed, if usable; extra stripes on following devices
+  const Params& p = params();
+  const int first = g_cm->bid_tx(c->channel_id, c->own_dev, d.proposed_dev) % c->ndev;
+  int nstripes = (int)p.degree;
+  if (nstripes > c->ndev) nstripes = c->ndev;
+  while (nstripes > 1 && (uint64_t)size / (uint64_t)nstripes < (uint64_t)p.min_stripe_bytes) --nstripes;
+  const uint64_t mask = g_cm->tx_mask(c->own_dev);
+  const uint64_t per = nstripes > 1 ? ((uint64_t)size / (uint64_t)nstripes) & ~127ull : (uint64_t)size;  // 128-B multiples (src/plugin.cc:1467-1472)
+  uint64_t off = 0;
+  int dev = first;
+  for (int s = 0; s < nstripes; ++s) {
+    Stripe st;
+    st.dev = dev;
+    st.hdr.magic = kFrameMagic;
+    st.hdr.slot = d.slot;
+    st.hdr.total = (uint64_t)size;
+    st.hdr.offset = off;
+    st.hdr.len = s == nstripes - 1 ? (uint64_t)size - off : per;
+    st.hdr.tx_mask = mask;
+    off += st.hdr.len;
+    r->stripes.push_back(st);
+    dev = (dev + (int)(p.step > 0 ? p.step : 1)) % c->ndev;
+  }
+  for (size_t s = 0; s < r->stripes.size(); ++s) {
+    c->data[r->stripes[s].dev].txq.emplace_back(r, (int)s);
+    g_cm->mark_tx(r->stripes[s].dev, r->stripes[s].hdr.len);
+  }
+  c->msg_index++;
+  comm_progress(c, g_cm);
+  *request = r;
+  return ncclSuccess;
+}
+
+ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags, void** mhandles, void** request) {
+  (void)mhandles;
+  Comm* c = reinterpret_cast<Comm*>(recv_comm);
+  *request = nullptr;
+  ScopedTimer tm(&c->timers, T_IRECV, params().timers != 0);
+  if (c->error) return (ncclResult_t)c->error;
+  if (n != 1) {
+    FL_WARN("irecv: grouped receives (n=%d) are not supported", n);
+    return ncclInternalError;
+  }
+  if (sizes[0] < 0) return ncclInvalidArgument;
+  Request* r = get_request(c);
+  if (!r) return ncclSuccess;                      // everything in flight: NCCL retries
+  r->is_send = false;
+  r->data = reinterpret_cast<uint8_t*>(data[0]);
+  r->size = (uint64_t)sizes[0];
+  r->tag = tags[0];
+  // choose the device for this message: re-evaluated every kFinishedBatch completions and only when the
+  // connection is quiescent, so a path switch never races with data in flight (src/plugin.cc:1700-1716)
+  {
+    ScopedTimer ts(&c->timers, T_SELECT, params().timers != 0);
+    const bool quiescent = c->posted == c->completed;
+    if (c->cur_dev < 0 || (c->n_finished >= kFinishedBatch && quiescent)) {
+      c->cur_dev = g_cm->refresh_rx(c->channel_id, c->own_dev, c->cur_dev, c->peer_tx_mask, quiescent);
+      c->n_finished = 0;
+    }
+  }
+  RecvDesc d;
+  memset(&d, 0, sizeof d);
+  d.magic = kDescMagic;
+  d.slot = r->slot;
+  d.tag = r->tag;
+  d.proposed_dev = c->cur_dev;
+  d.size = r->size;
+  d.seq = c->post_seq++;
+  {
+    ScopedTimer tp(&c->timers, T_POST_DESC, params().timers != 0);
+    const uint8_t* p = reinterpret_cast<const uint8_t*>(&d);
+    c->ctrl_tx.insert(c->ctrl_tx.end(), p, p + sizeof d);
+    g_cm->mark_rx(c->cur_dev, r->size);
+    c->posted++;
+    comm_progress(c, g_cm);
+  }
+  *request = r;
+  return ncclSuccess;
+}
+
+// Data lands in host memory through the kernel's socket stack: nothing to flush.  (The reference's flush
+// is a 1-byte RDMA read that it disables by default, src/plugin.cc:887,1768-1799.)
+ncclResult_t fl_iflush(void* recv_comm, int n, void** data, int* sizes, void** mhandles, void** request) {
+  (void)recv_comm; (void)n; (void)data; (void)sizes; (void)mhandles;
+  *request = nullptr;
+  return ncclSuccess;
+}
+
+ncclResult_t fl_test(void* request, int* done, int* sizes) {
+  Request* r = reinterpret_cast<Request*>(request);
+  Comm* c = r->comm;
+  *done = 0;
+  {
+    ScopedTimer tm(&c->timers, T_PROGRESS, params().timers != 0);
+    comm_progress(c, g_cm);
+  }
+  if (r->done) {
+    *done = 1;
+    if (sizes) *sizes = (int)(r->is_send ? r->size : r->total);
+    if (!r->is_send) {
+      c->completed++;
+      c->n_finished++;
+      // the posted size was reserved on the device; what did not arrive will never arrive
+      if (r->total < r->size) g_cm->done_rx(c->cur_dev, r->size - r->total);
+    }
+    r->used = false;
+    return ncclSuccess;
+  }
+  if (c->error) return (ncclResult_t)c->error;
+  const uint64_t limit_ns = (uint64_t)params().net_timeout_ms * 1000000ull;
+  if (limit_ns && now_ns() - r->last_progress_ns > limit_ns) {
+    FL_WARN("%s request on channel %d made no progress for %ld ms: giving up", r->is_send ? "send" : "recv", c->channel_id,
+            (long)params().net_timeout_ms);
+    c->error = ncclRemoteError;
+    return ncclRemoteError;
+  }
+  return ncclSuccess;
+}
+
+ncclResult_t fl_close_send(void* send_comm) {
+  comm_close(reinterpret_cast<Comm*>(send_comm));
+  return ncclSuccess;
+}
+ncclResult_t fl_close_recv(void* recv_comm) {
+  Comm* c = reinterpret_cast<Comm*>(recv_comm);
+  if (c && g_cm && g_cm->monitor() && c->cur_dev >= 0 && c->cur_dev != c->own_dev)
+    fl_monitor_release(g_cm->monitor(), FL_DIR_RX, c->cur_dev);
+  comm_close(c);
+  return ncclSuccess;
+}
+ncclResult_t fl_close_listen(void* listen_comm) {
+  ListenComm* lc = reinterpret_cast<ListenComm*>(listen_comm);
+  if (!lc) return ncclSuccess;
+  for (auto& ps : lc->pending) close(ps.fd);
+  for (auto& p : lc->partials) comm_close(p.comm);
+  if (lc->fd >= 0) close(lc->fd);
+  delete lc;
+  return ncclSuccess;
+}
+
+}  // namespace
+
+extern "C" {
+
+__attribute__((visibility("default"))) ncclNet_v8_t ncclNetPlugin_v8 = {
+    "FuseLink", fl_init, fl_devices, fl_props_v8, fl_listen, fl_connect_v7, fl_accept_v7, fl_reg_mr_sz, fl_reg_mr_dmabuf,
+    fl_dereg_mr, fl_isend, fl_irecv, fl_iflush, fl_test, fl_close_send, fl_close_recv, fl_close_listen, nullptr, nullptr};
+
+__attribute__((visibility("default"))) ncclNet_v7_t ncclNetPlugin_v7 = {
+    "FuseLink", fl_init, fl_devices, fl_props_v7, fl_listen, fl_connect_v7, fl_accept_v7, fl_reg_mr, fl_reg_mr_dmabuf,
+    fl_dereg_mr, fl_isend, fl_irecv, fl_iflush, fl_test, fl_close_send, fl_close_recv, fl_close_listen, nullptr, nullptr};
+
+__attribute__((visibility("default"))) ncclNet_v6_t ncclNetPlugin_v6 = {
+    "FuseLink", fl_init, fl_devices, fl_props_v6, fl_listen, fl_connect_v6, fl_accept_v6, fl_reg_mr, fl_reg_mr_dmabuf,
+    fl_dereg_mr, fl_isend, fl_irecv, fl_iflush, fl_test, fl_close_send, fl_close_recv, fl_close_listen};
+
+// Introspection for tests and tools (not part of the NCCL ABI).
+__attribute__((visibility("default"))) unsigned long long fuselink_plugin_decisions(void) { return g_cm ? g_cm->decisions() : 0; }
+__attribute__((visibility("default"))) unsigned long long fuselink_plugin_fallbacks(void) { return g_cm ? g_cm->fallbacks() : 0; }
+__attribute__((visibility("default"))) void* fuselink_plugin_monitor(void) { return g_cm ? g_cm->monitor() : nullptr; }
+// Device carrying the stripes of a send request (stripe index s); -1 when out of range.
+__attribute__((visibility("default"))) int fuselink_request_stripe_dev(void* request, int s) {
+  Request* r = reinterpret_cast<Request*>(request);
+  if (!r || s < 0 || s >= (int)r->stripes.size()) return -1;
+  return r->stripes[s].dev;
+}
+
+}  // extern "C"

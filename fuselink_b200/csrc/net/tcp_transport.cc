@@ -1,0 +1,268 @@
+// Non-blocking progress engine of the TCP transport (see tcp_transport.h for the protocol).
+#include "tcp_transport.h"
+
+#include <arpa/inet.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <ifaddrs.h>
+#include <net/if.h>
+#include <netinet/tcp.h>
+#include <string.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include "params.h"
+
+namespace flnet {
+
+constexpr uint32_t kDescMagic = 0x464c4453u;   // "FLDS"
+constexpr uint32_t kFrameMagic = 0x464c4652u;  // "FLFR"
+
+int set_nonblock_nodelay(int fd) {
+  int fl = fcntl(fd, F_GETFL, 0);
+  if (fl < 0 || fcntl(fd, F_SETFL, fl | O_NONBLOCK) < 0) return -1;
+  int one = 1;
+  setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
+  int buf = 4 << 20;
+  setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &buf, sizeof buf);
+  setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &buf, sizeof buf);
+  return 0;
+}
+
+static void map_v4(const sockaddr_in* v4, sockaddr_in6* out) {
+  memset(out, 0, sizeof *out);
+  out->sin6_family = AF_INET6;
+  out->sin6_addr.s6_addr[10] = 0xff;
+  out->sin6_addr.s6_addr[11] = 0xff;
+  memcpy(&out->sin6_addr.s6_addr[12], &v4->sin_addr, 4);
+}
+
+// Interface selection: NCCL_SOCKET_IFNAME is a comma list of prefixes ("^" excludes, "=" exact), as in the
+// reference's OOB code (src/extern/socket.cc:86-99,323-357).  Without it: first non-loopback interface
+// that is up, else loopback.
+int pick_listen_addr(sockaddr_in6* out) {
+  const Params& p = params();
+  std::string spec = p.socket_ifname;
+  bool exclude = false, exact = false;
+  if (!spec.empty() && spec[0] == '^') { exclude = true; spec = spec.substr(1); }
+  if (!spec.empty() && spec[0] == '=') { exact = true; spec = spec.substr(1); }
+  std::vector<std::string> names;
+  size_t pos = 0;
+  while (pos <= spec.size() && !spec.empty()) {
+    size_t c = spec.find(',', pos);
+    if (c == std::string::npos) c = spec.size();
+    if (c > pos) names.push_back(spec.substr(pos, c - pos));
+    pos = c + 1;
+  }
+  auto matches = [&](const char* ifn) {
+    for (auto& n : names) {
+      if (exact ? n == ifn : strncmp(ifn, n.c_str(), n.size()) == 0) return true;
+    }
+    return false;
+  };
+  const bool want6 = p.socket_family == "AF_INET6";
+  ifaddrs* ifs = nullptr;
+  bool found = false;
+  sockaddr_in6 loop;
+  bool have_loop = false;
+  if (getifaddrs(&ifs) == 0) {
+    for (ifaddrs* i = ifs; i && !found; i = i->ifa_next) {
+      if (!i->ifa_addr || !(i->ifa_flags & IFF_UP)) continue;
+      const int fam = i->ifa_addr->sa_family;
+      if (fam != AF_INET && fam != AF_INET6) continue;
+      if (want6 != (fam == AF_INET6) && !p.socket_family.empty()) continue;
+      sockaddr_in6 a;
+      if (fam == AF_INET) map_v4(reinterpret_cast<sockaddr_in*>(i->ifa_addr), &a);
+      else { a = *reinterpret_cast<sockaddr_in6*>(i->ifa_addr); if (IN6_IS_ADDR_LINKLOCAL(&a.sin6_addr)) continue; }
+      const bool is_loop = i->ifa_flags & IFF_LOOPBACK;
+      if (!names.empty()) {
+        const bool m = matches(i->ifa_name);
+        if (m == exclude) continue;
+        *out = a; found = true;
+      } else if (is_loop) {
+        if (!have_loop && fam == AF_INET) { loop = a; have_loop = true; }
+      } else if (fam == AF_INET || want6) {
+        *out = a; found = true;
+      }
+    }
+    freeifaddrs(ifs);
+  }
+  if (!found) {
+    if (have_loop) { *out = loop; return 0; }
+    sockaddr_in v4;
+    memset(&v4, 0, sizeof v4);
+    v4.sin_family = AF_INET;
+    v4.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+    map_v4(&v4, out);
+  }
+  return 0;
+}
+
+// returns bytes moved, 0 if it would block, -1 on error / peer closed
+static ssize_t nb_send(int fd, const void* p, size_t n) {
+  ssize_t r = send(fd, p, n, MSG_DONTWAIT | MSG_NOSIGNAL);
+  if (r >= 0) return r;
+  if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return 0;
+  return -1;
+}
+static ssize_t nb_recv(int fd, void* p, size_t n) {
+  ssize_t r = recv(fd, p, n, MSG_DONTWAIT);
+  if (r > 0) return r;
+  if (r == 0) return -1;  // orderly shutdown by the peer while we still expect bytes
+  if (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) return 0;
+  return -1;
+}
+
+static void fail(Comm* c, ncclResult_t why, const char* what) {
+  if (!c->error) {
+    c->error = why;
+    FL_WARN("%s comm (channel %d, dev %d): %s (errno %d: %s)", c->is_send ? "send" : "recv", c->channel_id, c->own_dev, what,
+            errno, strerror(errno));
+  }
+}
+
+// ---- sender ----------------------------------------------------------------------------------------
+static void sender_read_descs(Comm* c) {
+  for (;;) {
+    ssize_t r = nb_recv(c->ctrl_fd, c->ctrl_rx + c->ctrl_rx_got, sizeof(RecvDesc) - c->ctrl_rx_got);
+    if (r < 0) {
+      // the receiver may close its side once everything it posted has completed; only an error if we still owe data
+      bool owing = false;
+      for (auto& rq : c->reqs) if (rq.used && !rq.done) owing = true;
+      if (owing) fail(c, ncclRemoteError, "control connection lost");
+      return;
+    }
+    if (r == 0) return;
+    c->ctrl_rx_got += (size_t)r;
+    if (c->ctrl_rx_got == sizeof(RecvDesc)) {
+      RecvDesc d;
+      memcpy(&d, c->ctrl_rx, sizeof d);
+      c->ctrl_rx_got = 0;
+      if (d.magic != kDescMagic) { fail(c, ncclInternalError, "bad descriptor magic"); return; }
+      c->fifo.push_back(d);
+    }
+  }
+}
+
+static void sender_push(Comm* c, ConnManager* cm) {
+  const int64_t fault_after = params().fault_drop_after;
+  for (int d = 0; d < c->ndev; ++d) {
+    DataSock& s = c->data[d];
+    while (!s.txq.empty()) {
+      Request* rq = s.txq.front().first;
+      Stripe& st = rq->stripes[s.txq.front().second];
+      if (st.hdr_sent < sizeof(FrameHdr)) {
+        ssize_t r = nb_send(s.fd, reinterpret_cast<uint8_t*>(&st.hdr) + st.hdr_sent, sizeof(FrameHdr) - st.hdr_sent);
+        if (r < 0) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }
+        if (r == 0) break;
+        st.hdr_sent += (size_t)r;
+        if (st.hdr_sent < sizeof(FrameHdr)) break;
+      }
+      if (st.sent < st.hdr.len) {
+        size_t want = st.hdr.len - st.sent;
+        if (fault_after > 0 && s.tx_bytes + want > (uint64_t)fault_after) {
+          // test hook: the link "breaks" in the middle of a stripe
+          size_t allowed = (uint64_t)fault_after > s.tx_bytes ? (size_t)(fault_after - s.tx_bytes) : 0;
+          if (allowed) nb_send(s.fd, rq->data + st.hdr.offset + st.sent, allowed);
+          shutdown(s.fd, SHUT_RDWR);
+          cm->set_dead(d, true);
+          fail(c, ncclSystemError, "injected link failure");
+          return;
+        }
+        ssize_t r = nb_send(s.fd, rq->data + st.hdr.offset + st.sent, want);
+        if (r < 0) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }
+        if (r == 0) break;
+        st.sent += (size_t)r;
+        s.tx_bytes += (uint64_t)r;
+        rq->moved += (uint64_t)r;
+        rq->last_progress_ns = now_ns();
+        cm->done_tx(d, (uint64_t)r);
+        if (st.sent < st.hdr.len) break;
+      }
+      rq->stripes_done++;
+      if (rq->stripes_done == rq->stripes.size()) rq->done = true;
+      s.txq.pop_front();
+    }
+  }
+}
+
+// ---- receiver --------------------------------------------------------------------------------------
+static void receiver_flush_ctrl(Comm* c) {
+  while (!c->ctrl_tx.empty()) {
+    ssize_t r = nb_send(c->ctrl_fd, c->ctrl_tx.data(), c->ctrl_tx.size());
+    if (r < 0) { fail(c, ncclRemoteError, "control connection lost"); return; }
+    if (r == 0) return;
+    c->ctrl_tx.erase(c->ctrl_tx.begin(), c->ctrl_tx.begin() + r);
+  }
+}
+
+static void receiver_pull(Comm* c, ConnManager* cm) {
+  for (int d = 0; d < c->ndev; ++d) {
+    DataSock& s = c->data[d];
+    for (;;) {
+      if (!s.rx_in_payload) {
+        ssize_t r = nb_recv(s.fd, reinterpret_cast<uint8_t*>(&s.rx_hdr) + s.rx_hdr_got, sizeof(FrameHdr) - s.rx_hdr_got);
+        if (r < 0) {
+          bool waiting = false;
+          for (auto& rq : c->reqs) if (rq.used && !rq.done) waiting = true;
+          if (waiting) { cm->set_dead(d, true); fail(c, ncclRemoteError, "data connection closed by the sender"); }
+          return;
+        }
+        if (r == 0) break;
+        s.rx_hdr_got += (size_t)r;
+        if (s.rx_hdr_got < sizeof(FrameHdr)) break;
+        s.rx_hdr_got = 0;
+        if (s.rx_hdr.magic != kFrameMagic || s.rx_hdr.slot >= (uint32_t)kMaxRequests) { fail(c, ncclInternalError, "bad frame header"); return; }
+        Request& rq = c->reqs[s.rx_hdr.slot];
+        if (!rq.used || rq.is_send) { fail(c, ncclInternalError, "frame for a slot that is not posted"); return; }
+        if (s.rx_hdr.total > rq.size || s.rx_hdr.offset + s.rx_hdr.len > s.rx_hdr.total) {
+          fail(c, ncclInvalidUsage, "message larger than the posted receive");   // src/plugin.cc:1555-1570
+          return;
+        }
+        rq.total = s.rx_hdr.total;
+        c->peer_tx_mask = s.rx_hdr.tx_mask;
+        s.rx_in_payload = true;
+        s.rx_payload_got = 0;
+        if (s.rx_hdr.len == 0) s.rx_in_payload = false;
+        if (rq.total == 0) rq.done = true;
+      }
+      if (s.rx_in_payload) {
+        Request& rq = c->reqs[s.rx_hdr.slot];
+        ssize_t r = nb_recv(s.fd, rq.data + s.rx_hdr.offset + s.rx_payload_got, s.rx_hdr.len - s.rx_payload_got);
+        if (r < 0) { cm->set_dead(d, true); fail(c, ncclRemoteError, "data connection closed in the middle of a message"); return; }
+        if (r == 0) break;
+        s.rx_payload_got += (uint64_t)r;
+        rq.moved += (uint64_t)r;
+        rq.last_progress_ns = now_ns();
+        cm->done_rx(d, (uint64_t)r);
+        if (s.rx_payload_got == s.rx_hdr.len) s.rx_in_payload = false;
+        if (rq.moved == rq.total) rq.done = true;
+      }
+    }
+  }
+}
+
+ncclResult_t comm_progress(Comm* c, ConnManager* cm) {
+  if (c->error) return (ncclResult_t)c->error;
+  if (c->is_send) {
+    sender_read_descs(c);
+    if (!c->error) sender_push(c, cm);
+  } else {
+    receiver_flush_ctrl(c);
+    if (!c->error) receiver_pull(c, cm);
+  }
+  return (ncclResult_t)c->error;
+}
+
+void comm_close(Comm* c) {
+  if (!c) return;
+  if (params().timers) c->timers.print(c->is_send ? "send" : "recv");
+  if (c->ctrl_fd >= 0) close(c->ctrl_fd);
+  for (int d = 0; d < kMaxDev; ++d)
+    if (c->data[d].fd >= 0) close(c->data[d].fd);
+  for (int fd : c->pending_fds)
+    if (fd >= 0) close(fd);
+  delete c;
+}
+
+}  // namespace flnet

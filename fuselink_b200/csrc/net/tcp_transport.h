@@ -1,0 +1,154 @@
+// TCP data transport of the plugin: every "device" is a virtual NIC (one data socket per device and
+// connection) and one control socket carries the receiver's descriptors.
+//
+// The reference has sockets for out-of-band control only (src/extern/socket.{h,cc}) and moves data with
+// RDMA writes; its wire protocol is receiver-driven: irecv publishes {address, size, tag, slot, chosen
+// NIC} into the sender's FIFO and isend consumes FIFO slots in order (src/plugin.cc:1616-1677,
+// 1500-1614).  The same protocol runs here over byte streams: a descriptor travels on the control socket,
+// data travels as framed stripes on the data socket of the device the receiver chose (or of several
+// devices when NCCL_FUSELINK_DEGREE > 1), and both ends progress from test() without blocking.
+#pragma once
+#include <netinet/in.h>
+#include <stdint.h>
+
+#include <deque>
+#include <vector>
+
+#include "conn_manager.h"
+#include "logging.h"
+#include "nccl_net_abi.h"
+
+namespace flnet {
+
+constexpr uint64_t kHandleMagic = 0x464c4e4b48444c31ull;  // "FLNKHDL1"
+constexpr int kMaxDev = 16;
+constexpr int kMaxRequests = 256;       // MAX_REQUESTS of the reference (src/plugin.cc:382-383)
+constexpr int kFinishedBatch = 8;       // N_FINISHED_BATCH (src/plugin.cc:38)
+
+struct Handle {                          // what listen() publishes; <= NCCL_NET_HANDLE_MAXSIZE bytes
+  uint64_t magic;
+  sockaddr_in6 addr;                     // v4 addresses are stored v4-mapped
+  int32_t channel_id;
+  int32_t ndev;
+  int32_t listen_dev;
+  int32_t pad;
+  void* connect_state;                   // in-progress SendComm between re-entrant connect() calls
+};
+static_assert(sizeof(Handle) <= NCCL_NET_HANDLE_MAXSIZE, "handle too large");
+
+struct Hello {                           // first bytes on every new socket
+  uint64_t magic;
+  uint64_t comm_uid;
+  int32_t kind;                          // 0 control, 1 data
+  int32_t dev;                           // virtual NIC index of a data socket
+  int32_t sender_dev;                    // the sender's own (affine) device
+  int32_t ndev;
+};
+
+struct RecvDesc {                        // receiver -> sender, control socket
+  uint32_t magic;
+  uint32_t slot;                         // receiver's request slot; echoed in every frame
+  int32_t tag;
+  int32_t proposed_dev;                  // the reference's fuselink_offset
+  uint64_t size;                         // posted receive size (upper bound)
+  uint64_t seq;                          // order of posting
+};
+
+struct FrameHdr {                        // sender -> receiver, in front of every stripe on a data socket
+  uint32_t magic;
+  uint32_t slot;
+  uint64_t total;                        // full message size (may be smaller than the posted size)
+  uint64_t offset;
+  uint64_t len;
+  uint64_t tx_mask;                      // sender's device availability (the reference's immediate data)
+};
+
+struct Stripe {
+  int dev;
+  FrameHdr hdr;
+  size_t hdr_sent = 0;
+  size_t sent = 0;
+};
+
+struct Comm;
+
+struct Request {
+  bool used = false;
+  bool is_send = false;
+  bool done = false;
+  Comm* comm = nullptr;
+  uint32_t slot = 0;
+  uint8_t* data = nullptr;
+  uint64_t size = 0;                     // send: message size; recv: posted size
+  uint64_t total = UINT64_MAX;           // recv: actual size once the first frame arrived
+  uint64_t moved = 0;                    // bytes sent / received so far
+  int tag = 0;
+  uint64_t last_progress_ns = 0;
+  std::vector<Stripe> stripes;           // send only
+  size_t stripes_done = 0;
+};
+
+struct DataSock {
+  int fd = -1;
+  // send side: stripes queued on this socket, in order
+  std::deque<std::pair<Request*, int>> txq;   // (request, stripe index)
+  uint64_t tx_bytes = 0;
+  // recv side: frame parser
+  FrameHdr rx_hdr;
+  size_t rx_hdr_got = 0;
+  uint64_t rx_payload_got = 0;
+  bool rx_in_payload = false;
+};
+
+struct Comm {
+  bool is_send = false;
+  int own_dev = 0;                       // device NCCL bound this comm to
+  int peer_dev = 0;
+  int ndev = 1;
+  int channel_id = 0;
+  uint64_t uid = 0;
+  int ctrl_fd = -1;
+  DataSock data[kMaxDev];
+  Request reqs[kMaxRequests];
+  int error = 0;                         // sticky ncclResult_t
+  // control stream
+  std::vector<uint8_t> ctrl_tx;          // receiver: descriptors not yet written
+  uint8_t ctrl_rx[sizeof(RecvDesc)];
+  size_t ctrl_rx_got = 0;
+  std::deque<RecvDesc> fifo;             // sender: descriptors received, in posting order
+  // selection state
+  int cur_dev = -1;                      // receiver: device proposed for new messages
+  int n_finished = 0;
+  int posted = 0, completed = 0;
+  uint64_t post_seq = 0;
+  uint64_t peer_tx_mask = ~0ull;         // receiver: last mask advertised by the sender (txAvailable)
+  uint64_t msg_index = 0;
+  // connect progress
+  int connect_stage = 0;
+  std::vector<int> pending_fds;
+  std::vector<size_t> hello_sent;
+  Timers timers;
+};
+
+struct PendingSock {
+  int fd;
+  Hello hello;
+  size_t got;
+};
+
+struct ListenComm {
+  int fd = -1;
+  int dev = 0;
+  int channel_id = 0;
+  std::vector<PendingSock> pending;      // accepted, hello not complete yet
+  struct Partial { uint64_t uid; Comm* comm; int have; };
+  std::vector<Partial> partials;         // sockets grouped by connection uid
+};
+
+// helpers shared with plugin.cc
+int set_nonblock_nodelay(int fd);
+int pick_listen_addr(sockaddr_in6* out);           // honours NCCL_SOCKET_IFNAME / NCCL_SOCKET_FAMILY
+ncclResult_t comm_progress(Comm* c, ConnManager* cm);
+void comm_close(Comm* c);
+
+}  // namespace flnet

@@ -1,0 +1,135 @@
+"""ncclNet plugin over the TCP transport, driven by two processes through the plugin's function table
+(no NCCL, no GPU, no RDMA): bitwise transfer of {4 KB, 1 MB, 64 MB} fp32 messages in 512 KB chunks with 8
+requests in flight, every ABI version, multi-path striping, and host-injected failures."""
+import ctypes
+import os
+import subprocess
+import sys
+import tempfile
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB = os.path.join(ROOT, "fuselink_b200", "lib")
+PLUGIN = os.path.join(LIB, "libnccl-net-fuselink.so")
+HARNESS = os.path.join(LIB, "fl_net_harness")
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _built():
+    if not (os.path.exists(PLUGIN) and os.path.exists(HARNESS)):
+        sys.path.insert(0, ROOT)
+        from fuselink_b200 import build
+        build.build_all()
+    assert os.path.exists(PLUGIN) and os.path.exists(HARNESS)
+
+
+def _pair(sizes, extra_send=(), extra_recv=(), env=None, common=(), timeout=120):
+    with tempfile.TemporaryDirectory() as d:
+        hf = os.path.join(d, "handle")
+        e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", **(env or {}))
+        sz = [str(s) for s in sizes]
+        rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, *common, *extra_recv, *sz], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        tx = subprocess.Popen([HARNESS, PLUGIN, "send", hf, *common, *extra_send, *sz], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        try:
+            txo, txe = tx.communicate(timeout=timeout)
+            rxo, rxe = rx.communicate(timeout=timeout)
+        finally:
+            for p in (rx, tx):
+                if p.poll() is None:
+                    p.kill()
+        return (tx.returncode, txo, txe), (rx.returncode, rxo, rxe)
+
+
+@pytest.mark.parametrize("abi", [6, 7, 8])
+def test_bitwise_transfer_reference_config(abi):
+    tx, rx = _pair([4096, 1 << 20, 64 << 20], common=["--abi", str(abi), "--chunk", "524288", "--inflight", "8", "--seed", "0"])
+    assert tx[0] == 0, tx
+    assert rx[0] == 0, rx
+    assert "OK received" in rx[1]
+
+
+def test_odd_sizes_and_zero_length():
+    tx, rx = _pair([0, 1, 3, 4097, 524288, 524289, 1234567], common=["--chunk", "65536"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+
+
+def test_striping_over_virtual_nics():
+    env = {"NCCL_FUSELINK_DEGREE": "4", "NCCL_FUSELINK_STEP": "1", "FUSELINK_TCP_NDEV": "4", "FUSELINK_MIN_STRIPE_BYTES": "4096"}
+    tx, rx = _pair([1 << 20, 8 << 20, 100_000], env=env)
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+
+
+def test_monitor_off_uses_channel_modulo():
+    tx, rx = _pair([1 << 20], env={"FUSELINK_MONITOR": "0"})
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+
+
+def test_sender_death_is_reported_not_hung():
+    """A sender that exits mid-transfer must surface as an error on the receiver (host-side fault)."""
+    tx, rx = _pair([32 << 20], extra_send=["--die-after-chunks", "5"], extra_recv=["--expect-error"],
+                   env={"FUSELINK_NET_TIMEOUT_MS": "3000"}, timeout=60)
+    assert tx[0] == 9
+    assert rx[0] == 0 and "EXPECTED-ERROR" in rx[1], rx
+
+
+def test_injected_link_failure_marks_path_dead():
+    tx, rx = _pair([16 << 20], extra_recv=["--expect-error"], env={"FUSELINK_FAULT_CLOSE_AFTER_BYTES": str(3 << 20), "FUSELINK_NET_TIMEOUT_MS": "3000"}, timeout=60)
+    assert tx[0] != 0            # the sender reports the broken link
+    assert rx[0] == 0 and "EXPECTED-ERROR" in rx[1], rx
+
+
+def test_stalled_peer_times_out():
+    """Receiver posts, the peer connects and then never sends: the request fails after
+    FUSELINK_NET_TIMEOUT_MS instead of spinning forever."""
+    import socket
+    import struct
+    import time
+    with tempfile.TemporaryDirectory() as d:
+        hf = os.path.join(d, "handle")
+        e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", NCCL_SOCKET_FAMILY="AF_INET", FUSELINK_NET_TIMEOUT_MS="500")
+        rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, "--expect-error", "65536"], env=e, stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True)
+        socks = []
+        try:
+            t0 = time.time()
+            while not os.path.exists(hf):
+                assert time.time() - t0 < 20
+                time.sleep(0.01)
+            h = open(hf, "rb").read()
+            port = struct.unpack("!H", h[10:12])[0]
+            ndev = struct.unpack("i", h[40:44])[0]
+            # raw sockets with valid hellos so accept() completes; then stay silent
+            for i in range(1 + ndev):
+                s = socket.create_connection(("127.0.0.1", port))
+                s.sendall(struct.pack("<QQiiii", 0x464c4e4b48454c4f, 0x1234, 0 if i == 0 else 1, -1 if i == 0 else i - 1, 0, ndev))
+                socks.append(s)
+            out, err = rx.communicate(timeout=30)
+        finally:
+            for s in socks:
+                s.close()
+            if rx.poll() is None:
+                rx.kill()
+        assert rx.returncode == 0 and "EXPECTED-ERROR" in out, (out, err)
+
+
+def test_plugin_symbols_and_properties():
+    lib = ctypes.CDLL(PLUGIN)
+    for sym in ("ncclNetPlugin_v6", "ncclNetPlugin_v7", "ncclNetPlugin_v8"):
+        assert hasattr(lib, sym)
+    name = ctypes.c_char_p.in_dll(lib, "ncclNetPlugin_v7")
+    assert name.value == b"FuseLink"
+
+
+def test_hca_filter_syntax():
+    lib = ctypes.CDLL(PLUGIN)
+    f = lib.fuselink_hca_allowed
+    f.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int]
+    assert f(b"", b"mlx5_0", 1) == 1
+    assert f(b"mlx5", b"mlx5_3", 1) == 1                       # prefix match
+    assert f(b"=mlx5_1", b"mlx5_10", 1) == 0                   # exact
+    assert f(b"^mlx5_1", b"mlx5_1", 1) == 0 and f(b"^mlx5_1", b"mlx5_2", 1) == 1
+    assert f(b"mlx5_0:2", b"mlx5_0", 1) == 0 and f(b"mlx5_0:2", b"mlx5_0", 2) == 1
+    spec = b"=mlx5_0,3,4,5,6,9,10,11"                          # the reference's 8-NIC list
+    allowed = [i for i in range(12) if f(spec, f"mlx5_{i}".encode(), 1)]
+    assert allowed == [0, 3, 4, 5, 6, 9, 10, 11]

@@ -1,0 +1,94 @@
+"""cuMem region layer against the memfd/mmap fake driver: the aliasing, export/import and remap semantics
+are the ones the CUDA driver gives (same virtual address, new physical backing)."""
+import os
+
+import pytest
+import torch
+
+from fuselink_b200 import C, have_native
+
+pytestmark = pytest.mark.skipif(not have_native() or torch.cuda.is_available(), reason="CPU-only test of the fake VMM backend")
+
+
+@pytest.fixture(autouse=True)
+def _fake():
+    C.vmm_init(1)
+    yield
+
+
+def _view(region, n=1024):
+    return C.tensor_from_ptr(C.vmm_ptr(region), [n], torch.int32, -1)
+
+
+def test_create_slabs_and_usage():
+    before = C.vmm_usage(2)
+    r = C.vmm_create(2, 5 << 20, 2 << 20)
+    assert C.vmm_num_slabs(r) == 3 and C.vmm_size(r) == 6 << 20 and C.vmm_slab_bytes(r) == 2 << 20
+    assert C.vmm_usage(2) - before == 6 << 20
+    assert [C.vmm_slab_device(r, i) for i in range(3)] == [2, 2, 2]
+    assert C.vmm_ptr2dev(C.vmm_ptr(r) + (3 << 20)) == 2 and C.vmm_ptr2dev(12345) == -1
+    C.vmm_destroy(r)
+    assert C.vmm_usage(2) == before
+
+
+def test_alias_sees_same_memory():
+    r = C.vmm_create(0, 2 << 20, 0)
+    a = C.vmm_alias(r, 1)
+    _view(r).fill_(11)
+    assert (_view(a) == 11).all()
+    _view(a)[5] = 99
+    assert _view(r)[5] == 99
+    C.vmm_destroy(a)
+    C.vmm_destroy(r)
+
+
+def test_export_import_roundtrip():
+    r = C.vmm_create(0, 4 << 20, 2 << 20)
+    fds = [C.vmm_export_fd(r, i) for i in range(2)]
+    imp = C.vmm_import(3, fds, 2 << 20)
+    for fd in fds:
+        os.close(fd)
+    _view(r, 1 << 20).copy_(torch.arange(1 << 20, dtype=torch.int32))
+    assert torch.equal(_view(imp, 1 << 20), torch.arange(1 << 20, dtype=torch.int32))
+    C.vmm_destroy(imp)
+    C.vmm_destroy(r)
+
+
+def test_remap_keeps_address_and_optionally_contents():
+    r = C.vmm_create(0, 4 << 20, 2 << 20)
+    ptr = C.vmm_ptr(r)
+    old_alias = C.vmm_alias(r, 0)
+    _view(r).fill_(7)
+    usec = C.vmm_remap_slab(r, 0, 5, True, [0])
+    assert usec >= 0 and C.vmm_ptr(r) == ptr
+    assert C.vmm_slab_device(r, 0) == 5 and C.vmm_slab_device(r, 1) == 0
+    assert (_view(r) == 7).all()                      # contents carried over
+    _view(r).fill_(8)
+    assert (_view(old_alias) == 7).all()              # the alias still holds the old physical memory
+    C.vmm_remap_slab(r, 0, 6, False, [])
+    assert C.vmm_slab_device(r, 0) == 6               # fresh backing: contents not carried
+    assert C.vmm_usage(6) >= 2 << 20
+    C.vmm_destroy(old_alias)
+    C.vmm_destroy(r)
+
+
+def test_adopt_foreign_allocation_and_rehome():
+    owner = C.vmm_create(1, 2 << 20, 0)               # stands in for a buffer another library allocated
+    _view(owner).fill_(3)
+    adopted = C.vmm_adopt(C.vmm_ptr(owner), 2 << 20, 1)
+    C.vmm_remap_slab(adopted, 0, 4, True, [1])        # same VA now backed by "GPU 4", opened to the source GPU
+    assert C.vmm_slab_device(adopted, 0) == 4
+    assert (_view(owner) == 3).all()
+    C.vmm_destroy(adopted)
+
+
+def test_symmetric_heap_emulated_on_cpu():
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    heaps = SymmetricHeap.emulated(3, 4 << 20)
+    a = [h.alloc_tensor([16], torch.int32) for h in heaps]
+    assert len({t.offset for t in a}) == 1
+    a[1].local.fill_(5)
+    assert (a[0].view_of(1) == 5).all() and (a[0].local == 0).all()
+    assert heaps[0].signal_slots("x", 4) == heaps[2].signal_slots("x", 4)
+    for h in heaps:
+        h.close()
