@@ -107,7 +107,7 @@ class LlamaShard(torch.nn.Module):
     # ------------------------------------------------------------------------------------------- prefill
     @torch.no_grad()
     def prefill(self, tokens: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
-                on_layer_done: Optional[Callable[[int], None]] = None) -> torch.Tensor:
+                on_layer_done: Optional[Callable[[int], None]] = None, last_pos: Optional[torch.Tensor] = None) -> torch.Tensor:
         """tokens: [B, S] (S a multiple of block_size); pools: flat bf16 in the BLHSD layout; block_table: [B, >=S/bs]
         int32.  Fills the pools, returns the greedy first token of every sequence [B] (int64)."""
         cfg = self.cfg
@@ -135,7 +135,8 @@ class LlamaShard(torch.nn.Module):
                                                enable_gqa=self.h_local != self.kvh_local)
             x = x + self._allreduce(o.transpose(1, 2).reshape(B, S, self.h_local * D) @ self.wo[l].t())
             x = x + self._mlp(l, _rms(x, self.n2[l], cfg.eps))
-        last = _rms(x[:, -1], self.final_norm, cfg.eps)
+        xl = x[:, -1] if last_pos is None else x[torch.arange(B, device=x.device), last_pos]
+        last = _rms(xl, self.final_norm, cfg.eps)
         return (last @ self.lm_head.t()).float().argmax(-1)
 
     # ------------------------------------------------------------------------------------------- decode

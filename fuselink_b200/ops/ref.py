@@ -55,5 +55,5 @@ def kv_gather_pages(pool, layout, block_table, num_blocks, layers, heads, block_
             else:             # [layer][block][slot][head][dim]
                 p = pool.view(layers, -1, block_size, heads, head_dim)[:, blk]
             pages.append(p)
-        outs.append(torch.cat(pages, dim=1))
+        outs.append(torch.cat(pages, dim=1) if pages else pool.new_zeros(layers, 0, heads, head_dim))
     return outs

@@ -1,0 +1,204 @@
+"""Disaggregated serving: a prefill (context) stage and a decode stage on different GPUs, linked by the fused
+KV hand-off kernel.
+
+Reference behaviour (experiments/serving/main.cc:184-202, model.hh:253-337,420-529): ranks below world/2 run
+the context stage, the rest decode; after the WHOLE prefill the context rank sends first tokens, the whole K
+pool, the whole V pool, the block table and the block counts to rank + world/2 in one NCCL group, and the
+decoder then generates tokens.  It prints elapsed time, KV send time and their ratio (main.cc:228-239).
+
+Here the pairing (rank -> rank + world/2) and the reports are kept; the transfer is `kv_pack_send`: only the
+pages in use move, they are re-laid-out for the decode pool on the fly, the small messages ride along as one
+header, and each layer's pages leave as soon as that layer has been computed (a side stream ordered by events),
+so the transfer overlaps the rest of the prefill.
+
+``KVLink`` is the transfer object, ``PrefillStage`` / ``DecodeStage`` wrap the model, ``run_offline`` is the
+two-stage experiment; all of them also work with both stages as virtual ranks on ONE GPU (emulated heap).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+import torch
+
+from .._ext import require_native
+from ..models.llama import KV_BLHSD, KV_LBSHD, LlamaConfig, LlamaShard
+from ..parallel.symm import SymmetricHeap
+
+HDR_MAX_BATCH = 32
+HDR_TOKENS, HDR_LENS, HDR_OUTS = 4, 4 + HDR_MAX_BATCH, 4 + 2 * HDR_MAX_BATCH
+HDR_INTS = 4 + 3 * HDR_MAX_BATCH   # [batch, prompt_len, max_blocks, batch_index] + first tokens + prompt lengths + output lengths
+
+
+@dataclass
+class ServeParams:
+    """The experiment's knobs (TestParams of the reference, experiments/serving/model.hh:31-49)."""
+    model: LlamaConfig
+    batch_size: int = 16
+    input_len: int = 2048
+    num_decoding_step: int = 256
+    tp_size: int = 1
+
+    @property
+    def block_size(self) -> int:
+        return self.model.block_size
+
+    @property
+    def max_blocks_per_req(self) -> int:          # ceil((input + decode) / block), model.hh:100-103
+        return (self.input_len + self.num_decoding_step + self.block_size - 1) // self.block_size
+
+    @property
+    def context_blocks_per_req(self) -> int:
+        return (self.input_len + self.block_size - 1) // self.block_size
+
+
+class KVLink:
+    """Decode-side pools inside the symmetric heap + the flags and header of the hand-off.  Collective: both
+    stages construct it with the same arguments so that offsets agree."""
+
+    def __init__(self, heap: SymmetricHeap, p: ServeParams, kv_heads_local: int, name: str = "kv"):
+        self.heap, self.p, self.kvh = heap, p, kv_heads_local
+        m = p.model
+        self.pool_blocks = p.batch_size * p.max_blocks_per_req
+        self.page_elems = kv_heads_local * m.block_size * m.head_dim
+        n = self.pool_blocks * m.layers * self.page_elems
+        self.k_pool = heap.alloc_tensor([n], torch.bfloat16)
+        self.v_pool = heap.alloc_tensor([n], torch.bfloat16)
+        self.hdr = heap.alloc_tensor([HDR_INTS], torch.int64)
+        self.layer_flags = heap.signal_slots(f"{name}:layers", m.layers)
+        self.final_flag = heap.signal_slots(f"{name}:final", 1)
+        self.seq = 0
+        self.C = require_native()
+        dev = self.k_pool.local.device
+        self.cta_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    # ---- prefill side -------------------------------------------------------------------------------------
+    def send_layers(self, dst_rank: int, src_k, src_v, src_blocks: int, src_bt, dst_bt, nblocks, l0: int, l1: int,
+                    hdr: Optional[torch.Tensor] = None, final: bool = False, num_ctas: int = 0):
+        m = self.p.model
+        flag = self.heap.sig_addr(self.final_flag if final else self.layer_flags + l0, dst_rank)
+        self.C.kv_pack_send(src_k, src_v, self.k_pool.addr(dst_rank), self.v_pool.addr(dst_rank), KV_BLHSD, KV_LBSHD,
+                            src_blocks, self.pool_blocks, m.layers, self.kvh, m.block_size, m.head_dim, l0, l1, src_bt, dst_bt,
+                            nblocks, hdr, self.hdr.addr(dst_rank) if hdr is not None else 0, flag, self.seq, self.cta_counter,
+                            num_ctas, self.heap.status_addr)
+
+    # ---- decode side --------------------------------------------------------------------------------------
+    def wait_final(self):
+        self.C.wait_flags([(self.heap.sig_addr(self.final_flag), self.seq)], self.heap.status_addr)
+
+    def wait_layer(self, l: int):
+        self.C.wait_flags([(self.heap.sig_addr(self.layer_flags + l), self.seq)], self.heap.status_addr)
+
+
+@dataclass
+class StageReport:
+    role: str
+    elapsed_ms: float = 0.0
+    compute_ms: float = 0.0
+    kv_ms: float = 0.0              # device time of the KV hand-off kernels (prefill) / of the wait (decode)
+    kv_bytes: int = 0
+    tokens: int = 0
+    extra: dict = field(default_factory=dict)
+
+
+class PrefillStage:
+    def __init__(self, p: ServeParams, model: LlamaShard, link: KVLink, dst_rank: int, pipeline_layers: bool = True):
+        self.p, self.model, self.link, self.dst = p, model, link, dst_rank
+        self.pipeline = pipeline_layers
+        m = p.model
+        dev = model.embed.device
+        self.ctx_blocks = p.batch_size * p.context_blocks_per_req
+        n = self.ctx_blocks * m.layers * link.page_elems
+        self.k_pool = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        self.v_pool = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        B, cb, mb = p.batch_size, p.context_blocks_per_req, p.max_blocks_per_req
+        # source pages: request-major; destination pages: the decode pool reserves max_blocks_per_req per request
+        self.src_bt = torch.arange(B * cb, dtype=torch.int32, device=dev).view(B, cb).contiguous()
+        self.dst_bt = (torch.arange(B, dtype=torch.int32, device=dev).unsqueeze(1) * mb +
+                       torch.arange(cb, dtype=torch.int32, device=dev).unsqueeze(0)).contiguous()
+        self.nblocks = torch.full((B,), cb, dtype=torch.int32, device=dev)
+        self.side = torch.cuda.Stream(device=dev)
+        self.hdr = torch.zeros(HDR_INTS, dtype=torch.int64, device=dev)
+
+    def run(self, tokens: torch.Tensor) -> StageReport:
+        p, link = self.p, self.link
+        link.seq += 1
+        main = torch.cuda.current_stream()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        first_kv = [True]
+
+        def on_layer(l: int):
+            if not self.pipeline:
+                return
+            ev = torch.cuda.Event()
+            ev.record(main)
+            with torch.cuda.stream(self.side):
+                self.side.wait_event(ev)
+                if first_kv[0]:
+                    k0.record(self.side)
+                    first_kv[0] = False
+                link.send_layers(self.dst, self.k_pool, self.v_pool, self.ctx_blocks, self.src_bt, self.dst_bt, self.nblocks, l, l + 1)
+
+        e0.record(main)
+        first = self.model.prefill(tokens, self.k_pool, self.v_pool, self.src_bt, on_layer)
+        e1.record(main)
+        self.hdr[0], self.hdr[1], self.hdr[2] = p.batch_size, p.input_len, p.max_blocks_per_req
+        self.hdr[4:4 + p.batch_size] = first
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            if not self.pipeline:
+                k0.record(self.side)
+                link.send_layers(self.dst, self.k_pool, self.v_pool, self.ctx_blocks, self.src_bt, self.dst_bt, self.nblocks, 0,
+                                 p.model.layers)
+            # header + final flag: a zero-layer-cost launch that only copies the control block
+            link.send_layers(self.dst, self.k_pool, self.v_pool, self.ctx_blocks, self.src_bt, self.dst_bt,
+                             torch.zeros_like(self.nblocks), 0, 1, hdr=self.hdr, final=True, num_ctas=1)
+            k1.record(self.side)
+        main.wait_stream(self.side)
+        torch.cuda.synchronize()
+        kv_bytes = 2 * self.ctx_blocks * p.model.layers * link.page_elems * 2
+        return StageReport("prefill", elapsed_ms=e0.elapsed_time(k1), compute_ms=e0.elapsed_time(e1), kv_ms=k0.elapsed_time(k1),
+                           kv_bytes=kv_bytes, tokens=p.batch_size * p.input_len)
+
+
+class DecodeStage:
+    def __init__(self, p: ServeParams, model: LlamaShard, link: KVLink):
+        self.p, self.model, self.link = p, model, link
+        dev = model.embed.device
+        B, mb = p.batch_size, p.max_blocks_per_req
+        self.bt = (torch.arange(B, dtype=torch.int32, device=dev).unsqueeze(1) * mb +
+                   torch.arange(mb, dtype=torch.int32, device=dev).unsqueeze(0)).contiguous()
+
+    def run(self) -> StageReport:
+        p, link = self.p, self.link
+        link.seq += 1
+        w0, w1, d1 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        w0.record()
+        link.wait_final()                       # header + every layer's pages have landed
+        w1.record()
+        hdr = link.hdr.local
+        tokens = hdr[4:4 + p.batch_size].clone()
+        torch.cuda.synchronize()
+        t_first = time.monotonic()              # first token is on the decode side: time-to-first-token ends here
+        out = [tokens]
+        pos = torch.full((p.batch_size,), p.input_len, dtype=torch.long, device=tokens.device)
+        for _ in range(p.num_decoding_step):
+            tokens = self.model.decode_step(tokens, pos, link.k_pool.local, link.v_pool.local, self.bt, link.pool_blocks)
+            out.append(tokens)
+            pos = pos + 1
+        d1.record()
+        torch.cuda.synchronize()
+        rep = StageReport("decode", elapsed_ms=w0.elapsed_time(d1), compute_ms=w1.elapsed_time(d1), kv_ms=w0.elapsed_time(w1),
+                          tokens=p.batch_size * p.num_decoding_step)
+        rep.extra["t_first_token"] = t_first
+        rep.extra["generated"] = torch.stack(out, 1)
+        return rep
+
+
+def make_prompts(p: ServeParams, device, seed: int = 0) -> torch.Tensor:
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randint(0, p.model.vocab, (p.batch_size, p.input_len), generator=g, device=device)
