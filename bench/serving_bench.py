@@ -1,0 +1,152 @@
+#!/usr/bin/env python
+"""Disaggregated serving: TTFT and decode tokens/s.
+
+Llama-3-8B-shaped random-init bf16 model, half of the GPUs prefill and half decode (TP = world/2 inside each
+stage), 16 prompts x 2048 tokens, 16-token pages, 256 greedy decode tokens.  KV moves prefill -> decode either
+with the fused pack+send kernel, layer by layer while the prefill is still running (--kv fuselink), or as the
+reference does it: whole K and V pools plus the small tensors in one NCCL group after the prefill (--kv nccl).
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 bench/serving_bench.py --kv fuselink
+    python bench/serving_bench.py --model tiny --emulate        # both stages on one GPU (functional check only)
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3_8b")
+    ap.add_argument("--kv", default="fuselink", choices=["fuselink", "fuselink-nopipe", "nccl"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--input-len", type=int, default=2048)
+    ap.add_argument("--decode-steps", type=int, default=256)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--emulate", action="store_true")
+    args = ap.parse_args()
+    from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    from fuselink_b200.serving.disagg import DecodeStage, KVLink, PrefillStage, ServeParams, make_prompts
+
+    rank = int(os.environ.get("RANK", 0)); local = int(os.environ.get("LOCAL_RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cfg = MODEL_ZOO[args.model]
+    if args.emulate or world == 1:
+        p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, 1)
+        net = LlamaShard(cfg, device=dev)
+        pool_bytes = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
+        heaps = SymmetricHeap.emulated(2, pool_bytes + (64 << 20), device=local)
+        links = [KVLink(h, p, net.kvh_local) for h in heaps]
+        pre = PrefillStage(p, net, links[0], 1, pipeline_layers=args.kv == "fuselink")
+        dec = DecodeStage(p, net, links[1])
+        prompts = make_prompts(p, dev)
+        res = []
+        for _ in range(args.iters):
+            torch.cuda.synchronize(); t0 = time.monotonic()
+            rp = pre.run(prompts); rd = dec.run()
+            res.append((rd.extra["t_first_token"] - t0, rp, rd))
+        ttft, rp, rd = res[-1]
+        print(json.dumps({"mode": "emulated-1gpu", "model": args.model, "ttft_ms": ttft * 1e3, "prefill_ms": rp.compute_ms,
+                          "kv_ms": rp.kv_ms, "kv_GB": rp.kv_bytes / 1e9, "decode_tok_s": rd.tokens / (rd.compute_ms / 1e3)}))
+        return
+    assert world % 2 == 0
+    dist.init_process_group("nccl", device_id=dev)
+    tp = world // 2
+    is_prefill = rank < tp
+    groups = [dist.new_group(list(range(0, tp))), dist.new_group(list(range(tp, world)))]
+    tp_group = groups[0] if is_prefill else groups[1]
+    tp_rank = rank % tp
+    p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, tp)
+    net = LlamaShard(cfg, tp_rank, tp, tp_group if tp > 1 else None, device=dev)
+    pool_elems = p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim
+    heap = SymmetricHeap.create(2 * pool_elems * 2 + (64 << 20), device=local)
+    link = KVLink(heap, p, net.kvh_local)
+    peer = rank + tp if is_prefill else rank - tp            # the reference's pairing: rank <-> rank + world/2
+    prompts = make_prompts(p, dev)
+    pre = PrefillStage(p, net, link, peer, pipeline_layers=args.kv == "fuselink") if is_prefill else None
+    dec = DecodeStage(p, net, link) if not is_prefill else None
+    out = None
+    for it in range(args.iters):
+        dist.barrier(); torch.cuda.synchronize()
+        t0 = time.monotonic()
+        if args.kv == "nccl":
+            out = _nccl_iteration(p, net, link, pre, dec, prompts, peer, is_prefill, t0)
+        elif is_prefill:
+            rp = pre.run(prompts)
+            out = {"prefill_ms": rp.compute_ms, "kv_ms": rp.kv_ms, "kv_GB": rp.kv_bytes / 1e9, "stage_ms": rp.elapsed_ms}
+        else:
+            rd = dec.run()
+            out = {"ttft_ms": (rd.extra["t_first_token"] - t0) * 1e3, "decode_ms": rd.compute_ms, "wait_ms": rd.kv_ms,
+                   "decode_tok_s": rd.tokens / (rd.compute_ms / 1e3)}
+        heap.check_status("serving")
+    gathered = [None] * world
+    dist.all_gather_object(gathered, out)
+    if rank == 0:
+        pre_o, dec_o = gathered[:tp], gathered[tp:]
+        line = {"metric": "disaggregated serving", "kv": args.kv, "model": args.model, "n_gpus": world, "tp": tp,
+                "batch": p.batch_size, "input_len": p.input_len, "decode_steps": p.num_decoding_step,
+                "ttft_ms": max(o["ttft_ms"] for o in dec_o), "decode_tok_s": min(o["decode_tok_s"] for o in dec_o),
+                "prefill_ms": max(o["prefill_ms"] for o in pre_o), "kv_ms_max": max(o["kv_ms"] for o in pre_o),
+                "kv_GB_per_rank": pre_o[0]["kv_GB"], "comm_over_elapsed": max(o["kv_ms"] for o in pre_o) / max(o["stage_ms"] for o in pre_o)}
+        print(json.dumps(line))
+    heap.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _nccl_iteration(p, net, link, pre, dec, prompts, peer, is_prefill, t0):
+    """The reference's hand-off (model.hh:280-309): one group of 5 sends after the whole prefill -- first tokens, K pool,
+    V pool, block table, block counts -- mirrored by 5 receives; the decoder then re-lays the pages out for its pool."""
+    cfg = p.model
+    B, cb, mb = p.batch_size, p.context_blocks_per_req, p.max_blocks_per_req
+    dev = prompts.device
+    kvh, bs, D, L = net.kvh_local, cfg.block_size, cfg.head_dim, cfg.layers
+    n = B * cb * L * kvh * bs * D
+    if is_prefill:
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        first = net.prefill(prompts, pre.k_pool, pre.v_pool, pre.src_bt, None)
+        e1.record()
+        ops = [dist.P2POp(dist.isend, t, peer) for t in (first, pre.k_pool, pre.v_pool, pre.src_bt, pre.nblocks)]
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+        e2.record()
+        torch.cuda.synchronize()
+        return {"prefill_ms": e0.elapsed_time(e1), "kv_ms": e1.elapsed_time(e2), "kv_GB": 2 * n * 2 / 1e9, "stage_ms": e0.elapsed_time(e2)}
+    first = torch.empty(B, dtype=torch.long, device=dev)
+    k_in = torch.empty(n, dtype=torch.bfloat16, device=dev); v_in = torch.empty_like(k_in)
+    bt = torch.empty(B, cb, dtype=torch.int32, device=dev); nb = torch.empty(B, dtype=torch.int32, device=dev)
+    w0, w1, d1 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+    w0.record()
+    ops = [dist.P2POp(dist.irecv, t, peer) for t in (first, k_in, v_in, bt, nb)]
+    for r in dist.batch_isend_irecv(ops):
+        r.wait()
+    # layout change into the decode pool: [blk][L][h][s][d] -> [L][blk'][s][h][d]
+    kd = link.k_pool.local.view(L, link.pool_blocks, bs, kvh, D); vd = link.v_pool.local.view(L, link.pool_blocks, bs, kvh, D)
+    dst_blocks = dec.bt[:, :cb].reshape(-1).long()
+    kd[:, dst_blocks] = k_in.view(B * cb, L, kvh, bs, D).permute(1, 0, 3, 2, 4)
+    vd[:, dst_blocks] = v_in.view(B * cb, L, kvh, bs, D).permute(1, 0, 3, 2, 4)
+    w1.record()
+    torch.cuda.synchronize()
+    t_first = time.monotonic()
+    tokens = first
+    pos = torch.full((B,), p.input_len, dtype=torch.long, device=dev)
+    for _ in range(p.num_decoding_step):
+        tokens = net.decode_step(tokens, pos, link.k_pool.local, link.v_pool.local, dec.bt, link.pool_blocks)
+        pos = pos + 1
+    d1.record()
+    torch.cuda.synchronize()
+    return {"ttft_ms": (t_first - t0) * 1e3, "decode_ms": w1.elapsed_time(d1), "wait_ms": w0.elapsed_time(w1),
+            "decode_tok_s": B * p.num_decoding_step / (w1.elapsed_time(d1) / 1e3)}
+
+
+if __name__ == "__main__":
+    main()

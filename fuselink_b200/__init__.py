@@ -14,3 +14,15 @@ Layers (bottom up):
 from ._ext import C, have_native, require_native  # noqa: F401
 
 __version__ = "0.1.0"
+
+
+def stats(selector=None) -> dict:
+    """Observability snapshot: cuMem bytes held per device and, when a selector is given, per-path state."""
+    out = {"native": have_native()}
+    if have_native():
+        out["vmm_backend"] = C.vmm_backend()
+        out["vmm_bytes"] = {d: C.vmm_usage(d) for d in range(8) if C.vmm_usage(d)}
+    if selector is not None:
+        out["paths"] = [vars(s) for s in selector.stats()]
+        out["selector"] = {"direct": selector.direct_answers, "relay": selector.relay_answers}
+    return out

@@ -1,0 +1,91 @@
+"""Failure detection without a GPU fault: every failure is made on the host (a rank that exits between steps,
+a dead path in the monitor, a process group whose collective times out)."""
+import datetime
+import os
+import socket
+import time
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fuselink_b200 import C, have_native
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _leaver(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    t = torch.ones(4)
+    dist.all_reduce(t)                      # step 0: everyone is here
+    if rank == 1:
+        dist.destroy_process_group()        # leaves BETWEEN steps, nothing in flight
+        return
+    t0 = time.time()
+    try:
+        dist.all_reduce(t)                  # step 1: the survivor's collective must end with an error, not hang
+        q.put(("no-error", time.time() - t0))
+    except Exception as e:                  # noqa: BLE001
+        q.put(("error", time.time() - t0, type(e).__name__))
+
+
+def test_rank_leaving_between_steps_is_detected_by_timeout():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_leaver, args=(r, 2, _free_port() if r == 0 else 0, q)) for r in range(2)]
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver, args=(r, 2, port, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = q.get(timeout=60)
+    [p.join(timeout=30) for p in procs]
+    assert res[0] == "error" and res[1] < 30, res
+
+
+@pytest.mark.skipif(not have_native(), reason="native extension not built")
+def test_dead_path_is_routed_around_and_recovers():
+    from fuselink_b200.parallel.selector import PathSelector
+    os.environ["NCCL_FUSELINK_DEGREE"] = "3"
+    os.environ["FUSELINK_MIN_STRIPE_BYTES"] = str(1 << 20)
+    try:
+        sel = PathSelector(4)
+        plan = sel.plan(0, 1, 64 << 20)
+        assert {p for p, _, _ in plan} == {1, 2, 3}
+        sel.complete(0, 1, 64 << 20, plan)
+        sel.mark_dead(2)
+        for _ in range(5):
+            plan = sel.plan(0, 1, 64 << 20)
+            assert 2 not in {p for p, _, _ in plan}, "a dead relay must never be selected"
+            assert sum(b for _, _, b in plan) == 64 << 20
+            sel.complete(0, 1, 64 << 20, plan)
+        sel.mark_dead(2, False)
+        time.sleep(0.01)
+        seen = set()
+        for _ in range(6):
+            plan = sel.plan(0, 1, 64 << 20)
+            seen |= {p for p, _, _ in plan}
+            sel.complete(0, 1, 64 << 20, plan)
+        assert 2 in seen, "a revived path is used again"
+        sel.close()
+    finally:
+        os.environ.pop("NCCL_FUSELINK_DEGREE")
+        os.environ.pop("FUSELINK_MIN_STRIPE_BYTES")
+
+
+@pytest.mark.skipif(not have_native(), reason="native extension not built")
+def test_crashed_borrower_releases_its_lease_by_timeout():
+    m = C.monitor_open("", True, 4, 1, 160)
+    t = C.monitor_now_ns()
+    p = C.monitor_borrow_idle(m, 0, 0, 0, 0xF, t)
+    assert p >= 0 and C.monitor_status(m, 0, p) == 2
+    # the borrower "crashes": no release, no stamps.  One lease period later the path is idle again.
+    C.monitor_sweep(m, t + 161_000)
+    assert C.monitor_status(m, 0, p) == 0
+    C.monitor_close(m, False)
