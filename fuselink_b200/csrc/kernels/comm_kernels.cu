@@ -7,6 +7,7 @@
 // publishes a flag per chunk, so a relay GPU can forward chunk c while chunk c+1 is still in flight.
 #include "comm_kernels.cuh"
 #include "../common/fl_ptx.cuh"
+#include <string.h>
 
 namespace fl {
 
@@ -124,6 +125,8 @@ __global__ void __launch_bounds__(1024) put_chunks_kernel(const FlPutArgs a) {
     }
     chunks_before += nch;
   }
+  if (blockIdx.x == 0 && (int)threadIdx.x < a.nwait)
+    wait_flag_ge(a.wait_flag[threadIdx.x], a.wait_want[threadIdx.x], a.status, 650 + threadIdx.x);
 }
 
 __global__ void wait_flags_kernel(const FlWaitArgs a) {
@@ -160,6 +163,34 @@ extern "C" int fl_put_chunks(const FlPutArgs* args, int num_ctas, int threads, c
   }
   fl::put_chunks_kernel<<<num_ctas, threads, smem, stream>>>(*args);
   return (int)cudaGetLastError();
+}
+
+extern "C" int fl_all_to_all(const void* send, void* const* recv_peers, unsigned long long bytes_per_peer, int rank,
+                             int world, FlSignalPtrs pads, int slot0, unsigned int chunk_bytes, const unsigned int* want,
+                             int use_bulk, int num_ctas, int threads, int* status, cudaStream_t stream) {
+  if (world < 1 || world > FL_MAX_SEGS) return -1;
+  FlPutArgs a;
+  memset(&a, 0, sizeof a);
+  a.nseg = world;
+  for (int k = 0; k < world; ++k) {
+    const int p = (rank + k) % world;   // own block first, then walk the ring so peers are hit evenly
+    a.seg[k].src = reinterpret_cast<const uint8_t*>(send) + (unsigned long long)p * bytes_per_peer;
+    a.seg[k].dst = reinterpret_cast<uint8_t*>(recv_peers[p]) + (unsigned long long)rank * bytes_per_peer;
+    a.seg[k].bytes = bytes_per_peer;
+    a.seg[k].flags = pads.p[p] + slot0 + rank;
+    a.seg[k].flag_mode = FL_FLAG_COUNT;
+  }
+  a.chunk_bytes = chunk_bytes;
+  a.use_bulk = use_bulk;
+  a.status = status;
+  if (want) {
+    a.nwait = world;
+    for (int r = 0; r < world; ++r) {
+      a.wait_flag[r] = pads.p[rank] + slot0 + r;
+      a.wait_want[r] = want[r];
+    }
+  }
+  return fl_put_chunks(&a, num_ctas, threads, stream);
 }
 
 extern "C" int fl_wait_flags(const FlWaitArgs* args, cudaStream_t stream) {

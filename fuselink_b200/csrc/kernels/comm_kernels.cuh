@@ -35,6 +35,12 @@ struct FlPutArgs {
   unsigned int seq;
   int use_bulk;               // 1: cp.async.bulk global->smem->global engine, 0: ld/st vectors
   int* status;
+  // optional tail: after its own copies CTA 0 waits until wait_flag[i] >= wait_want[i] for i < nwait, so one
+  // launch is "my data is on its way AND everybody's data for me has arrived" (multi-GPU only: the peers'
+  // kernels run on other GPUs)
+  const uint32_t* wait_flag[8];
+  unsigned int wait_want[8];
+  int nwait;
 };
 
 struct FlWaitArgs {
@@ -53,6 +59,12 @@ extern "C" {
 #endif
 int fl_put_chunks(const FlPutArgs* args, int num_ctas, int threads, cudaStream_t stream);
 int fl_wait_flags(const FlWaitArgs* args, cudaStream_t stream);
+// Uniform all-to-all in one launch: block p of `send` ([world, bytes_per_peer]) goes to recv_peers[p] + rank *
+// bytes_per_peer; arrival counters live at pads.p[dst][slot0 + src]; with want != NULL the launch also waits
+// until the local counters reach want[src] (cumulative chunk counts kept by the caller).
+int fl_all_to_all(const void* send, void* const* recv_peers, unsigned long long bytes_per_peer, int rank, int world,
+                  FlSignalPtrs pads, int slot0, unsigned int chunk_bytes, const unsigned int* want, int use_bulk,
+                  int num_ctas, int threads, int* status, cudaStream_t stream);
 // every rank: pads.p[r][slot0 + rank] = seq for all r, then wait pads.p[rank][slot0 + r] >= seq for all r
 int fl_barrier(FlSignalPtrs pads, int slot0, int rank, int world, unsigned int seq, int do_signal, int do_wait,
                int* status, cudaStream_t stream);

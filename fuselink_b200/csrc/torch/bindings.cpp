@@ -85,6 +85,24 @@ static void put_chunks(const std::vector<std::tuple<int64_t, int64_t, int64_t, i
   a.status = reinterpret_cast<int*>(status_addr);
   check_rc(fl_put_chunks(&a, (int)num_ctas, (int)threads, cur_stream()), "fl_put_chunks");
 }
+static void all_to_all(int64_t send_addr, const std::vector<int64_t>& recv_peers, int64_t bytes_per_peer, int64_t rank,
+                       const std::vector<int64_t>& pads, int64_t slot0, int64_t chunk_bytes,
+                       const std::vector<int64_t>& want, bool use_bulk, int64_t num_ctas, int64_t threads, int64_t status_addr) {
+  const int world = (int)recv_peers.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && (int)pads.size() == world, "1..8 ranks");
+  void* rp[8];
+  FlSignalPtrs sp;
+  memset(&sp, 0, sizeof sp);
+  unsigned int w[8];
+  for (int i = 0; i < world; ++i) {
+    rp[i] = reinterpret_cast<void*>(recv_peers[i]);
+    sp.p[i] = reinterpret_cast<uint32_t*>(pads[i]);
+    if (!want.empty()) w[i] = (unsigned)want[i];
+  }
+  check_rc(fl_all_to_all(reinterpret_cast<const void*>(send_addr), rp, (unsigned long long)bytes_per_peer, (int)rank, world, sp,
+                         (int)slot0, (unsigned)chunk_bytes, want.empty() ? nullptr : w, use_bulk, (int)num_ctas, (int)threads,
+                         reinterpret_cast<int*>(status_addr), cur_stream()), "fl_all_to_all");
+}
 static void wait_flags(const std::vector<std::pair<int64_t, int64_t>>& flags, int64_t status_addr) {
   FlWaitArgs a;
   memset(&a, 0, sizeof a);
@@ -241,6 +259,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &grouped_gemm);
   m.def("put_chunks", &put_chunks);
   m.def("wait_flags", &wait_flags);
+  m.def("all_to_all", &all_to_all);
   m.def("barrier", &barrier);
   m.def("embbag", &embbag);
   m.def("kv_pack_send", &kv_pack_send);

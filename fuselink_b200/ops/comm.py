@@ -25,26 +25,41 @@ _NUM_SMS = 148
 def chunking(nbytes: int, chunk_bytes: Optional[int] = None) -> Tuple[int, int]:
     """(chunk_bytes, number_of_chunks) both sides of a transfer agree on.
 
-    Large messages use the configured chunk (512 KiB, the reference's NCCL_P2P_NET_CHUNKSIZE setting); small
-    ones are cut so that a few hundred CTAs still share the work, never below 16 KiB.
+    Large messages use the configured chunk (512 KiB, the reference's NCCL_P2P_NET_CHUNKSIZE setting); smaller
+    ones are cut so that every SM gets about one chunk, never below 64 KiB.
     """
-    cfg = chunk_bytes or knobs().chunk_bytes
+    cfg = chunk_bytes or _chunk_default()
     if nbytes <= 0:
         return cfg, 0
     c = cfg
-    while c > 16 * 1024 and nbytes // c < 2 * _NUM_SMS:
+    # about one chunk per SM for mid sizes; a chunk is never cut below 64 KiB (a CTA streams it through a ring of
+    # 16 KiB slots, and every chunk costs one remote flag update)
+    while c > 64 * 1024 and nbytes // c < _NUM_SMS:
         c //= 2
     c = max(16, (c + 15) // 16 * 16)
     return c, (nbytes + c - 1) // c
 
 
+_CHUNK_DEFAULT = None
+
+
+def _chunk_default() -> int:
+    global _CHUNK_DEFAULT
+    if _CHUNK_DEFAULT is None:
+        _CHUNK_DEFAULT = knobs().chunk_bytes
+    return _CHUNK_DEFAULT
+
+
+_COPY_CTAS = None
+
+
 def _launch_shape(total_chunks: int, engine: str) -> Tuple[int, int]:
-    k = knobs()
+    global _COPY_CTAS
+    if _COPY_CTAS is None:
+        _COPY_CTAS = knobs().copy_ctas
     if engine == "bulk":
-        ctas = k.copy_ctas or min(max(total_chunks, 1), 3 * _NUM_SMS)
-        return ctas, 32
-    ctas = k.copy_ctas or min(max(total_chunks, 1), 2 * _NUM_SMS)
-    return ctas, 512
+        return _COPY_CTAS or min(max(total_chunks, 1), 3 * _NUM_SMS), 32
+    return _COPY_CTAS or min(max(total_chunks, 1), 2 * _NUM_SMS), 512
 
 
 class Channel:
@@ -126,15 +141,12 @@ def all_to_all(chan: Channel, send: torch.Tensor, recv: SymTensor, wait: bool = 
     assert send.shape[0] == W and send.is_contiguous()
     per = send[0].numel() * send.element_size()
     cb, n = chunking(per)
-    items = []
-    for k in range(W):
-        p = (heap.rank + k) % W   # start with the own block, then walk the ring so peers are hit evenly
-        items.append((send[p].data_ptr(), p, recv.offset + heap.rank * per, per))
-    chan.put_many(items, cb)
     for r in range(W):
-        chan.expect_chunks(r, n)
-    if wait:
-        chan.wait()
+        chan.expected[r] += n
+    ctas, threads = _launch_shape(n * W, chan.engine)
+    want = [e & 0xFFFFFFFF for e in chan.expected] if wait else []
+    chan.C.all_to_all(send.data_ptr(), recv.peers(), per, heap.rank, heap.pads(), chan.slot0, cb, want,
+                      chan.engine == "bulk", ctas, threads, heap.status_addr)
 
 
 def all_to_all_v(chan: Channel, send: torch.Tensor, send_offsets: Sequence[int], send_bytes: Sequence[int],

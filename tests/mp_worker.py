@@ -1,0 +1,106 @@
+"""Worker of tests/test_multigpu.py: one process per GPU (torchrun).  Checks, against NCCL / PyTorch results
+computed in the same job, the symmetric heap, p2p put, all-to-all, the MoE expert-parallel step and the DLRM step."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    rank, local, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from fuselink_b200.models.dlrm import DLRM, DLRMConfig, synthetic_batch
+    from fuselink_b200.models.dlrm_baseline import BaselineDLRM
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.models.moe_baseline import BaselineMoELayer
+    from fuselink_b200.ops.comm import Channel, all_to_all, barrier
+    from fuselink_b200.ops.moe import MoEConfig
+    from fuselink_b200.parallel.symm import SymmetricHeap
+
+    heap = SymmetricHeap.create(512 << 20, device=local)
+    # ---- p2p ring: rank r -> r+1 -------------------------------------------------------------------------
+    for engine in ("ldst", "bulk"):
+        ch = Channel(heap, f"ring-{engine}", engine=engine)
+        n = (3 << 20) + 48
+        dst = heap.alloc_tensor([n], torch.uint8)
+        src = torch.randint(0, 255, (n,), dtype=torch.uint8, device=dev, generator=torch.Generator(device=dev).manual_seed(rank))
+        ch.put(src, (rank + 1) % world, dst.offset)
+        ch.expect((rank - 1) % world, n)
+        ch.wait([(rank - 1) % world])
+        torch.cuda.synchronize()
+        want = torch.randint(0, 255, (n,), dtype=torch.uint8, device=dev, generator=torch.Generator(device=dev).manual_seed((rank - 1) % world))
+        assert torch.equal(dst.local, want), f"p2p {engine} mismatch on rank {rank}"
+        # ---- all-to-all vs NCCL --------------------------------------------------------------------------
+        per = 100_000
+        send = torch.randn(world, per, device=dev)
+        recv = heap.alloc_tensor([world, per], torch.float32)
+        ref = torch.empty(world * per, device=dev)
+        for _ in range(3):
+            all_to_all(ch, send, recv)
+            dist.all_to_all_single(ref, send.view(-1))
+            torch.cuda.synchronize()
+            assert torch.equal(recv.local.view(-1), ref), f"all-to-all {engine} mismatch on rank {rank}"
+            barrier(heap, "a2a-reuse")          # the receive buffer is reused by the next round
+    heap.check_status("comm")
+
+    # ---- MoE: fused path vs the PyTorch + NCCL formulation, same weights, same inputs ----------------------
+    cfg = MoEConfig(hidden=512, ffn=1024, num_experts=8, topk=2, tokens=768)
+    fused = MoELayer(cfg, heap, rank, world, device=dev, seed=4, fused_sgd_lr=0.0)
+    base = BaselineMoELayer(cfg, rank, world, device=dev, seed=4)
+    for step in range(2):
+        g = torch.Generator(device=dev).manual_seed(50 + step * 10 + rank)
+        x = torch.randn(cfg.tokens, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+        xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+        oa, ob = fused(xa), base(xb)
+        (oa.float().pow(2).mean()).backward()
+        (ob.float().pow(2).mean()).backward()
+        torch.cuda.synchronize()
+        heap.check_status("moe")
+
+        def close(a, b, what, tol=5e-2):
+            err = (a.float() - b.float()).abs().max().item()
+            den = b.float().abs().max().item() + 1e-6
+            assert err < tol * den, f"rank {rank} step {step} {what}: err {err} vs {den}"
+
+        close(oa, ob, "out")
+        close(xa.grad, xb.grad, "dx")
+        close(fused.router.grad, base.router.grad, "drouter", 8e-2)
+        from fuselink_b200.ops import gemm
+        dg, du = gemm.deinterleave_gate_up(fused.w13.grad)
+        F = cfg.ffn
+        close(dg, base.w13.grad[:, :F], "dWgate")
+        close(du, base.w13.grad[:, F:], "dWup")
+        close(fused.w2.grad, base.w2.grad, "dW2")
+        for m in (fused, base):
+            m.zero_grad(set_to_none=True)
+
+    # ---- DLRM: fused embedding-bag + all-to-all vs EmbeddingBag + NCCL ------------------------------------
+    dcfg = DLRMConfig(num_tables=10, rows=4000, dim=128, pooling=20, global_batch=64 * world, lr=0.05)
+    a = DLRM(dcfg, heap, rank, world, device=dev, seed=9)
+    b = BaselineDLRM(dcfg, rank, world, device=dev, seed=9)
+    b.tables.copy_(a.tables)
+    b.bottom.load_state_dict(a.bottom.state_dict())
+    b.top.load_state_dict(a.top.state_dict())
+    oa_, ob_ = torch.optim.SGD(a.dense_parameters(), lr=dcfg.lr), torch.optim.SGD(b.dense_parameters(), lr=dcfg.lr)
+    for step in range(3):
+        d, i, l = synthetic_batch(dcfg, rank, world, dev, seed=step)
+        la, lb = a.train_step(d, i, l, oa_), b.train_step(d, i, l, ob_)
+        assert abs(float(la) - float(lb)) < 1e-4, (rank, step, float(la), float(lb))
+    torch.cuda.synchronize()
+    heap.check_status("dlrm")
+    torch.testing.assert_close(a.tables, b.tables, rtol=1e-4, atol=1e-6)
+
+    dist.barrier()
+    heap.close()
+    if rank == 0:
+        print("MULTIGPU-OK world", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

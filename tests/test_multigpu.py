@@ -1,0 +1,22 @@
+"""Real multi-GPU run of the peer-memory paths (one process per GPU, NVLS off, plain peer loads/stores).
+Skipped on a box with fewer than two GPUs."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_two_or_more_gpus_against_nccl():
+    n = min(torch.cuda.device_count(), 8)
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29611", os.path.join(here, "mp_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0 and "MULTIGPU-OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
