@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (non-multicast only), tcgen05/TMEM,
 // system-scope release/acquire flags used between GPUs, and bounded spin-waits.
 //
-// Every wait in this library is bounded: after FL_SPIN_LIMIT polls the waiter records an error code
+// Every wait in this library is bounded by wall time (FL_WAIT_NS / FL_FLAG_WAIT_NS): on expiry the waiter records an error code
 // in a status word and returns false, the caller unwinds (drains its own async copies, frees TMEM)
 // and the kernel returns normally.  Nothing here traps, asserts or spins forever.
 #pragma once
@@ -10,7 +10,10 @@
 #include <stdint.h>
 
 #ifndef FL_WAIT_NS
-#define FL_WAIT_NS 2000000000ull  // every device-side wait gives up after 2 s of wall time
+#define FL_WAIT_NS 2000000000ull        // waits inside one kernel (mbarriers) give up after 2 s of wall time
+#endif
+#ifndef FL_FLAG_WAIT_NS
+#define FL_FLAG_WAIT_NS 10000000000ull  // waits on another GPU's flag give up after 10 s (ranks may start skewed)
 #endif
 
 namespace fl {
@@ -90,7 +93,7 @@ __device__ __forceinline__ void fence_sys() { asm volatile("fence.acq_rel.sys;" 
 
 // Spin until *p >= want (monotone counters / epochs).  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t want, int* status, int where,
-                                             uint64_t limit_ns = FL_WAIT_NS) {
+                                             uint64_t limit_ns = FL_FLAG_WAIT_NS) {
   if ((int32_t)(ld_acquire_sys(p) - want) >= 0) return true;
   uint64_t t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));

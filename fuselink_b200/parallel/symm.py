@@ -184,6 +184,26 @@ class SymmetricHeap:
         self._state["seq"][key] = v
         return v
 
+    def host_wait(self, slot: int, want: int, timeout_s: float = 120.0, poll_s: float = 0.0002) -> bool:
+        """Poll one of this rank's signal words from the HOST until it reaches ``want`` (4-byte device->host copies on
+        a private stream).  For waits that may last long (a decoder waiting for a prefill): no kernel spins on the GPU
+        meanwhile.  Returns False on timeout."""
+        import time as _time
+        if not hasattr(self, "_poll_stream"):
+            self._poll_stream = torch.cuda.Stream(device=self.device)
+            self._poll_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        word = self.tensor(4 * slot, [1], torch.int32)
+        t0 = _time.monotonic()
+        while True:
+            with torch.cuda.stream(self._poll_stream):
+                self._poll_host.copy_(word, non_blocking=True)
+            self._poll_stream.synchronize()
+            if ((int(self._poll_host[0]) - want) & 0xFFFFFFFF) < 0x80000000:
+                return True
+            if _time.monotonic() - t0 > timeout_s:
+                return False
+            _time.sleep(poll_s)
+
     # ------------------------------------------------------------------ status
     @property
     def status_addr(self) -> int:

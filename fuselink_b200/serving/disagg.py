@@ -84,7 +84,11 @@ class KVLink:
                             num_ctas, self.heap.status_addr)
 
     # ---- decode side --------------------------------------------------------------------------------------
-    def wait_final(self):
+    def wait_final(self, host_timeout_s: float = 300.0):
+        """Wait for the header + all pages of hand-off number ``seq``.  The long part of the wait is a host poll (the
+        prefill may take seconds); the device wait that follows only orders later kernels after the flag."""
+        if not self.heap.host_wait(self.final_flag, self.seq, host_timeout_s):
+            raise TimeoutError(f"KV hand-off {self.seq} did not arrive within {host_timeout_s} s")
         self.C.wait_flags([(self.heap.sig_addr(self.final_flag), self.seq)], self.heap.status_addr)
 
     def wait_layer(self, l: int):
