@@ -18,8 +18,8 @@ import torch.distributed as dist
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--lo", type=int, default=10)
-    ap.add_argument("--hi", type=int, default=27)
+    ap.add_argument("--size-lo", type=int, default=10)
+    ap.add_argument("--size-hi", type=int, default=27)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--out", default="")
@@ -30,7 +30,7 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     from fuselink_b200.ops.comm import Channel, all_to_all
     from fuselink_b200.parallel.symm import SymmetricHeap
-    maxb = 1 << args.hi
+    maxb = 1 << args.size_hi
     heap = SymmetricHeap.create(world * maxb + (64 << 20), device=local)
     recv = heap.alloc_tensor([world, maxb], torch.uint8)
     send = torch.randint(0, 255, (world, maxb), dtype=torch.uint8, device=dev)
@@ -53,7 +53,7 @@ def main():
         return float(t)
 
     from fuselink_b200.parallel.symm import SymTensor
-    for lg in range(args.lo, args.hi + 1):
+    for lg in range(args.size_lo, args.size_hi + 1):
         per = 1 << lg
         row = {"per_pair_bytes": per, "world": world}
         s = send[:, :per].contiguous()
@@ -68,7 +68,7 @@ def main():
         row["nccl_busGBs"] = per * (world - 1) / ms / 1e6
         row["nccl_us"] = ms * 1e3
         heap.check_status("a2a sweep")
-        if lg == args.lo:
+        if lg == args.size_lo:
             assert torch.equal(rview.local.view(-1), out), "all-to-all result differs from NCCL"
         if rank == 0:
             print(json.dumps(row), flush=True)

@@ -5,7 +5,7 @@ powers of two, 20 warm-up + 100 timed iterations, device-timed, max over the par
 Arms: this library's chunked put (ld/st and bulk-copy engines), the striped relay variant over idle GPUs
 (--relays), and NCCL send/recv on the same box.
 
-    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/p2p_sweep.py [--pairs 1] [--hi 30]
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/p2p_sweep.py [--pairs 1] [--size-hi 30]
 """
 import argparse
 import json
@@ -21,8 +21,8 @@ import torch.distributed as dist
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--pairs", type=int, default=1)
-    ap.add_argument("--lo", type=int, default=10)
-    ap.add_argument("--hi", type=int, default=30)
+    ap.add_argument("--size-lo", type=int, default=10)
+    ap.add_argument("--size-hi", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--relays", type=int, default=0, help="idle GPUs used as relays for the striped arm")
@@ -36,7 +36,7 @@ def main():
     from fuselink_b200.ops.comm import Channel, StripedP2P, barrier
     from fuselink_b200.parallel.symm import SymmetricHeap
     assert 2 * args.pairs <= world
-    maxb = 1 << args.hi
+    maxb = 1 << args.size_hi
     heap = SymmetricHeap.create(2 * maxb + (512 << 20 if args.relays else 0) + (64 << 20), device=local)
     dstbuf = heap.alloc_tensor([maxb], torch.uint8)
     chans = {e: Channel(heap, f"p2p-{e}", engine=e) for e in ("ldst", "bulk")}
@@ -63,7 +63,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t)
 
-    for lg in range(args.lo, args.hi + 1):
+    for lg in range(args.size_lo, args.size_hi + 1):
         nbytes = 1 << lg
         row = {"bytes": nbytes}
         view = src.view(torch.uint8)[:nbytes]

@@ -2,7 +2,8 @@
 //
 //   warp 0      : TMA producer  (cp.async.bulk.tensor, never multicast; operands are always local memory)
 //   warp 1      : MMA issuer    (tcgen05.mma kind::f16, one elected thread), owns the TMEM allocation
-//   warps 2..5  : epilogue      (tcgen05.ld -> registers -> fused epilogue -> global / peer stores)
+//   warps 2..9  : epilogue      (tcgen05.ld -> registers -> fused epilogue -> global / peer stores); two warps
+//                 share each TMEM lane quadrant and split the tile's columns
 //
 // One CTA per SM walks a tile list that is derived on the device from the per-expert row counts, so the
 // host never has to read the routing result back.  Tile = 128 x 256 fp32 accumulator in TMEM, two
@@ -33,7 +34,7 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * ROW_BYTES;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * ROW_BYTES;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_THREADS = 320;           // 1 TMA warp + 1 MMA warp + 8 epilogue warps
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers, counts*/;
 
@@ -163,7 +164,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&sh->tmem_full[a], 1);
-      mbar_init(&sh->tmem_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&sh->tmem_empty[a], 8);  // one arrival per epilogue warp
     }
     sh->abort_flag = 0;
     mbar_fence_init();
@@ -265,8 +266,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    // ------------------------------------------------------------------ epilogue (8 warps, 128 rows x 2 column halves)
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     uint32_t tile_i = 0;
     bool ok = true;
     Tile t;
@@ -301,7 +303,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           dst = p.C + (long long)t.g * p.gsc + (long long)row * p.ldc;
         }
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
           uint32_t r[32];
           float v[32];
           if (have_acc) {
@@ -336,7 +338,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         __nv_bfloat16* act = p.C + grow * p.ldc + t.n0 / 2;
         __nv_bfloat16* gu = p.gu ? p.gu + grow * p.ldgu + t.n0 : nullptr;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = half * 2; c < half * 2 + 2; ++c) {
           uint32_t rg[32], ru[32];
           tmem_ld_32x32(t_addr + c * 32, rg);
           tmem_ld_32x32(t_addr + 128 + c * 32, ru);
@@ -360,34 +362,69 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool valid = r_in_tile < t.rows;
         const bool zero_row = !valid && p.zero_tail && row < p.cap;
         const long long grow = (long long)t.g * p.cap + row;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        // Saved gate/up of the next 32-column chunk are fetched (packed bf16, 2 x 64 B) while the current chunk's
+        // accumulator read and math are in flight, so the global-load latency is paid once per tile, not per chunk.
+        const int c0 = half * (BN / 64), c1 = c0 + BN / 64;
+        auto gate_col = [&](int c) {
+          const int a_col = t.n0 + c * 32;                          // column of dAct
+          return (long long)(a_col >> 7) * 256 + (a_col & 127);     // gate position in the interleaved row; up is +128
+        };
+        const __nv_bfloat16* gu_row = p.gu + grow * p.ldgu;
+        __nv_bfloat16* dgu_row = p.dgu + grow * p.ldgu;
+        uint4 gq[4], uq[4];
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            gq[i] = ld_v4(gu_row + gate_col(c0) + 8 * i);
+            uq[i] = ld_v4(gu_row + gate_col(c0) + 128 + 8 * i);
+          }
+        }
+#pragma unroll
+        for (int c = c0; c < c1; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t_addr + c * 32, r);
-          tmem_ld_wait();
-          const int a_col = t.n0 + c * 32;                        // column of dAct
-          const int blk = a_col >> 7, within = a_col & 127;       // 128-wide gate/up block
-          const long long gcol = (long long)blk * 256 + within;   // gate position; up is +128
-          if (valid) {
-            float g[32], u[32], dg[32], du[32];
-            load32_bf16(p.gu + grow * p.ldgu + gcol, g);
-            load32_bf16(p.gu + grow * p.ldgu + gcol + 128, u);
+          uint4 gn[4], un[4];
+          if (valid && c + 1 < c1) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const float da = __uint_as_float(r[i]);
-              const float sg = 1.f / (1.f + __expf(-g[i]));
-              const float sl = g[i] * sg;
-              dg[i] = da * u[i] * (sg * (1.f + g[i] * (1.f - sg)));
-              du[i] = da * sl;
+            for (int i = 0; i < 4; ++i) {
+              gn[i] = ld_v4(gu_row + gate_col(c + 1) + 8 * i);
+              un[i] = ld_v4(gu_row + gate_col(c + 1) + 128 + 8 * i);
             }
-            store32_bf16(p.dgu + grow * p.ldgu + gcol, dg);
-            store32_bf16(p.dgu + grow * p.ldgu + gcol + 128, du);
+          }
+          tmem_ld_wait();
+          const long long gcol = gate_col(c);
+          if (valid) {
+            float dg[32], du[32];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t gw[4] = {gq[i].x, gq[i].y, gq[i].z, gq[i].w};
+              const uint32_t uw[4] = {uq[i].x, uq[i].y, uq[i].z, uq[i].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float g0, g1, u0, u1;
+                unpack_bf16(gw[j], g0, g1);
+                unpack_bf16(uw[j], u0, u1);
+                const int e = 8 * i + 2 * j;
+                const float da0 = __uint_as_float(r[e]), da1 = __uint_as_float(r[e + 1]);
+                const float s0 = 1.f / (1.f + __expf(-g0)), s1 = 1.f / (1.f + __expf(-g1));
+                dg[e] = da0 * u0 * (s0 * (1.f + g0 * (1.f - s0)));
+                dg[e + 1] = da1 * u1 * (s1 * (1.f + g1 * (1.f - s1)));
+                du[e] = da0 * g0 * s0;
+                du[e + 1] = da1 * g1 * s1;
+              }
+            }
+            store32_bf16(dgu_row + gcol, dg);
+            store32_bf16(dgu_row + gcol + 128, du);
           } else if (zero_row) {
             float z[32];
 #pragma unroll
             for (int i = 0; i < 32; ++i) z[i] = 0.f;
-            store32_bf16(p.dgu + grow * p.ldgu + gcol, z);
-            store32_bf16(p.dgu + grow * p.ldgu + gcol + 128, z);
+            store32_bf16(dgu_row + gcol, z);
+            store32_bf16(dgu_row + gcol + 128, z);
+          }
+          if (c + 1 < c1) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { gq[i] = gn[i]; uq[i] = un[i]; }
           }
         }
       }

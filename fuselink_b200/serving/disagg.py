@@ -170,36 +170,86 @@ class PrefillStage:
 
 
 class DecodeStage:
-    def __init__(self, p: ServeParams, model: LlamaShard, link: KVLink):
+    """Greedy decoding over the paged pool.  The per-token step is launch-bound (hundreds of small kernels), so it
+    is captured once in a CUDA graph and replayed; ``use_graph=False`` keeps the eager loop."""
+
+    def __init__(self, p: ServeParams, model: LlamaShard, link: KVLink, use_graph: bool = True):
         self.p, self.model, self.link = p, model, link
         dev = model.embed.device
         B, mb = p.batch_size, p.max_blocks_per_req
         self.bt = (torch.arange(B, dtype=torch.int32, device=dev).unsqueeze(1) * mb +
                    torch.arange(mb, dtype=torch.int32, device=dev).unsqueeze(0)).contiguous()
+        self.use_graph = use_graph
+        self.graph = None
+        self.g_tokens = torch.zeros(B, dtype=torch.long, device=dev)
+        self.g_pos = torch.zeros(B, dtype=torch.long, device=dev)
+        self.g_out = None
 
-    def run(self) -> StageReport:
-        p, link = self.p, self.link
-        link.seq += 1
-        w0, w1, d1 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-        w0.record()
-        link.wait_final()                       # header + every layer's pages have landed
-        w1.record()
-        hdr = link.hdr.local
-        tokens = hdr[4:4 + p.batch_size].clone()
-        torch.cuda.synchronize()
-        t_first = time.monotonic()              # first token is on the decode side: time-to-first-token ends here
+    def _step(self, tokens, pos):
+        link = self.link
+        return self.model.decode_step(tokens, pos, link.k_pool.local, link.v_pool.local, self.bt, link.pool_blocks)
+
+    def _capture(self):
+        """Capture one decode step on static buffers.  The step writes K/V at g_pos, so the capture (which runs the
+        step for real during warm-up) is done at a scratch position that the first real step overwrites anyway."""
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._step(self.g_tokens, self.g_pos)
+            torch.cuda.current_stream().wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self.g_out = self._step(self.g_tokens, self.g_pos)
+            self.graph = g
+        except Exception as e:  # noqa: BLE001 - capture is an optimisation; the eager loop is always valid
+            self.graph = None
+            self.use_graph = False
+            print(f"[fuselink] decode graph capture failed ({type(e).__name__}: {e}); running eagerly")
+
+    def decode(self, tokens: torch.Tensor):
+        """Generate num_decoding_step tokens after `tokens` ([B] first tokens).  Returns (generated [B, 1+steps],
+        device ms of the loop)."""
+        p = self.p
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         out = [tokens]
         pos = torch.full((p.batch_size,), p.input_len, dtype=torch.long, device=tokens.device)
+        if self.use_graph and self.graph is None:
+            self.g_tokens.copy_(tokens)
+            self.g_pos.copy_(pos)
+            self._capture()                     # one-off set-up, outside the timed loop
+        d0.record()
         for _ in range(p.num_decoding_step):
-            tokens = self.model.decode_step(tokens, pos, link.k_pool.local, link.v_pool.local, self.bt, link.pool_blocks)
+            if self.graph is not None:
+                self.g_tokens.copy_(tokens)
+                self.g_pos.copy_(pos)
+                self.graph.replay()
+                tokens = self.g_out.clone()
+            else:
+                tokens = self._step(tokens, pos)
             out.append(tokens)
             pos = pos + 1
         d1.record()
         torch.cuda.synchronize()
-        rep = StageReport("decode", elapsed_ms=w0.elapsed_time(d1), compute_ms=w1.elapsed_time(d1), kv_ms=w0.elapsed_time(w1),
+        return torch.stack(out, 1), d0.elapsed_time(d1)
+
+    def run(self) -> StageReport:
+        p, link = self.p, self.link
+        link.seq += 1
+        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0.record()
+        link.wait_final()                       # header + every layer's pages have landed
+        w1.record()
+        tokens = link.hdr.local[4:4 + p.batch_size].clone()
+        torch.cuda.synchronize()
+        t_first = time.monotonic()              # first token is on the decode side: time-to-first-token ends here
+        gen, ms = self.decode(tokens)
+        rep = StageReport("decode", elapsed_ms=w0.elapsed_time(w1) + ms, compute_ms=ms, kv_ms=w0.elapsed_time(w1),
                           tokens=p.batch_size * p.num_decoding_step)
         rep.extra["t_first_token"] = t_first
-        rep.extra["generated"] = torch.stack(out, 1)
+        rep.extra["generated"] = gen
+        rep.extra["graph"] = self.graph is not None
         return rep
 
 
