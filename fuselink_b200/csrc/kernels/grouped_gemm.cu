@@ -23,6 +23,7 @@
 #include "../common/fl_ptx.cuh"
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace fl {
@@ -56,6 +57,7 @@ struct KParams {
 
 struct Tile {
   int g, m0, n0, kblocks, rows;  // rows: valid rows of this tile (M-grouped), BM otherwise
+  int cnt;                       // rows routed to group g
 };
 
 struct Shared {
@@ -70,14 +72,14 @@ struct Shared {
 
 // Map a linear tile id to a tile.  Every role of the CTA calls this with the same id and gets the same
 // answer; the list ends at the first id that maps to nothing.
-__device__ __forceinline__ bool map_tile(const KParams& p, const int* counts, int id, Tile& t) {
+__device__ __forceinline__ bool map_tile(const KParams& p, const int* counts, int id, Tile& t, const int TM = BM) {
   const int NT = (p.N + BN - 1) / BN;
   if (p.group_mode == 0) {
     const int kblocks = (p.K * 2 /*bytes*/ + ROW_BYTES - 1) / ROW_BYTES;
     int acc = 0;
     for (int g = 0; g < p.num_groups; ++g) {
       const int cnt = counts[g];
-      const int mt = (cnt + BM - 1) / BM;
+      const int mt = (cnt + TM - 1) / TM;
       const int tiles = mt * NT;
       if (id < acc + tiles) {
         const int l = id - acc;
@@ -88,15 +90,16 @@ __device__ __forceinline__ bool map_tile(const KParams& p, const int* counts, in
         const int r = l - sg * per_sg;
         const int m = first_m + r % gsz;
         const int n = r / gsz;
-        t.g = g; t.m0 = m * BM; t.n0 = n * BN; t.kblocks = kblocks;
-        t.rows = min(BM, cnt - t.m0);
+        t.g = g; t.m0 = m * TM; t.n0 = n * BN; t.kblocks = kblocks;
+        t.rows = min(TM, cnt - t.m0);
+        t.cnt = cnt;
         return true;
       }
       acc += tiles;
     }
     return false;
   } else {
-    const int MT = (p.M + BM - 1) / BM;
+    const int MT = (p.M + TM - 1) / TM;
     const int per_group = MT * NT;
     const int g = id / per_group;
     if (g >= p.num_groups) return false;
@@ -106,9 +109,10 @@ __device__ __forceinline__ bool map_tile(const KParams& p, const int* counts, in
     const int first_m = sg * p.group_m;
     const int gsz = min(p.group_m, MT - first_m);
     const int r = l - sg * per_sg;
-    t.g = g; t.m0 = (first_m + r % gsz) * BM; t.n0 = (r / gsz) * BN;
+    t.g = g; t.m0 = (first_m + r % gsz) * TM; t.n0 = (r / gsz) * BN;
     t.kblocks = (counts[g] + 63) / 64;
-    t.rows = BM;
+    t.rows = TM;
+    t.cnt = counts[g];
     return true;
   }
 }
@@ -144,6 +148,172 @@ __device__ __forceinline__ void load32_bf16(const __nv_bfloat16* src, float* v) 
     unpack_bf16(o.y, v[8 * i + 2], v[8 * i + 3]);
     unpack_bf16(o.z, v[8 * i + 4], v[8 * i + 5]);
     unpack_bf16(o.w, v[8 * i + 6], v[8 * i + 7]);
+  }
+}
+
+// What one CTA drains from its accumulator: a slab of 128 rows x BN columns.
+struct EpiSlab {
+  int g;           // group (expert)
+  int row0;        // first row of the slab inside the group (M-grouped) or first output row (K-grouped)
+  int n0;          // first column
+  int valid_rows;  // M-grouped: rows of the slab that hold routed tokens (may be <= 0); K-grouped: 128
+  int zero_limit;  // rows in [valid, zero_limit) are written as zeros when zero_tail is set
+  bool have_acc;   // false when the contraction was empty (an expert that received no token)
+};
+
+// Fused epilogues, run by the 8 epilogue warps of a CTA: warp (q, half) owns TMEM lanes [32q, 32q+32) and half of
+// the columns; thread = one output row.
+__device__ __forceinline__ void epilogue_slab(const KParams& p, const EpiSlab& e, uint32_t acc_addr, int q, int half,
+                                              int lane) {
+  const int r_in_tile = q * 32 + lane;
+  const int row = e.row0 + r_in_tile;            // row inside the group (M-grouped) / output row (K-grouped)
+  const uint32_t t_addr = acc_addr + ((uint32_t)(q * 32) << 16);
+  const bool have_acc = e.have_acc;
+
+  if (p.epilogue == FL_EPI_STORE || p.epilogue == FL_EPI_SCATTER || p.epilogue == FL_EPI_WGRAD) {
+    bool valid, zero_row = false;
+    __nv_bfloat16* dst = nullptr;
+    if (p.epilogue == FL_EPI_STORE) {
+      valid = r_in_tile < e.valid_rows;
+      zero_row = !valid && p.zero_tail && row < e.zero_limit;
+      dst = p.C + (long long)e.g * p.gsc + (long long)row * p.ldc;
+    } else if (p.epilogue == FL_EPI_SCATTER) {
+      valid = r_in_tile < e.valid_rows;
+      if (valid) {
+        const int info = p.row_info[(long long)e.g * p.cap + row];
+        const int rk = (info >> 28) & 0xF;
+        const long long slot = info & 0x0FFFFFFF;
+        dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
+      }
+    } else {
+      valid = row < p.M;
+      dst = p.C + (long long)e.g * p.gsc + (long long)row * p.ldc;
+    }
+#pragma unroll 1
+    for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+      uint32_t r[32];
+      float v[32];
+      if (have_acc) {
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      const int col = e.n0 + c * 32;
+      if (col >= p.N) continue;
+      if (valid) {
+        if (p.epilogue == FL_EPI_WGRAD && p.sgd_lr != 0.f) {
+          float w[32];
+          load32_bf16(dst + col, w);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = w[i] - p.sgd_lr * v[i];
+        }
+        store32_bf16(dst + col, v);
+      } else if (zero_row) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+        store32_bf16(dst + col, v);
+      }
+    }
+  } else if (p.epilogue == FL_EPI_SWIGLU) {
+    const bool valid = r_in_tile < e.valid_rows;
+    const bool zero_row = !valid && p.zero_tail && row < e.zero_limit;
+    const long long grow = (long long)e.g * p.cap + row;
+    __nv_bfloat16* act = p.C + grow * p.ldc + e.n0 / 2;
+    __nv_bfloat16* gu = p.gu ? p.gu + grow * p.ldgu + e.n0 : nullptr;
+#pragma unroll 1
+    for (int c = half * 2; c < half * 2 + 2; ++c) {
+      uint32_t rg[32], ru[32];
+      tmem_ld_32x32(t_addr + c * 32, rg);
+      tmem_ld_32x32(t_addr + 128 + c * 32, ru);
+      tmem_ld_wait();
+      float g[32], u[32], a[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        g[i] = valid ? __uint_as_float(rg[i]) : 0.f;
+        u[i] = valid ? __uint_as_float(ru[i]) : 0.f;
+        a[i] = silu_f(g[i]) * u[i];
+      }
+      if (valid || zero_row) {
+        store32_bf16(act + c * 32, a);
+        if (gu) {
+          store32_bf16(gu + c * 32, g);
+          store32_bf16(gu + 128 + c * 32, u);
+        }
+      }
+    }
+  } else {  // FL_EPI_DSWIGLU
+    const bool valid = r_in_tile < e.valid_rows;
+    const bool zero_row = !valid && p.zero_tail && row < e.zero_limit;
+    const long long grow = (long long)e.g * p.cap + row;
+    // Saved gate/up of the next 32-column chunk are fetched (packed bf16, 2 x 64 B) while the current chunk's
+    // accumulator read and math are in flight, so the global-load latency is paid once per tile, not per chunk.
+    const int c0 = half * (BN / 64), c1 = c0 + BN / 64;
+    auto gate_col = [&](int c) {
+      const int a_col = e.n0 + c * 32;                          // column of dAct
+      return (long long)(a_col >> 7) * 256 + (a_col & 127);     // gate position in the interleaved row; up is +128
+    };
+    const __nv_bfloat16* gu_row = p.gu + grow * p.ldgu;
+    __nv_bfloat16* dgu_row = p.dgu + grow * p.ldgu;
+    uint4 gq[4], uq[4];
+    if (valid) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        gq[i] = ld_v4(gu_row + gate_col(c0) + 8 * i);
+        uq[i] = ld_v4(gu_row + gate_col(c0) + 128 + 8 * i);
+      }
+    }
+#pragma unroll
+    for (int c = c0; c < c1; ++c) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_addr + c * 32, r);
+      uint4 gn[4], un[4];
+      if (valid && c + 1 < c1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          gn[i] = ld_v4(gu_row + gate_col(c + 1) + 8 * i);
+          un[i] = ld_v4(gu_row + gate_col(c + 1) + 128 + 8 * i);
+        }
+      }
+      tmem_ld_wait();
+      const long long gcol = gate_col(c);
+      if (valid) {
+        float dg[32], du[32];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t gw[4] = {gq[i].x, gq[i].y, gq[i].z, gq[i].w};
+          const uint32_t uw[4] = {uq[i].x, uq[i].y, uq[i].z, uq[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float g0, g1, u0, u1;
+            unpack_bf16(gw[j], g0, g1);
+            unpack_bf16(uw[j], u0, u1);
+            const int e = 8 * i + 2 * j;
+            const float da0 = __uint_as_float(r[e]), da1 = __uint_as_float(r[e + 1]);
+            const float s0 = 1.f / (1.f + __expf(-g0)), s1 = 1.f / (1.f + __expf(-g1));
+            dg[e] = da0 * u0 * (s0 * (1.f + g0 * (1.f - s0)));
+            dg[e + 1] = da1 * u1 * (s1 * (1.f + g1 * (1.f - s1)));
+            du[e] = da0 * g0 * s0;
+            du[e + 1] = da1 * g1 * s1;
+          }
+        }
+        store32_bf16(dgu_row + gcol, dg);
+        store32_bf16(dgu_row + gcol + 128, du);
+      } else if (zero_row) {
+        float z[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) z[i] = 0.f;
+        store32_bf16(dgu_row + gcol, z);
+        store32_bf16(dgu_row + gcol + 128, z);
+      }
+      if (c + 1 < c1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { gq[i] = gn[i]; uq[i] = un[i]; }
+      }
+    }
   }
 }
 
@@ -278,156 +448,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ok = mbar_wait(&sh->tmem_full[acc], acc_ph, abort_flag, p.status, kTimeoutTmemFull, 400 + acc);
       if (!ok) break;
       tc_fence_after_sync();
-      const int r_in_tile = q * 32 + lane;
-      const int row = t.m0 + r_in_tile;            // row inside the group (M-grouped) / output row (K-grouped)
-      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
-      const bool have_acc = t.kblocks > 0;
-
-      if (p.epilogue == FL_EPI_STORE || p.epilogue == FL_EPI_SCATTER || p.epilogue == FL_EPI_WGRAD) {
-        bool valid, zero_row = false;
-        __nv_bfloat16* dst = nullptr;
-        if (p.epilogue == FL_EPI_STORE) {
-          valid = r_in_tile < t.rows;
-          zero_row = !valid && p.zero_tail && row < p.cap;
-          dst = p.C + (long long)t.g * p.gsc + (long long)row * p.ldc;
-        } else if (p.epilogue == FL_EPI_SCATTER) {
-          valid = r_in_tile < t.rows;
-          if (valid) {
-            const int info = p.row_info[(long long)t.g * p.cap + row];
-            const int rk = (info >> 28) & 0xF;
-            const long long slot = info & 0x0FFFFFFF;
-            dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
-          }
-        } else {
-          valid = row < p.M;
-          dst = p.C + (long long)t.g * p.gsc + (long long)row * p.ldc;
-        }
-#pragma unroll 1
-        for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
-          uint32_t r[32];
-          float v[32];
-          if (have_acc) {
-            tmem_ld_32x32(t_addr + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-          }
-          const int col = t.n0 + c * 32;
-          if (col >= p.N) continue;
-          if (valid) {
-            if (p.epilogue == FL_EPI_WGRAD && p.sgd_lr != 0.f) {
-              float w[32];
-              load32_bf16(dst + col, w);
-#pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = w[i] - p.sgd_lr * v[i];
-            }
-            store32_bf16(dst + col, v);
-          } else if (zero_row) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0.f;
-            store32_bf16(dst + col, v);
-          }
-        }
-      } else if (p.epilogue == FL_EPI_SWIGLU) {
-        const bool valid = r_in_tile < t.rows;
-        const bool zero_row = !valid && p.zero_tail && row < p.cap;
-        const long long grow = (long long)t.g * p.cap + row;
-        __nv_bfloat16* act = p.C + grow * p.ldc + t.n0 / 2;
-        __nv_bfloat16* gu = p.gu ? p.gu + grow * p.ldgu + t.n0 : nullptr;
-#pragma unroll 1
-        for (int c = half * 2; c < half * 2 + 2; ++c) {
-          uint32_t rg[32], ru[32];
-          tmem_ld_32x32(t_addr + c * 32, rg);
-          tmem_ld_32x32(t_addr + 128 + c * 32, ru);
-          tmem_ld_wait();
-          float g[32], u[32], a[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            g[i] = valid ? __uint_as_float(rg[i]) : 0.f;
-            u[i] = valid ? __uint_as_float(ru[i]) : 0.f;
-            a[i] = silu_f(g[i]) * u[i];
-          }
-          if (valid || zero_row) {
-            store32_bf16(act + c * 32, a);
-            if (gu) {
-              store32_bf16(gu + c * 32, g);
-              store32_bf16(gu + 128 + c * 32, u);
-            }
-          }
-        }
-      } else {  // FL_EPI_DSWIGLU
-        const bool valid = r_in_tile < t.rows;
-        const bool zero_row = !valid && p.zero_tail && row < p.cap;
-        const long long grow = (long long)t.g * p.cap + row;
-        // Saved gate/up of the next 32-column chunk are fetched (packed bf16, 2 x 64 B) while the current chunk's
-        // accumulator read and math are in flight, so the global-load latency is paid once per tile, not per chunk.
-        const int c0 = half * (BN / 64), c1 = c0 + BN / 64;
-        auto gate_col = [&](int c) {
-          const int a_col = t.n0 + c * 32;                          // column of dAct
-          return (long long)(a_col >> 7) * 256 + (a_col & 127);     // gate position in the interleaved row; up is +128
-        };
-        const __nv_bfloat16* gu_row = p.gu + grow * p.ldgu;
-        __nv_bfloat16* dgu_row = p.dgu + grow * p.ldgu;
-        uint4 gq[4], uq[4];
-        if (valid) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            gq[i] = ld_v4(gu_row + gate_col(c0) + 8 * i);
-            uq[i] = ld_v4(gu_row + gate_col(c0) + 128 + 8 * i);
-          }
-        }
-#pragma unroll
-        for (int c = c0; c < c1; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_addr + c * 32, r);
-          uint4 gn[4], un[4];
-          if (valid && c + 1 < c1) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              gn[i] = ld_v4(gu_row + gate_col(c + 1) + 8 * i);
-              un[i] = ld_v4(gu_row + gate_col(c + 1) + 128 + 8 * i);
-            }
-          }
-          tmem_ld_wait();
-          const long long gcol = gate_col(c);
-          if (valid) {
-            float dg[32], du[32];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t gw[4] = {gq[i].x, gq[i].y, gq[i].z, gq[i].w};
-              const uint32_t uw[4] = {uq[i].x, uq[i].y, uq[i].z, uq[i].w};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float g0, g1, u0, u1;
-                unpack_bf16(gw[j], g0, g1);
-                unpack_bf16(uw[j], u0, u1);
-                const int e = 8 * i + 2 * j;
-                const float da0 = __uint_as_float(r[e]), da1 = __uint_as_float(r[e + 1]);
-                const float s0 = 1.f / (1.f + __expf(-g0)), s1 = 1.f / (1.f + __expf(-g1));
-                dg[e] = da0 * u0 * (s0 * (1.f + g0 * (1.f - s0)));
-                dg[e + 1] = da1 * u1 * (s1 * (1.f + g1 * (1.f - s1)));
-                du[e] = da0 * g0 * s0;
-                du[e + 1] = da1 * g1 * s1;
-              }
-            }
-            store32_bf16(dgu_row + gcol, dg);
-            store32_bf16(dgu_row + gcol + 128, du);
-          } else if (zero_row) {
-            float z[32];
-#pragma unroll
-            for (int i = 0; i < 32; ++i) z[i] = 0.f;
-            store32_bf16(dgu_row + gcol, z);
-            store32_bf16(dgu_row + gcol + 128, z);
-          }
-          if (c + 1 < c1) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) { gq[i] = gn[i]; uq[i] = un[i]; }
-          }
-        }
-      }
+      EpiSlab e;
+      e.g = t.g; e.row0 = t.m0; e.n0 = t.n0; e.valid_rows = t.rows; e.have_acc = t.kblocks > 0;
+      e.zero_limit = p.group_mode == 0 ? min(p.cap, (t.cnt + 127) / 128 * 128) : 0;
+      epilogue_slab(p, e, tmem_base + acc * BN, q, half, lane);
       // accumulator drained: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
@@ -441,6 +465,188 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ==================================================================================================
+// CTA-pair variant: two CTAs (a cluster of 2, one per SM of a pair) work on one 256 x 256 tile with
+// tcgen05 cta_group::2.  Each CTA loads its own 128 rows of A and its own 128 columns' worth of B (so a pair
+// moves 64 KiB per k-block for twice the math of a single CTA's 48 KiB: a third less L2 -> SM traffic),
+// the leader CTA issues the MMAs for both, and each CTA drains the 128 accumulator rows that live in its own
+// TMEM.  No load is multicast: the second CTA fetches its halves itself.
+// ==================================================================================================
+constexpr int STAGES2 = 6;
+constexpr int HALF_BYTES = 128 * ROW_BYTES;            // 16 KiB: 128 rows (or 2 x 64-wide MN atoms) x 128 B
+constexpr int STAGE2_BYTES = 2 * HALF_BYTES;           // A half + B half per CTA
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 1024;
+
+struct SharedPair {
+  uint64_t full[STAGES2];
+  uint64_t empty[STAGES2];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int counts[FL_GEMM_MAX_GROUPS];
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const KParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SharedPair* sh = reinterpret_cast<SharedPair*>(smem + STAGES2 * STAGE2_BYTES);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_cta_rank();       // 0 = leader (issues the MMAs), 1 = peer
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  constexpr int TM = 2 * BM;                      // rows of a pair's tile
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&sh->full[s], 1);                 // used in the leader: one arrive.expect_tx covering both CTAs' bytes
+      mbar_init(&sh->empty[s], 1);                // one multicast commit from the leader's MMA thread
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&sh->tmem_full[a], 1);
+      mbar_init(&sh->tmem_empty[a], 16);          // used in the leader: 8 epilogue warps of each CTA
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  for (int g = threadIdx.x; g < p.num_groups; g += NUM_THREADS)
+    sh->counts[g] = p.counts ? min(p.counts[g], p.cap) : p.cap;
+  if (warp == 1) {
+    tmem_alloc_2cta(&sh->tmem_base, TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                              // both CTAs' barriers exist before either signals the other
+  tc_fence_after_sync();
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+  const int* counts = sh->counts;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      Tile t;
+      for (int id = pair_id; ok && map_tile(p, counts, id, t, TM); id += num_pairs) {
+        for (int kb = 0; kb < t.kblocks && ok; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          ok = mbar_wait(&sh->empty[s], ph ^ 1, abort_flag, p.status, kTimeoutMbarEmpty, 1100 + s);
+          if (!ok) break;
+          uint8_t* a_dst = smem + s * STAGE2_BYTES;
+          uint8_t* b_dst = a_dst + HALF_BYTES;
+          if (rank == 0) mbar_arrive_expect_tx(&sh->full[s], 2 * STAGE2_BYTES);   // bytes of both CTAs
+          const uint32_t full_leader = map_to_cta(smem_u32(&sh->full[s]), 0);
+          const int k0 = kb * 64;
+          const int mh = t.m0 + 128 * (int)rank;   // this CTA's rows of the tile
+          const int nh = t.n0 + 128 * (int)rank;   // this CTA's share of the tile's columns (B operand)
+          if (p.group_mode == 0) {
+            tma_load_3d_pair(a_dst, &tmA, full_leader, k0, mh, t.g);
+            if (!p.b_mn) {
+              tma_load_3d_pair(b_dst, &tmB, full_leader, k0, nh, t.g);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                tma_load_3d_pair(b_dst + j * (64 * ROW_BYTES), &tmB, full_leader, nh + 64 * j, k0, t.g);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_3d_pair(a_dst + j * (64 * ROW_BYTES), &tmA, full_leader, mh + 64 * j, k0, t.g);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              tma_load_3d_pair(b_dst + j * (64 * ROW_BYTES), &tmB, full_leader, nh + 64 * j, k0, t.g);
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = make_idesc(1, 1, p.a_mn ? 1u : 0u, p.b_mn ? 1u : 0u, TM, BN);
+      uint32_t it = 0, tile_i = 0;
+      bool ok = true;
+      Tile t;
+      for (int id = pair_id; ok && map_tile(p, counts, id, t, TM); id += num_pairs, ++tile_i) {
+        const int acc = tile_i & 1;
+        const uint32_t acc_ph = (tile_i >> 1) & 1;
+        ok = mbar_wait(&sh->tmem_empty[acc], acc_ph ^ 1, abort_flag, p.status, kTimeoutTmemEmpty, 1200 + acc);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.kblocks && ok; ++kb, ++it) {
+          const int s = it % STAGES2;
+          const uint32_t ph = (it / STAGES2) & 1;
+          ok = mbar_wait(&sh->full[s], ph, abort_flag, p.status, kTimeoutMbarFull, 1300 + s);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(smem + s * STAGE2_BYTES);
+          const uint32_t b_base = a_base + HALF_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = p.a_mn ? make_smem_desc(a_base + kk * 2048, 64 * ROW_BYTES, 1024)
+                                       : make_smem_desc(a_base + kk * 32, 16, 1024);
+            const uint64_t db = p.b_mn ? make_smem_desc(b_base + kk * 2048, 64 * ROW_BYTES, 1024)
+                                       : make_smem_desc(b_base + kk * 32, 16, 1024);
+            umma_f16_pair(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&sh->empty[s], 0x3);          // frees the stage in both CTAs
+        }
+        if (!ok) break;
+        if (t.kblocks > 0) {
+          umma_commit_pair(&sh->tmem_full[acc], 0x3);    // accumulator ready in both CTAs
+        } else {
+          mbar_arrive(&sh->tmem_full[acc]);
+          mbar_arrive_cluster(map_to_cta(smem_u32(&sh->tmem_full[acc]), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t tile_i = 0;
+    bool ok = true;
+    Tile t;
+    for (int id = pair_id; ok && map_tile(p, counts, id, t, TM); id += num_pairs, ++tile_i) {
+      const int acc = tile_i & 1;
+      const uint32_t acc_ph = (tile_i >> 1) & 1;
+      ok = mbar_wait(&sh->tmem_full[acc], acc_ph, abort_flag, p.status, kTimeoutTmemFull, 1400 + acc);
+      if (!ok) break;
+      tc_fence_after_sync();
+      EpiSlab e;
+      e.g = t.g; e.row0 = t.m0 + 128 * (int)rank; e.n0 = t.n0; e.have_acc = t.kblocks > 0;
+      e.valid_rows = p.group_mode == 0 ? min(128, t.cnt - e.row0) : 128;
+      e.zero_limit = p.group_mode == 0 ? min(p.cap, (t.cnt + 127) / 128 * 128) : 0;
+      epilogue_slab(p, e, tmem_base + acc * BN, q, half, lane);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->tmem_empty[acc]), 0));
+    }
+    if (p.epilogue == FL_EPI_SCATTER) fence_sys();
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();                              // neither CTA frees TMEM while the other may still use the pair's
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_2cta(tmem_base, TMEM_COLS);
   }
 }
 
@@ -496,6 +702,17 @@ static int make_map(CUtensorMap* m, const void* base, long long inner, long long
 
 extern "C" const char* fl_gemm_last_error(void) { return fl::g_err; }
 
+// 0 = one CTA per tile (128 x 256), 1 = CTA pairs (256 x 256, cta_group::2).  Default from FUSELINK_GEMM_PAIR (1).
+static int g_variant = -1;
+extern "C" void fl_gemm_set_variant(int v) { g_variant = v ? 1 : 0; }
+extern "C" int fl_gemm_get_variant(void) {
+  if (g_variant < 0) {
+    const char* e = getenv("FUSELINK_GEMM_PAIR");
+    g_variant = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_variant;
+}
+
 extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
   using namespace fl;
   g_err[0] = 0;
@@ -518,6 +735,7 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
   p.group_m = d->group_m > 0 ? d->group_m : 16;
   p.status = d->status;
 
+  const bool pair = fl_gemm_get_variant() == 1;
   CUtensorMap tmA, tmB;
   int rc;
   if (d->group_mode == 0) {
@@ -528,7 +746,7 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
     if ((d->epilogue == FL_EPI_DSWIGLU) && (d->N % 128)) return bad("DSWIGLU needs N % 128 == 0");
     rc = make_map(&tmA, d->A, d->K, d->cap, d->num_groups, d->lda, d->gsa, 64, BM);
     if (rc) return rc;
-    if (!d->b_mn_major) rc = make_map(&tmB, d->B, d->K, d->N, d->num_groups, d->ldb, d->gsb, 64, BN);
+    if (!d->b_mn_major) rc = make_map(&tmB, d->B, d->K, d->N, d->num_groups, d->ldb, d->gsb, 64, pair ? 128 : BN);
     else rc = make_map(&tmB, d->B, d->N, d->K, d->num_groups, d->ldb, d->gsb, 64, 64);
     if (rc) return rc;
   } else {
@@ -541,7 +759,7 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
     if (rc) return rc;
   }
 
-  static int num_sms = 0;
+  static int num_sms = 0, max_pairs = 0;
   static bool attr_set = false;
   if (!attr_set) {
     int dev = 0;
@@ -549,7 +767,32 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(grouped_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    // how many CTA pairs can be resident at once (SM pairs are not guaranteed for every SM of the chip)
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDim = dim3(num_sms & ~1, 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM2_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int nclusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&nclusters, grouped_gemm_pair_kernel, &cfg) == cudaSuccess && nclusters > 0)
+      max_pairs = nclusters;
+    else
+      max_pairs = num_sms / 2;
+    cudaGetLastError();
     attr_set = true;
+  }
+  if (pair) {
+    int pairs = max_pairs;
+    if (d->max_ctas > 0 && d->max_ctas / 2 < pairs) pairs = d->max_ctas / 2 > 0 ? d->max_ctas / 2 : 1;
+    grouped_gemm_pair_kernel<<<2 * pairs, NUM_THREADS, SMEM2_BYTES, stream>>>(tmA, tmB, p);
+    return (int)cudaGetLastError();
   }
   int grid = num_sms;
   if (d->max_ctas > 0 && d->max_ctas < grid) grid = d->max_ctas;

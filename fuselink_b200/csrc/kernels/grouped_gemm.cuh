@@ -62,6 +62,9 @@ extern "C" {
 // Returns 0 on success, a negative value for a rejected description, a positive cudaError otherwise.
 int fl_grouped_gemm(const FlGemmDesc* desc, cudaStream_t stream);
 const char* fl_gemm_last_error(void);
+// 0: one CTA per 128 x 256 tile; 1: CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2).  Default: FUSELINK_GEMM_PAIR or 1.
+void fl_gemm_set_variant(int pair);
+int fl_gemm_get_variant(void);
 #ifdef __cplusplus
 }
 #endif

@@ -257,6 +257,8 @@ static int64_t vmm_remap_slab(int64_t region, int64_t slab, int64_t target, bool
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &grouped_gemm);
+  m.def("gemm_set_variant", [](int64_t v) { fl_gemm_set_variant((int)v); });
+  m.def("gemm_get_variant", []() { return fl_gemm_get_variant(); });
   m.def("put_chunks", &put_chunks);
   m.def("wait_flags", &wait_flags);
   m.def("all_to_all", &all_to_all);

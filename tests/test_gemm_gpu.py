@@ -6,6 +6,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["single", "pair"])
+def _variant(request):
+    """Every test runs on both kernels: one CTA per 128x256 tile, and CTA pairs on 256x256 tiles (cta_group::2)."""
+    from fuselink_b200 import C
+    before = C.gemm_get_variant()
+    C.gemm_set_variant(1 if request.param == "pair" else 0)
+    yield request.param
+    C.gemm_set_variant(before)
+
+
 def _mk(shape, scale=1.0, seed=0):
     g = torch.Generator(device="cuda").manual_seed(seed)
     return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
