@@ -100,6 +100,7 @@ def parse():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--zipf", type=float, default=1.2)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="fp8: block-scaled e4m3 (1x128) forward/dgrad GEMMs")
     return ap.parse_args()
 
 
@@ -127,7 +128,8 @@ def main():
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops.moe import MoEConfig
 
-    cfg = MoEConfig(hidden=args.hidden, ffn=args.ffn, num_experts=args.experts, topk=args.topk, tokens=args.tokens)
+    cfg = MoEConfig(hidden=args.hidden, ffn=args.ffn, num_experts=args.experts, topk=args.topk, tokens=args.tokens,
+                    fp8=args.dtype == "fp8" and args.impl == "fuselink")
     T, H = cfg.tokens, cfg.hidden
 
     if args.impl == "fuselink":
@@ -230,7 +232,8 @@ def main():
         line = {
             "metric": "MoE-EP tokens/s (fwd+bwd+SGD)", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8 e4m3 1x128 block-scaled (fwd, dgrad) + bf16 (wgrad)" if cfg.fp8 else "bf16", "data": "synthetic",
             "impl": args.impl,
             "config": {"model": "MoE-EP layer: hidden 4096, 8 experts SwiGLU 4096-14336-4096, top-2, Zipf(1.2) router bias"
                        if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else

@@ -10,6 +10,7 @@
 #include "../kernels/embbag.cuh"
 #include "../kernels/kv_pack.cuh"
 #include "../kernels/moe_dispatch.cuh"
+#include "../kernels/fp8_gemm.cuh"
 #include "../mem/vmm.h"
 #include "../monitor/monitor.h"
 void fl_monitor_bind(pybind11::module& m);
@@ -214,6 +215,42 @@ static void moe_combine_dw(torch::Tensor dout, torch::Tensor slots, torch::Tenso
                              (int)dout.size(1), cur_stream()), "fl_moe_combine_dw");
 }
 
+// ------------------------------------------------------------------------------------------------ fp8
+static void fp8_quantize_rows(torch::Tensor x, torch::Tensor q, torch::Tensor scale, c10::optional<torch::Tensor> counts,
+                              int64_t cap) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 2, "x: [rows, K] bf16");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(fl_fp8_quantize_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), x.size(0), (int)x.size(1),
+                                counts.has_value() ? counts->data_ptr<int>() : nullptr, (int)cap, cur_stream()),
+           "fl_fp8_quantize_rows");
+}
+static void fp8_quantize_blocks(torch::Tensor w, torch::Tensor q, torch::Tensor scale) {
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kBFloat16 && w.is_contiguous() && w.dim() == 3, "w: [G, R, C] bf16");
+  c10::cuda::CUDAGuard guard(w.device());
+  check_rc(fl_fp8_quantize_blocks(w.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), (int)w.size(0), (int)w.size(1),
+                                  (int)w.size(2), cur_stream()), "fl_fp8_quantize_blocks");
+}
+static void fp8_grouped_gemm(int64_t num_groups, int64_t cap, int64_t N, int64_t K, c10::optional<torch::Tensor> counts,
+                             torch::Tensor A, torch::Tensor a_scale, torch::Tensor B, bool b_mn, torch::Tensor b_scale,
+                             int64_t epilogue, c10::optional<torch::Tensor> C, int64_t ldc, c10::optional<torch::Tensor> gu,
+                             int64_t ldgu, c10::optional<torch::Tensor> dgu, c10::optional<torch::Tensor> row_info,
+                             std::vector<int64_t> peers, bool zero_tail, int64_t group_m, int64_t max_ctas,
+                             c10::optional<torch::Tensor> status) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.element_size() == 1 && B.element_size() == 1, "fp8 operands expected");
+  c10::cuda::CUDAGuard guard(A.device());
+  FlFp8GemmDesc d;
+  memset(&d, 0, sizeof d);
+  d.num_groups = (int)num_groups; d.cap = (int)cap; d.N = (int)N; d.K = (int)K;
+  d.counts = counts.has_value() ? counts->data_ptr<int>() : nullptr;
+  d.A = A.data_ptr(); d.a_scale = a_scale.data_ptr<float>();
+  d.B = B.data_ptr(); d.b_mn_major = b_mn; d.b_scale = b_scale.data_ptr<float>();
+  d.epilogue = (int)epilogue; d.C = opt_ptr(C); d.ldc = ldc; d.gu = opt_ptr(gu); d.ldgu = ldgu; d.dgu = opt_ptr(dgu);
+  d.row_info = row_info.has_value() ? row_info->data_ptr<int>() : nullptr;
+  d.peers = to_peers(peers); d.zero_tail = zero_tail; d.group_m = (int)group_m; d.max_ctas = (int)max_ctas;
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  check_rc(fl_fp8_grouped_gemm(&d, cur_stream()), "fl_fp8_grouped_gemm", fl_fp8_last_error());
+}
+
 // ------------------------------------------------------------------------------------------------ memory
 static torch::Tensor tensor_from_ptr(int64_t ptr, std::vector<int64_t> shape, py::object dtype, int64_t device) {
   auto st = torch::python::detail::py_object_to_dtype(dtype);
@@ -259,6 +296,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &grouped_gemm);
   m.def("gemm_set_variant", [](int64_t v) { fl_gemm_set_variant((int)v); });
   m.def("gemm_get_variant", []() { return fl_gemm_get_variant(); });
+  m.def("fp8_quantize_rows", &fp8_quantize_rows);
+  m.def("fp8_quantize_blocks", &fp8_quantize_blocks);
+  m.def("fp8_grouped_gemm", &fp8_grouped_gemm);
   m.def("put_chunks", &put_chunks);
   m.def("wait_flags", &wait_flags);
   m.def("all_to_all", &all_to_all);

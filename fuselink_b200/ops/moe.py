@@ -31,6 +31,7 @@ class MoEConfig:
     num_experts: int = 8
     topk: int = 2
     tokens: int = 8192          # tokens per rank and step
+    fp8: bool = False           # block-scaled e4m3 ("1 x 128") for the forward and dgrad GEMMs; wgrad stays bf16
 
 
 class MoEWorkspace:
@@ -62,6 +63,16 @@ class MoEWorkspace:
         self.base = torch.zeros(cfg.num_experts, dtype=torch.int32, device=dev)
         self.pos = torch.zeros(T, k, dtype=torch.int32, device=dev)
         self.slot = torch.zeros(T, k, dtype=torch.int32, device=dev)
+        if cfg.fp8:
+            from . import fp8 as _f8
+            f8 = _f8.FP8
+            self.q_in = torch.empty(rows, H, dtype=f8, device=dev)          # quantised xd / dyd
+            self.s_in = torch.empty(rows, H // 128, dtype=torch.float32, device=dev)
+            self.q_act = torch.empty(rows, F, dtype=f8, device=dev)         # quantised act
+            self.s_act = torch.empty(rows, F // 128, dtype=torch.float32, device=dev)
+            self.q_dgu = torch.empty(rows, 2 * F, dtype=f8, device=dev)     # quantised dgate/dup
+            self.s_dgu = torch.empty(rows, 2 * F // 128, dtype=torch.float32, device=dev)
+            self.wq = {}                                                     # per-weight (e4m3, scales), refreshed each step
         self.parity = 0
         self.step_parity = 0
         self.launches = 0   # kernels of this library launched through this workspace (bench accounting)
@@ -76,6 +87,16 @@ def _dispatch(ws: MoEWorkspace, x: torch.Tensor, idx: torch.Tensor, scale: Optio
     C.moe_dispatch(x, idx, scale, cfg.num_experts, ws.epr, ws.cap, h.rank, h.world, ws.local_count, ws.base, ws.pos,
                    ws.slot, ws.counts.peers(), ws.step_parity, dst.peers(), ws.info.peers(), reuse, h.status_addr)
     ws.launches += 1 if reuse else 3
+
+
+def _wq(ws: MoEWorkspace, name: str, w: torch.Tensor):
+    """(e4m3 buffer, scale buffer) of weight `name`, allocated on first use."""
+    if name not in ws.wq:
+        from . import fp8 as f8
+        G, R, Cc = w.shape
+        ws.wq[name] = (torch.empty(G, R, Cc, dtype=f8.FP8, device=w.device),
+                       torch.empty(G, R // 128, Cc // 128, dtype=torch.float32, device=w.device))
+    return ws.wq[name]
 
 
 def moe_forward_dispatch(ws: MoEWorkspace, x: torch.Tensor, topk_idx: torch.Tensor) -> None:
@@ -93,10 +114,22 @@ def moe_forward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor) -
     counts = ws.counts_now()
     C.moe_zero_tail(ws.xd.addr(), counts.data_ptr(), ws.epr, ws.cap, ws.cfg.hidden)
     st = h.status()
-    gemm.grouped_gemm_rows(ws.xd.local, w13, counts, ws.cap, epilogue=gemm.EPI_SWIGLU, out=ws.act, gu=ws.gu,
-                           zero_tail=True, status=st)
-    gemm.grouped_gemm_rows(ws.act, w2, counts, ws.cap, epilogue=gemm.EPI_SCATTER, row_info=ws.info.local,
-                           peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st)
+    if ws.cfg.fp8:
+        from . import fp8 as f8
+        C.fp8_quantize_blocks(w13, *_wq(ws, "w13", w13))
+        C.fp8_quantize_blocks(w2, *_wq(ws, "w2", w2))
+        C.fp8_quantize_rows(ws.xd.local, ws.q_in, ws.s_in, counts, ws.cap)
+        f8.grouped_gemm_rows_fp8(ws.q_in, ws.s_in, *ws.wq["w13"], counts, ws.cap, epilogue=gemm.EPI_SWIGLU, out=ws.act,
+                                 gu=ws.gu, zero_tail=True, status=st)
+        C.fp8_quantize_rows(ws.act, ws.q_act, ws.s_act, counts, ws.cap)
+        f8.grouped_gemm_rows_fp8(ws.q_act, ws.s_act, *ws.wq["w2"], counts, ws.cap, epilogue=gemm.EPI_SCATTER,
+                                 row_info=ws.info.local, peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st)
+        ws.launches += 4
+    else:
+        gemm.grouped_gemm_rows(ws.xd.local, w13, counts, ws.cap, epilogue=gemm.EPI_SWIGLU, out=ws.act, gu=ws.gu,
+                               zero_tail=True, status=st)
+        gemm.grouped_gemm_rows(ws.act, w2, counts, ws.cap, epilogue=gemm.EPI_SCATTER, row_info=ws.info.local,
+                               peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st)
     barrier(h, ws.name + ":c", signal=True, wait=False)
     ws.launches += 5
 
@@ -131,13 +164,26 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     counts = ws.counts_now()
     C.moe_zero_tail(ws.dyd.addr(), counts.data_ptr(), ws.epr, ws.cap, cfg.hidden)
     st = h.status()
-    # dAct = dY @ W2 ; the epilogue turns it into dGate/dUp using the saved gate/up
-    gemm.grouped_gemm_rows(ws.dyd.local, w2, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=ws.gu,
-                           dgu=ws.dgu, zero_tail=True, status=st)
-    # dX rows go home first (needs the pre-update W13), then the weight gradients
-    if need_dx:
-        gemm.grouped_gemm_rows(ws.dgu, w13, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER,
-                               row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st)
+    # dAct = dY @ W2 ; the epilogue turns it into dGate/dUp using the saved gate/up.  dX rows go home next (needs the
+    # pre-update W13), then the weight gradients.
+    if cfg.fp8:
+        from . import fp8 as f8
+        # the quantised weights of the forward pass are reused: a 128 x 128 scale block is its own transpose
+        C.fp8_quantize_rows(ws.dyd.local, ws.q_in, ws.s_in, counts, ws.cap)
+        f8.grouped_gemm_rows_fp8(ws.q_in, ws.s_in, *ws.wq["w2"], counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU,
+                                 gu=ws.gu, dgu=ws.dgu, zero_tail=True, status=st)
+        if need_dx:
+            C.fp8_quantize_rows(ws.dgu, ws.q_dgu, ws.s_dgu, counts, ws.cap)
+            f8.grouped_gemm_rows_fp8(ws.q_dgu, ws.s_dgu, *ws.wq["w13"], counts, ws.cap, b_mn_major=True,
+                                     epilogue=gemm.EPI_SCATTER, row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden,
+                                     status=st)
+        ws.launches += 2
+    else:
+        gemm.grouped_gemm_rows(ws.dyd.local, w2, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=ws.gu,
+                               dgu=ws.dgu, zero_tail=True, status=st)
+        if need_dx:
+            gemm.grouped_gemm_rows(ws.dgu, w13, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER,
+                                   row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st)
     if sgd_lr:
         gemm.grouped_gemm_wgrad(ws.dyd.local, ws.act, counts, ws.cap, ws.epr, out=w2, sgd_lr=sgd_lr, status=st)
         gemm.grouped_gemm_wgrad(ws.dgu, ws.xd.local, counts, ws.cap, ws.epr, out=w13, sgd_lr=sgd_lr, status=st)
