@@ -1,0 +1,69 @@
+#!/usr/bin/env python
+"""Online (trace-driven) serving experiment, the counterpart of experiments/serving/run_online_test.sh: replays a trace
+(`ts: .. prompt: .. shared: .. out: ..` lines, or a synthetic Poisson trace) through one prefill and one decode stage.
+
+    python experiments/run_online_serving.py [--trace FILE] [--model tiny] [--requests 40] [--rate 200]
+
+With one visible GPU both stages run as virtual ranks on it; the report is the reference's: communication volume per
+batch (KV bytes, header bytes), send window, prefill time."""
+import argparse
+import json
+import os
+import queue
+import random
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--trace", default="")
+    ap.add_argument("--model", default="tiny")
+    ap.add_argument("--requests", type=int, default=40)
+    ap.add_argument("--rate", type=float, default=200.0, help="synthetic arrivals per second")
+    ap.add_argument("--input-len", type=int, default=512)
+    ap.add_argument("--decode-steps", type=int, default=8)
+    ap.add_argument("--decode-sleep-ms", type=float, default=0.0, help="stand-in for decoding, 25 in the reference")
+    args = ap.parse_args()
+    from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    from fuselink_b200.serving.disagg import KVLink, ServeParams
+    from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader, next_batch, parse_trace
+    cfg = MODEL_ZOO[args.model]
+    p = ServeParams(cfg, MAX_BATCH, args.input_len, args.decode_steps)
+    if args.trace:
+        reqs = parse_trace(open(args.trace))
+    else:
+        rng, t, lines = random.Random(0), 0.0, []
+        for _ in range(args.requests):
+            t += rng.expovariate(args.rate)
+            prompt = rng.randint(32, args.input_len)
+            lines.append(f"ts: {t:.4f} prompt: {prompt} shared: {rng.randint(0, prompt // 4)} out: {rng.randint(4, 64)}")
+        reqs = parse_trace(lines)
+    net = LlamaShard(cfg, device="cuda")
+    pool = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
+    heaps = SymmetricHeap.emulated(2, 2 * pool + (64 << 20))
+    links = [[KVLink(h, p, net.kvh_local, name=f"kv{i}") for i in range(2)] for h in heaps]
+    pre, dec = OnlinePrefill(p, net, links[0], 1), OnlineDecode(p, net, links[1], 0, sleep_ms=args.decode_sleep_ms)
+    q = queue.Queue()
+    TraceReader(reqs, q).start()
+    finished, served = False, 0
+    while not finished:
+        batch, finished = next_batch(q, MAX_BATCH, p.input_len)
+        if not batch:
+            continue
+        st = pre.serve_batch(batch)
+        dec.serve_batch(args.decode_steps)
+        served += len(batch)
+        print(json.dumps({"batch": st.batch, "prompt_tokens": st.prompt_tokens, "kv_MB": st.kv_bytes / 1e6, "header_B": st.header_bytes,
+                          "prefill_ms": round(st.prefill_ms, 3), "send_window_ms": round(st.send_ms, 3)}))
+    print(json.dumps({"served": served, "batches": pre.batches, "total_kv_GB": sum(s.kv_bytes for s in pre.stats) / 1e9}))
+    for h in heaps:
+        h.close()
+
+
+if __name__ == "__main__":
+    main()
