@@ -5,6 +5,7 @@
 #include <dlfcn.h>
 #include <fcntl.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <sys/mman.h>
 #include <unistd.h>
@@ -40,6 +41,9 @@ struct Driver {
   virtual int import_fd(int fd, uint64_t* h) = 0;
   virtual int retain(void* ptr, uint64_t* h) = 0;
   virtual int copy(uintptr_t dst, uintptr_t src, size_t n) = 0;
+  virtual int any_copy(void* dst, const void* src, size_t n) = 0;
+  virtual int device_count() = 0;
+  virtual int pointer_device(const void* ptr) = 0;   // -1 when unknown
 };
 
 // ---- real CUDA driver, resolved at run time -----------------------------------------------------
@@ -62,6 +66,9 @@ struct CudaDriver : Driver {
   CUresult (*MemRetainAllocationHandle)(CUmemGenericAllocationHandle*, void*) = nullptr;
   CUresult (*MemcpyDtoD)(CUdeviceptr, CUdeviceptr, size_t) = nullptr;
   CUresult (*CtxSynchronize)() = nullptr;
+  CUresult (*Memcpy)(CUdeviceptr, CUdeviceptr, size_t) = nullptr;
+  CUresult (*DeviceGetCount)(int*) = nullptr;
+  CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr) = nullptr;
 
   template <class F>
   bool sym(const char* name, F& fn) {
@@ -93,7 +100,8 @@ struct CudaDriver : Driver {
               sym("cuMemSetAccess", MemSetAccess) && sym("cuMemExportToShareableHandle", MemExportToShareableHandle) &&
               sym("cuMemImportFromShareableHandle", MemImportFromShareableHandle) &&
               sym("cuMemRetainAllocationHandle", MemRetainAllocationHandle) && sym("cuMemcpyDtoD", MemcpyDtoD) &&
-              sym("cuCtxSynchronize", CtxSynchronize);
+              sym("cuCtxSynchronize", CtxSynchronize) && sym("cuMemcpy", Memcpy) && sym("cuDeviceGetCount", DeviceGetCount) &&
+              sym("cuPointerGetAttribute", PointerGetAttribute);
     if (!ok) return false;
     return chk(Init(0), "cuInit") == 0;
   }
@@ -170,6 +178,18 @@ struct CudaDriver : Driver {
     if (rc) return rc;
     return chk(CtxSynchronize(), "cuCtxSynchronize");
   }
+  int any_copy(void* dst, const void* src, size_t n) override {
+    return chk(Memcpy((CUdeviceptr)(uintptr_t)dst, (CUdeviceptr)(uintptr_t)src, n), "cuMemcpy");
+  }
+  int device_count() override {
+    int n = 0;
+    return DeviceGetCount(&n) == CUDA_SUCCESS ? n : 0;
+  }
+  int pointer_device(const void* ptr) override {
+    int ord = -1;
+    if (PointerGetAttribute(&ord, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS) return -1;
+    return ord;
+  }
 };
 
 // ---- fake driver: physical memory = memfd, mapping = mmap(MAP_SHARED|MAP_FIXED) ------------------
@@ -233,6 +253,12 @@ struct FakeDriver : Driver {
     return 0;
   }
   int copy(uintptr_t dst, uintptr_t src, size_t n) override { memcpy((void*)dst, (void*)src, n); return 0; }
+  int any_copy(void* dst, const void* src, size_t n) override { memcpy(dst, src, n); return 0; }
+  int device_count() override {
+    const char* e = getenv("FUSELINK_VMM_FAKE_NGPUS");
+    return e ? atoi(e) : 8;
+  }
+  int pointer_device(const void*) override { return -1; }
 };
 
 Driver* g_drv = nullptr;
@@ -504,6 +530,19 @@ int fl_vmm_ptr2dev(const void* ptr) {
   const uintptr_t p = (uintptr_t)ptr;
   if (p < r->va || p >= r->va + r->size) return -1;
   return r->slabs[(p - r->va) / r->slab_bytes].device;
+}
+
+int fl_vmm_memcpy(void* dst, const void* src, size_t bytes) {
+  if (!g_drv) { set_err("%s: fl_vmm_init not called (%ld)", "vmm", 0); return 1; }
+  return g_drv->any_copy(dst, src, bytes);
+}
+
+int fl_vmm_device_count(void) { return g_drv ? g_drv->device_count() : 0; }
+
+int fl_vmm_pointer_device(const void* ptr) {
+  const int known = fl_vmm_ptr2dev(ptr);
+  if (known >= 0 || !g_drv) return known;
+  return g_drv->pointer_device(ptr);
 }
 
 size_t fl_vmm_usage(int device) {

@@ -56,6 +56,12 @@ int fl_vmm_remap_slab(FlVmmRegion* r, int slab, int target_device, int keep_cont
                       int n_access, long* usec_out);
 // Which device backs the slab that contains ptr (-1 if ptr is not inside a known region).
 int fl_vmm_ptr2dev(const void* ptr);
+// Synchronous copy between any two addresses the backend knows (device or host, unified addressing).
+int fl_vmm_memcpy(void* dst, const void* src, size_t bytes);
+// Device that owns `ptr`: a region of this layer, else what the driver reports, else -1.
+int fl_vmm_pointer_device(const void* ptr);
+// Number of devices the backend sees (fake backend: FUSELINK_VMM_FAKE_NGPUS or 8).
+int fl_vmm_device_count(void);
 // Bytes of physical memory this layer currently holds on `device`.
 size_t fl_vmm_usage(int device);
 

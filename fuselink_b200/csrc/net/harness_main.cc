@@ -70,9 +70,10 @@ struct Api {
     ncclNetDeviceHandle_v7_t* dh = nullptr;
     return abi == 7 ? v7->accept(lc, rc, &dh) : v8->accept(lc, rc, &dh);
   }
+  int ptr_type = NCCL_PTR_HOST;
   ncclResult_t regMr(void* c, void* d, size_t s, void** mh) {
-    if (abi == 8) return v8->regMr(c, d, s, NCCL_PTR_HOST, mh);
-    return abi == 6 ? v6->regMr(c, d, (int)s, NCCL_PTR_HOST, mh) : v7->regMr(c, d, (int)s, NCCL_PTR_HOST, mh);
+    if (abi == 8) return v8->regMr(c, d, s, ptr_type, mh);
+    return abi == 6 ? v6->regMr(c, d, (int)s, ptr_type, mh) : v7->regMr(c, d, (int)s, ptr_type, mh);
   }
   ncclResult_t deregMr(void* c, void* mh) { return PICK(deregMr)(c, mh); }
   ncclResult_t isend(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(isend)(c, d, s, tag, mh, r); }
@@ -93,9 +94,9 @@ int main(int argc, char** argv) {
   const bool is_send = !strcmp(argv[2], "send");
   const std::string hfile = argv[3];
   size_t chunk = 512 * 1024;
-  int inflight = 8, dev = 0, die_after = -1;
+  int inflight = 8, dev = 0, die_after = -1, channel = 0;
   uint64_t seed = 0;
-  bool expect_error = false;
+  bool expect_error = false, device_bufs = false;
   Api api;
   std::vector<size_t> sizes;
   for (int i = 4; i < argc; ++i) {
@@ -106,8 +107,10 @@ int main(int argc, char** argv) {
     else if (a == "--seed") seed = val();
     else if (a == "--dev") dev = (int)val();
     else if (a == "--abi") api.abi = (int)val();
+    else if (a == "--channel") channel = (int)val();      // receiver: burn this many channel ids first
     else if (a == "--die-after-chunks") die_after = (int)val();
     else if (a == "--expect-error") expect_error = true;
+    else if (a == "--device-buffers") device_bufs = true;   // buffers come from the plugin's cuMem layer and are registered as CUDA
     else sizes.push_back(strtoull(a.c_str(), nullptr, 0));
   }
   void* lib = dlopen(so, RTLD_NOW);
@@ -126,6 +129,10 @@ int main(int argc, char** argv) {
   void *lcomm = nullptr, *comm = nullptr;
   const double t_limit = now_s() + 120.0;
   if (!is_send) {
+    for (int i = 0; i < channel; ++i) {   // every listen takes the next global channel id
+      void* tmp = nullptr;
+      if (api.listen(dev, handle, &tmp) == ncclSuccess) api.closeListen(tmp);
+    }
     if (api.listen(dev, handle, &lcomm) != ncclSuccess) { fprintf(stderr, "listen failed\n"); return 2; }
     std::string tmp = hfile + ".tmp";
     FILE* f = fopen(tmp.c_str(), "wb");
@@ -158,11 +165,27 @@ int main(int argc, char** argv) {
   int chunks_done_total = 0;
   for (size_t mi = 0; mi < sizes.size() && rc == 0; ++mi) {
     const size_t bytes = sizes[mi];
-    std::vector<float> buf((bytes + 3) / 4), expect;
-    if (is_send) fill(buf, seed, mi);
-    else { expect.resize(buf.size()); fill(expect, seed, mi); memset(buf.data(), 0xA5, buf.size() * 4); }
+    std::vector<float> host((bytes + 3) / 4), expect;
+    float* bufp = host.data();
+    void* region = nullptr;
+    if (device_bufs) {
+      // a "GPU" buffer from the plugin's cuMem layer (memfd-backed when FUSELINK_VMM_FAKE=1), owned by device `dev`
+      auto create = (void* (*)(int, size_t, size_t))dlsym(lib, "fl_vmm_create");
+      auto vptr = (void* (*)(const void*))dlsym(lib, "fl_vmm_ptr");
+      region = create ? create(dev, host.size() * 4 + 16, 0) : nullptr;
+      if (!region) { fprintf(stderr, "fl_vmm_create failed\n"); return 2; }
+      bufp = (float*)vptr(region);
+      api.ptr_type = NCCL_PTR_CUDA;
+    }
+    struct BufView { float* p; size_t n; float* data() { return p; } size_t size() { return n; } } buf{bufp, host.size()};
+    if (is_send) { fill(host, seed, mi); memcpy(bufp, host.data(), host.size() * 4); }
+    else { expect.resize(host.size()); fill(expect, seed, mi); memset(bufp, 0xA5, host.size() * 4); }
     void* mh = nullptr;
     if (api.regMr(comm, buf.data(), buf.size() * 4, &mh) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
+    if (device_bufs && mi == 0) {
+      auto p2d = (int (*)(const void*))dlsym(lib, "fl_vmm_ptr2dev");
+      printf("REGISTERED device-buffer owner %d now-backed-by %d\n", dev, p2d ? p2d(bufp) : -1);
+    }
     const size_t nchunks = bytes == 0 ? 1 : (bytes + chunk - 1) / chunk;
     size_t next = 0, done_chunks = 0;
     std::deque<void*> reqs;

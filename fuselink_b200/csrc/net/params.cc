@@ -77,6 +77,9 @@ const Params& params() {
   p.min_stripe_bytes = param_i64("FUSELINK_MIN_STRIPE_BYTES", 65536);
   p.net_timeout_ms = param_i64("FUSELINK_NET_TIMEOUT_MS", 30000);
   p.timers = param_i64("FUSELINK_TIMERS", 0);
+  p.cuda_ptrs = param_i64("FUSELINK_CUDA_PTRS", 0);
+  p.vmm_fake = param_i64("FUSELINK_VMM_FAKE", 0);
+  p.remap = param_i64("FUSELINK_REMAP", 1);
   p.fault_drop_after = param_i64("FUSELINK_FAULT_CLOSE_AFTER_BYTES", 0);
   if (p.tcp_ndev < 1) p.tcp_ndev = 1;
   if (p.tcp_ndev > 16) p.tcp_ndev = 16;

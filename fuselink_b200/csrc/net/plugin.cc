@@ -42,6 +42,7 @@ constexpr uint32_t kFrameMagic = 0x464c4652u;
 std::mutex g_mu;
 ConnManager* g_cm = nullptr;
 int g_ndev = 0;
+int g_ngpus = 0;          // devices the cuMem layer sees; 0 = CUDA registrations unavailable
 std::atomic<int> g_channel_counter{0};
 char g_names[kMaxDev][32];
 char g_pci[kMaxDev][64];
@@ -77,6 +78,10 @@ ncclResult_t fl_init(ncclDebugLogger_t logger) {
   int prio = (int)p.priority_dev;
   if (prio < 0 || prio >= g_ndev) prio = 0;
   g_cm = new ConnManager(g_ndev, prio, p.monitor_enable != 0, p.monitor_shm.c_str(), (int)p.monitor_timeout_us);
+  if (p.cuda_ptrs) {
+    if (fl_vmm_init(p.vmm_fake ? 1 : 0) == 0) g_ngpus = fl_vmm_device_count();
+    else FL_WARN("CUDA registrations requested but the cuMem layer is unavailable: %s", fl_vmm_last_error());
+  }
   FL_INFO("FuseLink plugin: %d virtual NIC(s) over TCP, %d verbs device(s) found, degree %ld step %ld, monitor %s", g_ndev, n_ib,
           (long)p.degree, (long)p.step, g_cm->monitor() ? "on" : "off");
   return ncclSuccess;
@@ -92,7 +97,8 @@ void fill_props_common(int dev, P* props) {
   props->name = g_names[dev];
   props->pciPath = g_pci[dev];
   props->guid = 0x464c0000ull + (uint64_t)dev;
-  props->ptrSupport = NCCL_PTR_HOST;      // the TCP transport reads/writes host memory; NCCL stages GPU data
+  // the TCP transport reads/writes host memory; GPU buffers are accepted (and staged by the plugin) only on request
+  props->ptrSupport = NCCL_PTR_HOST | (g_ngpus > 0 ? NCCL_PTR_CUDA : 0);
   props->speed = 100000;                  // Mbps, nominal
   props->port = 0;
   props->latency = 0;
@@ -301,12 +307,35 @@ ncclResult_t fl_accept_v7(void* listen_comm, void** recv_comm, ncclNetDeviceHand
 // relay GPU, which is what the reference's regMr does (src/plugin.cc:1168-1330).  The TCP data path itself
 // only touches host memory, so a CUDA registration is refused unless the device transport is active.
 ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
-  (void)comm;
-  if (type != NCCL_PTR_HOST) {
-    FL_WARN("regMr: pointer type %d is not supported by the TCP transport (ptrSupport is HOST)", type);
+  if (type == NCCL_PTR_HOST) {
+    *mhandle = new MemHandle{data, size, type, nullptr};
+    return ncclSuccess;
+  }
+  if (type != NCCL_PTR_CUDA || g_ngpus <= 0) {
+    FL_WARN("regMr: pointer type %d is not supported (set FUSELINK_CUDA_PTRS=1 for device buffers)", type);
     return ncclInvalidUsage;
   }
+  // Device buffer: adopt the cuMem allocation behind it and re-home it onto the relay GPU of this channel,
+  // relay = (owner + channelId) % nGPUs (src/plugin.cc:1201), keeping the address and the contents and leaving the
+  // owner GPU with read/write access (src/fuselink.cc:43-56).  A buffer that is not a cuMem allocation (or that is
+  // registered again) is used where it is.
+  Comm* c = reinterpret_cast<Comm*>(comm);
   MemHandle* m = new MemHandle{data, size, type, nullptr};
+  if (params().remap) {
+    int dev = fl_vmm_pointer_device(data);
+    if (dev < 0) dev = 0;
+    FlVmmRegion* r = fl_vmm_adopt(data, size, dev);
+    if (r) {
+      const int relay = (dev + (c ? c->channel_id : 0)) % g_ngpus;
+      long usec = 0;
+      const int access[2] = {dev, relay};
+      if (relay != dev && fl_vmm_remap_slab(r, 0, relay, 1, access, 2, &usec) == 0)
+        FL_INFO("regMr: %zu bytes at %p re-homed GPU %d -> GPU %d in %ld us", size, data, dev, relay, usec);   // "Remap time"
+      m->region = r;
+    } else {
+      FL_INFO("regMr: %p is not a cuMem allocation (%s): registered in place", data, fl_vmm_last_error());
+    }
+  }
   *mhandle = m;
   return ncclSuccess;
 }
@@ -346,7 +375,6 @@ Request* get_request(Comm* c) {
 }
 
 ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhandle, void** request) {
-  (void)mhandle;
   Comm* c = reinterpret_cast<Comm*>(send_comm);
   *request = nullptr;
   ScopedTimer tm(&c->timers, T_ISEND, params().timers != 0);
@@ -374,6 +402,17 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
   r->data = reinterpret_cast<uint8_t*>(data);
   r->size = (uint64_t)size;
   r->tag = tag;
+  MemHandle* mh = reinterpret_cast<MemHandle*>(mhandle);
+  if (mh && mh->type == NCCL_PTR_CUDA && size > 0) {
+    // device memory cannot be handed to send(2): bounce it through host memory
+    r->stage.resize((size_t)size);
+    if (fl_vmm_memcpy(r->stage.data(), data, (size_t)size) != 0) {
+      FL_WARN("isend: device -> host staging copy failed: %s", fl_vmm_last_error());
+      r->used = false;
+      return ncclUnhandledCudaError;
+    }
+    r->data = r->stage.data();
+  }
   // path: the device the receiver proposed, if usable; extra stripes on following devices
   const Params& p = params();
   const int first = g_cm->bid_tx(c->channel_id, c->own_dev, d.proposed_dev) % c->ndev;
@@ -408,7 +447,6 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
 }
 
 ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags, void** mhandles, void** request) {
-  (void)mhandles;
   Comm* c = reinterpret_cast<Comm*>(recv_comm);
   *request = nullptr;
   ScopedTimer tm(&c->timers, T_IRECV, params().timers != 0);
@@ -424,6 +462,12 @@ ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags
   r->data = reinterpret_cast<uint8_t*>(data[0]);
   r->size = (uint64_t)sizes[0];
   r->tag = tags[0];
+  MemHandle* mh = reinterpret_cast<MemHandle*>(mhandles[0]);
+  if (mh && mh->type == NCCL_PTR_CUDA && sizes[0] > 0) {
+    r->stage.resize((size_t)sizes[0]);
+    r->user = r->data;                       // bytes land in the bounce buffer and are copied up when complete
+    r->data = r->stage.data();
+  }
   // choose the device for this message: re-evaluated every kFinishedBatch completions and only when the
   // connection is quiescent, so a path switch never races with data in flight (src/plugin.cc:1700-1716)
   {
@@ -471,6 +515,12 @@ ncclResult_t fl_test(void* request, int* done, int* sizes) {
     comm_progress(c, g_cm);
   }
   if (r->done) {
+    if (r->user && r->total != UINT64_MAX && r->total > 0) {
+      if (fl_vmm_memcpy(r->user, r->stage.data(), (size_t)r->total) != 0) {
+        FL_WARN("test: host -> device staging copy failed: %s", fl_vmm_last_error());
+        return ncclUnhandledCudaError;
+      }
+    }
     *done = 1;
     if (sizes) *sizes = (int)(r->is_send ? r->size : r->total);
     if (!r->is_send) {

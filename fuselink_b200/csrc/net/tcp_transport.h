@@ -85,6 +85,8 @@ struct Request {
   int tag = 0;
   uint64_t last_progress_ns = 0;
   std::vector<Stripe> stripes;           // send only
+  std::vector<uint8_t> stage;            // host bounce buffer when the user buffer is device memory
+  uint8_t* user = nullptr;               // device address the staged bytes belong to (null: no staging)
   size_t stripes_done = 0;
 };
 

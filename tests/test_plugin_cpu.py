@@ -113,6 +113,22 @@ def test_stalled_peer_times_out():
         assert rx.returncode == 0 and "EXPECTED-ERROR" in out, (out, err)
 
 
+def test_device_buffers_are_adopted_rehomed_and_staged():
+    """regMr on a "GPU" buffer (cuMem layer on its memfd stand-in): the buffer is adopted, re-homed onto the relay GPU
+    (owner + channel) % nGPUs with its contents kept, and the bytes still arrive intact through the staging path."""
+    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "8", "FL_HARNESS_VERBOSE": "1"}
+    tx, rx = _pair([3 << 20, 70000], env=env, common=["--device-buffers", "--dev", "2", "--chunk", "524288"],
+                   extra_recv=["--channel", "3"], extra_send=[])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "REGISTERED device-buffer owner 2 now-backed-by 5" in rx[1] + tx[1]     # (2 + 3) % 8
+    assert "re-homed GPU 2 -> GPU 5" in rx[2] + tx[2]
+
+
+def test_device_buffers_refused_unless_enabled():
+    tx, rx = _pair([4096], common=["--device-buffers"], env={"FUSELINK_VMM_FAKE": "1"}, timeout=30)
+    assert tx[0] != 0 and rx[0] != 0
+
+
 def test_plugin_symbols_and_properties():
     lib = ctypes.CDLL(PLUGIN)
     for sym in ("ncclNetPlugin_v6", "ncclNetPlugin_v7", "ncclNetPlugin_v8"):
