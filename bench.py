@@ -245,11 +245,17 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch,
         }
         print(json.dumps(line))
+    # the result is out: teardown must never be able to hang the job (a watchdog ends the process after 60 s)
+    sys.stdout.flush()
+    wd = threading.Timer(60.0, lambda: os._exit(0))
+    wd.daemon = True
+    wd.start()
     if heap is not None:
         heap.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    wd.cancel()
     return 0
 
 

@@ -76,9 +76,14 @@ def main():
     if rank == 0 and args.out:
         with open(args.out, "w") as f:
             json.dump({"world": world, "rows": rows}, f, indent=1)
+    import threading
+    wd = threading.Timer(60.0, lambda: os._exit(0))
+    wd.daemon = True
+    wd.start()
     heap.close()
     dist.barrier()
     dist.destroy_process_group()
+    wd.cancel()
 
 
 if __name__ == "__main__":

@@ -79,10 +79,15 @@ def main():
                                      "global_batch": cfg.global_batch, "tables_on_rank0": t_local},
                           "rank0_gather_bytes_per_step": gather_bytes,
                           "gpu_launches_per_step": getattr(model, "launches", 0) / (args.steps + args.warmup)}))
+    import threading
+    wd = threading.Timer(60.0, lambda: os._exit(0))
+    wd.daemon = True
+    wd.start()
     if heap is not None:
         heap.close()
     if world > 1:
         dist.destroy_process_group()
+    wd.cancel()
 
 
 if __name__ == "__main__":

@@ -96,10 +96,21 @@ def main():
                 "ttft_ms": max(o["ttft_ms"] for o in dec_o), "decode_tok_s": min(o["decode_tok_s"] for o in dec_o),
                 "prefill_ms": max(o["prefill_ms"] for o in pre_o), "kv_ms_max": max(o["kv_ms"] for o in pre_o),
                 "kv_GB_per_rank": pre_o[0]["kv_GB"], "comm_over_elapsed": max(o["kv_ms"] for o in pre_o) / max(o["stage_ms"] for o in pre_o)}
-        print(json.dumps(line))
-    heap.close()
+        print(json.dumps(line), flush=True)
+    # Teardown.  CUDA graphs that captured NCCL kernels are released before the process group goes away, and a
+    # watchdog ends the process if the teardown stalls: the measurement is already printed.
+    import threading
+    wd = threading.Timer(60.0, lambda: os._exit(0))
+    wd.daemon = True
+    wd.start()
+    if dec is not None:
+        dec.graph = None
+        dec.g_out = None
+    torch.cuda.synchronize()
     dist.barrier()
+    heap.close()
     dist.destroy_process_group()
+    wd.cancel()
 
 
 def _nccl_iteration(p, net, link, pre, dec, prompts, peer, is_prefill, t0):

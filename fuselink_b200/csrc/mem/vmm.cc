@@ -100,9 +100,13 @@ struct CudaDriver : Driver {
               sym("cuMemSetAccess", MemSetAccess) && sym("cuMemExportToShareableHandle", MemExportToShareableHandle) &&
               sym("cuMemImportFromShareableHandle", MemImportFromShareableHandle) &&
               sym("cuMemRetainAllocationHandle", MemRetainAllocationHandle) && sym("cuMemcpyDtoD", MemcpyDtoD) &&
-              sym("cuCtxSynchronize", CtxSynchronize) && sym("cuMemcpy", Memcpy) && sym("cuDeviceGetCount", DeviceGetCount) &&
-              sym("cuPointerGetAttribute", PointerGetAttribute);
+              sym("cuCtxSynchronize", CtxSynchronize);
     if (!ok) return false;
+    // used only by the plugin's device-buffer registration: their absence must not disable the region layer
+    (void)sym("cuMemcpy", Memcpy);
+    (void)sym("cuDeviceGetCount", DeviceGetCount);
+    (void)sym("cuPointerGetAttribute", PointerGetAttribute);
+    g_err[0] = 0;
     return chk(Init(0), "cuInit") == 0;
   }
   int chk(CUresult r, const char* what) {
@@ -179,14 +183,16 @@ struct CudaDriver : Driver {
     return chk(CtxSynchronize(), "cuCtxSynchronize");
   }
   int any_copy(void* dst, const void* src, size_t n) override {
+    if (!Memcpy) { set_err("%s: cuMemcpy not available (%ld)", "vmm", 0); return 1; }
     return chk(Memcpy((CUdeviceptr)(uintptr_t)dst, (CUdeviceptr)(uintptr_t)src, n), "cuMemcpy");
   }
   int device_count() override {
     int n = 0;
-    return DeviceGetCount(&n) == CUDA_SUCCESS ? n : 0;
+    return DeviceGetCount && DeviceGetCount(&n) == CUDA_SUCCESS ? n : 0;
   }
   int pointer_device(const void* ptr) override {
     int ord = -1;
+    if (!PointerGetAttribute) return -1;
     if (PointerGetAttribute(&ord, CU_POINTER_ATTRIBUTE_DEVICE_ORDINAL, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS) return -1;
     return ord;
   }

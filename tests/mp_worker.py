@@ -96,10 +96,15 @@ def main():
     torch.testing.assert_close(a.tables, b.tables, rtol=1e-4, atol=1e-6)
 
     dist.barrier()
-    heap.close()
     if rank == 0:
-        print("MULTIGPU-OK world", world)
+        print("MULTIGPU-OK world", world, flush=True)
+    import threading
+    wd = threading.Timer(60.0, lambda: os._exit(0))     # the checks are done: teardown may not hang the job
+    wd.daemon = True
+    wd.start()
+    heap.close()
     dist.destroy_process_group()
+    wd.cancel()
 
 
 if __name__ == "__main__":
