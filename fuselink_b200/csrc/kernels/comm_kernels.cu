@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(1024) put_chunks_kernel(const FlPutArgs a) {
 
 __global__ void wait_flags_kernel(const FlWaitArgs a) {
   const int i = threadIdx.x;
-  if (i < a.n) wait_flag_ge(a.flag[i], a.want[i], a.status, 700 + i);
+  if (i < a.n) wait_flag_ge(a.flag[i], a.want[i], a.status, 700 + i, a.limit_ns ? a.limit_ns : (uint64_t)FL_FLAG_WAIT_NS);
 }
 
 __global__ void barrier_kernel(FlSignalPtrs pads, int slot0, int rank, int world, unsigned int seq, int do_signal,

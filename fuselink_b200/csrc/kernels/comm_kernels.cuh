@@ -48,6 +48,7 @@ struct FlWaitArgs {
   unsigned int want[16];
   int n;
   int* status;
+  unsigned long long limit_ns;   // 0: the library default (10 s); tests of the timeout path pass a few milliseconds
 };
 
 struct FlSignalPtrs {

@@ -287,6 +287,7 @@ struct FlVmmRegion {
   std::vector<int> access;  // devices granted RW
   bool owns_va = true;      // adopted regions keep the foreign VA reservation
   bool owns_phys = true;    // aliases / imports hold their own references but did not allocate
+  bool pooled = false;      // slabs come from (and return to) the slab pool
 };
 
 namespace {
@@ -555,6 +556,194 @@ size_t fl_vmm_usage(int device) {
   std::lock_guard<std::mutex> l(g_mu);
   auto it = g_usage.find(device);
   return it == g_usage.end() ? 0 : it->second;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// slab pool
+// ------------------------------------------------------------------------------------------------
+namespace {
+struct Pool {
+  size_t slab_bytes = 0;
+  std::vector<std::vector<uint64_t>> free_handles;   // per device
+  bool ready = false;
+};
+Pool g_pool;
+
+bool pool_take(int dev, uint64_t* h) {
+  std::lock_guard<std::mutex> l(g_mu);
+  if (!g_pool.ready || dev < 0 || dev >= (int)g_pool.free_handles.size() || g_pool.free_handles[dev].empty()) return false;
+  *h = g_pool.free_handles[dev].back();
+  g_pool.free_handles[dev].pop_back();
+  return true;
+}
+void pool_give(int dev, uint64_t h) {
+  std::lock_guard<std::mutex> l(g_mu);
+  if (g_pool.ready && dev >= 0 && dev < (int)g_pool.free_handles.size()) g_pool.free_handles[dev].push_back(h);
+}
+}  // namespace
+
+extern "C" {
+
+int fl_pool_init(int ndev, int slabs_per_dev, size_t slab_bytes) {
+  if (!g_drv) { set_err("%s: fl_vmm_init not called (%ld)", "pool", 0); return 1; }
+  if (g_pool.ready) { set_err("%s: already initialised (%ld)", "pool", 0); return 1; }
+  if (ndev < 1 || ndev > 64) { set_err("%s: bad device count (%ld)", "pool", ndev); return 1; }
+  if (slabs_per_dev <= 0) slabs_per_dev = 256;
+  if (slab_bytes == 0) slab_bytes = 2u << 20;
+  size_t gran = 0;
+  if (g_drv->granularity(0, &gran) || gran == 0) return 1;
+  slab_bytes = round_up(slab_bytes, gran);
+  g_pool.slab_bytes = slab_bytes;
+  g_pool.free_handles.assign(ndev, {});
+  for (int d = 0; d < ndev; ++d) {
+    for (int i = 0; i < slabs_per_dev; ++i) {
+      uint64_t h = 0;
+      if (g_drv->create(d, slab_bytes, &h)) {
+        g_pool.ready = true;
+        fl_pool_shutdown();
+        return 1;
+      }
+      g_pool.free_handles[d].push_back(h);
+      std::lock_guard<std::mutex> l(g_mu);
+      g_usage[d] += slab_bytes;
+    }
+  }
+  g_pool.ready = true;
+  return 0;
+}
+
+void fl_pool_shutdown(void) {
+  if (!g_pool.ready || !g_drv) return;
+  for (size_t d = 0; d < g_pool.free_handles.size(); ++d) {
+    for (uint64_t h : g_pool.free_handles[d]) {
+      g_drv->release(h);
+      std::lock_guard<std::mutex> l(g_mu);
+      if (g_usage[(int)d] >= g_pool.slab_bytes) g_usage[(int)d] -= g_pool.slab_bytes;
+    }
+  }
+  g_pool.free_handles.clear();
+  g_pool.ready = false;
+}
+
+int fl_pool_free_slabs(int dev) {
+  std::lock_guard<std::mutex> l(g_mu);
+  if (!g_pool.ready || dev < 0 || dev >= (int)g_pool.free_handles.size()) return 0;
+  return (int)g_pool.free_handles[dev].size();
+}
+
+size_t fl_pool_slab_bytes(void) { return g_pool.slab_bytes; }
+
+FlVmmRegion* fl_pool_alloc(int dev, size_t size) {
+  if (!g_pool.ready || size == 0) { set_err("%s: pool not initialised or zero size (%ld)", "pool", 0); return nullptr; }
+  const size_t sb = g_pool.slab_bytes;
+  const size_t n = (size + sb - 1) / sb;
+  if ((size_t)fl_pool_free_slabs(dev) < n) { set_err("%s: not enough free slabs on the device (%ld needed)", "pool", (long)n); return nullptr; }
+  FlVmmRegion* r = new FlVmmRegion();
+  r->slab_bytes = sb;
+  r->size = n * sb;
+  r->pooled = true;
+  r->access.push_back(dev);
+  if (g_drv->reserve(r->size, sb, &r->va)) { delete r; return nullptr; }
+  for (size_t i = 0; i < n; ++i) {
+    Slab s;
+    pool_take(dev, &s.handle);
+    s.device = dev;
+    r->slabs.push_back(s);
+  }
+  if (map_all(r)) { fl_pool_release(r); return nullptr; }
+  register_region(r);
+  return r;
+}
+
+FlVmmRegion* fl_pool_register(void* ptr, size_t size, int owner_dev) {
+  if (!g_pool.ready) { set_err("%s: pool not initialised (%ld)", "pool", 0); return nullptr; }
+  const size_t sb = g_pool.slab_bytes;
+  if (size == 0 || size % sb || ((uintptr_t)ptr % sb)) { set_err("%s: pointer and size must be multiples of the slab size (%ld)", "pool", (long)sb); return nullptr; }
+  const size_t n = size / sb;
+  if ((size_t)fl_pool_free_slabs(owner_dev) < n) { set_err("%s: not enough free slabs on the owner (%ld needed)", "pool", (long)n); return nullptr; }
+  // stage the contents in pool slabs through a temporary mapping, then swap the mappings under the user's address
+  FlVmmRegion* r = new FlVmmRegion();
+  r->va = (uintptr_t)ptr;
+  r->size = size;
+  r->slab_bytes = sb;
+  r->owns_va = false;
+  r->pooled = true;
+  r->access.push_back(owner_dev);
+  uintptr_t tmp = 0;
+  if (g_drv->reserve(sb, sb, &tmp)) { delete r; return nullptr; }
+  int rc = 0;
+  for (size_t i = 0; i < n && !rc; ++i) {
+    Slab s;
+    pool_take(owner_dev, &s.handle);
+    s.device = owner_dev;
+    rc = g_drv->map(tmp, sb, s.handle);
+    if (!rc) rc = g_drv->set_access(tmp, sb, owner_dev);
+    if (!rc) rc = g_drv->copy(tmp, r->va + i * sb, sb);
+    g_drv->unmap(tmp, sb);
+    r->slabs.push_back(s);
+  }
+  g_drv->free_va(tmp, sb);
+  if (!rc) rc = g_drv->unmap(r->va, size);          // the caller's original backing is dropped here
+  if (!rc) rc = map_all(r);
+  if (rc) {
+    for (auto& s : r->slabs) pool_give(s.device, s.handle);
+    delete r;
+    return nullptr;
+  }
+  register_region(r);
+  return r;
+}
+
+int fl_pool_remap(FlVmmRegion* r, int slab, int target_dev, int keep_contents, const int* access_devices, int n_access,
+                  long* usec_out) {
+  if (!r || !r->pooled || slab < 0 || slab >= (int)r->slabs.size()) { set_err("%s: not a pool region / bad slab (%ld)", "pool", slab); return 1; }
+  auto t0 = std::chrono::steady_clock::now();
+  uint64_t nh = 0;
+  if (!pool_take(target_dev, &nh)) { set_err("%s: no free slab on the target device (%ld)", "pool", target_dev); return 1; }
+  Slab& s = r->slabs[slab];
+  const size_t sb = r->slab_bytes;
+  const uintptr_t va = r->va + (size_t)slab * sb;
+  int rc = 0;
+  if (keep_contents) {
+    uintptr_t tmp = 0;
+    rc = g_drv->reserve(sb, sb, &tmp);
+    if (!rc) rc = g_drv->map(tmp, sb, nh);
+    if (!rc) rc = g_drv->set_access(tmp, sb, target_dev);
+    if (!rc && !r->access.empty() && r->access[0] != target_dev) rc = g_drv->set_access(tmp, sb, r->access[0]);
+    if (!rc) rc = g_drv->copy(tmp, va, sb);
+    if (tmp) { g_drv->unmap(tmp, sb); g_drv->free_va(tmp, sb); }
+  }
+  if (!rc) rc = g_drv->unmap(va, sb);
+  if (rc) { pool_give(target_dev, nh); return rc; }
+  pool_give(s.device, s.handle);                    // the slab of the OLD device goes back to the OLD device's pool
+  s.handle = nh;
+  s.device = target_dev;
+  rc = g_drv->map(va, sb, nh);
+  if (rc) return rc;
+  if (n_access > 0 && access_devices) {
+    for (int i = 0; i < n_access && !rc; ++i) rc = g_drv->set_access(va, sb, access_devices[i]);
+  } else {
+    for (int d : r->access) if (!rc) rc = g_drv->set_access(va, sb, d);
+  }
+  if (usec_out)
+    *usec_out = (long)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count();
+  return rc;
+}
+
+void fl_pool_release(FlVmmRegion* r) {
+  if (!r || !g_drv) return;
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    g_regions.erase(r->va);
+  }
+  for (size_t i = 0; i < r->slabs.size(); ++i) {
+    if (r->slabs[i].mapped) g_drv->unmap(r->va + i * r->slab_bytes, r->slab_bytes);
+    if (r->slabs[i].handle) pool_give(r->slabs[i].device, r->slabs[i].handle);
+  }
+  if (r->owns_va && r->va) g_drv->free_va(r->va, r->size);
+  delete r;
 }
 
 }  // extern "C"

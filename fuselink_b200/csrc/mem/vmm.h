@@ -65,6 +65,28 @@ int fl_vmm_device_count(void);
 // Bytes of physical memory this layer currently holds on `device`.
 size_t fl_vmm_usage(int device);
 
+// ---- slab pool -------------------------------------------------------------------------------------------
+// Physical slabs created up-front per device, so that re-homing a live buffer costs an unmap + map + set-access and
+// no allocation.  This is the fine-grained design of the reference's src/cumem.cu (256 slabs of 2 MiB per GPU,
+// register_cumem / remap_cumem / free_cumem / show_cumem_usage): a registered buffer is re-backed slab by slab from its
+// owner's pool, and any single slab can then be re-backed from another GPU's pool.  Sizes are size_t throughout (the
+// reference's int arithmetic overflows at 2 GiB, src/cumem.cu:146-147) and a remap always takes the slab of the device
+// it was asked for (src/cumem.cu:76-83 reuses the old device's handle).
+int fl_pool_init(int ndev, int slabs_per_dev, size_t slab_bytes);   // 0 slabs_per_dev => 256, 0 slab_bytes => 2 MiB
+void fl_pool_shutdown(void);
+int fl_pool_free_slabs(int dev);                                     // slabs still available on `dev`
+size_t fl_pool_slab_bytes(void);
+// A fresh region of `size` bytes backed by pool slabs of `dev`.
+FlVmmRegion* fl_pool_alloc(int dev, size_t size);
+// Take over an existing cuMem allocation at `ptr` (size a multiple of the slab size): its contents are carried into
+// slabs of the owner's pool and the address stays valid.
+FlVmmRegion* fl_pool_register(void* ptr, size_t size, int owner_dev);
+// Re-back slab `slab` of a pool region from `target_dev`'s pool; the old slab goes back to its pool.
+int fl_pool_remap(FlVmmRegion* r, int slab, int target_dev, int keep_contents, const int* access_devices, int n_access,
+                  long* usec_out);
+// Return every slab of the region to the pools and drop the region (the address range is freed if this layer reserved it).
+void fl_pool_release(FlVmmRegion* r);
+
 #ifdef __cplusplus
 }
 #endif

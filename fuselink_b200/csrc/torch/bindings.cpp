@@ -104,7 +104,7 @@ static void all_to_all(int64_t send_addr, const std::vector<int64_t>& recv_peers
                          (int)slot0, (unsigned)chunk_bytes, want.empty() ? nullptr : w, use_bulk, (int)num_ctas, (int)threads,
                          reinterpret_cast<int*>(status_addr), cur_stream()), "fl_all_to_all");
 }
-static void wait_flags(const std::vector<std::pair<int64_t, int64_t>>& flags, int64_t status_addr) {
+static void wait_flags(const std::vector<std::pair<int64_t, int64_t>>& flags, int64_t status_addr, int64_t limit_ms) {
   FlWaitArgs a;
   memset(&a, 0, sizeof a);
   TORCH_CHECK(flags.size() <= 16, "at most 16 flags per wait");
@@ -114,6 +114,7 @@ static void wait_flags(const std::vector<std::pair<int64_t, int64_t>>& flags, in
     a.want[i] = (unsigned)flags[i].second;
   }
   a.status = reinterpret_cast<int*>(status_addr);
+  a.limit_ns = limit_ms > 0 ? (unsigned long long)limit_ms * 1000000ull : 0ull;
   check_rc(fl_wait_flags(&a, cur_stream()), "fl_wait_flags");
 }
 static void barrier(const std::vector<int64_t>& pads, int64_t slot0, int64_t rank, int64_t world, int64_t seq,
@@ -300,7 +301,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fp8_quantize_blocks", &fp8_quantize_blocks);
   m.def("fp8_grouped_gemm", &fp8_grouped_gemm);
   m.def("put_chunks", &put_chunks);
-  m.def("wait_flags", &wait_flags);
+  m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("status_addr"), py::arg("limit_ms") = 0);
   m.def("all_to_all", &all_to_all);
   m.def("barrier", &barrier);
   m.def("embbag", &embbag);
@@ -336,6 +337,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   m.def("vmm_remap_slab", &vmm_remap_slab);
   m.def("vmm_ptr2dev", [](int64_t p) { return fl_vmm_ptr2dev(reinterpret_cast<const void*>(p)); });
+  m.def("pool_init", [](int64_t ndev, int64_t slabs, int64_t slab_bytes) {
+    if (fl_pool_init((int)ndev, (int)slabs, (size_t)slab_bytes)) throw std::runtime_error(std::string("fl_pool_init: ") + fl_vmm_last_error());
+  });
+  m.def("pool_shutdown", []() { fl_pool_shutdown(); });
+  m.def("pool_free_slabs", [](int64_t dev) { return fl_pool_free_slabs((int)dev); });
+  m.def("pool_slab_bytes", []() { return (int64_t)fl_pool_slab_bytes(); });
+  m.def("pool_alloc", [](int64_t dev, int64_t size) {
+    FlVmmRegion* r = fl_pool_alloc((int)dev, (size_t)size);
+    if (!r) throw std::runtime_error(std::string("fl_pool_alloc: ") + fl_vmm_last_error());
+    return reinterpret_cast<int64_t>(r);
+  });
+  m.def("pool_register", [](int64_t ptr, int64_t size, int64_t dev) {
+    FlVmmRegion* r = fl_pool_register(reinterpret_cast<void*>(ptr), (size_t)size, (int)dev);
+    if (!r) throw std::runtime_error(std::string("fl_pool_register: ") + fl_vmm_last_error());
+    return reinterpret_cast<int64_t>(r);
+  });
+  m.def("pool_remap", [](int64_t r, int64_t slab, int64_t target, bool keep, std::vector<int> access) {
+    long usec = 0;
+    if (fl_pool_remap(reinterpret_cast<FlVmmRegion*>(r), (int)slab, (int)target, keep, access.data(), (int)access.size(), &usec))
+      throw std::runtime_error(std::string("fl_pool_remap: ") + fl_vmm_last_error());
+    return (int64_t)usec;
+  });
+  m.def("pool_release", [](int64_t r) { fl_pool_release(reinterpret_cast<FlVmmRegion*>(r)); });
   m.def("vmm_usage", [](int64_t dev) { return (int64_t)fl_vmm_usage((int)dev); });
 
   fl_monitor_bind(m);

@@ -92,3 +92,34 @@ def test_symmetric_heap_emulated_on_cpu():
     assert heaps[0].signal_slots("x", 4) == heaps[2].signal_slots("x", 4)
     for h in heaps:
         h.close()
+
+
+def test_slab_pool_register_remap_release():
+    """Pre-created slabs: registering a live buffer re-backs it slab by slab, a single slab can be re-homed without any
+    allocation, the old slab returns to its own device's pool, and sizes beyond 2 GiB are plain size_t arithmetic."""
+    C.pool_init(4, 6, 2 << 20)
+    try:
+        sb = C.pool_slab_bytes()
+        assert sb == 2 << 20 and [C.pool_free_slabs(d) for d in range(4)] == [6, 6, 6, 6]
+        owner = C.vmm_create(1, 3 * sb, 0)                      # someone else's 6 MiB buffer on GPU 1
+        view = C.tensor_from_ptr(C.vmm_ptr(owner), [3 * sb // 4], torch.int32, -1)
+        view.copy_(torch.arange(3 * sb // 4, dtype=torch.int32))
+        r = C.pool_register(C.vmm_ptr(owner), 3 * sb, 1)
+        assert C.pool_free_slabs(1) == 3 and C.vmm_num_slabs(r) == 3
+        assert torch.equal(view, torch.arange(3 * sb // 4, dtype=torch.int32))       # same address, same bytes
+        usec = C.pool_remap(r, 1, 3, True, [1])
+        assert usec >= 0 and C.vmm_slab_device(r, 1) == 3 and C.vmm_slab_device(r, 0) == 1
+        assert C.pool_free_slabs(3) == 5 and C.pool_free_slabs(1) == 4               # old slab went back to GPU 1's pool
+        assert C.vmm_ptr2dev(C.vmm_ptr(r) + sb + 5) == 3
+        assert torch.equal(view, torch.arange(3 * sb // 4, dtype=torch.int32))
+        C.pool_remap(r, 1, 2, True, [1])                        # second remap takes GPU 2's slab, not the old device's
+        assert C.vmm_slab_device(r, 1) == 2 and C.pool_free_slabs(3) == 6 and C.pool_free_slabs(2) == 5
+        fresh = C.pool_alloc(0, sb + 1)
+        assert C.vmm_num_slabs(fresh) == 2 and C.pool_free_slabs(0) == 4
+        with pytest.raises(RuntimeError):
+            C.pool_alloc(0, 5 * sb)                             # only 4 slabs left on GPU 0
+        C.pool_release(fresh)
+        C.pool_release(r)
+        assert [C.pool_free_slabs(d) for d in range(4)] == [6, 6, 6, 6]
+    finally:
+        C.pool_shutdown()
