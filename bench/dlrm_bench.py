@@ -15,7 +15,6 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 import torch.distributed as dist
-import torch.nn.functional as F
 
 torch.backends.cuda.matmul.allow_tf32 = True   # dense MLPs on the tensor cores (both arms)
 torch.backends.cudnn.allow_tf32 = True

@@ -33,7 +33,7 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from fuselink_b200 import C
-    from fuselink_b200.ops.comm import Channel, StripedP2P, barrier
+    from fuselink_b200.ops.comm import Channel, StripedP2P
     from fuselink_b200.parallel.symm import SymmetricHeap
     assert 2 * args.pairs <= world
     maxb = 1 << args.size_hi
@@ -42,7 +42,7 @@ def main():
     chans = {e: Channel(heap, f"p2p-{e}", engine=e) for e in ("ldst", "bulk")}
     striped = StripedP2P(heap, "sweep", 256 << 20) if args.relays else None
     mon = C.monitor_open("", True, world, 1, 160) if args.relays else None
-    src = torch.randn(maxb // 2, device=dev).to(torch.bfloat16) if True else None
+    src = torch.randn(maxb // 2, device=dev).to(torch.bfloat16)
     # pair i: rank 2i -> rank 2i+1
     pair = rank // 2 if rank < 2 * args.pairs else -1
     sender = pair >= 0 and rank % 2 == 0

@@ -15,8 +15,6 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-import torch
-
 
 def main():
     ap = argparse.ArgumentParser()

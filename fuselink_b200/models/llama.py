@@ -12,7 +12,6 @@ Paged KV layouts (block = `block_size` tokens):
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 from typing import Callable, Optional
 

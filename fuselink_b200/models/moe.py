@@ -6,7 +6,6 @@ math runs as plain PyTorch with an all-gather of the tokens and a reduce-scatter
 """
 from __future__ import annotations
 
-import math
 from typing import Optional
 
 import torch

@@ -10,7 +10,7 @@ the receiver waits for its running total.  No word is ever reset.
 """
 from __future__ import annotations
 
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 
