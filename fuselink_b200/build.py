@@ -189,6 +189,51 @@ def build_all(verbose: bool = False, jobs: int | None = None) -> dict:
     return arts
 
 
+def build_sanitized(kind: str = "address,undefined", verbose: bool = False) -> dict:
+    """Sanitizer builds of the host-side code (plugin, harness, monitor stress driver) under ``lib/san-<kind>/``.
+
+    ``kind`` is what goes after ``-fsanitize=``: "address,undefined" or "thread".  Used by the CPU test tier; the
+    default build never links a sanitizer run time."""
+    tag = kind.replace(",", "-")
+    out = LIB / f"san-{tag}"
+    out.mkdir(parents=True, exist_ok=True)
+    flags = ["-O1", "-g", "-std=c++17", "-fPIC", f"-fsanitize={kind}", "-fno-omit-frame-pointer", "-pthread",
+             f"-I{CUDA_HOME}/include"]
+    net = [CSRC / "net" / f"{n}.cc" for n in NET_SRCS if (CSRC / "net" / f"{n}.cc").exists()]
+    host = [CSRC / "mem" / "vmm.cc", CSRC / "monitor" / "monitor.cc"]
+    plug, har, stress = out / "libnccl-net-fuselink.so", out / "fl_net_harness", out / "monitor_stress"
+    stamp = _Stamp()
+    hdrs = _headers()
+    jobs = [
+        (plug, net + host, [CXX, *flags, "-shared", "-o", plug, *net, *host, "-ldl", "-lrt", "-lpthread"]),
+        (har, [CSRC / "net" / "harness_main.cc"], [CXX, *flags, "-o", har, CSRC / "net" / "harness_main.cc", "-ldl", "-lpthread"]),
+        (stress, [CSRC / "monitor" / "monitor_stress.cc", host[1]],
+         [CXX, *flags, "-o", stress, CSRC / "monitor" / "monitor_stress.cc", host[1], "-lrt", "-lpthread"]),
+    ]
+    todo = []
+    for o, srcs, cmd in jobs:
+        key = _sha(list(srcs) + hdrs, " ".join(map(str, cmd)))
+        if not stamp.fresh(o, key):
+            todo.append((o, cmd, key))
+    def run_with_fallback(t):
+        # the configured compiler may ship without the sanitizer run times: fall back to the system one
+        cmd = t[1]
+        last = None
+        for cxx in dict.fromkeys([cmd[0], "/usr/bin/g++", "g++"]):
+            try:
+                return _run([cxx, *cmd[1:]], verbose)
+            except RuntimeError as e:
+                last = e
+        raise last
+
+    with ThreadPoolExecutor(max_workers=3) as ex:
+        list(ex.map(run_with_fallback, todo))
+    for o, _, key in todo:
+        stamp.mark(o, key)
+    stamp.save()
+    return {"plugin": str(plug), "harness": str(har), "monitor_stress": str(stress)}
+
+
 if __name__ == "__main__":
     out = build_all(verbose="-q" not in sys.argv)
     for k, v in out.items():

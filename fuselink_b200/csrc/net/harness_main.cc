@@ -178,8 +178,8 @@ int main(int argc, char** argv) {
       api.ptr_type = NCCL_PTR_CUDA;
     }
     struct BufView { float* p; size_t n; float* data() { return p; } size_t size() { return n; } } buf{bufp, host.size()};
-    if (is_send) { fill(host, seed, mi); memcpy(bufp, host.data(), host.size() * 4); }
-    else { expect.resize(host.size()); fill(expect, seed, mi); memset(bufp, 0xA5, host.size() * 4); }
+    if (is_send) { fill(host, seed, mi); if (!host.empty()) memcpy(bufp, host.data(), host.size() * 4); }
+    else { expect.resize(host.size()); fill(expect, seed, mi); if (!host.empty()) memset(bufp, 0xA5, host.size() * 4); }
     void* mh = nullptr;
     if (api.regMr(comm, buf.data(), buf.size() * 4, &mh) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
     if (device_bufs && mi == 0) {
@@ -216,7 +216,7 @@ int main(int argc, char** argv) {
       }
       if (now_s() > msg_limit) { fprintf(stderr, "message %zu timed out\n", mi); rc = 3; }
     }
-    if (rc == 0 && !is_send && memcmp(buf.data(), expect.data(), bytes) != 0) {
+    if (rc == 0 && !is_send && bytes > 0 && memcmp(buf.data(), expect.data(), bytes) != 0) {
       size_t bad = 0;
       while (bad < bytes && ((char*)buf.data())[bad] == ((char*)expect.data())[bad]) ++bad;
       fprintf(stderr, "message %zu (%zu bytes) differs at byte %zu\n", mi, bytes, bad);
