@@ -122,6 +122,8 @@ __global__ void __launch_bounds__(1024) put_chunks_kernel(const FlPutArgs a) {
         if (sg.flag_mode == FL_FLAG_SEQ_PER_CHUNK) st_release_sys(sg.flags + c, a.seq);
         else red_release_sys_add(sg.flags, 1u);
       }
+      // device-side completion counter: the host monitor folds it into the path's completed bytes
+      if (threadIdx.x == 0 && sg.bytes_done != nullptr) atomicAdd_system(sg.bytes_done, (unsigned long long)len);
     }
     chunks_before += nch;
   }

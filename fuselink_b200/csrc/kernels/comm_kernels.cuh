@@ -26,6 +26,7 @@ struct FlSeg {
   uint32_t* flags;            // see FlFlagMode (address in the consumer's signal pad)
   int flag_mode;
   const uint32_t* wait_flags; // if set: chunk c is copied only after wait_flags[c] >= seq (relay forward)
+  unsigned long long* bytes_done;  // optional completion counter (mapped pinned host memory read by the monitor thread)
 };
 
 struct FlPutArgs {

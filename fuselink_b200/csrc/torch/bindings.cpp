@@ -69,7 +69,7 @@ static void grouped_gemm(int64_t group_mode, int64_t num_groups, int64_t cap, in
 // segs: list of (src_addr, dst_addr, bytes, flags_addr, flag_mode, wait_flags_addr)
 static void put_chunks(const std::vector<std::tuple<int64_t, int64_t, int64_t, int64_t, int64_t, int64_t>>& segs,
                        int64_t chunk_bytes, int64_t seq, bool use_bulk, int64_t num_ctas, int64_t threads,
-                       int64_t status_addr) {
+                       int64_t status_addr, const std::vector<int64_t>& counters) {
   FlPutArgs a;
   memset(&a, 0, sizeof a);
   TORCH_CHECK(segs.size() >= 1 && segs.size() <= FL_MAX_SEGS, "1..8 segments per launch");
@@ -81,6 +81,7 @@ static void put_chunks(const std::vector<std::tuple<int64_t, int64_t, int64_t, i
     a.seg[i].flags = reinterpret_cast<uint32_t*>(std::get<3>(segs[i]));
     a.seg[i].flag_mode = (int)std::get<4>(segs[i]);
     a.seg[i].wait_flags = reinterpret_cast<const uint32_t*>(std::get<5>(segs[i]));
+    a.seg[i].bytes_done = i < counters.size() ? reinterpret_cast<unsigned long long*>(counters[i]) : nullptr;
   }
   a.chunk_bytes = (unsigned)chunk_bytes; a.seq = (unsigned)seq; a.use_bulk = use_bulk;
   a.status = reinterpret_cast<int*>(status_addr);
@@ -300,7 +301,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fp8_quantize_rows", &fp8_quantize_rows);
   m.def("fp8_quantize_blocks", &fp8_quantize_blocks);
   m.def("fp8_grouped_gemm", &fp8_grouped_gemm);
-  m.def("put_chunks", &put_chunks);
+  m.def("put_chunks", &put_chunks, py::arg("segs"), py::arg("chunk_bytes"), py::arg("seq"), py::arg("use_bulk"), py::arg("num_ctas"),
+        py::arg("threads"), py::arg("status_addr"), py::arg("counters") = std::vector<int64_t>());
   m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("status_addr"), py::arg("limit_ms") = 0);
   m.def("all_to_all", &all_to_all);
   m.def("barrier", &barrier);

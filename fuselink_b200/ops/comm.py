@@ -71,6 +71,14 @@ class Channel:
         self.slot0 = heap.signal_slots(f"chan:{name}", heap.world)
         self.expected = [0] * heap.world
         self.engine = engine or knobs().copy_engine
+        self.counters = None      # optional pinned int64[world]: bytes this rank has finished sending to each peer
+
+    def attach_counters(self, selector) -> torch.Tensor:
+        """Let the put kernel report completed bytes per destination straight to the monitor: a pinned host array the
+        kernel adds to (system-scope atomics) and the monitor's sweeper thread reads (`fl_monitor_attach_counters`)."""
+        self.counters = torch.zeros(max(self.heap.world, 64), dtype=torch.int64).pin_memory()
+        self.C.monitor_attach_counters(selector.mon, 0, self.counters.data_ptr())
+        return self.counters
 
     # -- sender ------------------------------------------------------------------------------------
     def put(self, src: torch.Tensor, dst_rank: int, dst_offset: int, nbytes: Optional[int] = None,
@@ -84,7 +92,8 @@ class Channel:
         seg = (src.data_ptr(), self.heap.addr(dst_offset, dst_rank), nbytes,
                self.heap.sig_addr(self.slot0 + self.heap.rank, dst_rank), FLAG_COUNT, 0)
         ctas, threads = _launch_shape(n, self.engine)
-        self.C.put_chunks([seg], cb, 0, self.engine == "bulk", ctas, threads, self.heap.status_addr)
+        ctr = [self.counters.data_ptr() + 8 * dst_rank] if self.counters is not None else []
+        self.C.put_chunks([seg], cb, 0, self.engine == "bulk", ctas, threads, self.heap.status_addr, ctr)
         return n
 
     def put_many(self, items: Sequence[Tuple[int, int, int, int]], chunk_bytes: int) -> None:

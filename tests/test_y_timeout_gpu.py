@@ -33,3 +33,31 @@ def test_flag_wait_runs_out_and_reports_status():
     finally:
         for hh in heaps:
             hh.close()
+
+
+@pytest.mark.skipif(__import__("os").environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1",
+                    reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
+def test_put_kernel_feeds_monitor_counters():
+    """The put kernel adds the bytes of every finished chunk to a pinned host counter that the monitor's sweeper folds
+    into the path's completed bytes (device-side completion counters -> lock-free host thread)."""
+    from fuselink_b200 import C
+    from fuselink_b200.ops.comm import Channel
+    from fuselink_b200.parallel.selector import PathSelector
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    heaps = SymmetricHeap.emulated(2, 32 << 20)
+    sel = PathSelector(2)
+    try:
+        ch = Channel(heaps[0], "ctr")
+        ctr = ch.attach_counters(sel)
+        dst = heaps[0].alloc_tensor([4 << 20], torch.uint8)
+        src = torch.randint(0, 255, (4 << 20,), dtype=torch.uint8, device="cuda")
+        C.monitor_post_bytes(sel.mon, 0, 1, 4 << 20, C.monitor_now_ns())
+        ch.put(src, 1, dst.offset)
+        torch.cuda.synchronize()
+        assert int(ctr[1]) == 4 << 20 and int(ctr[0]) == 0
+        time.sleep(0.01)                                  # a few sweeps of the monitor thread
+        assert C.monitor_outstanding(sel.mon, 0, 1) == 0
+    finally:
+        sel.close()
+        for h in heaps:
+            h.close()
