@@ -227,6 +227,23 @@ def main():
         if heap is not None:
             heap.check_status("e2e region")
 
+    # ---------------------------------------------------------------- roofline of the fused path (hottest rank)
+    roof = None
+    try:
+        if args.impl == "fuselink":
+            from fuselink_b200.utils import roofline as rl
+            rows = layer.ws.counts_now().sum().to(torch.float64).reshape(1)
+            if world > 1:
+                dist.all_reduce(rows, op=dist.ReduceOp.MAX)
+            hot_rows = int(rows.item())
+            m = rl.moe_step_model(T, world, cfg.hidden, cfg.ffn, cfg.topk, hot_rows)
+            roof = {"hot_rank_rows": hot_rows, "mean_rows": T * cfg.topk, "flops_hot_rank": m["flops"],
+                    "nvlink_bytes_hot_rank": m["nvlink_bytes"], "target_ms": m["target_ms"],
+                    "achieved_fraction": m["target_ms"] / ms_per_step, "peaks": rl.peaks().source,
+                    "definition": "max(FLOPs / measured sustained cuBLAS bf16, NVLink bytes / 770 GB/s) on the rank with most routed rows"}
+    except Exception as e:  # noqa: BLE001 - reporting only
+        roof = {"error": repr(e)}
+
     if rank == 0:
         flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
         line = {
@@ -242,7 +259,7 @@ def main():
                        "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
                        "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
             "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roof,
         }
         print(json.dumps(line))
     # the result is out: teardown must never be able to hang the job (a watchdog ends the process after 60 s)
