@@ -94,7 +94,7 @@ int main(int argc, char** argv) {
   const bool is_send = !strcmp(argv[2], "send");
   const std::string hfile = argv[3];
   size_t chunk = 512 * 1024;
-  int inflight = 8, dev = 0, die_after = -1, channel = 0;
+  int inflight = 8, dev = 0, die_after = -1, channel = 0, nch = 1;
   uint64_t seed = 0;
   bool expect_error = false, device_bufs = false;
   Api api;
@@ -107,6 +107,7 @@ int main(int argc, char** argv) {
     else if (a == "--seed") seed = val();
     else if (a == "--dev") dev = (int)val();
     else if (a == "--abi") api.abi = (int)val();
+    else if (a == "--channels") nch = (int)val();          // connections used side by side; chunk c travels on channel c % N
     else if (a == "--channel") channel = (int)val();      // receiver: burn this many channel ids first
     else if (a == "--die-after-chunks") die_after = (int)val();
     else if (a == "--expect-error") expect_error = true;
@@ -125,24 +126,29 @@ int main(int argc, char** argv) {
   api.devices(&ndev);
   if (dev >= ndev) { fprintf(stderr, "device %d of %d\n", dev, ndev); return 2; }
 
+  if (nch < 1 || nch > 16) { fprintf(stderr, "--channels must be in [1, 16]\n"); return 2; }
   char handle[NCCL_NET_HANDLE_MAXSIZE];
-  void *lcomm = nullptr, *comm = nullptr;
+  std::vector<void*> lcomms(nch, nullptr), comms(nch, nullptr);
   const double t_limit = now_s() + 120.0;
   if (!is_send) {
     for (int i = 0; i < channel; ++i) {   // every listen takes the next global channel id
       void* tmp = nullptr;
       if (api.listen(dev, handle, &tmp) == ncclSuccess) api.closeListen(tmp);
     }
-    if (api.listen(dev, handle, &lcomm) != ncclSuccess) { fprintf(stderr, "listen failed\n"); return 2; }
     std::string tmp = hfile + ".tmp";
     FILE* f = fopen(tmp.c_str(), "wb");
-    fwrite(handle, 1, sizeof handle, f);
+    for (int c = 0; c < nch; ++c) {
+      if (api.listen((dev + c) % ndev, handle, &lcomms[c]) != ncclSuccess) { fprintf(stderr, "listen failed\n"); return 2; }
+      fwrite(handle, 1, sizeof handle, f);
+    }
     fclose(f);
     rename(tmp.c_str(), hfile.c_str());
-    while (!comm) {
-      if (api.accept(lcomm, &comm) != ncclSuccess) { fprintf(stderr, "accept failed\n"); return 2; }
-      if (now_s() > t_limit) { fprintf(stderr, "accept timed out\n"); return 3; }
-      if (!comm) usleep(200);
+    for (int c = 0; c < nch; ++c) {
+      while (!comms[c]) {
+        if (api.accept(lcomms[c], &comms[c]) != ncclSuccess) { fprintf(stderr, "accept failed\n"); return 2; }
+        if (now_s() > t_limit) { fprintf(stderr, "accept timed out\n"); return 3; }
+        if (!comms[c]) usleep(200);
+      }
     }
   } else {
     FILE* f = nullptr;
@@ -150,14 +156,19 @@ int main(int argc, char** argv) {
       if (now_s() > t_limit) { fprintf(stderr, "no handle file\n"); return 3; }
       usleep(1000);
     }
-    if (fread(handle, 1, sizeof handle, f) != sizeof handle) { fprintf(stderr, "short handle\n"); return 2; }
+    std::vector<char> handles((size_t)nch * sizeof handle);
+    if (fread(handles.data(), 1, handles.size(), f) != handles.size()) { fprintf(stderr, "short handle file\n"); return 2; }
     fclose(f);
-    while (!comm) {
-      if (api.connect(dev, handle, &comm) != ncclSuccess) { fprintf(stderr, "connect failed\n"); return 2; }
-      if (now_s() > t_limit) { fprintf(stderr, "connect timed out\n"); return 3; }
-      if (!comm) usleep(200);
+    for (int c = 0; c < nch; ++c) {
+      memcpy(handle, handles.data() + (size_t)c * sizeof handle, sizeof handle);
+      while (!comms[c]) {
+        if (api.connect((dev + c) % ndev, handle, &comms[c]) != ncclSuccess) { fprintf(stderr, "connect failed\n"); return 2; }
+        if (now_s() > t_limit) { fprintf(stderr, "connect timed out\n"); return 3; }
+        if (!comms[c]) usleep(200);
+      }
     }
   }
+  void* comm = comms[0];
 
   int rc = 0;
   size_t total_bytes = 0;
@@ -180,35 +191,40 @@ int main(int argc, char** argv) {
     struct BufView { float* p; size_t n; float* data() { return p; } size_t size() { return n; } } buf{bufp, host.size()};
     if (is_send) { fill(host, seed, mi); if (!host.empty()) memcpy(bufp, host.data(), host.size() * 4); }
     else { expect.resize(host.size()); fill(expect, seed, mi); if (!host.empty()) memset(bufp, 0xA5, host.size() * 4); }
-    void* mh = nullptr;
-    if (api.regMr(comm, buf.data(), buf.size() * 4, &mh) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
+    std::vector<void*> mhs(nch, nullptr);
+    for (int c = 0; c < nch; ++c)
+      if (api.regMr(comms[c], buf.data(), buf.size() * 4, &mhs[c]) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
     if (device_bufs && mi == 0) {
       auto p2d = (int (*)(const void*))dlsym(lib, "fl_vmm_ptr2dev");
       printf("REGISTERED device-buffer owner %d now-backed-by %d\n", dev, p2d ? p2d(bufp) : -1);
     }
     const size_t nchunks = bytes == 0 ? 1 : (bytes + chunk - 1) / chunk;
     size_t next = 0, done_chunks = 0;
-    std::deque<void*> reqs;
+    std::vector<std::deque<void*>> reqs(nch);
     const double msg_limit = now_s() + 90.0;
     while (done_chunks < nchunks && rc == 0) {
-      while (next < nchunks && (int)reqs.size() < inflight) {
+      // post: chunk `next` belongs to channel next % nch; stop at the first channel that is full or would block
+      while (next < nchunks) {
+        const int c = (int)(next % nch);
+        if ((int)reqs[c].size() >= inflight) break;
         const size_t off = next * chunk;
         const int len = (int)(bytes - off < chunk ? bytes - off : chunk);
         void* r = nullptr;
-        ncclResult_t e = is_send ? api.isend(comm, (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mh, &r)
-                                 : api.irecv(comm, (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mh, &r);
+        ncclResult_t e = is_send ? api.isend(comms[c], (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mhs[c], &r)
+                                 : api.irecv(comms[c], (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mhs[c], &r);
         if (e != ncclSuccess) { fprintf(stderr, "%s failed with %d\n", is_send ? "isend" : "irecv", (int)e); rc = 4; break; }
         if (!r) break;   // would block
-        reqs.push_back(r);
+        reqs[c].push_back(r);
         ++next;
       }
       if (rc) break;
-      if (!reqs.empty()) {
+      for (int c = 0; c < nch && rc == 0; ++c) {
+        if (reqs[c].empty()) continue;
         int done = 0, sz = 0;
-        ncclResult_t e = api.test(reqs.front(), &done, &sz);
+        ncclResult_t e = api.test(reqs[c].front(), &done, &sz);
         if (e != ncclSuccess) { fprintf(stderr, "test failed with %d\n", (int)e); rc = 4; break; }
         if (done) {
-          reqs.pop_front();
+          reqs[c].pop_front();
           ++done_chunks;
           ++chunks_done_total;
           if (is_send && die_after >= 0 && chunks_done_total >= die_after) _exit(9);   // abrupt death: no close, no flush
@@ -222,7 +238,7 @@ int main(int argc, char** argv) {
       fprintf(stderr, "message %zu (%zu bytes) differs at byte %zu\n", mi, bytes, bad);
       rc = 5;
     }
-    api.deregMr(comm, mh);
+    for (int c = 0; c < nch; ++c) api.deregMr(comms[c], mhs[c]);
     total_bytes += bytes;
   }
   const double dt = now_s() - t0;
@@ -232,7 +248,13 @@ int main(int argc, char** argv) {
   } else if (rc == 0) {
     printf("OK %s %zu bytes in %.4f s (%.3f GB/s) abi v%d\n", is_send ? "sent" : "received", total_bytes, dt, total_bytes / dt / 1e9, api.abi);
   }
-  if (is_send) api.closeSend(comm);
-  else { api.closeRecv(comm); api.closeListen(lcomm); }
+  auto decisions = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_decisions");
+  auto fallbacks = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_fallbacks");
+  if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);
+  for (int c = 0; c < nch; ++c) {
+    if (is_send) api.closeSend(comms[c]);
+    else { api.closeRecv(comms[c]); api.closeListen(lcomms[c]); }
+  }
+  (void)comm;
   return rc;
 }

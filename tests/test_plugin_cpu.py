@@ -60,6 +60,16 @@ def test_striping_over_virtual_nics():
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
 
 
+def test_four_channels_side_by_side_spread_over_nics():
+    """The reference's bandwidth configuration: 4 channels per peer, 512 KiB chunks, 8 steps in flight each
+    (NCCL_NCHANNELS_PER_NET_PEER=4).  Chunk c travels on channel c % 4; every channel picks its NIC through the monitor."""
+    env = {"FUSELINK_TCP_NDEV": "8", "NCCL_FUSELINK_DEGREE": "2", "FUSELINK_MIN_STRIPE_BYTES": "65536"}
+    tx, rx = _pair([64 << 20, 1 << 20, 3], common=["--channels", "4", "--chunk", "524288", "--inflight", "8"], env=env)
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    line = [l for l in rx[1].splitlines() if l.startswith("SELECTOR")][0].split()
+    assert int(line[2]) >= 4            # at least one path decision per channel
+
+
 def test_monitor_off_uses_channel_modulo():
     tx, rx = _pair([1 << 20], env={"FUSELINK_MONITOR": "0"})
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
