@@ -84,7 +84,8 @@ class DLRM(nn.Module):
         for t in range(self.t_first, self.t_first + self.t_local):
             gt = torch.Generator(device=device if str(device) != "cpu" else "cpu").manual_seed(seed * 977 + t)
             tabs.append((torch.rand(cfg.rows, cfg.dim, generator=gt, device=device) * 2 - 1) * bound)
-        self.tables = torch.stack(tabs) if tabs else torch.zeros(0, cfg.rows, cfg.dim, device=device)  # not a Parameter: updated by the kernel
+        # a buffer, not a Parameter: the backward kernel applies SGD to it in place; it is part of state_dict() for checkpoints
+        self.register_buffer("tables", torch.stack(tabs) if tabs else torch.zeros(0, cfg.rows, cfg.dim, device=device))
         torch.manual_seed(seed)
         self.bottom = _mlp((cfg.dense_features,) + tuple(cfg.bottom), last_act=True).to(device)
         n_vec = cfg.num_tables + 1

@@ -97,3 +97,17 @@ def test_checkpoint_roundtrip_moe_state():
         b.load_state_dict(torch.load(os.path.join(d, "ck.pt")))
     x = torch.randn(8, 64).to(torch.bfloat16)
     assert torch.equal(a(x), b(x))
+
+
+def test_checkpoint_roundtrip_dlrm_includes_tables():
+    from fuselink_b200.models.dlrm import DLRM, DLRMConfig, synthetic_batch
+    cfg = DLRMConfig(num_tables=3, rows=200, dim=128, pooling=4, global_batch=16, lr=0.1)
+    a, b = DLRM(cfg, None, 0, 1, device="cpu", seed=1), DLRM(cfg, None, 0, 1, device="cpu", seed=2)
+    opt = torch.optim.SGD(a.dense_parameters(), lr=cfg.lr)
+    a.train_step(*synthetic_batch(cfg, 0, 1, "cpu", seed=0), opt)          # tables now differ from their init
+    with tempfile.TemporaryDirectory() as d:
+        torch.save(a.state_dict(), os.path.join(d, "ck.pt"))
+        b.load_state_dict(torch.load(os.path.join(d, "ck.pt")))
+    assert "tables" in a.state_dict() and torch.equal(a.tables, b.tables)
+    dense, idx, _ = synthetic_batch(cfg, 0, 1, "cpu", seed=3)
+    assert torch.equal(a.dense_forward(dense, a._pooled_reference(idx)), b.dense_forward(dense, b._pooled_reference(idx)))
