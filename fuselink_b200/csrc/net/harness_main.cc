@@ -250,6 +250,9 @@ int main(int argc, char** argv) {
   }
   auto decisions = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_decisions");
   auto fallbacks = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_fallbacks");
+  auto direct_b = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_direct_bytes");
+  auto direct_m = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_direct_msgs");
+  if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes);
   if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);
   for (int c = 0; c < nch; ++c) {
     if (is_send) api.closeSend(comms[c]);

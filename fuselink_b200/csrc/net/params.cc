@@ -79,6 +79,7 @@ const Params& params() {
   p.timers = param_i64("FUSELINK_TIMERS", 0);
   p.cuda_ptrs = param_i64("FUSELINK_CUDA_PTRS", 0);
   p.vmm_fake = param_i64("FUSELINK_VMM_FAKE", 0);
+  p.nvl = param_i64("FUSELINK_NVL", 1);
   p.remap = param_i64("FUSELINK_REMAP", 1);
   p.fault_drop_after = param_i64("FUSELINK_FAULT_CLOSE_AFTER_BYTES", 0);
   if (p.tcp_ndev < 1) p.tcp_ndev = 1;

@@ -35,6 +35,7 @@ struct Params {
   int64_t timers;              // FUSELINK_TIMERS (0): print per-phase timers at close
   int64_t cuda_ptrs;           // FUSELINK_CUDA_PTRS (0): accept NCCL_PTR_CUDA registrations (cuMem adopt + relay remap + staging)
   int64_t vmm_fake;            // FUSELINK_VMM_FAKE (0): memfd-backed stand-in for the CUDA driver (CPU tests)
+  int64_t nvl;                 // FUSELINK_NVL (1): same-host direct path, receive buffers exported as cuMem handles
   int64_t remap;               // FUSELINK_REMAP (1): re-home a registered CUDA buffer onto the relay GPU
   int64_t fault_drop_after;    // FUSELINK_FAULT_CLOSE_AFTER_BYTES (0): test hook, sender closes a data socket mid-stream
 };

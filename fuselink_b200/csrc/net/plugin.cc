@@ -17,9 +17,11 @@
 #include <stdlib.h>
 #include <string.h>
 #include <sys/socket.h>
+#include <sys/un.h>
 #include <unistd.h>
 
 #include <atomic>
+#include <map>
 #include <mutex>
 #include <random>
 
@@ -38,6 +40,7 @@ namespace {
 constexpr uint64_t kHelloMagic = 0x464c4e4b48454c4full;  // "FLNKHELO"
 constexpr uint32_t kDescMagic = 0x464c4453u;
 constexpr uint32_t kFrameMagic = 0x464c4652u;
+constexpr uint32_t kFrameDirectMagic = 0x464c4452u;
 
 std::mutex g_mu;
 ConnManager* g_cm = nullptr;
@@ -52,7 +55,101 @@ struct MemHandle {
   size_t size;
   int type;
   FlVmmRegion* region;   // CUDA registrations made through the cuMem layer, else null
+  uint32_t mr_id;        // non-zero for a region that can be exported to a same-host sender
 };
+std::atomic<uint32_t> g_mr_counter{1};
+struct Adopted { FlVmmRegion* region; uint32_t mr_id; int refs; };
+std::map<void*, Adopted> g_adopted;          // cuMem allocations taken over by regMr, by base address (under g_mu)
+std::atomic<uint64_t> g_direct_bytes{0};     // payload bytes that went through the direct path (sender side)
+std::atomic<uint64_t> g_direct_msgs{0};
+
+// ---- same-host side channel ---------------------------------------------------------------------------
+// A receive buffer that lives in a cuMem allocation can be written by a sender on the same machine without
+// touching host memory: the receiver hands the allocation's file descriptors over a Unix socket
+// (SCM_RIGHTS), the sender maps them, stores the payload through that mapping and sends a frame header with
+// no payload.  The reference gets the same effect inside one process by copying from the relay GPU's alias
+// address (src/fuselink.cc:25-41); across processes the descriptor has to travel, which is what this does.
+// The socket lives in the abstract namespace under a random token published in the listen handle, so a
+// sender on another host (or in another network namespace) simply fails to connect and stays on TCP.
+void nvl_sockaddr(uint64_t token, sockaddr_un* sa, socklen_t* len) {
+  memset(sa, 0, sizeof *sa);
+  sa->sun_family = AF_UNIX;
+  const int n = snprintf(sa->sun_path + 1, sizeof sa->sun_path - 1, "fuselink-nvl-%016llx", (unsigned long long)token);
+  *len = (socklen_t)(offsetof(sockaddr_un, sun_path) + 1 + n);
+}
+
+int nvl_send_fds(int sock, const NvlExportMsg& msg, const int* fds, int nfds) {
+  char cbuf[CMSG_SPACE(sizeof(int) * 16)];
+  if (nfds > 16) return -1;
+  memset(cbuf, 0, sizeof cbuf);
+  iovec iov{const_cast<NvlExportMsg*>(&msg), sizeof msg};
+  msghdr mh;
+  memset(&mh, 0, sizeof mh);
+  mh.msg_iov = &iov;
+  mh.msg_iovlen = 1;
+  mh.msg_control = cbuf;
+  mh.msg_controllen = CMSG_SPACE(sizeof(int) * nfds);
+  cmsghdr* cm = CMSG_FIRSTHDR(&mh);
+  cm->cmsg_level = SOL_SOCKET;
+  cm->cmsg_type = SCM_RIGHTS;
+  cm->cmsg_len = CMSG_LEN(sizeof(int) * nfds);
+  memcpy(CMSG_DATA(cm), fds, sizeof(int) * nfds);
+  ssize_t r;
+  do { r = sendmsg(sock, &mh, MSG_NOSIGNAL); } while (r < 0 && errno == EINTR);
+  return r == (ssize_t)sizeof msg ? 0 : -1;
+}
+
+// returns 1 when a message was read, 0 when nothing is waiting, -1 on error / closed
+int nvl_recv_fds(int sock, NvlExportMsg* msg, int* fds, int* nfds) {
+  char cbuf[CMSG_SPACE(sizeof(int) * 16)];
+  iovec iov{msg, sizeof *msg};
+  msghdr mh;
+  memset(&mh, 0, sizeof mh);
+  mh.msg_iov = &iov;
+  mh.msg_iovlen = 1;
+  mh.msg_control = cbuf;
+  mh.msg_controllen = sizeof cbuf;
+  ssize_t r = recvmsg(sock, &mh, MSG_DONTWAIT | MSG_CMSG_CLOEXEC);
+  if (r < 0) return (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR) ? 0 : -1;
+  if (r == 0) return -1;
+  *nfds = 0;
+  for (cmsghdr* cm = CMSG_FIRSTHDR(&mh); cm; cm = CMSG_NXTHDR(&mh, cm)) {
+    if (cm->cmsg_level == SOL_SOCKET && cm->cmsg_type == SCM_RIGHTS) {
+      const int n = (int)((cm->cmsg_len - CMSG_LEN(0)) / sizeof(int));
+      memcpy(fds, CMSG_DATA(cm), sizeof(int) * n);
+      *nfds = n;
+    }
+  }
+  if (r != (ssize_t)sizeof *msg || msg->magic != kNvlMagic || *nfds != msg->nslabs) {
+    for (int i = 0; i < *nfds; ++i) close(fds[i]);
+    return -1;
+  }
+  return 1;
+}
+
+// sender: map every region the peer has announced so far
+void nvl_ingest(Comm* c, int device) {
+  while (c->nvl_fd >= 0) {
+    NvlExportMsg msg;
+    int fds[16], nfds = 0;
+    const int rc = nvl_recv_fds(c->nvl_fd, &msg, fds, &nfds);
+    if (rc == 0) return;
+    if (rc < 0) {
+      close(c->nvl_fd);
+      c->nvl_fd = -1;                              // direct path off for this connection; TCP carries on
+      return;
+    }
+    FlVmmRegion* r = fl_vmm_import(device < 0 ? 0 : device, fds, nfds, (size_t)msg.slab_bytes);
+    for (int i = 0; i < nfds; ++i) close(fds[i]);
+    if (!r) {
+      FL_WARN("direct path: cannot map the peer's region %u (%s); that region stays on the staged path", msg.mr_id, fl_vmm_last_error());
+      c->peer_mrs.push_back({msg.mr_id, nullptr, 0, nullptr});
+      continue;
+    }
+    c->peer_mrs.push_back({msg.mr_id, fl_vmm_ptr(r), msg.size, r});
+    FL_INFO("direct path: peer region %u (%llu bytes) mapped at %p", msg.mr_id, (unsigned long long)msg.size, fl_vmm_ptr(r));
+  }
+}
 
 uint64_t random_u64() {
   static std::mt19937_64 rng{std::random_device{}()};
@@ -156,6 +253,21 @@ ncclResult_t fl_listen(int dev, void* opaque, void** listen_comm) {
   h->channel_id = lc->channel_id;
   h->ndev = g_ndev;
   h->listen_dev = dev;
+  if (g_ngpus > 0 && params().nvl) {
+    // same-host side channel for cuMem handles; failing to set it up only means every peer stays on TCP
+    const uint64_t token = random_u64() | 1ull;
+    int ufd = socket(AF_UNIX, SOCK_SEQPACKET | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
+    sockaddr_un sa;
+    socklen_t sl;
+    nvl_sockaddr(token, &sa, &sl);
+    if (ufd >= 0 && bind(ufd, reinterpret_cast<sockaddr*>(&sa), sl) == 0 && listen(ufd, 64) == 0) {
+      lc->uds_fd = ufd;
+      lc->nvl_token = token;
+      h->nvl_token = token;
+    } else if (ufd >= 0) {
+      close(ufd);
+    }
+  }
   *listen_comm = lc;
   return ncclSuccess;
 }
@@ -193,6 +305,20 @@ ncclResult_t fl_connect_impl(int dev, void* opaque, void** send_comm) {
       c->pending_fds.push_back(fd);
       c->hello_sent.push_back(0);
     }
+    if (h->nvl_token && g_ngpus > 0 && params().nvl) {
+      // the abstract Unix address only resolves on the listener's own machine; a refusal means "remote peer"
+      int ufd = socket(AF_UNIX, SOCK_SEQPACKET | SOCK_CLOEXEC, 0);
+      sockaddr_un sa;
+      socklen_t sl;
+      nvl_sockaddr(h->nvl_token, &sa, &sl);
+      const uint64_t hello[2] = {kNvlMagic, c->uid};
+      if (ufd >= 0 && connect(ufd, reinterpret_cast<sockaddr*>(&sa), sl) == 0 &&
+          send(ufd, hello, sizeof hello, MSG_NOSIGNAL) == (ssize_t)sizeof hello) {
+        c->nvl_fd = ufd;
+      } else if (ufd >= 0) {
+        close(ufd);
+      }
+    }
     h->connect_state = c;
   }
   bool all = true;
@@ -215,7 +341,7 @@ ncclResult_t fl_connect_impl(int dev, void* opaque, void** send_comm) {
     hello.magic = kHelloMagic;
     hello.comm_uid = c->uid;
     hello.kind = i == 0 ? 0 : 1;
-    hello.dev = i == 0 ? -1 : (int)i - 1;
+    hello.dev = i == 0 ? (c->nvl_fd >= 0 ? -2 : -1) : (int)i - 1;   // control hello: -2 announces a side channel
     hello.sender_dev = c->own_dev;
     hello.ndev = c->ndev;
     ssize_t r = send(fd, reinterpret_cast<uint8_t*>(&hello) + c->hello_sent[i], sizeof hello - c->hello_sent[i], MSG_DONTWAIT | MSG_NOSIGNAL);
@@ -242,6 +368,26 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
     ps.fd = fd;
     ps.got = 0;
     lc->pending.push_back(ps);
+  }
+  while (lc->uds_fd >= 0) {
+    int ufd = accept4(lc->uds_fd, nullptr, nullptr, SOCK_CLOEXEC);
+    if (ufd < 0) break;
+    lc->nvl_pending.push_back({ufd, 0});
+  }
+  for (size_t i = 0; i < lc->nvl_pending.size();) {
+    auto& np = lc->nvl_pending[i];
+    if (np.uid == 0) {
+      uint64_t hello[2] = {0, 0};
+      ssize_t r = recv(np.fd, hello, sizeof hello, MSG_DONTWAIT);
+      if (r == (ssize_t)sizeof hello && hello[0] == kNvlMagic && hello[1] != 0) {
+        np.uid = hello[1];
+      } else if (r >= 0 || (errno != EAGAIN && errno != EWOULDBLOCK && errno != EINTR)) {
+        close(np.fd);
+        lc->nvl_pending.erase(lc->nvl_pending.begin() + i);
+        continue;
+      }
+    }
+    ++i;
   }
   for (size_t i = 0; i < lc->pending.size();) {
     PendingSock& ps = lc->pending[i];
@@ -273,6 +419,7 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
       lc->partials.push_back({ps.hello.comm_uid, c, 0});
       part = &lc->partials.back();
     }
+    if (ps.hello.kind == 0 && ps.hello.dev == -2) part->comm->nvl_fd = -2;   // a side channel belongs to this connection
     if (ps.hello.kind == 0) part->comm->ctrl_fd = ps.fd;
     else part->comm->data[ps.hello.dev].fd = ps.fd;
     part->have++;
@@ -281,6 +428,17 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
   for (size_t i = 0; i < lc->partials.size(); ++i) {
     if (lc->partials[i].have == 1 + lc->partials[i].comm->ndev) {
       Comm* c = lc->partials[i].comm;
+      if (c->nvl_fd == -2) {
+        // the sender connected its side channel before it sent the hello, so it is in the backlog by now
+        for (size_t k = 0; k < lc->nvl_pending.size(); ++k) {
+          if (lc->nvl_pending[k].uid == c->uid) {
+            c->nvl_fd = lc->nvl_pending[k].fd;
+            lc->nvl_pending.erase(lc->nvl_pending.begin() + k);
+            break;
+          }
+        }
+        if (c->nvl_fd == -2) continue;             // its hello has not been read yet: next call
+      }
       lc->partials.erase(lc->partials.begin() + i);
       c->cur_dev = -1;
       *recv_comm = c;
@@ -308,7 +466,7 @@ ncclResult_t fl_accept_v7(void* listen_comm, void** recv_comm, ncclNetDeviceHand
 // only touches host memory, so a CUDA registration is refused unless the device transport is active.
 ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
   if (type == NCCL_PTR_HOST) {
-    *mhandle = new MemHandle{data, size, type, nullptr};
+    *mhandle = new MemHandle{data, size, type, nullptr, 0};
     return ncclSuccess;
   }
   if (type != NCCL_PTR_CUDA || g_ngpus <= 0) {
@@ -320,20 +478,32 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
   // owner GPU with read/write access (src/fuselink.cc:43-56).  A buffer that is not a cuMem allocation (or that is
   // registered again) is used where it is.
   Comm* c = reinterpret_cast<Comm*>(comm);
-  MemHandle* m = new MemHandle{data, size, type, nullptr};
-  if (params().remap) {
-    int dev = fl_vmm_pointer_device(data);
-    if (dev < 0) dev = 0;
-    FlVmmRegion* r = fl_vmm_adopt(data, size, dev);
-    if (r) {
-      const int relay = (dev + (c ? c->channel_id : 0)) % g_ngpus;
-      long usec = 0;
-      const int access[2] = {dev, relay};
-      if (relay != dev && fl_vmm_remap_slab(r, 0, relay, 1, access, 2, &usec) == 0)
-        FL_INFO("regMr: %zu bytes at %p re-homed GPU %d -> GPU %d in %ld us", size, data, dev, relay, usec);   // "Remap time"
-      m->region = r;
+  MemHandle* m = new MemHandle{data, size, type, nullptr, 0};
+  if (params().remap || params().nvl) {
+    std::lock_guard<std::mutex> l(g_mu);
+    auto it = g_adopted.find(data);
+    if (it != g_adopted.end()) {
+      // NCCL registers one buffer once per channel: the allocation is adopted (and re-homed) by the first
+      // registration only, the others share it, so that an exported descriptor always names what the address maps
+      it->second.refs++;
+      m->region = it->second.region;
+      m->mr_id = it->second.mr_id;
     } else {
-      FL_INFO("regMr: %p is not a cuMem allocation (%s): registered in place", data, fl_vmm_last_error());
+      int dev = fl_vmm_pointer_device(data);
+      if (dev < 0) dev = 0;
+      FlVmmRegion* r = fl_vmm_adopt(data, size, dev);
+      if (r) {
+        const int relay = (dev + (c ? c->channel_id : 0)) % g_ngpus;
+        long usec = 0;
+        const int access[2] = {dev, relay};
+        if (params().remap && relay != dev && fl_vmm_remap_slab(r, 0, relay, 1, access, 2, &usec) == 0)
+          FL_INFO("regMr: %zu bytes at %p re-homed GPU %d -> GPU %d in %ld us", size, data, dev, relay, usec);   // "Remap time"
+        m->region = r;
+        m->mr_id = g_mr_counter.fetch_add(1);
+        g_adopted[data] = Adopted{r, m->mr_id, 1};
+      } else {
+        FL_INFO("regMr: %p is not a cuMem allocation (%s): registered in place", data, fl_vmm_last_error());
+      }
     }
   }
   *mhandle = m;
@@ -349,7 +519,18 @@ ncclResult_t fl_reg_mr_dmabuf(void* comm, void* data, size_t size, int type, uin
 ncclResult_t fl_dereg_mr(void* comm, void* mhandle) {
   (void)comm;
   MemHandle* m = reinterpret_cast<MemHandle*>(mhandle);
-  if (m && m->region) fl_vmm_destroy(m->region);
+  if (m && m->region) {
+    std::lock_guard<std::mutex> l(g_mu);
+    auto it = g_adopted.find(m->data);
+    if (it != g_adopted.end() && it->second.region == m->region) {
+      if (--it->second.refs == 0) {
+        fl_vmm_destroy(m->region);
+        g_adopted.erase(it);
+      }
+    } else {
+      fl_vmm_destroy(m->region);
+    }
+  }
   delete m;
   return ncclSuccess;
 }
@@ -392,6 +573,19 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
     FL_WARN("isend: message of %d bytes does not fit the posted receive of %llu bytes", size, (unsigned long long)d.size);
     return ncclInvalidUsage;
   }
+  MemHandle* mh = reinterpret_cast<MemHandle*>(mhandle);
+  // Direct path: the receiver exported the buffer of this descriptor.  Its announcement travels on another
+  // socket than the descriptor, so it may not be here yet: come back later rather than fall back.
+  uint8_t* direct_dst = nullptr;
+  if ((d.flags & kDescDirectOk) && c->nvl_fd >= 0 && size > 0) {
+    const Comm::PeerMr* pm = nullptr;
+    for (int pass = 0; pass < 2 && !pm; ++pass) {
+      for (auto& m : c->peer_mrs) if (m.id == d.mr_id) pm = &m;
+      if (!pm && pass == 0) nvl_ingest(c, mh && mh->type == NCCL_PTR_CUDA ? fl_vmm_pointer_device(data) : 0);
+    }
+    if (!pm && c->nvl_fd >= 0) return ncclSuccess;
+    if (pm && pm->base && d.mr_off + (uint64_t)size <= pm->size) direct_dst = reinterpret_cast<uint8_t*>(pm->base) + d.mr_off;
+  }
   Request* r = get_request(c);
   if (!r) {
     FL_WARN("isend: out of request slots");        // src/plugin.cc:1082-1084
@@ -402,7 +596,28 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
   r->data = reinterpret_cast<uint8_t*>(data);
   r->size = (uint64_t)size;
   r->tag = tag;
-  MemHandle* mh = reinterpret_cast<MemHandle*>(mhandle);
+  if (direct_dst && fl_vmm_memcpy(direct_dst, data, (size_t)size) == 0) {
+    // the payload is in place: one header-only frame on the proposed device tells the receiver
+    const int dev0 = g_cm->bid_tx(c->channel_id, c->own_dev, d.proposed_dev) % c->ndev;
+    Stripe st;
+    st.dev = dev0;
+    st.hdr.magic = kFrameDirectMagic;
+    st.hdr.slot = d.slot;
+    st.hdr.total = (uint64_t)size;
+    st.hdr.offset = 0;
+    st.hdr.len = 0;
+    st.hdr.tx_mask = g_cm->tx_mask(c->own_dev);
+    r->stripes.push_back(st);
+    c->data[dev0].txq.emplace_back(r, 0);
+    r->moved = (uint64_t)size;
+    g_direct_bytes.fetch_add((uint64_t)size, std::memory_order_relaxed);
+    g_direct_msgs.fetch_add(1, std::memory_order_relaxed);
+    c->msg_index++;
+    comm_progress(c, g_cm);
+    *request = r;
+    return ncclSuccess;
+  }
+  if (direct_dst) FL_WARN("isend: direct store failed (%s): message goes through the staged path", fl_vmm_last_error());
   if (mh && mh->type == NCCL_PTR_CUDA && size > 0) {
     // device memory cannot be handed to send(2): bounce it through host memory
     r->stage.resize((size_t)size);
@@ -486,6 +701,40 @@ ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags
   d.proposed_dev = c->cur_dev;
   d.size = r->size;
   d.seq = c->post_seq++;
+  if (mh && mh->mr_id && mh->region && c->nvl_fd >= 0 && sizes[0] > 0) {
+    bool known = false;
+    for (uint32_t id : c->exported) if (id == mh->mr_id) known = true;
+    if (!known) {
+      // first use of this region on this connection: send its descriptors ahead of the receive that names it
+      NvlExportMsg msg;
+      memset(&msg, 0, sizeof msg);
+      msg.magic = kNvlMagic;
+      msg.mr_id = mh->mr_id;
+      msg.nslabs = fl_vmm_num_slabs(mh->region);
+      msg.size = fl_vmm_size(mh->region);
+      msg.slab_bytes = fl_vmm_slab_bytes(mh->region);
+      int fds[16];
+      int nf = 0;
+      bool ok = msg.nslabs >= 1 && msg.nslabs <= 16;
+      for (int i = 0; ok && i < msg.nslabs; ++i) {
+        if (fl_vmm_export_fd(mh->region, i, &fds[nf]) == 0) ++nf;
+        else ok = false;
+      }
+      if (ok && nvl_send_fds(c->nvl_fd, msg, fds, nf) == 0) {
+        c->exported.push_back(mh->mr_id);
+        known = true;
+      } else {
+        FL_INFO("direct path: region %u cannot be exported (%s): staged path", mh->mr_id, fl_vmm_last_error());
+        mh->mr_id = 0;                               // do not try again for every message
+      }
+      for (int i = 0; i < nf; ++i) close(fds[i]);
+    }
+    if (known) {
+      d.mr_id = mh->mr_id;
+      d.flags |= kDescDirectOk;
+      d.mr_off = (uint64_t)(reinterpret_cast<uint8_t*>(data[0]) - reinterpret_cast<uint8_t*>(fl_vmm_ptr(mh->region)));
+    }
+  }
   {
     ScopedTimer tp(&c->timers, T_POST_DESC, params().timers != 0);
     const uint8_t* p = reinterpret_cast<const uint8_t*>(&d);
@@ -515,7 +764,7 @@ ncclResult_t fl_test(void* request, int* done, int* sizes) {
     comm_progress(c, g_cm);
   }
   if (r->done) {
-    if (r->user && r->total != UINT64_MAX && r->total > 0) {
+    if (r->user && !r->direct && r->total != UINT64_MAX && r->total > 0) {
       if (fl_vmm_memcpy(r->user, r->stage.data(), (size_t)r->total) != 0) {
         FL_WARN("test: host -> device staging copy failed: %s", fl_vmm_last_error());
         return ncclUnhandledCudaError;
@@ -559,6 +808,8 @@ ncclResult_t fl_close_listen(void* listen_comm) {
   if (!lc) return ncclSuccess;
   for (auto& ps : lc->pending) close(ps.fd);
   for (auto& p : lc->partials) comm_close(p.comm);
+  for (auto& np : lc->nvl_pending) close(np.fd);
+  if (lc->uds_fd >= 0) close(lc->uds_fd);
   if (lc->fd >= 0) close(lc->fd);
   delete lc;
   return ncclSuccess;
@@ -584,6 +835,9 @@ __attribute__((visibility("default"))) ncclNet_v6_t ncclNetPlugin_v6 = {
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_decisions(void) { return g_cm ? g_cm->decisions() : 0; }
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_fallbacks(void) { return g_cm ? g_cm->fallbacks() : 0; }
 __attribute__((visibility("default"))) void* fuselink_plugin_monitor(void) { return g_cm ? g_cm->monitor() : nullptr; }
+// Payload bytes / messages this process stored straight into a same-host peer's exported receive buffer.
+__attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_bytes(void) { return g_direct_bytes.load(); }
+__attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_msgs(void) { return g_direct_msgs.load(); }
 // Device carrying the stripes of a send request (stripe index s); -1 when out of range.
 __attribute__((visibility("default"))) int fuselink_request_stripe_dev(void* request, int s) {
   Request* r = reinterpret_cast<Request*>(request);

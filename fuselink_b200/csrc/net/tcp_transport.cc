@@ -12,11 +12,13 @@
 #include <unistd.h>
 
 #include "params.h"
+#include "../mem/vmm.h"
 
 namespace flnet {
 
 constexpr uint32_t kDescMagic = 0x464c4453u;   // "FLDS"
 constexpr uint32_t kFrameMagic = 0x464c4652u;  // "FLFR"
+constexpr uint32_t kFrameDirectMagic = 0x464c4452u;  // "FLDR": no payload follows, the bytes were written into the exported buffer
 
 int set_nonblock_nodelay(int fd) {
   int fl = fcntl(fd, F_GETFL, 0);
@@ -212,7 +214,10 @@ static void receiver_pull(Comm* c, ConnManager* cm) {
         s.rx_hdr_got += (size_t)r;
         if (s.rx_hdr_got < sizeof(FrameHdr)) break;
         s.rx_hdr_got = 0;
-        if (s.rx_hdr.magic != kFrameMagic || s.rx_hdr.slot >= (uint32_t)kMaxRequests) { fail(c, ncclInternalError, "bad frame header"); return; }
+        if ((s.rx_hdr.magic != kFrameMagic && s.rx_hdr.magic != kFrameDirectMagic) || s.rx_hdr.slot >= (uint32_t)kMaxRequests) {
+          fail(c, ncclInternalError, "bad frame header");
+          return;
+        }
         Request& rq = c->reqs[s.rx_hdr.slot];
         if (!rq.used || rq.is_send) { fail(c, ncclInternalError, "frame for a slot that is not posted"); return; }
         if (s.rx_hdr.total > rq.size || s.rx_hdr.offset + s.rx_hdr.len > s.rx_hdr.total) {
@@ -221,6 +226,14 @@ static void receiver_pull(Comm* c, ConnManager* cm) {
         }
         rq.total = s.rx_hdr.total;
         c->peer_tx_mask = s.rx_hdr.tx_mask;
+        if (s.rx_hdr.magic == kFrameDirectMagic) {      // the sender already stored the payload through its mapping
+          rq.direct = true;
+          rq.moved = rq.total;
+          rq.done = true;
+          rq.last_progress_ns = now_ns();
+          cm->done_rx(d, rq.total);
+          continue;
+        }
         s.rx_in_payload = true;
         s.rx_payload_got = 0;
         if (s.rx_hdr.len == 0) s.rx_in_payload = false;
@@ -262,6 +275,9 @@ void comm_close(Comm* c) {
     if (c->data[d].fd >= 0) close(c->data[d].fd);
   for (int fd : c->pending_fds)
     if (fd >= 0) close(fd);
+  if (c->nvl_fd >= 0) close(c->nvl_fd);
+  for (auto& m : c->peer_mrs)
+    if (m.region) fl_vmm_destroy(reinterpret_cast<FlVmmRegion*>(m.region));
   delete c;
 }
 

@@ -32,6 +32,7 @@ struct Handle {                          // what listen() publishes; <= NCCL_NET
   int32_t ndev;
   int32_t listen_dev;
   int32_t pad;
+  uint64_t nvl_token;                    // non-zero: the listener also accepts a same-host side channel for cuMem handles
   void* connect_state;                   // in-progress SendComm between re-entrant connect() calls
 };
 static_assert(sizeof(Handle) <= NCCL_NET_HANDLE_MAXSIZE, "handle too large");
@@ -52,7 +53,20 @@ struct RecvDesc {                        // receiver -> sender, control socket
   int32_t proposed_dev;                  // the reference's fuselink_offset
   uint64_t size;                         // posted receive size (upper bound)
   uint64_t seq;                          // order of posting
+  uint32_t mr_id;                        // direct path: id of the exported receive region (0 = none)
+  uint32_t flags;                        // bit 0: the receive buffer was exported, the sender may write it directly
+  uint64_t mr_off;                       // byte offset of the receive buffer inside that region
 };
+constexpr uint32_t kDescDirectOk = 1u;
+
+struct NvlExportMsg {                    // receiver -> sender on the Unix side channel, with the slab fds as SCM_RIGHTS
+  uint64_t magic;
+  uint32_t mr_id;
+  int32_t nslabs;
+  uint64_t size;
+  uint64_t slab_bytes;
+};
+constexpr uint64_t kNvlMagic = 0x464c4e564c313030ull;   // "FLNVL100"
 
 struct FrameHdr {                        // sender -> receiver, in front of every stripe on a data socket
   uint32_t magic;
@@ -87,6 +101,7 @@ struct Request {
   std::vector<Stripe> stripes;           // send only
   std::vector<uint8_t> stage;            // host bounce buffer when the user buffer is device memory
   uint8_t* user = nullptr;               // device address the staged bytes belong to (null: no staging)
+  bool direct = false;                   // recv: the sender wrote the bytes straight into the exported buffer
   size_t stripes_done = 0;
 };
 
@@ -130,6 +145,11 @@ struct Comm {
   std::vector<int> pending_fds;
   std::vector<size_t> hello_sent;
   Timers timers;
+  // same-host direct path (cuMem export/import)
+  int nvl_fd = -1;                       // Unix side channel, -1 when the peer is on another host or the path is off
+  std::vector<uint32_t> exported;        // receiver: region ids already sent to this peer
+  struct PeerMr { uint32_t id; void* base; uint64_t size; void* region; };
+  std::vector<PeerMr> peer_mrs;          // sender: the peer's regions as mapped here
 };
 
 struct PendingSock {
@@ -145,6 +165,10 @@ struct ListenComm {
   std::vector<PendingSock> pending;      // accepted, hello not complete yet
   struct Partial { uint64_t uid; Comm* comm; int have; };
   std::vector<Partial> partials;         // sockets grouped by connection uid
+  int uds_fd = -1;                       // listener of the same-host side channel
+  uint64_t nvl_token = 0;
+  struct NvlPending { int fd; uint64_t uid; };
+  std::vector<NvlPending> nvl_pending;   // side channels accepted, not yet matched to a connection
 };
 
 // helpers shared with plugin.cc

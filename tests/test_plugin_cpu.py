@@ -24,13 +24,13 @@ def _built():
     assert os.path.exists(PLUGIN) and os.path.exists(HARNESS)
 
 
-def _pair(sizes, extra_send=(), extra_recv=(), env=None, common=(), timeout=120):
+def _pair(sizes, extra_send=(), extra_recv=(), env=None, common=(), timeout=120, env_send=None):
     with tempfile.TemporaryDirectory() as d:
         hf = os.path.join(d, "handle")
         e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", **(env or {}))
         sz = [str(s) for s in sizes]
         rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, *common, *extra_recv, *sz], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
-        tx = subprocess.Popen([HARNESS, PLUGIN, "send", hf, *common, *extra_send, *sz], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        tx = subprocess.Popen([HARNESS, PLUGIN, "send", hf, *common, *extra_send, *sz], env=dict(e, **(env_send or {})), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         try:
             txo, txe = tx.communicate(timeout=timeout)
             rxo, rxe = rx.communicate(timeout=timeout)
@@ -126,12 +126,47 @@ def test_stalled_peer_times_out():
 def test_device_buffers_are_adopted_rehomed_and_staged():
     """regMr on a "GPU" buffer (cuMem layer on its memfd stand-in): the buffer is adopted, re-homed onto the relay GPU
     (owner + channel) % nGPUs with its contents kept, and the bytes still arrive intact through the staging path."""
-    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "8", "FL_HARNESS_VERBOSE": "1"}
+    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "8", "FL_HARNESS_VERBOSE": "1",
+           "FUSELINK_NVL": "0"}
     tx, rx = _pair([3 << 20, 70000], env=env, common=["--device-buffers", "--dev", "2", "--chunk", "524288"],
                    extra_recv=["--channel", "3"], extra_send=[])
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     assert "REGISTERED device-buffer owner 2 now-backed-by 5" in rx[1] + tx[1]     # (2 + 3) % 8
     assert "re-homed GPU 2 -> GPU 5" in rx[2] + tx[2]
+    assert "DIRECT bytes 0 msgs 0" in tx[1]
+
+
+def test_same_host_direct_path_writes_the_exported_receive_buffer():
+    """With the side channel on (the default once device buffers are enabled) the receiver exports the cuMem
+    allocation behind its registered buffer over a Unix socket, the sender maps it and stores every chunk straight
+    into it: all payload bytes are counted as direct, none cross the TCP data sockets, and the receiver (which
+    compares against the generator) still sees the right bytes -- in a buffer that was re-homed to the relay GPU."""
+    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "8", "FL_HARNESS_VERBOSE": "1"}
+    sizes = [3 << 20, 70000, 0, 5]
+    tx, rx = _pair(sizes, env=env, common=["--device-buffers", "--dev", "2", "--chunk", "524288"],
+                   extra_recv=["--channel", "3"], extra_send=[])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    total = sum(sizes)
+    nmsgs = 6 + 1 + 0 + 1                                         # chunks with a payload; the empty message has nothing to store
+    assert f"DIRECT bytes {total} msgs {nmsgs} of {total} bytes" in tx[1], tx[1]
+    assert "re-homed GPU 2 -> GPU 5" in rx[2] + tx[2]
+    assert "mapped at" in tx[2]
+
+
+def test_direct_path_is_negotiated_per_connection():
+    """A sender that does not open the side channel (as one on another host cannot) gets the staged path from a
+    receiver that offers it."""
+    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "2"}
+    tx, rx = _pair([1 << 20, 17], env=env, env_send={"FUSELINK_NVL": "0"}, common=["--device-buffers", "--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "DIRECT bytes 0 msgs 0" in tx[1]
+
+
+def test_direct_path_over_several_channels():
+    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "4", "FUSELINK_TCP_NDEV": "4"}
+    tx, rx = _pair([(8 << 20) + 12], env=env, common=["--device-buffers", "--channels", "4", "--chunk", "1048576", "--inflight", "4"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert f"DIRECT bytes {(8 << 20) + 12} " in tx[1], tx[1]
 
 
 def test_device_buffers_refused_unless_enabled():
