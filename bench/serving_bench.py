@@ -41,7 +41,7 @@ def main():
     cfg = MODEL_ZOO[args.model]
     if args.emulate or world == 1:
         p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, 1)
-        net = LlamaShard(cfg, device=dev)
+        net = LlamaShard(cfg, device=dev, max_positions=args.input_len + args.decode_steps)
         pool_bytes = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
         heaps = SymmetricHeap.emulated(2, pool_bytes + (64 << 20), device=local)
         links = [KVLink(h, p, net.kvh_local) for h in heaps]
@@ -65,7 +65,7 @@ def main():
     tp_group = groups[0] if is_prefill else groups[1]
     tp_rank = rank % tp
     p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, tp)
-    net = LlamaShard(cfg, tp_rank, tp, tp_group if tp > 1 else None, device=dev)
+    net = LlamaShard(cfg, tp_rank, tp, tp_group if tp > 1 else None, device=dev, max_positions=args.input_len + args.decode_steps)
     pool_elems = p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim
     heap = SymmetricHeap.create(2 * pool_elems * 2 + (64 << 20), device=local)
     link = KVLink(heap, p, net.kvh_local)

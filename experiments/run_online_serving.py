@@ -41,7 +41,7 @@ def main():
             prompt = rng.randint(32, args.input_len)
             lines.append(f"ts: {t:.4f} prompt: {prompt} shared: {rng.randint(0, prompt // 4)} out: {rng.randint(4, 64)}")
         reqs = parse_trace(lines)
-    net = LlamaShard(cfg, device="cuda")
+    net = LlamaShard(cfg, device="cuda", max_positions=args.input_len + args.decode_steps)
     pool = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
     heaps = SymmetricHeap.emulated(2, 2 * pool + (64 << 20))
     links = [[KVLink(h, p, net.kvh_local, name=f"kv{i}") for i in range(2)] for h in heaps]
