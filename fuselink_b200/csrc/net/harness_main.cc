@@ -97,6 +97,7 @@ int main(int argc, char** argv) {
   int inflight = 8, dev = 0, die_after = -1, channel = 0, nch = 1;
   uint64_t seed = 0;
   bool expect_error = false, device_bufs = false;
+  const char* inject_event = nullptr;
   Api api;
   std::vector<size_t> sizes;
   for (int i = 4; i < argc; ++i) {
@@ -111,6 +112,7 @@ int main(int argc, char** argv) {
     else if (a == "--channel") channel = (int)val();      // receiver: burn this many channel ids first
     else if (a == "--die-after-chunks") die_after = (int)val();
     else if (a == "--expect-error") expect_error = true;
+    else if (a == "--inject-event") inject_event = argv[++i];   // raise an asynchronous device event after init (software NIC)
     else if (a == "--device-buffers") device_bufs = true;   // buffers come from the plugin's cuMem layer and are registered as CUDA
     else sizes.push_back(strtoull(a.c_str(), nullptr, 0));
   }
@@ -122,6 +124,11 @@ int main(int argc, char** argv) {
   if (!api.v6 || !api.v7 || !api.v8) { fprintf(stderr, "plugin symbols missing\n"); return 2; }
   if (strcmp(api.v7->name, "FuseLink")) { fprintf(stderr, "unexpected plugin name %s\n", api.v7->name); return 2; }
   if (api.init() != ncclSuccess) { fprintf(stderr, "init failed\n"); return 2; }
+  if (inject_event) {
+    auto inject = (void (*)(int, const char*))dlsym(lib, "fuselink_soft_inject_event");
+    if (inject) inject(0, inject_event);
+    usleep(200 * 1000);                                       // the device's watcher thread logs it
+  }
   int ndev = 0;
   api.devices(&ndev);
   if (dev >= ndev) { fprintf(stderr, "device %d of %d\n", dev, ndev); return 2; }
@@ -252,6 +259,12 @@ int main(int argc, char** argv) {
   auto fallbacks = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_fallbacks");
   auto direct_b = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_direct_bytes");
   auto direct_m = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_direct_msgs");
+  auto rdma_ctr = (void (*)(unsigned long long*, unsigned long long*, unsigned long long*))dlsym(lib, "fuselink_rdma_counters");
+  if (rdma_ctr && is_send) {
+    unsigned long long m = 0, pc = 0, w = 0;
+    rdma_ctr(&m, &pc, &w);
+    if (m) printf("RDMA messages %llu pieces %llu work-requests %llu\n", m, pc, w);
+  }
   if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes);
   if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);
   for (int c = 0; c < nch; ++c) {

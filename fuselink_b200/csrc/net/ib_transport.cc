@@ -1,6 +1,5 @@
 #include "ib_transport.h"
 
-#include <dlfcn.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -8,22 +7,6 @@
 #include "params.h"
 
 namespace flnet {
-namespace {
-std::vector<IbDevice> g_devs;
-
-// The two verbs structures whose leading fields are read here.  Layout prefix of rdma-core's public
-// `struct ibv_device` (ops table of two pointers, two enums, then the fixed-size name arrays).
-struct ibv_device_prefix {
-  void* ops[2];
-  int node_type;
-  int transport_type;
-  char name[64];
-  char dev_name[64];
-  char dev_path[256];
-  char ibdev_path[256];
-};
-}  // namespace
-
 HcaFilter parse_hca_filter(const std::string& spec_in) {
   HcaFilter f;
   std::string spec = spec_in;
@@ -64,41 +47,6 @@ bool hca_allowed(const HcaFilter& f, const std::string& name, int port) {
     if (name_ok && (e.second < 0 || e.second == port)) match = true;
   }
   return f.exclude ? !match : match;
-}
-
-const std::vector<IbDevice>& ib_devices() { return g_devs; }
-
-int ib_discover() {
-  g_devs.clear();
-  void* lib = dlopen("libibverbs.so.1", RTLD_NOW);
-  if (!lib) lib = dlopen("libibverbs.so", RTLD_NOW);
-  if (!lib) {
-    FL_INFO("libibverbs not found: verbs path disabled");
-    return 0;
-  }
-  using get_list_t = void** (*)(int*);
-  using free_list_t = void (*)(void**);
-  auto get_list = reinterpret_cast<get_list_t>(dlsym(lib, "ibv_get_device_list"));
-  auto free_list = reinterpret_cast<free_list_t>(dlsym(lib, "ibv_free_device_list"));
-  if (!get_list || !free_list) return 0;
-  int n = 0;
-  void** list = get_list(&n);
-  if (!list) return 0;
-  const HcaFilter f = parse_hca_filter(params().ib_hca);
-  for (int i = 0; i < n; ++i) {
-    const ibv_device_prefix* d = reinterpret_cast<const ibv_device_prefix*>(list[i]);
-    std::string name(d->name, strnlen(d->name, sizeof d->name));
-    if (!hca_allowed(f, name, 1)) continue;
-    IbDevice dev;
-    dev.name = name;
-    dev.port = 1;
-    dev.guid = 0;
-    dev.pci_path = std::string(d->ibdev_path, strnlen(d->ibdev_path, sizeof d->ibdev_path));
-    g_devs.push_back(dev);
-  }
-  free_list(list);
-  FL_INFO("verbs: %d device(s) after NCCL_IB_HCA filter", (int)g_devs.size());
-  return (int)g_devs.size();
 }
 
 }  // namespace flnet

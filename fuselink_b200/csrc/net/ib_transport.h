@@ -1,9 +1,8 @@
-// Optional verbs (RDMA) side of the plugin.  libibverbs is opened at run time (the reference does the same
-// through NCCL's ibvsymbols, src/extern/ibvwrap.h:30-90, src/plugin.cc:177) so the plugin loads on machines
-// without RDMA.  What is here: device discovery with the NCCL_IB_HCA filter syntax of the reference
-// (src/plugin.cc:194-230: leading '^' excludes, leading '=' matches exactly, "name:port" selects a port)
-// and the per-device record the connection manager needs.  A queue-pair data path needs RDMA hardware to
-// be exercised; on a box without NICs discovery returns 0 devices and the TCP transport carries the data.
+// NCCL_IB_HCA filter of the verbs path, with the syntax of the reference (src/plugin.cc:194-230): a comma list of
+// device-name prefixes, a leading '^' excludes, a leading '=' matches exactly, "name:port" selects one port, and bare
+// numbers continue the previous prefix ("=mlx5_0,3,4" names mlx5_0, mlx5_3 and mlx5_4, as the reference's bandwidth
+// script writes it).  Device discovery itself and the queue-pair data path are in verbs_provider.cc and
+// rdma_transport.cc; the filter is separate so that it can be tested without a NIC.
 #pragma once
 #include <stdint.h>
 #include <string>
@@ -11,18 +10,6 @@
 
 namespace flnet {
 
-struct IbDevice {
-  std::string name;
-  int port;
-  uint64_t guid;
-  std::string pci_path;
-};
-
-// Number of usable verbs devices (0 when libibverbs or devices are missing).
-int ib_discover();
-const std::vector<IbDevice>& ib_devices();
-
-// Filter evaluation, separated from discovery so it can be tested anywhere.
 struct HcaFilter {
   bool exclude = false, exact = false;
   std::vector<std::pair<std::string, int>> entries;   // (name prefix, port or -1)

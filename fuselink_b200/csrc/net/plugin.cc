@@ -30,6 +30,7 @@
 #include "logging.h"
 #include "nccl_net_abi.h"
 #include "params.h"
+#include "rdma_transport.h"
 #include "tcp_transport.h"
 #include "../mem/vmm.h"
 
@@ -46,9 +47,13 @@ std::mutex g_mu;
 ConnManager* g_cm = nullptr;
 int g_ndev = 0;
 int g_ngpus = 0;          // devices the cuMem layer sees; 0 = CUDA registrations unavailable
+bool g_rdma = false;      // the RDMA transport carries the data (FUSELINK_TRANSPORT=rdma, or auto with verbs devices present)
 std::atomic<int> g_channel_counter{0};
 char g_names[kMaxDev][32];
-char g_pci[kMaxDev][64];
+char g_pci[kMaxDev][256];
+int g_speed[kMaxDev];
+uint64_t g_guid[kMaxDev];
+int g_max_comms[kMaxDev];
 
 struct MemHandle {
   void* data;
@@ -56,6 +61,7 @@ struct MemHandle {
   int type;
   FlVmmRegion* region;   // CUDA registrations made through the cuMem layer, else null
   uint32_t mr_id;        // non-zero for a region that can be exported to a same-host sender
+  RdmaMrSet* rdma;       // RDMA transport: the registration on every device
 };
 std::atomic<uint32_t> g_mr_counter{1};
 struct Adopted { FlVmmRegion* region; uint32_t mr_id; int refs; };
@@ -165,12 +171,31 @@ ncclResult_t fl_init(ncclDebugLogger_t logger) {
   if (g_cm) return ncclSuccess;
   params_reload();
   const Params& p = params();
+  // Transport: "tcp", "rdma", or "auto" = RDMA when the provider finds devices (verbs NICs), else TCP.
+  const std::string want = param_str("FUSELINK_TRANSPORT", "auto");
   int n_ib = 0;
-  if (!p.ib_disable) n_ib = ib_discover();   // 0 on a machine without verbs devices
-  g_ndev = (int)p.tcp_ndev;
-  for (int d = 0; d < g_ndev; ++d) {
-    snprintf(g_names[d], sizeof g_names[d], "fuselink-tcp%d", d);
-    snprintf(g_pci[d], sizeof g_pci[d], "/sys/devices/virtual/net/fuselink%d", d);
+  if (want != "tcp" && !(p.ib_disable && param_str("FUSELINK_RDMA_PROVIDER", "verbs") == "verbs")) n_ib = rdma_init(nullptr);
+  g_rdma = n_ib > 0;
+  if (want == "rdma" && !g_rdma) FL_WARN("FUSELINK_TRANSPORT=rdma but no RDMA device was found: using TCP");
+  if (g_rdma) {
+    g_ndev = n_ib;
+    for (int d = 0; d < g_ndev; ++d) {
+      const rdma::DeviceInfo di = rdma_device(d);
+      snprintf(g_names[d], sizeof g_names[d], "%s", di.name.c_str());
+      snprintf(g_pci[d], sizeof g_pci[d], "%s", di.pci_path.c_str());
+      g_speed[d] = di.speed_mbps;
+      g_guid[d] = di.guid;
+      g_max_comms[d] = di.max_qp;
+    }
+  } else {
+    g_ndev = (int)p.tcp_ndev;
+    for (int d = 0; d < g_ndev; ++d) {
+      snprintf(g_names[d], sizeof g_names[d], "fuselink-tcp%d", d);
+      snprintf(g_pci[d], sizeof g_pci[d], "/sys/devices/virtual/net/fuselink%d", d);
+      g_speed[d] = 100000;
+      g_guid[d] = 0x464c0000ull + (uint64_t)d;
+      g_max_comms[d] = 65536;
+    }
   }
   int prio = (int)p.priority_dev;
   if (prio < 0 || prio >= g_ndev) prio = 0;
@@ -179,7 +204,7 @@ ncclResult_t fl_init(ncclDebugLogger_t logger) {
     if (fl_vmm_init(p.vmm_fake ? 1 : 0) == 0) g_ngpus = fl_vmm_device_count();
     else FL_WARN("CUDA registrations requested but the cuMem layer is unavailable: %s", fl_vmm_last_error());
   }
-  FL_INFO("FuseLink plugin: %d virtual NIC(s) over TCP, %d verbs device(s) found, degree %ld step %ld, monitor %s", g_ndev, n_ib,
+  FL_INFO("FuseLink plugin: %d device(s) over %s, degree %ld step %ld, monitor %s", g_ndev, g_rdma ? "RDMA" : "TCP (virtual NICs)",
           (long)p.degree, (long)p.step, g_cm->monitor() ? "on" : "off");
   return ncclSuccess;
 }
@@ -193,13 +218,13 @@ template <class P>
 void fill_props_common(int dev, P* props) {
   props->name = g_names[dev];
   props->pciPath = g_pci[dev];
-  props->guid = 0x464c0000ull + (uint64_t)dev;
+  props->guid = g_guid[dev];
   // the TCP transport reads/writes host memory; GPU buffers are accepted (and staged by the plugin) only on request
   props->ptrSupport = NCCL_PTR_HOST | (g_ngpus > 0 ? NCCL_PTR_CUDA : 0);
-  props->speed = 100000;                  // Mbps, nominal
+  props->speed = g_speed[dev];            // Mbps
   props->port = 0;
   props->latency = 0;
-  props->maxComms = 65536;
+  props->maxComms = g_max_comms[dev];
   props->maxRecvs = 1;                    // grouped receives are not supported (as in the reference)
 }
 ncclResult_t fl_props_v6(int dev, ncclNetProperties_v6_t* props) {
@@ -227,6 +252,12 @@ ncclResult_t fl_props_v8(int dev, ncclNetProperties_v8_t* props) {
 ncclResult_t fl_listen(int dev, void* opaque, void** listen_comm) {
   if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
   Handle* h = reinterpret_cast<Handle*>(opaque);
+  if (g_rdma) {
+    RdmaListenComm* rl = nullptr;
+    ncclResult_t rc = rdma_listen(dev, g_channel_counter.fetch_add(1), h, &rl);
+    *listen_comm = rl;
+    return rc;
+  }
   memset(h, 0, NCCL_NET_HANDLE_MAXSIZE);
   sockaddr_in6 addr;
   pick_listen_addr(&addr);
@@ -281,6 +312,12 @@ ncclResult_t fl_connect_impl(int dev, void* opaque, void** send_comm) {
   Handle* h = reinterpret_cast<Handle*>(opaque);
   if (h->magic != kHandleMagic) return ncclInvalidArgument;
   if (dev < 0 || dev >= g_ndev) return ncclInvalidArgument;
+  if (g_rdma) {
+    RdmaComm* rc = nullptr;
+    ncclResult_t e = rdma_connect(dev, h, &rc);
+    *send_comm = rc;
+    return e;
+  }
   Comm* c = reinterpret_cast<Comm*>(h->connect_state);
   if (!c) {
     c = new Comm();
@@ -359,6 +396,12 @@ ncclResult_t fl_connect_impl(int dev, void* opaque, void** send_comm) {
 
 ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
   *recv_comm = nullptr;
+  if (g_rdma) {
+    RdmaComm* rc = nullptr;
+    ncclResult_t e = rdma_accept(reinterpret_cast<RdmaListenComm*>(listen_comm), &rc);
+    *recv_comm = rc;
+    return e;
+  }
   ListenComm* lc = reinterpret_cast<ListenComm*>(listen_comm);
   for (;;) {
     int fd = accept(lc->fd, nullptr, nullptr);
@@ -464,11 +507,34 @@ ncclResult_t fl_accept_v7(void* listen_comm, void** recv_comm, ncclNetDeviceHand
 // (a VMM allocation, NCCL_CUMEM_ENABLE=1): the region handle is kept so the buffer can be re-homed onto a
 // relay GPU, which is what the reference's regMr does (src/plugin.cc:1168-1330).  The TCP data path itself
 // only touches host memory, so a CUDA registration is refused unless the device transport is active.
-ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
-  if (type == NCCL_PTR_HOST) {
-    *mhandle = new MemHandle{data, size, type, nullptr, 0};
-    return ncclSuccess;
+void fl_dereg_region(MemHandle* m) {
+  std::lock_guard<std::mutex> l(g_mu);
+  auto it = g_adopted.find(m->data);
+  if (it != g_adopted.end() && it->second.region == m->region) {
+    if (--it->second.refs == 0) {
+      fl_vmm_destroy(m->region);
+      g_adopted.erase(it);
+    }
+  } else {
+    fl_vmm_destroy(m->region);
   }
+  m->region = nullptr;
+}
+
+ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
+  auto finish = [&](MemHandle* m) -> ncclResult_t {
+    if (g_rdma) {
+      m->rdma = rdma_reg(data, size);
+      if (!m->rdma) {
+        if (m->region) fl_dereg_region(m);
+        delete m;
+        return ncclSystemError;
+      }
+    }
+    *mhandle = m;
+    return ncclSuccess;
+  };
+  if (type == NCCL_PTR_HOST) return finish(new MemHandle{data, size, type, nullptr, 0, nullptr});
   if (type != NCCL_PTR_CUDA || g_ngpus <= 0) {
     FL_WARN("regMr: pointer type %d is not supported (set FUSELINK_CUDA_PTRS=1 for device buffers)", type);
     return ncclInvalidUsage;
@@ -477,8 +543,8 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
   // relay = (owner + channelId) % nGPUs (src/plugin.cc:1201), keeping the address and the contents and leaving the
   // owner GPU with read/write access (src/fuselink.cc:43-56).  A buffer that is not a cuMem allocation (or that is
   // registered again) is used where it is.
-  Comm* c = reinterpret_cast<Comm*>(comm);
-  MemHandle* m = new MemHandle{data, size, type, nullptr, 0};
+  const int channel = !comm ? 0 : g_rdma ? reinterpret_cast<RdmaComm*>(comm)->channel_id : reinterpret_cast<Comm*>(comm)->channel_id;
+  MemHandle* m = new MemHandle{data, size, type, nullptr, 0, nullptr};
   if (params().remap || params().nvl) {
     std::lock_guard<std::mutex> l(g_mu);
     auto it = g_adopted.find(data);
@@ -493,7 +559,7 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
       if (dev < 0) dev = 0;
       FlVmmRegion* r = fl_vmm_adopt(data, size, dev);
       if (r) {
-        const int relay = (dev + (c ? c->channel_id : 0)) % g_ngpus;
+        const int relay = (dev + channel) % g_ngpus;
         long usec = 0;
         const int access[2] = {dev, relay};
         if (params().remap && relay != dev && fl_vmm_remap_slab(r, 0, relay, 1, access, 2, &usec) == 0)
@@ -506,8 +572,7 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
       }
     }
   }
-  *mhandle = m;
-  return ncclSuccess;
+  return finish(m);
 }
 ncclResult_t fl_reg_mr(void* comm, void* data, int size, int type, void** mhandle) {
   return fl_reg_mr_sz(comm, data, (size_t)size, type, mhandle);
@@ -519,18 +584,8 @@ ncclResult_t fl_reg_mr_dmabuf(void* comm, void* data, size_t size, int type, uin
 ncclResult_t fl_dereg_mr(void* comm, void* mhandle) {
   (void)comm;
   MemHandle* m = reinterpret_cast<MemHandle*>(mhandle);
-  if (m && m->region) {
-    std::lock_guard<std::mutex> l(g_mu);
-    auto it = g_adopted.find(m->data);
-    if (it != g_adopted.end() && it->second.region == m->region) {
-      if (--it->second.refs == 0) {
-        fl_vmm_destroy(m->region);
-        g_adopted.erase(it);
-      }
-    } else {
-      fl_vmm_destroy(m->region);
-    }
-  }
+  if (m && m->rdma) rdma_dereg(m->rdma);
+  if (m && m->region) fl_dereg_region(m);
   delete m;
   return ncclSuccess;
 }
@@ -556,6 +611,13 @@ Request* get_request(Comm* c) {
 }
 
 ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhandle, void** request) {
+  if (g_rdma) {
+    RdmaRequest* rr = nullptr;
+    MemHandle* m = reinterpret_cast<MemHandle*>(mhandle);
+    ncclResult_t e = rdma_isend(reinterpret_cast<RdmaComm*>(send_comm), g_cm, data, size, tag, m ? m->rdma : nullptr, &rr);
+    *request = rr;
+    return e;
+  }
   Comm* c = reinterpret_cast<Comm*>(send_comm);
   *request = nullptr;
   ScopedTimer tm(&c->timers, T_ISEND, params().timers != 0);
@@ -662,6 +724,18 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
 }
 
 ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags, void** mhandles, void** request) {
+  if (g_rdma) {
+    *request = nullptr;
+    if (n != 1) {
+      FL_WARN("irecv: grouped receives (n=%d) are not supported", n);
+      return ncclInternalError;
+    }
+    RdmaRequest* rr = nullptr;
+    MemHandle* m = reinterpret_cast<MemHandle*>(mhandles[0]);
+    ncclResult_t e = rdma_irecv(reinterpret_cast<RdmaComm*>(recv_comm), g_cm, data[0], sizes[0], tags[0], m ? m->rdma : nullptr, &rr);
+    *request = rr;
+    return e;
+  }
   Comm* c = reinterpret_cast<Comm*>(recv_comm);
   *request = nullptr;
   ScopedTimer tm(&c->timers, T_IRECV, params().timers != 0);
@@ -756,6 +830,7 @@ ncclResult_t fl_iflush(void* recv_comm, int n, void** data, int* sizes, void** m
 }
 
 ncclResult_t fl_test(void* request, int* done, int* sizes) {
+  if (g_rdma) return rdma_test(reinterpret_cast<RdmaRequest*>(request), g_cm, done, sizes);
   Request* r = reinterpret_cast<Request*>(request);
   Comm* c = r->comm;
   *done = 0;
@@ -793,10 +868,20 @@ ncclResult_t fl_test(void* request, int* done, int* sizes) {
 }
 
 ncclResult_t fl_close_send(void* send_comm) {
+  if (g_rdma) {
+    rdma_close(reinterpret_cast<RdmaComm*>(send_comm));
+    return ncclSuccess;
+  }
   comm_close(reinterpret_cast<Comm*>(send_comm));
   return ncclSuccess;
 }
 ncclResult_t fl_close_recv(void* recv_comm) {
+  if (g_rdma) {
+    RdmaComm* rc = reinterpret_cast<RdmaComm*>(recv_comm);
+    if (rc && g_cm && g_cm->monitor() && rc->cur_dev >= 0 && rc->cur_dev != rc->own_dev) fl_monitor_release(g_cm->monitor(), FL_DIR_RX, rc->cur_dev);
+    rdma_close(rc);
+    return ncclSuccess;
+  }
   Comm* c = reinterpret_cast<Comm*>(recv_comm);
   if (c && g_cm && g_cm->monitor() && c->cur_dev >= 0 && c->cur_dev != c->own_dev)
     fl_monitor_release(g_cm->monitor(), FL_DIR_RX, c->cur_dev);
@@ -804,6 +889,10 @@ ncclResult_t fl_close_recv(void* recv_comm) {
   return ncclSuccess;
 }
 ncclResult_t fl_close_listen(void* listen_comm) {
+  if (g_rdma) {
+    rdma_close_listen(reinterpret_cast<RdmaListenComm*>(listen_comm));
+    return ncclSuccess;
+  }
   ListenComm* lc = reinterpret_cast<ListenComm*>(listen_comm);
   if (!lc) return ncclSuccess;
   for (auto& ps : lc->pending) close(ps.fd);
@@ -840,6 +929,10 @@ __attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_msgs(void) { return g_direct_msgs.load(); }
 // Device carrying the stripes of a send request (stripe index s); -1 when out of range.
 __attribute__((visibility("default"))) int fuselink_request_stripe_dev(void* request, int s) {
+  if (g_rdma) {
+    RdmaRequest* rr = reinterpret_cast<RdmaRequest*>(request);
+    return (!rr || s < 0 || s >= (int)rr->pieces.size()) ? -1 : rr->pieces[s].dev;
+  }
   Request* r = reinterpret_cast<Request*>(request);
   if (!r || s < 0 || s >= (int)r->stripes.size()) return -1;
   return r->stripes[s].dev;

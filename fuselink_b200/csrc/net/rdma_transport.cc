@@ -1,0 +1,651 @@
+// RDMA transport: bootstrap, registration, posting and completion handling (protocol in rdma_transport.h).
+#include "rdma_transport.h"
+
+#include <errno.h>
+#include <poll.h>
+#include <stdlib.h>
+#include <string.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <thread>
+
+#include "logging.h"
+#include "params.h"
+
+namespace flnet {
+namespace {
+
+constexpr uint64_t kHelloMagic = 0x464c4e4b48454c4full;   // same hello as the TCP transport, kind 2
+constexpr uint32_t kInfoMagic = 0x464c5244u;              // "FLRD"
+constexpr uint64_t kWrFifo = 1ull << 62;                   // wr_id of a signalled descriptor write
+constexpr uint64_t kWrRecv = 1ull << 61;                   // wr_id of the anonymous zero-length receives
+
+rdma::Provider* g_prov = nullptr;
+rdma::Pd* g_pd[kMaxDev];
+int g_ndev = 0;
+std::atomic<uint64_t> g_uid{1};
+std::atomic<uint64_t> g_pieces{0}, g_work_requests{0}, g_messages{0};
+
+int access_flags() {
+  int f = rdma::kAccessLocalWrite | rdma::kAccessRemoteWrite | rdma::kAccessRemoteRead;
+  const int64_t ro = params().ib_pci_relaxed_ordering;      // 0 off, 1 on, 2 when the library supports it
+  if (ro == 1 || (ro == 2 && g_ndev > 0 && g_prov->device(0).relaxed_ordering)) f |= rdma::kAccessRelaxedOrdering;
+  return f;
+}
+
+void fail(RdmaComm* c, ncclResult_t why, const char* what) {
+  if (!c->error) {
+    c->error = why;
+    FL_WARN("rdma %s comm (channel %d, dev %d): %s", c->is_send ? "send" : "recv", c->channel_id, c->own_dev, what);
+  }
+}
+
+void* alloc_zeroed(size_t bytes) {
+  void* p = nullptr;
+  if (posix_memalign(&p, 4096, bytes) != 0) return nullptr;
+  memset(p, 0, bytes);
+  return p;
+}
+
+// One completion queue and nqps queue pairs on every device, receives pre-posted on the receiving side.
+bool make_endpoints(RdmaComm* c) {
+  rdma::QpCaps caps;
+  caps.max_send_wr = 4 * kMaxRequests;
+  caps.max_recv_wr = 2 * kMaxRequests;
+  caps.max_inline = params().ib_use_inline ? (int)sizeof(RdmaDesc) : 0;
+  memset(&c->mine, 0, sizeof c->mine);
+  c->mine.magic = kInfoMagic;
+  c->mine.ndev = c->ndev;
+  c->mine.nqps = c->nqps;
+  c->mine.own_dev = c->own_dev;
+  for (int d = 0; d < c->ndev; ++d) {
+    c->dev[d].cq = g_prov->create_cq(d, 8 * kMaxRequests);
+    if (!c->dev[d].cq) return false;
+    for (int q = 0; q < c->nqps; ++q) {
+      c->dev[d].qp[q] = g_prov->create_qp(g_pd[d], c->dev[d].cq, caps);
+      if (!c->dev[d].qp[q]) return false;
+      if (g_prov->query_qp_info(c->dev[d].qp[q], (int)params().ib_gid_index, &c->mine.qp[d][q])) return false;
+    }
+  }
+  return true;
+}
+
+bool connect_endpoints(RdmaComm* c) {
+  rdma::QpConnectParams p;
+  const Params& e = params();
+  p.gid_index = (int)e.ib_gid_index; p.timeout = (int)e.ib_timeout; p.retry_cnt = (int)e.ib_retry_cnt;
+  p.pkey = (int)e.ib_pkey; p.sl = (int)e.ib_sl; p.tc = (int)e.ib_tc;
+  for (int d = 0; d < c->ndev; ++d)
+    for (int q = 0; q < c->nqps; ++q)
+      if (g_prov->connect_qp(c->dev[d].qp[q], c->theirs.qp[d][q], p)) return false;
+  return true;
+}
+
+// returns 1 when all `total` bytes moved, 0 to come back later, -1 on error
+int io_step(int fd, void* buf, size_t total, size_t* done, bool sending) {
+  while (*done < total) {
+    ssize_t r = sending ? send(fd, (uint8_t*)buf + *done, total - *done, MSG_DONTWAIT | MSG_NOSIGNAL)
+                        : recv(fd, (uint8_t*)buf + *done, total - *done, MSG_DONTWAIT);
+    if (r > 0) { *done += (size_t)r; continue; }
+    if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) return 0;
+    return -1;
+  }
+  return 1;
+}
+
+RdmaRequest* get_request(RdmaComm* c) {
+  static thread_local int hint = 0;
+  for (int i = 0; i < kMaxRequests; ++i) {
+    const int s = (hint + i) % kMaxRequests;
+    if (!c->reqs[s].used) {
+      hint = s + 1;
+      RdmaRequest& r = c->reqs[s];
+      r = RdmaRequest();
+      r.used = true;
+      r.comm = c;
+      r.slot = (uint32_t)s;
+      r.last_progress_ns = now_ns();
+      return &r;
+    }
+  }
+  return nullptr;
+}
+
+void poll_all(RdmaComm* c, ConnManager* cm) {
+  g_prov->progress();
+  rdma::Completion wc[16];
+  for (int d = 0; d < c->ndev; ++d) {
+    if (!c->dev[d].cq) continue;
+    for (;;) {
+      const int n = g_prov->poll_cq(c->dev[d].cq, 16, wc);
+      if (n <= 0) break;
+      for (int i = 0; i < n; ++i) {
+        if (wc[i].status != rdma::kWcOk) {
+          if (cm && wc[i].status == rdma::kWcRetryExceeded) cm->set_dead(d, true);
+          char msg[96];
+          snprintf(msg, sizeof msg, "completion with status %d on device %d", wc[i].status, d);
+          fail(c, wc[i].status == rdma::kWcRemoteAccess ? ncclInvalidUsage : ncclRemoteError, msg);
+          continue;
+        }
+        if (wc[i].is_recv) {
+          // keep the pool of zero-length receives full on the queue pair that consumed one
+          for (int q = 0; q < c->nqps; ++q)
+            if (c->dev[d].qp[q] && c->mine.qp[d][q].qpn == wc[i].qpn) g_prov->post_recv(c->dev[d].qp[q], kWrRecv);
+          const uint32_t slot = wc[i].imm & 0xffu;
+          const int npieces = (int)((wc[i].imm >> 8) & 0xffu);
+          RdmaRequest& r = c->reqs[slot];
+          if (!r.used || r.is_send || npieces < 1) { fail(c, ncclInternalError, "immediate for a slot that is not posted"); continue; }
+          r.pieces_total = npieces;
+          r.pieces_done++;
+          r.last_progress_ns = now_ns();
+        } else if (wc[i].wr_id & kWrFifo) {
+          // a signalled descriptor write: nothing to do but to have reaped the send queue
+        } else {
+          const uint32_t slot = (uint32_t)(wc[i].wr_id & 0xffffu);
+          const uint32_t piece = (uint32_t)((wc[i].wr_id >> 16) & 0xffffu);
+          RdmaRequest& r = c->reqs[slot % kMaxRequests];
+          if (!r.used || !r.is_send || piece >= r.pieces.size()) { fail(c, ncclInternalError, "send completion for an unknown piece"); continue; }
+          r.pieces_done++;
+          r.last_progress_ns = now_ns();
+          if (cm) cm->done_tx(r.pieces[piece].dev, r.pieces[piece].len);
+        }
+      }
+    }
+  }
+}
+
+void async_thread(int dev) {
+  // one watcher per device, as the reference starts one per port (src/plugin.cc:100-113): events are logged
+  for (;;) {
+    std::string what;
+    const int rc = g_prov->wait_async_event(dev, 500, &what);
+    if (rc < 0) return;
+    if (rc > 0) FL_WARN("rdma device %d (%s): asynchronous event: %s", dev, g_prov->device(dev).name.c_str(), what.c_str());
+  }
+}
+
+}  // namespace
+
+// -----------------------------------------------------------------------------------------------------
+int rdma_init(ConnManager* cm) {
+  (void)cm;
+  if (g_ndev > 0) return g_ndev;
+  g_prov = rdma::get_provider();
+  if (!g_prov) return 0;
+  int n = g_prov->device_count();
+  if (n > kMaxDev) n = kMaxDev;
+  for (int d = 0; d < n; ++d) {
+    g_pd[d] = g_prov->alloc_pd(d);                         // up front, shared by every connection
+    if (!g_pd[d]) {
+      FL_WARN("rdma: no protection domain on device %d", d);
+      return 0;
+    }
+  }
+  g_ndev = n;
+  for (int d = 0; d < n; ++d) std::thread(async_thread, d).detach();
+  if (n) FL_INFO("rdma transport: %d device(s) through the %s provider", n, g_prov->name());
+  return n;
+}
+
+rdma::DeviceInfo rdma_device(int dev) { return g_prov->device(dev); }
+
+RdmaMrSet* rdma_reg(void* data, size_t size) {
+  RdmaMrSet* m = new RdmaMrSet();
+  memset(m, 0, sizeof *m);
+  m->data = data;
+  m->size = size;
+  const int flags = access_flags();
+  for (int d = 0; d < g_ndev; ++d) {
+    // every device gets its own registration so that any of them can carry a stripe (the reference registers
+    // every per-GPU alias on every NIC, src/plugin.cc:1250-1320)
+    m->mr[d] = g_prov->reg_mr(g_pd[d], data, size ? size : 1, flags);
+    if (!m->mr[d]) {
+      FL_WARN("rdma: registration of %zu bytes at %p failed on device %d", size, data, d);
+      rdma_dereg(m);
+      return nullptr;
+    }
+  }
+  return m;
+}
+
+void rdma_dereg(RdmaMrSet* m) {
+  if (!m) return;
+  for (int d = 0; d < kMaxDev; ++d)
+    if (m->mr[d]) g_prov->dereg_mr(m->mr[d]);
+  delete m;
+}
+
+ncclResult_t rdma_listen(int dev, int channel_id, Handle* h, RdmaListenComm** out) {
+  memset(h, 0, NCCL_NET_HANDLE_MAXSIZE);
+  sockaddr_in6 addr;
+  pick_listen_addr(&addr);
+  addr.sin6_port = 0;
+  int fd = socket(AF_INET6, SOCK_STREAM, 0);
+  if (fd < 0) return ncclSystemError;
+  int zero = 0, one = 1;
+  setsockopt(fd, IPPROTO_IPV6, IPV6_V6ONLY, &zero, sizeof zero);
+  setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
+  if (bind(fd, reinterpret_cast<sockaddr*>(&addr), sizeof addr) != 0 || listen(fd, 256) != 0) {
+    close(fd);
+    return ncclSystemError;
+  }
+  socklen_t len = sizeof addr;
+  getsockname(fd, reinterpret_cast<sockaddr*>(&addr), &len);
+  set_nonblock_nodelay(fd);
+  RdmaListenComm* lc = new RdmaListenComm();
+  lc->fd = fd;
+  lc->dev = dev;
+  lc->channel_id = channel_id;
+  h->magic = kHandleMagic;
+  h->addr = addr;
+  h->channel_id = channel_id;
+  h->ndev = g_ndev;
+  h->listen_dev = dev;
+  *out = lc;
+  return ncclSuccess;
+}
+
+static int clamp_qps() {
+  int64_t n = params().ib_qps_per_conn;
+  if (n < 1) n = 1;
+  if (n > kRdmaMaxQps) n = kRdmaMaxQps;
+  return (int)n;
+}
+
+// Sender: stage 0 TCP connect, 1 hello + own info, 2 peer info + queue pairs to RTS + "ready".
+ncclResult_t rdma_connect(int dev, Handle* h, RdmaComm** out) {
+  *out = nullptr;
+  if (h->magic != kHandleMagic) return ncclInvalidArgument;
+  RdmaComm* c = reinterpret_cast<RdmaComm*>(h->connect_state);
+  auto abandon = [&](ncclResult_t rc, const char* why) {
+    FL_WARN("rdma connect: %s", why);
+    h->connect_state = nullptr;
+    rdma_close(c);
+    return rc;
+  };
+  if (!c) {
+    c = new RdmaComm();
+    c->is_send = true;
+    c->own_dev = dev;
+    c->peer_dev = h->listen_dev;
+    c->ndev = h->ndev < g_ndev ? h->ndev : g_ndev;
+    c->nqps = clamp_qps();
+    c->channel_id = h->channel_id;
+    c->ctrl_fd = socket(AF_INET6, SOCK_STREAM, 0);
+    h->connect_state = c;
+    if (c->ctrl_fd < 0) return abandon(ncclSystemError, "no socket");
+    set_nonblock_nodelay(c->ctrl_fd);
+    if (connect(c->ctrl_fd, reinterpret_cast<sockaddr*>(&h->addr), sizeof h->addr) != 0 && errno != EINPROGRESS)
+      return abandon(ncclSystemError, strerror(errno));
+    c->stage = 0;
+  }
+  if (c->stage == 0) {
+    pollfd pfd{c->ctrl_fd, POLLOUT, 0};
+    if (poll(&pfd, 1, 0) <= 0 || !(pfd.revents & (POLLOUT | POLLERR | POLLHUP))) return ncclSuccess;
+    int err = 0;
+    socklen_t el = sizeof err;
+    getsockopt(c->ctrl_fd, SOL_SOCKET, SO_ERROR, &err, &el);
+    if (err) return abandon(ncclSystemError, strerror(err));
+    Hello hello;
+    memset(&hello, 0, sizeof hello);
+    hello.magic = kHelloMagic;
+    hello.comm_uid = g_uid.fetch_add(1);
+    hello.kind = 2;
+    hello.dev = -1;
+    hello.sender_dev = c->own_dev;
+    hello.ndev = c->ndev;
+    if (send(c->ctrl_fd, &hello, sizeof hello, MSG_NOSIGNAL) != (ssize_t)sizeof hello) return abandon(ncclSystemError, "hello not sent");
+    if (!make_endpoints(c)) return abandon(ncclSystemError, "cannot create queue pairs");
+    c->fifo = reinterpret_cast<RdmaDesc*>(alloc_zeroed(sizeof(RdmaDesc) * kMaxRequests));
+    c->done_src = reinterpret_cast<RdmaDoneRec*>(alloc_zeroed(sizeof(RdmaDoneRec) * kMaxRequests));
+    if (!c->fifo || !c->done_src) return abandon(ncclSystemError, "out of memory");
+    c->fifo_mr = rdma_reg(c->fifo, sizeof(RdmaDesc) * kMaxRequests);
+    c->done_src_mr = rdma_reg(c->done_src, sizeof(RdmaDoneRec) * kMaxRequests);
+    if (!c->fifo_mr || !c->done_src_mr) return abandon(ncclSystemError, "cannot register the FIFO");
+    c->mine.fifo_addr = (uint64_t)(uintptr_t)c->fifo;
+    for (int d = 0; d < c->ndev; ++d) c->mine.fifo_rkey[d] = c->fifo_mr->mr[d]->rkey;
+    c->io_done = 0;
+    c->stage = 1;
+  }
+  if (c->stage == 1) {
+    const int rc = io_step(c->ctrl_fd, &c->mine, sizeof c->mine, &c->io_done, true);
+    if (rc < 0) return abandon(ncclSystemError, "bootstrap socket closed");
+    if (rc == 0) return ncclSuccess;
+    c->io_done = 0;
+    c->stage = 2;
+  }
+  if (c->stage == 2) {
+    const int rc = io_step(c->ctrl_fd, &c->theirs, sizeof c->theirs, &c->io_done, false);
+    if (rc < 0) return abandon(ncclSystemError, "bootstrap socket closed");
+    if (rc == 0) return ncclSuccess;
+    if (c->theirs.magic != kInfoMagic || c->theirs.ndev != c->ndev || c->theirs.nqps != c->nqps)
+      return abandon(ncclInternalError, "peer disagrees on devices / queue pairs per connection");
+    if (!connect_endpoints(c)) return abandon(ncclSystemError, "cannot connect queue pairs");
+    c->remote_done_addr = c->theirs.done_addr;
+    memcpy(c->remote_done_rkey, c->theirs.done_rkey, sizeof c->remote_done_rkey);
+    const uint8_t ready = 1;
+    if (send(c->ctrl_fd, &ready, 1, MSG_NOSIGNAL) != 1) return abandon(ncclSystemError, "ready not sent");
+    c->stage = 3;
+    h->connect_state = nullptr;
+    *out = c;
+  }
+  return ncclSuccess;
+}
+
+// Receiver: per pending connection, stage 0 hello, 1 peer info, then endpoints + receives + own info, 2 "ready".
+ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out) {
+  *out = nullptr;
+  for (;;) {
+    int fd = accept(lc->fd, nullptr, nullptr);
+    if (fd < 0) break;
+    set_nonblock_nodelay(fd);
+    RdmaComm* c = new RdmaComm();
+    c->is_send = false;
+    c->own_dev = lc->dev;
+    c->channel_id = lc->channel_id;
+    c->ctrl_fd = fd;
+    c->stage = 0;
+    c->io_done = 0;
+    lc->pending.push_back(c);
+  }
+  for (size_t i = 0; i < lc->pending.size();) {
+    RdmaComm* c = lc->pending[i];
+    auto drop = [&](const char* why) {
+      FL_WARN("rdma accept: dropping a connection: %s", why);
+      rdma_close(c);
+      lc->pending.erase(lc->pending.begin() + i);
+    };
+    if (c->stage == 0) {
+      static_assert(sizeof(Hello) <= sizeof(RdmaConnInfo), "hello is staged in the info buffer");
+      const int rc = io_step(c->ctrl_fd, &c->theirs, sizeof(Hello), &c->io_done, false);
+      if (rc < 0) { drop("closed before the hello"); continue; }
+      if (rc == 0) { ++i; continue; }
+      Hello hello;
+      memcpy(&hello, &c->theirs, sizeof hello);
+      if (hello.magic != kHelloMagic || hello.kind != 2 || hello.ndev < 1 || hello.ndev > kMaxDev) { drop("bad hello"); continue; }
+      c->peer_dev = hello.sender_dev;
+      c->io_done = 0;
+      c->stage = 1;
+    }
+    if (c->stage == 1) {
+      const int rc = io_step(c->ctrl_fd, &c->theirs, sizeof c->theirs, &c->io_done, false);
+      if (rc < 0) { drop("closed during the exchange"); continue; }
+      if (rc == 0) { ++i; continue; }
+      if (c->theirs.magic != kInfoMagic || c->theirs.ndev < 1 || c->theirs.ndev > g_ndev || c->theirs.nqps < 1 || c->theirs.nqps > kRdmaMaxQps) {
+        drop("bad connection info");
+        continue;
+      }
+      c->ndev = c->theirs.ndev;
+      c->nqps = c->theirs.nqps;
+      c->ctrl_dev = c->own_dev % c->ndev;
+      bool ok = make_endpoints(c);
+      c->done = reinterpret_cast<RdmaDoneRec*>(alloc_zeroed(sizeof(RdmaDoneRec) * kMaxRequests));
+      c->fifo_src = reinterpret_cast<RdmaDesc*>(alloc_zeroed(sizeof(RdmaDesc) * kMaxRequests));
+      ok = ok && c->done && c->fifo_src;
+      if (ok) {
+        c->done_mr = rdma_reg(c->done, sizeof(RdmaDoneRec) * kMaxRequests);
+        c->fifo_src_mr = rdma_reg(c->fifo_src, sizeof(RdmaDesc) * kMaxRequests);
+        ok = c->done_mr && c->fifo_src_mr;
+      }
+      if (ok) {
+        // zero-length receives for every write-with-immediate that can be outstanding, on every queue pair
+        for (int d = 0; d < c->ndev && ok; ++d)
+          for (int q = 0; q < c->nqps && ok; ++q)
+            for (int k = 0; k < kMaxRequests && ok; ++k) ok = g_prov->post_recv(c->dev[d].qp[q], kWrRecv) == 0;
+      }
+      ok = ok && connect_endpoints(c);
+      if (!ok) { drop("cannot set up queue pairs"); continue; }
+      c->remote_fifo_addr = c->theirs.fifo_addr;
+      memcpy(c->remote_fifo_rkey, c->theirs.fifo_rkey, sizeof c->remote_fifo_rkey);
+      c->mine.done_addr = (uint64_t)(uintptr_t)c->done;
+      for (int d = 0; d < c->ndev; ++d) c->mine.done_rkey[d] = c->done_mr->mr[d]->rkey;
+      size_t sent = 0;
+      // a few KB into an empty socket buffer: completes at once; anything else is treated as a failure
+      if (io_step(c->ctrl_fd, &c->mine, sizeof c->mine, &sent, true) != 1) { drop("cannot send the connection info"); continue; }
+      c->io_done = 0;
+      c->stage = 2;
+    }
+    if (c->stage == 2) {
+      uint8_t ready = 0;
+      const int rc = io_step(c->ctrl_fd, &ready, 1, &c->io_done, false);
+      if (rc < 0) { drop("closed before ready"); continue; }
+      if (rc == 0) { ++i; continue; }
+      lc->pending.erase(lc->pending.begin() + i);
+      c->stage = 3;
+      c->cur_dev = -1;
+      *out = c;
+      return ncclSuccess;
+    }
+    ++i;
+  }
+  return ncclSuccess;
+}
+
+// -----------------------------------------------------------------------------------------------------
+ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out) {
+  *out = nullptr;
+  if (c->error) return (ncclResult_t)c->error;
+  if (size < 0 || !mr) return ncclInvalidArgument;
+  poll_all(c, cm);
+  if (c->error) return (ncclResult_t)c->error;
+  volatile RdmaDesc* slot = &c->fifo[c->fifo_head % kMaxRequests];
+  if (slot->seq != c->fifo_head + 1) return ncclSuccess;          // the receiver has not posted yet
+  __atomic_thread_fence(__ATOMIC_ACQUIRE);
+  RdmaDesc d;
+  memcpy(&d, const_cast<RdmaDesc*>(slot), sizeof d);
+  if (d.tag != tag) {
+    FL_WARN("rdma isend: tag mismatch (posted %d, sending %d)", d.tag, tag);
+    return ncclInternalError;
+  }
+  if ((uint64_t)size > d.size) {
+    FL_WARN("rdma isend: message of %d bytes does not fit the posted receive of %llu bytes", size, (unsigned long long)d.size);
+    return ncclInvalidUsage;                                       // src/plugin.cc:1555-1570
+  }
+  RdmaRequest* r = get_request(c);
+  if (!r) return ncclSuccess;
+  c->fifo_head++;
+  r->is_send = true;
+  r->size = (uint64_t)size;
+  r->tag = tag;
+
+  // plan: stripes over devices, each stripe over the queue pairs of its device
+  const Params& p = params();
+  const int first = cm->bid_tx(c->channel_id, c->own_dev, d.proposed_dev) % c->ndev;
+  int nstripes = (int)p.degree;
+  if (nstripes > c->ndev) nstripes = c->ndev;
+  if (nstripes < 1) nstripes = 1;
+  while (nstripes > 1 && (uint64_t)size / (uint64_t)nstripes < (uint64_t)p.min_stripe_bytes) --nstripes;
+  const int per_dev_qps = (p.ib_split_data_on_qps && c->nqps > 1 && (uint64_t)size >= 128ull * c->nqps * nstripes) ? c->nqps : 1;
+  const int npieces = nstripes * per_dev_qps;
+  const uint64_t per = npieces > 1 ? ((uint64_t)size / (uint64_t)npieces) & ~127ull : (uint64_t)size;
+  const uint32_t imm = (d.slot & 0xffu) | ((uint32_t)npieces << 8);
+  const bool use_inline = p.ib_use_inline != 0;
+  c->done_src[d.slot % kMaxRequests].size = (uint64_t)size;
+  c->done_src[d.slot % kMaxRequests].tx_mask = cm->tx_mask(c->own_dev);
+
+  uint64_t off = 0;
+  int dev = first, piece = 0;
+  for (int s = 0; s < nstripes; ++s) {
+    for (int k = 0; k < per_dev_qps; ++k, ++piece) {
+      const uint64_t len = piece == npieces - 1 ? (uint64_t)size - off : per;
+      const int q = per_dev_qps > 1 ? k : (int)(c->msg_index % (uint64_t)c->nqps);
+      rdma::SendWr wr[3];
+      int n = 0;
+      if (piece == 0) {                       // the record for the slot travels ahead of the first immediate
+        wr[n].wr_id = 0;
+        wr[n].op = rdma::kWrite;
+        wr[n].laddr = &c->done_src[d.slot % kMaxRequests];
+        wr[n].len = sizeof(RdmaDoneRec);
+        wr[n].lkey = c->done_src_mr->mr[dev]->lkey;
+        wr[n].raddr = c->remote_done_addr + sizeof(RdmaDoneRec) * (d.slot % kMaxRequests);
+        wr[n].rkey = c->remote_done_rkey[dev];
+        wr[n].inline_data = use_inline;
+        ++n;
+      }
+      const uint64_t wr_id = (uint64_t)r->slot | ((uint64_t)piece << 16);
+      const bool split = len > (uint64_t)p.ib_ar_threshold;     // large: data write, then an empty write carrying the immediate
+      if (split) {
+        wr[n].wr_id = wr_id;
+        wr[n].op = rdma::kWrite;
+        wr[n].laddr = (const uint8_t*)data + off;
+        wr[n].len = (uint32_t)len;
+        wr[n].lkey = mr->mr[dev]->lkey;
+        wr[n].raddr = d.addr + off;
+        wr[n].rkey = d.rkey[dev];
+        ++n;
+      }
+      wr[n].wr_id = wr_id;
+      wr[n].op = rdma::kWriteImm;
+      wr[n].laddr = split || len == 0 ? nullptr : (const uint8_t*)data + off;
+      wr[n].len = split ? 0 : (uint32_t)len;
+      wr[n].lkey = mr->mr[dev]->lkey;
+      wr[n].raddr = d.addr + off;
+      wr[n].rkey = d.rkey[dev];
+      wr[n].imm = imm;
+      wr[n].signaled = true;
+      ++n;
+      if (p.fault_bad_rkey_after > 0 && (int64_t)c->msg_index + 1 == p.fault_bad_rkey_after)      // test hook: wrong key on the payload
+        for (int k = piece == 0 ? 1 : 0; k < n; ++k) wr[k].rkey ^= 0x5a5a5a5au;
+      g_pieces.fetch_add(1, std::memory_order_relaxed);
+      g_work_requests.fetch_add((uint64_t)n, std::memory_order_relaxed);
+      if (g_prov->post_send(c->dev[dev].qp[q], wr, n) != 0) {
+        fail(c, ncclSystemError, "post_send failed");
+        r->used = false;
+        return ncclSystemError;
+      }
+      r->pieces.push_back(RdmaPiece{dev, len});
+      cm->mark_tx(dev, len);
+      off += len;
+    }
+    dev = (dev + (int)(p.step > 0 ? p.step : 1)) % c->ndev;
+  }
+  r->pieces_total = npieces;
+  c->msg_index++;
+  g_messages.fetch_add(1, std::memory_order_relaxed);
+  poll_all(c, cm);
+  *out = r;
+  return ncclSuccess;
+}
+
+ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out) {
+  *out = nullptr;
+  if (c->error) return (ncclResult_t)c->error;
+  if (size < 0 || !mr) return ncclInvalidArgument;
+  RdmaRequest* r = get_request(c);
+  if (!r) return ncclSuccess;
+  r->is_send = false;
+  r->size = (uint64_t)size;
+  r->tag = tag;
+  const bool quiescent = c->posted == c->completed;
+  if (c->cur_dev < 0 || (c->n_finished >= kFinishedBatch && quiescent)) {
+    c->cur_dev = cm->refresh_rx(c->channel_id, c->own_dev, c->cur_dev, c->peer_tx_mask, quiescent);
+    c->n_finished = 0;
+  }
+  r->rx_dev = c->cur_dev;
+  const uint64_t idx = c->fifo_tail;
+  RdmaDesc* d = &c->fifo_src[idx % kMaxRequests];
+  memset(d, 0, sizeof *d);
+  d->addr = (uint64_t)(uintptr_t)data;
+  d->size = r->size;
+  d->tag = tag;
+  d->slot = r->slot;
+  d->proposed_dev = c->cur_dev;
+  for (int k = 0; k < c->ndev; ++k) d->rkey[k] = mr->mr[k]->rkey;
+  d->seq = idx + 1;
+  rdma::SendWr wr;
+  wr.wr_id = kWrFifo;
+  wr.op = rdma::kWrite;
+  wr.laddr = d;
+  wr.len = sizeof *d;
+  wr.lkey = c->fifo_src_mr->mr[c->ctrl_dev]->lkey;
+  wr.raddr = c->remote_fifo_addr + sizeof(RdmaDesc) * (idx % kMaxRequests);
+  wr.rkey = c->remote_fifo_rkey[c->ctrl_dev];
+  wr.signaled = (idx % kFifoSignalEvery) == kFifoSignalEvery - 1;
+  wr.inline_data = params().ib_use_inline != 0;
+  if (g_prov->post_send(c->dev[c->ctrl_dev].qp[0], &wr, 1) != 0) {
+    fail(c, ncclSystemError, "descriptor write failed");
+    r->used = false;
+    return ncclSystemError;
+  }
+  c->fifo_tail++;
+  cm->mark_rx(c->cur_dev, r->size);
+  c->posted++;
+  poll_all(c, cm);
+  *out = r;
+  return ncclSuccess;
+}
+
+ncclResult_t rdma_test(RdmaRequest* r, ConnManager* cm, int* done, int* size) {
+  RdmaComm* c = r->comm;
+  *done = 0;
+  poll_all(c, cm);
+  if (r->pieces_total >= 0 && r->pieces_done >= r->pieces_total) {
+    if (!r->is_send) {
+      const RdmaDoneRec rec = c->done[r->slot];
+      if (rec.size > r->size) {
+        fail(c, ncclInvalidUsage, "message larger than the posted receive");
+        return ncclInvalidUsage;
+      }
+      r->total = rec.size;
+      c->peer_tx_mask = rec.tx_mask;
+      c->completed++;
+      c->n_finished++;
+      cm->done_rx(r->rx_dev, r->size);
+    }
+    *done = 1;
+    if (size) *size = (int)(r->is_send ? r->size : r->total);
+    r->used = false;
+    return ncclSuccess;
+  }
+  if (c->error) return (ncclResult_t)c->error;
+  const uint64_t limit_ns = (uint64_t)params().net_timeout_ms * 1000000ull;
+  if (limit_ns && now_ns() - r->last_progress_ns > limit_ns) {
+    FL_WARN("rdma %s request on channel %d made no progress for %ld ms: giving up", r->is_send ? "send" : "recv", c->channel_id,
+            (long)params().net_timeout_ms);
+    c->error = ncclRemoteError;
+    return ncclRemoteError;
+  }
+  return ncclSuccess;
+}
+
+void rdma_close(RdmaComm* c) {
+  if (!c) return;
+  for (int d = 0; d < kMaxDev; ++d) {
+    for (int q = 0; q < kRdmaMaxQps; ++q)
+      if (c->dev[d].qp[q]) g_prov->destroy_qp(c->dev[d].qp[q]);
+    if (c->dev[d].cq) g_prov->destroy_cq(c->dev[d].cq);
+  }
+  rdma_dereg(c->fifo_mr);
+  rdma_dereg(c->done_src_mr);
+  rdma_dereg(c->done_mr);
+  rdma_dereg(c->fifo_src_mr);
+  free(c->fifo);
+  free(c->done_src);
+  free(c->done);
+  free(c->fifo_src);
+  if (c->ctrl_fd >= 0) close(c->ctrl_fd);
+  delete c;
+}
+
+void rdma_close_listen(RdmaListenComm* lc) {
+  if (!lc) return;
+  for (RdmaComm* c : lc->pending) rdma_close(c);
+  if (lc->fd >= 0) close(lc->fd);
+  delete lc;
+}
+
+void rdma_counters(unsigned long long* m, unsigned long long* p, unsigned long long* w) {
+  *m = g_messages.load();
+  *p = g_pieces.load();
+  *w = g_work_requests.load();
+}
+
+}  // namespace flnet
+
+// Counters for tests and tools: messages sent, pieces they were cut into, work requests posted for them.
+extern "C" __attribute__((visibility("default"))) void fuselink_rdma_counters(unsigned long long* messages, unsigned long long* pieces,
+                                                                            unsigned long long* work_requests) {
+  flnet::rdma_counters(messages, pieces, work_requests);
+}

@@ -1,0 +1,151 @@
+// RDMA data transport of the plugin: the receiver-driven write protocol of the reference's verbs path
+// (src/plugin.cc:1394-1677, 1816-1955) on top of the provider interface, so the same code drives libibverbs
+// and the software NIC.
+//
+//   irecv   keeps zero-length receives posted on every queue pair and RDMA-writes a descriptor {address, size,
+//           tag, slot, proposed device, the buffer's remote key on every device} into the sender's FIFO
+//           (256 slots; the reference's ncclIbSendFifo, src/plugin.cc:487-503).
+//   isend   takes the FIFO entry at its head, checks tag and size, cuts the message into pieces -- one stripe per
+//           selected device (NCCL_FUSELINK_DEGREE / _STEP), each stripe over the queue pairs of that device when
+//           NCCL_IB_SPLIT_DATA_ON_QPS is set, in multiples of 128 bytes (src/plugin.cc:1467-1472) -- and posts for
+//           every piece an RDMA write followed by a zero-length write-with-immediate, or a single
+//           write-with-immediate below NCCL_IB_AR_THRESHOLD (src/plugin.cc:1454-1462).  The first piece also
+//           writes {actual size, sender's device mask} into the receiver's record for the slot.
+//   test    polls the completion queues: a send is done when all its pieces completed, a receive when it has
+//           seen as many immediates as the immediate data announces (slot in bits 0-7, piece count in 8-15).
+//
+// Connections are bootstrapped over TCP like the reference's (src/plugin.cc:700-880): the two ends exchange
+// queue-pair addresses, FIFO address and keys, then a "ready" byte.
+#pragma once
+#include <stdint.h>
+
+#include <deque>
+#include <vector>
+
+#include "conn_manager.h"
+#include "nccl_net_abi.h"
+#include "rdma_provider.h"
+#include "tcp_transport.h"
+
+namespace flnet {
+
+constexpr int kRdmaMaxQps = 4;            // per device and connection (NCCL_IB_QPS_PER_CONNECTION, capped)
+constexpr int kFifoSignalEvery = 64;      // descriptor writes are unsignalled except one in this many
+
+struct RdmaMrSet {                        // one registration per device
+  rdma::Mr* mr[kMaxDev];
+  void* data;
+  size_t size;
+};
+
+struct RdmaDesc {                         // 128 bytes, receiver -> sender FIFO
+  uint64_t addr;
+  uint64_t size;
+  int32_t tag;
+  uint32_t slot;
+  int32_t proposed_dev;
+  uint32_t pad0;
+  uint32_t rkey[kMaxDev];
+  uint64_t pad1[3];
+  uint64_t seq;                           // index of the post + 1; written last, polled by the sender
+};
+static_assert(sizeof(RdmaDesc) == 128, "descriptor layout");
+
+struct RdmaDoneRec {                      // sender -> receiver, per slot
+  uint64_t size;
+  uint64_t tx_mask;
+};
+
+struct RdmaConnInfo {                     // exchanged over the bootstrap socket
+  uint32_t magic;
+  int32_t ndev;
+  int32_t nqps;
+  int32_t own_dev;
+  rdma::QpInfo qp[kMaxDev][kRdmaMaxQps];
+  uint64_t fifo_addr;                     // sender only
+  uint32_t fifo_rkey[kMaxDev];
+  uint64_t done_addr;                     // receiver only
+  uint32_t done_rkey[kMaxDev];
+};
+
+struct RdmaPiece {
+  int dev;
+  uint64_t len;
+};
+
+struct RdmaComm;
+struct RdmaRequest {
+  bool used = false, is_send = false;
+  RdmaComm* comm = nullptr;
+  uint32_t slot = 0;
+  uint64_t size = 0;
+  uint64_t total = UINT64_MAX;
+  int tag = 0;
+  int pieces_total = -1;                  // recv: unknown until the first immediate arrives
+  int pieces_done = 0;
+  int rx_dev = 0;
+  uint64_t last_progress_ns = 0;
+  std::vector<RdmaPiece> pieces;          // send only
+};
+
+struct RdmaDevEnd {
+  rdma::Cq* cq = nullptr;
+  rdma::Qp* qp[kRdmaMaxQps] = {nullptr, nullptr, nullptr, nullptr};
+};
+
+struct RdmaComm {
+  bool is_send = false;
+  int own_dev = 0, peer_dev = 0, ndev = 1, nqps = 1, channel_id = 0;
+  int ctrl_fd = -1;
+  int error = 0;
+  RdmaDevEnd dev[kMaxDev];
+  RdmaRequest reqs[kMaxRequests];
+  // sender
+  RdmaDesc* fifo = nullptr;               // written by the peer
+  RdmaMrSet* fifo_mr = nullptr;
+  uint64_t fifo_head = 0;
+  RdmaDoneRec* done_src = nullptr;        // staging for the per-slot records
+  RdmaMrSet* done_src_mr = nullptr;
+  uint64_t remote_done_addr = 0;
+  uint32_t remote_done_rkey[kMaxDev];
+  // receiver
+  RdmaDoneRec* done = nullptr;            // written by the peer
+  RdmaMrSet* done_mr = nullptr;
+  RdmaDesc* fifo_src = nullptr;           // staging for descriptors
+  RdmaMrSet* fifo_src_mr = nullptr;
+  uint64_t remote_fifo_addr = 0;
+  uint32_t remote_fifo_rkey[kMaxDev];
+  uint64_t fifo_tail = 0;
+  int ctrl_dev = 0;                       // device whose queue pair carries the descriptor writes
+  // selection state (same meaning as in the TCP transport)
+  int cur_dev = -1, n_finished = 0, posted = 0, completed = 0;
+  uint64_t peer_tx_mask = ~0ull, msg_index = 0;
+  // bootstrap
+  int stage = 0;
+  size_t io_done = 0;
+  RdmaConnInfo mine, theirs;
+};
+
+struct RdmaListenComm {
+  int fd = -1;
+  int dev = 0;
+  int channel_id = 0;
+  std::vector<RdmaComm*> pending;         // accepted, bootstrap in progress
+};
+
+// Device table / lifetime
+int rdma_init(ConnManager* cm);                           // number of devices (0: transport unavailable)
+rdma::DeviceInfo rdma_device(int dev);
+
+ncclResult_t rdma_listen(int dev, int channel_id, Handle* h, RdmaListenComm** out);
+ncclResult_t rdma_connect(int dev, Handle* h, RdmaComm** out);      // re-entrant, *out stays null until connected
+ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out);       // re-entrant
+RdmaMrSet* rdma_reg(void* data, size_t size);
+void rdma_dereg(RdmaMrSet* m);
+ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out);
+ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out);
+ncclResult_t rdma_test(RdmaRequest* r, ConnManager* cm, int* done, int* size);
+void rdma_close(RdmaComm* c);
+void rdma_close_listen(RdmaListenComm* lc);
+
+}  // namespace flnet

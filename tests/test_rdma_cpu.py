@@ -1,0 +1,116 @@
+"""The RDMA transport of the plugin (receiver-written descriptor FIFO, RDMA write + write-with-immediate, striping
+over devices and queue pairs) driven through the ncclNet entry points by two processes, on the software NIC that
+stands in for libibverbs devices.  Same harness and the same bitwise checks as the TCP transport."""
+import ctypes
+import os
+
+import pytest
+
+from test_plugin_cpu import PLUGIN, _pair
+
+SOFT = {"FUSELINK_TRANSPORT": "rdma", "FUSELINK_RDMA_PROVIDER": "soft", "FUSELINK_SOFT_NDEV": "4"}
+
+
+def _counters(out):
+    line = [l for l in out.splitlines() if l.startswith("RDMA messages")]
+    assert line, out
+    w = line[0].split()
+    return int(w[2]), int(w[4]), int(w[6])
+
+
+@pytest.mark.parametrize("abi", [6, 7, 8])
+def test_bitwise_transfer_reference_config(abi):
+    tx, rx = _pair([4096, 1 << 20, 64 << 20], env=SOFT, common=["--abi", str(abi), "--chunk", "524288", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    msgs, pieces, wrs = _counters(tx[1])
+    assert msgs == 1 + 2 + 128 and pieces == msgs                    # degree 1: one piece per chunk
+    # 4096 B is below the adaptive-routing threshold (one write-with-immediate), the others are a write plus an
+    # empty write-with-immediate; every message also carries its 16-byte size record
+    assert wrs == 2 + 130 * 3
+
+
+def test_odd_sizes_zero_length_and_many_in_flight():
+    tx, rx = _pair([0, 1, 3, 4097, 8192, 8193, 524289, 1234567], env=SOFT, common=["--chunk", "4096", "--inflight", "64"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+
+
+def test_striping_over_devices_and_queue_pairs():
+    """NCCL_FUSELINK_DEGREE devices x NCCL_IB_QPS_PER_CONNECTION queue pairs: every 1 MiB chunk becomes 2 x 2 pieces
+    in multiples of 128 bytes."""
+    env = dict(SOFT, NCCL_FUSELINK_DEGREE="2", NCCL_FUSELINK_STEP="1", FUSELINK_MIN_STRIPE_BYTES="65536",
+               NCCL_IB_QPS_PER_CONNECTION="2", NCCL_IB_SPLIT_DATA_ON_QPS="1")
+    tx, rx = _pair([8 << 20, (1 << 20) + 77], env=env, common=["--chunk", "1048576", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    msgs, pieces, _ = _counters(tx[1])
+    assert msgs == 8 + 2
+    assert pieces == 9 * 4 + 1                                       # the 77-byte tail is too small to cut
+
+
+def test_round_robin_over_queue_pairs_without_splitting():
+    env = dict(SOFT, NCCL_IB_QPS_PER_CONNECTION="4", NCCL_IB_SPLIT_DATA_ON_QPS="0", NCCL_IB_USE_INLINE="1")
+    tx, rx = _pair([4 << 20], env=env, common=["--chunk", "262144", "--inflight", "16"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    msgs, pieces, _ = _counters(tx[1])
+    assert msgs == pieces == 16
+
+
+def test_four_channels_with_the_monitor_choosing_devices():
+    env = dict(SOFT, FUSELINK_SOFT_NDEV="8", NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536")
+    tx, rx = _pair([32 << 20, 3], env=env, common=["--channels", "4", "--chunk", "524288", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "channels 4" in rx[1]
+
+
+def test_wrong_remote_key_is_refused_by_the_responder():
+    """The responder checks key and bounds of every write; a bad key comes back as a remote-access completion error,
+    the queue pair goes to the error state and the connection reports it instead of corrupting memory."""
+    env = dict(SOFT, FUSELINK_FAULT_BAD_RKEY_AFTER="3", FUSELINK_NET_TIMEOUT_MS="2000")
+    tx, rx = _pair([1 << 20], env=env, common=["--chunk", "65536", "--expect-error"], timeout=60)
+    assert tx[0] == 0 and "EXPECTED-ERROR" in tx[1], tx
+    assert rx[0] == 0 and "EXPECTED-ERROR" in rx[1], rx            # the receiver's request never completes: timeout
+    assert "status 10" in tx[2]
+
+
+def test_sender_death_is_detected_by_the_receiver():
+    env = dict(SOFT, FUSELINK_NET_TIMEOUT_MS="1500")
+    tx, rx = _pair([8 << 20], env=env, common=["--chunk", "524288"], extra_send=["--die-after-chunks", "3"],
+                   extra_recv=["--expect-error"], timeout=60)
+    assert tx[0] == 9
+    assert rx[0] == 0 and "EXPECTED-ERROR" in rx[1], rx
+
+
+def test_device_buffers_travel_by_rdma_after_rehoming():
+    env = dict(SOFT, FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS="8", FL_HARNESS_VERBOSE="1")
+    tx, rx = _pair([3 << 20, 70000], env=env, common=["--device-buffers", "--dev", "2", "--chunk", "524288"], extra_recv=["--channel", "3"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "re-homed GPU 2 -> GPU 5" in rx[2] + tx[2]
+
+
+def test_asynchronous_device_event_is_logged():
+    env = dict(SOFT, FL_HARNESS_VERBOSE="1")
+    tx, rx = _pair([4096], env=env, extra_recv=["--inject-event", "port error (injected)"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "asynchronous event: port error (injected)" in rx[2]
+
+
+def test_properties_come_from_the_provider():
+    """With the RDMA transport the devices NCCL sees are the provider's ports."""
+    import subprocess, sys, textwrap
+    code = textwrap.dedent(f"""
+        import ctypes
+        lib = ctypes.CDLL({PLUGIN!r})
+        class V7(ctypes.Structure):
+            _fields_ = [("name", ctypes.c_char_p), ("init", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)),
+                        ("devices", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(ctypes.c_int))),
+                        ("props", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_int, ctypes.c_void_p))]
+        v7 = V7.in_dll(lib, "ncclNetPlugin_v7")
+        assert v7.init(None) == 0
+        n = ctypes.c_int(0); v7.devices(ctypes.byref(n))
+        buf = ctypes.create_string_buffer(256)
+        assert v7.props(1, buf) == 0
+        name = ctypes.cast(buf, ctypes.POINTER(ctypes.c_char_p))[0]
+        print(n.value, name.decode())
+    """)
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, **SOFT), capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["4", "softnic_1"]

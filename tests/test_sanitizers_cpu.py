@@ -20,13 +20,23 @@ def _build(kind):
         pytest.skip(f"sanitizer build not available here: {str(e)[:200]}")
 
 
-def test_plugin_transfer_under_asan_ubsan():
+TRANSPORTS = {
+    "tcp": {},
+    "tcp-direct": {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "4"},
+    "rdma-soft": {"FUSELINK_TRANSPORT": "rdma", "FUSELINK_RDMA_PROVIDER": "soft", "NCCL_IB_QPS_PER_CONNECTION": "2"},
+}
+
+
+@pytest.mark.parametrize("transport", list(TRANSPORTS))
+def test_plugin_transfer_under_asan_ubsan(transport):
     art = _build("address,undefined")
     with tempfile.TemporaryDirectory() as d:
         hf = os.path.join(d, "h")
         env = dict(os.environ, NCCL_SOCKET_IFNAME="lo", ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
-                   NCCL_FUSELINK_DEGREE="3", FUSELINK_MIN_STRIPE_BYTES="4096")
+                   NCCL_FUSELINK_DEGREE="3", FUSELINK_MIN_STRIPE_BYTES="4096", **TRANSPORTS[transport])
         sizes = ["0", "4097", str(1 << 20), str(5 << 20)]
+        if transport == "tcp-direct":
+            sizes = ["--device-buffers"] + sizes
         rx = subprocess.Popen([art["harness"], art["plugin"], "recv", hf, "--chunk", "262144", *sizes], env=env, stdout=subprocess.PIPE,
                               stderr=subprocess.PIPE, text=True)
         tx = subprocess.Popen([art["harness"], art["plugin"], "send", hf, "--chunk", "262144", *sizes], env=env, stdout=subprocess.PIPE,
