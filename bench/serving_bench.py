@@ -28,10 +28,11 @@ def main():
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--input-len", type=int, default=2048)
     ap.add_argument("--decode-steps", type=int, default=256)
+    ap.add_argument("--model-path", default="dummy", help="'dummy' = random weights, else a Hugging Face state_dict file or directory")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--emulate", action="store_true")
     args = ap.parse_args()
-    from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard
+    from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard, load_checkpoint_file
     from fuselink_b200.parallel.symm import SymmetricHeap
     from fuselink_b200.serving.disagg import DecodeStage, KVLink, PrefillStage, ServeParams, make_prompts
 
@@ -42,6 +43,8 @@ def main():
     if args.emulate or world == 1:
         p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, 1)
         net = LlamaShard(cfg, device=dev, max_positions=args.input_len + args.decode_steps)
+        if args.model_path != "dummy":
+            net.load_hf_state_dict(load_checkpoint_file(args.model_path))
         pool_bytes = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
         heaps = SymmetricHeap.emulated(2, pool_bytes + (64 << 20), device=local)
         links = [KVLink(h, p, net.kvh_local) for h in heaps]
@@ -66,6 +69,8 @@ def main():
     tp_rank = rank % tp
     p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, tp)
     net = LlamaShard(cfg, tp_rank, tp, tp_group if tp > 1 else None, device=dev, max_positions=args.input_len + args.decode_steps)
+    if args.model_path != "dummy":
+        net.load_hf_state_dict(load_checkpoint_file(args.model_path))      # every shard cuts its part out of the full checkpoint
     pool_elems = p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim
     heap = SymmetricHeap.create(2 * pool_elems * 2 + (64 << 20), device=local)
     link = KVLink(heap, p, net.kvh_local)

@@ -394,4 +394,23 @@ class LlamaShard(torch.nn.Module):
             t.copy_(sd[k].to(device=t.device, dtype=t.dtype))
 
 
+def load_checkpoint_file(path: str) -> dict:
+    """A Hugging Face style ``state_dict`` from ``path``: a ``.pt`` / ``.bin`` file (``torch.load``), a ``.safetensors``
+    file, or a directory holding any number of those shards."""
+    import os
+    if os.path.isdir(path):
+        sd = {}
+        for f in sorted(os.listdir(path)):
+            if f.endswith((".pt", ".bin", ".safetensors")):
+                sd.update(load_checkpoint_file(os.path.join(path, f)))
+        if not sd:
+            raise FileNotFoundError(f"no .pt / .bin / .safetensors file in {path}")
+        return sd
+    if path.endswith(".safetensors"):
+        from safetensors.torch import load_file
+        return load_file(path)
+    sd = torch.load(path, map_location="cpu", weights_only=True)
+    return sd.get("state_dict", sd) if isinstance(sd, dict) else sd
+
+
 DecoderShard = LlamaShard      # the class serves every family of the zoo; the old name is kept for callers

@@ -160,3 +160,21 @@ def test_two_tensor_parallel_shards_equal_the_unsharded_model(name):
         outs = [torch.load(os.path.join(d, f"r{r}.pt")) for r in range(2)]
     for o in outs:
         assert (o - want).abs().max() < 1e-4 * max(1.0, want.abs().max().item())
+
+
+def test_checkpoint_files_and_directories_load(tmp_path):
+    from fuselink_b200.models.llama import load_checkpoint_file
+    cfg = MODEL_ZOO["tiny_gpt2"]
+    a = LlamaShard(cfg, device="cpu", dtype=torch.float32, seed=1)
+    sd = a.export_hf_state_dict()
+    keys = sorted(sd)
+    torch.save({k: sd[k] for k in keys[: len(keys) // 2]}, tmp_path / "part-0.bin")
+    try:
+        from safetensors.torch import save_file
+        save_file({k: sd[k].contiguous() for k in keys[len(keys) // 2:] if k != "lm_head.weight"}, str(tmp_path / "part-1.safetensors"))
+    except ImportError:
+        torch.save({k: sd[k] for k in keys[len(keys) // 2:]}, tmp_path / "part-1.pt")
+    b = LlamaShard(cfg, device="cpu", dtype=torch.float32, seed=2)
+    b.load_hf_state_dict(load_checkpoint_file(str(tmp_path)))
+    tokens = torch.randint(0, cfg.vocab, (1, 12), generator=torch.Generator().manual_seed(1))
+    assert torch.equal(a.forward_dense(tokens), b.forward_dense(tokens))
