@@ -4,8 +4,14 @@
 
     python experiments/run_online_serving.py [--trace FILE] [--model tiny] [--requests 40] [--rate 200]
 
-With one visible GPU both stages run as virtual ranks on it; the report is the reference's: communication volume per
-batch (KV bytes, header bytes), send window, prefill time."""
+With one process both stages run as virtual ranks on one GPU.  Under torchrun with 2 x TP ranks, ranks below world/2
+are the context stage (rank 0 reads the trace and shares each batch with its tensor-parallel group), the others
+decode, and rank r hands its KV shard to rank r + world/2 -- the reference's layout (online_main.cc:117-170):
+
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 experiments/run_online_serving.py --model opt_6.7b
+
+The report is the reference's: communication volume per batch (KV bytes, header bytes), send window, prefill time.
+The multi-process mode has not been run on hardware yet (the single-process mode has)."""
 import argparse
 import json
 import os
@@ -41,6 +47,9 @@ def main():
             prompt = rng.randint(32, args.input_len)
             lines.append(f"ts: {t:.4f} prompt: {prompt} shared: {rng.randint(0, prompt // 4)} out: {rng.randint(4, 64)}")
         reqs = parse_trace(lines)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1:
+        return multi_process(args, cfg, p, reqs)
     net = LlamaShard(cfg, device="cuda", max_positions=args.input_len + args.decode_steps)
     pool = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
     heaps = SymmetricHeap.emulated(2, 2 * pool + (64 << 20))
@@ -61,6 +70,76 @@ def main():
     print(json.dumps({"served": served, "batches": pre.batches, "total_kv_GB": sum(s.kv_bytes for s in pre.stats) / 1e9}))
     for h in heaps:
         h.close()
+
+
+def multi_process(args, cfg, p, reqs):
+    import threading
+
+    import torch
+    import torch.distributed as dist
+    from fuselink_b200.models.llama import LlamaShard
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    from fuselink_b200.serving.disagg import KVLink, ServeParams
+    from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader, next_batch
+    rank, local, world = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ["WORLD_SIZE"])
+    assert world % 2 == 0, "half of the ranks prefill, half decode"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    tp = world // 2
+    is_prefill = rank < tp
+    groups = [dist.new_group(list(range(0, tp))), dist.new_group(list(range(tp, world)))]
+    group = groups[0] if is_prefill else groups[1]
+    p = ServeParams(cfg, MAX_BATCH, args.input_len, args.decode_steps, tp)
+    net = LlamaShard(cfg, rank % tp, tp, group if tp > 1 else None, device=dev, max_positions=args.input_len + args.decode_steps)
+    pool = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
+    heap = SymmetricHeap.create(2 * pool + (64 << 20), device=local)
+    links = [KVLink(heap, p, net.kvh_local, name=f"kv{i}") for i in range(2)]
+    peer = rank + tp if is_prefill else rank - tp
+    served = 0
+    if is_prefill:
+        pre = OnlinePrefill(p, net, links, peer)
+        q = queue.Queue()
+        if rank == 0:
+            TraceReader(reqs, q).start()
+        finished = False
+        while not finished:
+            box = [None]
+            if rank == 0:
+                batch, finished = next_batch(q, MAX_BATCH, p.input_len)
+                box[0] = (batch, finished)
+            if tp > 1:
+                dist.broadcast_object_list(box, src=0, group=group)
+            batch, finished = box[0]
+            if not batch:
+                continue
+            st = pre.serve_batch(batch)
+            served += len(batch)
+            if rank == 0:
+                print(json.dumps({"batch": st.batch, "prompt_tokens": st.prompt_tokens, "kv_MB": st.kv_bytes / 1e6, "header_B": st.header_bytes,
+                                  "prefill_ms": round(st.prefill_ms, 3), "send_window_ms": round(st.send_ms, 3)}), flush=True)
+        pre.send_end()
+        heap.check_status("online prefill")
+        if rank == 0:
+            print(json.dumps({"served": served, "batches": pre.batches - 1, "total_kv_GB_per_rank": sum(s.kv_bytes for s in pre.stats) / 1e9}), flush=True)
+    else:
+        dec = OnlineDecode(p, net, links, peer, sleep_ms=args.decode_sleep_ms)
+        while True:
+            out = dec.serve_batch(args.decode_steps)
+            if out["batch"] == 0:
+                break
+            served += out["batch"]
+        heap.check_status("online decode")
+        if rank == tp:
+            print(json.dumps({"decoded_requests": served, "batches": dec.batches - 1}), flush=True)
+    wd = threading.Timer(60.0, lambda: os._exit(0))      # the report is out: never hang in teardown
+    wd.daemon = True
+    wd.start()
+    torch.cuda.synchronize()
+    dist.barrier()
+    heap.close()
+    dist.destroy_process_group()
+    wd.cancel()
 
 
 if __name__ == "__main__":

@@ -145,7 +145,7 @@ class OnlinePrefill:
         first = self.model.prefill(tokens, self.k_pool, self.v_pool, src_bt, None, last_pos=last_pos)
         e1.record()
         if use > 0:   # wait until the decoder has released this pool (credit = number of batches it finished on it)
-            C.wait_flags([(heap.sig_addr(self.credit_slot + self.batches % len(self.links)), use)], heap.status_addr)
+            self._wait_credit(use)
         link.seq += 1
         hdr = torch.zeros(HDR_INTS, dtype=torch.int64, device=self.dev)
         hdr[0], hdr[1], hdr[2], hdr[3] = B, S, mb, self.batches
@@ -162,6 +162,31 @@ class OnlinePrefill:
         self.stats.append(st)
         self.batches += 1
         return st
+
+
+    def _wait_credit(self, use: int):
+        """The long part of the wait is a host poll (a decoder may work on the pool for seconds); the device wait
+        behind it only orders the following kernels after the credit."""
+        heap = self.links[0].heap
+        slot = self.credit_slot + self.batches % len(self.links)
+        if not heap.host_wait(slot, use, 600.0):
+            raise TimeoutError(f"decoder did not release pool {self.batches % len(self.links)} within 600 s")
+        self.links[0].C.wait_flags([(heap.sig_addr(slot), use)], heap.status_addr)
+
+    def send_end(self):
+        """Tell the decoder that the trace is over: a header with batch size 0 on the next pool."""
+        link = self.links[self.batches % len(self.links)]
+        use = self.batches // len(self.links)
+        if use > 0:
+            self._wait_credit(use)
+        link.seq += 1
+        hdr = torch.zeros(HDR_INTS, dtype=torch.int64, device=self.dev)
+        hdr[3] = self.batches
+        one = torch.zeros(1, 1, dtype=torch.int32, device=self.dev)
+        link.send_layers(self.dst, self.k_pool, self.v_pool, 1, one, one, torch.zeros(1, dtype=torch.int32, device=self.dev), 0, 1,
+                         hdr=hdr, final=True, num_ctas=1)
+        torch.cuda.synchronize()
+        self.batches += 1
 
 
 class OnlineDecode:
@@ -186,6 +211,9 @@ class OnlineDecode:
         heap.check_status("online decode wait")
         hdr = link.hdr.local.cpu()
         B, S, mb = int(hdr[0]), int(hdr[1]), int(hdr[2])
+        if B == 0:                                   # end of the trace (OnlinePrefill.send_end)
+            self.batches += 1
+            return {"batch": 0, "padded_len": 0, "steps": 0, "generated": None, "output_lens": []}
         lens = hdr[HDR_LENS:HDR_LENS + B].clone()
         outs = hdr[HDR_OUTS:HDR_OUTS + B].clone()
         dev = link.k_pool.local.device
