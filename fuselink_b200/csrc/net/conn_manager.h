@@ -10,6 +10,9 @@
 // rule as the fallback when the monitor is off.
 #pragma once
 #include <stdint.h>
+
+#include <atomic>
+
 #include "../monitor/monitor.h"
 
 namespace flnet {
@@ -37,13 +40,13 @@ class ConnManager {
   // 64-bit mask of devices this process considers available for tx (bit set = idle or own)
   uint64_t tx_mask(int own_dev);
   void set_dead(int dev, bool dead);
-  uint64_t decisions() const { return decisions_; }
-  uint64_t fallbacks() const { return fallbacks_; }
+  uint64_t decisions() const { return decisions_.load(std::memory_order_relaxed); }
+  uint64_t fallbacks() const { return fallbacks_.load(std::memory_order_relaxed); }
 
  private:
   int ndev_, priority_dev_;
   FlMonitor* mon_ = nullptr;
-  uint64_t decisions_ = 0, fallbacks_ = 0;
+  std::atomic<uint64_t> decisions_{0}, fallbacks_{0};   // entered from every proxy thread
 };
 
 }  // namespace flnet

@@ -8,7 +8,9 @@
 // sender mirrors it.  Payloads are fp32 uniform[-1,1] generated from --seed on both sides, so the receiver
 // can compare bit for bit without a side channel.  Exit code 0 = all messages identical.
 //
-// Options: --chunk N  --inflight N  --seed N  --dev N  --abi 6|7|8  --die-after-chunks N (sender exits
+// Options: --chunk N  --inflight N  --seed N  --dev N  --abi 6|7|8  --channels N (connections side by side)  --threads
+// (one thread per channel, each moving every message on its own connection, the way NCCL runs one proxy thread per
+// device)  --die-after-chunks N (sender exits
 // abruptly after N chunks: peer-failure test)  --expect-error (receiver: a transfer error is the
 // expected outcome; exit 0 if it is reported within the timeout, 3 if the transfer hangs or succeeds).
 #include <dlfcn.h>
@@ -19,22 +21,23 @@
 #include <time.h>
 #include <unistd.h>
 
+#include <atomic>
 #include <deque>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "nccl_net_abi.h"
 
-static uint64_t rng_state;
-static inline uint64_t next_u64() {  // xorshift64*
+static inline uint64_t next_u64(uint64_t& rng_state) {  // xorshift64*
   rng_state ^= rng_state >> 12;
   rng_state ^= rng_state << 25;
   rng_state ^= rng_state >> 27;
   return rng_state * 2685821657736338717ull;
 }
 static void fill(std::vector<float>& v, uint64_t seed, size_t msg_index) {
-  rng_state = seed * 0x9E3779B97F4A7C15ull + msg_index * 0xD1B54A32D192ED03ull + 1;
-  for (auto& x : v) x = (float)((double)(next_u64() >> 11) / (double)(1ull << 53) * 2.0 - 1.0);
+  uint64_t rng_state = seed * 0x9E3779B97F4A7C15ull + msg_index * 0xD1B54A32D192ED03ull + 1;
+  for (auto& x : v) x = (float)((double)(next_u64(rng_state) >> 11) / (double)(1ull << 53) * 2.0 - 1.0);
 }
 static double now_s() {
   timespec ts;
@@ -96,7 +99,7 @@ int main(int argc, char** argv) {
   size_t chunk = 512 * 1024;
   int inflight = 8, dev = 0, die_after = -1, channel = 0, nch = 1;
   uint64_t seed = 0;
-  bool expect_error = false, device_bufs = false;
+  bool expect_error = false, device_bufs = false, threaded = false;
   const char* inject_event = nullptr;
   Api api;
   std::vector<size_t> sizes;
@@ -112,6 +115,7 @@ int main(int argc, char** argv) {
     else if (a == "--channel") channel = (int)val();      // receiver: burn this many channel ids first
     else if (a == "--die-after-chunks") die_after = (int)val();
     else if (a == "--expect-error") expect_error = true;
+    else if (a == "--threads") threaded = true;
     else if (a == "--inject-event") inject_event = argv[++i];   // raise an asynchronous device event after init (software NIC)
     else if (a == "--device-buffers") device_bufs = true;   // buffers come from the plugin's cuMem layer and are registered as CUDA
     else sizes.push_back(strtoull(a.c_str(), nullptr, 0));
@@ -177,10 +181,13 @@ int main(int argc, char** argv) {
   }
   void* comm = comms[0];
 
-  int rc = 0;
-  size_t total_bytes = 0;
+  if (device_bufs) api.ptr_type = NCCL_PTR_CUDA;
+  std::atomic<size_t> total_bytes{0};
+  std::atomic<int> chunks_done_total{0};
   const double t0 = now_s();
-  int chunks_done_total = 0;
+  // moves every message over the connections [ch0, ch0 + nch): chunk c of a message travels on connection ch0 + c % nch
+  auto transfer = [&](const int ch0, const int nch, uint64_t seed) -> int {
+  int rc = 0;
   for (size_t mi = 0; mi < sizes.size() && rc == 0; ++mi) {
     const size_t bytes = sizes[mi];
     std::vector<float> host((bytes + 3) / 4), expect;
@@ -193,14 +200,13 @@ int main(int argc, char** argv) {
       region = create ? create(dev, host.size() * 4 + 16, 0) : nullptr;
       if (!region) { fprintf(stderr, "fl_vmm_create failed\n"); return 2; }
       bufp = (float*)vptr(region);
-      api.ptr_type = NCCL_PTR_CUDA;
     }
     struct BufView { float* p; size_t n; float* data() { return p; } size_t size() { return n; } } buf{bufp, host.size()};
     if (is_send) { fill(host, seed, mi); if (!host.empty()) memcpy(bufp, host.data(), host.size() * 4); }
     else { expect.resize(host.size()); fill(expect, seed, mi); if (!host.empty()) memset(bufp, 0xA5, host.size() * 4); }
     std::vector<void*> mhs(nch, nullptr);
     for (int c = 0; c < nch; ++c)
-      if (api.regMr(comms[c], buf.data(), buf.size() * 4, &mhs[c]) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
+      if (api.regMr(comms[ch0 + c], buf.data(), buf.size() * 4, &mhs[c]) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
     if (device_bufs && mi == 0) {
       auto p2d = (int (*)(const void*))dlsym(lib, "fl_vmm_ptr2dev");
       printf("REGISTERED device-buffer owner %d now-backed-by %d\n", dev, p2d ? p2d(bufp) : -1);
@@ -217,8 +223,8 @@ int main(int argc, char** argv) {
         const size_t off = next * chunk;
         const int len = (int)(bytes - off < chunk ? bytes - off : chunk);
         void* r = nullptr;
-        ncclResult_t e = is_send ? api.isend(comms[c], (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mhs[c], &r)
-                                 : api.irecv(comms[c], (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mhs[c], &r);
+        ncclResult_t e = is_send ? api.isend(comms[ch0 + c], (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mhs[c], &r)
+                                 : api.irecv(comms[ch0 + c], (char*)buf.data() + off, len, (int)(mi * 1000003 + next), mhs[c], &r);
         if (e != ncclSuccess) { fprintf(stderr, "%s failed with %d\n", is_send ? "isend" : "irecv", (int)e); rc = 4; break; }
         if (!r) break;   // would block
         reqs[c].push_back(r);
@@ -245,15 +251,28 @@ int main(int argc, char** argv) {
       fprintf(stderr, "message %zu (%zu bytes) differs at byte %zu\n", mi, bytes, bad);
       rc = 5;
     }
-    for (int c = 0; c < nch; ++c) api.deregMr(comms[c], mhs[c]);
+    for (int c = 0; c < nch; ++c) api.deregMr(comms[ch0 + c], mhs[c]);
     total_bytes += bytes;
+  }
+  return rc;
+  };
+  int rc = 0;
+  if (!threaded) {
+    rc = transfer(0, nch, seed);
+  } else {
+    std::vector<int> rcs(nch, 0);
+    std::vector<std::thread> th;
+    for (int c = 0; c < nch; ++c) th.emplace_back([&, c] { rcs[c] = transfer(c, 1, seed + 1000003ull * c); });
+    for (auto& t : th) t.join();
+    for (int c = 0; c < nch; ++c)
+      if (rcs[c] && !rc) rc = rcs[c];
   }
   const double dt = now_s() - t0;
   if (expect_error) {
     if (rc == 4) { printf("EXPECTED-ERROR after %.3f s\n", dt); rc = 0; }
     else if (rc == 0) { fprintf(stderr, "transfer succeeded but an error was expected\n"); rc = 3; }
   } else if (rc == 0) {
-    printf("OK %s %zu bytes in %.4f s (%.3f GB/s) abi v%d\n", is_send ? "sent" : "received", total_bytes, dt, total_bytes / dt / 1e9, api.abi);
+    printf("OK %s %zu bytes in %.4f s (%.3f GB/s) abi v%d\n", is_send ? "sent" : "received", total_bytes.load(), dt, total_bytes.load() / dt / 1e9, api.abi);
   }
   auto decisions = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_decisions");
   auto fallbacks = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_fallbacks");
@@ -265,7 +284,7 @@ int main(int argc, char** argv) {
     rdma_ctr(&m, &pc, &w);
     if (m) printf("RDMA messages %llu pieces %llu work-requests %llu\n", m, pc, w);
   }
-  if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes);
+  if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes.load());
   if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);
   for (int c = 0; c < nch; ++c) {
     if (is_send) api.closeSend(comms[c]);

@@ -430,11 +430,11 @@ ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int 
   if (size < 0 || !mr) return ncclInvalidArgument;
   poll_all(c, cm);
   if (c->error) return (ncclResult_t)c->error;
-  volatile RdmaDesc* slot = &c->fifo[c->fifo_head % kMaxRequests];
-  if (slot->seq != c->fifo_head + 1) return ncclSuccess;          // the receiver has not posted yet
-  __atomic_thread_fence(__ATOMIC_ACQUIRE);
+  RdmaDesc* slot = &c->fifo[c->fifo_head % kMaxRequests];
+  // the NIC writes this memory; the sequence word is the last one of the entry to land
+  if (__atomic_load_n(&slot->seq, __ATOMIC_ACQUIRE) != c->fifo_head + 1) return ncclSuccess;   // the receiver has not posted yet
   RdmaDesc d;
-  memcpy(&d, const_cast<RdmaDesc*>(slot), sizeof d);
+  memcpy(&d, slot, sizeof d);
   if (d.tag != tag) {
     FL_WARN("rdma isend: tag mismatch (posted %d, sending %d)", d.tag, tag);
     return ncclInternalError;

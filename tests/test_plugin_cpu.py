@@ -123,6 +123,15 @@ def test_stalled_peer_times_out():
         assert rx.returncode == 0 and "EXPECTED-ERROR" in out, (out, err)
 
 
+def test_one_thread_per_channel():
+    """NCCL drives the plugin from one proxy thread per device: four threads, each with its own connection, move every
+    message concurrently through the shared selector and monitor."""
+    env = {"FUSELINK_TCP_NDEV": "4", "NCCL_FUSELINK_DEGREE": "2", "FUSELINK_MIN_STRIPE_BYTES": "65536"}
+    tx, rx = _pair([8 << 20, 4097, 0], common=["--channels", "4", "--threads", "--chunk", "262144", "--inflight", "8"], env=env)
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert f"OK received {4 * ((8 << 20) + 4097)} bytes" in rx[1]
+
+
 def test_device_buffers_are_adopted_rehomed_and_staged():
     """regMr on a "GPU" buffer (cuMem layer on its memfd stand-in): the buffer is adopted, re-homed onto the relay GPU
     (owner + channel) % nGPUs with its contents kept, and the bytes still arrive intact through the staging path."""

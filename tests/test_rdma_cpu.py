@@ -61,6 +61,13 @@ def test_four_channels_with_the_monitor_choosing_devices():
     assert "channels 4" in rx[1]
 
 
+def test_one_thread_per_channel():
+    env = dict(SOFT, NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536", NCCL_IB_QPS_PER_CONNECTION="2")
+    tx, rx = _pair([8 << 20, 4097, 0], env=env, common=["--channels", "4", "--threads", "--chunk", "262144", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert f"OK received {4 * ((8 << 20) + 4097)} bytes" in rx[1]
+
+
 def test_wrong_remote_key_is_refused_by_the_responder():
     """The responder checks key and bounds of every write; a bad key comes back as a remote-access completion error,
     the queue pair goes to the error state and the connection reports it instead of corrupting memory."""

@@ -47,6 +47,24 @@ def test_plugin_transfer_under_asan_ubsan(transport):
     assert "ERROR: AddressSanitizer" not in txe + rxe and "runtime error" not in txe + rxe
 
 
+@pytest.mark.parametrize("transport", ["tcp", "rdma-soft"])
+def test_threaded_plugin_under_tsan(transport):
+    """Four proxy-like threads per process drive four connections through the plugin built with ThreadSanitizer: the
+    shared state (channel counter, selector, monitor table, registration table, software NIC) must be race-free."""
+    art = _build("thread")
+    with tempfile.TemporaryDirectory() as d:
+        hf = os.path.join(d, "h")
+        env = dict(os.environ, NCCL_SOCKET_IFNAME="lo", TSAN_OPTIONS="halt_on_error=1", NCCL_FUSELINK_DEGREE="2",
+                   FUSELINK_MIN_STRIPE_BYTES="4096", **TRANSPORTS[transport])
+        args = ["--channels", "4", "--threads", "--chunk", "131072", "--inflight", "4", str(2 << 20), "4097"]
+        rx = subprocess.Popen([art["harness"], art["plugin"], "recv", hf, *args], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        tx = subprocess.Popen([art["harness"], art["plugin"], "send", hf, *args], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        txo, txe = tx.communicate(timeout=300)
+        rxo, rxe = rx.communicate(timeout=300)
+    assert "WARNING: ThreadSanitizer" not in txe + rxe, (txe[-3000:], rxe[-3000:])
+    assert tx.returncode == 0 and rx.returncode == 0, (txo, txe[-2000:], rxo, rxe[-2000:])
+
+
 @pytest.mark.parametrize("kind", ["thread", "address,undefined"])
 def test_monitor_stress_under_sanitizer(kind):
     art = _build(kind)
