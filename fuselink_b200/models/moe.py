@@ -22,12 +22,53 @@ def zipf_log_bias(num_experts: int, s: float = 1.2) -> torch.Tensor:
     return (p / p.sum()).log()
 
 
+def expert_capacity(tokens: int, num_experts: int, topk: int, capacity_factor: float, min_capacity: int = 4) -> int:
+    """Rows one expert accepts from one rank's batch: ceil(tokens / experts * factor) per routing choice."""
+    import math
+    return max(int(math.ceil(tokens / num_experts * capacity_factor)) * topk, min_capacity)
+
+
+def capacity_keep_mask(idx: torch.Tensor, num_experts: int, capacity: int) -> torch.Tensor:
+    """[T, k] bool: which routing choices fit when every expert accepts at most ``capacity`` rows of this batch.
+    Choices are admitted in token order, all first choices before any second choice (the GShard / DeepSpeed rule)."""
+    T, k = idx.shape
+    keep = torch.zeros(T, k, dtype=torch.bool, device=idx.device)
+    taken = torch.zeros(num_experts, dtype=torch.long, device=idx.device)
+    for j in range(k):
+        onehot = torch.nn.functional.one_hot(idx[:, j].long(), num_experts)            # [T, E]
+        pos = (onehot.cumsum(0) - 1 + taken.unsqueeze(0)).gather(1, idx[:, j:j + 1].long()).squeeze(1)
+        keep[:, j] = pos < capacity
+        taken = taken + onehot.sum(0)
+    return keep
+
+
+def load_balancing_loss(probs: torch.Tensor, idx: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """E * sum_e (share of tokens whose first choice is e) * (mean router probability of e): 1 when balanced."""
+    me = probs.mean(0)
+    ce = torch.nn.functional.one_hot(idx[:, 0].long(), num_experts).float().mean(0)
+    return (me * ce).sum() * num_experts
+
+
 class MoELayer(nn.Module):
+    """Router + this rank's experts.
+
+    Gating options (what the MoE layer of the reference's Megatron-DeepSpeed experiment exposes): ``capacity_factor``
+    with ``drop_tokens`` (choices over an expert's capacity contribute nothing; on the fused path their rows still
+    travel, with weight zero, because the transport is sized for the worst case), ``noisy_gate`` ("jitter": inputs of
+    the router are scaled by U(1-eps, 1+eps) in training; "rsample": Gumbel noise on the logits), and the
+    load-balancing auxiliary loss of the last forward in ``self.l_aux``."""
+
     def __init__(self, cfg: MoEConfig, heap: Optional[SymmetricHeap] = None, rank: int = 0, world: int = 1,
                  device="cuda", zipf_s: Optional[float] = 1.2, seed: int = 0, fused_sgd_lr: float = 0.0,
-                 name: str = "moe"):
+                 name: str = "moe", capacity_factor: float = 0.0, drop_tokens: bool = False, min_capacity: int = 4,
+                 noisy_gate: Optional[str] = None, jitter_eps: float = 1e-2):
         super().__init__()
         self.cfg, self.rank, self.world = cfg, rank, world
+        assert noisy_gate in (None, "jitter", "rsample")
+        self.capacity_factor, self.drop_tokens, self.min_capacity = capacity_factor, drop_tokens, min_capacity
+        self.noisy_gate, self.jitter_eps = noisy_gate, jitter_eps
+        self.l_aux = torch.zeros((), device=device)
+        self.dropped_fraction = 0.0
         assert cfg.num_experts % world == 0
         self.epr = cfg.num_experts // world
         self.fused_sgd_lr = fused_sgd_lr
@@ -51,10 +92,23 @@ class MoELayer(nn.Module):
 
     # -- routing ------------------------------------------------------------------------------------------
     def route(self, x: torch.Tensor):
-        logits = (x @ self.router.t()).float() + self.router_bias
+        xr = x
+        if self.training and self.noisy_gate == "jitter":
+            xr = x * torch.empty_like(x).uniform_(1.0 - self.jitter_eps, 1.0 + self.jitter_eps)
+        logits = (xr @ self.router.t()).float() + self.router_bias
         probs = torch.softmax(logits, dim=-1)
-        w, idx = torch.topk(probs, self.cfg.topk, dim=-1)
+        pick = logits
+        if self.training and self.noisy_gate == "rsample":
+            pick = logits - torch.log(-torch.log(torch.rand_like(logits).clamp_min(1e-20)))    # Gumbel-max sampling
+        _, idx = torch.topk(pick, self.cfg.topk, dim=-1)
+        w = probs.gather(1, idx)
         w = w / w.sum(dim=-1, keepdim=True)
+        self.l_aux = load_balancing_loss(probs, idx, self.cfg.num_experts)
+        if self.drop_tokens and self.capacity_factor > 0:
+            cap = expert_capacity(x.shape[0], self.cfg.num_experts, self.cfg.topk, self.capacity_factor, self.min_capacity)
+            keep = capacity_keep_mask(idx, self.cfg.num_experts, cap)
+            self.dropped_fraction = 1.0 - keep.float().mean()
+            w = w * keep.to(w.dtype)
         return w, idx.int()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:

@@ -111,3 +111,56 @@ def test_checkpoint_roundtrip_dlrm_includes_tables():
     assert "tables" in a.state_dict() and torch.equal(a.tables, b.tables)
     dense, idx, _ = synthetic_batch(cfg, 0, 1, "cpu", seed=3)
     assert torch.equal(a.dense_forward(dense, a._pooled_reference(idx)), b.dense_forward(dense, b._pooled_reference(idx)))
+
+
+def test_gating_capacity_mask_matches_a_sequential_admission():
+    from fuselink_b200.models.moe import capacity_keep_mask, expert_capacity
+    g = torch.Generator().manual_seed(0)
+    T, E, k = 200, 8, 2
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    idx[:120, 0] = 3                                    # a hot expert
+    cap = expert_capacity(T, E, k, 1.0)
+    assert cap == 50
+    keep = capacity_keep_mask(idx, E, cap)
+    taken, want = [0] * E, torch.zeros(T, k, dtype=torch.bool)
+    for j in range(k):                                  # all first choices, then all second choices, in token order
+        for t in range(T):
+            e = int(idx[t, j])
+            want[t, j] = taken[e] < cap
+            taken[e] += 1
+    assert torch.equal(keep, want)
+    assert keep[:50, 0].all() and not keep[50:120, 0].any()
+
+
+def test_moe_layer_gating_options_on_cpu():
+    from fuselink_b200.models.moe import MoELayer, load_balancing_loss
+    from fuselink_b200.ops.moe import MoEConfig
+    cfg = MoEConfig(hidden=64, ffn=128, num_experts=4, topk=2, tokens=64)
+    x = torch.randn(cfg.tokens, cfg.hidden, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)
+    plain = MoELayer(cfg, None, 0, 1, device="cpu", seed=5, zipf_s=None)
+    out0 = plain(x)
+    assert 0.9 < float(plain.l_aux) < 4.0               # 1 when balanced, E when everything goes to one expert
+    skew = MoELayer(cfg, None, 0, 1, device="cpu", seed=5, zipf_s=3.0)
+    skew(x)
+    assert float(skew.l_aux) > float(plain.l_aux)
+    # aux loss reaches the router
+    (plain.l_aux * 0.01).backward()
+    assert plain.router.grad is not None and plain.router.grad.abs().sum() > 0
+    # dropping: choices over capacity contribute nothing
+    drop = MoELayer(cfg, None, 0, 1, device="cpu", seed=5, zipf_s=3.0, capacity_factor=0.5, drop_tokens=True)
+    out1 = drop(x)
+    assert 0.0 < float(drop.dropped_fraction) < 1.0
+    w, idx = drop.route(x)
+    assert (w == 0).any() and torch.isfinite(out1.float()).all()
+    # jitter only in training
+    noisy = MoELayer(cfg, None, 0, 1, device="cpu", seed=5, zipf_s=None, noisy_gate="jitter", jitter_eps=0.5)
+    noisy.eval()
+    assert torch.equal(noisy(x), out0)
+    noisy.train()
+    w_a, _ = noisy.route(x)
+    w_b, _ = noisy.route(x)
+    assert not torch.equal(w_a, w_b)
+    rs = MoELayer(cfg, None, 0, 1, device="cpu", seed=5, zipf_s=None, noisy_gate="rsample")
+    _, i_a = rs.route(x)
+    _, i_b = rs.route(x)
+    assert not torch.equal(i_a, i_b)
