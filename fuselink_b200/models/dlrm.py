@@ -155,11 +155,14 @@ class DLRM(nn.Module):
         logits = self.dense_forward(dense, pooled)
         loss = F.binary_cross_entropy_with_logits(logits, labels)
         loss.backward()
+        work = flat = grads = None
         if self.world > 1:
+            # data-parallel part: one bucket for every dense gradient, reduced while the sparse backward runs
             import torch.distributed as dist
-            for p in self.dense_parameters():
-                dist.all_reduce(p.grad)
-                p.grad /= self.world
+            from torch._utils import _flatten_dense_tensors, _unflatten_dense_tensors
+            grads = [p.grad for p in self.dense_parameters()]
+            flat = _flatten_dense_tensors(grads)
+            work = dist.all_reduce(flat, async_op=True)
         # the loss is a mean over the local batch; the global objective is the mean over ranks
         gp = pooled.grad / self.world if self.world > 1 else pooled.grad
         if dense.is_cuda:
@@ -167,6 +170,11 @@ class DLRM(nn.Module):
             self.sparse_backward_apply(indices)
         else:
             self._sparse_backward_reference(indices, gp)
+        if work is not None:
+            work.wait()
+            flat /= self.world
+            for g, r in zip(grads, _unflatten_dense_tensors(flat, grads)):
+                g.copy_(r)
         opt.step()
         opt.zero_grad(set_to_none=True)
         return loss.detach()
