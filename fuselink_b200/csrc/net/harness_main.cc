@@ -82,6 +82,7 @@ struct Api {
   ncclResult_t isend(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(isend)(c, d, s, tag, mh, r); }
   ncclResult_t irecv(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(irecv)(c, 1, &d, &s, &tag, &mh, r); }
   ncclResult_t test(void* r, int* done, int* sz) { return PICK(test)(r, done, sz); }
+  ncclResult_t iflush(void* c, void* d, int s, void* mh, void** r) { return PICK(iflush)(c, 1, &d, &s, &mh, r); }
   ncclResult_t closeSend(void* c) { return PICK(closeSend)(c); }
   ncclResult_t closeRecv(void* c) { return PICK(closeRecv)(c); }
   ncclResult_t closeListen(void* c) { return PICK(closeListen)(c); }
@@ -99,7 +100,7 @@ int main(int argc, char** argv) {
   size_t chunk = 512 * 1024;
   int inflight = 8, dev = 0, die_after = -1, channel = 0, nch = 1;
   uint64_t seed = 0;
-  bool expect_error = false, device_bufs = false, threaded = false;
+  bool expect_error = false, device_bufs = false, threaded = false, do_flush = false;
   const char* inject_event = nullptr;
   Api api;
   std::vector<size_t> sizes;
@@ -116,6 +117,7 @@ int main(int argc, char** argv) {
     else if (a == "--die-after-chunks") die_after = (int)val();
     else if (a == "--expect-error") expect_error = true;
     else if (a == "--threads") threaded = true;
+    else if (a == "--flush") do_flush = true;               // receiver: iflush the whole buffer after every message
     else if (a == "--inject-event") inject_event = argv[++i];   // raise an asynchronous device event after init (software NIC)
     else if (a == "--device-buffers") device_bufs = true;   // buffers come from the plugin's cuMem layer and are registered as CUDA
     else sizes.push_back(strtoull(a.c_str(), nullptr, 0));
@@ -183,7 +185,7 @@ int main(int argc, char** argv) {
 
   if (device_bufs) api.ptr_type = NCCL_PTR_CUDA;
   std::atomic<size_t> total_bytes{0};
-  std::atomic<int> chunks_done_total{0};
+  std::atomic<int> chunks_done_total{0}, flushes{0};
   const double t0 = now_s();
   // moves every message over the connections [ch0, ch0 + nch): chunk c of a message travels on connection ch0 + c % nch
   auto transfer = [&](const int ch0, const int nch, uint64_t seed) -> int {
@@ -245,6 +247,18 @@ int main(int argc, char** argv) {
       }
       if (now_s() > msg_limit) { fprintf(stderr, "message %zu timed out\n", mi); rc = 3; }
     }
+    if (rc == 0 && !is_send && do_flush && bytes > 0) {
+      void* fr = nullptr;
+      const int flen = (int)(bytes < chunk ? bytes : chunk);
+      if (api.iflush(comms[ch0], buf.data(), flen, mhs[0], &fr) != ncclSuccess) { fprintf(stderr, "iflush failed\n"); rc = 4; }
+      int fdone = fr ? 0 : 1, fsz = 0;
+      const double flimit = now_s() + 30.0;
+      while (rc == 0 && !fdone) {
+        if (api.test(fr, &fdone, &fsz) != ncclSuccess) { fprintf(stderr, "flush test failed\n"); rc = 4; }
+        if (now_s() > flimit) { fprintf(stderr, "flush timed out\n"); rc = 3; }
+      }
+      if (rc == 0) flushes += fr ? 1 : 0;
+    }
     if (rc == 0 && !is_send && bytes > 0 && memcmp(buf.data(), expect.data(), bytes) != 0) {
       size_t bad = 0;
       while (bad < bytes && ((char*)buf.data())[bad] == ((char*)expect.data())[bad]) ++bad;
@@ -285,6 +299,7 @@ int main(int argc, char** argv) {
     if (m) printf("RDMA messages %llu pieces %llu work-requests %llu\n", m, pc, w);
   }
   if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes.load());
+  if (do_flush && !is_send) printf("FLUSHES %d\n", flushes.load());
   if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);
   for (int c = 0; c < nch; ++c) {
     if (is_send) api.closeSend(comms[c]);

@@ -821,12 +821,18 @@ ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags
   return ncclSuccess;
 }
 
-// Data lands in host memory through the kernel's socket stack: nothing to flush.  (The reference's flush
-// is a 1-byte RDMA read that it disables by default, src/plugin.cc:887,1768-1799.)
+// TCP: data lands in host memory through the kernel's socket stack, nothing to flush.  RDMA into device memory:
+// a one-byte read through the NIC when NCCL_GDR_FLUSH_DISABLE=0 (the reference ships with it set to 1,
+// src/plugin.cc:887,1768-1799, and so does this plugin).
 ncclResult_t fl_iflush(void* recv_comm, int n, void** data, int* sizes, void** mhandles, void** request) {
-  (void)recv_comm; (void)n; (void)data; (void)sizes; (void)mhandles;
   *request = nullptr;
-  return ncclSuccess;
+  if (!g_rdma || n < 1) return ncclSuccess;
+  MemHandle* m = reinterpret_cast<MemHandle*>(mhandles[0]);
+  if (!m || m->type != NCCL_PTR_CUDA) return ncclSuccess;
+  RdmaRequest* rr = nullptr;
+  ncclResult_t e = rdma_iflush(reinterpret_cast<RdmaComm*>(recv_comm), g_cm, data[0], sizes[0], m->rdma, &rr);
+  *request = rr;
+  return e;
 }
 
 ncclResult_t fl_test(void* request, int* done, int* sizes) {

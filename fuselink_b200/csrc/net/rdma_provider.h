@@ -55,7 +55,7 @@ struct Mr {
   void* impl = nullptr;
 };
 
-enum Opcode : uint8_t { kWrite = 0, kWriteImm = 1 };
+enum Opcode : uint8_t { kWrite = 0, kWriteImm = 1, kRead = 2 };   // kRead: laddr receives len bytes from raddr
 
 struct SendWr {
   uint64_t wr_id = 0;

@@ -21,6 +21,7 @@ constexpr uint64_t kHelloMagic = 0x464c4e4b48454c4full;   // same hello as the T
 constexpr uint32_t kInfoMagic = 0x464c5244u;              // "FLRD"
 constexpr uint64_t kWrFifo = 1ull << 62;                   // wr_id of a signalled descriptor write
 constexpr uint64_t kWrRecv = 1ull << 61;                   // wr_id of the anonymous zero-length receives
+constexpr uint64_t kWrFlush = 1ull << 60;                  // wr_id of a flush read (low bits: request slot)
 
 rdma::Provider* g_prov = nullptr;
 rdma::Pd* g_pd[kMaxDev];
@@ -142,6 +143,9 @@ void poll_all(RdmaComm* c, ConnManager* cm) {
           r.last_progress_ns = now_ns();
         } else if (wc[i].wr_id & kWrFifo) {
           // a signalled descriptor write: nothing to do but to have reaped the send queue
+        } else if (wc[i].wr_id & kWrFlush) {
+          RdmaRequest& r = c->reqs[wc[i].wr_id & 0xffffu];
+          if (r.used && r.is_flush) r.pieces_done = r.pieces_total = 1;
         } else {
           const uint32_t slot = (uint32_t)(wc[i].wr_id & 0xffffu);
           const uint32_t piece = (uint32_t)((wc[i].wr_id >> 16) & 0xffffu);
@@ -396,6 +400,19 @@ ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out) {
             for (int k = 0; k < kMaxRequests && ok; ++k) ok = g_prov->post_recv(c->dev[d].qp[q], kWrRecv) == 0;
       }
       ok = ok && connect_endpoints(c);
+      if (ok && !params().gdr_flush_disable) {
+        rdma::QpCaps fc;
+        fc.max_send_wr = kMaxRequests;
+        fc.max_recv_wr = 1;
+        c->flush_qp = g_prov->create_qp(g_pd[c->ctrl_dev], c->dev[c->ctrl_dev].cq, fc);
+        c->flush_buf = reinterpret_cast<uint8_t*>(alloc_zeroed(64));
+        rdma::QpInfo self;
+        rdma::QpConnectParams qp;
+        ok = c->flush_qp && c->flush_buf && g_prov->query_qp_info(c->flush_qp, (int)params().ib_gid_index, &self) == 0 &&
+             g_prov->connect_qp(c->flush_qp, self, qp) == 0;
+        if (ok) c->flush_mr = rdma_reg(c->flush_buf, 64);
+        ok = ok && c->flush_mr;
+      }
       if (!ok) { drop("cannot set up queue pairs"); continue; }
       c->remote_fifo_addr = c->theirs.fifo_addr;
       memcpy(c->remote_fifo_rkey, c->theirs.fifo_rkey, sizeof c->remote_fifo_rkey);
@@ -577,6 +594,34 @@ ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int 
   return ncclSuccess;
 }
 
+ncclResult_t rdma_iflush(RdmaComm* c, ConnManager* cm, void* data, int size, RdmaMrSet* mr, RdmaRequest** out) {
+  *out = nullptr;
+  if (!c->flush_qp || size <= 0 || !mr) return ncclSuccess;
+  if (c->error) return (ncclResult_t)c->error;
+  RdmaRequest* r = get_request(c);
+  if (!r) return ncclInternalError;
+  r->is_flush = true;
+  r->is_send = true;                       // nothing of the receive bookkeeping applies
+  r->size = 0;
+  rdma::SendWr wr;
+  wr.wr_id = kWrFlush | r->slot;
+  wr.op = rdma::kRead;
+  wr.laddr = c->flush_buf;
+  wr.len = 1;
+  wr.lkey = c->flush_mr->mr[c->ctrl_dev]->lkey;
+  wr.raddr = (uint64_t)(uintptr_t)data;
+  wr.rkey = mr->mr[c->ctrl_dev]->rkey;
+  wr.signaled = true;
+  if (g_prov->post_send(c->flush_qp, &wr, 1) != 0) {
+    r->used = false;
+    fail(c, ncclSystemError, "flush read failed");
+    return ncclSystemError;
+  }
+  poll_all(c, cm);
+  *out = r;
+  return ncclSuccess;
+}
+
 ncclResult_t rdma_test(RdmaRequest* r, ConnManager* cm, int* done, int* size) {
   RdmaComm* c = r->comm;
   *done = 0;
@@ -612,11 +657,14 @@ ncclResult_t rdma_test(RdmaRequest* r, ConnManager* cm, int* done, int* size) {
 
 void rdma_close(RdmaComm* c) {
   if (!c) return;
+  if (c->flush_qp) g_prov->destroy_qp(c->flush_qp);      // queue pairs go before the completion queue they use
   for (int d = 0; d < kMaxDev; ++d) {
     for (int q = 0; q < kRdmaMaxQps; ++q)
       if (c->dev[d].qp[q]) g_prov->destroy_qp(c->dev[d].qp[q]);
     if (c->dev[d].cq) g_prov->destroy_cq(c->dev[d].cq);
   }
+  rdma_dereg(c->flush_mr);
+  free(c->flush_buf);
   rdma_dereg(c->fifo_mr);
   rdma_dereg(c->done_src_mr);
   rdma_dereg(c->done_mr);

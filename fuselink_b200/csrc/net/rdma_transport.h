@@ -75,7 +75,7 @@ struct RdmaPiece {
 
 struct RdmaComm;
 struct RdmaRequest {
-  bool used = false, is_send = false;
+  bool used = false, is_send = false, is_flush = false;
   RdmaComm* comm = nullptr;
   uint32_t slot = 0;
   uint64_t size = 0;
@@ -117,6 +117,11 @@ struct RdmaComm {
   uint32_t remote_fifo_rkey[kMaxDev];
   uint64_t fifo_tail = 0;
   int ctrl_dev = 0;                       // device whose queue pair carries the descriptor writes
+  // flush of device memory after a receive (NCCL_GDR_FLUSH_DISABLE=0): a queue pair connected to itself reads one
+  // byte of the buffer back through the NIC, which orders the NIC's earlier writes before it (src/plugin.cc:1768-1799)
+  rdma::Qp* flush_qp = nullptr;
+  uint8_t* flush_buf = nullptr;
+  RdmaMrSet* flush_mr = nullptr;
   // selection state (same meaning as in the TCP transport)
   int cur_dev = -1, n_finished = 0, posted = 0, completed = 0;
   uint64_t peer_tx_mask = ~0ull, msg_index = 0;
@@ -144,6 +149,7 @@ RdmaMrSet* rdma_reg(void* data, size_t size);
 void rdma_dereg(RdmaMrSet* m);
 ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out);
 ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out);
+ncclResult_t rdma_iflush(RdmaComm* c, ConnManager* cm, void* data, int size, RdmaMrSet* mr, RdmaRequest** out);   // *out null: nothing to do
 ncclResult_t rdma_test(RdmaRequest* r, ConnManager* cm, int* done, int* size);
 void rdma_close(RdmaComm* c);
 void rdma_close_listen(RdmaListenComm* lc);

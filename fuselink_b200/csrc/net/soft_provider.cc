@@ -72,6 +72,7 @@ struct Inflight {
   uint64_t wr_id;
   bool signaled;
   uint32_t len;
+  uint8_t* read_dst;               // RDMA read: where the returned bytes go (null for writes)
 };
 
 struct SoftMr {
@@ -104,6 +105,8 @@ struct QpImpl {
   std::deque<uint64_t> rq;          // posted zero-length receives
   WireAck ack_rx;
   size_t ack_got = 0;
+  uint32_t read_left = 0;           // bytes of a read response still to arrive behind its ACK
+  uint32_t read_got = 0;
   QpCaps caps;
 };
 
@@ -259,12 +262,18 @@ class SoftProvider : public Provider {
       OutMsg m;
       m.hdr = WireHdr{kWireMagic, (uint32_t)w.op, w.len, w.rkey, w.raddr, w.imm, 0};
       m.payload = reinterpret_cast<const uint8_t*>(w.laddr);
-      if (w.inline_data && w.len) {
+      uint8_t* read_dst = nullptr;
+      if (w.op == kRead) {                         // the request carries no payload; the response does
+        read_dst = const_cast<uint8_t*>(m.payload);
+        m.payload = nullptr;
+        m.hdr.pad = w.len;                         // bytes wanted
+        m.hdr.len = 0;
+      } else if (w.inline_data && w.len) {
         m.copy.assign(m.payload, m.payload + w.len);
         m.payload = nullptr;
       }
       q->sendq.push_back(std::move(m));
-      q->inflight.push_back(Inflight{w.wr_id, w.signaled, w.len});
+      q->inflight.push_back(Inflight{w.wr_id, w.signaled, w.len, read_dst});
     }
     progress_locked();
     return 0;
@@ -347,7 +356,20 @@ class SoftProvider : public Provider {
       }
       q->sendq.pop_front();
     }
-    for (;;) {          // acknowledgements
+    for (;;) {          // acknowledgements (a read's ACK is followed by the bytes it asked for)
+      if (q->read_left) {
+        const size_t want = q->read_left < sizeof bounce_ ? q->read_left : sizeof bounce_;
+        ssize_t r = recv(q->out_fd, bounce_, want, MSG_DONTWAIT);
+        if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) break;
+        if (r <= 0) { fail_qp(q, kWcRetryExceeded); return; }
+        Inflight& f = q->inflight.front();
+        dma_place(f.read_dst + q->read_got, bounce_, (size_t)r);
+        q->read_got += (uint32_t)r;
+        q->read_left -= (uint32_t)r;
+        if (q->read_left) continue;
+        complete_head(q);
+        continue;
+      }
       ssize_t r = recv(q->out_fd, reinterpret_cast<uint8_t*>(&q->ack_rx) + q->ack_got, sizeof(WireAck) - q->ack_got, MSG_DONTWAIT);
       if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) break;
       if (r <= 0) {
@@ -360,15 +382,23 @@ class SoftProvider : public Provider {
       q->ack_got = 0;
       if (q->ack_rx.magic != kWireMagic || q->inflight.empty()) { fail_qp(q, kWcGeneral); return; }
       if (q->ack_rx.kind == kNak) { fail_qp(q, kWcRemoteAccess); return; }
-      Inflight f = q->inflight.front();
-      q->inflight.pop_front();
-      if (f.signaled) {
-        Completion c;
-        c.wr_id = f.wr_id;
-        c.byte_len = f.len;
-        c.qpn = q->qpn;
-        q->cq->done.push_back(c);
+      if (q->inflight.front().read_dst && q->inflight.front().len) {
+        q->read_left = q->inflight.front().len;
+        q->read_got = 0;
+        continue;
       }
+      complete_head(q);
+    }
+  }
+  void complete_head(QpImpl* q) {
+    Inflight f = q->inflight.front();
+    q->inflight.pop_front();
+    if (f.signaled) {
+      Completion c;
+      c.wr_id = f.wr_id;
+      c.byte_len = f.len;
+      c.qpn = q->qpn;
+      q->cq->done.push_back(c);
     }
   }
 
@@ -415,6 +445,21 @@ class SoftProvider : public Provider {
         if (in.hdr.magic != kWireMagic) return false;
         in.bad = false;
         in.dst = nullptr;
+        if (in.hdr.op == (uint32_t)kRead) {        // answer: ACK + the bytes, or NAK
+          const uint32_t want = in.hdr.pad;
+          auto it = mrs_.find(in.hdr.rkey);
+          const uint8_t* a = reinterpret_cast<const uint8_t*>(in.hdr.raddr);
+          if (it == mrs_.end() || !(it->second.access & kAccessRemoteRead) || a < it->second.addr || a + want > it->second.addr + it->second.len) {
+            queue_ack(in, kNak);
+          } else {
+            queue_ack(in, kAck);
+            const size_t at = in.ack_tx.size();
+            in.ack_tx.resize(at + want);
+            dma_fetch(in.ack_tx.data() + at, a, want);
+          }
+          flush_acks(in);
+          continue;
+        }
         if (in.hdr.len) {
           auto it = mrs_.find(in.hdr.rkey);
           uint8_t* a = reinterpret_cast<uint8_t*>(in.hdr.raddr);
@@ -464,6 +509,12 @@ class SoftProvider : public Provider {
       __builtin_memcpy(&last, src + body, 8);
       __atomic_store_n(reinterpret_cast<uint64_t*>(dst + body), last, __ATOMIC_RELEASE);
     }
+  }
+
+  // the NIC reading application memory (the other direction of dma_place)
+  __attribute__((no_sanitize("thread"))) static void dma_fetch(uint8_t* dst, const uint8_t* src, size_t n) {
+    const volatile uint8_t* s = src;
+    for (size_t i = 0; i < n; ++i) dst[i] = s[i];
   }
 
   void finish_imm(Inbound& in) {

@@ -34,7 +34,7 @@ struct ibv_qp {
 
 struct ibv_sge { uint64_t addr; uint32_t length; uint32_t lkey; };
 
-enum { IBV_WR_RDMA_WRITE = 0, IBV_WR_RDMA_WRITE_WITH_IMM = 1 };
+enum { IBV_WR_RDMA_WRITE = 0, IBV_WR_RDMA_WRITE_WITH_IMM = 1, IBV_WR_RDMA_READ = 4 };
 enum { IBV_SEND_SIGNALED = 2, IBV_SEND_INLINE = 8 };
 
 struct ibv_send_wr {

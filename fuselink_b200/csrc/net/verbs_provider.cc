@@ -242,7 +242,7 @@ class VerbsProvider : public Provider {
       w[i].next = i + 1 < n ? &w[i + 1] : nullptr;
       w[i].sg_list = wrs[i].len ? &sge[i] : nullptr;
       w[i].num_sge = wrs[i].len ? 1 : 0;
-      w[i].opcode = wrs[i].op == kWriteImm ? IBV_WR_RDMA_WRITE_WITH_IMM : IBV_WR_RDMA_WRITE;
+      w[i].opcode = wrs[i].op == kWriteImm ? IBV_WR_RDMA_WRITE_WITH_IMM : wrs[i].op == kRead ? IBV_WR_RDMA_READ : IBV_WR_RDMA_WRITE;
       w[i].send_flags = (wrs[i].signaled ? IBV_SEND_SIGNALED : 0) | (wrs[i].inline_data ? IBV_SEND_INLINE : 0);
       w[i].imm_data = wrs[i].imm;
       w[i].wr.rdma.remote_addr = wrs[i].raddr;

@@ -121,3 +121,15 @@ def test_properties_come_from_the_provider():
     out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, **SOFT), capture_output=True, text=True, timeout=60)
     assert out.returncode == 0, out.stderr
     assert out.stdout.split() == ["4", "softnic_1"]
+
+
+def test_flush_reads_device_memory_back_through_the_nic():
+    """NCCL_GDR_FLUSH_DISABLE=0: iflush on a device buffer posts a one-byte RDMA read on a queue pair connected to itself
+    and completes through test(); with the default (disabled, as the reference sets it) iflush returns no request."""
+    base = dict(SOFT, FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS="2")
+    tx, rx = _pair([1 << 20, 4097], env=dict(base, NCCL_GDR_FLUSH_DISABLE="0"), common=["--device-buffers", "--chunk", "262144"], extra_recv=["--flush"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "FLUSHES 2" in rx[1]
+    tx, rx = _pair([1 << 20], env=base, common=["--device-buffers", "--chunk", "262144"], extra_recv=["--flush"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "FLUSHES 0" in rx[1]
