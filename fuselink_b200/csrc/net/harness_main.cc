@@ -298,6 +298,8 @@ int main(int argc, char** argv) {
     rdma_ctr(&m, &pc, &w);
     if (m) printf("RDMA messages %llu pieces %llu work-requests %llu\n", m, pc, w);
   }
+  auto failovers = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_failovers");
+  if (failovers && is_send && failovers()) printf("FAILOVERS %llu\n", failovers());
   if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes.load());
   if (do_flush && !is_send) printf("FLUSHES %d\n", flushes.load());
   if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);

@@ -660,7 +660,8 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
   r->tag = tag;
   if (direct_dst && fl_vmm_memcpy(direct_dst, data, (size_t)size) == 0) {
     // the payload is in place: one header-only frame on the proposed device tells the receiver
-    const int dev0 = g_cm->bid_tx(c->channel_id, c->own_dev, d.proposed_dev) % c->ndev;
+    int dev0 = next_alive_dev(c, g_cm->bid_tx(c->channel_id, c->own_dev, d.proposed_dev) % c->ndev);
+    if (dev0 < 0) dev0 = 0;
     Stripe st;
     st.dev = dev0;
     st.hdr.magic = kFrameDirectMagic;
@@ -701,6 +702,13 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
   uint64_t off = 0;
   int dev = first;
   for (int s = 0; s < nstripes; ++s) {
+    dev = next_alive_dev(c, dev);                     // a device whose socket broke earlier is skipped
+    if (dev < 0) {
+      r->used = false;
+      c->error = ncclRemoteError;
+      FL_WARN("isend: every data connection of channel %d is gone", c->channel_id);
+      return ncclRemoteError;
+    }
     Stripe st;
     st.dev = dev;
     st.hdr.magic = kFrameMagic;
@@ -930,6 +938,8 @@ __attribute__((visibility("default"))) ncclNet_v6_t ncclNetPlugin_v6 = {
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_decisions(void) { return g_cm ? g_cm->decisions() : 0; }
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_fallbacks(void) { return g_cm ? g_cm->fallbacks() : 0; }
 __attribute__((visibility("default"))) void* fuselink_plugin_monitor(void) { return g_cm ? g_cm->monitor() : nullptr; }
+// Stripes that were re-sent on another device after a data socket broke.
+__attribute__((visibility("default"))) unsigned long long fuselink_plugin_failovers(void) { return flnet::failover_count(); }
 // Payload bytes / messages this process stored straight into a same-host peer's exported receive buffer.
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_bytes(void) { return g_direct_bytes.load(); }
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_msgs(void) { return g_direct_msgs.load(); }

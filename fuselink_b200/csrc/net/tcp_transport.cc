@@ -11,6 +11,9 @@
 #include <sys/socket.h>
 #include <unistd.h>
 
+#include <algorithm>
+#include <atomic>
+
 #include "params.h"
 #include "../mem/vmm.h"
 
@@ -123,6 +126,49 @@ static void fail(Comm* c, ncclResult_t why, const char* what) {
   }
 }
 
+static std::atomic<uint64_t> g_failovers{0};
+uint64_t failover_count() { return g_failovers.load(); }
+
+int next_alive_dev(const Comm* c, int from) {
+  for (int i = 0; i < c->ndev; ++i) {
+    const int d = (from + i) % c->ndev;
+    if (c->data[d].fd >= 0) return d;
+  }
+  return -1;
+}
+
+// Recovery from a broken data socket (sender side): the device is marked dead for the selector, and every stripe
+// queued on it -- the one in flight from its first byte, since the receiver discards a partial stripe -- moves to the
+// next device that is still connected.  What the kernel had already accepted for the broken socket is not known to be
+// delivered; a stripe that was counted as sent and then lost shows up as the receiver's request timing out.
+static bool failover_tx(Comm* c, ConnManager* cm, int d, const char* why) {
+  DataSock& s = c->data[d];
+  if (s.fd >= 0) {
+    shutdown(s.fd, SHUT_RDWR);
+    close(s.fd);
+    s.fd = -1;
+  }
+  cm->set_dead(d, true);
+  const int to = params().failover ? next_alive_dev(c, d + 1) : -1;
+  if (to < 0) return false;
+  size_t moved = 0;
+  while (!s.txq.empty()) {
+    Request* rq = s.txq.front().first;
+    const int si = s.txq.front().second;
+    Stripe& st = rq->stripes[si];
+    rq->moved -= st.sent;
+    st.sent = 0;
+    st.hdr_sent = 0;
+    st.dev = to;
+    c->data[to].txq.emplace_back(rq, si);
+    s.txq.pop_front();
+    ++moved;
+  }
+  g_failovers.fetch_add(moved, std::memory_order_relaxed);
+  FL_WARN("send comm (channel %d): device %d lost (%s); %zu stripe(s) continue on device %d", c->channel_id, d, why, moved, to);
+  return true;
+}
+
 // ---- sender ----------------------------------------------------------------------------------------
 static void sender_read_descs(Comm* c) {
   for (;;) {
@@ -150,29 +196,35 @@ static void sender_push(Comm* c, ConnManager* cm) {
   const int64_t fault_after = params().fault_drop_after;
   for (int d = 0; d < c->ndev; ++d) {
     DataSock& s = c->data[d];
+    if (s.fd < 0) continue;
     while (!s.txq.empty()) {
       Request* rq = s.txq.front().first;
       Stripe& st = rq->stripes[s.txq.front().second];
       if (st.hdr_sent < sizeof(FrameHdr)) {
         ssize_t r = nb_send(s.fd, reinterpret_cast<uint8_t*>(&st.hdr) + st.hdr_sent, sizeof(FrameHdr) - st.hdr_sent);
-        if (r < 0) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }
+        if (r < 0) {
+          if (!failover_tx(c, cm, d, "send failed")) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }
+          break;
+        }
         if (r == 0) break;
         st.hdr_sent += (size_t)r;
         if (st.hdr_sent < sizeof(FrameHdr)) break;
       }
       if (st.sent < st.hdr.len) {
         size_t want = st.hdr.len - st.sent;
-        if (fault_after > 0 && s.tx_bytes + want > (uint64_t)fault_after) {
+        if (fault_after > 0 && !c->fault_fired && s.tx_bytes + want > (uint64_t)fault_after) {
           // test hook: the link "breaks" in the middle of a stripe
           size_t allowed = (uint64_t)fault_after > s.tx_bytes ? (size_t)(fault_after - s.tx_bytes) : 0;
           if (allowed) nb_send(s.fd, rq->data + st.hdr.offset + st.sent, allowed);
-          shutdown(s.fd, SHUT_RDWR);
-          cm->set_dead(d, true);
-          fail(c, ncclSystemError, "injected link failure");
-          return;
+          c->fault_fired = true;
+          if (!failover_tx(c, cm, d, "injected link failure")) { fail(c, ncclSystemError, "injected link failure"); return; }
+          break;
         }
         ssize_t r = nb_send(s.fd, rq->data + st.hdr.offset + st.sent, want);
-        if (r < 0) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }
+        if (r < 0) {
+          if (!failover_tx(c, cm, d, "send failed")) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }
+          break;
+        }
         if (r == 0) break;
         st.sent += (size_t)r;
         s.tx_bytes += (uint64_t)r;
@@ -198,16 +250,44 @@ static void receiver_flush_ctrl(Comm* c) {
   }
 }
 
+// A stripe counts when its last byte is in, and once: after a failover the sender may repeat one that had arrived.
+static void stripe_arrived(Request& rq, uint64_t offset, uint64_t len) {
+  if (std::find(rq.got_offsets.begin(), rq.got_offsets.end(), offset) == rq.got_offsets.end()) {
+    rq.got_offsets.push_back(offset);
+    rq.moved += len;
+  }
+  if (rq.moved == rq.total) rq.done = true;
+}
+
+// Receiver side of the recovery: the broken socket is closed, its half-received stripe forgotten, and the connection
+// lives on as long as another data socket does.
+static bool failover_rx(Comm* c, ConnManager* cm, int d) {
+  DataSock& s = c->data[d];
+  close(s.fd);
+  s.fd = -1;
+  s.rx_in_payload = false;
+  s.rx_hdr_got = 0;
+  s.rx_payload_got = 0;
+  cm->set_dead(d, true);
+  if (!params().failover || next_alive_dev(c, d + 1) < 0) return false;
+  FL_WARN("recv comm (channel %d): device %d lost; waiting for its stripes on the other devices", c->channel_id, d);
+  return true;
+}
+
 static void receiver_pull(Comm* c, ConnManager* cm) {
   for (int d = 0; d < c->ndev; ++d) {
     DataSock& s = c->data[d];
+    if (s.fd < 0) continue;
     for (;;) {
       if (!s.rx_in_payload) {
         ssize_t r = nb_recv(s.fd, reinterpret_cast<uint8_t*>(&s.rx_hdr) + s.rx_hdr_got, sizeof(FrameHdr) - s.rx_hdr_got);
         if (r < 0) {
           bool waiting = false;
           for (auto& rq : c->reqs) if (rq.used && !rq.done) waiting = true;
-          if (waiting) { cm->set_dead(d, true); fail(c, ncclRemoteError, "data connection closed by the sender"); }
+          if (!waiting) return;                       // the sender is done with this connection
+          if (failover_rx(c, cm, d)) break;
+          cm->set_dead(d, true);
+          fail(c, ncclRemoteError, "data connection closed by the sender");
           return;
         }
         if (r == 0) break;
@@ -236,20 +316,28 @@ static void receiver_pull(Comm* c, ConnManager* cm) {
         }
         s.rx_in_payload = true;
         s.rx_payload_got = 0;
-        if (s.rx_hdr.len == 0) s.rx_in_payload = false;
-        if (rq.total == 0) rq.done = true;
+        if (s.rx_hdr.len == 0) {
+          s.rx_in_payload = false;
+          stripe_arrived(rq, s.rx_hdr.offset, 0);
+        }
       }
       if (s.rx_in_payload) {
         Request& rq = c->reqs[s.rx_hdr.slot];
         ssize_t r = nb_recv(s.fd, rq.data + s.rx_hdr.offset + s.rx_payload_got, s.rx_hdr.len - s.rx_payload_got);
-        if (r < 0) { cm->set_dead(d, true); fail(c, ncclRemoteError, "data connection closed in the middle of a message"); return; }
+        if (r < 0) {
+          if (failover_rx(c, cm, d)) break;           // the partial stripe is dropped; the sender sends it again elsewhere
+          cm->set_dead(d, true);
+          fail(c, ncclRemoteError, "data connection closed in the middle of a message");
+          return;
+        }
         if (r == 0) break;
         s.rx_payload_got += (uint64_t)r;
-        rq.moved += (uint64_t)r;
         rq.last_progress_ns = now_ns();
         cm->done_rx(d, (uint64_t)r);
-        if (s.rx_payload_got == s.rx_hdr.len) s.rx_in_payload = false;
-        if (rq.moved == rq.total) rq.done = true;
+        if (s.rx_payload_got == s.rx_hdr.len) {
+          s.rx_in_payload = false;
+          stripe_arrived(rq, s.rx_hdr.offset, s.rx_hdr.len);
+        }
       }
     }
   }

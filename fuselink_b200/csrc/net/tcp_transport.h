@@ -102,6 +102,7 @@ struct Request {
   std::vector<uint8_t> stage;            // host bounce buffer when the user buffer is device memory
   uint8_t* user = nullptr;               // device address the staged bytes belong to (null: no staging)
   bool direct = false;                   // recv: the sender wrote the bytes straight into the exported buffer
+  std::vector<uint64_t> got_offsets;     // recv: offsets of the stripes that arrived completely (a re-sent stripe counts once)
   size_t stripes_done = 0;
 };
 
@@ -128,6 +129,7 @@ struct Comm {
   DataSock data[kMaxDev];
   Request reqs[kMaxRequests];
   int error = 0;                         // sticky ncclResult_t
+  bool fault_fired = false;              // test hook: the injected link failure happens once per connection
   // control stream
   std::vector<uint8_t> ctrl_tx;          // receiver: descriptors not yet written
   uint8_t ctrl_rx[sizeof(RecvDesc)];
@@ -175,6 +177,8 @@ struct ListenComm {
 int set_nonblock_nodelay(int fd);
 int pick_listen_addr(sockaddr_in6* out);           // honours NCCL_SOCKET_IFNAME / NCCL_SOCKET_FAMILY
 ncclResult_t comm_progress(Comm* c, ConnManager* cm);
+int next_alive_dev(const Comm* c, int from);       // first device >= from (cyclic) whose data socket is open, -1 if none
+uint64_t failover_count();                          // stripes moved to another device after a socket failure (process-wide)
 void comm_close(Comm* c);
 
 }  // namespace flnet

@@ -83,8 +83,19 @@ def test_sender_death_is_reported_not_hung():
     assert rx[0] == 0 and "EXPECTED-ERROR" in rx[1], rx
 
 
+def test_link_failure_is_survived_by_moving_stripes_to_another_device():
+    """A data socket breaks in the middle of a stripe: the sender marks the device dead and sends the stripe again, from
+    its first byte, on the next device; the receiver drops the half stripe and the transfer completes bit for bit."""
+    env = {"FUSELINK_FAULT_CLOSE_AFTER_BYTES": str(3 << 20), "FUSELINK_TCP_NDEV": "4", "NCCL_FUSELINK_DEGREE": "2",
+           "FUSELINK_MIN_STRIPE_BYTES": "65536", "FUSELINK_NET_TIMEOUT_MS": "5000"}
+    tx, rx = _pair([16 << 20, 4 << 20, 5], env=env, common=["--chunk", "524288", "--inflight", "8"], timeout=90)
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "FAILOVERS" in tx[1] and "lost (injected link failure)" in tx[2], tx
+
+
 def test_injected_link_failure_marks_path_dead():
-    tx, rx = _pair([16 << 20], extra_recv=["--expect-error"], env={"FUSELINK_FAULT_CLOSE_AFTER_BYTES": str(3 << 20), "FUSELINK_NET_TIMEOUT_MS": "3000"}, timeout=60)
+    tx, rx = _pair([16 << 20], extra_recv=["--expect-error"], env={"FUSELINK_FAULT_CLOSE_AFTER_BYTES": str(3 << 20), "FUSELINK_NET_TIMEOUT_MS": "3000",
+                                                                   "FUSELINK_FAILOVER": "0"}, timeout=60)
     assert tx[0] != 0            # the sender reports the broken link
     assert rx[0] == 0 and "EXPECTED-ERROR" in rx[1], rx
 
