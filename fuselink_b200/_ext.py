@@ -10,6 +10,7 @@ import importlib
 C = None
 _import_error = None
 try:  # pragma: no cover - depends on the build
+    import torch  # noqa: F401 - the extension links libtorch: PyTorch has to be initialised before it is loaded
     C = importlib.import_module("fuselink_b200._C")
 except Exception as e:  # noqa: BLE001
     _import_error = e

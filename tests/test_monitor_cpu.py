@@ -198,3 +198,27 @@ def test_daemon_binary_creates_and_removes_table():
     assert C.monitor_status(m, TX, 0) == IDLE                     # the daemon's sweeper expired it
     C.monitor_close(m, False)
     assert p.wait(timeout=10) == 0
+
+
+def test_metrics_endpoint_serves_the_table():
+    """The Prometheus endpoint reads the same table the selector writes: state, outstanding bytes and decisions."""
+    import urllib.request
+    from fuselink_b200.utils.metrics import MetricsServer, render
+    m = C.monitor_open("", True, 4, 1, 160)
+    t = C.monitor_now_ns()
+    C.monitor_post_bytes(m, TX, 2, 12345, t)
+    C.monitor_mark_dead(m, RX, 1, True)
+    text = render(C, m, {"failovers": 3})
+    assert 'fuselink_path_outstanding_bytes{dir="tx",path="2"} 12345' in text
+    assert f'fuselink_path_state{{dir="rx",path="1"}} {DEAD}' in text
+    assert f'fuselink_path_state{{dir="tx",path="2"}} {BUSY}' in text
+    assert "fuselink_failovers 3" in text
+    srv = MetricsServer(C, m, port=0)
+    try:
+        body = urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/metrics", timeout=10).read().decode()
+        assert 'fuselink_path_outstanding_bytes{dir="tx",path="2"} 12345' in body and "fuselink_borrow_decisions_total" in body
+        with pytest.raises(Exception):
+            urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/nope", timeout=10)
+    finally:
+        srv.close()
+        C.monitor_close(m, False)
