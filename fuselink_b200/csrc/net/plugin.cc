@@ -367,8 +367,27 @@ ncclResult_t fl_connect_impl(int dev, void* opaque, void** send_comm) {
     int err = 0;
     socklen_t el = sizeof err;
     getsockopt(fd, SOL_SOCKET, SO_ERROR, &err, &el);
+    if ((err == ECONNREFUSED || err == ETIMEDOUT) && c->connect_retries < params().connect_retries) {
+      // the listener may not be up yet (or its backlog is full): try again a little later, within a budget
+      c->connect_retries++;
+      close(fd);
+      usleep(1000);
+      int nfd = socket(AF_INET6, SOCK_STREAM, 0);
+      if (nfd >= 0) {
+        set_nonblock_nodelay(nfd);
+        int rc2 = connect(nfd, reinterpret_cast<sockaddr*>(&h->addr), sizeof h->addr);
+        if (rc2 != 0 && errno != EINPROGRESS) { close(nfd); nfd = -1; }
+      }
+      if (nfd >= 0) {
+        c->pending_fds[i] = nfd;
+        all = false;
+        continue;
+      }
+      err = errno ? errno : ECONNREFUSED;
+    }
     if (err) {
-      FL_WARN("connect to listener failed: %s", strerror(err));
+      FL_WARN("connect to listener failed after %d retries: %s", c->connect_retries, strerror(err));
+      c->pending_fds[i] = -1;
       h->connect_state = nullptr;
       comm_close(c);
       return ncclSystemError;

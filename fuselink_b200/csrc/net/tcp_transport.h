@@ -146,6 +146,7 @@ struct Comm {
   int connect_stage = 0;
   std::vector<int> pending_fds;
   std::vector<size_t> hello_sent;
+  int connect_retries = 0;               // refused connection attempts so far (all sockets of this connect)
   Timers timers;
   // same-host direct path (cuMem export/import)
   int nvl_fd = -1;                       // Unix side channel, -1 when the peer is on another host or the path is off

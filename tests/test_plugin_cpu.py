@@ -214,3 +214,30 @@ def test_hca_filter_syntax():
     spec = b"=mlx5_0,3,4,5,6,9,10,11"                          # the reference's 8-NIC list
     allowed = [i for i in range(12) if f(spec, f"mlx5_{i}".encode(), 1)]
     assert allowed == [0, 3, 4, 5, 6, 9, 10, 11]
+
+
+def test_refused_connect_is_retried_within_a_budget():
+    """Nothing listens at the address of the handle: the sender retries the refused connection 1 ms apart and gives up
+    after FUSELINK_CONNECT_RETRIES attempts with an error, instead of failing at the first refusal or spinning forever."""
+    import socket
+    import struct
+    import time
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()                                                            # a port nobody listens on
+    v4mapped = b"\x00" * 10 + b"\xff\xff" + socket.inet_aton("127.0.0.1")
+    sockaddr_in6 = struct.pack("<H", socket.AF_INET6) + struct.pack(">H", port) + struct.pack("<I", 0) + v4mapped + struct.pack("<I", 0)
+    handle = struct.pack("<Q", 0x464c4e4b48444c31) + sockaddr_in6 + struct.pack("<iiii", 0, 4, 0, 0)
+    handle = handle.ljust(56, b"\x00") + struct.pack("<QQ", 0, 0)
+    handle = handle.ljust(128, b"\x00")
+    with tempfile.TemporaryDirectory() as d:
+        hf = os.path.join(d, "handle")
+        open(hf, "wb").write(handle)
+        e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", FUSELINK_CONNECT_RETRIES="150")
+        t0 = time.time()
+        tx = subprocess.run([HARNESS, PLUGIN, "send", hf, "4096"], env=e, capture_output=True, text=True, timeout=60)
+        dt = time.time() - t0
+    assert tx.returncode == 2 and "connect failed" in tx.stderr
+    assert "after 150 retries" in tx.stderr, tx.stderr
+    assert 0.15 <= dt < 30
