@@ -27,7 +27,7 @@ rdma::Provider* g_prov = nullptr;
 rdma::Pd* g_pd[kMaxDev];
 int g_ndev = 0;
 std::atomic<uint64_t> g_uid{1};
-std::atomic<uint64_t> g_pieces{0}, g_work_requests{0}, g_messages{0};
+std::atomic<uint64_t> g_pieces{0}, g_work_requests{0}, g_messages{0}, g_failovers{0};
 
 int access_flags() {
   int f = rdma::kAccessLocalWrite | rdma::kAccessRemoteWrite | rdma::kAccessRemoteRead;
@@ -114,6 +114,117 @@ RdmaRequest* get_request(RdmaComm* c) {
   return nullptr;
 }
 
+int rdma_next_alive(const RdmaComm* c, int from) {
+  for (int i = 0; i < c->ndev; ++i) {
+    const int d = ((from % c->ndev) + c->ndev + i) % c->ndev;
+    if (!c->dead[d]) return d;
+  }
+  return -1;
+}
+
+// Posts piece `pi` of send request `r` on the device / queue pair recorded in the piece.
+bool post_piece(RdmaComm* c, RdmaRequest* r, int pi) {
+  const Params& p = params();
+  RdmaPiece& pc = r->pieces[pi];
+  const RdmaDesc& d = r->desc;
+  const int dev = pc.dev;
+  const int npieces = (int)r->pieces.size();
+  const uint32_t imm = (d.slot & 0xffu) | ((uint32_t)npieces << 8) | ((uint32_t)pi << 16);
+  rdma::SendWr wr[3];
+  int n = 0;
+  if (pi == 0) {                            // the record for the slot travels ahead of the first immediate
+    wr[n].wr_id = 0;
+    wr[n].op = rdma::kWrite;
+    wr[n].laddr = &c->done_src[d.slot % kMaxRequests];
+    wr[n].len = sizeof(RdmaDoneRec);
+    wr[n].lkey = c->done_src_mr->mr[dev]->lkey;
+    wr[n].raddr = c->remote_done_addr + sizeof(RdmaDoneRec) * (d.slot % kMaxRequests);
+    wr[n].rkey = c->remote_done_rkey[dev];
+    wr[n].inline_data = p.ib_use_inline != 0;
+    ++n;
+  }
+  const uint64_t wr_id = (uint64_t)r->slot | ((uint64_t)pi << 16) | ((uint64_t)pc.gen << 32);
+  const bool split = pc.len > (uint64_t)p.ib_ar_threshold;     // large: data write, then an empty write carrying the immediate
+  if (split) {
+    wr[n].wr_id = wr_id;
+    wr[n].op = rdma::kWrite;
+    wr[n].laddr = r->data + pc.off;
+    wr[n].len = (uint32_t)pc.len;
+    wr[n].lkey = r->mr->mr[dev]->lkey;
+    wr[n].raddr = d.addr + pc.off;
+    wr[n].rkey = d.rkey[dev];
+    ++n;
+  }
+  wr[n].wr_id = wr_id;
+  wr[n].op = rdma::kWriteImm;
+  wr[n].laddr = split || pc.len == 0 ? nullptr : r->data + pc.off;
+  wr[n].len = split ? 0 : (uint32_t)pc.len;
+  wr[n].lkey = r->mr->mr[dev]->lkey;
+  wr[n].raddr = d.addr + pc.off;
+  wr[n].rkey = d.rkey[dev];
+  wr[n].imm = imm;
+  wr[n].signaled = true;
+  ++n;
+  if (r->bad_key)                            // test hook: wrong key on the payload
+    for (int k = pi == 0 ? 1 : 0; k < n; ++k) wr[k].rkey ^= 0x5a5a5a5au;
+  g_pieces.fetch_add(1, std::memory_order_relaxed);
+  g_work_requests.fetch_add((uint64_t)n, std::memory_order_relaxed);
+  return g_prov->post_send(c->dev[dev].qp[pc.q], wr, n) == 0;
+}
+
+bool post_descriptor(RdmaComm* c, uint64_t idx) {
+  RdmaDesc* d = &c->fifo_src[idx % kMaxRequests];
+  rdma::SendWr wr;
+  wr.wr_id = kWrFifo;
+  wr.op = rdma::kWrite;
+  wr.laddr = d;
+  wr.len = sizeof *d;
+  wr.lkey = c->fifo_src_mr->mr[c->ctrl_dev]->lkey;
+  wr.raddr = c->remote_fifo_addr + sizeof(RdmaDesc) * (idx % kMaxRequests);
+  wr.rkey = c->remote_fifo_rkey[c->ctrl_dev];
+  wr.signaled = (idx % kFifoSignalEvery) == kFifoSignalEvery - 1;
+  wr.inline_data = params().ib_use_inline != 0;
+  return g_prov->post_send(c->dev[c->ctrl_dev].qp[0], &wr, 1) == 0;
+}
+
+// A completion came back in error on device d.  Returns false when the connection cannot go on.
+bool device_failed(RdmaComm* c, ConnManager* cm, int d, const rdma::Completion& wc) {
+  if (wc.status == rdma::kWcRemoteAccess || !params().failover) return false;
+  if (wc.wr_id & kWrFlush) return false;
+  const bool first = !c->dead[d];
+  c->dead[d] = true;
+  if (cm) cm->set_dead(d, true);
+  const int to = rdma_next_alive(c, d + 1);
+  if (to < 0) return false;
+  if (first)
+    FL_WARN("rdma %s comm (channel %d): device %d gave completion status %d and is given up; traffic moves to device %d",
+            c->is_send ? "send" : "recv", c->channel_id, d, wc.status, to);
+  if (!c->is_send) {
+    // receiver: the descriptor writes went through this device.  Move them and write the descriptors of every
+    // unfinished receive again (entries the sender has consumed already are behind its head and are ignored).
+    if (!first) return true;
+    if (d == c->ctrl_dev) c->ctrl_dev = to;
+    uint64_t lo = UINT64_MAX;
+    for (auto& r : c->reqs)
+      if (r.used && !r.is_send && !r.is_flush && (r.pieces_total < 0 || r.pieces_done < r.pieces_total) && r.fifo_idx < lo) lo = r.fifo_idx;
+    for (uint64_t idx = lo; lo != UINT64_MAX && idx < c->fifo_tail; ++idx) {
+      if (!post_descriptor(c, idx)) return false;
+      g_failovers.fetch_add(1, std::memory_order_relaxed);
+    }
+    return true;
+  }
+  if ((wc.wr_id & kWrFifo) || wc.wr_id == 0) return true;   // wr_id 0: the unsignalled record write, its piece reports separately
+  const uint32_t slot = (uint32_t)(wc.wr_id & 0xffffu), pi = (uint32_t)((wc.wr_id >> 16) & 0xffffu), gen = (uint32_t)((wc.wr_id >> 32) & 0xffu);
+  RdmaRequest& r = c->reqs[slot % kMaxRequests];
+  if (!r.used || !r.is_send || pi >= r.pieces.size()) return true;
+  RdmaPiece& pc = r.pieces[pi];
+  if (pc.done || pc.gen != gen) return true;               // an older posting of a piece that has moved on
+  pc.gen++;
+  pc.dev = to;
+  g_failovers.fetch_add(1, std::memory_order_relaxed);
+  return post_piece(c, &r, (int)pi);
+}
+
 void poll_all(RdmaComm* c, ConnManager* cm) {
   g_prov->progress();
   rdma::Completion wc[16];
@@ -124,6 +235,7 @@ void poll_all(RdmaComm* c, ConnManager* cm) {
       if (n <= 0) break;
       for (int i = 0; i < n; ++i) {
         if (wc[i].status != rdma::kWcOk) {
+          if (!wc[i].is_recv && device_failed(c, cm, d, wc[i])) continue;
           if (cm && wc[i].status == rdma::kWcRetryExceeded) cm->set_dead(d, true);
           char msg[96];
           snprintf(msg, sizeof msg, "completion with status %d on device %d", wc[i].status, d);
@@ -136,10 +248,14 @@ void poll_all(RdmaComm* c, ConnManager* cm) {
             if (c->dev[d].qp[q] && c->mine.qp[d][q].qpn == wc[i].qpn) g_prov->post_recv(c->dev[d].qp[q], kWrRecv);
           const uint32_t slot = wc[i].imm & 0xffu;
           const int npieces = (int)((wc[i].imm >> 8) & 0xffu);
+          const int pi = (int)((wc[i].imm >> 16) & 0xffu);
           RdmaRequest& r = c->reqs[slot];
-          if (!r.used || r.is_send || npieces < 1) { fail(c, ncclInternalError, "immediate for a slot that is not posted"); continue; }
+          if (!r.used || r.is_send || npieces < 1 || npieces > 64 || pi >= npieces) { fail(c, ncclInternalError, "immediate for a slot that is not posted"); continue; }
           r.pieces_total = npieces;
-          r.pieces_done++;
+          if (!((r.piece_mask >> pi) & 1ull)) {
+            r.piece_mask |= 1ull << pi;
+            r.pieces_done++;
+          }
           r.last_progress_ns = now_ns();
         } else if (wc[i].wr_id & kWrFifo) {
           // a signalled descriptor write: nothing to do but to have reaped the send queue
@@ -149,8 +265,11 @@ void poll_all(RdmaComm* c, ConnManager* cm) {
         } else {
           const uint32_t slot = (uint32_t)(wc[i].wr_id & 0xffffu);
           const uint32_t piece = (uint32_t)((wc[i].wr_id >> 16) & 0xffffu);
+          const uint32_t gen = (uint32_t)((wc[i].wr_id >> 32) & 0xffu);
           RdmaRequest& r = c->reqs[slot % kMaxRequests];
           if (!r.used || !r.is_send || piece >= r.pieces.size()) { fail(c, ncclInternalError, "send completion for an unknown piece"); continue; }
+          if (r.pieces[piece].done || r.pieces[piece].gen != gen) continue;     // an earlier posting of a piece that was sent again
+          r.pieces[piece].done = true;
           r.pieces_done++;
           r.last_progress_ns = now_ns();
           if (cm) cm->done_tx(r.pieces[piece].dev, r.pieces[piece].len);
@@ -477,66 +596,39 @@ ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int 
   const int per_dev_qps = (p.ib_split_data_on_qps && c->nqps > 1 && (uint64_t)size >= 128ull * c->nqps * nstripes) ? c->nqps : 1;
   const int npieces = nstripes * per_dev_qps;
   const uint64_t per = npieces > 1 ? ((uint64_t)size / (uint64_t)npieces) & ~127ull : (uint64_t)size;
-  const uint32_t imm = (d.slot & 0xffu) | ((uint32_t)npieces << 8);
-  const bool use_inline = p.ib_use_inline != 0;
   c->done_src[d.slot % kMaxRequests].size = (uint64_t)size;
   c->done_src[d.slot % kMaxRequests].tx_mask = cm->tx_mask(c->own_dev);
+  r->data = reinterpret_cast<const uint8_t*>(data);
+  r->mr = mr;
+  r->desc = d;
+  r->bad_key = p.fault_bad_rkey_after > 0 && (int64_t)c->msg_index + 1 == p.fault_bad_rkey_after;
 
   uint64_t off = 0;
   int dev = first, piece = 0;
   for (int s = 0; s < nstripes; ++s) {
+    dev = rdma_next_alive(c, dev);            // devices given up earlier are skipped
+    if (dev < 0) {
+      fail(c, ncclRemoteError, "every device of the connection is gone");
+      r->used = false;
+      return ncclRemoteError;
+    }
     for (int k = 0; k < per_dev_qps; ++k, ++piece) {
       const uint64_t len = piece == npieces - 1 ? (uint64_t)size - off : per;
       const int q = per_dev_qps > 1 ? k : (int)(c->msg_index % (uint64_t)c->nqps);
-      rdma::SendWr wr[3];
-      int n = 0;
-      if (piece == 0) {                       // the record for the slot travels ahead of the first immediate
-        wr[n].wr_id = 0;
-        wr[n].op = rdma::kWrite;
-        wr[n].laddr = &c->done_src[d.slot % kMaxRequests];
-        wr[n].len = sizeof(RdmaDoneRec);
-        wr[n].lkey = c->done_src_mr->mr[dev]->lkey;
-        wr[n].raddr = c->remote_done_addr + sizeof(RdmaDoneRec) * (d.slot % kMaxRequests);
-        wr[n].rkey = c->remote_done_rkey[dev];
-        wr[n].inline_data = use_inline;
-        ++n;
-      }
-      const uint64_t wr_id = (uint64_t)r->slot | ((uint64_t)piece << 16);
-      const bool split = len > (uint64_t)p.ib_ar_threshold;     // large: data write, then an empty write carrying the immediate
-      if (split) {
-        wr[n].wr_id = wr_id;
-        wr[n].op = rdma::kWrite;
-        wr[n].laddr = (const uint8_t*)data + off;
-        wr[n].len = (uint32_t)len;
-        wr[n].lkey = mr->mr[dev]->lkey;
-        wr[n].raddr = d.addr + off;
-        wr[n].rkey = d.rkey[dev];
-        ++n;
-      }
-      wr[n].wr_id = wr_id;
-      wr[n].op = rdma::kWriteImm;
-      wr[n].laddr = split || len == 0 ? nullptr : (const uint8_t*)data + off;
-      wr[n].len = split ? 0 : (uint32_t)len;
-      wr[n].lkey = mr->mr[dev]->lkey;
-      wr[n].raddr = d.addr + off;
-      wr[n].rkey = d.rkey[dev];
-      wr[n].imm = imm;
-      wr[n].signaled = true;
-      ++n;
-      if (p.fault_bad_rkey_after > 0 && (int64_t)c->msg_index + 1 == p.fault_bad_rkey_after)      // test hook: wrong key on the payload
-        for (int k = piece == 0 ? 1 : 0; k < n; ++k) wr[k].rkey ^= 0x5a5a5a5au;
-      g_pieces.fetch_add(1, std::memory_order_relaxed);
-      g_work_requests.fetch_add((uint64_t)n, std::memory_order_relaxed);
-      if (g_prov->post_send(c->dev[dev].qp[q], wr, n) != 0) {
-        fail(c, ncclSystemError, "post_send failed");
-        r->used = false;
-        return ncclSystemError;
-      }
-      r->pieces.push_back(RdmaPiece{dev, len});
-      cm->mark_tx(dev, len);
+      RdmaPiece pc;
+      pc.dev = dev; pc.q = q; pc.off = off; pc.len = len;
+      r->pieces.push_back(pc);
       off += len;
     }
     dev = (dev + (int)(p.step > 0 ? p.step : 1)) % c->ndev;
+  }
+  for (int pi = 0; pi < npieces; ++pi) {
+    if (!post_piece(c, r, pi)) {
+      fail(c, ncclSystemError, "post_send failed");
+      r->used = false;
+      return ncclSystemError;
+    }
+    cm->mark_tx(r->pieces[pi].dev, r->pieces[pi].len);
   }
   r->pieces_total = npieces;
   c->msg_index++;
@@ -571,17 +663,9 @@ ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int 
   d->proposed_dev = c->cur_dev;
   for (int k = 0; k < c->ndev; ++k) d->rkey[k] = mr->mr[k]->rkey;
   d->seq = idx + 1;
-  rdma::SendWr wr;
-  wr.wr_id = kWrFifo;
-  wr.op = rdma::kWrite;
-  wr.laddr = d;
-  wr.len = sizeof *d;
-  wr.lkey = c->fifo_src_mr->mr[c->ctrl_dev]->lkey;
-  wr.raddr = c->remote_fifo_addr + sizeof(RdmaDesc) * (idx % kMaxRequests);
-  wr.rkey = c->remote_fifo_rkey[c->ctrl_dev];
-  wr.signaled = (idx % kFifoSignalEvery) == kFifoSignalEvery - 1;
-  wr.inline_data = params().ib_use_inline != 0;
-  if (g_prov->post_send(c->dev[c->ctrl_dev].qp[0], &wr, 1) != 0) {
+  r->fifo_idx = idx;
+  if (c->dead[c->ctrl_dev] && rdma_next_alive(c, c->ctrl_dev) >= 0) c->ctrl_dev = rdma_next_alive(c, c->ctrl_dev);
+  if (!post_descriptor(c, idx)) {
     fail(c, ncclSystemError, "descriptor write failed");
     r->used = false;
     return ncclSystemError;
@@ -684,6 +768,8 @@ void rdma_close_listen(RdmaListenComm* lc) {
   delete lc;
 }
 
+unsigned long long rdma_failovers() { return g_failovers.load(); }
+
 void rdma_counters(unsigned long long* m, unsigned long long* p, unsigned long long* w) {
   *m = g_messages.load();
   *p = g_pieces.load();
@@ -691,6 +777,8 @@ void rdma_counters(unsigned long long* m, unsigned long long* p, unsigned long l
 }
 
 }  // namespace flnet
+
+extern "C" __attribute__((visibility("default"))) unsigned long long fuselink_rdma_failovers(void) { return flnet::rdma_failovers(); }
 
 // Counters for tests and tools: messages sent, pieces they were cut into, work requests posted for them.
 extern "C" __attribute__((visibility("default"))) void fuselink_rdma_counters(unsigned long long* messages, unsigned long long* pieces,

@@ -12,7 +12,11 @@
 //           write-with-immediate below NCCL_IB_AR_THRESHOLD (src/plugin.cc:1454-1462).  The first piece also
 //           writes {actual size, sender's device mask} into the receiver's record for the slot.
 //   test    polls the completion queues: a send is done when all its pieces completed, a receive when it has
-//           seen as many immediates as the immediate data announces (slot in bits 0-7, piece count in 8-15).
+//           seen every piece the immediate data announces (slot in bits 0-7, piece count in 8-15, piece index in 16-23).
+//   A device whose queue pair fails (retry exceeded, flushed) is marked dead for the connection: the sender posts the
+//   affected pieces again on another device, the receiver moves its descriptor writes to another device and writes the
+//   descriptors of its unfinished receives again (both are idempotent).  A remote-access error is not a link failure
+//   and fails the connection.
 //
 // Connections are bootstrapped over TCP like the reference's (src/plugin.cc:700-880): the two ends exchange
 // queue-pair addresses, FIFO address and keys, then a "ready" byte.
@@ -70,7 +74,11 @@ struct RdmaConnInfo {                     // exchanged over the bootstrap socket
 
 struct RdmaPiece {
   int dev;
+  int q;                                  // queue pair index on that device
+  uint64_t off;
   uint64_t len;
+  uint8_t gen = 0;                        // bumped when the piece is posted again after a device failure
+  bool done = false;
 };
 
 struct RdmaComm;
@@ -83,9 +91,15 @@ struct RdmaRequest {
   int tag = 0;
   int pieces_total = -1;                  // recv: unknown until the first immediate arrives
   int pieces_done = 0;
+  uint64_t piece_mask = 0;                // recv: pieces whose immediate arrived (a piece sent twice counts once)
   int rx_dev = 0;
+  uint64_t fifo_idx = 0;                  // recv: position of the descriptor in the sender's FIFO
   uint64_t last_progress_ns = 0;
   std::vector<RdmaPiece> pieces;          // send only
+  const uint8_t* data = nullptr;          // send: what is needed to post a piece again
+  RdmaMrSet* mr = nullptr;
+  RdmaDesc desc;
+  bool bad_key = false;                   // test hook
 };
 
 struct RdmaDevEnd {
@@ -117,6 +131,7 @@ struct RdmaComm {
   uint32_t remote_fifo_rkey[kMaxDev];
   uint64_t fifo_tail = 0;
   int ctrl_dev = 0;                       // device whose queue pair carries the descriptor writes
+  bool dead[kMaxDev] = {};                // devices given up after a queue-pair failure
   // flush of device memory after a receive (NCCL_GDR_FLUSH_DISABLE=0): a queue pair connected to itself reads one
   // byte of the buffer back through the NIC, which orders the NIC's earlier writes before it (src/plugin.cc:1768-1799)
   rdma::Qp* flush_qp = nullptr;

@@ -126,6 +126,8 @@ class SoftProvider : public Provider {
  public:
   SoftProvider() {
     ndev_ = (int)param_i64("FUSELINK_SOFT_NDEV", 4);
+    fault_dev_ = (int)param_i64("FUSELINK_SOFT_FAULT_DEV", -1);               // test hook: this device breaks ...
+    fault_after_ = (uint64_t)param_i64("FUSELINK_SOFT_FAULT_AFTER_BYTES", 0);  // ... once it has carried this many bytes
     if (ndev_ < 1) ndev_ = 1;
     if (ndev_ > 16) ndev_ = 16;
     listen_fd_ = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
@@ -347,11 +349,22 @@ class SoftProvider : public Provider {
         if (m.hdr_sent < sizeof m.hdr) break;
       }
       const uint8_t* p = m.payload ? m.payload : m.copy.data();
+      if (q->dev == fault_dev_ && !fault_fired_ && fault_after_ && dev_bytes_ + m.hdr.len - m.sent > fault_after_) {
+        // the link of this device goes down in the middle of a message: what a cable pull does to a queue pair
+        const size_t allowed = fault_after_ > dev_bytes_ ? (size_t)(fault_after_ - dev_bytes_) : 0;
+        if (allowed && m.sent < m.hdr.len) (void)!send(q->out_fd, p + m.sent, allowed < m.hdr.len - m.sent ? allowed : m.hdr.len - m.sent, MSG_DONTWAIT | MSG_NOSIGNAL);
+        fault_fired_ = true;
+        close(q->out_fd);
+        q->out_fd = -1;
+        fail_qp(q, kWcRetryExceeded);
+        return;
+      }
       if (m.sent < m.hdr.len) {
         ssize_t r = send(q->out_fd, p + m.sent, m.hdr.len - m.sent, MSG_DONTWAIT | MSG_NOSIGNAL);
         if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) break;
         if (r <= 0) { fail_qp(q, kWcRetryExceeded); return; }
         m.sent += (size_t)r;
+        if (q->dev == fault_dev_) dev_bytes_ += (uint64_t)r;
         if (m.sent < m.hdr.len) break;
       }
       q->sendq.pop_front();
@@ -554,6 +567,9 @@ class SoftProvider : public Provider {
   }
 
   std::mutex mu_;
+  int fault_dev_ = -1;
+  uint64_t fault_after_ = 0, dev_bytes_ = 0;
+  bool fault_fired_ = false;
   uint8_t bounce_[64 * 1024];
   int ndev_ = 0;
   int listen_fd_ = -1;

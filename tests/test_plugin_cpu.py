@@ -24,12 +24,12 @@ def _built():
     assert os.path.exists(PLUGIN) and os.path.exists(HARNESS)
 
 
-def _pair(sizes, extra_send=(), extra_recv=(), env=None, common=(), timeout=120, env_send=None):
+def _pair(sizes, extra_send=(), extra_recv=(), env=None, common=(), timeout=120, env_send=None, env_recv=None):
     with tempfile.TemporaryDirectory() as d:
         hf = os.path.join(d, "handle")
         e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", **(env or {}))
         sz = [str(s) for s in sizes]
-        rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, *common, *extra_recv, *sz], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, *common, *extra_recv, *sz], env=dict(e, **(env_recv or {})), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         tx = subprocess.Popen([HARNESS, PLUGIN, "send", hf, *common, *extra_send, *sz], env=dict(e, **(env_send or {})), stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
         try:
             txo, txe = tx.communicate(timeout=timeout)

@@ -133,3 +133,31 @@ def test_flush_reads_device_memory_back_through_the_nic():
     tx, rx = _pair([1 << 20], env=base, common=["--device-buffers", "--chunk", "262144"], extra_recv=["--flush"])
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     assert "FLUSHES 0" in rx[1]
+
+
+def test_device_failure_on_the_sender_moves_pieces_to_another_device():
+    """One device's link dies in the middle of a message (the software NIC breaks its queue pair after 3 MB): the
+    completion error marks the device dead for the connection, the affected pieces are posted again on the next device,
+    the receiver counts each piece once, and every byte arrives."""
+    env = dict(SOFT, NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536", FL_HARNESS_VERBOSE="1", FUSELINK_NET_TIMEOUT_MS="8000")
+    tx, rx = _pair([16 << 20, 1 << 20, 7], env=env, common=["--chunk", "524288", "--inflight", "8"], timeout=90,
+                   env_send={"FUSELINK_SOFT_FAULT_DEV": "1", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "RDMA-FAILOVERS" in tx[1] and "is given up; traffic moves to device" in tx[2], tx
+
+
+def test_device_failure_under_the_descriptor_writes_is_survived():
+    """The device that carries the receiver's descriptor writes dies: the receiver moves them to another device and
+    writes the descriptors of its unfinished receives again."""
+    env = dict(SOFT, FL_HARNESS_VERBOSE="1", FUSELINK_NET_TIMEOUT_MS="8000")
+    tx, rx = _pair([8 << 20, 3], env=env, common=["--chunk", "262144", "--inflight", "8"], timeout=90,
+                   env_recv={"FUSELINK_SOFT_FAULT_DEV": "0", "FUSELINK_SOFT_FAULT_AFTER_BYTES": "1500"})
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "RDMA-FAILOVERS" in rx[1] and "is given up" in rx[2], rx
+
+
+def test_failover_can_be_switched_off():
+    env = dict(SOFT, NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536", FUSELINK_FAILOVER="0", FUSELINK_NET_TIMEOUT_MS="2000")
+    tx, rx = _pair([16 << 20], env=env, common=["--chunk", "524288", "--expect-error"], timeout=60,
+                   env_send={"FUSELINK_SOFT_FAULT_DEV": "1", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
+    assert tx[0] == 0 and "EXPECTED-ERROR" in tx[1], tx
