@@ -3,6 +3,8 @@
 # sendrecv_perf through the plugin with 4 channels, 512 KiB chunks).  Two arms on one box:
 #   1. device path: p2p sweep of this library vs NCCL over NVLink (needs >= 2 GPUs)
 #   2. plugin path: the ncclNet plugin's TCP transport driven by two processes (no GPU needed)
+#   3. NCCL through the plugin: torch.distributed send/recv with NCCL_NET_PLUGIN pointing at this build, NVLink and shared
+#      memory switched off so that NCCL has to use its network transport (needs >= 2 GPUs; PLUGIN_ARM=1)
 set -euo pipefail
 cd "$(dirname "$0")/.."
 export NCCL_P2P_NET_CHUNKSIZE=${NCCL_P2P_NET_CHUNKSIZE:-524288}
@@ -11,6 +13,9 @@ export NCCL_FUSELINK_STEP=${NCCL_FUSELINK_STEP:-1}
 NGPU=${NGPU:-2}
 if python -c "import torch,sys; sys.exit(0 if torch.cuda.device_count() >= $NGPU else 1)"; then
   python -m torch.distributed.run --nnodes=1 --nproc-per-node "$NGPU" --master-addr 127.0.0.1 bench/p2p_sweep.py --size-lo 10 --size-hi 30
+fi
+if [ "${PLUGIN_ARM:-0}" = 1 ]; then
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29631 bench/nccl_plugin_sendrecv.py --size-lo 20 --size-hi 28
 fi
 H=$(mktemp -u /tmp/fl_handle.XXXX)
 LIB=fuselink_b200/lib
