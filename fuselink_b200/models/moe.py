@@ -97,11 +97,12 @@ class MoELayer(nn.Module):
             xr = x * torch.empty_like(x).uniform_(1.0 - self.jitter_eps, 1.0 + self.jitter_eps)
         logits = (xr @ self.router.t()).float() + self.router_bias
         probs = torch.softmax(logits, dim=-1)
-        pick = logits
         if self.training and self.noisy_gate == "rsample":
-            pick = logits - torch.log(-torch.log(torch.rand_like(logits).clamp_min(1e-20)))    # Gumbel-max sampling
-        _, idx = torch.topk(pick, self.cfg.topk, dim=-1)
-        w = probs.gather(1, idx)
+            noisy = logits - torch.log(-torch.log(torch.rand_like(logits).clamp_min(1e-20)))   # Gumbel-max sampling
+            _, idx = torch.topk(noisy, self.cfg.topk, dim=-1)
+            w = probs.gather(1, idx)
+        else:
+            w, idx = torch.topk(probs, self.cfg.topk, dim=-1)
         w = w / w.sum(dim=-1, keepdim=True)
         self.l_aux = load_balancing_loss(probs, idx, self.cfg.num_experts)
         if self.drop_tokens and self.capacity_factor > 0:
