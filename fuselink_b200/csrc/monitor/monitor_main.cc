@@ -4,8 +4,12 @@
 // reference's daemon (src/monitor_main.cpp:5-13) starts its thread without initialising the shared segment
 // first; here the table is created and validated before the sweeper starts.
 //
-//   fuselink-monitor [--shm /fuselink_monitor] [--groups 8] [--paths-per-group 1] [--timeout-us 160]
+//   fuselink-monitor [--shm /fuselink_monitor] [--groups 8|auto] [--paths-per-group 1] [--timeout-us 160]
 //                    [--period-us 40] [--seconds N] [--print-every-ms M]
+//
+// --groups auto sizes the table from the machine the way the reference's detectRdmaNics does
+// (src/monitor.cpp:88-100): the RDMA devices under /sys/class/infiniband, else the GPUs the NVIDIA driver lists, else 8.
+#include <dirent.h>
 #include <signal.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -15,6 +19,22 @@
 #include <string>
 
 #include "monitor.h"
+
+static int count_entries(const char* dir) {
+  DIR* d = opendir(dir);
+  if (!d) return 0;
+  int n = 0;
+  while (dirent* e = readdir(d))
+    if (e->d_name[0] != '.') ++n;
+  closedir(d);
+  return n;
+}
+static int detect_paths() {
+  int n = count_entries("/sys/class/infiniband");
+  if (n <= 0) n = count_entries("/proc/driver/nvidia/gpus");
+  if (n <= 0) n = 8;
+  return n > 64 ? 64 : n;
+}
 
 static volatile sig_atomic_t g_stop = 0;
 static void on_sig(int) { g_stop = 1; }
@@ -27,7 +47,7 @@ int main(int argc, char** argv) {
     std::string a = argv[i];
     auto next = [&]() { return i + 1 < argc ? argv[++i] : (char*)"0"; };
     if (a == "--shm") shm = next();
-    else if (a == "--groups") groups = atoi(next());
+    else if (a == "--groups") { const char* v = next(); groups = !strcmp(v, "auto") ? detect_paths() : atoi(v); }
     else if (a == "--paths-per-group") ppg = atoi(next());
     else if (a == "--timeout-us") timeout_us = atoi(next());
     else if (a == "--period-us") period_us = atoi(next());

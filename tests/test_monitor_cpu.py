@@ -200,6 +200,20 @@ def test_daemon_binary_creates_and_removes_table():
     assert p.wait(timeout=10) == 0
 
 
+def test_daemon_sizes_its_table_from_the_machine():
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "fuselink_b200", "lib", "fuselink-monitor")
+    if not os.path.exists(exe):
+        pytest.skip("daemon not built")
+    name = "/fl_daemon_" + uuid.uuid4().hex[:10]
+    out = subprocess.run([exe, "--shm", name, "--groups", "auto", "--seconds", "0.2"], capture_output=True, text=True, timeout=30)
+    assert out.returncode == 0
+    want = 0
+    for d in ("/sys/class/infiniband", "/proc/driver/nvidia/gpus"):
+        if want == 0 and os.path.isdir(d):
+            want = len([e for e in os.listdir(d) if not e.startswith(".")])
+    assert f"{want or 8} paths" in out.stdout, out.stdout
+
+
 def test_metrics_endpoint_serves_the_table():
     """The Prometheus endpoint reads the same table the selector writes: state, outstanding bytes and decisions."""
     import urllib.request
