@@ -44,6 +44,7 @@ struct Driver {
   virtual int any_copy(void* dst, const void* src, size_t n) = 0;
   virtual int device_count() = 0;
   virtual int pointer_device(const void* ptr) = 0;   // -1 when unknown
+  virtual int address_range(const void* ptr, uintptr_t* base, size_t* size) { (void)ptr; (void)base; (void)size; return 1; }
 };
 
 // ---- real CUDA driver, resolved at run time -----------------------------------------------------
@@ -69,6 +70,7 @@ struct CudaDriver : Driver {
   CUresult (*Memcpy)(CUdeviceptr, CUdeviceptr, size_t) = nullptr;
   CUresult (*DeviceGetCount)(int*) = nullptr;
   CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr) = nullptr;
+  CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr) = nullptr;
 
   template <class F>
   bool sym(const char* name, F& fn) {
@@ -106,6 +108,7 @@ struct CudaDriver : Driver {
     (void)sym("cuMemcpy", Memcpy);
     (void)sym("cuDeviceGetCount", DeviceGetCount);
     (void)sym("cuPointerGetAttribute", PointerGetAttribute);
+    (void)sym("cuMemGetAddressRange", MemGetAddressRange);
     g_err[0] = 0;
     return chk(Init(0), "cuInit") == 0;
   }
@@ -189,6 +192,15 @@ struct CudaDriver : Driver {
   int device_count() override {
     int n = 0;
     return DeviceGetCount && DeviceGetCount(&n) == CUDA_SUCCESS ? n : 0;
+  }
+  int address_range(const void* ptr, uintptr_t* base, size_t* size) override {
+    if (!MemGetAddressRange) return 1;
+    CUdeviceptr b = 0;
+    size_t n = 0;
+    if (MemGetAddressRange(&b, &n, (CUdeviceptr)(uintptr_t)ptr) != CUDA_SUCCESS || !n) return 1;
+    *base = (uintptr_t)b;
+    *size = n;
+    return 0;
   }
   int pointer_device(const void* ptr) override {
     int ord = -1;
@@ -537,6 +549,31 @@ int fl_vmm_ptr2dev(const void* ptr) {
   const uintptr_t p = (uintptr_t)ptr;
   if (p < r->va || p >= r->va + r->size) return -1;
   return r->slabs[(p - r->va) / r->slab_bytes].device;
+}
+
+int fl_vmm_address_range(const void* ptr, void** base, size_t* size) {
+  {
+    std::lock_guard<std::mutex> l(g_mu);
+    auto it = g_regions.upper_bound((uintptr_t)ptr);
+    if (it != g_regions.begin()) {
+      --it;
+      FlVmmRegion* r = it->second;
+      const uintptr_t p = (uintptr_t)ptr;
+      if (p >= r->va && p < r->va + r->size) {
+        const size_t slab = (p - r->va) / r->slab_bytes;
+        *base = reinterpret_cast<void*>(r->va + slab * r->slab_bytes);
+        *size = r->slab_bytes;
+        return 0;
+      }
+    }
+  }
+  if (!g_drv) return 1;
+  uintptr_t b = 0;
+  size_t n = 0;
+  if (g_drv->address_range(ptr, &b, &n)) return 1;
+  *base = reinterpret_cast<void*>(b);
+  *size = n;
+  return 0;
 }
 
 int fl_vmm_memcpy(void* dst, const void* src, size_t bytes) {

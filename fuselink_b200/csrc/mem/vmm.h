@@ -56,6 +56,10 @@ int fl_vmm_remap_slab(FlVmmRegion* r, int slab, int target_device, int keep_cont
                       int n_access, long* usec_out);
 // Which device backs the slab that contains ptr (-1 if ptr is not inside a known region).
 int fl_vmm_ptr2dev(const void* ptr);
+// The mapping that contains `ptr`: base address and size of the physical allocation mapped there (for a region of this
+// layer, the slab).  What the reference asks cuMemGetAddressRange for before it takes a buffer over
+// (src/plugin.cc:1186-1194): NCCL registers sub-ranges of larger allocations.  Returns 0 on success.
+int fl_vmm_address_range(const void* ptr, void** base, size_t* size);
 // Synchronous copy between any two addresses the backend knows (device or host, unified addressing).
 int fl_vmm_memcpy(void* dst, const void* src, size_t bytes);
 // Device that owns `ptr`: a region of this layer, else what the driver reports, else -1.

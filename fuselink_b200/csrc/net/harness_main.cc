@@ -102,6 +102,7 @@ int main(int argc, char** argv) {
   uint64_t seed = 0;
   bool expect_error = false, device_bufs = false, threaded = false, do_flush = false;
   const char* inject_event = nullptr;
+  size_t reg_offset = 0;
   Api api;
   std::vector<size_t> sizes;
   for (int i = 4; i < argc; ++i) {
@@ -117,6 +118,7 @@ int main(int argc, char** argv) {
     else if (a == "--die-after-chunks") die_after = (int)val();
     else if (a == "--expect-error") expect_error = true;
     else if (a == "--threads") threaded = true;
+    else if (a == "--reg-offset") reg_offset = (size_t)val();  // device buffers: the registered buffer starts this far into its allocation
     else if (a == "--flush") do_flush = true;               // receiver: iflush the whole buffer after every message
     else if (a == "--inject-event") inject_event = argv[++i];   // raise an asynchronous device event after init (software NIC)
     else if (a == "--device-buffers") device_bufs = true;   // buffers come from the plugin's cuMem layer and are registered as CUDA
@@ -199,9 +201,9 @@ int main(int argc, char** argv) {
       // a "GPU" buffer from the plugin's cuMem layer (memfd-backed when FUSELINK_VMM_FAKE=1), owned by device `dev`
       auto create = (void* (*)(int, size_t, size_t))dlsym(lib, "fl_vmm_create");
       auto vptr = (void* (*)(const void*))dlsym(lib, "fl_vmm_ptr");
-      region = create ? create(dev, host.size() * 4 + 16, 0) : nullptr;
+      region = create ? create(dev, host.size() * 4 + 16 + reg_offset, 0) : nullptr;
       if (!region) { fprintf(stderr, "fl_vmm_create failed\n"); return 2; }
-      bufp = (float*)vptr(region);
+      bufp = (float*)((char*)vptr(region) + reg_offset);
     }
     struct BufView { float* p; size_t n; float* data() { return p; } size_t size() { return n; } } buf{bufp, host.size()};
     if (is_send) { fill(host, seed, mi); if (!host.empty()) memcpy(bufp, host.data(), host.size() * 4); }

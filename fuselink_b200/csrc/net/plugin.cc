@@ -62,6 +62,7 @@ struct MemHandle {
   FlVmmRegion* region;   // CUDA registrations made through the cuMem layer, else null
   uint32_t mr_id;        // non-zero for a region that can be exported to a same-host sender
   RdmaMrSet* rdma;       // RDMA transport: the registration on every device
+  void* base;            // start of the cuMem allocation `data` lies in (key of the adoption table), else null
 };
 std::atomic<uint32_t> g_mr_counter{1};
 struct Adopted { FlVmmRegion* region; uint32_t mr_id; int refs; };
@@ -528,7 +529,7 @@ ncclResult_t fl_accept_v7(void* listen_comm, void** recv_comm, ncclNetDeviceHand
 // only touches host memory, so a CUDA registration is refused unless the device transport is active.
 void fl_dereg_region(MemHandle* m) {
   std::lock_guard<std::mutex> l(g_mu);
-  auto it = g_adopted.find(m->data);
+  auto it = g_adopted.find(m->base ? m->base : m->data);
   if (it != g_adopted.end() && it->second.region == m->region) {
     if (--it->second.refs == 0) {
       fl_vmm_destroy(m->region);
@@ -553,7 +554,7 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
     *mhandle = m;
     return ncclSuccess;
   };
-  if (type == NCCL_PTR_HOST) return finish(new MemHandle{data, size, type, nullptr, 0, nullptr});
+  if (type == NCCL_PTR_HOST) return finish(new MemHandle{data, size, type, nullptr, 0, nullptr, nullptr});
   if (type != NCCL_PTR_CUDA || g_ngpus <= 0) {
     FL_WARN("regMr: pointer type %d is not supported (set FUSELINK_CUDA_PTRS=1 for device buffers)", type);
     return ncclInvalidUsage;
@@ -563,10 +564,15 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
   // owner GPU with read/write access (src/fuselink.cc:43-56).  A buffer that is not a cuMem allocation (or that is
   // registered again) is used where it is.
   const int channel = !comm ? 0 : g_rdma ? reinterpret_cast<RdmaComm*>(comm)->channel_id : reinterpret_cast<Comm*>(comm)->channel_id;
-  MemHandle* m = new MemHandle{data, size, type, nullptr, 0, nullptr};
+  MemHandle* m = new MemHandle{data, size, type, nullptr, 0, nullptr, nullptr};
   if (params().remap || params().nvl) {
+    // NCCL registers sub-ranges of larger allocations: the unit that can be taken over is the whole mapping
+    void* base = data;
+    size_t span = size;
+    if (fl_vmm_address_range(data, &base, &span) != 0) { base = data; span = size; }
+    m->base = base;
     std::lock_guard<std::mutex> l(g_mu);
-    auto it = g_adopted.find(data);
+    auto it = g_adopted.find(base);
     if (it != g_adopted.end()) {
       // NCCL registers one buffer once per channel: the allocation is adopted (and re-homed) by the first
       // registration only, the others share it, so that an exported descriptor always names what the address maps
@@ -576,16 +582,16 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
     } else {
       int dev = fl_vmm_pointer_device(data);
       if (dev < 0) dev = 0;
-      FlVmmRegion* r = fl_vmm_adopt(data, size, dev);
+      FlVmmRegion* r = fl_vmm_adopt(base, span, dev);
       if (r) {
         const int relay = (dev + channel) % g_ngpus;
         long usec = 0;
         const int access[2] = {dev, relay};
         if (params().remap && relay != dev && fl_vmm_remap_slab(r, 0, relay, 1, access, 2, &usec) == 0)
-          FL_INFO("regMr: %zu bytes at %p re-homed GPU %d -> GPU %d in %ld us", size, data, dev, relay, usec);   // "Remap time"
+          FL_INFO("regMr: %zu bytes at %p re-homed GPU %d -> GPU %d in %ld us", span, base, dev, relay, usec);   // "Remap time"
         m->region = r;
         m->mr_id = g_mr_counter.fetch_add(1);
-        g_adopted[data] = Adopted{r, m->mr_id, 1};
+        g_adopted[base] = Adopted{r, m->mr_id, 1};
       } else {
         FL_INFO("regMr: %p is not a cuMem allocation (%s): registered in place", data, fl_vmm_last_error());
       }

@@ -241,3 +241,15 @@ def test_refused_connect_is_retried_within_a_budget():
     assert tx.returncode == 2 and "connect failed" in tx.stderr
     assert "after 150 retries" in tx.stderr, tx.stderr
     assert 0.15 <= dt < 30
+
+
+def test_registering_a_sub_range_takes_over_the_whole_allocation():
+    """NCCL registers buffers that start inside a larger cuMem allocation: the plugin finds the mapping the pointer lies
+    in, re-homes that whole mapping (contents kept) and exports it; the direct path then writes at the right offset."""
+    env = {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "8", "FL_HARNESS_VERBOSE": "1"}
+    sizes = [(1 << 20) + 40, 4096]
+    tx, rx = _pair(sizes, env=env, common=["--device-buffers", "--dev", "1", "--reg-offset", str((2 << 20) + 256), "--chunk", "262144"],
+                   extra_recv=["--channel", "2"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "re-homed GPU 1 -> GPU 3" in rx[2] + tx[2]
+    assert f"DIRECT bytes {sum(sizes)} " in tx[1], tx[1]
