@@ -89,3 +89,47 @@ def test_crashed_borrower_releases_its_lease_by_timeout():
     C.monitor_sweep(m, t + 161_000)
     assert C.monitor_status(m, 0, p) == 0
     C.monitor_close(m, False)
+
+
+def _hb_worker(rank, world, port, q, mode):
+    from fuselink_b200.parallel.health import Heartbeat, PeerLost, renumber
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=datetime.timedelta(seconds=20))
+    hb = Heartbeat(store, rank, world, interval_s=0.05, timeout_s=0.6)
+    assert hb.wait_all_seen(20)
+    hb.check()                                     # step 0: everybody is here
+    if rank == world - 1:
+        if mode == "crash":
+            os._exit(0)                            # dies between steps without a word
+        hb.leave()                                 # or says goodbye
+        time.sleep(2.0)                            # keep the process (not the heartbeat) around
+        return
+    t0 = time.time()
+    err = None
+    while time.time() - t0 < 15 and err is None:
+        try:
+            hb.check()                             # what a training loop calls before the next launch
+            time.sleep(0.05)
+        except PeerLost as e:
+            err = e
+    surv = hb.survivors()
+    q.put((rank, None if err is None else (err.lost, err.left), time.time() - t0, surv, renumber(surv, rank)))
+    time.sleep(1.0 if rank == 0 else 0.0)          # the store's host outlives the others' last reads
+    hb.close()
+
+
+@pytest.mark.parametrize("mode", ["crash", "leave"])
+def test_heartbeat_detects_a_lost_or_leaving_rank_before_the_next_launch(mode):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    world = 3
+    procs = [ctx.Process(target=_hb_worker, args=(r, world, port, q, mode)) for r in range(world)]
+    [p.start() for p in procs]
+    got = sorted(q.get(timeout=60) for _ in range(world - 1))
+    [p.join(timeout=30) for p in procs]
+    for rank, err, dt, surv, (new_rank, new_world) in got:
+        assert err is not None, "the loss went unnoticed"
+        lost, left = err
+        assert (lost, left) == (([2], []) if mode == "crash" else ([], [2]))
+        assert dt < (5.0 if mode == "crash" else 2.0)            # lease expiry vs an explicit goodbye
+        assert surv == [0, 1] and (new_rank, new_world) == (rank, 2)

@@ -20,3 +20,18 @@ def test_two_or_more_gpus_against_nccl():
            "--master-port", "29611", os.path.join(here, "mp_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0 and "MULTIGPU-OK" in out.stdout, out.stdout[-3000:] + out.stderr[-3000:]
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+@pytest.mark.skipif(os.environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1",
+                    reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
+def test_rank_leaving_between_steps_on_gpus():
+    """A rank leaves between steps with nothing in flight; the others learn of it on the host (heartbeat) before their
+    next launch and go on among themselves.  NVLS off, plain peer stores, no GPU fault involved."""
+    n = 4 if torch.cuda.device_count() >= 4 else 2
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29641", os.path.join(here, "mp_leave_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+    assert out.stdout.count("LEAVE-OK") == n - 1, out.stdout[-3000:] + out.stderr[-3000:]
