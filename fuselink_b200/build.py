@@ -5,6 +5,7 @@ loads):
 
 * ``fuselink_b200/_C.so``                    torch extension: sm_100a kernels, cuMem layer, monitor bindings
 * ``fuselink_b200/lib/libnccl-net-fuselink.so``  the ncclNet plugin (``NCCL_NET_PLUGIN=fuselink``)
+* ``fuselink_b200/lib/libfuselink.so``           kernels + cuMem regions + monitor as a C library (``include/fuselink.h``)
 * ``fuselink_b200/lib/fuselink-monitor``      stand-alone monitor daemon
 * ``fuselink_b200/lib/fl_net_harness``        two-process driver of the plugin vtable used by the CPU tests
 
@@ -170,6 +171,12 @@ def build_all(verbose: bool = False, jobs: int | None = None) -> dict:
     ext = PKG / "_C.so"
     link(ext, cu_objs + host_objs + ext_objs,
          [CXX, "-shared", "-o", ext, *cu_objs, *host_objs, *ext_objs, *tlink])
+
+    # ---- the same kernels, region layer and monitor as a plain C library (no Python, no PyTorch) -------------
+    core = LIB / "libfuselink.so"
+    link(core, cu_objs + host_objs,
+         [CXX, "-shared", "-o", core, *cu_objs, *host_objs, f"-L{CUDA_HOME}/lib64", f"-Wl,-rpath,{CUDA_HOME}/lib64", "-lcudart",
+          "-ldl", "-lrt", "-lpthread"])
 
     if net_objs:
         plug = LIB / "libnccl-net-fuselink.so"

@@ -123,3 +123,25 @@ def test_slab_pool_register_remap_release():
         assert [C.pool_free_slabs(d) for d in range(4)] == [6, 6, 6, 6]
     finally:
         C.pool_shutdown()
+
+
+def test_c_library_example_builds_and_runs_without_python(tmp_path):
+    """examples/cpp/regions_and_paths.cc against lib/libfuselink.so and include/fuselink.h, on the memfd stand-in."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib = os.path.join(root, "fuselink_b200", "lib")
+    if not os.path.exists(os.path.join(lib, "libfuselink.so")):
+        pytest.skip("libfuselink.so not built")
+    cxx = next((c for c in (os.environ.get("CXX"), "g++", "/usr/bin/g++") if c and shutil.which(c)), None)
+    if cxx is None:
+        pytest.skip("no C++ compiler")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    exe = str(tmp_path / "regions_and_paths")
+    cmd = [cxx, "-std=c++17", "-I", os.path.join(root, "fuselink_b200", "include"), "-I", os.path.join(cuda, "include"),
+           os.path.join(root, "examples", "cpp", "regions_and_paths.cc"), "-L", lib, "-lfuselink", f"-Wl,-rpath,{lib}", "-o", exe]
+    b = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert b.returncode == 0, b.stderr[-3000:]
+    out = subprocess.run([exe, "--fake"], capture_output=True, text=True, timeout=60, env=dict(os.environ, FUSELINK_VMM_FAKE_NGPUS="4"))
+    assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout + out.stderr
+    assert "slab 2 now on device 1" in out.stdout and "stripe 0: via path 1" in out.stdout
