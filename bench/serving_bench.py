@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--input-len", type=int, default=2048)
     ap.add_argument("--decode-steps", type=int, default=256)
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16", "fp32"], help="model and KV cache element type")
     ap.add_argument("--model-path", default="dummy", help="'dummy' = random weights, else a Hugging Face state_dict file or directory")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--emulate", action="store_true")
@@ -40,12 +41,13 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     cfg = MODEL_ZOO[args.model]
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.precision]
     if args.emulate or world == 1:
-        p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, 1)
-        net = LlamaShard(cfg, device=dev, max_positions=args.input_len + args.decode_steps)
+        p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, 1, dtype)
+        net = LlamaShard(cfg, device=dev, dtype=dtype, max_positions=args.input_len + args.decode_steps)
         if args.model_path != "dummy":
             net.load_hf_state_dict(load_checkpoint_file(args.model_path))
-        pool_bytes = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
+        pool_bytes = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * p.elem_bytes
         heaps = SymmetricHeap.emulated(2, pool_bytes + (64 << 20), device=local)
         links = [KVLink(h, p, net.kvh_local) for h in heaps]
         pre = PrefillStage(p, net, links[0], 1, pipeline_layers=args.kv == "fuselink")
@@ -67,12 +69,12 @@ def main():
     groups = [dist.new_group(list(range(0, tp))), dist.new_group(list(range(tp, world)))]
     tp_group = groups[0] if is_prefill else groups[1]
     tp_rank = rank % tp
-    p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, tp)
-    net = LlamaShard(cfg, tp_rank, tp, tp_group if tp > 1 else None, device=dev, max_positions=args.input_len + args.decode_steps)
+    p = ServeParams(cfg, args.batch, args.input_len, args.decode_steps, tp, dtype)
+    net = LlamaShard(cfg, tp_rank, tp, tp_group if tp > 1 else None, device=dev, dtype=dtype, max_positions=args.input_len + args.decode_steps)
     if args.model_path != "dummy":
         net.load_hf_state_dict(load_checkpoint_file(args.model_path))      # every shard cuts its part out of the full checkpoint
     pool_elems = p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim
-    heap = SymmetricHeap.create(2 * pool_elems * 2 + (64 << 20), device=local)
+    heap = SymmetricHeap.create(2 * pool_elems * p.elem_bytes + (64 << 20), device=local)
     link = KVLink(heap, p, net.kvh_local)
     peer = rank + tp if is_prefill else rank - tp            # the reference's pairing: rank <-> rank + world/2
     prompts = make_prompts(p, dev)
@@ -136,9 +138,9 @@ def _nccl_iteration(p, net, link, pre, dec, prompts, peer, is_prefill, t0):
             r.wait()
         e2.record()
         torch.cuda.synchronize()
-        return {"prefill_ms": e0.elapsed_time(e1), "kv_ms": e1.elapsed_time(e2), "kv_GB": 2 * n * 2 / 1e9, "stage_ms": e0.elapsed_time(e2)}
+        return {"prefill_ms": e0.elapsed_time(e1), "kv_ms": e1.elapsed_time(e2), "kv_GB": 2 * n * p.elem_bytes / 1e9, "stage_ms": e0.elapsed_time(e2)}
     first = torch.empty(B, dtype=torch.long, device=dev)
-    k_in = torch.empty(n, dtype=torch.bfloat16, device=dev); v_in = torch.empty_like(k_in)
+    k_in = torch.empty(n, dtype=p.dtype, device=dev); v_in = torch.empty_like(k_in)
     bt = torch.empty(B, cb, dtype=torch.int32, device=dev); nb = torch.empty(B, dtype=torch.int32, device=dev)
     w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0.record()

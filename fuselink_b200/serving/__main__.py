@@ -21,7 +21,7 @@ def main():
     ap.add_argument("--model_name", default="llama3_8b")
     ap.add_argument("--model_path", default="dummy", help="'dummy' (random weights, as the reference's scripts pass) or a Hugging Face state_dict file / directory")
     ap.add_argument("--vocab_json_path", default="")
-    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16"])
+    ap.add_argument("--precision", default="bf16", choices=["bf16", "fp16", "fp32"])
     ap.add_argument("--input_len", type=int, default=2048)
     ap.add_argument("--batch_size", type=int, default=16)
     ap.add_argument("--block_size", type=int, default=16)
@@ -45,7 +45,7 @@ def main():
         runpy.run_path(os.path.join(root, "experiments", "run_online_serving.py"), run_name="__main__")
     else:
         sys.argv = ["serving_bench.py", "--model", a.model_name, "--kv", a.kv, "--batch", str(a.batch_size), "--input-len",
-                    str(a.input_len), "--decode-steps", str(a.num_decoding_step), "--model-path", a.model_path] + (["--emulate"] if world == 1 else [])
+                    str(a.input_len), "--decode-steps", str(a.num_decoding_step), "--model-path", a.model_path, "--precision", a.precision] + (["--emulate"] if world == 1 else [])
         runpy.run_path(os.path.join(root, "bench", "serving_bench.py"), run_name="__main__")
 
 

@@ -39,6 +39,17 @@ class ServeParams:
     input_len: int = 2048
     num_decoding_step: int = 256
     tp_size: int = 1
+    dtype: torch.dtype = torch.bfloat16     # --precision of the reference's binaries (fp16 / fp32 there); KV pools use it too
+
+    @property
+    def elem_bytes(self) -> int:
+        return torch.empty((), dtype=self.dtype).element_size()
+
+    @property
+    def kv_dim_units(self) -> int:
+        """Head dimension as the KV kernel sees it: the kernel moves 2-byte elements, so a 4-byte type is a head twice
+        as wide (the innermost run of a page is one head vector either way)."""
+        return self.model.head_dim * self.elem_bytes // 2
 
     @property
     def block_size(self) -> int:
@@ -63,8 +74,8 @@ class KVLink:
         self.pool_blocks = p.batch_size * p.max_blocks_per_req
         self.page_elems = kv_heads_local * m.block_size * m.head_dim
         n = self.pool_blocks * m.layers * self.page_elems
-        self.k_pool = heap.alloc_tensor([n], torch.bfloat16)
-        self.v_pool = heap.alloc_tensor([n], torch.bfloat16)
+        self.k_pool = heap.alloc_tensor([n], p.dtype)
+        self.v_pool = heap.alloc_tensor([n], p.dtype)
         self.hdr = heap.alloc_tensor([HDR_INTS], torch.int64)
         self.layer_flags = heap.signal_slots(f"{name}:layers", m.layers)
         self.final_flag = heap.signal_slots(f"{name}:final", 1)
@@ -79,7 +90,7 @@ class KVLink:
         m = self.p.model
         flag = self.heap.sig_addr(self.final_flag if final else self.layer_flags + l0, dst_rank)
         self.C.kv_pack_send(src_k, src_v, self.k_pool.addr(dst_rank), self.v_pool.addr(dst_rank), KV_BLHSD, KV_LBSHD,
-                            src_blocks, self.pool_blocks, m.layers, self.kvh, m.block_size, m.head_dim, l0, l1, src_bt, dst_bt,
+                            src_blocks, self.pool_blocks, m.layers, self.kvh, m.block_size, self.p.kv_dim_units, l0, l1, src_bt, dst_bt,
                             nblocks, hdr, self.hdr.addr(dst_rank) if hdr is not None else 0, flag, self.seq, self.cta_counter,
                             num_ctas, self.heap.status_addr)
 
@@ -114,8 +125,8 @@ class PrefillStage:
         dev = model.embed.device
         self.ctx_blocks = p.batch_size * p.context_blocks_per_req
         n = self.ctx_blocks * m.layers * link.page_elems
-        self.k_pool = torch.empty(n, dtype=torch.bfloat16, device=dev)
-        self.v_pool = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        self.k_pool = torch.empty(n, dtype=p.dtype, device=dev)
+        self.v_pool = torch.empty(n, dtype=p.dtype, device=dev)
         B, cb, mb = p.batch_size, p.context_blocks_per_req, p.max_blocks_per_req
         # source pages: request-major; destination pages: the decode pool reserves max_blocks_per_req per request
         self.src_bt = torch.arange(B * cb, dtype=torch.int32, device=dev).view(B, cb).contiguous()
@@ -164,7 +175,7 @@ class PrefillStage:
             k1.record(self.side)
         main.wait_stream(self.side)
         torch.cuda.synchronize()
-        kv_bytes = 2 * self.ctx_blocks * p.model.layers * link.page_elems * 2
+        kv_bytes = 2 * self.ctx_blocks * p.model.layers * link.page_elems * p.elem_bytes
         return StageReport("prefill", elapsed_ms=e0.elapsed_time(k1), compute_ms=e0.elapsed_time(e1), kv_ms=k0.elapsed_time(k1),
                            kv_bytes=kv_bytes, tokens=p.batch_size * p.input_len)
 

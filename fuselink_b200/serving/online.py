@@ -113,8 +113,8 @@ class OnlinePrefill:
         cb = p.context_blocks_per_req
         self.max_src_blocks = MAX_BATCH * cb
         n = self.max_src_blocks * m.layers * links[0].page_elems
-        self.k_pool = torch.empty(n, dtype=torch.bfloat16, device=dev)
-        self.v_pool = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        self.k_pool = torch.empty(n, dtype=p.dtype, device=dev)
+        self.v_pool = torch.empty(n, dtype=p.dtype, device=dev)
         self.credit_slot = links[0].heap.signal_slots("online:credit", len(links))
         self.credit_pad = links[0].heap.alloc_tensor([16], torch.uint8)     # landing zone of the decoder's credit write
         self.batches = 0
@@ -157,7 +157,7 @@ class OnlinePrefill:
                          final=True, num_ctas=1)
         e2.record()
         torch.cuda.synchronize()
-        kv_bytes = int(nblocks.sum().item()) * m.layers * link.page_elems * 2 * 2
+        kv_bytes = int(nblocks.sum().item()) * m.layers * link.page_elems * 2 * p.elem_bytes
         st = BatchStats(B, sum(lens), kv_bytes, HDR_INTS * 8, e1.elapsed_time(e2), e0.elapsed_time(e1))
         self.stats.append(st)
         self.batches += 1
