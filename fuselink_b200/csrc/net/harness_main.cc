@@ -312,6 +312,8 @@ int main(int argc, char** argv) {
   if (failovers && is_send && failovers()) printf("FAILOVERS %llu\n", failovers());
   auto rfail = (unsigned long long (*)(void))dlsym(lib, "fuselink_rdma_failovers");
   if (rfail && rfail()) printf("RDMA-FAILOVERS %llu\n", rfail());
+  auto peer_regions = (int (*)(void*))dlsym(lib, "fuselink_comm_peer_regions");
+  if (peer_regions && is_send && device_bufs) printf("PEER-REGIONS-MAPPED %d\n", peer_regions(comms[0]));
   if (direct_b && is_send) printf("DIRECT bytes %llu msgs %llu of %zu bytes\n", direct_b(), direct_m ? direct_m() : 0ull, total_bytes.load());
   if (do_flush && !is_send) printf("FLUSHES %d\n", flushes.load());
   if (decisions && !is_send) printf("SELECTOR decisions %llu fallbacks %llu channels %d\n", decisions(), fallbacks ? fallbacks() : 0ull, nch);

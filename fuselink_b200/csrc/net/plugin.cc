@@ -94,13 +94,15 @@ int nvl_send_fds(int sock, const NvlExportMsg& msg, const int* fds, int nfds) {
   memset(&mh, 0, sizeof mh);
   mh.msg_iov = &iov;
   mh.msg_iovlen = 1;
-  mh.msg_control = cbuf;
-  mh.msg_controllen = CMSG_SPACE(sizeof(int) * nfds);
-  cmsghdr* cm = CMSG_FIRSTHDR(&mh);
-  cm->cmsg_level = SOL_SOCKET;
-  cm->cmsg_type = SCM_RIGHTS;
-  cm->cmsg_len = CMSG_LEN(sizeof(int) * nfds);
-  memcpy(CMSG_DATA(cm), fds, sizeof(int) * nfds);
+  if (nfds > 0) {
+    mh.msg_control = cbuf;
+    mh.msg_controllen = CMSG_SPACE(sizeof(int) * nfds);
+    cmsghdr* cm = CMSG_FIRSTHDR(&mh);
+    cm->cmsg_level = SOL_SOCKET;
+    cm->cmsg_type = SCM_RIGHTS;
+    cm->cmsg_len = CMSG_LEN(sizeof(int) * nfds);
+    memcpy(CMSG_DATA(cm), fds, sizeof(int) * nfds);
+  }
   ssize_t r;
   do { r = sendmsg(sock, &mh, MSG_NOSIGNAL); } while (r < 0 && errno == EINTR);
   return r == (ssize_t)sizeof msg ? 0 : -1;
@@ -145,6 +147,16 @@ void nvl_ingest(Comm* c, int device) {
       close(c->nvl_fd);
       c->nvl_fd = -1;                              // direct path off for this connection; TCP carries on
       return;
+    }
+    if (msg.nslabs == 0) {                         // the peer deregistered the region: unmap it
+      for (auto it = c->peer_mrs.begin(); it != c->peer_mrs.end(); ++it) {
+        if (it->id == msg.mr_id) {
+          if (it->region) fl_vmm_destroy(reinterpret_cast<FlVmmRegion*>(it->region));
+          c->peer_mrs.erase(it);
+          break;
+        }
+      }
+      continue;
     }
     FlVmmRegion* r = fl_vmm_import(device < 0 ? 0 : device, fds, nfds, (size_t)msg.slab_bytes);
     for (int i = 0; i < nfds; ++i) close(fds[i]);
@@ -607,8 +619,23 @@ ncclResult_t fl_reg_mr_dmabuf(void* comm, void* data, size_t size, int type, uin
   return fl_reg_mr_sz(comm, data, size, type, mhandle);
 }
 ncclResult_t fl_dereg_mr(void* comm, void* mhandle) {
-  (void)comm;
   MemHandle* m = reinterpret_cast<MemHandle*>(mhandle);
+  if (m && m->mr_id && comm && !g_rdma) {
+    // a sender of this connection may hold a mapping of the region: tell it to let go
+    Comm* c = reinterpret_cast<Comm*>(comm);
+    for (auto it = c->exported.begin(); it != c->exported.end(); ++it) {
+      if (*it != m->mr_id) continue;
+      c->exported.erase(it);
+      if (c->nvl_fd >= 0) {
+        NvlExportMsg bye;
+        memset(&bye, 0, sizeof bye);
+        bye.magic = kNvlMagic;
+        bye.mr_id = m->mr_id;
+        nvl_send_fds(c->nvl_fd, bye, nullptr, 0);
+      }
+      break;
+    }
+  }
   if (m && m->rdma) rdma_dereg(m->rdma);
   if (m && m->region) fl_dereg_region(m);
   delete m;
@@ -661,6 +688,7 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
     return ncclInvalidUsage;
   }
   MemHandle* mh = reinterpret_cast<MemHandle*>(mhandle);
+  if (c->nvl_fd >= 0 && !c->peer_mrs.empty()) nvl_ingest(c, 0);     // notices of regions the peer has deregistered
   // Direct path: the receiver exported the buffer of this descriptor.  Its announcement travels on another
   // socket than the descriptor, so it may not be here yet: come back later rather than fall back.
   uint8_t* direct_dst = nullptr;
@@ -968,6 +996,10 @@ __attribute__((visibility("default"))) unsigned long long fuselink_plugin_failov
 // Payload bytes / messages this process stored straight into a same-host peer's exported receive buffer.
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_bytes(void) { return g_direct_bytes.load(); }
 __attribute__((visibility("default"))) unsigned long long fuselink_plugin_direct_msgs(void) { return g_direct_msgs.load(); }
+// Peer regions a send connection currently has mapped (direct path).
+__attribute__((visibility("default"))) int fuselink_comm_peer_regions(void* send_comm) {
+  return g_rdma || !send_comm ? 0 : (int)reinterpret_cast<Comm*>(send_comm)->peer_mrs.size();
+}
 // Device carrying the stripes of a send request (stripe index s); -1 when out of range.
 __attribute__((visibility("default"))) int fuselink_request_stripe_dev(void* request, int s) {
   if (g_rdma) {

@@ -171,6 +171,10 @@ def test_same_host_direct_path_writes_the_exported_receive_buffer():
     assert f"DIRECT bytes {total} msgs {nmsgs} of {total} bytes" in tx[1], tx[1]
     assert "re-homed GPU 2 -> GPU 5" in rx[2] + tx[2]
     assert "mapped at" in tx[2]
+    # the harness registers a fresh buffer per message and deregisters it afterwards: the sender unmaps what the receiver
+    # has let go of, so at most the last region is still mapped at the end (its notice may arrive after the last send)
+    mapped = int([l for l in tx[1].splitlines() if l.startswith("PEER-REGIONS-MAPPED")][0].split()[1])
+    assert mapped <= 1, tx[1]
 
 
 def test_direct_path_is_negotiated_per_connection():
