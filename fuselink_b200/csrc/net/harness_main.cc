@@ -272,6 +272,10 @@ int main(int argc, char** argv) {
       rc = 5;
     }
     for (int c = 0; c < nch; ++c) api.deregMr(comms[ch0 + c], mhs[c]);
+    if (region) {
+      auto destroy = (void (*)(void*))dlsym(lib, "fl_vmm_destroy");
+      if (destroy) destroy(region);
+    }
     total_bytes += bytes;
   }
   long long mine = (long long)(my_xfer * 1e9), cur = xfer_ns.load();

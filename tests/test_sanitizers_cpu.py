@@ -32,7 +32,7 @@ def test_plugin_transfer_under_asan_ubsan(transport):
     art = _build("address,undefined")
     with tempfile.TemporaryDirectory() as d:
         hf = os.path.join(d, "h")
-        env = dict(os.environ, NCCL_SOCKET_IFNAME="lo", ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
+        env = dict(os.environ, NCCL_SOCKET_IFNAME="lo", ASAN_OPTIONS="detect_leaks=1:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
                    NCCL_FUSELINK_DEGREE="3", FUSELINK_MIN_STRIPE_BYTES="4096", **TRANSPORTS[transport])
         sizes = ["0", "4097", str(1 << 20), str(5 << 20)]
         if transport == "tcp-direct":
@@ -45,6 +45,7 @@ def test_plugin_transfer_under_asan_ubsan(transport):
         rxo, rxe = rx.communicate(timeout=180)
     assert tx.returncode == 0 and rx.returncode == 0, (txo, txe[-2000:], rxo, rxe[-2000:])
     assert "ERROR: AddressSanitizer" not in txe + rxe and "runtime error" not in txe + rxe
+    assert "LeakSanitizer" not in txe + rxe, (txe[-2000:], rxe[-2000:])       # every connection, request and mapping is given back
 
 
 @pytest.mark.parametrize("transport", ["tcp", "rdma-soft"])
