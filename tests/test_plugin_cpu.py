@@ -257,3 +257,62 @@ def test_registering_a_sub_range_takes_over_the_whole_allocation():
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     assert "re-homed GPU 1 -> GPU 3" in rx[2] + tx[2]
     assert f"DIRECT bytes {sum(sizes)} " in tx[1], tx[1]
+
+
+@pytest.mark.parametrize("transport", ["tcp", "rdma-soft"])
+def test_stray_and_malformed_connections_do_not_disturb_a_transfer(transport):
+    """Port scanners and broken peers: random bytes, truncated hellos, hellos with a valid magic and nonsense fields,
+    and connections that say nothing arrive at the listener before and while the real sender connects.  They are dropped
+    (the reference validates magic and type the same way, src/extern/socket.cc:431-437) and the transfer is bit-exact."""
+    import random
+    import socket
+    import struct
+    import time
+    extra = {} if transport == "tcp" else {"FUSELINK_TRANSPORT": "rdma", "FUSELINK_RDMA_PROVIDER": "soft"}
+    rng = random.Random(7)
+    with tempfile.TemporaryDirectory() as d:
+        hf = os.path.join(d, "handle")
+        e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", NCCL_SOCKET_FAMILY="AF_INET", **extra)
+        sizes = [str(1 << 20), "4097"]
+        rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, "--chunk", "131072", *sizes], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        keep = []
+        try:
+            t0 = time.time()
+            while not os.path.exists(hf):
+                assert time.time() - t0 < 20
+                time.sleep(0.01)
+            port = struct.unpack("!H", open(hf, "rb").read()[10:12])[0]
+            magic = 0x464c4e4b48454c4f
+
+            def junk(i):
+                kind = i % 6
+                if kind == 0:
+                    return bytes(rng.randrange(256) for _ in range(rng.randrange(1, 200)))
+                if kind == 1:
+                    return struct.pack("<QQ", magic, 1)                                        # truncated hello
+                if kind == 2:
+                    return struct.pack("<QQiiii", magic, rng.getrandbits(60), 1, 99, 0, 4)     # data socket of device 99
+                if kind == 3:
+                    return struct.pack("<QQiiii", magic, rng.getrandbits(60), 0, -1, 0, 4000)  # absurd device count
+                if kind == 4:
+                    return struct.pack("<QQiiii", magic ^ 1, 5, 0, -1, 0, 4)                   # wrong magic
+                return b""                                                                     # connects and says nothing
+
+            for i in range(24):
+                s = socket.create_connection(("127.0.0.1", port))
+                b = junk(i)
+                if b:
+                    s.sendall(b)
+                if i % 3 == 0:
+                    keep.append(s)                        # some stay open for the whole transfer
+                else:
+                    s.close()
+            tx = subprocess.run([HARNESS, PLUGIN, "send", hf, "--chunk", "131072", *sizes], env=e, capture_output=True, text=True, timeout=90)
+            out, err = rx.communicate(timeout=60)
+        finally:
+            for s in keep:
+                s.close()
+            if rx.poll() is None:
+                rx.kill()
+        assert tx.returncode == 0, (tx.stdout, tx.stderr)
+        assert rx.returncode == 0 and "OK received" in out, (out, err)
