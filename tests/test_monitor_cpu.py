@@ -236,3 +236,41 @@ def test_metrics_endpoint_serves_the_table():
     finally:
         srv.close()
         C.monitor_close(m, False)
+
+
+def test_selector_plans_partition_the_transfer_for_any_parameters():
+    """Property test: whatever the size, degree, step, minimum stripe, alignment and set of busy paths, the stripes cover
+    [0, bytes) exactly once, stripe 0 is the direct path, relay stripes start on the alignment and respect the minimum
+    size, no relay is the source, the destination, a busy path or used twice."""
+    hyp = pytest.importorskip("hypothesis")
+    st = hyp.strategies
+
+    @hyp.settings(max_examples=200, deadline=None)
+    @hyp.given(nbytes=st.integers(0, 1 << 34), degree=st.integers(1, 8), step=st.integers(1, 4),
+               min_stripe=st.sampled_from([4096, 1 << 16, 1 << 20, 1 << 24]), align=st.sampled_from([16, 256, 4096, 1 << 19]),
+               src=st.integers(0, 7), dst=st.integers(0, 7), busy=st.sets(st.integers(0, 7)), index=st.integers(0, 1000))
+    def check(nbytes, degree, step, min_stripe, align, src, dst, busy, index):
+        hyp.assume(src != dst)
+        m = C.monitor_open("", True, 8, 1, 160)
+        try:
+            now = C.monitor_now_ns()
+            for p in busy:
+                C.monitor_mark_active(m, TX, p, now)
+            plan = C.select_paths(m, degree, step, min_stripe, align, True, src, dst, nbytes, index, now)
+            assert 1 <= len(plan) <= degree
+            assert plan[0][0] == dst
+            pieces = sorted((off, n) for _, off, n in plan)
+            pos = 0
+            for off, n in pieces:
+                assert off == pos
+                pos += n
+            assert pos == nbytes
+            relays = [p for p, _, _ in plan[1:]]
+            assert len(set(relays)) == len(relays)
+            for p, off, n in plan[1:]:
+                assert p not in (src, dst) and p not in busy
+                assert off % align == 0 and n >= min_stripe
+        finally:
+            C.monitor_close(m, False)
+
+    check()
