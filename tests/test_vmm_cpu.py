@@ -145,3 +145,57 @@ def test_c_library_example_builds_and_runs_without_python(tmp_path):
     out = subprocess.run([exe, "--fake"], capture_output=True, text=True, timeout=60, env=dict(os.environ, FUSELINK_VMM_FAKE_NGPUS="4"))
     assert out.returncode == 0 and out.stdout.strip().endswith("OK"), out.stdout + out.stderr
     assert "slab 2 now on device 1" in out.stdout and "stripe 0: via path 1" in out.stdout
+
+
+def test_random_sequences_keep_accounting_and_contents():
+    """A long random walk over create / alias / remap (with and without contents) / destroy: the bytes held per device
+    always equal the sum over live slabs, addresses never change, and contents survive every keep-contents remap."""
+    import random
+    rng = random.Random(11)
+    base = {d: C.vmm_usage(d) for d in range(8)}
+    live = []                                       # (region, slab_bytes, [device per slab], fill value per slab or None)
+
+    def expect_usage():
+        u = dict(base)
+        for _, sb, devs, _ in live:
+            for d in devs:
+                u[d] += sb
+        return u
+
+    for step in range(300):
+        op = rng.random()
+        if op < 0.3 or not live:
+            dev, nslab = rng.randrange(8), rng.randint(1, 4)
+            sb = rng.choice([2 << 20, 4 << 20])
+            r = C.vmm_create(dev, nslab * sb, sb)
+            live.append((r, sb, [dev] * nslab, [None] * nslab))
+        elif op < 0.75:
+            r, sb, devs, fills = rng.choice(live)
+            s, target, keep = rng.randrange(len(devs)), rng.randrange(8), rng.random() < 0.7
+            ptr = C.vmm_ptr(r)
+            view = C.tensor_from_ptr(ptr + s * sb, [sb // 4], torch.int32, -1)
+            if fills[s] is None or not keep:
+                fills[s] = rng.randrange(1 << 30)
+                view.fill_(fills[s])
+            C.vmm_remap_slab(r, s, target, keep, [devs[0]])
+            assert C.vmm_ptr(r) == ptr and C.vmm_slab_device(r, s) == target
+            devs[s] = target
+            view = C.tensor_from_ptr(ptr + s * sb, [sb // 4], torch.int32, -1)
+            if keep:
+                assert int(view[0]) == fills[s] and int(view[-1]) == fills[s] and bool((view == fills[s]).all())
+            else:
+                fills[s] = None
+        elif op < 0.85:
+            r, sb, devs, fills = rng.choice(live)
+            a = C.vmm_alias(r, rng.randrange(8))
+            assert C.vmm_size(a) == C.vmm_size(r)
+            C.vmm_destroy(a)                            # an alias owns no memory
+        else:
+            i = rng.randrange(len(live))
+            C.vmm_destroy(live.pop(i)[0])
+        if step % 10 == 0:
+            want = expect_usage()
+            assert {d: C.vmm_usage(d) for d in range(8)} == want, step
+    while live:
+        C.vmm_destroy(live.pop()[0])
+    assert {d: C.vmm_usage(d) for d in range(8)} == base
