@@ -442,6 +442,7 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
     PendingSock ps;
     ps.fd = fd;
     ps.got = 0;
+    ps.since_ns = now_ns();
     lc->pending.push_back(ps);
   }
   while (lc->uds_fd >= 0) {
@@ -473,7 +474,15 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
       lc->pending.erase(lc->pending.begin() + i);
       continue;
     }
-    if (ps.got < sizeof(Hello)) { ++i; continue; }
+    if (ps.got < sizeof(Hello)) {
+      if (now_ns() - ps.since_ns > kHelloTimeoutNs) {   // connected and never introduced itself
+        close(ps.fd);
+        lc->pending.erase(lc->pending.begin() + i);
+        continue;
+      }
+      ++i;
+      continue;
+    }
     if (ps.hello.magic != kHelloMagic || ps.hello.ndev < 1 || ps.hello.ndev > kMaxDev ||
         (ps.hello.kind == 1 && (ps.hello.dev < 0 || ps.hello.dev >= ps.hello.ndev))) {
       FL_WARN("accept: dropping a connection with a bad hello");
@@ -491,7 +500,7 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
       c->ndev = ps.hello.ndev;
       c->channel_id = lc->channel_id;
       c->uid = ps.hello.comm_uid;
-      lc->partials.push_back({ps.hello.comm_uid, c, 0});
+      lc->partials.push_back({ps.hello.comm_uid, c, 0, now_ns()});
       part = &lc->partials.back();
     }
     if (ps.hello.kind == 0 && ps.hello.dev == -2) part->comm->nvl_fd = -2;   // a side channel belongs to this connection
@@ -499,6 +508,15 @@ ncclResult_t fl_accept_impl(void* listen_comm, void** recv_comm) {
     else part->comm->data[ps.hello.dev].fd = ps.fd;
     part->have++;
     lc->pending.erase(lc->pending.begin() + i);
+  }
+  for (size_t i = 0; i < lc->partials.size();) {        // connections whose remaining sockets never came
+    if (now_ns() - lc->partials[i].since_ns > kPartialTimeoutNs && lc->partials[i].have < 1 + lc->partials[i].comm->ndev) {
+      FL_WARN("accept: dropping a connection that stayed incomplete (%d of %d sockets)", lc->partials[i].have, 1 + lc->partials[i].comm->ndev);
+      comm_close(lc->partials[i].comm);
+      lc->partials.erase(lc->partials.begin() + i);
+    } else {
+      ++i;
+    }
   }
   for (size_t i = 0; i < lc->partials.size(); ++i) {
     if (lc->partials[i].have == 1 + lc->partials[i].comm->ndev) {

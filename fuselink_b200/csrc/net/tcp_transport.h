@@ -159,14 +159,17 @@ struct PendingSock {
   int fd;
   Hello hello;
   size_t got;
+  uint64_t since_ns = 0;                 // accepted at; a socket that does not finish its hello in time is dropped
 };
+constexpr uint64_t kHelloTimeoutNs = 10ull * 1000000000ull;       // silent accepted sockets
+constexpr uint64_t kPartialTimeoutNs = 120ull * 1000000000ull;    // a connection whose sockets never all arrive
 
 struct ListenComm {
   int fd = -1;
   int dev = 0;
   int channel_id = 0;
   std::vector<PendingSock> pending;      // accepted, hello not complete yet
-  struct Partial { uint64_t uid; Comm* comm; int have; };
+  struct Partial { uint64_t uid; Comm* comm; int have; uint64_t since_ns; };
   std::vector<Partial> partials;         // sockets grouped by connection uid
   int uds_fd = -1;                       // listener of the same-host side channel
   uint64_t nvl_token = 0;
