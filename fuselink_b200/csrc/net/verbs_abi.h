@@ -2,7 +2,9 @@
 // that the plugin builds without rdma-core headers and loads without the library.  The reference vendors NCCL's
 // copy of these declarations for the same reason (src/extern/ibvcore.h:19-1058, src/extern/ibvwrap.h:30-90).
 //
-// Only the leading fields that are read or written are spelled out; the fast-path calls (poll, post send, post
+// Field order and enum values were checked against that copy (context function table slots 11 / 25 / 26, work request,
+// completion, queue-pair attribute, port and device attribute layouts).  Only the leading fields that are read or
+// written are spelled out; the fast-path calls (poll, post send, post
 // receive) are inline in the public header and go through the function table inside the context, whose slots
 // are addressed by index below.
 #pragma once
@@ -97,6 +99,7 @@ struct ibv_qp_init_attr {
   ibv_qp_cap cap;
   int qp_type;
   int sq_sig_all;
+  void* reserved;                 // older vendor stacks read one more pointer here (XRC domain): keep it zero
 };
 
 struct ibv_global_route { ibv_gid dgid; uint32_t flow_label; uint8_t sgid_index, hop_limit, traffic_class; };
