@@ -471,6 +471,7 @@ ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out) {
     c->ctrl_fd = fd;
     c->stage = 0;
     c->io_done = 0;
+    c->since_ns = now_ns();
     lc->pending.push_back(c);
   }
   for (size_t i = 0; i < lc->pending.size();) {
@@ -480,6 +481,11 @@ ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out) {
       rdma_close(c);
       lc->pending.erase(lc->pending.begin() + i);
     };
+    const uint64_t age = now_ns() - c->since_ns;
+    if ((c->stage == 0 && age > kHelloTimeoutNs) || age > kPartialTimeoutNs) {
+      drop("bootstrap stalled");
+      continue;
+    }
     if (c->stage == 0) {
       static_assert(sizeof(Hello) <= sizeof(RdmaConnInfo), "hello is staged in the info buffer");
       const int rc = io_step(c->ctrl_fd, &c->theirs, sizeof(Hello), &c->io_done, false);

@@ -143,6 +143,7 @@ struct RdmaComm {
   // bootstrap
   int stage = 0;
   size_t io_done = 0;
+  uint64_t since_ns = 0;                  // accepted at (receiver): a bootstrap that stalls is dropped
   RdmaConnInfo mine, theirs;
 };
 
