@@ -13,6 +13,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <mutex>
 
 #include "params.h"
 #include "../mem/vmm.h"
@@ -127,6 +128,35 @@ static void fail(Comm* c, ncclResult_t why, const char* what) {
 }
 
 static std::atomic<uint64_t> g_failovers{0};
+
+// Line rate of the virtual NICs (FUSELINK_TCP_NIC_MBPS): one token bucket per NIC index, shared by every connection of
+// the process, so that experiments on one machine see what several NICs of limited speed give: a single path is held
+// to the rate of its NIC, stripes over idle NICs add up.
+namespace {
+struct NicBucket {
+  std::mutex mu;
+  double tokens = 0;          // bytes that may be sent now
+  uint64_t last_ns = 0;
+};
+NicBucket g_nic[kMaxDev];
+
+size_t nic_allowance(int dev, size_t want) {
+  const int64_t mbps = params().nic_mbps;
+  if (mbps <= 0) return want;
+  NicBucket& b = g_nic[dev];
+  std::lock_guard<std::mutex> l(b.mu);
+  const uint64_t now = now_ns();
+  const double rate = (double)mbps * 1e6;                      // bytes per second
+  if (b.last_ns == 0) b.last_ns = now;
+  b.tokens += rate * (double)(now - b.last_ns) * 1e-9;
+  b.last_ns = now;
+  const double burst = rate * 2e-3;                            // at most 2 ms worth of line rate in one go
+  if (b.tokens > burst) b.tokens = burst;
+  const size_t ok = b.tokens < 1.0 ? 0 : (size_t)b.tokens < want ? (size_t)b.tokens : want;
+  b.tokens -= (double)ok;
+  return ok;
+}
+}  // namespace
 uint64_t failover_count() { return g_failovers.load(); }
 
 int next_alive_dev(const Comm* c, int from) {
@@ -220,6 +250,8 @@ static void sender_push(Comm* c, ConnManager* cm) {
           if (!failover_tx(c, cm, d, "injected link failure")) { fail(c, ncclSystemError, "injected link failure"); return; }
           break;
         }
+        want = nic_allowance(d, want);
+        if (want == 0) break;                                  // this NIC is at its line rate: come back later
         ssize_t r = nb_send(s.fd, rq->data + st.hdr.offset + st.sent, want);
         if (r < 0) {
           if (!failover_tx(c, cm, d, "send failed")) { fail(c, ncclRemoteError, "data connection lost while sending"); return; }

@@ -316,3 +316,22 @@ def test_stray_and_malformed_connections_do_not_disturb_a_transfer(transport):
                 rx.kill()
         assert tx.returncode == 0, (tx.stdout, tx.stderr)
         assert rx.returncode == 0 and "OK received" in out, (out, err)
+
+
+def _xfer_gbs(out):
+    line = [l for l in out.splitlines() if l.startswith("OK ")][0]
+    return float(line.split("(")[2].split()[0])
+
+
+def test_striping_over_rate_limited_nics_adds_their_bandwidth():
+    """The reference's central claim in miniature: one transfer held to the line rate of its own NIC gets the sum of the
+    rates of the idle NICs it is striped over.  Eight virtual NICs of 200 MB/s each; degree 1, 2 and 4."""
+    got = {}
+    for degree in (1, 2, 4):
+        env = {"FUSELINK_TCP_NDEV": "8", "FUSELINK_TCP_NIC_MBPS": "200", "NCCL_FUSELINK_DEGREE": str(degree), "NCCL_FUSELINK_STEP": "1",
+               "FUSELINK_MIN_STRIPE_BYTES": "65536"}
+        tx, rx = _pair([96 << 20], env=env, common=["--chunk", "1048576", "--inflight", "8"], timeout=120)
+        assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+        got[degree] = _xfer_gbs(rx[1])
+    assert 0.15 < got[1] < 0.26, got                       # one NIC: its 0.2 GB/s
+    assert got[2] > 1.6 * got[1] and got[4] > 3.0 * got[1], got
