@@ -50,6 +50,17 @@ int ConnManager::bid_tx(int channel, int own_dev, int proposed) {
   return proposed;
 }
 
+int ConnManager::borrow_tx(int own_dev, uint64_t used_mask, int after) {
+  if (!mon_ || ndev_ <= 1) return -1;
+  const int p = fl_monitor_borrow_idle(mon_, FL_DIR_TX, own_dev, after, ~used_mask, fl_monitor_now_ns());
+  if (p >= 0) decisions_++;
+  return p >= ndev_ ? -1 : p;
+}
+
+void ConnManager::release_tx(int dev) {
+  if (mon_ && dev >= 0) fl_monitor_release(mon_, FL_DIR_TX, dev);
+}
+
 void ConnManager::mark_tx(int dev, uint64_t bytes) { if (mon_) fl_monitor_post_bytes(mon_, FL_DIR_TX, dev, bytes, fl_monitor_now_ns()); }
 void ConnManager::done_tx(int dev, uint64_t bytes) { if (mon_) fl_monitor_complete_bytes(mon_, FL_DIR_TX, dev, bytes, fl_monitor_now_ns()); }
 void ConnManager::mark_rx(int dev, uint64_t bytes) { if (mon_) fl_monitor_post_bytes(mon_, FL_DIR_RX, dev, bytes, fl_monitor_now_ns()); }

@@ -32,6 +32,10 @@ class ConnManager {
   int refresh_rx(int channel, int own_dev, int current, uint64_t tx_mask, bool quiescent);
   // Sender side: accept the receiver's proposal if that device is usable for tx, else fall back to own_dev.
   int bid_tx(int channel, int own_dev, int proposed);
+  // Sender side, stripes after the first: an idle device (tx direction) outside `used_mask`, borrowed from the monitor;
+  // -1 when the monitor is off or nothing is idle (the caller then walks on by NCCL_FUSELINK_STEP).  `release_tx` gives it back.
+  int borrow_tx(int own_dev, uint64_t used_mask, int after);
+  void release_tx(int dev);
   // Activity stamps (the "todo: update nic activities" of src/plugin.cc:1812).
   void mark_tx(int dev, uint64_t bytes_posted);
   void done_tx(int dev, uint64_t bytes);

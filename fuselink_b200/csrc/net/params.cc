@@ -82,6 +82,7 @@ const Params& params() {
   p.nvl = param_i64("FUSELINK_NVL", 1);
   p.remap = param_i64("FUSELINK_REMAP", 1);
   p.nic_mbps = param_i64("FUSELINK_TCP_NIC_MBPS", 0);
+  p.nic_shm = param_str("FUSELINK_TCP_NIC_SHM", "");
   p.connect_retries = param_i64("FUSELINK_CONNECT_RETRIES", 20000);
   p.failover = param_i64("FUSELINK_FAILOVER", 1);
   p.fault_bad_rkey_after = param_i64("FUSELINK_FAULT_BAD_RKEY_AFTER", 0);

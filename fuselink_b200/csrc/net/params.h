@@ -38,6 +38,7 @@ struct Params {
   int64_t nvl;                 // FUSELINK_NVL (1): same-host direct path, receive buffers exported as cuMem handles
   int64_t remap;               // FUSELINK_REMAP (1): re-home a registered CUDA buffer onto the relay GPU
   int64_t nic_mbps;            // FUSELINK_TCP_NIC_MBPS (0 = unlimited): line rate of every virtual NIC in MB/s, per process (experiments)
+  std::string nic_shm;         // FUSELINK_TCP_NIC_SHM (""): POSIX shm name; with it the line-rate buckets are shared by every process that names it
   int64_t connect_retries;     // FUSELINK_CONNECT_RETRIES (20000): refused connects are retried this many times, 1 ms apart (the reference's budget, src/extern/socket.h:15-17)
   int64_t failover;            // FUSELINK_FAILOVER (1): a broken data socket's stripes are re-sent on another device instead of failing the connection
   int64_t fault_bad_rkey_after; // FUSELINK_FAULT_BAD_RKEY_AFTER (0): test hook, the Nth RDMA message carries a wrong remote key

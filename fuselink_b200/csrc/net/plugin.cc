@@ -772,7 +772,13 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
   const uint64_t per = nstripes > 1 ? ((uint64_t)size / (uint64_t)nstripes) & ~127ull : (uint64_t)size;  // 128-B multiples (src/plugin.cc:1467-1472)
   uint64_t off = 0;
   int dev = first;
+  uint64_t used = 0;
   for (int s = 0; s < nstripes; ++s) {
+    if (s > 0) {                                      // further stripes go to devices the monitor knows to be idle
+      const int b = g_cm->borrow_tx(c->own_dev, used, dev);
+      if (b >= 0 && c->data[b].fd >= 0) dev = b;
+      else if (b >= 0) g_cm->release_tx(b);
+    }
     dev = next_alive_dev(c, dev);                     // a device whose socket broke earlier is skipped
     if (dev < 0) {
       r->used = false;
@@ -790,6 +796,7 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
     st.hdr.tx_mask = mask;
     off += st.hdr.len;
     r->stripes.push_back(st);
+    used |= 1ull << dev;
     dev = (dev + (int)(p.step > 0 ? p.step : 1)) % c->ndev;
   }
   for (size_t s = 0; s < r->stripes.size(); ++s) {

@@ -611,7 +611,13 @@ ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int 
 
   uint64_t off = 0;
   int dev = first, piece = 0;
+  uint64_t used = 0;
   for (int s = 0; s < nstripes; ++s) {
+    if (s > 0) {                              // further stripes go to devices the monitor knows to be idle
+      const int b = cm->borrow_tx(c->own_dev, used, dev);
+      if (b >= 0 && b < c->ndev && !c->dead[b]) dev = b;
+      else if (b >= 0) cm->release_tx(b);
+    }
     dev = rdma_next_alive(c, dev);            // devices given up earlier are skipped
     if (dev < 0) {
       fail(c, ncclRemoteError, "every device of the connection is gone");
@@ -626,6 +632,7 @@ ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int 
       r->pieces.push_back(pc);
       off += len;
     }
+    used |= 1ull << dev;
     dev = (dev + (int)(p.step > 0 ? p.step : 1)) % c->ndev;
   }
   for (int pi = 0; pi < npieces; ++pi) {

@@ -335,3 +335,66 @@ def test_striping_over_rate_limited_nics_adds_their_bandwidth():
         got[degree] = _xfer_gbs(rx[1])
     assert 0.15 < got[1] < 0.26, got                       # one NIC: its 0.2 GB/s
     assert got[2] > 1.6 * got[1] and got[4] > 3.0 * got[1], got
+
+
+def _two_jobs(env, size=48 << 20):
+    """Two sender/receiver pairs at the same time (four processes); returns the transfer rate each receiver saw."""
+    procs, dirs = [], []
+    try:
+        for j in range(2):
+            d = tempfile.mkdtemp()
+            dirs.append(d)
+            hf = os.path.join(d, "handle")
+            e = dict(os.environ, NCCL_SOCKET_IFNAME="lo", **env)
+            args = ["--chunk", "1048576", "--inflight", "8", str(size)]
+            rx = subprocess.Popen([HARNESS, PLUGIN, "recv", hf, *args], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+            tx = subprocess.Popen([HARNESS, PLUGIN, "send", hf, *args], env=e, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+            procs.append((tx, rx))
+        rates = []
+        for tx, rx in procs:
+            txo, txe = tx.communicate(timeout=180)
+            rxo, rxe = rx.communicate(timeout=180)
+            assert tx.returncode == 0 and rx.returncode == 0, (txo, txe, rxo, rxe)
+            rates.append(_xfer_gbs(rxo))
+        return rates
+    finally:
+        import shutil
+        for tx, rx in procs:
+            for p in (tx, rx):
+                if p.poll() is None:
+                    p.kill()
+        for d in dirs:
+            shutil.rmtree(d, ignore_errors=True)
+
+
+def test_two_jobs_contend_for_one_nic_unless_the_monitor_is_shared():
+    """The contention scenario of the reference's two-task experiment (experiments/serving/run_test_twotask.sh): two jobs
+    whose traffic would land on the same NIC.  The NICs are shared between the processes (line-rate buckets in shared
+    memory, 200 MB/s each).  Without the monitor both jobs sit on NIC 0 and split it; with one monitor table shared by
+    all four processes each job takes an idle NIC and runs at line rate."""
+    import uuid
+    tag = uuid.uuid4().hex[:10]
+    nic_shm, mon_shm = f"/fl_nic_{tag}", f"/fl_mon_{tag}"
+    base = {"FUSELINK_TCP_NDEV": "8", "FUSELINK_TCP_NIC_MBPS": "200", "FUSELINK_TCP_NIC_SHM": nic_shm, "NCCL_FUSELINK_DEGREE": "1"}
+    daemon = None
+    try:
+        alone = _two_jobs(dict(base, FUSELINK_MONITOR="0"))
+        exe = os.path.join(os.path.dirname(HARNESS), "fuselink-monitor")
+        daemon = subprocess.Popen([exe, "--shm", mon_shm, "--groups", "8", "--seconds", "120"], stdout=subprocess.PIPE, text=True)
+        daemon.stdout.readline()                                   # table is up
+        shared = _two_jobs(dict(base, FUSELINK_MONITOR_SHM=mon_shm))
+        striped = _two_jobs(dict(base, FUSELINK_MONITOR_SHM=mon_shm, NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536"))
+    finally:
+        if daemon is not None:
+            daemon.terminate()
+            daemon.wait(timeout=10)
+        for n in (nic_shm, mon_shm):
+            try:
+                os.unlink("/dev/shm" + n)
+            except OSError:
+                pass
+    assert sum(alone) < 0.26 and max(alone) < 0.19, alone         # one 0.2 GB/s NIC for both
+    assert min(shared) > 0.16, shared                              # a NIC each
+    assert sum(shared) > 1.5 * sum(alone), (alone, shared)
+    # degree 2: the second stripe of each job goes to a NIC the shared table shows idle, not blindly to the neighbour's
+    assert min(striped) > 0.3, striped
