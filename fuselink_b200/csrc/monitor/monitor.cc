@@ -257,6 +257,22 @@ int fl_monitor_borrow_idle(FlMonitor* m, int dir, int group, int primary, uint64
   return -1;
 }
 
+int fl_monitor_claim(FlMonitor* m, int dir, int path, int owner, uint64_t now_ns) {
+  Slot* s = slot_of(m, dir, path);
+  if (!s) return 0;
+  uint32_t expect = FL_PATH_IDLE;
+  if (s->status.compare_exchange_strong(expect, FL_PATH_BORROWED, std::memory_order_acq_rel)) {
+    s->borrower.store(owner, std::memory_order_relaxed);
+    s->last_active_ns.store(now_ns, std::memory_order_relaxed);
+    return 1;
+  }
+  if (expect == FL_PATH_BORROWED && s->borrower.load(std::memory_order_relaxed) == owner) {
+    s->last_active_ns.store(now_ns, std::memory_order_relaxed);
+    return 1;
+  }
+  return 0;
+}
+
 void fl_monitor_release(FlMonitor* m, int dir, int path) {
   Slot* s = slot_of(m, dir, path);
   if (!s) return;

@@ -54,6 +54,10 @@ void fl_monitor_attach_counters(FlMonitor* m, int dir, const volatile uint64_t* 
 // Returns the path index or -1.  The first idle candidate after `primary` (round-robin) wins.
 int fl_monitor_borrow_idle(FlMonitor* m, int dir, int group, int primary, uint64_t mask, uint64_t now_ns);
 void fl_monitor_release(FlMonitor* m, int dir, int path);
+// Take a path for oneself without competing for it: succeeds (1) when the path is idle (it becomes BORROWED by `owner`) or
+// already held by `owner`, fails (0) when somebody else is active on it.  The claim lapses like any lease.  `owner` is any
+// id that is unique among the users of the table (a process id).
+int fl_monitor_claim(FlMonitor* m, int dir, int path, int owner, uint64_t now_ns);
 void fl_monitor_mark_dead(FlMonitor* m, int dir, int path, int dead);
 
 // observation

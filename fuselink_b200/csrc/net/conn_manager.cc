@@ -1,10 +1,17 @@
 #include "conn_manager.h"
+#include <unistd.h>
+
 #include "logging.h"
+#include "params.h"
 
 namespace flnet {
 
 ConnManager::ConnManager(int ndev, int priority_dev, bool use_monitor, const char* shm_name, int timeout_us)
     : ndev_(ndev), priority_dev_(priority_dev) {
+  for (auto& dir : own_out_)
+    for (auto& v : dir) v.store(0, std::memory_order_relaxed);
+  prefer_own_ = param_i64("FUSELINK_PREFER_OWN", 1) != 0;
+  owner_id_ = 0x40000000 | (int)(getpid() & 0x3fffffff);    // never equal to a group index
   if (use_monitor && ndev > 0) {
     const bool shared = shm_name && shm_name[0];
     if (shared) mon_ = fl_monitor_open(shm_name, 0, ndev, 1, timeout_us);      // a daemon owns the table
@@ -29,6 +36,10 @@ int ConnManager::refresh_rx(int channel, int own_dev, int current, uint64_t tx_m
   }
   const uint64_t now = fl_monitor_now_ns();
   if (current >= 0 && current != own_dev) fl_monitor_release(mon_, FL_DIR_RX, current);
+  if (prefer_own_ && own_dev >= 0 && own_dev < 64 && fl_monitor_claim(mon_, FL_DIR_RX, own_dev, owner_id_, now)) {
+    decisions_++;
+    return own_dev;             // nobody else is on the affine device: it is now held by this process (one atomic claim,
+  }                             // so two jobs that start together cannot both conclude that it is free)
   const int p = fl_monitor_borrow_idle(mon_, FL_DIR_RX, own_dev, own_dev + channel, tx_mask, now);
   decisions_++;
   if (p < 0) {
@@ -61,10 +72,29 @@ void ConnManager::release_tx(int dev) {
   if (mon_ && dev >= 0) fl_monitor_release(mon_, FL_DIR_TX, dev);
 }
 
-void ConnManager::mark_tx(int dev, uint64_t bytes) { if (mon_) fl_monitor_post_bytes(mon_, FL_DIR_TX, dev, bytes, fl_monitor_now_ns()); }
-void ConnManager::done_tx(int dev, uint64_t bytes) { if (mon_) fl_monitor_complete_bytes(mon_, FL_DIR_TX, dev, bytes, fl_monitor_now_ns()); }
-void ConnManager::mark_rx(int dev, uint64_t bytes) { if (mon_) fl_monitor_post_bytes(mon_, FL_DIR_RX, dev, bytes, fl_monitor_now_ns()); }
-void ConnManager::done_rx(int dev, uint64_t bytes) { if (mon_) fl_monitor_complete_bytes(mon_, FL_DIR_RX, dev, bytes, fl_monitor_now_ns()); }
+void ConnManager::mark_tx(int dev, uint64_t bytes) {
+  if (!mon_) return;
+  if (dev >= 0 && dev < 64) own_out_[FL_DIR_TX][dev].fetch_add((int64_t)bytes, std::memory_order_relaxed);
+  fl_monitor_post_bytes(mon_, FL_DIR_TX, dev, bytes, fl_monitor_now_ns());
+}
+void ConnManager::done_tx(int dev, uint64_t bytes) {
+  if (!mon_) return;
+  if (dev >= 0 && dev < 64) own_out_[FL_DIR_TX][dev].fetch_sub((int64_t)bytes, std::memory_order_relaxed);
+  fl_monitor_complete_bytes(mon_, FL_DIR_TX, dev, bytes, fl_monitor_now_ns());
+}
+void ConnManager::touch_rx(int dev) {
+  if (mon_) fl_monitor_mark_active(mon_, FL_DIR_RX, dev, fl_monitor_now_ns());
+}
+void ConnManager::mark_rx(int dev, uint64_t bytes) {
+  if (!mon_) return;
+  if (dev >= 0 && dev < 64) own_out_[FL_DIR_RX][dev].fetch_add((int64_t)bytes, std::memory_order_relaxed);
+  fl_monitor_post_bytes(mon_, FL_DIR_RX, dev, bytes, fl_monitor_now_ns());
+}
+void ConnManager::done_rx(int dev, uint64_t bytes) {
+  if (!mon_) return;
+  if (dev >= 0 && dev < 64) own_out_[FL_DIR_RX][dev].fetch_sub((int64_t)bytes, std::memory_order_relaxed);
+  fl_monitor_complete_bytes(mon_, FL_DIR_RX, dev, bytes, fl_monitor_now_ns());
+}
 
 uint64_t ConnManager::tx_mask(int own_dev) {
   if (!mon_) return ~0ull;    // the reference's placeholder value (src/fuselink.h:261-267)

@@ -25,7 +25,9 @@ class ConnManager {
   int priority_dev() const { return priority_dev_; }
   FlMonitor* monitor() { return mon_; }
 
-  // Receiver side: device that should carry the next message of `channel`.  `current` is the device in
+  // Receiver side: device that should carry the next message of `channel`.  The own (affine) device is kept while the
+  // shared table shows no load on it besides this process's own; otherwise an idle device of another group is borrowed
+  // (the reference's intended getIdleNicRx, src/fuselink.h:239-243).  FUSELINK_PREFER_OWN=0 always tries to borrow first.  `current` is the device in
   // use (or -1); `tx_mask` is the sender's last advertised availability mask.  A new device is looked for
   // only when `quiescent` (nothing posted is still incomplete), as the reference does every 8 completions
   // when received == done (src/plugin.cc:1700-1716).
@@ -40,6 +42,7 @@ class ConnManager {
   void mark_tx(int dev, uint64_t bytes_posted);
   void done_tx(int dev, uint64_t bytes);
   void mark_rx(int dev, uint64_t bytes_posted);
+  void touch_rx(int dev);                    // a receive was posted with this device proposed: activity stamp only
   void done_rx(int dev, uint64_t bytes);
   // 64-bit mask of devices this process considers available for tx (bit set = idle or own)
   uint64_t tx_mask(int own_dev);
@@ -51,6 +54,9 @@ class ConnManager {
   int ndev_, priority_dev_;
   FlMonitor* mon_ = nullptr;
   std::atomic<uint64_t> decisions_{0}, fallbacks_{0};   // entered from every proxy thread
+  std::atomic<int64_t> own_out_[2][64];                // bytes this process has posted and not completed, per direction and device
+  int owner_id_ = 0;                                    // identifies this process in the shared table
+  bool prefer_own_ = true;                              // FUSELINK_PREFER_OWN (1): stay on the own device while nobody else loads it
 };
 
 }  // namespace flnet

@@ -774,10 +774,20 @@ ncclResult_t fl_isend(void* send_comm, void* data, int size, int tag, void* mhan
   int dev = first;
   uint64_t used = 0;
   for (int s = 0; s < nstripes; ++s) {
-    if (s > 0) {                                      // further stripes go to devices the monitor knows to be idle
-      const int b = g_cm->borrow_tx(c->own_dev, used, dev);
-      if (b >= 0 && c->data[b].fd >= 0) dev = b;
-      else if (b >= 0) g_cm->release_tx(b);
+    if (s > 0) {
+      // further stripes go to a device the monitor showed idle when the connection first needed it; it is kept (its
+      // lease is renewed by the traffic itself) so that concurrent jobs settle on disjoint devices
+      int& held = c->extra_dev[s];
+      if (held >= 0 && (c->data[held].fd < 0 || ((used >> held) & 1ull))) {
+        g_cm->release_tx(held);
+        held = -1;
+      }
+      if (held < 0) {
+        const int b = g_cm->borrow_tx(c->own_dev, used, dev);
+        if (b >= 0 && c->data[b].fd >= 0) held = b;
+        else if (b >= 0) g_cm->release_tx(b);
+      }
+      if (held >= 0) dev = held;
     }
     dev = next_alive_dev(c, dev);                     // a device whose socket broke earlier is skipped
     if (dev < 0) {
@@ -899,7 +909,7 @@ ncclResult_t fl_irecv(void* recv_comm, int n, void** data, int* sizes, int* tags
     ScopedTimer tp(&c->timers, T_POST_DESC, params().timers != 0);
     const uint8_t* p = reinterpret_cast<const uint8_t*>(&d);
     c->ctrl_tx.insert(c->ctrl_tx.end(), p, p + sizeof d);
-    g_cm->mark_rx(c->cur_dev, r->size);
+    g_cm->touch_rx(c->cur_dev);                 // bytes are accounted on the device their stripes really arrive on
     c->posted++;
     comm_progress(c, g_cm);
   }
@@ -942,8 +952,6 @@ ncclResult_t fl_test(void* request, int* done, int* sizes) {
     if (!r->is_send) {
       c->completed++;
       c->n_finished++;
-      // the posted size was reserved on the device; what did not arrive will never arrive
-      if (r->total < r->size) g_cm->done_rx(c->cur_dev, r->size - r->total);
     }
     r->used = false;
     return ncclSuccess;
@@ -961,9 +969,12 @@ ncclResult_t fl_test(void* request, int* done, int* sizes) {
 
 ncclResult_t fl_close_send(void* send_comm) {
   if (g_rdma) {
-    rdma_close(reinterpret_cast<RdmaComm*>(send_comm));
+    RdmaComm* rc = reinterpret_cast<RdmaComm*>(send_comm);
+    if (rc && g_cm) for (int d : rc->extra_dev) if (d >= 0) g_cm->release_tx(d);
+    rdma_close(rc);
     return ncclSuccess;
   }
+  if (send_comm && g_cm) for (int d : reinterpret_cast<Comm*>(send_comm)->extra_dev) if (d >= 0) g_cm->release_tx(d);
   comm_close(reinterpret_cast<Comm*>(send_comm));
   return ncclSuccess;
 }

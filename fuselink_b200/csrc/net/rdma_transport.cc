@@ -613,10 +613,18 @@ ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int 
   int dev = first, piece = 0;
   uint64_t used = 0;
   for (int s = 0; s < nstripes; ++s) {
-    if (s > 0) {                              // further stripes go to devices the monitor knows to be idle
-      const int b = cm->borrow_tx(c->own_dev, used, dev);
-      if (b >= 0 && b < c->ndev && !c->dead[b]) dev = b;
-      else if (b >= 0) cm->release_tx(b);
+    if (s > 0) {                              // further stripes: a device the monitor showed idle, kept for the connection
+      int& held = c->extra_dev[s];
+      if (held >= 0 && (c->dead[held] || ((used >> held) & 1ull))) {
+        cm->release_tx(held);
+        held = -1;
+      }
+      if (held < 0) {
+        const int b = cm->borrow_tx(c->own_dev, used, dev);
+        if (b >= 0 && b < c->ndev && !c->dead[b]) held = b;
+        else if (b >= 0) cm->release_tx(b);
+      }
+      if (held >= 0) dev = held;
     }
     dev = rdma_next_alive(c, dev);            // devices given up earlier are skipped
     if (dev < 0) {

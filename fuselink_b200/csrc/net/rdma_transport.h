@@ -140,6 +140,8 @@ struct RdmaComm {
   // selection state (same meaning as in the TCP transport)
   int cur_dev = -1, n_finished = 0, posted = 0, completed = 0;
   uint64_t peer_tx_mask = ~0ull, msg_index = 0;
+  int extra_dev[kMaxDev];                 // sender: device borrowed for stripe k > 0, kept for the life of the connection
+  RdmaComm() { for (int& d : extra_dev) d = -1; }
   // bootstrap
   int stage = 0;
   size_t io_done = 0;

@@ -327,6 +327,7 @@ static bool failover_rx(Comm* c, ConnManager* cm, int d) {
   DataSock& s = c->data[d];
   close(s.fd);
   s.fd = -1;
+  if (s.rx_in_payload) cm->done_rx(d, s.rx_hdr.len - s.rx_payload_got);   // what will never arrive here any more
   s.rx_in_payload = false;
   s.rx_hdr_got = 0;
   s.rx_payload_got = 0;
@@ -373,11 +374,12 @@ static void receiver_pull(Comm* c, ConnManager* cm) {
           rq.moved = rq.total;
           rq.done = true;
           rq.last_progress_ns = now_ns();
-          cm->done_rx(d, rq.total);
+          cm->touch_rx(d);
           continue;
         }
         s.rx_in_payload = true;
         s.rx_payload_got = 0;
+        cm->mark_rx(d, s.rx_hdr.len);                 // this stripe is now in flight on device d
         if (s.rx_hdr.len == 0) {
           s.rx_in_payload = false;
           stripe_arrived(rq, s.rx_hdr.offset, 0);

@@ -142,6 +142,8 @@ struct Comm {
   uint64_t post_seq = 0;
   uint64_t peer_tx_mask = ~0ull;         // receiver: last mask advertised by the sender (txAvailable)
   uint64_t msg_index = 0;
+  int extra_dev[kMaxDev];                // sender: device borrowed for stripe k > 0, kept for the life of the connection (-1: none yet)
+  Comm() { for (int& d : extra_dev) d = -1; }
   // connect progress
   int connect_stage = 0;
   std::vector<int> pending_fds;

@@ -141,7 +141,7 @@ def test_device_failure_on_the_sender_moves_pieces_to_another_device():
     the receiver counts each piece once, and every byte arrives."""
     env = dict(SOFT, NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536", FL_HARNESS_VERBOSE="1", FUSELINK_NET_TIMEOUT_MS="8000")
     tx, rx = _pair([16 << 20, 1 << 20, 7], env=env, common=["--chunk", "524288", "--inflight", "8"], timeout=90,
-                   env_send={"FUSELINK_SOFT_FAULT_DEV": "1", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
+                   env_send={"FUSELINK_SOFT_FAULT_DEV": "0", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     assert "RDMA-FAILOVERS" in tx[1] and "is given up; traffic moves to device" in tx[2], tx
 
@@ -159,5 +159,5 @@ def test_device_failure_under_the_descriptor_writes_is_survived():
 def test_failover_can_be_switched_off():
     env = dict(SOFT, NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536", FUSELINK_FAILOVER="0", FUSELINK_NET_TIMEOUT_MS="2000")
     tx, rx = _pair([16 << 20], env=env, common=["--chunk", "524288", "--expect-error"], timeout=60,
-                   env_send={"FUSELINK_SOFT_FAULT_DEV": "1", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
+                   env_send={"FUSELINK_SOFT_FAULT_DEV": "0", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
     assert tx[0] == 0 and "EXPECTED-ERROR" in tx[1], tx
