@@ -29,6 +29,7 @@ void fl_monitor_bind(py::module& m) {
   m.def("monitor_borrow_idle", [](int64_t h, int64_t d, int64_t group, int64_t primary, uint64_t mask, uint64_t now) {
     return fl_monitor_borrow_idle(M(h), (int)d, (int)group, (int)primary, mask, now);
   });
+  m.def("monitor_claim", [](int64_t h, int64_t d, int64_t p, int64_t owner, uint64_t now) { return fl_monitor_claim(M(h), (int)d, (int)p, (int)owner, now); });
   m.def("monitor_release", [](int64_t h, int64_t d, int64_t p) { fl_monitor_release(M(h), (int)d, (int)p); });
   m.def("monitor_mark_dead", [](int64_t h, int64_t d, int64_t p, bool dead) { fl_monitor_mark_dead(M(h), (int)d, (int)p, dead); });
   m.def("monitor_status", [](int64_t h, int64_t d, int64_t p) { return fl_monitor_status(M(h), (int)d, (int)p); });

@@ -274,3 +274,19 @@ def test_selector_plans_partition_the_transfer_for_any_parameters():
             C.monitor_close(m, False)
 
     check()
+
+
+def test_claim_is_exclusive_and_lapses_like_a_lease():
+    m = C.monitor_open("", True, 4, 1, 160)
+    t = 2_000_000
+    assert C.monitor_claim(m, RX, 0, 111, t) == 1                    # idle -> held by owner 111
+    assert C.monitor_status(m, RX, 0) == BORROWED
+    assert C.monitor_claim(m, RX, 0, 111, t + 10 * US) == 1          # the holder may claim again
+    assert C.monitor_claim(m, RX, 0, 222, t + 20 * US) == 0          # anybody else may not
+    assert C.monitor_borrow_idle(m, RX, 1, 3, (1 << 64) - 1, t + 20 * US) != 0   # and it is not handed out as idle either
+    C.monitor_sweep(m, t + 10 * US + 160 * US)
+    assert C.monitor_status(m, RX, 0) == IDLE                        # nothing outstanding, no stamp for 160 us
+    assert C.monitor_claim(m, RX, 0, 222, t + 400 * US) == 1
+    C.monitor_mark_active(m, RX, 1, t)
+    assert C.monitor_claim(m, RX, 1, 111, t + US) == 0               # busy with somebody's traffic
+    C.monitor_close(m, False)
