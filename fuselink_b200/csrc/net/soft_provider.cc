@@ -26,6 +26,7 @@
 #include <vector>
 
 #include "logging.h"
+#include "nic_rate.h"
 #include "params.h"
 #include "rdma_provider.h"
 
@@ -360,7 +361,9 @@ class SoftProvider : public Provider {
         return;
       }
       if (m.sent < m.hdr.len) {
-        ssize_t r = send(q->out_fd, p + m.sent, m.hdr.len - m.sent, MSG_DONTWAIT | MSG_NOSIGNAL);
+        const size_t may = nic_allowance(q->dev, m.hdr.len - m.sent);   // emulated line rate of this device, if one is set
+        if (may == 0) break;
+        ssize_t r = send(q->out_fd, p + m.sent, may, MSG_DONTWAIT | MSG_NOSIGNAL);
         if (r < 0 && (errno == EAGAIN || errno == EWOULDBLOCK || errno == EINTR)) break;
         if (r <= 0) { fail_qp(q, kWcRetryExceeded); return; }
         m.sent += (size_t)r;

@@ -161,3 +161,16 @@ def test_failover_can_be_switched_off():
     tx, rx = _pair([16 << 20], env=env, common=["--chunk", "524288", "--expect-error"], timeout=60,
                    env_send={"FUSELINK_SOFT_FAULT_DEV": "0", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(3 << 20)})
     assert tx[0] == 0 and "EXPECTED-ERROR" in tx[1], tx
+
+
+def test_striping_over_rate_limited_devices_adds_their_bandwidth():
+    """Same experiment as on the TCP transport: eight software devices of 200 MB/s, one connection, degree 1 / 2 / 4."""
+    from test_plugin_cpu import _xfer_gbs
+    got = {}
+    for degree in (1, 2, 4):
+        env = dict(SOFT, FUSELINK_SOFT_NDEV="8", FUSELINK_TCP_NIC_MBPS="200", NCCL_FUSELINK_DEGREE=str(degree), FUSELINK_MIN_STRIPE_BYTES="65536")
+        tx, rx = _pair([64 << 20], env=env, common=["--chunk", "1048576", "--inflight", "8"], timeout=120)
+        assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+        got[degree] = _xfer_gbs(rx[1])
+    assert 0.15 < got[1] < 0.26, got
+    assert got[2] > 1.6 * got[1] and got[4] > 3.0 * got[1], got
