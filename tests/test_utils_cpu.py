@@ -61,3 +61,15 @@ def test_trace_recorder_writes_chrome_trace(tmp_path):
     ev = json.load(open(out))["traceEvents"]
     assert {e["ph"] for e in ev} == {"X", "i", "C"}
     assert [e for e in ev if e["ph"] == "X"][0]["dur"] >= 0
+
+
+def test_bench_reference_arm_reports_why_it_is_unavailable():
+    """`bench.py --impl reference` must print one JSON line with "impl": "reference" and exit 0 even without a GPU."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1"],
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
