@@ -18,6 +18,8 @@
 #include "logging.h"
 #include "nccl_net_abi.h"
 
+struct FlVmmRegion;   // csrc/mem/vmm.h
+
 namespace flnet {
 
 constexpr uint64_t kHandleMagic = 0x464c4e4b48444c31ull;  // "FLNKHDL1"
@@ -178,6 +180,25 @@ struct ListenComm {
   struct NvlPending { int fd; uint64_t uid; };
   std::vector<NvlPending> nvl_pending;   // side channels accepted, not yet matched to a connection
 };
+
+// What the transport needs to know about a registered buffer (plugin.cc owns the registration itself).
+struct TcpMem {
+  int type;                              // NCCL_PTR_HOST / NCCL_PTR_CUDA
+  ::FlVmmRegion* region;                 // buffer taken over by the cuMem layer, else null
+  uint32_t mr_id;                        // export id of that region; irecv sets it to 0 when the region turns out not to be exportable
+};
+
+// entry points (tcp_endpoints.cc)
+ncclResult_t tcp_listen(int dev, int ndev, int channel_id, bool offer_nvl, Handle* h, ListenComm** out);
+ncclResult_t tcp_connect(int dev, int ndev, bool want_nvl, Handle* h, Comm** out);     // re-entrant, *out null until connected
+ncclResult_t tcp_accept(ListenComm* lc, Comm** out);                                   // re-entrant
+ncclResult_t tcp_isend(Comm* c, ConnManager* cm, void* data, int size, int tag, const TcpMem* mem, Request** out);
+ncclResult_t tcp_irecv(Comm* c, ConnManager* cm, void* data, int size, int tag, TcpMem* mem, Request** out);
+ncclResult_t tcp_test(Request* r, ConnManager* cm, int* done, int* sizes);
+void tcp_close_listen(ListenComm* lc);
+uint64_t tcp_direct_bytes();                        // payload bytes / messages stored straight into a same-host peer's buffer
+uint64_t tcp_direct_msgs();
+uint64_t random_u64();
 
 // helpers shared with plugin.cc
 int set_nonblock_nodelay(int fd);
