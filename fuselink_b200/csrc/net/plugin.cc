@@ -5,25 +5,19 @@
 // rejected (src/plugin.cc:1449-1450,1879-1880).  A v8 table (size_t registration sizes) is exported too so
 // that current NCCL releases find a version they probe for.
 //
-// What differs: devices are the virtual NICs of a transport.  The TCP transport (tcp_transport.*) works on
-// any machine and is what the CPU tests drive; the verbs transport (ib_transport.*) is compiled in and
-// used only where libibverbs and RDMA devices exist.  Path selection goes through ConnManager and the
-// lock-free monitor instead of peeking into NCCL's private proxy structures (src/fuselink.h:18-37): the
-// plugin counts its own posted / completed requests to know when a connection is quiescent.
-#include <arpa/inet.h>
-#include <errno.h>
-#include <poll.h>
+// What differs: this file is the table, the registration of buffers and the dispatch to one of two transports.  The
+// TCP transport (tcp_endpoints.cc, tcp_transport.*) works on any machine; the RDMA transport (rdma_transport.*) drives
+// libibverbs devices where they exist (verbs_provider.cc) or a software NIC in tests (soft_provider.cc).  Path
+// selection goes through ConnManager and the lock-free monitor instead of peeking into NCCL's private proxy
+// structures (src/fuselink.h:18-37): each transport counts its own posted / completed requests to know when a
+// connection is quiescent.
 #include <stdio.h>
-#include <stdlib.h>
 #include <string.h>
-#include <sys/socket.h>
-#include <sys/un.h>
 #include <unistd.h>
 
 #include <atomic>
 #include <map>
 #include <mutex>
-#include <random>
 
 #include "conn_manager.h"
 #include "ib_transport.h"
@@ -38,7 +32,6 @@
 using namespace flnet;
 
 namespace {
-
 
 std::mutex g_mu;
 ConnManager* g_cm = nullptr;
