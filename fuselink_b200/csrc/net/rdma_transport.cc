@@ -144,7 +144,12 @@ bool post_piece(RdmaComm* c, RdmaRequest* r, int pi) {
     ++n;
   }
   const uint64_t wr_id = (uint64_t)r->slot | ((uint64_t)pi << 16) | ((uint64_t)pc.gen << 32);
-  const bool split = pc.len > (uint64_t)p.ib_ar_threshold;     // large: data write, then an empty write carrying the immediate
+  // With adaptive routing packets of one write may overtake each other, so a large payload goes as a plain write and
+  // the immediate follows in an empty write of its own; NCCL_IB_ADAPTIVE_ROUTING = -2 means "on for InfiniBand, off for
+  // RoCE" (src/plugin.cc:96,253-254,1454-1462).  Without it one write-with-immediate carries the payload.
+  const int64_t ar_knob = p.ib_adaptive_routing;
+  const bool ar = ar_knob == -2 ? g_prov->device(dev).link == rdma::kLinkIB : ar_knob != 0;
+  const bool split = ar && pc.len > (uint64_t)p.ib_ar_threshold;
   if (split) {
     wr[n].wr_id = wr_id;
     wr[n].op = rdma::kWrite;

@@ -24,9 +24,23 @@ def test_bitwise_transfer_reference_config(abi):
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     msgs, pieces, wrs = _counters(tx[1])
     assert msgs == 1 + 2 + 128 and pieces == msgs                    # degree 1: one piece per chunk
-    # 4096 B is below the adaptive-routing threshold (one write-with-immediate), the others are a write plus an
-    # empty write-with-immediate; every message also carries its 16-byte size record
-    assert wrs == 2 + 130 * 3
+    # the software NIC is an Ethernet (RoCE-like) device: adaptive routing is off by default, so every message is its
+    # 16-byte size record plus one write-with-immediate that carries the payload
+    assert wrs == 131 * 2
+
+
+def test_adaptive_routing_splits_large_writes():
+    """NCCL_IB_ADAPTIVE_ROUTING=1: above NCCL_IB_AR_THRESHOLD the payload goes as a plain write followed by an empty
+    write-with-immediate; at or below it one write-with-immediate carries everything."""
+    env = dict(SOFT, NCCL_IB_ADAPTIVE_ROUTING="1")
+    tx, rx = _pair([4096, 1 << 20], env=env, common=["--chunk", "524288", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    msgs, pieces, wrs = _counters(tx[1])
+    assert msgs == 3 and wrs == 2 + 2 * 3
+    env = dict(SOFT, NCCL_IB_ADAPTIVE_ROUTING="1", NCCL_IB_AR_THRESHOLD=str(1 << 20))
+    tx, rx = _pair([4096, 1 << 20], env=env, common=["--chunk", "524288", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert _counters(tx[1])[2] == 3 * 2
 
 
 def test_odd_sizes_zero_length_and_many_in_flight():
