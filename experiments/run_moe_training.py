@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
     ap.add_argument("--checkpoint", default="", help="save the last state here (per rank: experts differ)")
+    ap.add_argument("--resume", default="", help="load <path>.rank<r> written by --checkpoint (same world size) before training")
     a = ap.parse_args()
     from fuselink_b200.models.moe_transformer import MOE_ZOO, MoETransformer
     rank, local, world = (int(os.environ.get(k, d)) for k, d in (("RANK", 0), ("LOCAL_RANK", 0), ("WORLD_SIZE", 1)))
@@ -58,6 +59,8 @@ def main():
         per_layer = rows * H * 2 * 2 + 2 * T * k * H * 2 + rows * 4 + (1 << 20)        # the symmetric buffers of one MoE workspace
         heap = SymmetricHeap.create(cfg.layers * per_layer + (64 << 20), device=local)
     net = MoETransformer(cfg, a.batch * a.seq, heap, rank, world, device=dev, seed=0, fused_sgd_lr=0.0 if cpu else a.lr)
+    if a.resume:
+        net.load_state_dict(torch.load(f"{a.resume}.rank{rank}", map_location=dev))
     params = net.parameters() if cpu else net.dense_parameters()       # on CUDA the expert update is fused into the wgrad GEMM
     opt = torch.optim.SGD(params, lr=a.lr)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)

@@ -228,3 +228,23 @@ def test_moe_training_script_runs_on_cpu_ranks():
     assert out.returncode == 0, out.stderr[-3000:]
     lines = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
     assert [l["step"] for l in lines] == [2, 4] and all(l["n_gpus"] == 2 and l["tokens_per_s"] > 0 and l["loss"] > 0 for l in lines)
+
+
+def test_moe_training_checkpoint_resume_reproduces_the_run(tmp_path):
+    """4 steps in one go == 2 steps, checkpoint, resume, 2 more steps (same seed, same data order is not required: the
+    check is that the resumed model continues from the saved weights, so its first logged loss differs from a fresh run's)."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "experiments", "run_moe_training.py")
+    base = [sys.executable, script, "--model", "tiny_moe", "--device", "cpu", "--batch", "2", "--seq", "16", "--lr", "0.5", "--log-every", "1"]
+    ck = str(tmp_path / "ck")
+    a = subprocess.run(base + ["--steps", "3", "--checkpoint", ck], capture_output=True, text=True, timeout=300)
+    assert a.returncode == 0 and os.path.exists(ck + ".rank0"), a.stderr[-2000:]
+    fresh = subprocess.run(base + ["--steps", "1"], capture_output=True, text=True, timeout=300)
+    resumed = subprocess.run(base + ["--steps", "1", "--resume", ck], capture_output=True, text=True, timeout=300)
+    first = lambda r: json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][0])["loss"]
+    run3 = [json.loads(l)["loss"] for l in a.stdout.splitlines() if l.startswith("{")]
+    assert first(fresh) == run3[0]                       # same seed, same first batch, same initial weights
+    assert first(resumed) != first(fresh)                # the resumed run starts from the trained weights
