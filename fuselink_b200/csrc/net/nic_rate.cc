@@ -56,7 +56,7 @@ size_t nic_allowance(int dev, size_t want) {
   int spins = 0;
   while (!b.lock.compare_exchange_weak(expect, 1, std::memory_order_acquire)) {
     expect = 0;
-    if (++spins > 100000) return 0;                            // a holder died: give up this round, never hang
+    if (++spins > 100000) return 0;                            // a holder died: give up for now, never hang
   }
   const uint64_t now = now_ns();
   const double rate = (double)mbps * 1e6;                      // bytes per second

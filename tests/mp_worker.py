@@ -45,7 +45,7 @@ def main():
             dist.all_to_all_single(ref, send.view(-1))
             torch.cuda.synchronize()
             assert torch.equal(recv.local.view(-1), ref), f"all-to-all {engine} mismatch on rank {rank}"
-            barrier(heap, "a2a-reuse")          # the receive buffer is reused by the next round
+            barrier(heap, "a2a-reuse")          # the receive buffer is reused by the next iteration
     heap.check_status("comm")
 
     # ---- MoE: fused path vs the PyTorch + NCCL formulation, same weights, same inputs ----------------------
