@@ -32,8 +32,11 @@ def main():
     ap.add_argument("--keep-intranode", action="store_true", help="do not disable NCCL's P2P / SHM transports")
     args = ap.parse_args()
     # the environment NCCL reads at communicator creation; the values are the reference script's
-    os.environ["LD_LIBRARY_PATH"] = LIB_DIR + ":" + os.environ.get("LD_LIBRARY_PATH", "")
-    os.environ.setdefault("NCCL_NET_PLUGIN", os.path.join(LIB_DIR, "libnccl-net-fuselink.so"))
+    # NCCL looks the plugin up by name (libnccl-net-<name>.so) with dlopen.  Loading the library first by its full path makes
+    # that lookup succeed whatever LD_LIBRARY_PATH was when the process started: the loader matches the soname.
+    plugin_path = os.path.join(LIB_DIR, "libnccl-net-fuselink.so")
+    preloaded = ctypes.CDLL(plugin_path, mode=ctypes.RTLD_GLOBAL)
+    os.environ.setdefault("NCCL_NET_PLUGIN", "fuselink")
     os.environ.setdefault("NCCL_P2P_NET_CHUNKSIZE", "524288")
     os.environ.setdefault("NCCL_NCHANNELS_PER_NET_PEER", "4")
     os.environ.setdefault("NCCL_MIN_NCHANNELS", "4")
@@ -80,7 +83,7 @@ def main():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         results.append({"bytes": 1 << lg, "ms": float(ms.item()), "GBps_per_direction": (1 << lg) / (float(ms.item()) / 1e3) / 1e9})
     # did the traffic go through the plugin?  NCCL and this handle share one loaded library.
-    lib = ctypes.CDLL(os.environ["NCCL_NET_PLUGIN"] if os.path.isabs(os.environ["NCCL_NET_PLUGIN"]) else os.path.join(LIB_DIR, "libnccl-net-fuselink.so"))
+    lib = preloaded
     lib.fuselink_plugin_decisions.restype = ctypes.c_ulonglong
     used = torch.tensor([int(lib.fuselink_plugin_decisions())], device=dev)
     dist.all_reduce(used)

@@ -181,7 +181,7 @@ def build_all(verbose: bool = False, jobs: int | None = None) -> dict:
     if net_objs:
         plug = LIB / "libnccl-net-fuselink.so"
         link(plug, net_objs + host_objs,
-             [CXX, "-shared", "-o", plug, *net_objs, *host_objs, "-ldl", "-lrt", "-lpthread"])
+             [CXX, "-shared", "-Wl,-soname,libnccl-net-fuselink.so", "-o", plug, *net_objs, *host_objs, "-ldl", "-lrt", "-lpthread"])
         mon_src = CSRC / "monitor" / "monitor_main.cc"
         if mon_src.exists():
             mon = LIB / "fuselink-monitor"
