@@ -523,13 +523,15 @@ ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out) {
         c->fifo_src_mr = rdma_reg(c->fifo_src, sizeof(RdmaDesc) * kMaxRequests);
         ok = c->done_mr && c->fifo_src_mr;
       }
+      ok = ok && connect_endpoints(c);
       if (ok) {
-        // zero-length receives for every write-with-immediate that can be outstanding, on every queue pair
+        // zero-length receives for every write-with-immediate that can be outstanding, on every queue pair.  (Receives
+        // cannot be posted to a queue pair that is still in the RESET state, hence after the transitions; no immediate
+        // can arrive earlier, because the sender only writes in answer to descriptors this side has not posted yet.)
         for (int d = 0; d < c->ndev && ok; ++d)
           for (int q = 0; q < c->nqps && ok; ++q)
             for (int k = 0; k < kMaxRequests && ok; ++k) ok = g_prov->post_recv(c->dev[d].qp[q], kWrRecv) == 0;
       }
-      ok = ok && connect_endpoints(c);
       if (ok && !params().gdr_flush_disable) {
         rdma::QpCaps fc;
         fc.max_send_wr = kMaxRequests;

@@ -188,3 +188,68 @@ def test_striping_over_rate_limited_devices_adds_their_bandwidth():
         got[degree] = _xfer_gbs(rx[1])
     assert 0.15 < got[1] < 0.26, got
     assert got[2] > 1.6 * got[1] and got[4] > 3.0 * got[1], got
+
+
+def _build_fake_ibverbs(tmp_path):
+    """tests/fake_ibverbs/fake_ibverbs.cc + the software NIC as `libibverbs.so.1` in a directory of its own."""
+    import shutil
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    net = os.path.join(root, "fuselink_b200", "csrc", "net")
+    cxx = next((c for c in (os.environ.get("CXX"), "g++", "/usr/bin/g++") if c and shutil.which(c)), None)
+    if cxx is None:
+        pytest.skip("no C++ compiler")
+    out = os.path.join(str(tmp_path), "libibverbs.so.1")
+    srcs = [os.path.join(root, "tests", "fake_ibverbs", "fake_ibverbs.cc")] + [os.path.join(net, f) for f in
+                                                                              ("soft_provider.cc", "nic_rate.cc", "params.cc", "logging.cc")]
+    b = subprocess.run([cxx, "-O1", "-g", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", out, *srcs, "-lrt"], capture_output=True, text=True, timeout=600)
+    assert b.returncode == 0, b.stderr[-3000:]
+    return str(tmp_path)
+
+
+def test_verbs_provider_end_to_end_against_a_fake_libibverbs(tmp_path):
+    """The libibverbs provider (dlopen, device / port discovery, NCCL_IB_HCA, queue pairs through INIT -> RTR -> RTS with the
+    attribute masks the library insists on, work-request and completion translation through the function table inside the
+    context) carrying real transfers: the library it loads is a stand-in with the real calling conventions."""
+    libdir = _build_fake_ibverbs(tmp_path)
+    env = {"FUSELINK_TRANSPORT": "rdma", "LD_LIBRARY_PATH": libdir + ":" + os.environ.get("LD_LIBRARY_PATH", ""), "FUSELINK_FAKE_IB_NDEV": "3",
+           "FUSELINK_SOFT_NDEV": "4", "NCCL_FUSELINK_DEGREE": "2", "FUSELINK_MIN_STRIPE_BYTES": "65536", "NCCL_IB_QPS_PER_CONNECTION": "2",
+           "FL_HARNESS_VERBOSE": "1"}
+    tx, rx = _pair([4096, 3 << 20, 0, 70001], env=env, common=["--chunk", "524288", "--inflight", "8"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "3 device(s) through the verbs provider" in tx[2] and "3 device(s) over RDMA" in tx[2], tx[2]
+    msgs, pieces, _ = _counters(tx[1])
+    assert msgs == 1 + 6 + 1 + 1 and pieces > msgs                   # stripes over two devices x two queue pairs
+    # the HCA filter picks devices by name, exactly
+    tx, rx = _pair([1 << 20], env=dict(env, NCCL_IB_HCA="=mlx5_1,2"), common=["--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "2 device(s) through the verbs provider" in tx[2]
+    # NCCL_IB_DISABLE=1 turns the provider off: the plugin falls back to TCP
+    tx, rx = _pair([1 << 20], env=dict(env, NCCL_IB_DISABLE="1", FUSELINK_TRANSPORT="auto"), common=["--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0 and "over TCP" in tx[2], (tx, rx)
+
+
+def test_properties_of_a_verbs_device(tmp_path):
+    """Speed from the width and rate codes (4x EDR = 100 Gb/s), the port that is down is skipped, maxComms = max_qp."""
+    import subprocess, sys, textwrap
+    libdir = _build_fake_ibverbs(tmp_path)
+    code = textwrap.dedent(f"""
+        import ctypes
+        lib = ctypes.CDLL({PLUGIN!r})
+        class Props(ctypes.Structure):
+            _fields_ = [("name", ctypes.c_char_p), ("pci", ctypes.c_char_p), ("guid", ctypes.c_uint64), ("ptr", ctypes.c_int), ("speed", ctypes.c_int),
+                        ("port", ctypes.c_int), ("latency", ctypes.c_float), ("maxComms", ctypes.c_int), ("maxRecvs", ctypes.c_int)]
+        class V6(ctypes.Structure):
+            _fields_ = [("name", ctypes.c_char_p), ("init", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)),
+                        ("devices", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(ctypes.c_int))),
+                        ("props", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_int, ctypes.POINTER(Props)))]
+        v6 = V6.in_dll(lib, "ncclNetPlugin_v6")
+        assert v6.init(None) == 0
+        n = ctypes.c_int(0); v6.devices(ctypes.byref(n))
+        p = Props(); assert v6.props(1, ctypes.byref(p)) == 0
+        print(n.value, p.name.decode(), p.speed, p.maxComms, p.maxRecvs, hex(p.guid))
+    """)
+    env = dict(os.environ, FUSELINK_TRANSPORT="rdma", LD_LIBRARY_PATH=libdir + ":" + os.environ.get("LD_LIBRARY_PATH", ""), FUSELINK_FAKE_IB_NDEV="2")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=60)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["2", "mlx5_1", "100000", "4096", "1", "0xfa4e000000000001"]
