@@ -22,6 +22,7 @@ constexpr uint32_t kInfoMagic = 0x464c5244u;              // "FLRD"
 constexpr uint64_t kWrFifo = 1ull << 62;                   // wr_id of a signalled descriptor write
 constexpr uint64_t kWrRecv = 1ull << 61;                   // wr_id of the anonymous zero-length receives
 constexpr uint64_t kWrFlush = 1ull << 60;                  // wr_id of a flush read (low bits: request slot)
+constexpr uint64_t kWrRecord = 1ull << 59;                 // wr_id of the unsignalled per-slot record write (a piece's own id may be 0)
 
 rdma::Provider* g_prov = nullptr;
 rdma::Pd* g_pd[kMaxDev];
@@ -133,7 +134,7 @@ bool post_piece(RdmaComm* c, RdmaRequest* r, int pi) {
   rdma::SendWr wr[3];
   int n = 0;
   if (pi == 0) {                            // the record for the slot travels ahead of the first immediate
-    wr[n].wr_id = 0;
+    wr[n].wr_id = kWrRecord;
     wr[n].op = rdma::kWrite;
     wr[n].laddr = &c->done_src[d.slot % kMaxRequests];
     wr[n].len = sizeof(RdmaDoneRec);
@@ -218,7 +219,7 @@ bool device_failed(RdmaComm* c, ConnManager* cm, int d, const rdma::Completion& 
     }
     return true;
   }
-  if ((wc.wr_id & kWrFifo) || wc.wr_id == 0) return true;   // wr_id 0: the unsignalled record write, its piece reports separately
+  if (wc.wr_id & (kWrFifo | kWrRecord)) return true;        // the unsignalled record write: its piece reports separately
   const uint32_t slot = (uint32_t)(wc.wr_id & 0xffffu), pi = (uint32_t)((wc.wr_id >> 16) & 0xffffu), gen = (uint32_t)((wc.wr_id >> 32) & 0xffu);
   RdmaRequest& r = c->reqs[slot % kMaxRequests];
   if (!r.used || !r.is_send || pi >= r.pieces.size()) return true;

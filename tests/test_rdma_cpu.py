@@ -253,3 +253,19 @@ def test_properties_of_a_verbs_device(tmp_path):
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=60)
     assert out.returncode == 0, out.stderr
     assert out.stdout.split() == ["2", "mlx5_1", "100000", "4096", "1", "0xfa4e000000000001"]
+
+
+def test_verbs_provider_error_completions_and_reads(tmp_path):
+    """Through the stand-in library too: a queue pair that breaks reports "retry exceeded" and its pieces move to another
+    device; the flush is an RDMA READ work request on a queue pair connected to itself."""
+    libdir = _build_fake_ibverbs(tmp_path)
+    env = {"FUSELINK_TRANSPORT": "rdma", "LD_LIBRARY_PATH": libdir + ":" + os.environ.get("LD_LIBRARY_PATH", ""), "FUSELINK_FAKE_IB_NDEV": "4",
+           "NCCL_FUSELINK_DEGREE": "2", "FUSELINK_MIN_STRIPE_BYTES": "65536", "FL_HARNESS_VERBOSE": "1", "FUSELINK_NET_TIMEOUT_MS": "8000"}
+    tx, rx = _pair([8 << 20, 9], env=env, common=["--chunk", "524288", "--inflight", "8"], timeout=90,
+                   env_send={"FUSELINK_SOFT_FAULT_DEV": "0", "FUSELINK_SOFT_FAULT_AFTER_BYTES": str(2 << 20)})
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "RDMA-FAILOVERS" in tx[1] and "completion status 12" in tx[2], tx
+    flush = dict(env, FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS="2", NCCL_GDR_FLUSH_DISABLE="0")
+    tx, rx = _pair([1 << 20], env=flush, common=["--device-buffers", "--chunk", "262144"], extra_recv=["--flush"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "FLUSHES 1" in rx[1]
