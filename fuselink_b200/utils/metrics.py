@@ -47,6 +47,28 @@ def render(C, mon: int, extra: Optional[dict] = None) -> str:
     return "\n".join(lines) + "\n"
 
 
+def plugin_counters(path: Optional[str] = None) -> dict:
+    """Counters of the ncclNet plugin as loaded in THIS process (NCCL and ``ctypes`` share one copy of the library):
+    selector decisions and fallbacks, stripes moved after a link failure, bytes stored through the same-host direct
+    path, RDMA messages / pieces / work requests.  Usable as ``extra`` of :func:`render` / :class:`MetricsServer`."""
+    import ctypes
+    import os
+    if path is None:
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libnccl-net-fuselink.so")
+    lib = ctypes.CDLL(path)
+    out = {}
+    for name in ("decisions", "fallbacks", "failovers", "direct_bytes", "direct_msgs"):
+        fn = getattr(lib, f"fuselink_plugin_{name}")
+        fn.restype = ctypes.c_ulonglong
+        out[f"plugin_{name}"] = int(fn())
+    lib.fuselink_rdma_failovers.restype = ctypes.c_ulonglong
+    out["plugin_rdma_failovers"] = int(lib.fuselink_rdma_failovers())
+    m, p, w = ctypes.c_ulonglong(), ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    lib.fuselink_rdma_counters(ctypes.byref(m), ctypes.byref(p), ctypes.byref(w))
+    out.update(plugin_rdma_messages=m.value, plugin_rdma_pieces=p.value, plugin_rdma_work_requests=w.value)
+    return out
+
+
 class MetricsServer:
     """``/metrics`` over HTTP on a background thread.  ``port=0`` picks a free port (see ``.port``)."""
 

@@ -290,3 +290,15 @@ def test_claim_is_exclusive_and_lapses_like_a_lease():
     C.monitor_mark_active(m, RX, 1, t)
     assert C.monitor_claim(m, RX, 1, 111, t + US) == 0               # busy with somebody's traffic
     C.monitor_close(m, False)
+
+
+def test_plugin_counters_are_readable_from_python():
+    from fuselink_b200.utils.metrics import plugin_counters, render
+    c = plugin_counters()
+    assert set(c) >= {"plugin_decisions", "plugin_fallbacks", "plugin_failovers", "plugin_direct_bytes", "plugin_rdma_pieces"}
+    assert all(isinstance(v, int) and v >= 0 for v in c.values())
+    m = C.monitor_open("", True, 2, 1, 160)
+    try:
+        assert "fuselink_plugin_failovers 0" in render(C, m, c)
+    finally:
+        C.monitor_close(m, False)
