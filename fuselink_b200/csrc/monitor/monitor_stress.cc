@@ -34,6 +34,20 @@ int main(int argc, char** argv) {
       }
     });
   }
+  // claimers: each wants "its own" path for itself; a claim that succeeds for two different owners at once is a violation
+  for (int o = 0; o < 3; ++o) {
+    ths.emplace_back([&, o]() {
+      const int owner = 1000 + o;
+      for (int i = 0; i < iters; ++i) {
+        const int p = (i + o) % npaths;
+        if (!fl_monitor_claim(m, FL_DIR_TX, p, owner, fl_monitor_now_ns())) continue;
+        grants.fetch_add(1);
+        if (holders[p].fetch_add(1) != 0) violations.fetch_add(1);
+        holders[p].fetch_sub(1);
+        fl_monitor_release(m, FL_DIR_TX, p);
+      }
+    });
+  }
   ths.emplace_back([&]() {
     for (int i = 0; i < iters; ++i) {
       fl_monitor_mark_active(m, FL_DIR_RX, i % npaths, fl_monitor_now_ns());
