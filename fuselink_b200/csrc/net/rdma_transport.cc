@@ -232,6 +232,7 @@ bool device_failed(RdmaComm* c, ConnManager* cm, int d, const rdma::Completion& 
 }
 
 void poll_all(RdmaComm* c, ConnManager* cm) {
+  ScopedTimer tm(&c->timers, T_PROGRESS, params().timers != 0);
   g_prov->progress();
   rdma::Completion wc[16];
   for (int d = 0; d < c->ndev; ++d) {
@@ -576,6 +577,7 @@ ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out) {
 // -----------------------------------------------------------------------------------------------------
 ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out) {
   *out = nullptr;
+  ScopedTimer tm(&c->timers, T_ISEND, params().timers != 0);
   if (c->error) return (ncclResult_t)c->error;
   if (size < 0 || !mr) return ncclInvalidArgument;
   poll_all(c, cm);
@@ -669,6 +671,7 @@ ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int 
 
 ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out) {
   *out = nullptr;
+  ScopedTimer tm(&c->timers, T_IRECV, params().timers != 0);
   if (c->error) return (ncclResult_t)c->error;
   if (size < 0 || !mr) return ncclInvalidArgument;
   RdmaRequest* r = get_request(c);
@@ -694,10 +697,13 @@ ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int 
   d->seq = idx + 1;
   r->fifo_idx = idx;
   if (c->dead[c->ctrl_dev] && rdma_next_alive(c, c->ctrl_dev) >= 0) c->ctrl_dev = rdma_next_alive(c, c->ctrl_dev);
-  if (!post_descriptor(c, idx)) {
-    fail(c, ncclSystemError, "descriptor write failed");
-    r->used = false;
-    return ncclSystemError;
+  {
+    ScopedTimer tp(&c->timers, T_POST_DESC, params().timers != 0);
+    if (!post_descriptor(c, idx)) {
+      fail(c, ncclSystemError, "descriptor write failed");
+      r->used = false;
+      return ncclSystemError;
+    }
   }
   c->fifo_tail++;
   cm->mark_rx(c->cur_dev, r->size);
@@ -709,6 +715,7 @@ ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int 
 
 ncclResult_t rdma_iflush(RdmaComm* c, ConnManager* cm, void* data, int size, RdmaMrSet* mr, RdmaRequest** out) {
   *out = nullptr;
+  ScopedTimer tm(&c->timers, T_FLUSH, params().timers != 0);
   if (!c->flush_qp || size <= 0 || !mr) return ncclSuccess;
   if (c->error) return (ncclResult_t)c->error;
   RdmaRequest* r = get_request(c);
@@ -770,6 +777,7 @@ ncclResult_t rdma_test(RdmaRequest* r, ConnManager* cm, int* done, int* size) {
 
 void rdma_close(RdmaComm* c) {
   if (!c) return;
+  if (params().timers && c->stage == 3) c->timers.print(c->is_send ? "rdma send" : "rdma recv");
   if (c->flush_qp) g_prov->destroy_qp(c->flush_qp);      // queue pairs go before the completion queue they use
   for (int d = 0; d < kMaxDev; ++d) {
     for (int q = 0; q < kRdmaMaxQps; ++q)

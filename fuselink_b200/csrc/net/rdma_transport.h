@@ -147,6 +147,7 @@ struct RdmaComm {
   size_t io_done = 0;
   uint64_t since_ns = 0;                  // accepted at (receiver): a bootstrap that stalls is dropped
   RdmaConnInfo mine, theirs;
+  Timers timers;                          // FUSELINK_TIMERS=1: isend / irecv / descriptor post / completion polling / flush
 };
 
 struct RdmaListenComm {

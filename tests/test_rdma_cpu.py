@@ -269,3 +269,12 @@ def test_verbs_provider_error_completions_and_reads(tmp_path):
     tx, rx = _pair([1 << 20], env=flush, common=["--device-buffers", "--chunk", "262144"], extra_recv=["--flush"])
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     assert "FLUSHES 1" in rx[1]
+
+
+def test_phase_timers_are_printed_at_close():
+    """FUSELINK_TIMERS=1: the run-time version of the timers the reference compiles out (isend, irecv, descriptor post,
+    completion polling)."""
+    tx, rx = _pair([1 << 20], env=dict(SOFT, FUSELINK_TIMERS="1"), common=["--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "[fuselink timer] rdma send isend" in tx[2] and "[fuselink timer] rdma send progress" in tx[2]
+    assert "[fuselink timer] rdma recv irecv" in rx[2] and "[fuselink timer] rdma recv post_desc" in rx[2]
