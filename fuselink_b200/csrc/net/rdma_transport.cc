@@ -244,8 +244,10 @@ void poll_all(RdmaComm* c, ConnManager* cm) {
         if (wc[i].status != rdma::kWcOk) {
           if (!wc[i].is_recv && device_failed(c, cm, d, wc[i])) continue;
           if (cm && wc[i].status == rdma::kWcRetryExceeded) cm->set_dead(d, true);
-          char msg[96];
-          snprintf(msg, sizeof msg, "completion with status %d on device %d", wc[i].status, d);
+          char msg[192];
+          snprintf(msg, sizeof msg, "completion with status %d on device %d (%s), queue pair %u, %s, wr_id 0x%llx, %u bytes, peer device %d",
+                   wc[i].status, d, g_prov->device(d).name.c_str(), wc[i].qpn, wc[i].is_recv ? "receive" : "send side",
+                   (unsigned long long)wc[i].wr_id, wc[i].byte_len, c->peer_dev);
           fail(c, wc[i].status == rdma::kWcRemoteAccess ? ncclInvalidUsage : ncclRemoteError, msg);
           continue;
         }
