@@ -4,6 +4,7 @@
 // translation of work requests and completions run end to end through the plugin on a machine without RDMA hardware.
 // The transitions check the attribute masks the real library requires, so a missing attribute fails here too.
 #include <errno.h>
+#include <stdarg.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -27,6 +28,25 @@ struct FakeQp { ibv_qp qp; rd::Qp* impl; int dev; int state; uint32_t dest_qpn; 
 
 FakeDevice g_devs[8];
 int g_ndevs = 0;
+
+// FUSELINK_FAKE_IB_LOG=<file>: one line per call whose arguments a test wants to see (queue-pair attributes, access flags).
+void record(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+void record(const char* fmt, ...) {
+  const char* path = getenv("FUSELINK_FAKE_IB_LOG");
+  if (!path || !*path) return;
+  char line[512];
+  va_list ap;
+  va_start(ap, fmt);
+  int n = vsnprintf(line, sizeof line - 1, fmt, ap);
+  va_end(ap);
+  if (n < 0) return;
+  if (n > (int)sizeof line - 2) n = (int)sizeof line - 2;
+  line[n++] = '\n';
+  FILE* f = fopen(path, "a");                   // O_APPEND: whole lines from both processes of a test
+  if (!f) return;
+  fwrite(line, 1, (size_t)n, f);
+  fclose(f);
+}
 
 int ndevs() {
   const char* e = getenv("FUSELINK_FAKE_IB_NDEV");
@@ -168,6 +188,7 @@ ibv_mr* ibv_reg_mr(ibv_pd* pd, void* addr, size_t len, int access) {
   if (access & IBV_ACCESS_REMOTE_WRITE) a |= rd::kAccessRemoteWrite;
   if (access & IBV_ACCESS_REMOTE_READ) a |= rd::kAccessRemoteRead;
   if ((access & IBV_ACCESS_REMOTE_WRITE) && !(access & IBV_ACCESS_LOCAL_WRITE)) { errno = EINVAL; return nullptr; }   // verbs rule
+  record("reg_mr len=%zu access=0x%x", len, (unsigned)access);
   FakeMr* m = static_cast<FakeMr*>(calloc(1, sizeof(FakeMr)));
   m->impl = nic()->reg_mr(reinterpret_cast<FakePd*>(pd)->impl, addr, len, a);
   m->mr.context = pd->context;
@@ -177,6 +198,11 @@ ibv_mr* ibv_reg_mr(ibv_pd* pd, void* addr, size_t len, int access) {
   m->mr.lkey = m->impl->lkey;
   m->mr.rkey = m->impl->rkey;
   return &m->mr;
+}
+// The entry point newer libraries add; relaxed ordering can only be asked for through it.
+ibv_mr* ibv_reg_mr_iova2(ibv_pd* pd, void* addr, size_t len, uint64_t iova, unsigned int access) {
+  if (iova != (uint64_t)(uintptr_t)addr) { errno = EINVAL; return nullptr; }
+  return ibv_reg_mr(pd, addr, len, (int)access);
 }
 int ibv_dereg_mr(ibv_mr* mr) {
   FakeMr* m = reinterpret_cast<FakeMr*>(mr);
@@ -213,6 +239,7 @@ ibv_qp* ibv_create_qp(ibv_pd* pd, ibv_qp_init_attr* ia) {
   q->qp.recv_cq = ia->recv_cq;
   q->qp.qp_num = info.qpn;
   q->state = IBV_QPS_RESET;
+  record("create_qp dev=%d max_send_wr=%u max_recv_wr=%u max_inline=%u", q->dev, ia->cap.max_send_wr, ia->cap.max_recv_wr, ia->cap.max_inline_data);
   return &q->qp;
 }
 int ibv_modify_qp(ibv_qp* qp, ibv_qp_attr* a, int mask) {
@@ -221,14 +248,18 @@ int ibv_modify_qp(ibv_qp* qp, ibv_qp_attr* a, int mask) {
   if (a->qp_state == IBV_QPS_INIT) {
     const int need = IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS;
     if (q->state != IBV_QPS_RESET || (mask & need) != need || a->port_num != 1) return EINVAL;
+    record("init dev=%d pkey=%u access=0x%x", q->dev, (unsigned)a->pkey_index, a->qp_access_flags);
   } else if (a->qp_state == IBV_QPS_RTR) {
     const int need = IBV_QP_AV | IBV_QP_PATH_MTU | IBV_QP_DEST_QPN | IBV_QP_RQ_PSN | IBV_QP_MAX_DEST_RD_ATOMIC | IBV_QP_MIN_RNR_TIMER;
     if (q->state != IBV_QPS_INIT || (mask & need) != need || !a->ah_attr.is_global || a->path_mtu < 1 || a->path_mtu > 5) return EINVAL;
     q->dest_qpn = a->dest_qp_num;
+    record("rtr dev=%d mtu=%d sgid_index=%u tc=%u sl=%u hop_limit=%u", q->dev, (int)a->path_mtu, (unsigned)a->ah_attr.grh.sgid_index,
+           (unsigned)a->ah_attr.grh.traffic_class, (unsigned)a->ah_attr.sl, (unsigned)a->ah_attr.grh.hop_limit);
     memcpy(&q->dest_cookie, a->ah_attr.grh.dgid.raw, 8);
   } else if (a->qp_state == IBV_QPS_RTS) {
     const int need = IBV_QP_TIMEOUT | IBV_QP_RETRY_CNT | IBV_QP_RNR_RETRY | IBV_QP_SQ_PSN | IBV_QP_MAX_QP_RD_ATOMIC;
     if (q->state != IBV_QPS_RTR || (mask & need) != need) return EINVAL;
+    record("rts dev=%d timeout=%u retry_cnt=%u rnr_retry=%u", q->dev, (unsigned)a->timeout, (unsigned)a->retry_cnt, (unsigned)a->rnr_retry);
     rd::QpInfo remote;
     memset(&remote, 0, sizeof remote);
     remote.qpn = q->dest_qpn;
@@ -247,11 +278,22 @@ int ibv_destroy_qp(ibv_qp* qp) {
   free(q);
   return 0;
 }
-int ibv_get_async_event(ibv_context*, ibv_async_event*) {
-  for (;;) sleep(3600);          // nothing ever happens to a fake port
+int ibv_get_async_event(ibv_context* ctx, ibv_async_event* ev) {
+  // FUSELINK_FAKE_IB_EVENT_MS=<ms>: device 0 reports "port error" once, that long after the first wait; otherwise nothing
+  // ever happens to a fake port
+  static int fired = 0;
+  const char* e = getenv("FUSELINK_FAKE_IB_EVENT_MS");
+  if (e && reinterpret_cast<FakeContext*>(ctx)->dev == 0 && !__atomic_exchange_n(&fired, 1, __ATOMIC_ACQ_REL)) {
+    usleep((useconds_t)atoi(e) * 1000);
+    memset(ev, 0, sizeof *ev);
+    ev->element.port_num = 1;
+    ev->event_type = 10;         // IBV_EVENT_PORT_ERR
+    return 0;
+  }
+  for (;;) sleep(3600);
   return -1;
 }
-void ibv_ack_async_event(ibv_async_event*) {}
-const char* ibv_event_type_str(int) { return "fake event"; }
+void ibv_ack_async_event(ibv_async_event* ev) { record("ack_async_event type=%d", ev->event_type); }
+const char* ibv_event_type_str(int t) { return t == 10 ? "port error" : "fake event"; }
 
 }  // extern "C"

@@ -278,3 +278,40 @@ def test_phase_timers_are_printed_at_close():
     assert tx[0] == 0 and rx[0] == 0, (tx, rx)
     assert "[fuselink timer] rdma send isend" in tx[2] and "[fuselink timer] rdma send progress" in tx[2]
     assert "[fuselink timer] rdma recv irecv" in rx[2] and "[fuselink timer] rdma recv post_desc" in rx[2]
+
+
+def test_verbs_attributes_follow_the_environment(tmp_path):
+    """NCCL_IB_GID_INDEX / _TIMEOUT / _RETRY_CNT / _PKEY / _SL / _TC / _USE_INLINE / _PCI_RELAXED_ORDERING reach the calls of
+    the verbs library with the values given (the stand-in library writes down what it is called with), and an asynchronous
+    port event is fetched, logged and acknowledged by the watcher thread."""
+    libdir = _build_fake_ibverbs(tmp_path)
+    log = os.path.join(str(tmp_path), "calls.log")
+    env = {"FUSELINK_TRANSPORT": "rdma", "LD_LIBRARY_PATH": libdir + ":" + os.environ.get("LD_LIBRARY_PATH", ""), "FUSELINK_FAKE_IB_NDEV": "2",
+           "FUSELINK_FAKE_IB_LOG": log, "FUSELINK_FAKE_IB_EVENT_MS": "1", "FL_HARNESS_VERBOSE": "1",
+           "NCCL_IB_GID_INDEX": "3", "NCCL_IB_TIMEOUT": "20", "NCCL_IB_RETRY_CNT": "5", "NCCL_IB_PKEY": "2", "NCCL_IB_SL": "4", "NCCL_IB_TC": "106",
+           "NCCL_IB_USE_INLINE": "1", "NCCL_IB_PCI_RELAXED_ORDERING": "0"}
+    tx, rx = _pair([1 << 20, 77], env=env, common=["--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    calls = open(log).read().splitlines()
+    kv = lambda l: dict(f.split("=") for f in l.split()[1:])
+    init = [kv(l) for l in calls if l.startswith("init ")]
+    rtr = [kv(l) for l in calls if l.startswith("rtr ")]
+    rts = [kv(l) for l in calls if l.startswith("rts ")]
+    qps = [kv(l) for l in calls if l.startswith("create_qp ")]
+    mrs = [kv(l) for l in calls if l.startswith("reg_mr ")]
+    assert init and len(init) == len(rtr) == len(rts)
+    assert all(c["pkey"] == "2" and int(c["access"], 16) == 0x7 for c in init)
+    assert all(c["sgid_index"] == "3" and c["tc"] == "106" and c["sl"] == "4" and c["hop_limit"] == "255" for c in rtr)
+    assert all(c["timeout"] == "20" and c["retry_cnt"] == "5" and c["rnr_retry"] == "7" for c in rts)
+    assert all(int(c["max_inline"]) >= 128 for c in qps if int(c["max_send_wr"]) > 1) and qps
+    assert mrs and all(int(c["access"], 16) & (1 << 20) == 0 for c in mrs)           # relaxed ordering switched off
+    assert any(l.startswith("ack_async_event type=10") for l in calls)
+    assert "asynchronous event: port error" in tx[2] + rx[2]
+    # relaxed ordering on: the flag is in every registration
+    os.remove(log)
+    tx, rx = _pair([1 << 20], env=dict(env, NCCL_IB_PCI_RELAXED_ORDERING="1", NCCL_IB_USE_INLINE="0"), common=["--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    calls = open(log).read().splitlines()
+    mrs = [kv(l) for l in calls if l.startswith("reg_mr ")]
+    assert mrs and all(int(c["access"], 16) & (1 << 20) for c in mrs)
+    assert all(c["max_inline"] == "0" for c in (kv(l) for l in calls if l.startswith("create_qp ")))
