@@ -73,3 +73,27 @@ def test_bench_reference_arm_reports_why_it_is_unavailable():
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+
+
+def test_every_environment_variable_read_by_the_sources_is_documented():
+    """docs/environment.md lists every FUSELINK_* / NCCL_* / FL_* name that appears as a string in the package, the benches
+    and the experiment scripts."""
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    doc = open(os.path.join(root, "docs", "environment.md")).read()
+    documented = set(re.findall(r"`((?:FUSELINK|NCCL|FL)_[A-Z0-9_]+)`", doc))
+    names = set()
+    tops = [os.path.join(root, d) for d in ("fuselink_b200", "bench", "experiments")] + [os.path.join(root, "bench.py")]
+    for top in tops:
+        files = [top] if os.path.isfile(top) else [os.path.join(d, f) for d, _, fs in os.walk(top) for f in fs]
+        for path in files:
+            if not path.endswith((".py", ".cc", ".cu", ".cpp", ".h", ".cuh", ".sh")):
+                continue
+            text = open(path, errors="replace").read()
+            names |= set(re.findall(r"\"((?:FUSELINK|NCCL|FL)_[A-Z0-9_]+)\"", text))
+            if path.endswith(".sh"):
+                names |= set(re.findall(r"\b((?:FUSELINK|NCCL)_[A-Z0-9_]+)=", text))
+    names = {n for n in names if not n.startswith(("NCCL_PTR_", "NCCL_LOG_", "NCCL_NET_HANDLE", "NCCL_NET_MAX", "NCCL_ALL", "NCCL_INIT", "NCCL_NET_DEVICE"))}
+    missing = sorted(names - documented)
+    assert not missing, f"not in docs/environment.md: {missing}"
