@@ -45,6 +45,8 @@ struct Driver {
   virtual int device_count() = 0;
   virtual int pointer_device(const void* ptr) = 0;   // -1 when unknown
   virtual int address_range(const void* ptr, uintptr_t* base, size_t* size) { (void)ptr; (void)base; (void)size; return 1; }
+  // A dma-buf descriptor for [ptr, ptr + size): *offset is where ptr lies inside the exported range.
+  virtual int dmabuf_fd(const void* ptr, size_t size, int* fd, uint64_t* offset) { (void)ptr; (void)size; (void)fd; (void)offset; return 1; }
 };
 
 // ---- real CUDA driver, resolved at run time -----------------------------------------------------
@@ -71,6 +73,7 @@ struct CudaDriver : Driver {
   CUresult (*DeviceGetCount)(int*) = nullptr;
   CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr) = nullptr;
   CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr) = nullptr;
+  CUresult (*MemGetHandleForAddressRange)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long) = nullptr;
 
   template <class F>
   bool sym(const char* name, F& fn) {
@@ -109,6 +112,7 @@ struct CudaDriver : Driver {
     (void)sym("cuDeviceGetCount", DeviceGetCount);
     (void)sym("cuPointerGetAttribute", PointerGetAttribute);
     (void)sym("cuMemGetAddressRange", MemGetAddressRange);
+    (void)sym("cuMemGetHandleForAddressRange", MemGetHandleForAddressRange);
     g_err[0] = 0;
     return chk(Init(0), "cuInit") == 0;
   }
@@ -202,6 +206,20 @@ struct CudaDriver : Driver {
     *size = n;
     return 0;
   }
+  int dmabuf_fd(const void* ptr, size_t size, int* fd, uint64_t* offset) override {
+    if (!MemGetHandleForAddressRange) { set_err("%s: cuMemGetHandleForAddressRange not available (%ld)", "vmm", 0); return 1; }
+    // address and size have to be multiples of the host page size: export the pages around the range
+    const uintptr_t page = (uintptr_t)sysconf(_SC_PAGESIZE);
+    const uintptr_t lo = (uintptr_t)ptr / page * page;
+    const uintptr_t hi = ((uintptr_t)ptr + size + page - 1) / page * page;
+    int out = -1;
+    int rc = chk(MemGetHandleForAddressRange(&out, (CUdeviceptr)lo, hi - lo, CU_MEM_RANGE_HANDLE_TYPE_DMA_BUF_FD, 0),
+                 "cuMemGetHandleForAddressRange");
+    if (rc) return rc;
+    *fd = out;
+    *offset = (uintptr_t)ptr - lo;
+    return 0;
+  }
   int pointer_device(const void* ptr) override {
     int ord = -1;
     if (!PointerGetAttribute) return -1;
@@ -277,6 +295,20 @@ struct FakeDriver : Driver {
     return e ? atoi(e) : 8;
   }
   int pointer_device(const void*) override { return -1; }
+  // the memfd behind the mapping that contains ptr stands in for the dma-buf
+  int dmabuf_fd(const void* ptr, size_t size, int* fd, uint64_t* offset) override {
+    std::lock_guard<std::mutex> l(mu);
+    auto it = mapped.upper_bound((uintptr_t)ptr);
+    if (it == mapped.begin()) { set_err("%s: pointer is not inside a mapping (%ld)", "fake", 0); return 1; }
+    --it;
+    const size_t bytes = handles[it->second];
+    if ((uintptr_t)ptr + size > it->first + bytes) { set_err("%s: range crosses the end of its mapping (%ld)", "fake", 0); return 1; }
+    const int d = dup((int)it->second);
+    if (d < 0) return 1;
+    *fd = d;
+    *offset = (uintptr_t)ptr - it->first;
+    return 0;
+  }
 };
 
 Driver* g_drv = nullptr;
@@ -574,6 +606,11 @@ int fl_vmm_address_range(const void* ptr, void** base, size_t* size) {
   *base = reinterpret_cast<void*>(b);
   *size = n;
   return 0;
+}
+
+int fl_vmm_dmabuf_fd(const void* ptr, size_t size, int* fd_out, uint64_t* offset_out) {
+  if (!g_drv || !ptr || !size || !fd_out || !offset_out) return 1;
+  return g_drv->dmabuf_fd(ptr, size, fd_out, offset_out);
 }
 
 int fl_vmm_memcpy(void* dst, const void* src, size_t bytes) {

@@ -60,6 +60,11 @@ int fl_vmm_ptr2dev(const void* ptr);
 // layer, the slab).  What the reference asks cuMemGetAddressRange for before it takes a buffer over
 // (src/plugin.cc:1186-1194): NCCL registers sub-ranges of larger allocations.  Returns 0 on success.
 int fl_vmm_address_range(const void* ptr, void** base, size_t* size);
+// A dma-buf file descriptor for the memory mapped at [ptr, ptr + size) right now (cuMemGetHandleForAddressRange), for a
+// NIC registration of device memory without a peer-memory kernel module.  The exported range is widened to whole host
+// pages; *offset_out is where `ptr` lies inside it.  A buffer that was re-homed needs a descriptor taken AFTER the move:
+// one taken before names the old physical memory.  The caller closes the descriptor.  Returns 0 on success.
+int fl_vmm_dmabuf_fd(const void* ptr, size_t size, int* fd_out, uint64_t* offset_out);
 // Synchronous copy between any two addresses the backend knows (device or host, unified addressing).
 int fl_vmm_memcpy(void* dst, const void* src, size_t bytes);
 // Device that owns `ptr`: a region of this layer, else what the driver reports, else -1.

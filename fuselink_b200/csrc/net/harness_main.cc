@@ -78,6 +78,7 @@ struct Api {
     if (abi == 8) return v8->regMr(c, d, s, ptr_type, mh);
     return abi == 6 ? v6->regMr(c, d, (int)s, ptr_type, mh) : v7->regMr(c, d, (int)s, ptr_type, mh);
   }
+  ncclResult_t regMrDmaBuf(void* c, void* d, size_t s, uint64_t off, int fd, void** mh) { return PICK(regMrDmaBuf)(c, d, s, ptr_type, off, fd, mh); }
   ncclResult_t deregMr(void* c, void* mh) { return PICK(deregMr)(c, mh); }
   ncclResult_t isend(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(isend)(c, d, s, tag, mh, r); }
   ncclResult_t irecv(void* c, void* d, int s, int tag, void* mh, void** r) { return PICK(irecv)(c, 1, &d, &s, &tag, &mh, r); }
@@ -100,7 +101,7 @@ int main(int argc, char** argv) {
   size_t chunk = 512 * 1024;
   int inflight = 8, dev = 0, die_after = -1, channel = 0, nch = 1;
   uint64_t seed = 0;
-  bool expect_error = false, device_bufs = false, threaded = false, do_flush = false;
+  bool expect_error = false, device_bufs = false, threaded = false, do_flush = false, nccl_dmabuf = false;
   const char* inject_event = nullptr;
   size_t reg_offset = 0;
   Api api;
@@ -121,6 +122,7 @@ int main(int argc, char** argv) {
     else if (a == "--reg-offset") reg_offset = (size_t)val();  // device buffers: the registered buffer starts this far into its allocation
     else if (a == "--flush") do_flush = true;               // receiver: iflush the whole buffer after every message
     else if (a == "--inject-event") inject_event = argv[++i];   // raise an asynchronous device event after init (software NIC)
+    else if (a == "--nccl-dmabuf") { device_bufs = true; nccl_dmabuf = true; }   // register through regMrDmaBuf with a descriptor taken beforehand, as NCCL does
     else if (a == "--device-buffers") device_bufs = true;   // buffers come from the plugin's cuMem layer and are registered as CUDA
     else sizes.push_back(strtoull(a.c_str(), nullptr, 0));
   }
@@ -211,8 +213,20 @@ int main(int argc, char** argv) {
     if (is_send) { fill(host, seed, mi); if (!host.empty()) memcpy(bufp, host.data(), host.size() * 4); }
     else { expect.resize(host.size()); fill(expect, seed, mi); if (!host.empty()) memset(bufp, 0xA5, host.size() * 4); }
     std::vector<void*> mhs(nch, nullptr);
-    for (int c = 0; c < nch; ++c)
-      if (api.regMr(comms[ch0 + c], buf.data(), buf.size() * 4, &mhs[c]) != ncclSuccess) { fprintf(stderr, "regMr failed\n"); return 2; }
+    for (int c = 0; c < nch; ++c) {
+      if (nccl_dmabuf) {
+        auto get_fd = (int (*)(const void*, size_t, int*, uint64_t*))dlsym(lib, "fl_vmm_dmabuf_fd");
+        int fd = -1;
+        uint64_t off = 0;
+        if (!get_fd || get_fd(buf.data(), buf.size() * 4 ? buf.size() * 4 : 1, &fd, &off)) { fprintf(stderr, "no dma-buf for the buffer\n"); return 2; }
+        const ncclResult_t e = api.regMrDmaBuf(comms[ch0 + c], buf.data(), buf.size() * 4, off, fd, &mhs[c]);
+        close(fd);
+        if (e != ncclSuccess) { fprintf(stderr, "regMrDmaBuf failed\n"); return 2; }
+      } else if (api.regMr(comms[ch0 + c], buf.data(), buf.size() * 4, &mhs[c]) != ncclSuccess) {
+        fprintf(stderr, "regMr failed\n");
+        return 2;
+      }
+    }
     if (device_bufs && mi == 0) {
       auto p2d = (int (*)(const void*))dlsym(lib, "fl_vmm_ptr2dev");
       printf("REGISTERED device-buffer owner %d now-backed-by %d\n", dev, p2d ? p2d(bufp) : -1);
@@ -311,6 +325,12 @@ int main(int argc, char** argv) {
     unsigned long long m = 0, pc = 0, w = 0;
     rdma_ctr(&m, &pc, &w);
     if (m) printf("RDMA messages %llu pieces %llu work-requests %llu\n", m, pc, w);
+  }
+  auto mr_ctr = (void (*)(unsigned long long*, unsigned long long*, unsigned long long*))dlsym(lib, "fuselink_rdma_mr_counters");
+  if (mr_ctr) {
+    unsigned long long regs = 0, hits = 0, dmabuf = 0;
+    mr_ctr(&regs, &hits, &dmabuf);
+    if (regs) printf("MR registrations %llu cache-hits %llu dma-buf %llu\n", regs, hits, dmabuf);
   }
   auto failovers = (unsigned long long (*)(void))dlsym(lib, "fuselink_plugin_failovers");
   if (failovers && is_send && failovers()) printf("FAILOVERS %llu\n", failovers());

@@ -114,7 +114,11 @@ void fill_props_common(int dev, P* props) {
   props->pciPath = g_pci[dev];
   props->guid = g_guid[dev];
   // the TCP transport reads/writes host memory; GPU buffers are accepted (and staged by the plugin) only on request
-  props->ptrSupport = NCCL_PTR_HOST | (g_ngpus > 0 ? NCCL_PTR_CUDA : 0);
+  // on the RDMA transport a NIC must be able to reach device memory: by address (peer-memory module) or through a dma-buf
+  // (the reference's ncclIbGdrSupport / ncclIbDmaBufSupport, src/plugin.cc:321-356, 367-372)
+  const bool dmabuf = g_rdma && g_ngpus > 0 && rdma_dmabuf_supported();
+  const bool cuda = g_ngpus > 0 && (!g_rdma || dmabuf || rdma_peer_memory_supported());
+  props->ptrSupport = NCCL_PTR_HOST | (cuda ? NCCL_PTR_CUDA : 0) | (dmabuf ? NCCL_PTR_DMABUF : 0);
   props->speed = g_speed[dev];            // Mbps
   props->port = 0;
   props->latency = 0;
@@ -219,10 +223,33 @@ void fl_dereg_region(MemHandle* m) {
   m->region = nullptr;
 }
 
-ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
+// `given_fd` / `given_offset`: the dma-buf NCCL hands to regMrDmaBuf (-1: none).
+ncclResult_t fl_reg_mr_impl(void* comm, void* data, size_t size, int type, int given_fd, uint64_t given_offset, void** mhandle) {
   auto finish = [&](MemHandle* m) -> ncclResult_t {
     if (g_rdma) {
-      m->rdma = rdma_reg(data, size);
+      // How a NIC reaches device memory (src/plugin.cc:321-356, 1277-1289): by address when a peer-memory module is
+      // loaded, else through a dma-buf.  A buffer this plugin has taken over may have been re-homed, and a descriptor
+      // NCCL took before that names the old physical memory: such a buffer gets a descriptor of its own, taken now.
+      int fd = -1, own_fd = -1;
+      uint64_t off = 0;
+      if (type == NCCL_PTR_CUDA) {
+        if (given_fd >= 0 && !m->region) {
+          fd = given_fd;
+          off = given_offset;
+        } else if ((given_fd >= 0 || !rdma_peer_memory_supported()) && rdma_dmabuf_supported() &&
+                   fl_vmm_dmabuf_fd(data, size ? size : 1, &own_fd, &off) == 0) {
+          fd = own_fd;
+        } else if (!rdma_peer_memory_supported()) {
+          FL_WARN("regMr: the NICs cannot reach device memory at %p: no peer-memory module and no dma-buf (%s)", data, fl_vmm_last_error());
+          if (m->region) fl_dereg_region(m);
+          delete m;
+          return ncclInvalidUsage;
+        } else {
+          FL_INFO("regMr: no dma-buf for %p (%s); registering by address", data, fl_vmm_last_error());
+        }
+      }
+      m->rdma = rdma_reg(data, size, fd, off);
+      if (own_fd >= 0) close(own_fd);
       if (!m->rdma) {
         if (m->region) fl_dereg_region(m);
         delete m;
@@ -277,12 +304,14 @@ ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** 
   }
   return finish(m);
 }
+ncclResult_t fl_reg_mr_sz(void* comm, void* data, size_t size, int type, void** mhandle) {
+  return fl_reg_mr_impl(comm, data, size, type, -1, 0, mhandle);
+}
 ncclResult_t fl_reg_mr(void* comm, void* data, int size, int type, void** mhandle) {
-  return fl_reg_mr_sz(comm, data, (size_t)size, type, mhandle);
+  return fl_reg_mr_impl(comm, data, (size_t)size, type, -1, 0, mhandle);
 }
 ncclResult_t fl_reg_mr_dmabuf(void* comm, void* data, size_t size, int type, uint64_t offset, int fd, void** mhandle) {
-  (void)offset; (void)fd;
-  return fl_reg_mr_sz(comm, data, size, type, mhandle);
+  return fl_reg_mr_impl(comm, data, size, type, fd, offset, mhandle);
 }
 ncclResult_t fl_dereg_mr(void* comm, void* mhandle) {
   MemHandle* m = reinterpret_cast<MemHandle*>(mhandle);

@@ -103,6 +103,17 @@ class Provider {
   virtual Pd* alloc_pd(int dev) = 0;                 // one per device, shared by every connection (reference: up-front, :290-297)
   virtual void dealloc_pd(Pd* pd) = 0;
   virtual Mr* reg_mr(Pd* pd, void* addr, size_t len, int access) = 0;
+  // Registration of device memory through a dma-buf file descriptor: `len` bytes starting `offset` bytes into the
+  // buffer behind `fd`, addressed by the peer (and by local work requests) as [iova, iova + len).  The descriptor may be
+  // closed once the call returns.  Null when the provider cannot (src/plugin.cc:1277-1280 is the reference's use).
+  virtual Mr* reg_dmabuf_mr(Pd* pd, int fd, uint64_t offset, size_t len, uint64_t iova, int access) {
+    (void)pd; (void)fd; (void)offset; (void)len; (void)iova; (void)access;
+    return nullptr;
+  }
+  // Can device `dev` register dma-bufs (the reference probes ibv_reg_dmabuf_mr with a dummy descriptor,
+  // src/plugin.cc:337-356), and can it register device pointers by address (a peer-memory kernel module, :321-331)?
+  virtual bool dmabuf_supported(int dev) { (void)dev; return false; }
+  virtual bool peer_memory_supported() { return false; }
   virtual void dereg_mr(Mr* mr) = 0;
   virtual Cq* create_cq(int dev, int depth) = 0;
   virtual void destroy_cq(Cq* cq) = 0;

@@ -9,7 +9,9 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <mutex>
 #include <thread>
+#include <vector>
 
 #include "logging.h"
 #include "params.h"
@@ -323,30 +325,101 @@ int rdma_init(ConnManager* cm) {
 
 rdma::DeviceInfo rdma_device(int dev) { return g_prov->device(dev); }
 
-RdmaMrSet* rdma_reg(void* data, size_t size) {
+// Registration cache, one per device, as NCCL's verbs transport keeps one (the reference fills it in
+// src/plugin.cc:1265-1305): NCCL registers the same buffer once per channel and connection, and a registration pins
+// pages through the kernel, so a range that is registered already is shared and counted.  Ordinary registrations are
+// widened to whole pages, which lets neighbouring sub-buffers of one allocation share an entry too; a dma-buf
+// registration is keyed by its exact range.
+namespace {
+struct MrSlot {
+  uintptr_t addr;
+  size_t len;
+  bool dmabuf;
+  int refs;
+  rdma::Mr* mr;
+};
+std::mutex g_mr_mu;
+std::vector<MrSlot> g_mr_cache[kMaxDev];
+std::atomic<uint64_t> g_mr_regs{0}, g_mr_hits{0}, g_mr_dmabuf{0};
+
+void release_mr_locked(int dev, rdma::Mr* mr) {
+  std::vector<MrSlot>& cache = g_mr_cache[dev];
+  for (size_t i = 0; i < cache.size(); ++i) {
+    if (cache[i].mr != mr) continue;
+    if (--cache[i].refs == 0) {
+      g_prov->dereg_mr(mr);
+      cache[i] = cache.back();
+      cache.pop_back();
+    }
+    return;
+  }
+  g_prov->dereg_mr(mr);          // not cached (cannot happen through rdma_reg)
+}
+}  // namespace
+
+RdmaMrSet* rdma_reg(void* data, size_t size, int dmabuf_fd, uint64_t dmabuf_offset) {
   RdmaMrSet* m = new RdmaMrSet();
   memset(m, 0, sizeof *m);
   m->data = data;
   m->size = size;
   const int flags = access_flags();
+  const bool dmabuf = dmabuf_fd >= 0;
+  uintptr_t addr = (uintptr_t)data;
+  size_t len = size ? size : 1;
+  if (!dmabuf) {
+    const uintptr_t page = (uintptr_t)sysconf(_SC_PAGESIZE);
+    addr = (uintptr_t)data / page * page;
+    len = ((uintptr_t)data + len - addr + page - 1) / page * page;
+  }
+  std::lock_guard<std::mutex> l(g_mr_mu);
   for (int d = 0; d < g_ndev; ++d) {
     // every device gets its own registration so that any of them can carry a stripe (the reference registers
     // every per-GPU alias on every NIC, src/plugin.cc:1250-1320)
-    m->mr[d] = g_prov->reg_mr(g_pd[d], data, size ? size : 1, flags);
-    if (!m->mr[d]) {
-      FL_WARN("rdma: registration of %zu bytes at %p failed on device %d", size, data, d);
-      rdma_dereg(m);
+    for (MrSlot& s : g_mr_cache[d]) {
+      if (s.addr == addr && s.len == len && s.dmabuf == dmabuf) {
+        ++s.refs;
+        m->mr[d] = s.mr;
+        g_mr_hits.fetch_add(1, std::memory_order_relaxed);
+        break;
+      }
+    }
+    if (m->mr[d]) continue;
+    rdma::Mr* mr = dmabuf ? g_prov->reg_dmabuf_mr(g_pd[d], dmabuf_fd, dmabuf_offset, len, (uint64_t)addr, flags)
+                          : g_prov->reg_mr(g_pd[d], reinterpret_cast<void*>(addr), len, flags);
+    if (!mr) {
+      FL_WARN("rdma: registration of %zu bytes at %p failed on device %d%s", size, data, d, dmabuf ? " (dma-buf)" : "");
+      for (int k = 0; k < d; ++k) release_mr_locked(k, m->mr[k]);
+      delete m;
       return nullptr;
     }
+    g_mr_regs.fetch_add(1, std::memory_order_relaxed);
+    if (dmabuf) g_mr_dmabuf.fetch_add(1, std::memory_order_relaxed);
+    g_mr_cache[d].push_back(MrSlot{addr, len, dmabuf, 1, mr});
+    m->mr[d] = mr;
   }
   return m;
 }
 
 void rdma_dereg(RdmaMrSet* m) {
   if (!m) return;
+  std::lock_guard<std::mutex> l(g_mr_mu);
   for (int d = 0; d < kMaxDev; ++d)
-    if (m->mr[d]) g_prov->dereg_mr(m->mr[d]);
+    if (m->mr[d]) release_mr_locked(d, m->mr[d]);
   delete m;
+}
+
+bool rdma_dmabuf_supported() {
+  if (!g_prov || g_ndev <= 0) return false;
+  for (int d = 0; d < g_ndev; ++d)
+    if (!g_prov->dmabuf_supported(d)) return false;      // a stripe may take any device: all of them or none
+  return true;
+}
+bool rdma_peer_memory_supported() { return g_prov && g_ndev > 0 && g_prov->peer_memory_supported(); }
+
+void rdma_mr_counters(unsigned long long* registrations, unsigned long long* cache_hits, unsigned long long* dmabuf) {
+  *registrations = g_mr_regs.load();
+  *cache_hits = g_mr_hits.load();
+  *dmabuf = g_mr_dmabuf.load();
 }
 
 ncclResult_t rdma_listen(int dev, int channel_id, Handle* h, RdmaListenComm** out) {
@@ -817,6 +890,11 @@ void rdma_counters(unsigned long long* m, unsigned long long* p, unsigned long l
 
 }  // namespace flnet
 
+// Registration counters: registrations made, requests answered from the cache, registrations that went through a dma-buf.
+extern "C" __attribute__((visibility("default"))) void fuselink_rdma_mr_counters(unsigned long long* registrations, unsigned long long* cache_hits,
+                                                                               unsigned long long* dmabuf) {
+  flnet::rdma_mr_counters(registrations, cache_hits, dmabuf);
+}
 extern "C" __attribute__((visibility("default"))) unsigned long long fuselink_rdma_failovers(void) { return flnet::rdma_failovers(); }
 
 // Counters for tests and tools: messages sent, pieces they were cut into, work requests posted for them.

@@ -164,8 +164,13 @@ rdma::DeviceInfo rdma_device(int dev);
 ncclResult_t rdma_listen(int dev, int channel_id, Handle* h, RdmaListenComm** out);
 ncclResult_t rdma_connect(int dev, Handle* h, RdmaComm** out);      // re-entrant, *out stays null until connected
 ncclResult_t rdma_accept(RdmaListenComm* lc, RdmaComm** out);       // re-entrant
-RdmaMrSet* rdma_reg(void* data, size_t size);
+// Registers [data, data + size) on every device, through the registration cache.  With dmabuf_fd >= 0 the memory is
+// reached through that dma-buf (`data` lies dmabuf_offset bytes into it) instead of by address.
+RdmaMrSet* rdma_reg(void* data, size_t size, int dmabuf_fd = -1, uint64_t dmabuf_offset = 0);
 void rdma_dereg(RdmaMrSet* m);
+bool rdma_dmabuf_supported();                             // every device can register a dma-buf
+bool rdma_peer_memory_supported();                        // device pointers can be registered by address
+void rdma_mr_counters(unsigned long long* registrations, unsigned long long* cache_hits, unsigned long long* dmabuf);
 ncclResult_t rdma_isend(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out);
 ncclResult_t rdma_irecv(RdmaComm* c, ConnManager* cm, void* data, int size, int tag, RdmaMrSet* mr, RdmaRequest** out);
 ncclResult_t rdma_iflush(RdmaComm* c, ConnManager* cm, void* data, int size, RdmaMrSet* mr, RdmaRequest** out);   // *out null: nothing to do

@@ -15,6 +15,7 @@
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
 #include <sys/socket.h>
 #include <sys/un.h>
 #include <unistd.h>
@@ -77,9 +78,13 @@ struct Inflight {
 };
 
 struct SoftMr {
-  uint8_t* addr;
+  uint8_t* addr;                   // what work requests and the peer call this memory (the I/O virtual address)
   size_t len;
   int access;
+  uint8_t* local = nullptr;        // where the bytes are in this process; differs from addr for a dma-buf registration
+  void* map = nullptr;             // dma-buf: this NIC's own mapping of the buffer
+  size_t map_len = 0;
+  uint8_t* at(const uint8_t* a) const { return local + (a - addr); }
 };
 
 struct Inbound {                    // one accepted stream, attached to the queue pair its hello names
@@ -171,13 +176,44 @@ class SoftProvider : public Provider {
     m->lkey = m->rkey = next_key_++;
     m->addr = addr;
     m->len = len;
-    mrs_[m->rkey] = SoftMr{reinterpret_cast<uint8_t*>(addr), len, access};
+    SoftMr sm{reinterpret_cast<uint8_t*>(addr), len, access};
+    sm.local = sm.addr;
+    mrs_[m->rkey] = sm;
     return m;
   }
+  // A dma-buf is reached through a mapping of its own, never through the address the application uses: the way a NIC
+  // gets to device memory through the exporter's pages.  Anything mmap can map stands in for the dma-buf (the memfd
+  // slabs of the fake cuMem driver in the tests).
+  Mr* reg_dmabuf_mr(Pd* pd, int fd, uint64_t offset, size_t len, uint64_t iova, int access) override {
+    (void)pd;
+    if (fd < 0 || !len) { errno = EBADF; return nullptr; }
+    const uint64_t page = (uint64_t)sysconf(_SC_PAGESIZE);
+    const uint64_t lo = offset / page * page;
+    const size_t map_len = (size_t)(offset - lo) + len;
+    void* map = mmap(nullptr, map_len, PROT_READ | PROT_WRITE, MAP_SHARED, fd, (off_t)lo);
+    if (map == MAP_FAILED) return nullptr;
+    std::lock_guard<std::mutex> l(mu_);
+    Mr* m = new Mr();
+    m->lkey = m->rkey = next_key_++;
+    m->addr = reinterpret_cast<void*>(iova);
+    m->len = len;
+    SoftMr sm{reinterpret_cast<uint8_t*>(iova), len, access};
+    sm.local = static_cast<uint8_t*>(map) + (offset - lo);
+    sm.map = map;
+    sm.map_len = map_len;
+    mrs_[m->rkey] = sm;
+    return m;
+  }
+  bool dmabuf_supported(int) override { return true; }
+  bool peer_memory_supported() override { return param_i64("FUSELINK_SOFT_PEERMEM", 1) != 0; }
   void dereg_mr(Mr* mr) override {
     if (!mr) return;
     std::lock_guard<std::mutex> l(mu_);
-    mrs_.erase(mr->rkey);
+    auto it = mrs_.find(mr->rkey);
+    if (it != mrs_.end()) {
+      if (it->second.map) munmap(it->second.map, it->second.map_len);
+      mrs_.erase(it);
+    }
     delete mr;
   }
 
@@ -265,6 +301,13 @@ class SoftProvider : public Provider {
       OutMsg m;
       m.hdr = WireHdr{kWireMagic, (uint32_t)w.op, w.len, w.rkey, w.raddr, w.imm, 0};
       m.payload = reinterpret_cast<const uint8_t*>(w.laddr);
+      if (w.len && w.laddr) {                      // a dma-buf registration is read and written through its own mapping
+        auto lm = mrs_.find(w.lkey);
+        if (lm != mrs_.end() && lm->second.map) {
+          if (m.payload < lm->second.addr || m.payload + w.len > lm->second.addr + lm->second.len) return -EINVAL;
+          m.payload = lm->second.at(m.payload);
+        }
+      }
       uint8_t* read_dst = nullptr;
       if (w.op == kRead) {                         // the request carries no payload; the response does
         read_dst = const_cast<uint8_t*>(m.payload);
@@ -471,7 +514,7 @@ class SoftProvider : public Provider {
             queue_ack(in, kAck);
             const size_t at = in.ack_tx.size();
             in.ack_tx.resize(at + want);
-            dma_fetch(in.ack_tx.data() + at, a, want);
+            dma_fetch(in.ack_tx.data() + at, it->second.at(a), want);
           }
           flush_acks(in);
           continue;
@@ -483,7 +526,7 @@ class SoftProvider : public Provider {
               a + in.hdr.len > it->second.addr + it->second.len)
             in.bad = true;                      // wrong key or out of bounds: the payload is drained and refused
           else
-            in.dst = a;
+            in.dst = it->second.at(a);
         }
         in.in_payload = true;
         in.payload_got = 0;

@@ -7,9 +7,11 @@
 // No machine this project is tested on has RDMA hardware: this file is compiled and loaded everywhere, and
 // reports zero devices there.  The transport above it is exercised through the software NIC.
 #include <dlfcn.h>
+#include <errno.h>
 #include <limits.h>
 #include <stdlib.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <mutex>
 #include <vector>
@@ -40,6 +42,7 @@ struct Lib {
   int (*dealloc_pd)(ibv_pd*) = nullptr;
   ibv_mr* (*reg_mr)(ibv_pd*, void*, size_t, int) = nullptr;
   ibv_mr* (*reg_mr_iova2)(ibv_pd*, void*, size_t, uint64_t, unsigned int) = nullptr;   // newer libraries only
+  ibv_mr* (*reg_dmabuf_mr)(ibv_pd*, uint64_t, size_t, uint64_t, int, int) = nullptr;    // offset, length, iova, fd, access
   int (*dereg_mr)(ibv_mr*) = nullptr;
   ibv_cq* (*create_cq)(ibv_context*, int, void*, void*, int) = nullptr;
   int (*destroy_cq)(ibv_cq*) = nullptr;
@@ -129,6 +132,54 @@ class VerbsProvider : public Provider {
     m->len = len;
     m->impl = mr;
     return m;
+  }
+  Mr* reg_dmabuf_mr(Pd* h, int fd, uint64_t offset, size_t len, uint64_t iova, int access) override {
+    VPd* p = reinterpret_cast<VPd*>(h);
+    if (!lib_.reg_dmabuf_mr) return nullptr;
+    int flags = 0;
+    if (access & kAccessLocalWrite) flags |= IBV_ACCESS_LOCAL_WRITE;
+    if (access & kAccessRemoteWrite) flags |= IBV_ACCESS_REMOTE_WRITE;
+    if (access & kAccessRemoteRead) flags |= IBV_ACCESS_REMOTE_READ;
+    if (access & kAccessRelaxedOrdering) flags |= IBV_ACCESS_RELAXED_ORDERING;
+    ibv_mr* mr = lib_.reg_dmabuf_mr(p->pd, offset, len, iova, fd, flags);
+    if (!mr) return nullptr;
+    Mr* m = new Mr();
+    m->lkey = mr->lkey;
+    m->rkey = mr->rkey;
+    m->addr = reinterpret_cast<void*>(iova);
+    m->len = len;
+    m->impl = mr;
+    return m;
+  }
+  // The kernel side is probed with a registration that cannot succeed (no descriptor): a kernel or device without
+  // dma-buf support answers "not supported", one with it answers "bad descriptor" (src/plugin.cc:337-356).
+  bool dmabuf_supported(int dev) override {
+    if (!lib_.reg_dmabuf_mr || dev < 0 || dev >= (int)ports_.size()) return false;
+    std::lock_guard<std::mutex> l(probe_mu_);
+    if (dmabuf_probe_.size() < ports_.size()) dmabuf_probe_.resize(ports_.size(), -1);
+    if (dmabuf_probe_[dev] < 0) {
+      ibv_pd* pd = lib_.alloc_pd(ports_[dev].ctx);
+      int ok = 0;
+      if (pd) {
+        errno = 0;
+        ibv_mr* mr = lib_.reg_dmabuf_mr(pd, 0, 0, 0, -1, 0);
+        if (mr) lib_.dereg_mr(mr);
+        ok = errno != EOPNOTSUPP && errno != EPROTONOSUPPORT;
+        lib_.dealloc_pd(pd);
+      }
+      dmabuf_probe_[dev] = ok;
+    }
+    return dmabuf_probe_[dev] == 1;
+  }
+  // A peer-memory module lets ibv_reg_mr take a device pointer (src/plugin.cc:321-331).  FUSELINK_PEERMEM=0|1 overrides.
+  bool peer_memory_supported() override {
+    const int64_t forced = param_i64("FUSELINK_PEERMEM", -1);
+    if (forced >= 0) return forced != 0;
+    static const char* const kFiles[] = {"/sys/kernel/mm/memory_peers/nv_mem/version", "/sys/kernel/mm/memory_peers/nv_mem_nc/version",
+                                         "/sys/module/nvidia_peermem/version"};
+    for (const char* f : kFiles)
+      if (access(f, F_OK) == 0) return true;
+    return false;
   }
   void dereg_mr(Mr* m) override {
     if (!m) return;
@@ -288,6 +339,8 @@ class VerbsProvider : public Provider {
   }
 
  private:
+  std::mutex probe_mu_;
+  std::vector<int> dmabuf_probe_;      // per device: -1 not probed yet, 0 no, 1 yes
   void discover() {
     if (params().ib_disable) return;
     void* h = dlopen("libibverbs.so.1", RTLD_NOW);
@@ -306,6 +359,7 @@ class VerbsProvider : public Provider {
               sym(h, "ibv_destroy_cq", &lib_.destroy_cq) && sym(h, "ibv_create_qp", &lib_.create_qp) && sym(h, "ibv_modify_qp", &lib_.modify_qp) &&
               sym(h, "ibv_destroy_qp", &lib_.destroy_qp);
     sym(h, "ibv_reg_mr_iova2", &lib_.reg_mr_iova2, false);
+    sym(h, "ibv_reg_dmabuf_mr", &lib_.reg_dmabuf_mr, false);
     sym(h, "ibv_get_async_event", &lib_.get_async_event, false);
     sym(h, "ibv_ack_async_event", &lib_.ack_async_event, false);
     sym(h, "ibv_event_type_str", &lib_.event_type_str, false);

@@ -338,6 +338,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     if (fl_vmm_grant(reinterpret_cast<FlVmmRegion*>(r), (int)dev)) throw std::runtime_error(std::string("fl_vmm_grant: ") + fl_vmm_last_error());
   });
   m.def("vmm_remap_slab", &vmm_remap_slab);
+  m.def("vmm_dmabuf_fd", [](int64_t p, int64_t size) {
+    int fd = -1;
+    uint64_t off = 0;
+    if (fl_vmm_dmabuf_fd(reinterpret_cast<const void*>(p), (size_t)size, &fd, &off))
+      throw std::runtime_error(std::string("fl_vmm_dmabuf_fd: ") + fl_vmm_last_error());
+    return std::make_pair(fd, (int64_t)off);
+  });
   m.def("vmm_ptr2dev", [](int64_t p) { return fl_vmm_ptr2dev(reinterpret_cast<const void*>(p)); });
   m.def("pool_init", [](int64_t ndev, int64_t slabs, int64_t slab_bytes) {
     if (fl_pool_init((int)ndev, (int)slabs, (size_t)slab_bytes)) throw std::runtime_error(std::string("fl_pool_init: ") + fl_vmm_last_error());

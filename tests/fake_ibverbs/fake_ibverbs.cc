@@ -204,6 +204,28 @@ ibv_mr* ibv_reg_mr_iova2(ibv_pd* pd, void* addr, size_t len, uint64_t iova, unsi
   if (iova != (uint64_t)(uintptr_t)addr) { errno = EINVAL; return nullptr; }
   return ibv_reg_mr(pd, addr, len, (int)access);
 }
+// FUSELINK_FAKE_IB_DMABUF=0: a kernel without dma-buf support.
+ibv_mr* ibv_reg_dmabuf_mr(ibv_pd* pd, uint64_t offset, size_t len, uint64_t iova, int fd, int access) {
+  const char* e = getenv("FUSELINK_FAKE_IB_DMABUF");
+  if (e && e[0] == '0') { errno = EOPNOTSUPP; return nullptr; }
+  if (fd < 0) { errno = EBADF; return nullptr; }
+  int a = 0;
+  if (access & IBV_ACCESS_LOCAL_WRITE) a |= rd::kAccessLocalWrite;
+  if (access & IBV_ACCESS_REMOTE_WRITE) a |= rd::kAccessRemoteWrite;
+  if (access & IBV_ACCESS_REMOTE_READ) a |= rd::kAccessRemoteRead;
+  record("reg_dmabuf_mr len=%zu offset=%llu access=0x%x", len, (unsigned long long)offset, (unsigned)access);
+  rd::Mr* impl = nic()->reg_dmabuf_mr(reinterpret_cast<FakePd*>(pd)->impl, fd, offset, len, iova, a);
+  if (!impl) return nullptr;
+  FakeMr* m = static_cast<FakeMr*>(calloc(1, sizeof(FakeMr)));
+  m->impl = impl;
+  m->mr.context = pd->context;
+  m->mr.pd = pd;
+  m->mr.addr = reinterpret_cast<void*>(iova);
+  m->mr.length = len;
+  m->mr.lkey = impl->lkey;
+  m->mr.rkey = impl->rkey;
+  return &m->mr;
+}
 int ibv_dereg_mr(ibv_mr* mr) {
   FakeMr* m = reinterpret_cast<FakeMr*>(mr);
   nic()->dereg_mr(m->impl);

@@ -315,3 +315,104 @@ def test_verbs_attributes_follow_the_environment(tmp_path):
     mrs = [kv(l) for l in calls if l.startswith("reg_mr ")]
     assert mrs and all(int(c["access"], 16) & (1 << 20) for c in mrs)
     assert all(c["max_inline"] == "0" for c in (kv(l) for l in calls if l.startswith("create_qp ")))
+
+
+def _mr_counters(out):
+    line = [l for l in out.splitlines() if l.startswith("MR registrations")]
+    assert line, out
+    w = line[0].split()
+    return int(w[2]), int(w[4]), int(w[6])
+
+
+def test_registration_cache_shares_a_buffer_between_channels():
+    """NCCL registers one buffer once per connection: the second to fourth registration of the same pages is answered from
+    the per-device cache (the reference's MR cache, src/plugin.cc:1265-1305)."""
+    tx, rx = _pair([1 << 20], env=SOFT, common=["--chunk", "65536", "--channels", "4"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    regs, hits, dmabuf = _mr_counters(tx[1])
+    assert dmabuf == 0
+    assert hits >= 3 * 4                                          # 3 repeated registrations x 4 devices
+    one, _ = _pair([1 << 20], env=SOFT, common=["--chunk", "65536"])
+    assert one[0] == 0
+    regs1, hits1, _ = _mr_counters(one[1])
+    assert regs - regs1 == 3 * 2 * 4 and hits1 == 0               # the extra connections add only their own FIFO + record registrations
+
+
+def test_device_memory_is_registered_through_a_dmabuf_without_peer_memory():
+    """No peer-memory module (FUSELINK_SOFT_PEERMEM=0): a device buffer reaches the NIC through a dma-buf descriptor the
+    cuMem layer exports AFTER the buffer was re-homed, and the software NIC goes through its own mapping of that
+    descriptor, never through the application's address."""
+    env = dict(SOFT, FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS="8", FL_HARNESS_VERBOSE="1", FUSELINK_SOFT_PEERMEM="0")
+    tx, rx = _pair([3 << 20, 70000, 5], env=env, common=["--device-buffers", "--dev", "2", "--chunk", "524288", "--reg-offset", "4096"],
+                   extra_recv=["--channel", "3"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert "re-homed GPU 2 -> GPU 5" in rx[2]
+    assert _mr_counters(tx[1])[2] == 3 * 4 and _mr_counters(rx[1])[2] == 3 * 4     # 3 buffers x 4 devices, both ends
+    # with a peer-memory module the same buffers are registered by address
+    tx, rx = _pair([3 << 20], env=dict(env, FUSELINK_SOFT_PEERMEM="1"), common=["--device-buffers", "--chunk", "524288"])
+    assert tx[0] == 0 and rx[0] == 0 and _mr_counters(tx[1])[2] == 0, (tx, rx)
+
+
+@pytest.mark.parametrize("remap", ["0", "1"])
+def test_regmr_dmabuf_entry_point(remap):
+    """regMrDmaBuf with a descriptor taken before the registration, as NCCL does.  A buffer the plugin leaves alone is
+    registered through NCCL's descriptor; one it takes over (and re-homes) gets a fresh descriptor, because the old one
+    names the memory the buffer no longer lives in."""
+    env = dict(SOFT, FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS="4", FL_HARNESS_VERBOSE="1", FUSELINK_SOFT_PEERMEM="0",
+               FUSELINK_REMAP=remap, FUSELINK_NVL=remap)
+    tx, rx = _pair([2 << 20, 4097], env=env, common=["--nccl-dmabuf", "--dev", "1", "--chunk", "262144"], extra_recv=["--channel", "2"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert _mr_counters(rx[1])[2] == 2 * 4
+    assert ("re-homed GPU 1 -> GPU 3" in rx[2]) == (remap == "1")
+
+
+def test_pointer_support_follows_what_the_nics_can_reach():
+    import subprocess, sys, textwrap
+    code = textwrap.dedent(f"""
+        import ctypes
+        lib = ctypes.CDLL({PLUGIN!r})
+        class Props(ctypes.Structure):
+            _fields_ = [("name", ctypes.c_char_p), ("pci", ctypes.c_char_p), ("guid", ctypes.c_uint64), ("ptr", ctypes.c_int)]
+        class V6(ctypes.Structure):
+            _fields_ = [("name", ctypes.c_char_p), ("init", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_void_p)),
+                        ("devices", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.POINTER(ctypes.c_int))),
+                        ("props", ctypes.CFUNCTYPE(ctypes.c_int, ctypes.c_int, ctypes.c_void_p))]
+        v6 = V6.in_dll(lib, "ncclNetPlugin_v6")
+        assert v6.init(None) == 0
+        buf = ctypes.create_string_buffer(256)
+        assert v6.props(0, buf) == 0
+        print(Props.from_buffer(buf).ptr)
+    """)
+    def ptr(**kw):
+        env = {**os.environ, **SOFT, "FUSELINK_VMM_FAKE": "1", **kw}
+        out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=60)
+        assert out.returncode == 0, out.stderr
+        return int(out.stdout.split()[-1])
+    HOST, CUDA, DMABUF = 1, 2, 4
+    assert ptr() == HOST                                                         # device buffers not asked for
+    assert ptr(FUSELINK_CUDA_PTRS="1") == HOST | CUDA | DMABUF
+    assert ptr(FUSELINK_CUDA_PTRS="1", FUSELINK_SOFT_PEERMEM="0") == HOST | CUDA | DMABUF
+    assert ptr(FUSELINK_CUDA_PTRS="1", FUSELINK_TRANSPORT="tcp") == HOST | CUDA  # the TCP transport stages device memory itself
+
+
+def test_verbs_provider_registers_device_memory_by_dmabuf_or_by_address(tmp_path):
+    """Through the stand-in libibverbs: without a peer-memory module the provider probes ibv_reg_dmabuf_mr (a descriptor of
+    -1 must answer "bad descriptor", not "unsupported") and registers device buffers through it; FUSELINK_PEERMEM=1 (a
+    loaded nvidia-peermem) registers them by address; a kernel without dma-buf support and without the module has no
+    way to reach device memory and the plugin does not offer NCCL_PTR_CUDA."""
+    libdir = _build_fake_ibverbs(tmp_path)
+    log = os.path.join(str(tmp_path), "calls.log")
+    env = {"FUSELINK_TRANSPORT": "rdma", "LD_LIBRARY_PATH": libdir + ":" + os.environ.get("LD_LIBRARY_PATH", ""), "FUSELINK_FAKE_IB_NDEV": "2",
+           "FUSELINK_FAKE_IB_LOG": log, "FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "2", "FL_HARNESS_VERBOSE": "1",
+           "FUSELINK_PEERMEM": "0"}
+    tx, rx = _pair([1 << 20, 33], env=env, common=["--device-buffers", "--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert _mr_counters(rx[1])[2] == 2 * 2
+    calls = open(log).read().splitlines()
+    assert sum(l.startswith("reg_dmabuf_mr ") for l in calls) == 2 * 2 * 2          # 2 buffers x 2 devices x 2 processes
+    os.remove(log)
+    tx, rx = _pair([1 << 20], env=dict(env, FUSELINK_PEERMEM="1"), common=["--device-buffers", "--chunk", "262144"])
+    assert tx[0] == 0 and rx[0] == 0 and _mr_counters(rx[1])[2] == 0, (tx, rx)
+    assert not any(l.startswith("reg_dmabuf_mr ") for l in open(log).read().splitlines())
+    tx, rx = _pair([1 << 20], env=dict(env, FUSELINK_FAKE_IB_DMABUF="0"), common=["--device-buffers", "--chunk", "262144"], timeout=30)
+    assert tx[0] != 0 and rx[0] != 0 and "regMr failed" in tx[2] + rx[2], (tx, rx)

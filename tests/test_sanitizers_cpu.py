@@ -24,6 +24,9 @@ TRANSPORTS = {
     "tcp": {},
     "tcp-direct": {"FUSELINK_CUDA_PTRS": "1", "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "4"},
     "rdma-soft": {"FUSELINK_TRANSPORT": "rdma", "FUSELINK_RDMA_PROVIDER": "soft", "NCCL_IB_QPS_PER_CONNECTION": "2"},
+    # device buffers, re-homed, registered through dma-buf descriptors (the software NIC maps them itself)
+    "rdma-dmabuf": {"FUSELINK_TRANSPORT": "rdma", "FUSELINK_RDMA_PROVIDER": "soft", "FUSELINK_SOFT_PEERMEM": "0", "FUSELINK_CUDA_PTRS": "1",
+                    "FUSELINK_VMM_FAKE": "1", "FUSELINK_VMM_FAKE_NGPUS": "4"},
 }
 
 
@@ -35,7 +38,7 @@ def test_plugin_transfer_under_asan_ubsan(transport):
         env = dict(os.environ, NCCL_SOCKET_IFNAME="lo", ASAN_OPTIONS="detect_leaks=1:abort_on_error=1", UBSAN_OPTIONS="halt_on_error=1",
                    NCCL_FUSELINK_DEGREE="3", FUSELINK_MIN_STRIPE_BYTES="4096", **TRANSPORTS[transport])
         sizes = ["0", "4097", str(1 << 20), str(5 << 20)]
-        if transport == "tcp-direct":
+        if transport in ("tcp-direct", "rdma-dmabuf"):
             sizes = ["--device-buffers"] + sizes
         rx = subprocess.Popen([art["harness"], art["plugin"], "recv", hf, "--chunk", "262144", *sizes], env=env, stdout=subprocess.PIPE,
                               stderr=subprocess.PIPE, text=True)

@@ -72,6 +72,33 @@ def test_remap_keeps_address_and_optionally_contents():
     C.vmm_destroy(r)
 
 
+def test_dmabuf_descriptor_names_the_memory_mapped_now():
+    """The descriptor a NIC registration goes through: it names what is mapped at the address when it is taken, so one
+    taken before a re-homing keeps naming the old memory and one taken after names the new."""
+    import mmap
+    r = C.vmm_create(0, 4 << 20, 2 << 20)
+    _view(r, 4096).fill_(21)
+    ptr = C.vmm_ptr(r)
+    fd_old, off = C.vmm_dmabuf_fd(ptr + 4096, 8192)
+    assert off == 4096
+    C.vmm_remap_slab(r, 0, 3, True, [0])
+    _view(r, 4096).fill_(22)
+    fd_new, off_new = C.vmm_dmabuf_fd(ptr + 4096, 8192)
+    assert off_new == 4096
+    old = mmap.mmap(fd_old, 2 << 20)
+    new = mmap.mmap(fd_new, 2 << 20)
+    assert int.from_bytes(old[4096:4100], "little") == 21 and int.from_bytes(new[4096:4100], "little") == 22
+    new[4096:4100] = (23).to_bytes(4, "little")                     # what a NIC writes through the descriptor ...
+    assert _view(r, 4096)[1024] == 23                                     # ... is what the address shows
+    old.close(); new.close(); os.close(fd_old); os.close(fd_new)
+    fd2, off2 = C.vmm_dmabuf_fd(ptr + (2 << 20) + 100, 64)          # second slab: its own mapping
+    assert off2 == 100
+    os.close(fd2)
+    with pytest.raises(RuntimeError):
+        C.vmm_dmabuf_fd(ptr + (2 << 20) - 16, 64)                   # a range that crosses two physical allocations
+    C.vmm_destroy(r)
+
+
 def test_adopt_foreign_allocation_and_rehome():
     owner = C.vmm_create(1, 2 << 20, 0)               # stands in for a buffer another library allocated
     _view(owner).fill_(3)
