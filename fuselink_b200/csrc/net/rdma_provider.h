@@ -43,6 +43,13 @@ struct QpInfo {
   uint8_t pad[7];
   uint8_t gid[16];
   uint64_t cookie;              // provider-private (the software NIC puts its process id here)
+  // enhanced connection establishment: vendor options the two ends agree on before the queue pair is connected
+  // (src/plugin.cc:393-395, 801-802, 856-857, 986-994)
+  uint32_t ece_vendor_id, ece_options, ece_comp_mask, ece_supported;
+};
+
+struct Ece {
+  uint32_t vendor_id = 0, options = 0, comp_mask = 0;
 };
 
 struct Pd;
@@ -121,6 +128,10 @@ class Provider {
   virtual void destroy_qp(Qp* qp) = 0;
   virtual int query_qp_info(Qp* qp, int gid_index, QpInfo* out) = 0;           // local side of the exchange
   virtual int connect_qp(Qp* qp, const QpInfo& remote, const QpConnectParams& p) = 0;   // INIT -> RTR -> RTS
+  // Enhanced connection establishment, both before connect_qp.  query: the options this queue pair offers (after a
+  // set: what is left of them).  set: take the peer's options.  False when the device or the library has none.
+  virtual bool query_ece(Qp* qp, Ece* out) { (void)qp; (void)out; return false; }
+  virtual bool set_ece(Qp* qp, const Ece& ece) { (void)qp; (void)ece; return false; }
   virtual int post_send(Qp* qp, const SendWr* wrs, int n) = 0;                 // a chain, executed in order
   virtual int post_recv(Qp* qp, uint64_t wr_id) = 0;                           // zero-length receive
   virtual int poll_cq(Cq* cq, int max, Completion* out) = 0;

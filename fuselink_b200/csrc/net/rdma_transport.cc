@@ -70,7 +70,25 @@ bool make_endpoints(RdmaComm* c) {
     for (int q = 0; q < c->nqps; ++q) {
       c->dev[d].qp[q] = g_prov->create_qp(g_pd[d], c->dev[d].cq, caps);
       if (!c->dev[d].qp[q]) return false;
-      if (g_prov->query_qp_info(c->dev[d].qp[q], (int)params().ib_gid_index, &c->mine.qp[d][q])) return false;
+      rdma::QpInfo& mine = c->mine.qp[d][q];
+      if (g_prov->query_qp_info(c->dev[d].qp[q], (int)params().ib_gid_index, &mine)) return false;
+      // Enhanced connection establishment.  The connecting side offers its options; the accepting side (which knows
+      // the offer by now) takes them and answers with what is left; the connecting side applies the answer in
+      // connect_endpoints.  All of it before the queue pair leaves INIT.
+      rdma::Ece ece;
+      mine.ece_supported = 0;
+      if (c->is_send) {
+        if (g_prov->query_ece(c->dev[d].qp[q], &ece)) mine.ece_supported = 1;
+      } else if (c->theirs.qp[d][q].ece_supported) {
+        const rdma::QpInfo& t = c->theirs.qp[d][q];
+        rdma::Ece offer;
+        offer.vendor_id = t.ece_vendor_id; offer.options = t.ece_options; offer.comp_mask = t.ece_comp_mask;
+        if (g_prov->set_ece(c->dev[d].qp[q], offer) && g_prov->query_ece(c->dev[d].qp[q], &ece)) mine.ece_supported = 1;
+      }
+      if (mine.ece_supported) {
+        mine.ece_vendor_id = ece.vendor_id; mine.ece_options = ece.options; mine.ece_comp_mask = ece.comp_mask;
+        FL_INFO("rdma dev %d qp %d: ece %s vendor 0x%x options 0x%x", d, q, c->is_send ? "offered" : "agreed", ece.vendor_id, ece.options);
+      }
     }
   }
   return true;
@@ -82,8 +100,15 @@ bool connect_endpoints(RdmaComm* c) {
   p.gid_index = (int)e.ib_gid_index; p.timeout = (int)e.ib_timeout; p.retry_cnt = (int)e.ib_retry_cnt;
   p.pkey = (int)e.ib_pkey; p.sl = (int)e.ib_sl; p.tc = (int)e.ib_tc;
   for (int d = 0; d < c->ndev; ++d)
-    for (int q = 0; q < c->nqps; ++q)
-      if (g_prov->connect_qp(c->dev[d].qp[q], c->theirs.qp[d][q], p)) return false;
+    for (int q = 0; q < c->nqps; ++q) {
+      const rdma::QpInfo& t = c->theirs.qp[d][q];
+      if (c->is_send && t.ece_supported && c->mine.qp[d][q].ece_supported) {
+        rdma::Ece agreed;
+        agreed.vendor_id = t.ece_vendor_id; agreed.options = t.ece_options; agreed.comp_mask = t.ece_comp_mask;
+        if (!g_prov->set_ece(c->dev[d].qp[q], agreed)) FL_WARN("rdma dev %d qp %d: the agreed ece options were refused", d, q);
+      }
+      if (g_prov->connect_qp(c->dev[d].qp[q], t, p)) return false;
+    }
   return true;
 }
 

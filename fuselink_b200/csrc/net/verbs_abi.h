@@ -151,6 +151,8 @@ struct ibv_device_attr {
   uint8_t reserve[64];
 };
 
+struct ibv_ece { uint32_t vendor_id, options, comp_mask; };
+
 struct ibv_async_event {
   union { void* cq; void* qp; void* srq; void* wq; int port_num; } element;
   int event_type;

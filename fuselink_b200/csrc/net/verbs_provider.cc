@@ -49,6 +49,8 @@ struct Lib {
   ibv_qp* (*create_qp)(ibv_pd*, ibv_qp_init_attr*) = nullptr;
   int (*modify_qp)(ibv_qp*, ibv_qp_attr*, int) = nullptr;
   int (*destroy_qp)(ibv_qp*) = nullptr;
+  int (*query_ece)(ibv_qp*, ibv_ece*) = nullptr;      // newer libraries only
+  int (*set_ece)(ibv_qp*, ibv_ece*) = nullptr;
   int (*get_async_event)(ibv_context*, ibv_async_event*) = nullptr;
   void (*ack_async_event)(ibv_async_event*) = nullptr;
   const char* (*event_type_str)(int) = nullptr;
@@ -234,6 +236,20 @@ class VerbsProvider : public Provider {
     }
     return 0;
   }
+  bool query_ece(Qp* h, Ece* out) override {
+    if (!lib_.query_ece || !lib_.set_ece) return false;
+    ibv_ece e;
+    memset(&e, 0, sizeof e);
+    if (lib_.query_ece(reinterpret_cast<VQp*>(h)->qp, &e)) return false;      // EOPNOTSUPP on devices without it
+    out->vendor_id = e.vendor_id; out->options = e.options; out->comp_mask = e.comp_mask;
+    return true;
+  }
+  bool set_ece(Qp* h, const Ece& in) override {
+    if (!lib_.set_ece) return false;
+    ibv_ece e;
+    e.vendor_id = in.vendor_id; e.options = in.options; e.comp_mask = in.comp_mask;
+    return lib_.set_ece(reinterpret_cast<VQp*>(h)->qp, &e) == 0;
+  }
   int connect_qp(Qp* h, const QpInfo& remote, const QpConnectParams& p) override {
     VQp* q = reinterpret_cast<VQp*>(h);
     const Port& pt = ports_[q->dev];
@@ -360,6 +376,8 @@ class VerbsProvider : public Provider {
               sym(h, "ibv_destroy_qp", &lib_.destroy_qp);
     sym(h, "ibv_reg_mr_iova2", &lib_.reg_mr_iova2, false);
     sym(h, "ibv_reg_dmabuf_mr", &lib_.reg_dmabuf_mr, false);
+    sym(h, "ibv_query_ece", &lib_.query_ece, false);
+    sym(h, "ibv_set_ece", &lib_.set_ece, false);
     sym(h, "ibv_get_async_event", &lib_.get_async_event, false);
     sym(h, "ibv_ack_async_event", &lib_.ack_async_event, false);
     sym(h, "ibv_event_type_str", &lib_.event_type_str, false);

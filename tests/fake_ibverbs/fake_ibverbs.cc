@@ -24,7 +24,7 @@ struct FakeContext { ibv_context ctx; int dev; };
 struct FakePd { ibv_pd pd; rd::Pd* impl; int dev; };
 struct FakeMr { ibv_mr mr; rd::Mr* impl; };
 struct FakeCq { ibv_cq cq; rd::Cq* impl; };
-struct FakeQp { ibv_qp qp; rd::Qp* impl; int dev; int state; uint32_t dest_qpn; uint64_t dest_cookie; };
+struct FakeQp { ibv_qp qp; rd::Qp* impl; int dev; int state; uint32_t dest_qpn; uint64_t dest_cookie; uint32_t ece_options; int ece_set; };
 
 FakeDevice g_devs[8];
 int g_ndevs = 0;
@@ -292,6 +292,29 @@ int ibv_modify_qp(ibv_qp* qp, ibv_qp_attr* a, int mask) {
     return EINVAL;
   }
   q->state = a->qp_state;
+  return 0;
+}
+// FUSELINK_FAKE_IB_ECE=<options>: the device offers these enhanced-connection options (vendor 0x15b3); unset: the calls
+// answer "not supported".  Options may only be set while the queue pair has not been connected, and what a later query
+// returns is what both ends have in common.
+int ibv_query_ece(ibv_qp* qp, ibv_ece* ece) {
+  const char* e = getenv("FUSELINK_FAKE_IB_ECE");
+  if (!e) return EOPNOTSUPP;
+  FakeQp* q = reinterpret_cast<FakeQp*>(qp);
+  ece->vendor_id = 0x15b3;
+  ece->options = q->ece_set ? q->ece_options : (uint32_t)strtoul(e, nullptr, 0);
+  ece->comp_mask = 0;
+  return 0;
+}
+int ibv_set_ece(ibv_qp* qp, ibv_ece* ece) {
+  const char* e = getenv("FUSELINK_FAKE_IB_ECE");
+  if (!e) return EOPNOTSUPP;
+  FakeQp* q = reinterpret_cast<FakeQp*>(qp);
+  if (q->state != IBV_QPS_RESET && q->state != IBV_QPS_INIT) return EINVAL;
+  if (ece->vendor_id != 0x15b3) return EINVAL;
+  q->ece_options = ece->options & (uint32_t)strtoul(e, nullptr, 0);
+  q->ece_set = 1;
+  record("set_ece dev=%d given=0x%x kept=0x%x", q->dev, ece->options, q->ece_options);
   return 0;
 }
 int ibv_destroy_qp(ibv_qp* qp) {

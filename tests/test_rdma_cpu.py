@@ -416,3 +416,23 @@ def test_verbs_provider_registers_device_memory_by_dmabuf_or_by_address(tmp_path
     assert not any(l.startswith("reg_dmabuf_mr ") for l in open(log).read().splitlines())
     tx, rx = _pair([1 << 20], env=dict(env, FUSELINK_FAKE_IB_DMABUF="0"), common=["--device-buffers", "--chunk", "262144"], timeout=30)
     assert tx[0] != 0 and rx[0] != 0 and "regMr failed" in tx[2] + rx[2], (tx, rx)
+
+
+def test_enhanced_connection_establishment_is_negotiated(tmp_path):
+    """ECE through the stand-in libibverbs: the connecting side offers its options, the accepting side keeps what both
+    have and answers with that, the connecting side applies the answer -- all before the queue pairs are connected
+    (src/plugin.cc:801-802, 856-857, 986-994).  A library without the calls connects as before."""
+    libdir = _build_fake_ibverbs(tmp_path)
+    log = os.path.join(str(tmp_path), "calls.log")
+    env = {"FUSELINK_TRANSPORT": "rdma", "LD_LIBRARY_PATH": libdir + ":" + os.environ.get("LD_LIBRARY_PATH", ""), "FUSELINK_FAKE_IB_NDEV": "2",
+           "FUSELINK_FAKE_IB_LOG": log, "FL_HARNESS_VERBOSE": "1"}
+    tx, rx = _pair([1 << 20], env=env, common=["--chunk", "262144"], env_send={"FUSELINK_FAKE_IB_ECE": "0x7"}, env_recv={"FUSELINK_FAKE_IB_ECE": "0xd"})
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    sets = [l for l in open(log).read().splitlines() if l.startswith("set_ece ")]
+    assert sorted(set(l.split(" ", 2)[2] for l in sets)) == ["given=0x5 kept=0x5", "given=0x7 kept=0x5"]
+    assert len(sets) == 2 * 2                                      # one queue pair per device, both ends
+    assert "ece offered vendor 0x15b3 options 0x7" in tx[2] and "ece agreed vendor 0x15b3 options 0x5" in rx[2]
+    os.remove(log)
+    tx, rx = _pair([1 << 20], env=env, common=["--chunk", "262144"], env_send={"FUSELINK_FAKE_IB_ECE": "0x7"})     # the receiver's device has none
+    assert tx[0] == 0 and rx[0] == 0, (tx, rx)
+    assert not [l for l in open(log).read().splitlines() if l.startswith("set_ece ")]
