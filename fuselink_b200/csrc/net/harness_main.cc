@@ -218,7 +218,7 @@ int main(int argc, char** argv) {
         auto get_fd = (int (*)(const void*, size_t, int*, uint64_t*))dlsym(lib, "fl_vmm_dmabuf_fd");
         int fd = -1;
         uint64_t off = 0;
-        if (!get_fd || get_fd(buf.data(), buf.size() * 4 ? buf.size() * 4 : 1, &fd, &off)) { fprintf(stderr, "no dma-buf for the buffer\n"); return 2; }
+        if (!get_fd || get_fd(buf.data(), buf.size() > 0 ? buf.size() * 4 : 1, &fd, &off)) { fprintf(stderr, "no dma-buf for the buffer\n"); return 2; }
         const ncclResult_t e = api.regMrDmaBuf(comms[ch0 + c], buf.data(), buf.size() * 4, off, fd, &mhs[c]);
         close(fd);
         if (e != ncclSuccess) { fprintf(stderr, "regMrDmaBuf failed\n"); return 2; }

@@ -398,3 +398,26 @@ def test_two_jobs_contend_for_one_nic_unless_the_monitor_is_shared():
     assert sum(shared) > 1.5 * sum(alone), (alone, shared)
     # degree 2: the second stripe of each job goes to a NIC the shared table shows idle, not blindly to the neighbour's
     assert min(striped) > 0.3, striped
+
+
+def test_makefile_builds_a_working_plugin_without_python(tmp_path):
+    """`make fl monitor harness` (the reference's target names, Makefile:33-49) into a scratch directory: the plugin it links
+    moves data between two processes and the monitor daemon starts."""
+    import shutil
+    if not shutil.which("make") or not shutil.which(os.environ.get("CXX", "g++")):
+        pytest.skip("no make / C++ compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = str(tmp_path / "b")
+    b = subprocess.run(["make", "-C", root, "-j8", f"BUILD={out}", "OPT=-O1", "fl", "monitor", "harness"], capture_output=True, text=True, timeout=900)
+    assert b.returncode == 0, b.stdout[-2000:] + b.stderr[-3000:]
+    harness, plugin = os.path.join(out, "bin", "fl_net_harness"), os.path.join(out, "lib", "libnccl-net-fuselink.so")
+    hf = str(tmp_path / "h")
+    env = dict(os.environ, NCCL_SOCKET_IFNAME="lo", NCCL_FUSELINK_DEGREE="2", FUSELINK_MIN_STRIPE_BYTES="65536")
+    rx = subprocess.Popen([harness, plugin, "recv", hf, "--chunk", "262144", str(3 << 20), "77"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    tx = subprocess.Popen([harness, plugin, "send", hf, "--chunk", "262144", str(3 << 20), "77"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    txo, txe = tx.communicate(timeout=120)
+    rxo, rxe = rx.communicate(timeout=120)
+    assert tx.returncode == 0 and rx.returncode == 0 and "OK received" in rxo, (txo, txe, rxo, rxe)
+    mon = subprocess.run([os.path.join(out, "bin", "fuselink-monitor"), "--shm", f"/fl_mk_{os.getpid()}", "--groups", "4", "--seconds", "0.2"],
+                         capture_output=True, text=True, timeout=30)
+    assert mon.returncode == 0, mon.stdout + mon.stderr
