@@ -4,6 +4,8 @@ import os
 import socket
 import tempfile
 
+import pytest
+
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -248,3 +250,29 @@ def test_moe_training_checkpoint_resume_reproduces_the_run(tmp_path):
     run3 = [json.loads(l)["loss"] for l in a.stdout.splitlines() if l.startswith("{")]
     assert first(fresh) == run3[0]                       # same seed, same first batch, same initial weights
     assert first(resumed) != first(fresh)                # the resumed run starts from the trained weights
+
+
+def test_dlrm_training_script_two_ranks_checkpoint_and_resume(tmp_path):
+    """experiments/run_dlrm_training.py on two gloo ranks: per-rank checkpoints (the tables differ), and a resumed run is
+    the same as the run that was never interrupted."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "experiments", "run_dlrm_training.py")
+    port = _free_port()
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", str(port),
+            script, "--device", "cpu", "--tables", "5", "--rows", "300", "--global-batch", "64", "--pooling", "4", "--lr", "0.5", "--log-every", "1"]
+    ck = str(tmp_path / "ck")
+    losses = lambda r: [json.loads(l)["loss"] for l in r.stdout.splitlines() if l.startswith("{")]
+    whole = subprocess.run(base + ["--steps", "4"], capture_output=True, text=True, timeout=300)
+    assert whole.returncode == 0, whole.stderr[-3000:]
+    first = subprocess.run(base + ["--steps", "2", "--checkpoint", ck], capture_output=True, text=True, timeout=300)
+    assert first.returncode == 0 and os.path.exists(ck + ".rank0") and os.path.exists(ck + ".rank1"), first.stderr[-3000:]
+    rest = subprocess.run(base + ["--steps", "2", "--resume", ck], capture_output=True, text=True, timeout=300)
+    assert rest.returncode == 0, rest.stderr[-3000:]
+    assert [json.loads(l)["step"] for l in rest.stdout.splitlines() if l.startswith("{")] == [3, 4]
+    assert losses(first) + losses(rest) == pytest.approx(losses(whole), abs=1e-5)
+    wrong = subprocess.run([sys.executable, script, "--device", "cpu", "--tables", "5", "--rows", "300", "--global-batch", "64", "--pooling", "4",
+                            "--steps", "1", "--resume", ck], capture_output=True, text=True, timeout=300)
+    assert wrong.returncode != 0 and "written by 2 ranks" in wrong.stderr
