@@ -203,6 +203,49 @@ def main():
     ms_per_step = ms / args.steps
     value = world * T * args.steps / (ms / 1e3)
 
+    # ---------------------------------------------------------------- the result line
+    def make_line(e2e, roof):
+        flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
+        return {
+            "metric": "MoE-EP tokens/s (fwd+bwd+SGD)", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "fp8 e4m3 1x128 block-scaled (fwd, dgrad) + bf16 (wgrad)" if cfg.fp8 else "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": "MoE-EP layer: hidden 4096, 8 experts SwiGLU 4096-14336-4096, top-2, Zipf(1.2) router bias"
+                       if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else
+                       f"MoE-EP layer h{args.hidden} f{args.ffn} e{args.experts} k{args.topk}",
+                       "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T, "parallelism": f"ep{world}",
+                       "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
+                       "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
+            "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roof,
+        }
+
+    # The device-timed number exists from here on.  Whatever happens in the end-to-end region (a rank that raises while
+    # the others wait in a collective, for instance), the line is printed exactly once: by the main thread, or by this
+    # timer when the region has not finished within its limit, after which the process ends.
+    out_lock = threading.Lock()
+    printed = [False]
+
+    def emit(e2e, roof):
+        with out_lock:
+            if printed[0]:
+                return
+            printed[0] = True
+            if rank == 0:
+                print(json.dumps(make_line(e2e, roof)))
+            sys.stdout.flush()
+
+    def give_up():
+        emit({"error": "the end-to-end region did not finish within its time limit"}, None)
+        os._exit(0)
+
+    limit_s = max(240.0, 40.0 * ms / 1e3)
+    guard = threading.Timer(limit_s, give_up)
+    guard.daemon = True
+    guard.start()
+
     # ---------------------------------------------------------------- end-to-end region (public API)
     e2e = None
     if not args.no_e2e:
@@ -273,24 +316,8 @@ def main():
     except Exception as e:  # noqa: BLE001 - reporting only
         roof = {"error": repr(e)}
 
-    if rank == 0:
-        flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
-        line = {
-            "metric": "MoE-EP tokens/s (fwd+bwd+SGD)", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
-            "dtype": "fp8 e4m3 1x128 block-scaled (fwd, dgrad) + bf16 (wgrad)" if cfg.fp8 else "bf16", "data": "synthetic",
-            "impl": args.impl,
-            "config": {"model": "MoE-EP layer: hidden 4096, 8 experts SwiGLU 4096-14336-4096, top-2, Zipf(1.2) router bias"
-                       if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else
-                       f"MoE-EP layer h{args.hidden} f{args.ffn} e{args.experts} k{args.topk}",
-                       "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T, "parallelism": f"ep{world}",
-                       "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
-                       "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
-            "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
-            "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roof,
-        }
-        print(json.dumps(line))
+    guard.cancel()
+    emit(e2e, roof)
     # the result is out: teardown must never be able to hang the job (a watchdog ends the process after 60 s)
     sys.stdout.flush()
     wd = threading.Timer(60.0, lambda: os._exit(0))
