@@ -106,6 +106,32 @@ def test_paged_prefill_and_decode_follow_the_dense_model(name):
         seq = torch.cat([seq, nxt.unsqueeze(1)], 1)
 
 
+@pytest.mark.parametrize("name", FAMILIES)
+def test_paged_path_runs_in_bf16(name):
+    """The serving dtype: every family goes through paged prefill and decode in bf16 without a dtype mismatch (norms in
+    fp32, everything else in bf16) and still mostly agrees with its own dense forward."""
+    cfg = MODEL_ZOO[name]
+    net = LlamaShard(cfg, device="cpu", dtype=torch.bfloat16, seed=2)
+    B, S, steps, bs = 2, 32, 3, cfg.block_size
+    nblk_max = (S + steps + bs - 1) // bs
+    nblocks = B * nblk_max + 3
+    perm = torch.randperm(nblocks, generator=torch.Generator().manual_seed(3))[: B * nblk_max].view(B, nblk_max).int()
+    elems = nblocks * cfg.layers * cfg.kv_heads * bs * cfg.head_dim
+    kp, vp = torch.zeros(elems, dtype=torch.bfloat16), torch.zeros(elems, dtype=torch.bfloat16)
+    tokens = torch.randint(0, cfg.vocab, (B, S), generator=torch.Generator().manual_seed(4))
+    first = net.prefill(tokens, kp, vp, perm)
+    L, H, D = cfg.layers, cfg.kv_heads, cfg.head_dim
+    kd = kp.view(nblocks, L, H, bs, D).permute(1, 0, 3, 2, 4).contiguous().view(-1)
+    vd = vp.view(nblocks, L, H, bs, D).permute(1, 0, 3, 2, 4).contiguous().view(-1)
+    seq = torch.cat([tokens, first.unsqueeze(1)], 1)
+    agree = 0
+    for t in range(steps):
+        nxt = net.decode_step(seq[:, -1], torch.full((B,), S + t, dtype=torch.long), kd, vd, perm, nblocks)
+        agree += int((nxt == net.forward_dense(seq).argmax(-1)).sum())
+        seq = torch.cat([seq, nxt.unsqueeze(1)], 1)
+    assert agree >= steps * B // 2
+
+
 def test_flat_checkpoint_round_trip():
     cfg = MODEL_ZOO["tiny_opt"]
     a = LlamaShard(cfg, device="cpu", dtype=torch.float32, seed=1)
