@@ -100,6 +100,9 @@ def parse():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--zipf", type=float, default=1.2)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--shadow", type=int, default=0,
+                    help="replicate the N experts the router favours most on every rank: their rows are computed where they originate and "
+                         "their weight gradients are summed over the ranks (fuselink arm, N GPUs > 1)")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="fp8: block-scaled e4m3 (1x128) forward/dgrad GEMMs")
     return ap.parse_args()
 
@@ -137,10 +140,11 @@ def main():
 
         W = world
         cap = (T * W + 127) // 128 * 128
-        rows = (cfg.num_experts // W) * cap
+        shadow = args.shadow if W > 1 else 0
+        rows = (cfg.num_experts // W + shadow) * cap
         heap_bytes = 2 * rows * H * 2 + rows * 4 + 2 * T * cfg.topk * H * 2 + (64 << 20)
         heap = SymmetricHeap.create(heap_bytes, device=local_rank)
-        layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr)
+        layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr, shadow_experts=shadow)
         expert_params = []          # updated inside the wgrad kernels' epilogue
     else:
         from fuselink_b200.models.moe_baseline import BaselineMoELayer
@@ -204,6 +208,8 @@ def main():
     value = world * T * args.steps / (ms / 1e3)
 
     # ---------------------------------------------------------------- the result line
+    shadowed = getattr(getattr(layer, "cfg", None), "shadow", ())
+
     def make_line(e2e, roof):
         flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
         return {
@@ -215,7 +221,8 @@ def main():
             "config": {"model": "MoE-EP layer: hidden 4096, 8 experts SwiGLU 4096-14336-4096, top-2, Zipf(1.2) router bias"
                        if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else
                        f"MoE-EP layer h{args.hidden} f{args.ffn} e{args.experts} k{args.topk}",
-                       "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T, "parallelism": f"ep{world}",
+                       "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T,
+                       "parallelism": f"ep{world}" + (f" + shadow experts {list(shadowed)}" if shadowed else ""),
                        "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
                        "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
             "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,

@@ -6,6 +6,7 @@ math runs as plain PyTorch with an all-gather of the tokens and a reduce-scatter
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Optional
 
 import torch
@@ -61,8 +62,14 @@ class MoELayer(nn.Module):
     def __init__(self, cfg: MoEConfig, heap: Optional[SymmetricHeap] = None, rank: int = 0, world: int = 1,
                  device="cuda", zipf_s: Optional[float] = 1.2, seed: int = 0, fused_sgd_lr: float = 0.0,
                  name: str = "moe", capacity_factor: float = 0.0, drop_tokens: bool = False, min_capacity: int = 4,
-                 noisy_gate: Optional[str] = None, jitter_eps: float = 1e-2):
+                 noisy_gate: Optional[str] = None, jitter_eps: float = 1e-2, shadow_experts=0):
         super().__init__()
+        bias = zipf_log_bias(cfg.num_experts, zipf_s) if zipf_s else torch.zeros(cfg.num_experts)
+        if isinstance(shadow_experts, int):
+            # the n experts the router favours most (its bias is the same on every rank, so is the choice)
+            shadow_experts = torch.argsort(bias, descending=True, stable=True)[:shadow_experts].tolist() if shadow_experts > 0 else []
+        if tuple(shadow_experts) != tuple(cfg.shadow):
+            cfg = dataclasses.replace(cfg, shadow=tuple(int(e) for e in shadow_experts))
         self.cfg, self.rank, self.world = cfg, rank, world
         assert noisy_gate in (None, "jitter", "rsample")
         self.capacity_factor, self.drop_tokens, self.min_capacity = capacity_factor, drop_tokens, min_capacity
@@ -75,19 +82,19 @@ class MoELayer(nn.Module):
         g = torch.Generator().manual_seed(seed)
         H, F, E = cfg.hidden, cfg.ffn, cfg.num_experts
         self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16).to(device))
-        bias = zipf_log_bias(E, zipf_s) if zipf_s else torch.zeros(E)
         self.register_buffer("router_bias", bias.to(device))
-        # this rank's experts only; every expert's init depends on (seed, global expert id), not on the layout
+        # this rank's experts, then its copies of the shadowed experts (ops.moe.slot_table); every expert's init depends on
+        # (seed, global expert id), not on the layout, so a copy starts out equal to the owner's expert
         w13, w2 = [], []
-        for le in range(self.epr):
-            ge = torch.Generator().manual_seed(seed * 1000 + 17 + rank * self.epr + le)
+        for e in [rank * self.epr + le for le in range(self.epr)] + list(cfg.shadow):
+            ge = torch.Generator().manual_seed(seed * 1000 + 17 + e)
             wg = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
             wu = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
             wd = (torch.randn(H, F, generator=ge) * 0.02).to(torch.bfloat16)
             w13.append(gemm.interleave_gate_up(wg, wu))
             w2.append(wd)
-        self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr, 2F, H], gate/up interleaved by 128
-        self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr, H, F]
+        self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr + shadows, 2F, H], gate/up interleaved by 128
+        self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr + shadows, H, F]
         self.ws = MoEWorkspace(heap, cfg, name) if heap is not None else None
 
     # -- routing ------------------------------------------------------------------------------------------
@@ -111,6 +118,15 @@ class MoELayer(nn.Module):
             self.dropped_fraction = 1.0 - keep.float().mean()
             w = w * keep.to(w.dtype)
         return w, idx.int()
+
+    @torch.no_grad()
+    def sync_shadow_to_real(self) -> None:
+        """Copy this rank's copy of every shadowed expert it owns into the expert's own slot (which receives no rows while
+        the expert is shadowed and so goes stale): call before exporting the experts or changing the set of shadows."""
+        for j, e in enumerate(self.cfg.shadow):
+            if e // self.epr == self.rank:
+                self.w13[e % self.epr].copy_(self.w13[self.epr + j])
+                self.w2[e % self.epr].copy_(self.w2[self.epr + j])
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, idx = self.route(x)

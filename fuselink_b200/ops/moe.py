@@ -14,7 +14,7 @@ There is no stand-alone all-to-all and no framework permute in either direction;
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -32,6 +32,31 @@ class MoEConfig:
     topk: int = 2
     tokens: int = 8192          # tokens per rank and step
     fp8: bool = False           # block-scaled e4m3 ("1 x 128") for the forward and dgrad GEMMs; wgrad stays bf16
+    shadow: Tuple[int, ...] = ()  # experts replicated on every rank ("shadow" experts), see slot_table()
+
+
+def slot_table(num_experts: int, world: int, shadow: Sequence[int], rank: int) -> torch.Tensor:
+    """Where rank ``rank`` sends a row that chose expert e: the slot number ``dest_rank * slots_per_rank + local_slot``.
+
+    Every rank has ``E / W`` slots for the experts it owns followed by one slot per shadowed expert.  A row for an
+    ordinary expert goes to the owner's slot.  A row for a shadowed expert stays on the rank it comes from, in that
+    rank's copy of the expert; the owner's own slot for it stays empty.  This is what removes the load imbalance of a
+    skewed router: a hot expert's rows are computed where they originate, spread over all ranks, at the price of
+    summing that expert's weight gradients over the ranks (FasterMoE calls such replicas shadow experts).  The kernels
+    see slots as "experts" and need no change: owner = slot // slots_per_rank.
+
+    The table has E + 2 entries and is indexed with ``clamp(e, -1, E) + 1``, so an expert id out of range maps to -1,
+    which the dispatch kernel reports through the status word like any other bad index."""
+    assert num_experts % world == 0
+    real = num_experts // world
+    spr = real + len(shadow)
+    assert len(set(shadow)) == len(shadow) and all(0 <= e < num_experts for e in shadow)
+    t = torch.full((num_experts + 2,), -1, dtype=torch.int32)
+    for e in range(num_experts):
+        t[e + 1] = (e // real) * spr + e % real
+    for j, e in enumerate(shadow):
+        t[e + 1] = rank * spr + real + j
+    return t
 
 
 class MoEWorkspace:
@@ -42,7 +67,10 @@ class MoEWorkspace:
         self.heap, self.cfg, self.name = heap, cfg, name
         W = heap.world
         assert cfg.num_experts % W == 0, "experts must divide evenly over ranks"
-        self.epr = cfg.num_experts // W
+        self.epr_real = cfg.num_experts // W              # experts this rank owns
+        self.nshadow = len(cfg.shadow)                    # + its copies of the shadowed experts
+        self.epr = self.epr_real + self.nshadow           # slots per rank: what the kernels call experts per rank
+        self.num_slots = W * self.epr
         self.cap = (cfg.tokens * W + 127) // 128 * 128
         rows = self.epr * self.cap
         H, F, T, k = cfg.hidden, cfg.ffn, cfg.tokens, cfg.topk
@@ -59,8 +87,11 @@ class MoEWorkspace:
         self.act = torch.empty(rows, F, dtype=bf, device=dev)
         self.gu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
         self.dgu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
-        self.local_count = torch.zeros(cfg.num_experts, dtype=torch.int32, device=dev)
-        self.base = torch.zeros(cfg.num_experts, dtype=torch.int32, device=dev)
+        self.local_count = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
+        self.base = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
+        self.slots_of = slot_table(cfg.num_experts, W, cfg.shadow, heap.rank).to(dev) if self.nshadow else None
+        # sums the shadow experts' weight gradients over the ranks, in place; replaced in tests that emulate ranks on one GPU
+        self.reduce_shadow_grads = _allreduce_shadow_grads
         self.pos = torch.zeros(T, k, dtype=torch.int32, device=dev)
         self.slot = torch.zeros(T, k, dtype=torch.int32, device=dev)
         if cfg.fp8:
@@ -73,6 +104,7 @@ class MoEWorkspace:
             self.q_dgu = torch.empty(rows, 2 * F, dtype=f8, device=dev)     # quantised dgate/dup
             self.s_dgu = torch.empty(rows, 2 * F // 128, dtype=torch.float32, device=dev)
             self.wq = {}                                                     # per-weight (e4m3, scales), refreshed each step
+        self.pending_shadow = None
         self.parity = 0
         self.step_parity = 0
         self.launches = 0   # kernels of this library launched through this workspace (bench accounting)
@@ -81,10 +113,19 @@ class MoEWorkspace:
         return self.counts.local[self.step_parity]
 
 
+def _allreduce_shadow_grads(ws: MoEWorkspace, grads) -> None:
+    if ws.heap.world > 1:
+        import torch.distributed as dist
+        for g in grads:
+            dist.all_reduce(g)
+
+
 def _dispatch(ws: MoEWorkspace, x: torch.Tensor, idx: torch.Tensor, scale: Optional[torch.Tensor], dst, reuse: bool):
     C = require_native()
     h, cfg = ws.heap, ws.cfg
-    C.moe_dispatch(x, idx, scale, cfg.num_experts, ws.epr, ws.cap, h.rank, h.world, ws.local_count, ws.base, ws.pos,
+    if ws.slots_of is not None:
+        idx = ws.slots_of[(idx.clamp(-1, cfg.num_experts) + 1).long()]          # expert id -> slot (see slot_table)
+    C.moe_dispatch(x, idx, scale, ws.num_slots, ws.epr, ws.cap, h.rank, h.world, ws.local_count, ws.base, ws.pos,
                    ws.slot, ws.counts.peers(), ws.step_parity, dst.peers(), ws.info.peers(), reuse, h.status_addr)
     ws.launches += 1 if reuse else 3
 
@@ -184,7 +225,26 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
         if need_dx:
             gemm.grouped_gemm_rows(ws.dgu, w13, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER,
                                    row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st)
-    if sgd_lr:
+    shadow_grads = None
+    if ws.nshadow:
+        # Owned experts as below, on the leading slots.  The copies of the shadowed experts have seen this rank's rows
+        # only: their gradients are stored, summed over the ranks after the signal and applied then, identically on
+        # every rank, so the copies stay equal without ever being sent.
+        R, S, cut = ws.epr_real, ws.nshadow, ws.epr_real * ws.cap
+        dyd, dgu, act, xd = ws.dyd.local, ws.dgu, ws.act, ws.xd.local
+        if sgd_lr:
+            gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=w2[:R], sgd_lr=sgd_lr, status=st)
+            gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=w13[:R], sgd_lr=sgd_lr, status=st)
+            dw2 = dw13 = None
+        else:
+            dw2 = torch.empty_like(w2)
+            dw13 = torch.empty_like(w13)
+            gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=dw2[:R], status=st)
+            gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=dw13[:R], status=st)
+        shadow_grads = (gemm.grouped_gemm_wgrad(dgu[cut:], xd[cut:], counts[R:], ws.cap, S, status=st),
+                        gemm.grouped_gemm_wgrad(dyd[cut:], act[cut:], counts[R:], ws.cap, S, status=st))
+        ws.launches += 2
+    elif sgd_lr:
         gemm.grouped_gemm_wgrad(ws.dyd.local, ws.act, counts, ws.cap, ws.epr, out=w2, sgd_lr=sgd_lr, status=st)
         gemm.grouped_gemm_wgrad(ws.dgu, ws.xd.local, counts, ws.cap, ws.epr, out=w13, sgd_lr=sgd_lr, status=st)
         dw2 = dw13 = None
@@ -194,13 +254,33 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     # every read of the buffers peers will overwrite next step is enqueued before this signal
     barrier(h, ws.name + ":bx", signal=True, wait=False)
     ws.launches += 6 + (1 if need_dx else 0)
+    # finished in moe_backward_finish: the sum over ranks runs while the other ranks complete their GEMMs
+    ws.pending_shadow = None if shadow_grads is None else (shadow_grads, w13, w2, dw13, dw2, sgd_lr)
     return dw13, dw2
+
+
+def finish_shadow_grads(ws: MoEWorkspace) -> None:
+    """Sum the shadow experts' weight gradients over the ranks, then SGD on the copies (the same update on every rank, so
+    they stay equal) or, without the fused update, the trailing slots of the gradients moe_backward_experts returned."""
+    if ws.pending_shadow is None:
+        return
+    (g13, g2), w13, w2, dw13, dw2, sgd_lr = ws.pending_shadow
+    ws.pending_shadow = None
+    ws.reduce_shadow_grads(ws, (g13, g2))
+    R = ws.epr_real
+    if sgd_lr:
+        w13[R:].add_(g13, alpha=-sgd_lr)
+        w2[R:].add_(g2, alpha=-sgd_lr)
+    else:
+        dw13[R:].copy_(g13)
+        dw2[R:].copy_(g2)
 
 
 def moe_backward_finish(ws: MoEWorkspace, need_dx: bool = True) -> Optional[torch.Tensor]:
     """Phase 3: wait for the returned input-gradient rows and sum them over k."""
     C = require_native()
     cfg = ws.cfg
+    finish_shadow_grads(ws)
     barrier(ws.heap, ws.name + ":bx", signal=False, wait=True)
     ws.launches += 1
     if not need_dx:

@@ -79,6 +79,38 @@ def main():
         for m in (fused, base):
             m.zero_grad(set_to_none=True)
 
+    # ---- MoE with the two hottest experts replicated on every rank (not run on a GPU yet: opt-in) ----------------
+    if os.environ.get("FUSELINK_TEST_UNVERIFIED", "0") == "1":
+        from fuselink_b200.ops import gemm
+        sh = MoELayer(cfg, heap, rank, world, device=dev, seed=4, fused_sgd_lr=0.0, name="moe_sh", shadow_experts=2)
+        epr, F = cfg.num_experts // world, cfg.ffn
+        for step in range(2):
+            g = torch.Generator(device=dev).manual_seed(90 + step * 10 + rank)
+            x = torch.randn(cfg.tokens, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+            xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+            oa, ob = sh(xa), base(xb)
+            (oa.float().pow(2).mean()).backward()
+            (ob.float().pow(2).mean()).backward()
+            torch.cuda.synchronize()
+            heap.check_status("moe shadow")
+
+            def close(a, b, what, tol=5e-2):
+                err = (a.float() - b.float()).abs().max().item()
+                den = b.float().abs().max().item() + 1e-6
+                assert err < tol * den, f"rank {rank} step {step} shadow {what}: err {err} vs {den}"
+
+            close(oa, ob, "out")
+            close(xa.grad, xb.grad, "dx")
+            dg, du = gemm.deinterleave_gate_up(sh.w13.grad)
+            for le in range(epr):
+                e = rank * epr + le
+                slot = epr + sh.cfg.shadow.index(e) if e in sh.cfg.shadow else le     # the summed gradient sits in the copy
+                close(dg[slot], base.w13.grad[le, :F], f"dWgate expert {e}")
+                close(du[slot], base.w13.grad[le, F:], f"dWup expert {e}")
+                close(sh.w2.grad[slot], base.w2.grad[le], f"dW2 expert {e}")
+            for m in (sh, base):
+                m.zero_grad(set_to_none=True)
+
     # ---- DLRM: fused embedding-bag + all-to-all vs EmbeddingBag + NCCL ------------------------------------
     dcfg = DLRMConfig(num_tables=10, rows=4000, dim=128, pooling=20, global_batch=64 * world, lr=0.05)
     a = DLRM(dcfg, heap, rank, world, device=dev, seed=9)

@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False):
+def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=()):
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops import gemm, moe as M, ref
     from fuselink_b200.parallel.symm import SymmetricHeap
@@ -13,13 +13,15 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False):
     ftol = 4.0 if fp8 else 1.0      # e4m3 operands: a few percent of relative error per GEMM
     heaps = SymmetricHeap.emulated(world, 64 << 20)
     try:
-        layers = [MoELayer(cfg, heaps[r], r, world, device="cuda", seed=3, fused_sgd_lr=sgd, name="m") for r in range(world)]
+        layers = [MoELayer(cfg, heaps[r], r, world, device="cuda", seed=3, fused_sgd_lr=sgd, name="m", shadow_experts=list(shadow))
+                  for r in range(world)]
+        epr = E // world
         for r in range(1, world):
             layers[r].router.data.copy_(layers[0].router.data)
         wg_all, wu_all, w2_all = [], [], []
         for l in layers:
-            g_, u_ = gemm.deinterleave_gate_up(l.w13.data)
-            wg_all.append(g_.float()); wu_all.append(u_.float()); w2_all.append(l.w2.data.float())
+            g_, u_ = gemm.deinterleave_gate_up(l.w13.data[:epr])          # the experts themselves; copies of shadowed ones follow
+            wg_all.append(g_.float()); wu_all.append(u_.float()); w2_all.append(l.w2.data[:epr].float())
         wg, wu, w2 = (torch.cat(v).clone().requires_grad_(True) for v in (wg_all, wu_all, w2_all))
         for step in range(steps):
             gen = torch.Generator(device="cuda").manual_seed(100 + step)
@@ -52,6 +54,11 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False):
             # backward
             dws = [M.moe_backward_dispatch(wss[r], douts[r], routes[r][1].contiguous(), routes[r][0].contiguous()) for r in range(world)]
             grads = [M.moe_backward_experts(wss[r], layers[r].w13.data, layers[r].w2.data, sgd, True) for r in range(world)]
+            if shadow:
+                # the ranks are emulated on one GPU: the sum over ranks that NCCL would do is done here
+                totals = [sum(wss[r].pending_shadow[0][i] for r in range(world)) for i in range(2)]
+                for w_ in wss:
+                    w_.reduce_shadow_grads = lambda ws_, gs, totals=totals: [g.copy_(t) for g, t in zip(gs, totals)]
             dxs = [M.moe_backward_finish(wss[r], True) for r in range(world)]
             torch.cuda.synchronize()
             for h in heaps:
@@ -64,14 +71,16 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False):
             for r in range(world):
                 close(dxs[r], xr[r].grad, f"dx rank {r}")
                 close(dws[r], wr[r].grad, f"dw rank {r}")
-            epr = E // world
-            if not sgd:
+            # slot -> expert: a rank's own experts, then its copies of the shadowed ones (whose own slots stay idle)
+            own = lambda r: [e for e in range(r * epr, (r + 1) * epr)]
+            pick = lambda r: [i for i, e in enumerate(own(r)) if e not in shadow]
+            if not shadow and not sgd:
                 for r in range(world):
                     dg, du = gemm.deinterleave_gate_up(grads[r][0])
                     close(dg, wg.grad[r * epr:(r + 1) * epr], f"dWgate rank {r}")
                     close(du, wu.grad[r * epr:(r + 1) * epr], f"dWup rank {r}")
                     close(grads[r][1], w2.grad[r * epr:(r + 1) * epr], f"dW2 rank {r}")
-            else:
+            elif not shadow:
                 with torch.no_grad():
                     for t in (wg, wu, w2):
                         t -= sgd * t.grad
@@ -79,6 +88,30 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False):
                     g_, u_ = gemm.deinterleave_gate_up(layers[r].w13.data)
                     close(g_, wg.detach()[r * epr:(r + 1) * epr], f"Wgate after sgd rank {r}", 2e-2)
                     close(layers[r].w2.data, w2.detach()[r * epr:(r + 1) * epr], f"W2 after sgd rank {r}", 2e-2)
+            elif not sgd:
+                for r in range(world):
+                    dg, du = gemm.deinterleave_gate_up(grads[r][0])
+                    for i in pick(r):
+                        close(dg[i], wg.grad[own(r)[i]], f"dWgate rank {r} slot {i}")
+                        close(du[i], wu.grad[own(r)[i]], f"dWup rank {r} slot {i}")
+                        close(grads[r][1][i], w2.grad[own(r)[i]], f"dW2 rank {r} slot {i}")
+                    for j, e in enumerate(shadow):                      # summed over the ranks: the expert's whole gradient
+                        close(dg[epr + j], wg.grad[e], f"dWgate shadow {e} on rank {r}")
+                        close(du[epr + j], wu.grad[e], f"dWup shadow {e} on rank {r}")
+                        close(grads[r][1][epr + j], w2.grad[e], f"dW2 shadow {e} on rank {r}")
+            else:
+                with torch.no_grad():
+                    for t in (wg, wu, w2):
+                        t -= sgd * t.grad
+                for r in range(world):
+                    g_, u_ = gemm.deinterleave_gate_up(layers[r].w13.data)
+                    for i in pick(r):
+                        close(g_[i], wg.detach()[own(r)[i]], f"Wgate after sgd rank {r} slot {i}", 2e-2)
+                        close(layers[r].w2.data[i], w2.detach()[own(r)[i]], f"W2 after sgd rank {r} slot {i}", 2e-2)
+                    for j, e in enumerate(shadow):
+                        close(g_[epr + j], wg.detach()[e], f"Wgate copy of {e} after sgd rank {r}", 2e-2)
+                        close(layers[r].w2.data[epr + j], w2.detach()[e], f"W2 copy of {e} after sgd rank {r}", 2e-2)
+                        assert torch.equal(layers[r].w2.data[epr + j], layers[0].w2.data[epr + j]), "copies must stay identical"
     finally:
         for h in heaps:
             h.close()
@@ -93,6 +126,22 @@ def test_moe_fwd_bwd(world):
 @pytest.mark.parametrize("world", [1, 2])
 def test_moe_fwd_bwd_fp8_block_scaled(world):
     _run(world, fp8=True)
+
+
+_UNVERIFIED = pytest.mark.skipif(__import__("os").environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1",
+                                 reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
+
+
+@_UNVERIFIED
+@pytest.mark.parametrize("world,shadow", [(2, (0,)), (4, (0, 5)), (1, (2,))])
+def test_moe_shadow_experts(world, shadow):
+    """Hot experts replicated on every rank: same outputs and gradients as without, the copies' gradients summed."""
+    _run(world, shadow=shadow)
+
+
+@_UNVERIFIED
+def test_moe_shadow_experts_two_steps_fused_sgd():
+    _run(2, sgd=0.05, steps=2, shadow=(1,))
 
 
 def test_moe_two_steps_fused_sgd():

@@ -1,0 +1,96 @@
+"""Shadow experts: the slot arithmetic, the replicated initialisation and the gradient rule, checked on the CPU with the
+plain-PyTorch expert function standing in for the grouped GEMMs (the kernels see slots as experts and do not change)."""
+import torch
+
+from fuselink_b200.models.moe import MoELayer
+from fuselink_b200.ops import gemm, ref
+from fuselink_b200.ops.moe import MoEConfig, slot_table
+
+
+def test_slot_table_sends_ordinary_rows_to_the_owner_and_shadowed_rows_nowhere():
+    E, W, shadow = 8, 4, (5, 0)
+    real, spr = E // W, E // W + len(shadow)
+    for rank in range(W):
+        t = slot_table(E, W, shadow, rank)
+        assert t[0] == -1 and t[E + 1] == -1                       # ids out of range, after clamp(e, -1, E) + 1
+        slots = t[1:E + 1].tolist()
+        assert len(set(slots)) == E                                 # no two experts share a slot
+        for e, s in enumerate(slots):
+            dest, local = divmod(s, spr)
+            if e in shadow:
+                assert dest == rank and local == real + shadow.index(e)
+            else:
+                assert dest == e // real and local == e % real
+    bad = torch.tensor([-7, 99, 3])
+    assert slot_table(E, W, shadow, 0)[(bad.clamp(-1, E) + 1).long()].tolist()[:2] == [-1, -1]
+
+
+def test_shadow_choice_follows_the_router_bias_and_copies_start_equal():
+    cfg = MoEConfig(hidden=128, ffn=256, num_experts=8, topk=2, tokens=16)
+    W = 4
+    layers = [MoELayer(cfg, None, r, W, device="cpu", zipf_s=1.2, seed=5, shadow_experts=2) for r in range(W)]
+    assert all(l.cfg.shadow == (0, 1) for l in layers)              # Zipf bias: experts 0 and 1 are the hot ones
+    assert cfg.shadow == ()                                         # the caller's config is not modified
+    assert layers[0].w13.shape[0] == 2 + 2 and layers[0].w2.shape[0] == 4
+    for l in layers:                                                # every copy equals the owner's expert
+        assert torch.equal(l.w13[2], layers[0].w13[0]) and torch.equal(l.w13[3], layers[0].w13[1])
+        assert torch.equal(l.w2[2], layers[0].w2[0]) and torch.equal(l.w2[3], layers[0].w2[1])
+    explicit = MoELayer(cfg, None, 1, W, device="cpu", zipf_s=None, seed=5, shadow_experts=[6])
+    assert explicit.cfg.shadow == (6,) and torch.equal(explicit.w2[2], MoELayer(cfg, None, 3, W, device="cpu", seed=5).w2[0])
+    plain = MoELayer(cfg, None, 1, W, device="cpu", seed=5)
+    assert plain.cfg.shadow == () and plain.w13.shape[0] == 2 and torch.equal(plain.w13.data, layers[1].w13.data[:2])
+
+
+def test_slot_level_computation_equals_the_unshadowed_one_and_gradients_add_up():
+    """What the fused path does with slots, in plain PyTorch: every rank's rows for a shadowed expert run through that
+    rank's copy.  Outputs equal the ordinary formulation; the gradient of the expert is the sum of the copies' gradients
+    (which is why they are all-reduced), and the owner's own slot of a shadowed expert sees nothing."""
+    torch.manual_seed(0)
+    E, W, T, H, F, k = 8, 4, 24, 128, 256, 2
+    cfg = MoEConfig(hidden=H, ffn=F, num_experts=E, topk=k, tokens=T)
+    layers = [MoELayer(cfg, None, r, W, device="cpu", zipf_s=1.2, seed=9, shadow_experts=[0, 3]) for r in range(W)]
+    real, spr = E // W, E // W + 2
+    shadow = layers[0].cfg.shadow
+    xs = [torch.randn(T, H) for _ in range(W)]
+    routes = [layers[r].route(xs[r].to(torch.bfloat16)) for r in range(W)]
+    # the experts, once each (fp32 leaves)
+    wg_r, wu_r, w2_r = [], [], []
+    for l in layers:
+        g_, u_ = gemm.deinterleave_gate_up(l.w13.data[:real])
+        wg_r.append(g_.float()); wu_r.append(u_.float()); w2_r.append(l.w2.data[:real].float())
+    wg, wu, w2 = (torch.cat(v).clone().requires_grad_(True) for v in (wg_r, wu_r, w2_r))
+    want = [ref.moe_forward(xs[r], routes[r][1], routes[r][0].detach().float(), wg, wu, w2) for r in range(W)]
+    sum(o.sum() for o in want).backward()
+    # all slots of all ranks (fp32 leaves): [W * spr, ...]
+    sg_, su_, s2_ = [], [], []
+    for l in layers:
+        g_, u_ = gemm.deinterleave_gate_up(l.w13.data)
+        sg_.append(g_.float()); su_.append(u_.float()); s2_.append(l.w2.data.float())
+    sg, su, s2 = (torch.cat(v).clone().requires_grad_(True) for v in (sg_, su_, s2_))
+    got = []
+    for r in range(W):
+        slots = slot_table(E, W, shadow, r)[(routes[r][1].clamp(-1, E) + 1).long()]
+        got.append(ref.moe_forward(xs[r], slots, routes[r][0].detach().float(), sg, su, s2))
+    sum(o.sum() for o in got).backward()
+    for r in range(W):
+        assert torch.allclose(got[r], want[r], atol=1e-5)
+    grads = s2.grad.view(W, spr, H, F)
+    for e in range(E):
+        owner, local = divmod(e, real)
+        if e in shadow:
+            j = shadow.index(e)
+            assert torch.allclose(grads[:, real + j].sum(0), w2.grad[e], atol=1e-5)      # sum over the copies
+            assert grads[owner, local].abs().max() == 0                                   # the owner's own slot is idle
+        else:
+            assert torch.allclose(grads[owner, local], w2.grad[e], atol=1e-5)
+
+
+def test_sync_shadow_to_real_refreshes_the_owners_slot():
+    cfg = MoEConfig(hidden=128, ffn=256, num_experts=4, topk=2, tokens=8)
+    l = MoELayer(cfg, None, 1, 2, device="cpu", seed=1, shadow_experts=[2, 0])     # rank 1 owns experts 2 and 3
+    with torch.no_grad():
+        l.w13[2].add_(1.0); l.w2[2].add_(1.0)                                       # its copy of expert 2 has been trained
+        l.w13[3].add_(5.0)                                                          # copy of expert 0: not this rank's to export
+    before = l.w13[1].clone()
+    l.sync_shadow_to_real()
+    assert torch.equal(l.w13[0], l.w13[2]) and torch.equal(l.w2[0], l.w2[2]) and torch.equal(l.w13[1], before)
