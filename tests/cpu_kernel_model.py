@@ -1,0 +1,166 @@
+"""A functional model, in plain PyTorch on host memory, of the device entry points the MoE path calls
+(`moe_dispatch`, `moe_zero_tail`, `grouped_gemm` with its five epilogues, `moe_combine`, `moe_combine_dw`, `barrier`).
+
+It takes the same arguments as the bindings of the real extension, raw addresses of peers' buffers included, and does to
+the memory behind them what the kernels are specified to do.  With it the Python side of `ops/moe.py` -- buffer sizes,
+slices, parities, the order of the phases, what is handed to which call -- runs on a machine without a GPU, over a
+symmetric heap that lives in host memory (`SymmetricHeap.emulated` on the memfd backend).  It says nothing about the
+kernels themselves; those are tested on the GPU against the same fp32 oracle.
+
+Use: ``with cpu_kernel_model.installed(): ...`` replaces ``require_native`` in the modules of the MoE path.
+"""
+import contextlib
+
+import torch
+
+EPI_STORE, EPI_SWIGLU, EPI_SCATTER, EPI_DSWIGLU, EPI_WGRAD = 0, 1, 2, 3, 4
+
+
+class Model:
+    """Everything that is not modelled (the cuMem layer, tensor_from_ptr, ...) is the real extension's."""
+
+    def __init__(self, real):
+        self._real = real
+
+    def __getattr__(self, name):
+        return getattr(self._real, name)
+
+    def _view(self, addr, shape, dtype):
+        return self._real.tensor_from_ptr(int(addr), list(shape), dtype, -1)
+
+    def _status(self, status_addr, code, where):
+        st = self._view(status_addr, [8], torch.int32)
+        if st[0] == 0:
+            st[0], st[1] = code, where
+
+    # ---------------------------------------------------------------------------------------- barrier
+    def barrier(self, pads, slot0, rank, world, seq, do_signal, do_wait, status_addr):
+        # the phases of the emulated ranks run one after the other in one thread: nothing to wait for
+        return None
+
+    # ---------------------------------------------------------------------------------------- dispatch
+    def moe_dispatch(self, x, topk_idx, row_scale, num_experts, epr, cap, rank, world, local_count, base, pos, slot,
+                     count_peers, parity, x_peers, info_peers, reuse, status_addr):
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and topk_idx.dtype == torch.int32 and topk_idx.is_contiguous()
+        assert epr * world == num_experts and local_count.numel() >= num_experts and base.numel() >= num_experts
+        T, k = topk_idx.shape
+        H = x.shape[1]
+        idx = topk_idx.view(-1)
+        posf, slotf = pos.view(-1), slot.view(-1)
+        if not reuse:
+            for i in range(T * k):
+                e = int(idx[i])
+                if e < 0 or e >= num_experts:
+                    self._status(status_addr, 6, 1100)
+                    posf[i] = -1
+                    continue
+                posf[i] = local_count[e]
+                local_count[e] += 1
+            for e in range(num_experts):
+                owner, le = divmod(e, epr)
+                cnt = self._view(count_peers[owner], [2, epr], torch.int32)
+                n = int(local_count[e])
+                base[e] = int(cnt[parity, le]) if n > 0 else 0
+                cnt[parity, le] += n
+                local_count[e] = 0
+            self._view(count_peers[rank], [2, epr], torch.int32)[parity ^ 1].zero_()
+        for i in range(T * k):
+            e = int(idx[i])
+            if e < 0 or e >= num_experts:
+                continue
+            owner, le = divmod(e, epr)
+            if reuse:
+                row = int(slotf[i])
+            else:
+                r = int(base[e]) + int(posf[i])
+                row = le * cap + r if (0 <= r < cap and int(posf[i]) >= 0) else -1
+                slotf[i] = row
+            if row < 0 or row >= epr * cap:
+                self._status(status_addr, 6, 1101)
+                continue
+            dst = self._view(x_peers[owner], [epr * cap, H], torch.bfloat16)
+            src = x[i // k]
+            dst[row] = (src.float() * float(row_scale.view(-1)[i])).to(torch.bfloat16) if row_scale is not None else src
+            if not reuse:
+                self._view(info_peers[owner], [epr * cap], torch.int32)[row] = (rank << 28) | i
+
+    def moe_zero_tail(self, buf, counts, experts_local, cap, width):
+        cnt = self._view(counts, [experts_local], torch.int32)
+        rows = self._view(buf, [experts_local * cap, width], torch.bfloat16)
+        for e in range(experts_local):
+            n = min(int(cnt[e]), cap)
+            rows[e * cap + n: e * cap + min((n + 127) // 128 * 128, cap)].zero_()
+
+    def moe_combine(self, slots, w, out, topk):
+        T, H = out.shape
+        v = slots.view(T, topk, H).float()
+        out.copy_(((v * w.view(T, topk, 1)) if w is not None else v).sum(1).to(out.dtype))
+
+    def moe_combine_dw(self, dout, slots, dw, topk):
+        T, H = dout.shape
+        dw.copy_((slots.view(T, topk, H).float() * dout.float().view(T, 1, H)).sum(-1))
+
+    # ---------------------------------------------------------------------------------------- grouped GEMM
+    def grouped_gemm(self, mode, G, cap, M, N, K, counts, A, a_mn, lda, gsa, B, b_mn, ldb, gsb, epilogue, out, ldc, gsc,
+                     gu, ldgu, dgu, row_info, peers, sgd_lr, zero_tail, group_m, max_ctas, status):
+        assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
+        assert counts is None or (counts.dtype == torch.int32 and counts.numel() >= G)
+        if mode == 1:                                               # K-grouped: C_g = A_g^T @ B_g over the group's rows
+            assert epilogue == EPI_WGRAD and A.shape == (G * cap, M) and B.shape == (G * cap, N) and out.shape == (G, M, N)
+            for g in range(G):
+                n = min(int(counts[g]), cap)
+                c = A[g * cap: g * cap + n].float().t() @ B[g * cap: g * cap + n].float()
+                out[g] = ((out[g].float() - sgd_lr * c) if sgd_lr else c).to(torch.bfloat16)
+            return
+        assert A.shape == (G * cap, K) and B.shape[0] == G
+        for g in range(G):
+            n = min(int(counts[g]), cap) if counts is not None else cap
+            tail = min((n + 127) // 128 * 128, cap) if zero_tail else n
+            rows = slice(g * cap, g * cap + n)
+            pad = slice(g * cap + n, g * cap + tail)
+            b = B[g].float()
+            c = A[rows].float() @ (b if b_mn else b.t())            # [n, N]
+            assert c.shape[1] == N
+            if epilogue == EPI_STORE:
+                out[rows] = c.to(torch.bfloat16)
+                out[pad] = 0
+            elif epilogue == EPI_SWIGLU:                            # columns in blocks of 256: 128 gate | 128 up
+                v = c.view(n, N // 256, 2, 128)
+                gate, up = v[:, :, 0], v[:, :, 1]
+                out[rows] = (torch.nn.functional.silu(gate) * up).reshape(n, N // 2).to(torch.bfloat16)
+                out[pad] = 0
+                if gu is not None:
+                    gu[rows] = c.to(torch.bfloat16)
+                    gu[pad] = 0
+            elif epilogue == EPI_SCATTER:                           # every row goes back to where its token lives
+                info = row_info[rows]
+                for r in range(n):
+                    home, i = (int(info[r]) >> 28) & 0xF, int(info[r]) & 0x0FFFFFFF
+                    self._view(peers[home] + i * ldc * 2, [N], torch.bfloat16).copy_(c[r].to(torch.bfloat16))
+            elif epilogue == EPI_DSWIGLU:                           # c = dAct [n, F]; saved gate/up -> dGate/dUp, interleaved
+                v = gu[rows].float().view(n, N // 128, 2, 128)
+                gate, up = v[:, :, 0], v[:, :, 1]
+                da = c.view(n, N // 128, 128)
+                s = torch.sigmoid(gate)
+                dg = da * up * (s * (1 + gate * (1 - s)))
+                du = da * gate * s
+                dgu[rows] = torch.stack([dg, du], 2).reshape(n, 2 * N).to(torch.bfloat16)
+                dgu[pad] = 0
+            else:
+                raise AssertionError("WGRAD needs the K-grouped mode")
+
+
+@contextlib.contextmanager
+def installed():
+    """Inside the block the MoE path's modules get the model instead of the extension."""
+    from fuselink_b200 import _ext
+    from fuselink_b200.ops import comm, gemm, moe
+    model = Model(_ext.require_native())
+    saved = [(m, m.require_native) for m in (comm, gemm, moe)]
+    for m, _ in saved:
+        m.require_native = lambda model=model: model
+    try:
+        yield model
+    finally:
+        for m, f in saved:
+            m.require_native = f

@@ -5,15 +5,16 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=()):
+def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=(), device="cuda"):
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops import gemm, moe as M, ref
     from fuselink_b200.parallel.symm import SymmetricHeap
     cfg = M.MoEConfig(hidden=H, ffn=Fd, num_experts=E, topk=k, tokens=T, fp8=fp8)
     ftol = 4.0 if fp8 else 1.0      # e4m3 operands: a few percent of relative error per GEMM
     heaps = SymmetricHeap.emulated(world, 64 << 20)
+    sync = torch.cuda.synchronize if device == "cuda" else (lambda: None)
     try:
-        layers = [MoELayer(cfg, heaps[r], r, world, device="cuda", seed=3, fused_sgd_lr=sgd, name="m", shadow_experts=list(shadow))
+        layers = [MoELayer(cfg, heaps[r], r, world, device=device, seed=3, fused_sgd_lr=sgd, name="m", shadow_experts=list(shadow))
                   for r in range(world)]
         epr = E // world
         for r in range(1, world):
@@ -24,9 +25,9 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
             wg_all.append(g_.float()); wu_all.append(u_.float()); w2_all.append(l.w2.data[:epr].float())
         wg, wu, w2 = (torch.cat(v).clone().requires_grad_(True) for v in (wg_all, wu_all, w2_all))
         for step in range(steps):
-            gen = torch.Generator(device="cuda").manual_seed(100 + step)
-            xs = [torch.randn(T, H, generator=gen, device="cuda").to(torch.bfloat16) for _ in range(world)]
-            douts = [torch.randn(T, H, generator=gen, device="cuda").to(torch.bfloat16) for _ in range(world)]
+            gen = torch.Generator(device=device).manual_seed(100 + step)
+            xs = [torch.randn(T, H, generator=gen, device=device).to(torch.bfloat16) for _ in range(world)]
+            douts = [torch.randn(T, H, generator=gen, device=device).to(torch.bfloat16) for _ in range(world)]
             with torch.no_grad():
                 routes = [layers[r].route(xs[r]) for r in range(world)]
             wss = [l.ws for l in layers]
@@ -36,7 +37,7 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
             for r in range(world):
                 M.moe_forward_experts(wss[r], layers[r].w13.data, layers[r].w2.data)
             outs = [M.moe_forward_combine(wss[r], routes[r][0].contiguous()) for r in range(world)]
-            torch.cuda.synchronize()
+            sync()
             for h in heaps:
                 h.check_status("forward")
             total = sum(int(w_.counts_now().sum()) for w_ in wss)
@@ -60,7 +61,7 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
                 for w_ in wss:
                     w_.reduce_shadow_grads = lambda ws_, gs, totals=totals: [g.copy_(t) for g, t in zip(gs, totals)]
             dxs = [M.moe_backward_finish(wss[r], True) for r in range(world)]
-            torch.cuda.synchronize()
+            sync()
             for h in heaps:
                 h.check_status("backward")
 

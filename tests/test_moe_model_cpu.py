@@ -1,0 +1,91 @@
+"""The Python side of the fused MoE path (ops/moe.py: buffers, slices, parities, phases, shadow experts) run on the CPU:
+the device entry points are replaced by the functional model of tests/cpu_kernel_model.py and the symmetric heap lives
+in host memory.  The scenario and its checks are the ones of the GPU test, against the same fp32 oracle."""
+import pytest
+import torch
+
+from fuselink_b200 import have_native
+
+pytestmark = pytest.mark.skipif(not have_native() or torch.cuda.is_available(), reason="CPU-only run of the kernel model")
+
+
+def _run_on_model(*args, **kw):
+    import cpu_kernel_model
+    from test_moe_gpu import _run
+    with cpu_kernel_model.installed():
+        _run(*args, device="cpu", T=64, H=128, Fd=256, **kw)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_moe_forward_backward_on_the_model(world):
+    _run_on_model(world)
+
+
+def test_two_steps_with_the_update_fused_into_wgrad():
+    _run_on_model(2, sgd=0.05, steps=2)
+
+
+@pytest.mark.parametrize("world,shadow", [(2, (0,)), (4, (0, 5)), (1, (2,)), (4, (7, 1, 2))])
+def test_shadow_experts_on_the_model(world, shadow):
+    """Rows of a shadowed expert stay on their rank; outputs, input gradients and the summed weight gradients equal the oracle's."""
+    _run_on_model(world, shadow=shadow)
+
+
+def test_shadow_experts_two_steps_fused_update_keeps_the_copies_identical():
+    _run_on_model(2, sgd=0.05, steps=2, shadow=(1,))
+
+
+def test_shadowed_rows_do_not_cross_ranks():
+    """With every expert shadowed nothing is sent: each rank's counters show exactly its own tokens."""
+    import cpu_kernel_model
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops import moe as M
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    E, W, T, k = 4, 2, 32, 2
+    cfg = M.MoEConfig(hidden=128, ffn=256, num_experts=E, topk=k, tokens=T)
+    heaps = SymmetricHeap.emulated(W, 32 << 20)
+    try:
+        with cpu_kernel_model.installed():
+            layers = [MoELayer(cfg, heaps[r], r, W, device="cpu", seed=2, name="s", shadow_experts=list(range(E))) for r in range(W)]
+            xs = [torch.randn(T, 128).to(torch.bfloat16) for _ in range(W)]
+            routes = [l.route(x) for l, x in zip(layers, xs)]
+            for r in range(W):
+                M.moe_forward_dispatch(layers[r].ws, xs[r], routes[r][1].contiguous())
+            for r in range(W):
+                c = layers[r].ws.counts_now()
+                assert int(c[:E // W].sum()) == 0 and int(c[E // W:].sum()) == T * k
+    finally:
+        for h in heaps:
+            h.close()
+
+
+def test_shadowing_the_hot_experts_levels_the_load():
+    """8 ranks, one expert each, Zipf(1.2) router bias: the busiest rank's row count (what sets the step time) falls from
+    about a third of all rows to well under twice the mean when the three hottest experts are shadowed."""
+    import cpu_kernel_model
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops import moe as M
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    E = W = 8
+    T, k = 256, 2
+    cfg = M.MoEConfig(hidden=128, ffn=256, num_experts=E, topk=k, tokens=T)
+    busiest = {}
+    for nshadow in (0, 3):
+        heaps = SymmetricHeap.emulated(W, 48 << 20)
+        try:
+            with cpu_kernel_model.installed():
+                layers = [MoELayer(cfg, heaps[r], r, W, device="cpu", seed=2, name="l", shadow_experts=nshadow) for r in range(W)]
+                for r in range(1, W):
+                    layers[r].router.data.copy_(layers[0].router.data)
+                g = torch.Generator().manual_seed(7)
+                for r in range(W):
+                    x = torch.randn(T, 128, generator=g).to(torch.bfloat16)
+                    M.moe_forward_dispatch(layers[r].ws, x, layers[r].route(x)[1].contiguous())
+                rows = [int(l.ws.counts_now().sum()) for l in layers]
+                assert sum(rows) == W * T * k
+                busiest[nshadow] = max(rows)
+        finally:
+            for h in heaps:
+                h.close()
+    mean = T * k
+    assert busiest[0] > 2.2 * mean and busiest[3] < 1.5 * mean, busiest
