@@ -1,5 +1,6 @@
 """A functional model, in plain PyTorch on host memory, of the device entry points the MoE path calls
-(`moe_dispatch`, `moe_zero_tail`, `grouped_gemm` with its five epilogues, `moe_combine`, `moe_combine_dw`, `barrier`).
+(`moe_dispatch`, `moe_zero_tail`, `grouped_gemm` with its five epilogues, `moe_combine`, `moe_combine_dw`, `barrier`, the
+fp8 quantisers and the block-scaled fp8 grouped GEMM).
 
 It takes the same arguments as the bindings of the real extension, raw addresses of peers' buffers included, and does to
 the memory behind them what the kernels are specified to do.  With it the Python side of `ops/moe.py` -- buffer sizes,
@@ -102,8 +103,9 @@ class Model:
 
     # ---------------------------------------------------------------------------------------- grouped GEMM
     def grouped_gemm(self, mode, G, cap, M, N, K, counts, A, a_mn, lda, gsa, B, b_mn, ldb, gsb, epilogue, out, ldc, gsc,
-                     gu, ldgu, dgu, row_info, peers, sgd_lr, zero_tail, group_m, max_ctas, status):
-        assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
+                     gu, ldgu, dgu, row_info, peers, sgd_lr, zero_tail, group_m, max_ctas, status, _fp32_operands=False):
+        assert _fp32_operands or (A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16)
+        assert A.is_contiguous() and B.is_contiguous()
         assert counts is None or (counts.dtype == torch.int32 and counts.numel() >= G)
         if mode == 1:                                               # K-grouped: C_g = A_g^T @ B_g over the group's rows
             assert epilogue == EPI_WGRAD and A.shape == (G * cap, M) and B.shape == (G * cap, N) and out.shape == (G, M, N)
@@ -150,13 +152,52 @@ class Model:
                 raise AssertionError("WGRAD needs the K-grouped mode")
 
 
+    # ---------------------------------------------------------------------------------------- fp8 arm
+    def fp8_quantize_rows(self, x, q, scale, counts, cap):
+        from fuselink_b200.ops import fp8 as f8
+        rows = x.shape[0]
+        live = torch.ones(rows, dtype=torch.bool)
+        if counts is not None:                                      # only the rows a group holds are quantised
+            live = (torch.arange(rows) % cap) < counts.long().repeat_interleave(cap)[:rows].clamp(max=cap)
+        qq, ss = f8.ref_quantize_rows(x[live])
+        q[live] = qq
+        scale[live] = ss
+
+    def fp8_quantize_blocks(self, w, q, scale):
+        from fuselink_b200.ops import fp8 as f8
+        G, R, Cc = w.shape
+        v = w.float().view(G, R // 128, 128, Cc // 128, 128)
+        amax = v.abs().amax((2, 4))
+        s = torch.where(amax > 0, amax / f8.FP8_MAX, torch.ones_like(amax))
+        q.copy_((v / s.view(G, R // 128, 1, Cc // 128, 1)).clamp(-f8.FP8_MAX, f8.FP8_MAX).to(f8.FP8).view(G, R, Cc))
+        scale.copy_(s)
+
+    def fp8_grouped_gemm(self, G, cap, N, K, counts, A, a_scale, B, b_mn, b_scale, epilogue, out, ldc, gu, ldgu, dgu, row_info,
+                         peers, zero_tail, group_m, max_ctas, status):
+        from fuselink_b200.ops import fp8 as f8
+        assert A.element_size() == 1 and B.element_size() == 1 and A.shape == (G * cap, K)
+        assert a_scale.shape == (G * cap, K // 128)
+        assert b_scale.shape == ((G, K // 128, N // 128) if b_mn else (G, N // 128, K // 128)), (b_scale.shape, b_mn, N, K)
+        rows = A.shape[0]
+        live = torch.ones(rows, dtype=torch.bool)
+        if counts is not None:
+            live = (torch.arange(rows) % cap) < counts.long().repeat_interleave(cap)[:rows].clamp(max=cap)
+        a = torch.zeros(rows, K)
+        a[live] = f8.dequantize_rows(A[live], a_scale[live])       # rows beyond a group's count hold stale bytes
+        b = f8.dequantize_blocks(B, b_scale)
+        # the same epilogues, on operands that carry exactly the information the e4m3 values and their scales hold
+        self.grouped_gemm(0, G, cap, 0, N, K, counts, a.to(torch.float32), False, K, cap * K, b, b_mn, 0, 0, epilogue, out, ldc, 0,
+                          gu, ldgu, dgu, row_info, peers, 0.0, zero_tail, group_m, max_ctas, status, _fp32_operands=True)
+
+
 @contextlib.contextmanager
 def installed():
     """Inside the block the MoE path's modules get the model instead of the extension."""
     from fuselink_b200 import _ext
     from fuselink_b200.ops import comm, gemm, moe
     model = Model(_ext.require_native())
-    saved = [(m, m.require_native) for m in (comm, gemm, moe)]
+    from fuselink_b200.ops import fp8
+    saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8)]
     for m, _ in saved:
         m.require_native = lambda model=model: model
     try:

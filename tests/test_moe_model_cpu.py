@@ -25,6 +25,17 @@ def test_two_steps_with_the_update_fused_into_wgrad():
     _run_on_model(2, sgd=0.05, steps=2)
 
 
+@pytest.mark.parametrize("world", [1, 2])
+def test_fp8_arm_on_the_model(world):
+    """Quantise -> fp8 GEMM -> quantise ... in forward and dgrad, wgrad in bf16: what is quantised when, with which scales,
+    and that the forward's quantised weights serve the transposed use in backward."""
+    _run_on_model(world, fp8=True)
+
+
+def test_fp8_arm_with_shadow_experts_on_the_model():
+    _run_on_model(2, fp8=True, shadow=(0,))
+
+
 @pytest.mark.parametrize("world,shadow", [(2, (0,)), (4, (0, 5)), (1, (2,)), (4, (7, 1, 2))])
 def test_shadow_experts_on_the_model(world, shadow):
     """Rows of a shadowed expert stay on their rank; outputs, input gradients and the summed weight gradients equal the oracle's."""
@@ -89,3 +100,36 @@ def test_shadowing_the_hot_experts_levels_the_load():
                 h.close()
     mean = T * k
     assert busiest[0] > 2.2 * mean and busiest[3] < 1.5 * mean, busiest
+
+
+def test_autograd_node_returns_gradients_for_experts_and_copies():
+    """MoEFunction end to end (one rank): with expert 2 shadowed its gradient arrives in the copy's slot and the idle slot of
+    the expert itself gets zeros; everything equals the plain-PyTorch path of the same layer."""
+    import cpu_kernel_model
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops import moe as M
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    E, T, k, H = 4, 48, 2, 128
+    cfg = M.MoEConfig(hidden=H, ffn=256, num_experts=E, topk=k, tokens=T)
+    heaps = SymmetricHeap.emulated(1, 32 << 20)
+    try:
+        with cpu_kernel_model.installed():
+            layer = MoELayer(cfg, heaps[0], 0, 1, device="cpu", seed=6, name="a", shadow_experts=[2])
+            x = torch.randn(T, H).to(torch.bfloat16)
+            xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+            w, idx = layer.route(xa)
+            out = M.MoEFunction.apply(xa, w, idx, layer.w13, layer.w2, layer.ws, 0.0)
+            out.float().pow(2).sum().backward()
+            got13, got2, gotx = layer.w13.grad.clone(), layer.w2.grad.clone(), xa.grad.clone()
+            layer.zero_grad(set_to_none=True)
+            wb, idxb = layer.route(xb)
+            layer._forward_reference(xb, wb, idxb).float().pow(2).sum().backward()
+            want13, want2 = layer.w13.grad, layer.w2.grad                      # plain path: gradients in the experts' own slots
+        close = lambda a, b: (a.float() - b.float()).abs().max().item() < 4e-2 * (b.float().abs().max().item() + 1e-6)
+        assert got13.shape[0] == E + 1 and close(gotx, xb.grad)
+        for e in (0, 1, 3):
+            assert close(got13[e], want13[e]) and close(got2[e], want2[e])
+        assert close(got13[E], want13[2]) and close(got2[E], want2[2])          # the copy carries expert 2's gradient
+        assert got13[2].abs().max() == 0 and got2[2].abs().max() == 0           # expert 2's own slot saw no rows
+    finally:
+        heaps[0].close()
