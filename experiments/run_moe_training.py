@@ -34,6 +34,7 @@ def main():
     ap.add_argument("--log-every", type=int, default=5)
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
+    ap.add_argument("--shadow", type=int, default=0, help="replicate the N most favoured experts of every layer on every rank (CUDA, several ranks)")
     ap.add_argument("--checkpoint", default="", help="save the last state here (per rank: experts differ)")
     ap.add_argument("--resume", default="", help="load <path>.rank<r> written by --checkpoint (same world size) before training")
     a = ap.parse_args()
@@ -43,6 +44,8 @@ def main():
     cfg = MOE_ZOO[a.model]
     if a.layers:
         cfg = dataclasses.replace(cfg, layers=a.layers)
+    if a.shadow:
+        cfg = dataclasses.replace(cfg, shadow_experts=a.shadow)
     heap = None
     if cpu:
         dev = torch.device("cpu")
@@ -55,7 +58,7 @@ def main():
             dist.init_process_group("nccl", device_id=dev)
         from fuselink_b200.parallel.symm import SymmetricHeap
         T, k, H, F, E = a.batch * a.seq, cfg.topk, cfg.hidden, cfg.ffn, cfg.num_experts
-        rows = (E // world) * ((T * world + 127) // 128 * 128)
+        rows = (E // world + (a.shadow if world > 1 else 0)) * ((T * world + 127) // 128 * 128)
         per_layer = rows * H * 2 * 2 + 2 * T * k * H * 2 + rows * 4 + (1 << 20)        # the symmetric buffers of one MoE workspace
         heap = SymmetricHeap.create(cfg.layers * per_layer + (64 << 20), device=local)
     net = MoETransformer(cfg, a.batch * a.seq, heap, rank, world, device=dev, seed=0, fused_sgd_lr=0.0 if cpu else a.lr)

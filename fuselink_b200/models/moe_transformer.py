@@ -40,6 +40,7 @@ class MoEModelConfig:
     aux_loss_coef: float = 0.01
     capacity_factor: float = 0.0          # > 0 with drop_tokens: choices over an expert's capacity contribute nothing
     drop_tokens: bool = False
+    shadow_experts: int = 0               # copies of the n experts the router favours most on every rank (CUDA path)
 
 
 MOE_ZOO = {
@@ -94,7 +95,8 @@ class MoETransformer(nn.Module):
         blocks = []
         for l in range(cfg.layers):
             moe = MoELayer(mcfg, heap, rank, world, device=device, zipf_s=None, seed=seed * 100 + l, fused_sgd_lr=fused_sgd_lr,
-                           name=f"moe{l}", capacity_factor=cfg.capacity_factor, drop_tokens=cfg.drop_tokens)
+                           name=f"moe{l}", capacity_factor=cfg.capacity_factor, drop_tokens=cfg.drop_tokens,
+                           shadow_experts=cfg.shadow_experts if world > 1 else 0)
             blocks.append(_Block(cfg, moe, device, gen, dtype))
         self.blocks = nn.ModuleList(blocks)
 
