@@ -10,7 +10,6 @@ import argparse
 import json
 import os
 import subprocess
-import sys
 import tempfile
 import uuid
 

@@ -10,10 +10,6 @@ from .._ext import require_native
 EPI_STORE, EPI_SWIGLU, EPI_SCATTER, EPI_DSWIGLU, EPI_WGRAD = 0, 1, 2, 3, 4
 
 
-def _status_tensor(status):
-    return status
-
-
 def grouped_gemm_rows(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.Tensor], cap: int, *,
                       b_mn_major: bool = False, epilogue: int = EPI_STORE, out: Optional[torch.Tensor] = None,
                       gu: Optional[torch.Tensor] = None, dgu: Optional[torch.Tensor] = None,

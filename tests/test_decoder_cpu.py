@@ -3,7 +3,6 @@
     load direction), which pins the architecture details: norm type, position scheme, activation, biases, tied head;
   * paged prefill + decode steps reproduce the dense forward (greedy tokens), per family;
   * two tensor-parallel shards cut from one checkpoint reproduce the unsharded model (gloo ranks)."""
-import dataclasses
 import os
 import socket
 import tempfile

@@ -135,7 +135,7 @@ def test_gating_capacity_mask_matches_a_sequential_admission():
 
 
 def test_moe_layer_gating_options_on_cpu():
-    from fuselink_b200.models.moe import MoELayer, load_balancing_loss
+    from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops.moe import MoEConfig
     cfg = MoEConfig(hidden=64, ffn=128, num_experts=4, topk=2, tokens=64)
     x = torch.randn(cfg.tokens, cfg.hidden, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16)

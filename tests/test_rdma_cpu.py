@@ -1,7 +1,6 @@
 """The RDMA transport of the plugin (receiver-written descriptor FIFO, RDMA write + write-with-immediate, striping
 over devices and queue pairs) driven through the ncclNet entry points by two processes, on the software NIC that
 stands in for libibverbs devices.  Same harness and the same bitwise checks as the TCP transport."""
-import ctypes
 import os
 
 import pytest
