@@ -29,6 +29,9 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on the same shape")
+    ap.add_argument("--group-m", type=int, default=16, help="row tiles that share a column of weight tiles in the tile order (L2 reuse)")
+    ap.add_argument("--max-ctas", type=int, default=0, help="cap on the persistent grid (0: one CTA, or CTA pair, per SM)")
+    ap.add_argument("--sweep", action="store_true", help="time the case for group-m 4/8/16/32 x both kernel variants, one JSON line each")
     args = ap.parse_args()
     from fuselink_b200.ops import gemm
     from fuselink_b200.utils import roofline
@@ -43,42 +46,55 @@ def main():
         return (torch.randn(*shape, device=dev) * s).to(bf)
 
     info = torch.arange(G * cap, dtype=torch.int32, device=dev)
+    sched = {"group_m": args.group_m, "max_ctas": args.max_ctas}           # read by the lambdas at call time
     if args.case == "fwd1":
         a, b = rnd(G * cap, H), rnd(G, 2 * F, H, s=0.02)
         out, gu = torch.empty(G * cap, F, dtype=bf, device=dev), torch.empty(G * cap, 2 * F, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, epilogue=gemm.EPI_SWIGLU, out=out, gu=gu, zero_tail=True, status=st)
+        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, epilogue=gemm.EPI_SWIGLU, out=out, gu=gu, zero_tail=True, status=st, **sched)
         M, N, K = G * cap, 2 * F, H
     elif args.case == "fwd2":
         a, b = rnd(G * cap, F), rnd(G, H, F, s=0.02)
         dst = torch.empty(G * cap, H, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, epilogue=gemm.EPI_SCATTER, row_info=info, peers=[dst.data_ptr()], ldc=H, status=st)
+        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, epilogue=gemm.EPI_SCATTER, row_info=info, peers=[dst.data_ptr()], ldc=H, status=st, **sched)
         M, N, K = G * cap, H, F
     elif args.case == "dact":
         a, b = rnd(G * cap, H), rnd(G, H, F, s=0.02)
         gu, dgu = rnd(G * cap, 2 * F), torch.empty(G * cap, 2 * F, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=gu, dgu=dgu, zero_tail=True, status=st)
+        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=gu, dgu=dgu, zero_tail=True, status=st, **sched)
         M, N, K = G * cap, F, H
     elif args.case == "dx":
         a, b = rnd(G * cap, 2 * F), rnd(G, 2 * F, H, s=0.02)
         dst = torch.empty(G * cap, H, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER, row_info=info, peers=[dst.data_ptr()], ldc=H, status=st)
+        fn = lambda: gemm.grouped_gemm_rows(a, b, counts, cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER, row_info=info, peers=[dst.data_ptr()], ldc=H, status=st, **sched)
         M, N, K = G * cap, H, 2 * F
     elif args.case == "wgrad2":
         a, b = rnd(G * cap, H), rnd(G * cap, F)
         out = torch.empty(G, H, F, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, status=st)
+        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, status=st, **sched)
         M, N, K = H * G, F, cap
     elif args.case == "wgrad13":
         a, b = rnd(G * cap, 2 * F), rnd(G * cap, H)
         out = torch.empty(G, 2 * F, H, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, status=st)
+        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, status=st, **sched)
         M, N, K = 2 * F * G, H, cap
     else:
         raise SystemExit("unknown case")
+    flops = 2.0 * M * N * K
+    if args.sweep:
+        from fuselink_b200._ext import require_native
+        C = require_native()
+        for pair in (0, 1):
+            C.gemm_set_variant(pair)
+            for gm in (4, 8, 16, 32):
+                sched["group_m"] = gm
+                ms = time_kernel(fn, warmup=args.warmup, iters=args.iters)
+                assert st[0].item() == 0, st.tolist()
+                print(json.dumps({"case": args.case, "M": M, "N": N, "K": K, "pair": pair, "group_m": gm, "ms": ms, "tflops": flops / ms / 1e9,
+                                  "frac_of_measured_cublas_burst": roofline.gemm_fraction(flops, ms)}))
+        return
     ms = time_kernel(fn, warmup=args.warmup, iters=args.iters)
     assert st[0].item() == 0, st.tolist()
-    flops = 2.0 * M * N * K
-    row = {"case": args.case, "M": M, "N": N, "K": K, "ms": ms, "tflops": flops / ms / 1e9,
+    row = {"case": args.case, "M": M, "N": N, "K": K, "ms": ms, "tflops": flops / ms / 1e9, "group_m": args.group_m,
            "frac_of_measured_cublas_burst": roofline.gemm_fraction(flops, ms), "peaks": roofline.peaks().source}
     if args.cublas:
         x, w = rnd(M, K), rnd(N, K)
