@@ -6,6 +6,7 @@
 #   NGPU=1 bench/reproduce.sh            # kernels + flagship step on one GPU
 #   NGPU=8 bench/reproduce.sh            # adds p2p / all-to-all sweeps, DLRM, serving and the NCCL arms
 #   SECTIONS="moe dlrm" NGPU=8 bench/reproduce.sh
+#   SECTIONS="moe-shadow gemm-sweep" NGPU=8 bench/reproduce.sh     # optional sections
 set -uo pipefail
 cd "$(dirname "$0")/.."
 NGPU=${NGPU:-1}; OUT=${OUT:-bench_results.jsonl}; STEPS=${STEPS:-20}; WARMUP=${WARMUP:-5}
@@ -25,6 +26,10 @@ for s in $SECTIONS; do
       for v in 0 1; do FUSELINK_GEMM_PAIR=$v run "gemm pair=$v" python bench/gemm_case.py --case fwd1 --rows 8192 --iters 10; done ;;
     moe)
       for impl in fuselink nccl; do run "moe $impl" launch bench.py --impl "$impl" --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP"; done ;;
+    moe-shadow)   # not in the default list: the hottest experts replicated on every rank
+      if [ "$NGPU" -ge 2 ]; then for n in 1 2 3; do run "moe shadow=$n" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n"; done; fi ;;
+    gemm-sweep)   # not in the default list: tile order x kernel variant for every GEMM of the step
+      for c in fwd1 fwd2 dact dx wgrad2 wgrad13; do run "gemm sweep $c" python bench/gemm_case.py --case "$c" --rows 16384 --iters 5 --sweep; done ;;
     p2p)
       if [ "$NGPU" -ge 2 ]; then run "p2p" tr bench/p2p_sweep.py --pairs 1; fi
       if [ "$NGPU" -ge 4 ]; then run "p2p 2 pairs" tr bench/p2p_sweep.py --pairs 2; run "p2p relays" tr bench/p2p_sweep.py --pairs 1 --relays 2; fi ;;
