@@ -111,6 +111,7 @@ class MoELayer(nn.Module):
         else:
             w, idx = torch.topk(probs, self.cfg.topk, dim=-1)
         w = w / w.sum(dim=-1, keepdim=True)
+        self.last_topk_idx = idx.detach()       # what reshadow() looks at
         self.l_aux = load_balancing_loss(probs, idx, self.cfg.num_experts)
         if self.drop_tokens and self.capacity_factor > 0:
             cap = expert_capacity(x.shape[0], self.cfg.num_experts, self.cfg.topk, self.capacity_factor, self.min_capacity)
@@ -127,6 +128,48 @@ class MoELayer(nn.Module):
             if e // self.epr == self.rank:
                 self.w13[e % self.epr].copy_(self.w13[self.epr + j])
                 self.w2[e % self.epr].copy_(self.w2[self.epr + j])
+
+    @torch.no_grad()
+    def set_shadows(self, experts, group=None) -> None:
+        """Put other experts into the copy slots (the same number of them), between steps: the owners first take back the
+        copies they own (they hold the trained weights), then every new shadow's weights go from its owner to the slot on
+        every rank.  Collective over the ranks of the layer."""
+        experts = tuple(int(e) for e in experts)
+        assert len(experts) == len(self.cfg.shadow) and len(set(experts)) == len(experts)
+        if experts == tuple(self.cfg.shadow):
+            return
+        self.sync_shadow_to_real()
+        for j, e in enumerate(experts):
+            owner = e // self.epr
+            for w in (self.w13, self.w2):
+                slot = w[self.epr + j]
+                if owner == self.rank:
+                    slot.copy_(w[e % self.epr])
+                if self.world > 1:
+                    import torch.distributed as dist
+                    dist.broadcast(slot, src=owner if group is None else dist.get_global_rank(group, owner), group=group)
+        self.cfg = dataclasses.replace(self.cfg, shadow=experts)
+        if self.ws is not None:
+            self.ws.set_shadow(experts)
+
+    @torch.no_grad()
+    def reshadow(self, topk_idx: Optional[torch.Tensor] = None, group=None) -> tuple:
+        """Choose the shadows from the routing of a batch (``topk_idx`` of this rank, by default the last one routed; the
+        loads are summed over the ranks) and install them.  Returns the experts now shadowed.  An optimizer that keeps
+        per-parameter state (momentum, Adam moments) keeps the state of a slot, not of the expert that moves into it."""
+        from ..ops.moe import choose_shadows
+        n = len(self.cfg.shadow)
+        if topk_idx is None:
+            topk_idx = getattr(self, "last_topk_idx", None)
+        if n == 0 or topk_idx is None:
+            return tuple(self.cfg.shadow)
+        load = torch.bincount(topk_idx.reshape(-1).long().clamp(0, self.cfg.num_experts - 1), minlength=self.cfg.num_experts).double()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(load, group=group)
+        chosen = choose_shadows(load, n)
+        self.set_shadows(chosen, group)
+        return chosen
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, idx = self.route(x)

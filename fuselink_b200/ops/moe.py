@@ -13,6 +13,7 @@ There is no stand-alone all-to-all and no framework permute in either direction;
 """
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
@@ -111,6 +112,19 @@ class MoEWorkspace:
 
     def counts_now(self) -> torch.Tensor:
         return self.counts.local[self.step_parity]
+
+    def set_shadow(self, shadow: Sequence[int]) -> None:
+        """Other experts in the copy slots (as many as before: the buffers keep their size).  Between steps only."""
+        assert len(shadow) == self.nshadow and self.pending_shadow is None
+        self.cfg = dataclasses.replace(self.cfg, shadow=tuple(int(e) for e in shadow))
+        if self.nshadow:
+            self.slots_of = slot_table(self.cfg.num_experts, self.heap.world, self.cfg.shadow, self.heap.rank).to(self.slots_of.device)
+
+
+def choose_shadows(expert_load: torch.Tensor, n: int) -> Tuple[int, ...]:
+    """The n experts with the most routed rows (ties: the lower id), from the load summed over all ranks."""
+    order = torch.argsort(expert_load.double().cpu(), descending=True, stable=True)
+    return tuple(int(e) for e in order[:n])
 
 
 def _allreduce_shadow_grads(ws: MoEWorkspace, grads) -> None:

@@ -133,3 +133,54 @@ def test_autograd_node_returns_gradients_for_experts_and_copies():
         assert got13[2].abs().max() == 0 and got2[2].abs().max() == 0           # expert 2's own slot saw no rows
     finally:
         heaps[0].close()
+
+
+def test_changing_the_shadowed_expert_between_steps():
+    """Step with expert 0 shadowed, then with expert 5 instead (same slot, other table, weights moved): the forward result
+    equals the oracle both times and the rows of the shadowed expert are the ones that stay local."""
+    import dataclasses
+    import cpu_kernel_model
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops import gemm, moe as M, ref
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    E, W, T, k, H = 8, 2, 48, 2, 128
+    epr = E // W
+    cfg = M.MoEConfig(hidden=H, ffn=256, num_experts=E, topk=k, tokens=T)
+    heaps = SymmetricHeap.emulated(W, 48 << 20)
+    try:
+        with cpu_kernel_model.installed():
+            layers = [MoELayer(cfg, heaps[r], r, W, device="cpu", zipf_s=None, seed=8, name="c", shadow_experts=[0]) for r in range(W)]
+            for r in range(1, W):
+                layers[r].router.data.copy_(layers[0].router.data)
+            wg, wu = gemm.deinterleave_gate_up(torch.cat([l.w13.data[:epr] for l in layers]).float())
+            w2 = torch.cat([l.w2.data[:epr] for l in layers]).float()
+            for shadowed in (0, 5):
+                if shadowed != layers[0].cfg.shadow[0]:
+                    # what set_shadows does over a process group, done by hand for the ranks emulated in this process
+                    for l in layers:
+                        l.sync_shadow_to_real()
+                    owner = layers[shadowed // epr]
+                    for l in layers:
+                        l.w13.data[epr].copy_(owner.w13.data[shadowed % epr])
+                        l.w2.data[epr].copy_(owner.w2.data[shadowed % epr])
+                        l.cfg = dataclasses.replace(l.cfg, shadow=(shadowed,))
+                        l.ws.set_shadow((shadowed,))
+                xs = [torch.randn(T, H).to(torch.bfloat16) for _ in range(W)]
+                routes = [layers[r].route(xs[r]) for r in range(W)]
+                for r in range(W):
+                    M.moe_forward_dispatch(layers[r].ws, xs[r], routes[r][1].contiguous())
+                for r in range(W):
+                    local_rows = int((routes[r][1] == shadowed).sum())
+                    assert int(layers[r].ws.counts_now()[epr]) == local_rows              # the copy slot holds this rank's own rows only
+                    assert int(layers[r].ws.counts_now()[shadowed % epr]) == 0 or shadowed // epr != r
+                for r in range(W):
+                    M.moe_forward_experts(layers[r].ws, layers[r].w13.data, layers[r].w2.data)
+                for r in range(W):
+                    out = M.moe_forward_combine(layers[r].ws, routes[r][0].contiguous())
+                    want = ref.moe_forward(xs[r].float(), routes[r][1], routes[r][0].float(), wg, wu, w2)
+                    assert (out.float() - want).abs().max() < 3e-2 * (want.abs().max() + 1e-3)
+                for h in heaps:
+                    h.check_status("step")
+    finally:
+        for h in heaps:
+            h.close()

@@ -94,3 +94,39 @@ def test_sync_shadow_to_real_refreshes_the_owners_slot():
     before = l.w13[1].clone()
     l.sync_shadow_to_real()
     assert torch.equal(l.w13[0], l.w13[2]) and torch.equal(l.w2[0], l.w2[2]) and torch.equal(l.w13[1], before)
+
+
+def _reshadow_worker(rank, world, port, out_dir):
+    import os
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = MoEConfig(hidden=128, ffn=256, num_experts=4, topk=2, tokens=8)
+    l = MoELayer(cfg, None, rank, world, device="cpu", seed=3, shadow_experts=[0])        # expert 0 lives on rank 0
+    with torch.no_grad():
+        l.w2[2].add_(0.5)                       # every rank trained its copy of expert 0 (identically, as the all-reduce ensures)
+        if rank == 1:
+            l.w2[0].mul_(2.0)                   # rank 1 trained its own expert 2
+    # this batch's routing: expert 2 (owned by rank 1) is now the busiest one over both ranks
+    idx = torch.tensor([[2, 3], [2, 1]]) if rank == 0 else torch.tensor([[2, 0], [2, 3]])
+    chosen = l.reshadow(idx)
+    torch.save({"chosen": chosen, "w2": l.w2.data.clone(), "shadow": l.cfg.shadow}, os.path.join(out_dir, f"r{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_reshadow_moves_the_weights_between_owners_and_copies(tmp_path):
+    import os
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mp.spawn(_reshadow_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(2))
+    assert r0["chosen"] == r1["chosen"] == (2,) and r0["shadow"] == (2,)
+    cfg = MoEConfig(hidden=128, ffn=256, num_experts=4, topk=2, tokens=8)
+    fresh = [MoELayer(cfg, None, r, 2, device="cpu", seed=3) for r in range(2)]
+    # expert 0's owner took the trained copy back into the expert's own slot
+    assert torch.allclose(r0["w2"][0].float(), fresh[0].w2.data[0].float() + 0.5, atol=1e-2)
+    # both copy slots now hold expert 2 as its owner (rank 1) had it
+    want = fresh[1].w2.data[0].float() * 2.0
+    assert torch.allclose(r0["w2"][2].float(), want, atol=1e-2) and torch.equal(r0["w2"][2], r1["w2"][2])
