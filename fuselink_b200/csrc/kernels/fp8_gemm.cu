@@ -96,6 +96,32 @@ __device__ __forceinline__ void store32_bf16(__nv_bfloat16* dst, const float* v)
     st_v4(dst + 8 * i, o);
   }
 }
+// 16-column variants: the epilogues that need the saved gate/up beside the 128 accumulators of a thread work on 16
+// columns at a time, which keeps their temporaries (and with them the register spills) small
+__device__ __forceinline__ void store16_bf16(__nv_bfloat16* dst, const float* v) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 o;
+    o.x = pack_bf16(v[8 * i + 0], v[8 * i + 1]);
+    o.y = pack_bf16(v[8 * i + 2], v[8 * i + 3]);
+    o.z = pack_bf16(v[8 * i + 4], v[8 * i + 5]);
+    o.w = pack_bf16(v[8 * i + 6], v[8 * i + 7]);
+    st_v4(dst + 8 * i, o);
+  }
+}
+__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* src, float* v) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 o = ld_v4(src + 8 * i);
+    const uint32_t w[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+      v[8 * i + 2 * j] = __bfloat162float(h.x);
+      v[8 * i + 2 * j + 1] = __bfloat162float(h.y);
+    }
+  }
+}
 __device__ __forceinline__ void load32_bf16(const __nv_bfloat16* src, float* v) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -367,45 +393,45 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           __nv_bfloat16* act = p.C + grow * p.ldc + t.n0 / 2 + 64 * half;
           __nv_bfloat16* gu = p.gu ? p.gu + grow * p.ldgu + t.n0 + 64 * half : nullptr;
 #pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            float g[32], u[32], a[32];
+          for (int c = 0; c < 4; ++c) {                        // 16 columns at a time: gate in acc[0, 64), up in acc[64, 128)
+            float g[16], u[16], a[16];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              g[i] = valid ? acc[c * 32 + i] : 0.f;
-              u[i] = valid ? acc[(c + 2) * 32 + i] : 0.f;
+            for (int i = 0; i < 16; ++i) {
+              g[i] = valid ? acc[c * 16 + i] : 0.f;
+              u[i] = valid ? acc[64 + c * 16 + i] : 0.f;
               a[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
             }
-            store32_bf16(act + 32 * c, a);
+            store16_bf16(act + 16 * c, a);
             if (gu) {
-              store32_bf16(gu + 32 * c, g);
-              store32_bf16(gu + 128 + 32 * c, u);
+              store16_bf16(gu + 16 * c, g);
+              store16_bf16(gu + 128 + 16 * c, u);
             }
           }
         }
       } else {  // FL_EPI_DSWIGLU: acc = dAct over 256 activation columns
         if (valid || zero_row) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int a_col = t.n0 + chunk_col(half, c);
+          for (int c = 0; c < 8; ++c) {                        // 16 columns at a time: acc[16 c, 16 c + 16)
+            const int a_col = t.n0 + chunk_col(half, c >> 1) + 16 * (c & 1);
             const long long gcol = (long long)(a_col >> 7) * 256 + (a_col & 127);
-            float dg[32], du[32];
+            float dg[16], du[16];
             if (valid) {
-              float g[32], u[32];
-              load32_bf16(p.gu + grow * p.ldgu + gcol, g);
-              load32_bf16(p.gu + grow * p.ldgu + gcol + 128, u);
+              float g[16], u[16];
+              load16_bf16(p.gu + grow * p.ldgu + gcol, g);
+              load16_bf16(p.gu + grow * p.ldgu + gcol + 128, u);
 #pragma unroll
-              for (int i = 0; i < 32; ++i) {
-                const float da = acc[c * 32 + i];
+              for (int i = 0; i < 16; ++i) {
+                const float da = acc[c * 16 + i];
                 const float sg = 1.f / (1.f + __expf(-g[i]));
                 dg[i] = da * u[i] * (sg * (1.f + g[i] * (1.f - sg)));
                 du[i] = da * g[i] * sg;
               }
             } else {
 #pragma unroll
-              for (int i = 0; i < 32; ++i) dg[i] = du[i] = 0.f;
+              for (int i = 0; i < 16; ++i) dg[i] = du[i] = 0.f;
             }
-            store32_bf16(p.dgu + grow * p.ldgu + gcol, dg);
-            store32_bf16(p.dgu + grow * p.ldgu + gcol + 128, du);
+            store16_bf16(p.dgu + grow * p.ldgu + gcol, dg);
+            store16_bf16(p.dgu + grow * p.ldgu + gcol + 128, du);
           }
         }
       }
