@@ -127,11 +127,12 @@ def choose_shadows(expert_load: torch.Tensor, n: int) -> Tuple[int, ...]:
     return tuple(int(e) for e in order[:n])
 
 
-def _allreduce_shadow_grads(ws: MoEWorkspace, grads) -> None:
+def _allreduce_shadow_grads(ws: MoEWorkspace, grads):
+    """Starts the sums; the returned handles are waited for once the rest of the backward pass has been enqueued."""
     if ws.heap.world > 1:
         import torch.distributed as dist
-        for g in grads:
-            dist.all_reduce(g)
+        return [dist.all_reduce(g, async_op=True) for g in grads]
+    return []
 
 
 def _dispatch(ws: MoEWorkspace, x: torch.Tensor, idx: torch.Tensor, scale: Optional[torch.Tensor], dst, reuse: bool):
@@ -273,14 +274,24 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     return dw13, dw2
 
 
-def finish_shadow_grads(ws: MoEWorkspace) -> None:
-    """Sum the shadow experts' weight gradients over the ranks, then SGD on the copies (the same update on every rank, so
-    they stay equal) or, without the fused update, the trailing slots of the gradients moe_backward_experts returned."""
+def start_shadow_reduction(ws: MoEWorkspace):
+    """Start summing the shadow experts' weight gradients over the ranks; returns what finish_shadow_grads needs."""
     if ws.pending_shadow is None:
+        return None
+    pending, ws.pending_shadow = ws.pending_shadow, None
+    works = ws.reduce_shadow_grads(ws, pending[0]) or []
+    return pending, works
+
+
+def finish_shadow_grads(ws: MoEWorkspace, started) -> None:
+    """With the sums complete: SGD on the copies (the same update on every rank, so they stay equal) or, without the fused
+    update, the trailing slots of the gradients moe_backward_experts returned."""
+    if started is None:
         return
-    (g13, g2), w13, w2, dw13, dw2, sgd_lr = ws.pending_shadow
-    ws.pending_shadow = None
-    ws.reduce_shadow_grads(ws, (g13, g2))
+    ((g13, g2), w13, w2, dw13, dw2, sgd_lr), works = started
+    for w in works:
+        if hasattr(w, "wait"):
+            w.wait()
     R = ws.epr_real
     if sgd_lr:
         w13[R:].add_(g13, alpha=-sgd_lr)
@@ -294,14 +305,15 @@ def moe_backward_finish(ws: MoEWorkspace, need_dx: bool = True) -> Optional[torc
     """Phase 3: wait for the returned input-gradient rows and sum them over k."""
     C = require_native()
     cfg = ws.cfg
-    finish_shadow_grads(ws)
+    started = start_shadow_reduction(ws)          # runs beside the wait for the peers and the sum over k
     barrier(ws.heap, ws.name + ":bx", signal=False, wait=True)
     ws.launches += 1
-    if not need_dx:
-        return None
-    dx = torch.empty(cfg.tokens, cfg.hidden, dtype=torch.bfloat16, device=ws.dxs.local.device)
-    C.moe_combine(ws.dxs.local, None, dx, cfg.topk)
-    ws.launches += 1
+    dx = None
+    if need_dx:
+        dx = torch.empty(cfg.tokens, cfg.hidden, dtype=torch.bfloat16, device=ws.dxs.local.device)
+        C.moe_combine(ws.dxs.local, None, dx, cfg.topk)
+        ws.launches += 1
+    finish_shadow_grads(ws, started)
     return dx
 
 
