@@ -73,3 +73,16 @@ def test_command_line_has_the_reference_flags():
         assert flag in out.stdout, flag
     bad = subprocess.run([sys.executable, "-m", "fuselink_b200.serving", "--model_name", "no_such_model"], capture_output=True, text=True, timeout=120)
     assert bad.returncode != 0 and "unknown model" in bad.stderr
+
+
+def test_model_benchmark_script_runs_prefill_and_decode_on_one_group():
+    """experiments/run_model_benchmark.sh (the reference's benchmark_tp2 / benchmark_tp4 jobs): tensor parallelism 2 over gloo."""
+    import json
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, DEVICE="cpu", MODEL="tiny_opt", INPUT_LEN="64", TP="2", DECODE_STEPS="3", BATCH="2", PORT="29673")
+    out = subprocess.run([os.path.join(root, "experiments", "run_model_benchmark.sh")], env=env, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-3000:]
+    row = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
+    assert row["tp"] == 2 and row["decode_steps"] == 3 and row["prefill_ms"] > 0 and row["decode_ms_per_token"] > 0
