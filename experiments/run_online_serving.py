@@ -16,7 +16,6 @@ import argparse
 import json
 import os
 import queue
-import random
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
@@ -41,11 +40,8 @@ def main():
     if args.trace:
         reqs = parse_trace(open(args.trace))
     else:
-        rng, t, lines = random.Random(0), 0.0, []
-        for _ in range(args.requests):
-            t += rng.expovariate(args.rate)
-            prompt = rng.randint(32, args.input_len)
-            lines.append(f"ts: {t:.4f} prompt: {prompt} shared: {rng.randint(0, prompt // 4)} out: {rng.randint(4, 64)}")
+        from fuselink_b200.serving.tracegen import generate
+        lines = generate(args.requests, args.rate, 32, args.input_len, 0.25, 4, 64, seed=0)
         reqs = parse_trace(lines)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:

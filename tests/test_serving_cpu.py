@@ -86,3 +86,16 @@ def test_model_benchmark_script_runs_prefill_and_decode_on_one_group():
     assert out.returncode == 0, out.stderr[-3000:]
     row = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])
     assert row["tp"] == 2 and row["decode_steps"] == 3 and row["prefill_ms"] > 0 and row["decode_ms_per_token"] > 0
+
+
+def test_trace_generator_writes_what_the_reader_parses():
+    from fuselink_b200.serving.online import parse_trace
+    from fuselink_b200.serving.tracegen import generate
+    lines = generate(requests=200, rate=50.0, prompt_min=16, prompt_max=512, shared_fraction=0.5, out_min=2, out_max=9, seed=4)
+    assert lines == generate(requests=200, rate=50.0, prompt_min=16, prompt_max=512, shared_fraction=0.5, out_min=2, out_max=9, seed=4)
+    reqs = parse_trace(lines)
+    assert len(reqs) == 200
+    ts = [r.timestamp for r in reqs]
+    assert ts == sorted(ts) and 2.0 < ts[-1] < 8.0                       # 200 arrivals at 50 per second: about 4 s
+    assert all(16 <= r.prompt_len <= 512 and 2 <= r.output_len <= 9 for r in reqs)
+    assert all(r.prompt_len - r.prompt_len // 2 <= r.active_prompt_len <= r.prompt_len for r in reqs)
