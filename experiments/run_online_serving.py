@@ -30,11 +30,13 @@ def main():
     ap.add_argument("--input-len", type=int, default=512)
     ap.add_argument("--decode-steps", type=int, default=8)
     ap.add_argument("--decode-sleep-ms", type=float, default=0.0, help="stand-in for decoding, 25 in the reference")
+    ap.add_argument("--policy", default="fcfs", choices=["fcfs", "sjf", "aged"], help="order in which waiting requests are batched (fcfs: the reference)")
+    ap.add_argument("--max-batch-tokens", type=int, default=0, help="limit on the active prompt tokens of one batch (0: none)")
     args = ap.parse_args()
     from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard
     from fuselink_b200.parallel.symm import SymmetricHeap
     from fuselink_b200.serving.disagg import KVLink, ServeParams
-    from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader, next_batch, parse_trace
+    from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader, parse_trace
     cfg = MODEL_ZOO[args.model]
     p = ServeParams(cfg, MAX_BATCH, args.input_len, args.decode_steps)
     if args.trace:
@@ -53,9 +55,11 @@ def main():
     pre, dec = OnlinePrefill(p, net, links[0], 1), OnlineDecode(p, net, links[1], 0, sleep_ms=args.decode_sleep_ms)
     q = queue.Queue()
     TraceReader(reqs, q).start()
+    from fuselink_b200.serving.scheduler import Scheduler
+    sched = Scheduler(q, MAX_BATCH, p.input_len, policy=args.policy, max_batch_tokens=args.max_batch_tokens)
     finished, served = False, 0
     while not finished:
-        batch, finished = next_batch(q, MAX_BATCH, p.input_len)
+        batch, finished = sched.next_batch()
         if not batch:
             continue
         st = pre.serve_batch(batch)
@@ -76,7 +80,7 @@ def multi_process(args, cfg, p, reqs):
     from fuselink_b200.models.llama import LlamaShard
     from fuselink_b200.parallel.symm import SymmetricHeap
     from fuselink_b200.serving.disagg import KVLink, ServeParams
-    from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader, next_batch
+    from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader
     rank, local, world = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ["WORLD_SIZE"])
     assert world % 2 == 0, "half of the ranks prefill, half decode"
     torch.cuda.set_device(local)
@@ -98,11 +102,13 @@ def multi_process(args, cfg, p, reqs):
         q = queue.Queue()
         if rank == 0:
             TraceReader(reqs, q).start()
+        from fuselink_b200.serving.scheduler import Scheduler
+        sched = Scheduler(q, MAX_BATCH, p.input_len, policy=args.policy, max_batch_tokens=args.max_batch_tokens)
         finished = False
         while not finished:
             box = [None]
             if rank == 0:
-                batch, finished = next_batch(q, MAX_BATCH, p.input_len)
+                batch, finished = sched.next_batch()
                 box[0] = (batch, finished)
             if tp > 1:
                 dist.broadcast_object_list(box, src=0, group=group)

@@ -99,3 +99,46 @@ def test_trace_generator_writes_what_the_reader_parses():
     assert ts == sorted(ts) and 2.0 < ts[-1] < 8.0                       # 200 arrivals at 50 per second: about 4 s
     assert all(16 <= r.prompt_len <= 512 and 2 <= r.output_len <= 9 for r in reqs)
     assert all(r.prompt_len - r.prompt_len // 2 <= r.active_prompt_len <= r.prompt_len for r in reqs)
+
+
+def _sched(policy, reqs, **kw):
+    import queue
+    from fuselink_b200.serving.online import Request
+    from fuselink_b200.serving.scheduler import Scheduler
+    q = queue.Queue()
+    for i, (tokens, arrival) in enumerate(reqs):
+        q.put(Request(timestamp=float(i), prompt_len=tokens, active_prompt_len=tokens, output_len=4, arrival=arrival))
+    q.put(None)
+    warnings = []
+    s = Scheduler(q, policy=policy, warn=warnings.append, clock=lambda: 100.0, **kw)
+    batches = []
+    while True:
+        b, done = s.next_batch()
+        if b:
+            batches.append([r.active_prompt_len for r in b])
+        if done:
+            return batches, warnings, s
+
+
+def test_scheduler_policies_and_limits():
+    reqs = [(900, 99.0), (50, 99.1), (400, 99.2), (60, 99.3), (5000, 99.4), (70, 99.5)]
+    # the reference's behaviour: arrival order, up to the batch limit; the oversized request is dropped, not retried forever
+    b, w, s = _sched("fcfs", reqs, max_batch=3, input_len=1024)
+    assert b == [[900, 50, 400], [60, 70]] and len(w) == 1 and s.dropped == 1
+    # token limit in arrival order: a batch closes where the next request does not fit, nothing overtakes
+    b, _, _ = _sched("fcfs", reqs, max_batch=20, input_len=1024, max_batch_tokens=1000)
+    assert b == [[900, 50], [400, 60, 70]]
+    # shortest first, with the same limit: short prompts go together, the long one alone
+    b, _, _ = _sched("sjf", reqs, max_batch=20, input_len=1024, max_batch_tokens=1000)
+    assert b == [[50, 60, 70, 400], [900]]
+    # a single request over the token limit still runs (alone) instead of waiting forever
+    b, _, _ = _sched("sjf", [(800, 99.0)], max_batch=4, input_len=1024, max_batch_tokens=100)
+    assert b == [[800]]
+
+
+def test_aged_policy_lets_a_long_prompt_overtake_once_it_has_waited():
+    # 900 tokens, waiting 2 s at 400 tokens per second of ageing -> counts as 100: ahead of the fresh 300-token request
+    b, _, _ = _sched("aged", [(900, 98.0), (300, 100.0), (50, 100.0)], max_batch=2, input_len=1024, aging_tokens_per_s=400.0)
+    assert b == [[50, 900], [300]]
+    b, _, _ = _sched("sjf", [(900, 98.0), (300, 100.0), (50, 100.0)], max_batch=2, input_len=1024)
+    assert b == [[50, 300], [900]]
