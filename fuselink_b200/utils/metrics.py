@@ -50,7 +50,7 @@ def render(C, mon: int, extra: Optional[dict] = None) -> str:
 def plugin_counters(path: Optional[str] = None) -> dict:
     """Counters of the ncclNet plugin as loaded in THIS process (NCCL and ``ctypes`` share one copy of the library):
     selector decisions and fallbacks, stripes moved after a link failure, bytes stored through the same-host direct
-    path, RDMA messages / pieces / work requests.  Usable as ``extra`` of :func:`render` / :class:`MetricsServer`."""
+    path, RDMA messages / pieces / work requests, memory registrations (made, answered from the cache, through a dma-buf).  Usable as ``extra`` of :func:`render` / :class:`MetricsServer`."""
     import ctypes
     import os
     if path is None:
@@ -66,6 +66,9 @@ def plugin_counters(path: Optional[str] = None) -> dict:
     m, p, w = ctypes.c_ulonglong(), ctypes.c_ulonglong(), ctypes.c_ulonglong()
     lib.fuselink_rdma_counters(ctypes.byref(m), ctypes.byref(p), ctypes.byref(w))
     out.update(plugin_rdma_messages=m.value, plugin_rdma_pieces=p.value, plugin_rdma_work_requests=w.value)
+    r, h, d = ctypes.c_ulonglong(), ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    lib.fuselink_rdma_mr_counters(ctypes.byref(r), ctypes.byref(h), ctypes.byref(d))
+    out.update(plugin_rdma_registrations=r.value, plugin_rdma_registration_cache_hits=h.value, plugin_rdma_dmabuf_registrations=d.value)
     return out
 
 
