@@ -1,5 +1,5 @@
 """Randomised configurations of the plugin (fixed seeds): transport, number of devices, degree / step / minimum stripe,
-queue pairs, adaptive routing, inline, monitor on or off, device buffers, message sizes, chunk size, requests in flight,
+queue pairs, adaptive routing, inline, monitor on or off, device buffers (by address or dma-buf), message sizes, chunk size, requests in flight,
 channels, threads -- every transfer must be bit exact; and the same with one link broken at a random point, which the
 transfer must survive."""
 import random
@@ -23,8 +23,12 @@ def _config(rng):
     if rng.random() < 0.3:
         common.append("--threads")
     if rng.random() < 0.3:
-        env.update(FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS=str(rng.choice([1, 2, 8])))
-        common.append("--device-buffers")
+        # device buffers: registered by address or through a dma-buf (the plugin's own descriptor, or one handed in the way
+        # NCCL does), at the start of the allocation or inside it
+        env.update(FUSELINK_CUDA_PTRS="1", FUSELINK_VMM_FAKE="1", FUSELINK_VMM_FAKE_NGPUS=str(rng.choice([1, 2, 8])),
+                   FUSELINK_SOFT_PEERMEM=str(rng.choice([0, 1])), FUSELINK_REMAP=str(rng.choice([0, 1])))
+        common.append(rng.choice(["--device-buffers", "--device-buffers", "--nccl-dmabuf"]))
+        common += ["--reg-offset", str(rng.choice([0, 0, 256, 4096]))]
     sizes = [rng.choice([0, 1, 17, 4096, 4097, 65536, 1 << 20, (1 << 20) + 3, 5 << 20]) for _ in range(rng.randint(1, 4))]
     return env, common, sizes
 
