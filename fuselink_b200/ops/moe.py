@@ -72,6 +72,7 @@ class MoEWorkspace:
         self.nshadow = len(cfg.shadow)                    # + its copies of the shadowed experts
         self.epr = self.epr_real + self.nshadow           # slots per rank: what the kernels call experts per rank
         self.num_slots = W * self.epr
+        assert self.epr <= 64, "the grouped GEMM takes at most 64 groups per launch"
         self.cap = (cfg.tokens * W + 127) // 128 * 128
         rows = self.epr * self.cap
         H, F, T, k = cfg.hidden, cfg.ffn, cfg.tokens, cfg.topk
