@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--shadow", type=int, default=0, help="replicate the N most favoured experts of every layer on every rank (CUDA, several ranks)")
     ap.add_argument("--reshadow-every", type=int, default=0, help="with --shadow: every K steps choose the shadowed experts of each layer "
                                                                   "again from the loads of the last batch")
+    ap.add_argument("--reshadow-tolerance", type=float, default=0.15, help="copy slots stay empty once the busiest rank is within (1 + this) of the mean load")
     ap.add_argument("--checkpoint", default="", help="save the last state here (per rank: experts differ)")
     ap.add_argument("--resume", default="", help="load <path>.rank<r> written by --checkpoint (same world size) before training")
     a = ap.parse_args()
@@ -80,7 +81,7 @@ def main():
         tok += a.batch * a.seq
         if a.reshadow_every and step % a.reshadow_every == 0:
             for b in net.blocks:                 # between steps: nothing of the layer is in flight
-                b.moe.reshadow()
+                b.moe.reshadow(tolerance=a.reshadow_tolerance)
         if step % a.log_every == 0 or step == a.steps:
             if ev:
                 ev[1].record()

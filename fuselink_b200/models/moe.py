@@ -87,7 +87,7 @@ class MoELayer(nn.Module):
         # (seed, global expert id), not on the layout, so a copy starts out equal to the owner's expert
         w13, w2 = [], []
         for e in [rank * self.epr + le for le in range(self.epr)] + list(cfg.shadow):
-            ge = torch.Generator().manual_seed(seed * 1000 + 17 + e)
+            ge = torch.Generator().manual_seed(seed * 1000 + 17 + max(e, 0))      # e < 0: an empty copy slot, contents unused
             wg = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
             wu = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
             wd = (torch.randn(H, F, generator=ge) * 0.02).to(torch.bfloat16)
@@ -125,7 +125,7 @@ class MoELayer(nn.Module):
         """Copy this rank's copy of every shadowed expert it owns into the expert's own slot (which receives no rows while
         the expert is shadowed and so goes stale): call before exporting the experts or changing the set of shadows."""
         for j, e in enumerate(self.cfg.shadow):
-            if e // self.epr == self.rank:
+            if e >= 0 and e // self.epr == self.rank:
                 self.w13[e % self.epr].copy_(self.w13[self.epr + j])
                 self.w2[e % self.epr].copy_(self.w2[self.epr + j])
 
@@ -135,11 +135,15 @@ class MoELayer(nn.Module):
         copies they own (they hold the trained weights), then every new shadow's weights go from its owner to the slot on
         every rank.  Collective over the ranks of the layer."""
         experts = tuple(int(e) for e in experts)
-        assert len(experts) == len(self.cfg.shadow) and len(set(experts)) == len(experts)
+        experts = tuple(e for e in experts if e >= 0) + (-1,) * sum(1 for e in experts if e < 0)   # slots in use first
+        assert len(experts) <= len(self.cfg.shadow), "more shadows than copy slots"
+        experts += (-1,) * (len(self.cfg.shadow) - len(experts))
         if experts == tuple(self.cfg.shadow):
             return
         self.sync_shadow_to_real()
         for j, e in enumerate(experts):
+            if e < 0:
+                continue
             owner = e // self.epr
             for w in (self.w13, self.w2):
                 slot = w[self.epr + j]
@@ -153,9 +157,10 @@ class MoELayer(nn.Module):
             self.ws.set_shadow(experts)
 
     @torch.no_grad()
-    def reshadow(self, topk_idx: Optional[torch.Tensor] = None, group=None) -> tuple:
+    def reshadow(self, topk_idx: Optional[torch.Tensor] = None, group=None, tolerance: Optional[float] = None) -> tuple:
         """Choose the shadows from the routing of a batch (``topk_idx`` of this rank, by default the last one routed; the
-        loads are summed over the ranks) and install them.  Returns the experts now shadowed.  An optimizer that keeps
+        loads are summed over the ranks) and install them; with ``tolerance`` copy slots are left empty (-1) once the busiest rank is within (1 + tolerance) of the
+        mean load.  Returns the experts now shadowed.  An optimizer that keeps
         per-parameter state (momentum, Adam moments) keeps the state of a slot, not of the expert that moves into it."""
         from ..ops.moe import choose_shadows
         n = len(self.cfg.shadow)
@@ -167,7 +172,8 @@ class MoELayer(nn.Module):
         if self.world > 1:
             import torch.distributed as dist
             dist.all_reduce(load, group=group)
-        chosen = choose_shadows(load, n)
+        # with a tolerance: only as many copies as it takes to bring the busiest rank within (1 + tolerance) of the mean
+        chosen = choose_shadows(load, n) if tolerance is None else choose_shadows(load, n, self.world, tolerance)
         self.set_shadows(chosen, group)
         return chosen
 

@@ -33,7 +33,8 @@ class MoEConfig:
     topk: int = 2
     tokens: int = 8192          # tokens per rank and step
     fp8: bool = False           # block-scaled e4m3 ("1 x 128") for the forward and dgrad GEMMs; wgrad stays bf16
-    shadow: Tuple[int, ...] = ()  # experts replicated on every rank ("shadow" experts), see slot_table()
+    shadow: Tuple[int, ...] = ()  # experts replicated on every rank ("shadow" experts), see slot_table(); one entry per copy
+                                  # slot, the slots in use first, -1 for a slot that is empty at the moment
 
 
 def slot_table(num_experts: int, world: int, shadow: Sequence[int], rank: int) -> torch.Tensor:
@@ -51,11 +52,13 @@ def slot_table(num_experts: int, world: int, shadow: Sequence[int], rank: int) -
     assert num_experts % world == 0
     real = num_experts // world
     spr = real + len(shadow)
-    assert len(set(shadow)) == len(shadow) and all(0 <= e < num_experts for e in shadow)
+    used = [e for e in shadow if e >= 0]
+    assert len(set(used)) == len(used) and all(e < num_experts for e in used)
+    assert list(shadow[:len(used)]) == used, "the copy slots in use come first"
     t = torch.full((num_experts + 2,), -1, dtype=torch.int32)
     for e in range(num_experts):
         t[e + 1] = (e // real) * spr + e % real
-    for j, e in enumerate(shadow):
+    for j, e in enumerate(used):
         t[e + 1] = rank * spr + real + j
     return t
 
@@ -69,7 +72,7 @@ class MoEWorkspace:
         W = heap.world
         assert cfg.num_experts % W == 0, "experts must divide evenly over ranks"
         self.epr_real = cfg.num_experts // W              # experts this rank owns
-        self.nshadow = len(cfg.shadow)                    # + its copies of the shadowed experts
+        self.nshadow = len(cfg.shadow)                    # + its copy slots for shadowed experts (some may be empty)
         self.epr = self.epr_real + self.nshadow           # slots per rank: what the kernels call experts per rank
         self.num_slots = W * self.epr
         assert self.epr <= 64, "the grouped GEMM takes at most 64 groups per launch"
@@ -114,18 +117,43 @@ class MoEWorkspace:
     def counts_now(self) -> torch.Tensor:
         return self.counts.local[self.step_parity]
 
+    @property
+    def shadows_in_use(self) -> int:
+        return sum(1 for e in self.cfg.shadow if e >= 0)
+
     def set_shadow(self, shadow: Sequence[int]) -> None:
-        """Other experts in the copy slots (as many as before: the buffers keep their size).  Between steps only."""
+        """Other experts in the copy slots (as many slots as before: the buffers keep their size; -1 = empty, in-use slots
+        first).  Between steps only."""
         assert len(shadow) == self.nshadow and self.pending_shadow is None
         self.cfg = dataclasses.replace(self.cfg, shadow=tuple(int(e) for e in shadow))
         if self.nshadow:
             self.slots_of = slot_table(self.cfg.num_experts, self.heap.world, self.cfg.shadow, self.heap.rank).to(self.slots_of.device)
 
 
-def choose_shadows(expert_load: torch.Tensor, n: int) -> Tuple[int, ...]:
-    """The n experts with the most routed rows (ties: the lower id), from the load summed over all ranks."""
-    order = torch.argsort(expert_load.double().cpu(), descending=True, stable=True)
-    return tuple(int(e) for e in order[:n])
+def busiest_rank_load(expert_load: Sequence[float], world: int, shadow: Sequence[int]) -> float:
+    """Rows on the busiest rank when the experts in ``shadow`` are replicated: a rank computes the rows of the experts it
+    owns that are not shadowed, plus its own share (taken as 1 / world) of every shadowed expert's rows."""
+    E = len(expert_load)
+    real = E // world
+    sh = {e for e in shadow if e >= 0}
+    spread = sum(expert_load[e] for e in sh) / world
+    return max(sum(expert_load[e] for e in range(r * real, (r + 1) * real) if e not in sh) for r in range(world)) + spread
+
+
+def choose_shadows(expert_load: torch.Tensor, slots: int, world: int = 0, tolerance: float = 0.0) -> Tuple[int, ...]:
+    """Which experts to replicate, from the rows routed to each expert summed over all ranks: the busiest experts first
+    (ties: the lower id), one per copy slot.  With ``world`` and ``tolerance`` given, experts are added only while the
+    busiest rank would still carry more than (1 + tolerance) x the mean, so a router that has become balanced stops paying
+    for gradient all-reduces; the slots left over are returned as -1."""
+    load = [float(v) for v in expert_load.double().cpu()]
+    order = sorted(range(len(load)), key=lambda e: (-load[e], e))
+    if not world:
+        return tuple(order[:slots])
+    mean = sum(load) / world
+    chosen: list = []
+    while len(chosen) < slots and busiest_rank_load(load, world, chosen) > (1.0 + tolerance) * mean:
+        chosen.append(order[len(chosen)])
+    return tuple(chosen) + (-1,) * (slots - len(chosen))
 
 
 def _allreduce_shadow_grads(ws: MoEWorkspace, grads):
@@ -246,7 +274,7 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
         # Owned experts as below, on the leading slots.  The copies of the shadowed experts have seen this rank's rows
         # only: their gradients are stored, summed over the ranks after the signal and applied then, identically on
         # every rank, so the copies stay equal without ever being sent.
-        R, S, cut = ws.epr_real, ws.nshadow, ws.epr_real * ws.cap
+        R, S, cut = ws.epr_real, ws.shadows_in_use, ws.epr_real * ws.cap
         dyd, dgu, act, xd = ws.dyd.local, ws.dgu, ws.act, ws.xd.local
         if sgd_lr:
             gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=w2[:R], sgd_lr=sgd_lr, status=st)
@@ -257,9 +285,13 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
             dw13 = torch.empty_like(w13)
             gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=dw2[:R], status=st)
             gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=dw13[:R], status=st)
-        shadow_grads = (gemm.grouped_gemm_wgrad(dgu[cut:], xd[cut:], counts[R:], ws.cap, S, status=st),
-                        gemm.grouped_gemm_wgrad(dyd[cut:], act[cut:], counts[R:], ws.cap, S, status=st))
-        ws.launches += 2
+            dw2[R:].zero_()                                          # copy slots: filled in once the sums are complete, empty
+            dw13[R:].zero_()                                         # ones stay zero
+        if S:
+            end = cut + S * ws.cap                                   # empty copy slots at the end take no part
+            shadow_grads = (gemm.grouped_gemm_wgrad(dgu[cut:end], xd[cut:end], counts[R:R + S], ws.cap, S, status=st),
+                            gemm.grouped_gemm_wgrad(dyd[cut:end], act[cut:end], counts[R:R + S], ws.cap, S, status=st))
+            ws.launches += 2
     elif sgd_lr:
         gemm.grouped_gemm_wgrad(ws.dyd.local, ws.act, counts, ws.cap, ws.epr, out=w2, sgd_lr=sgd_lr, status=st)
         gemm.grouped_gemm_wgrad(ws.dgu, ws.xd.local, counts, ws.cap, ws.epr, out=w13, sgd_lr=sgd_lr, status=st)
@@ -293,13 +325,13 @@ def finish_shadow_grads(ws: MoEWorkspace, started) -> None:
     for w in works:
         if hasattr(w, "wait"):
             w.wait()
-    R = ws.epr_real
+    R, S = ws.epr_real, g13.shape[0]
     if sgd_lr:
-        w13[R:].add_(g13, alpha=-sgd_lr)
-        w2[R:].add_(g2, alpha=-sgd_lr)
+        w13[R:R + S].add_(g13, alpha=-sgd_lr)
+        w2[R:R + S].add_(g2, alpha=-sgd_lr)
     else:
-        dw13[R:].copy_(g13)
-        dw2[R:].copy_(g2)
+        dw13[R:R + S].copy_(g13)
+        dw2[R:R + S].copy_(g2)
 
 
 def moe_backward_finish(ws: MoEWorkspace, need_dx: bool = True) -> Optional[torch.Tensor]:

@@ -55,7 +55,7 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
             # backward
             dws = [M.moe_backward_dispatch(wss[r], douts[r], routes[r][1].contiguous(), routes[r][0].contiguous()) for r in range(world)]
             grads = [M.moe_backward_experts(wss[r], layers[r].w13.data, layers[r].w2.data, sgd, True) for r in range(world)]
-            if shadow:
+            if any(e >= 0 for e in shadow):
                 # the ranks are emulated on one GPU: the sum over ranks that NCCL would do is done here
                 totals = [sum(wss[r].pending_shadow[0][i] for r in range(world)) for i in range(2)]
                 for w_ in wss:
@@ -97,6 +97,9 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
                         close(du[i], wu.grad[own(r)[i]], f"dWup rank {r} slot {i}")
                         close(grads[r][1][i], w2.grad[own(r)[i]], f"dW2 rank {r} slot {i}")
                     for j, e in enumerate(shadow):                      # summed over the ranks: the expert's whole gradient
+                        if e < 0:                                       # an empty copy slot
+                            assert grads[r][1][epr + j].abs().max() == 0 and dg[epr + j].abs().max() == 0
+                            continue
                         close(dg[epr + j], wg.grad[e], f"dWgate shadow {e} on rank {r}")
                         close(du[epr + j], wu.grad[e], f"dWup shadow {e} on rank {r}")
                         close(grads[r][1][epr + j], w2.grad[e], f"dW2 shadow {e} on rank {r}")
@@ -110,6 +113,8 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
                         close(g_[i], wg.detach()[own(r)[i]], f"Wgate after sgd rank {r} slot {i}", 2e-2)
                         close(layers[r].w2.data[i], w2.detach()[own(r)[i]], f"W2 after sgd rank {r} slot {i}", 2e-2)
                     for j, e in enumerate(shadow):
+                        if e < 0:
+                            continue
                         close(g_[epr + j], wg.detach()[e], f"Wgate copy of {e} after sgd rank {r}", 2e-2)
                         close(layers[r].w2.data[epr + j], w2.detach()[e], f"W2 copy of {e} after sgd rank {r}", 2e-2)
                         assert torch.equal(layers[r].w2.data[epr + j], layers[0].w2.data[epr + j]), "copies must stay identical"

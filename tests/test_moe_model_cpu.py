@@ -184,3 +184,10 @@ def test_changing_the_shadowed_expert_between_steps():
     finally:
         for h in heaps:
             h.close()
+
+
+def test_an_empty_copy_slot_costs_nothing_and_changes_nothing():
+    """Two copy slots, one in use: same results as with exactly one slot, and the empty slot's gradient rows are zero."""
+    _run_on_model(2, shadow=(4, -1))
+    _run_on_model(2, sgd=0.05, steps=2, shadow=(4, -1))
+    _run_on_model(2, shadow=(-1, -1))

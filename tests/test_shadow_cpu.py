@@ -130,3 +130,31 @@ def test_reshadow_moves_the_weights_between_owners_and_copies(tmp_path):
     # both copy slots now hold expert 2 as its owner (rank 1) had it
     want = fresh[1].w2.data[0].float() * 2.0
     assert torch.allclose(r0["w2"][2].float(), want, atol=1e-2) and torch.equal(r0["w2"][2], r1["w2"][2])
+
+
+def test_choice_of_shadows_stops_when_the_load_is_level_enough():
+    from fuselink_b200.ops.moe import busiest_rank_load, choose_shadows
+    load = torch.tensor([4300., 2000., 1100., 900., 700., 600., 500., 400.])       # 8 ranks, one expert each; mean 1312.5
+    assert busiest_rank_load(load.tolist(), 8, ()) == 4300
+    assert busiest_rank_load(load.tolist(), 8, (0,)) == 2000 + 4300 / 8
+    assert choose_shadows(load, 3) == (0, 1, 2)                                    # no tolerance given: fill every slot
+    assert choose_shadows(load, 4, world=8, tolerance=0.6) == (0, 1, -1, -1)       # 1100 + 6300 / 8 = 1887 < 1.6 x mean
+    assert choose_shadows(load, 4, world=8, tolerance=0.05) == (0, 1, 2, 3)        # slots run out first
+    assert choose_shadows(torch.full((8,), 100.), 4, world=8, tolerance=0.1) == (-1, -1, -1, -1)   # balanced router: no copies
+    # two ranks, four experts each: rank 0 owns the hot ones
+    assert choose_shadows(torch.tensor([500., 400., 300., 200., 50., 50., 50., 50.]), 3, world=2, tolerance=0.2) == (0, 1, -1)
+
+
+def test_empty_copy_slots_in_the_table_and_the_layer():
+    t = slot_table(8, 4, (5, -1), 2)
+    assert t[6] == 2 * 4 + 2 and sorted(t[1:9].tolist()) == sorted([0, 1, 4, 5, 8, 9, 10, 12, 13][:0] + t[1:9].tolist())
+    assert (t[1:9] == 2 * 4 + 3).sum() == 0                                        # nothing maps to the empty slot
+    import pytest
+    with pytest.raises(AssertionError):
+        slot_table(8, 4, (-1, 5), 2)                                               # slots in use come first
+    cfg = MoEConfig(hidden=128, ffn=256, num_experts=4, topk=2, tokens=8)
+    l = MoELayer(cfg, None, 0, 1, device="cpu", seed=1, shadow_experts=[2, 3])
+    l.set_shadows([-1, 3])                                                         # normalised: the slot in use first
+    assert l.cfg.shadow == (3, -1) and torch.equal(l.w2[4], l.w2[3])
+    l.reshadow(torch.tensor([[0, 1], [2, 3], [0, 2], [1, 3]]), tolerance=0.5)     # one rank: always level
+    assert l.cfg.shadow == (-1, -1)
