@@ -139,7 +139,7 @@ _UNVERIFIED = pytest.mark.skipif(__import__("os").environ.get("FUSELINK_TEST_UNV
 
 
 @_UNVERIFIED
-@pytest.mark.parametrize("world,shadow", [(2, (0,)), (4, (0, 5)), (1, (2,))])
+@pytest.mark.parametrize("world,shadow", [(2, (0,)), (4, (0, 5)), (1, (2,)), (2, (4, -1))])
 def test_moe_shadow_experts(world, shadow):
     """Hot experts replicated on every rank: same outputs and gradients as without, the copies' gradients summed."""
     _run(world, shadow=shadow)
