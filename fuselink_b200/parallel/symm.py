@@ -50,21 +50,30 @@ class SymmetricHeap:
     # ------------------------------------------------------------------ construction
     @classmethod
     def create(cls, size: int, group=None, device: Optional[int] = None) -> "SymmetricHeap":
-        """Collective over ``group`` (default: the world group): one region per rank, all mapped everywhere."""
+        """Collective over ``group`` (default: the world group): one region per rank, all mapped everywhere.
+
+        On a machine without a GPU (or with ``device=-1``) the regions are memfd-backed host memory shared between the
+        processes the same way -- file descriptors over SCM_RIGHTS -- which is what multi-process CPU tests run on."""
         import torch.distributed as dist
 
         C = require_native()
-        if device is None:
-            device = torch.cuda.current_device()
-        torch.cuda.set_device(device)
-        torch.cuda.init()
-        torch.zeros(1, device=f"cuda:{device}")  # make sure the primary context exists and is current
-        C.vmm_init(0)
+        on_gpu = torch.cuda.is_available() and (device is None or device >= 0)
+        if on_gpu:
+            if device is None:
+                device = torch.cuda.current_device()
+            torch.cuda.set_device(device)
+            torch.cuda.init()
+            torch.zeros(1, device=f"cuda:{device}")  # make sure the primary context exists and is current
+            C.vmm_init(0)
+        else:
+            device = -1
+            C.vmm_init(1)
+        vdev = max(device, 0)
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         world = dist.get_world_size(group) if dist.is_initialized() else 1
-        gran = C.vmm_granularity(device)
+        gran = C.vmm_granularity(vdev)
         size = _round_up(max(size, SIGNAL_BYTES + STATUS_BYTES + _ALIGN), gran)
-        mine = C.vmm_create(device, size, 0)
+        mine = C.vmm_create(vdev, size, 0)
         regions = [None] * world
         bases = [0] * world
         regions[rank] = mine
@@ -78,13 +87,14 @@ class SymmetricHeap:
             for r in range(world):
                 if r == rank:
                     continue
-                imp = C.vmm_import(device, [fds[r]], size)
+                imp = C.vmm_import(vdev, [fds[r]], size)
                 os.close(fds[r])
                 regions[r] = imp
                 bases[r] = C.vmm_ptr(imp)
         heap = cls(rank, world, device, size, regions, bases)
         heap.local_bytes().zero_()
-        torch.cuda.synchronize(device)
+        if on_gpu:
+            torch.cuda.synchronize(device)
         if world > 1:
             dist.barrier(group=group)
         return heap

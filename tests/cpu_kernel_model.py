@@ -34,10 +34,60 @@ class Model:
         if st[0] == 0:
             st[0], st[1] = code, where
 
-    # ---------------------------------------------------------------------------------------- barrier
+    # ---------------------------------------------------------------------------------------- flags, copies, barrier
+    # Ranks emulated in ONE process run their phases one after the other, so a wait finds its flags already set.  Ranks
+    # that are separate processes over a shared-memory heap (SymmetricHeap.create on the memfd backend) really wait here,
+    # with the kernels' rule: a wait that runs out records a status and returns.
+    wait_limit_s = 2.0
+
+    def _flag(self, addr):
+        return self._view(addr, [1], torch.int32)
+
+    def _wait_ge(self, addr, want, status_addr, where):
+        import time
+        f = self._flag(addr)
+        t0 = time.monotonic()
+        while ((int(f[0]) - int(want)) & 0xFFFFFFFF) >= 0x80000000:          # wrap-around "less than"
+            if time.monotonic() - t0 > self.wait_limit_s:
+                self._status(status_addr, 1, where)
+                return False
+            time.sleep(0.0002)
+        return True
+
     def barrier(self, pads, slot0, rank, world, seq, do_signal, do_wait, status_addr):
-        # the phases of the emulated ranks run one after the other in one thread: nothing to wait for
-        return None
+        if do_signal:
+            for r in range(world):
+                self._flag(pads[r] + 4 * (slot0 + rank))[0] = int(seq) - (1 << 32 if int(seq) >= (1 << 31) else 0)
+        if do_wait and not self.single_process:
+            for r in range(world):
+                self._wait_ge(pads[rank] + 4 * (slot0 + r), seq, status_addr, 800 + r)
+
+    single_process = True
+
+    def put_chunks(self, segs, chunk_bytes, seq, use_bulk, num_ctas, threads, status_addr, counters=()):
+        for i, (src, dst, nbytes, flags, mode, wait_flags) in enumerate(segs):
+            assert not wait_flags, "relay segments are not modelled"
+            self._view(dst, [nbytes], torch.uint8).copy_(self._view(src, [nbytes], torch.uint8))
+            nchunks = (nbytes + chunk_bytes - 1) // chunk_bytes
+            if mode == 2:                                                     # arrival counter: one per chunk
+                f = self._flag(flags)
+                f[0] = ((int(f[0]) + nchunks + (1 << 31)) % (1 << 32)) - (1 << 31)
+            elif mode == 1:                                                   # one word per chunk = seq
+                self._view(flags, [nchunks], torch.int32).fill_(int(seq))
+            if i < len(counters) and counters[i]:
+                self._view(counters[i], [1], torch.int64)[0] += nbytes
+
+    def wait_flags(self, flags, status_addr, limit_ms=0):
+        for i, (addr, want) in enumerate(flags):
+            self._wait_ge(addr, want, status_addr, 700 + i)
+
+    def all_to_all(self, send_addr, recv_peers, per, rank, pads, slot0, chunk_bytes, want, use_bulk, num_ctas, threads, status_addr):
+        world = len(recv_peers)
+        segs = [(send_addr + p * per, recv_peers[p] + rank * per, per, pads[p] + 4 * (slot0 + rank), 2, 0)
+                for p in ((rank + k) % world for k in range(world))]
+        self.put_chunks(segs, chunk_bytes, 0, use_bulk, num_ctas, threads, status_addr)
+        for r, w in enumerate(want):
+            self._wait_ge(pads[rank] + 4 * (slot0 + r), w, status_addr, 600 + r)
 
     # ---------------------------------------------------------------------------------------- dispatch
     def moe_dispatch(self, x, topk_idx, row_scale, num_experts, epr, cap, rank, world, local_count, base, pos, slot,
@@ -191,11 +241,13 @@ class Model:
 
 
 @contextlib.contextmanager
-def installed():
-    """Inside the block the MoE path's modules get the model instead of the extension."""
+def installed(single_process=True):
+    """Inside the block the MoE path's and the transfer path's modules get the model instead of the extension.  With
+    ``single_process=False`` barriers really wait (the ranks are separate processes over a shared-memory heap)."""
     from fuselink_b200 import _ext
     from fuselink_b200.ops import comm, gemm, moe
     model = Model(_ext.require_native())
+    model.single_process = single_process
     from fuselink_b200.ops import fp8
     saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8)]
     for m, _ in saved:

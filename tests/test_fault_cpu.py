@@ -140,3 +140,17 @@ def test_heartbeat_detects_a_lost_or_leaving_rank_before_the_next_launch(mode):
         assert (lost, left) == (([2], []) if mode == "crash" else ([], [2]))
         assert dt < (10.0 if mode == "crash" else 6.0)           # lease expiry vs an explicit goodbye (generous: loaded CI hosts)
         assert surv == [0, 1] and (new_rank, new_world) == (rank, 2)
+
+
+def test_rank_leaves_between_steps_and_the_others_carry_on():
+    """Three processes over a heap they really share (memfd regions, descriptors over SCM_RIGHTS), the device entry
+    points replaced by their host model: an all-to-all with everybody, the last rank leaves cleanly, the other two learn
+    of it from the heartbeat, run a ring of puts among themselves, and a wait on the leaver runs out into the status word."""
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    port = _free_port()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "mp_leave_cpu_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=180)
+    assert out.stdout.count("LEAVE-OK") == 2, out.stdout[-3000:] + out.stderr[-3000:]
