@@ -63,6 +63,20 @@ class Model:
                 self._wait_ge(pads[rank] + 4 * (slot0 + r), seq, status_addr, 800 + r)
 
     single_process = True
+    lock_path = None                 # ranks in separate processes: a file all of them lock around a reservation
+
+    @contextlib.contextmanager
+    def _reserve_lock(self):
+        if self.single_process or not self.lock_path:
+            yield
+            return
+        import fcntl
+        with open(self.lock_path, "a") as f:
+            fcntl.flock(f, fcntl.LOCK_EX)
+            try:
+                yield
+            finally:
+                fcntl.flock(f, fcntl.LOCK_UN)
 
     def put_chunks(self, segs, chunk_bytes, seq, use_bulk, num_ctas, threads, status_addr, counters=()):
         for i, (src, dst, nbytes, flags, mode, wait_flags) in enumerate(segs):
@@ -107,13 +121,14 @@ class Model:
                     continue
                 posf[i] = local_count[e]
                 local_count[e] += 1
-            for e in range(num_experts):
-                owner, le = divmod(e, epr)
-                cnt = self._view(count_peers[owner], [2, epr], torch.int32)
-                n = int(local_count[e])
-                base[e] = int(cnt[parity, le]) if n > 0 else 0
-                cnt[parity, le] += n
-                local_count[e] = 0
+            with self._reserve_lock():                              # what atomicAdd_system gives the kernel
+                for e in range(num_experts):
+                    owner, le = divmod(e, epr)
+                    cnt = self._view(count_peers[owner], [2, epr], torch.int32)
+                    n = int(local_count[e])
+                    base[e] = int(cnt[parity, le]) if n > 0 else 0
+                    cnt[parity, le] += n
+                    local_count[e] = 0
             self._view(count_peers[rank], [2, epr], torch.int32)[parity ^ 1].zero_()
         for i in range(T * k):
             e = int(idx[i])
@@ -241,13 +256,14 @@ class Model:
 
 
 @contextlib.contextmanager
-def installed(single_process=True):
+def installed(single_process=True, lock_path=None):
     """Inside the block the MoE path's and the transfer path's modules get the model instead of the extension.  With
     ``single_process=False`` barriers really wait (the ranks are separate processes over a shared-memory heap)."""
     from fuselink_b200 import _ext
     from fuselink_b200.ops import comm, gemm, moe
     model = Model(_ext.require_native())
     model.single_process = single_process
+    model.lock_path = lock_path
     from fuselink_b200.ops import fp8
     saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8)]
     for m, _ in saved:
