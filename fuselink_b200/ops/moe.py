@@ -9,7 +9,9 @@ backward  dw = <dOut, y_k>; dispatch(w_k * dOut) to the slots chosen in forward 
           dAct GEMM (B MN-major, DSWIGLU epilogue) -> wgrad W2, wgrad W13 (K-grouped, both operands MN-major)
           -> dX GEMM (B MN-major, SCATTER epilogue) -> barrier -> sum over k
 
-There is no stand-alone all-to-all and no framework permute in either direction; NCCL is not called.
+There is no stand-alone all-to-all and no framework permute in either direction; NCCL is not called -- except for one
+all-reduce per step when experts are shadowed (``MoEConfig.shadow``, ``slot_table``): a hot expert is then replicated on
+every rank, its rows are computed where they originate, and the copies' weight gradients are summed over the ranks.
 """
 from __future__ import annotations
 
