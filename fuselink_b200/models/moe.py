@@ -179,9 +179,9 @@ class MoELayer(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, idx = self.route(x)
-        if x.is_cuda:
-            if self.ws is None:
-                raise RuntimeError("MoELayer on CUDA needs a SymmetricHeap (the fused kernels write peer memory)")
+        if x.is_cuda and self.ws is None:
+            raise RuntimeError("MoELayer on CUDA needs a SymmetricHeap (the fused kernels write peer memory)")
+        if self.ws is not None:          # a heap was given: the fused path (on host memory only in tests that model the kernels)
             return MoEFunction.apply(x, w, idx, self.w13, self.w2, self.ws, self.fused_sgd_lr)
         return self._forward_reference(x, w, idx)
 

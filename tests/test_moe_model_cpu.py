@@ -208,3 +208,19 @@ def test_expert_parallel_step_between_processes(world, tmp_path):
            "--master-port", str(port), os.path.join(here, "mp_moe_cpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.stdout.count("MOE-MP-OK") == world, out.stdout[-2000:] + out.stderr[-4000:]
+
+
+def test_moe_transformer_trains_between_processes(tmp_path):
+    """Two processes, the MoE transformer with one shadowed expert per layer chosen again every step: replicated
+    parameters and copies stay identical on both ranks and the loss falls."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    env = dict(os.environ, FL_MODEL_LOCK=str(tmp_path / "reserve.lock"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "mp_moe_train_cpu_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.stdout.count("MOE-TRAIN-OK") == 2, out.stdout[-2000:] + out.stderr[-4000:]
