@@ -147,7 +147,8 @@ class DLRM(nn.Module):
     # ---- one training step (public API) --------------------------------------------------------------------
     def train_step(self, dense: torch.Tensor, indices: torch.Tensor, labels: torch.Tensor, opt: torch.optim.Optimizer):
         """Forward + backward + SGD on dense and sparse parameters.  Returns the (detached) loss."""
-        if dense.is_cuda:
+        fused = self.heap is not None          # a heap was given: the fused kernels (on host memory only in tests that model them)
+        if fused:
             self.sparse_forward_launch(indices)
             pooled = self.sparse_forward_wait().detach().requires_grad_(True)
         else:
@@ -165,7 +166,7 @@ class DLRM(nn.Module):
             work = dist.all_reduce(flat, async_op=True)
         # the loss is a mean over the local batch; the global objective is the mean over ranks
         gp = pooled.grad / self.world if self.world > 1 else pooled.grad
-        if dense.is_cuda:
+        if fused:
             self.sparse_backward_launch(gp)
             self.sparse_backward_apply(indices)
         else:

@@ -103,6 +103,26 @@ class Model:
         for r, w in enumerate(want):
             self._wait_ge(pads[rank] + 4 * (slot0 + r), w, status_addr, 600 + r)
 
+    # ---------------------------------------------------------------------------------------- embedding bag + all-to-all
+    def embbag(self, backward, weights, indices, t_first, t_total, b_local, peers, lr, num_ctas, status_addr):
+        """forward: the pooled vector of (local table t, global sample b) is stored into the sample owner's
+        [b_local, t_total, dim] buffer; backward: the gradient is read from there and every pooled row gets -lr * grad."""
+        assert weights.dtype == torch.float32 and indices.dtype == torch.int64 and indices.shape[0] == weights.shape[0]
+        T, rows, dim = weights.shape
+        _, B, pooling = indices.shape
+        if ((indices < 0) | (indices >= rows)).any():
+            self._status(status_addr, 6, 900)
+        idx = indices.clamp(0, rows - 1)
+        bufs = [self._view(p, [b_local, t_total, dim], torch.float32) for p in peers]
+        for t in range(T):
+            for owner in range(B // b_local):
+                sl = slice(owner * b_local, (owner + 1) * b_local)
+                if not backward:
+                    bufs[owner][:, t_first + t] = weights[t][idx[t, sl]].sum(1)
+                else:
+                    g = bufs[owner][:, t_first + t]                                    # [b_local, dim]
+                    weights[t].index_add_(0, idx[t, sl].reshape(-1), (-lr * g).repeat_interleave(pooling, 0))
+
     # ---------------------------------------------------------------------------------------- dispatch
     def moe_dispatch(self, x, topk_idx, row_scale, num_experts, epr, cap, rank, world, local_count, base, pos, slot,
                      count_peers, parity, x_peers, info_peers, reuse, status_addr):
@@ -264,8 +284,9 @@ def installed(single_process=True, lock_path=None):
     model = Model(_ext.require_native())
     model.single_process = single_process
     model.lock_path = lock_path
+    from fuselink_b200.models import dlrm
     from fuselink_b200.ops import fp8
-    saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8)]
+    saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8, dlrm)]
     for m, _ in saved:
         m.require_native = lambda model=model: model
     try:

@@ -224,3 +224,19 @@ def test_moe_transformer_trains_between_processes(tmp_path):
            "--master-port", str(port), os.path.join(here, "mp_moe_train_cpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.stdout.count("MOE-TRAIN-OK") == 2, out.stdout[-2000:] + out.stderr[-4000:]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_dlrm_fused_step_between_processes(world):
+    """Real processes, shared-memory heap, modelled embedding-bag entry points: losses, tables and dense weights follow the
+    plain-PyTorch path of the same model step by step."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "mp_dlrm_cpu_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert out.stdout.count("DLRM-MP-OK") == world, out.stdout[-2000:] + out.stderr[-4000:]
