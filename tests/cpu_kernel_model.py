@@ -1,14 +1,17 @@
-"""A functional model, in plain PyTorch on host memory, of the device entry points the MoE path calls
-(`moe_dispatch`, `moe_zero_tail`, `grouped_gemm` with its five epilogues, `moe_combine`, `moe_combine_dw`, `barrier`, the
-fp8 quantisers and the block-scaled fp8 grouped GEMM).
+"""A functional model, in plain PyTorch on host memory, of the device entry points the fused paths call: the MoE step
+(`moe_dispatch`, `moe_zero_tail`, `grouped_gemm` with its five epilogues, `moe_combine`, `moe_combine_dw`, the fp8 quantisers
+and the block-scaled fp8 grouped GEMM), the DLRM step (`embbag` forward and backward) and the transfers (`put_chunks`,
+`all_to_all`, `wait_flags`, `barrier`).
 
 It takes the same arguments as the bindings of the real extension, raw addresses of peers' buffers included, and does to
-the memory behind them what the kernels are specified to do.  With it the Python side of `ops/moe.py` -- buffer sizes,
-slices, parities, the order of the phases, what is handed to which call -- runs on a machine without a GPU, over a
-symmetric heap that lives in host memory (`SymmetricHeap.emulated` on the memfd backend).  It says nothing about the
-kernels themselves; those are tested on the GPU against the same fp32 oracle.
+the memory behind them what the kernels are specified to do.  With it the Python side of the fused paths -- buffer sizes,
+slices, parities, the order of the phases, which barrier protects what, what is handed to which call -- runs on a machine
+without a GPU, over a symmetric heap that lives in host memory: ranks emulated in one process (`SymmetricHeap.emulated`
+on the memfd backend), or real processes that share the regions (`SymmetricHeap.create(device=-1)`), in which case waits
+and barriers are real and bounded like the kernels'.  It says nothing about the kernels themselves; those are tested on
+the GPU against the same fp32 oracles.
 
-Use: ``with cpu_kernel_model.installed(): ...`` replaces ``require_native`` in the modules of the MoE path.
+Use: ``with cpu_kernel_model.installed(): ...`` replaces ``require_native`` in the modules of those paths.
 """
 import contextlib
 
