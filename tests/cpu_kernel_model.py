@@ -83,16 +83,21 @@ class Model:
 
     def put_chunks(self, segs, chunk_bytes, seq, use_bulk, num_ctas, threads, status_addr, counters=()):
         for i, (src, dst, nbytes, flags, mode, wait_flags) in enumerate(segs):
-            assert not wait_flags, "relay segments are not modelled"
-            self._view(dst, [nbytes], torch.uint8).copy_(self._view(src, [nbytes], torch.uint8))
             nchunks = (nbytes + chunk_bytes - 1) // chunk_bytes
-            if mode == 2:                                                     # arrival counter: one per chunk
-                f = self._flag(flags)
-                f[0] = ((int(f[0]) + nchunks + (1 << 31)) % (1 << 32)) - (1 << 31)
-            elif mode == 1:                                                   # one word per chunk = seq
-                self._view(flags, [nchunks], torch.int32).fill_(int(seq))
-            if i < len(counters) and counters[i]:
-                self._view(counters[i], [1], torch.int64)[0] += nbytes
+            for c in range(nchunks):
+                off = c * chunk_bytes
+                n = min(chunk_bytes, nbytes - off)
+                if wait_flags and not self._wait_ge(wait_flags + 4 * c, seq, status_addr, 600 + i):
+                    return                                                    # a relay forwards a chunk once its flag shows this transfer
+                self._view(dst + off, [n], torch.uint8).copy_(self._view(src + off, [n], torch.uint8))
+                if mode == 2:                                                 # arrival counter: one per chunk, several senders
+                    with self._reserve_lock():                                # (the kernel's red.release.sys.add)
+                        f = self._flag(flags)
+                        f[0] = ((int(f[0]) + 1 + (1 << 31)) % (1 << 32)) - (1 << 31)
+                elif mode == 1:                                               # one word per chunk = seq
+                    self._flag(flags + 4 * c)[0] = int(seq)
+                if i < len(counters) and counters[i]:
+                    self._view(counters[i], [1], torch.int64)[0] += n
 
     def wait_flags(self, flags, status_addr, limit_ms=0):
         for i, (addr, want) in enumerate(flags):

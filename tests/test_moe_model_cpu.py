@@ -240,3 +240,19 @@ def test_dlrm_fused_step_between_processes(world):
            "--master-port", str(port), os.path.join(here, "mp_dlrm_cpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.stdout.count("DLRM-MP-OK") == world, out.stdout[-2000:] + out.stderr[-4000:]
+
+
+def test_striped_transfer_over_relays_between_processes(tmp_path):
+    """Four processes: the selector splits a 6 MiB transfer 0 -> 1 into a direct stripe and two relayed ones, the relays
+    forward chunk by chunk as the source's flags appear, the destination gets every byte."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    env = dict(os.environ, NCCL_FUSELINK_DEGREE="3", FUSELINK_MIN_STRIPE_BYTES="1048576", FL_MODEL_LOCK=str(tmp_path / "atomic.lock"))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "mp_relay_cpu_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.stdout.count("RELAY-MP-OK") == 4, out.stdout[-2000:] + out.stderr[-4000:]
