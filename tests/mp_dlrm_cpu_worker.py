@@ -1,4 +1,4 @@
-"""Worker of tests/test_moe_model_cpu.py::test_dlrm_fused_step_between_processes: the table-wise sharded DLRM step
+"""Worker of tests/test_kernel_model_cpu.py::test_dlrm_fused_step_between_processes: the table-wise sharded DLRM step
 between real processes on a machine without a GPU.  The fused path (pooled vectors stored into the sample owners' buffers,
 gradients read back from them, SGD on the tables inside the backward entry point, dense gradients all-reduced in one
 bucket while the sparse backward runs) goes through the host model of the embedding-bag entry points over a shared-memory

@@ -1,4 +1,4 @@
-"""Worker of tests/test_moe_model_cpu.py::test_expert_parallel_step_between_processes: the expert-parallel MoE step with
+"""Worker of tests/test_kernel_model_cpu.py::test_expert_parallel_step_between_processes: the expert-parallel MoE step with
 shadow experts between REAL processes on a machine without a GPU.  The symmetric heap is memfd-backed host memory shared by
 the ranks, the device entry points are the host model of tests/cpu_kernel_model.py (its barriers and waits are real), the
 sum of the shadow experts' gradients is a real all-reduce (gloo) and a change of the shadowed experts a real broadcast.

@@ -1,4 +1,4 @@
-"""Worker of tests/test_moe_model_cpu.py::test_moe_transformer_trains_between_processes: a tiny MoE transformer trained for a
+"""Worker of tests/test_kernel_model_cpu.py::test_moe_transformer_trains_between_processes: a tiny MoE transformer trained for a
 few steps by real processes on a machine without a GPU -- experts spread over the ranks with the hottest one shadowed and
 chosen again every step, everything else data parallel -- through the fused path of the MoE layer (device entry points
 modelled on the host, shared-memory heap).  Checks what a training job relies on: the replicated parameters and the copies

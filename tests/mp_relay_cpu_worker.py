@@ -1,4 +1,4 @@
-"""Worker of tests/test_moe_model_cpu.py::test_striped_transfer_over_relays_between_processes: one rank-0 -> rank-1
+"""Worker of tests/test_kernel_model_cpu.py::test_striped_transfer_over_relays_between_processes: one rank-0 -> rank-1
 transfer striped over the direct path and two relay ranks, four real processes on a machine without a GPU.  The stripes
 come from the path selector (monitor table, degree 3); the copy / flag entry points are the host model over a shared-memory
 heap, so the relays really wait for the source's per-chunk flags and the destination for its arrival counter."""

@@ -1,6 +1,8 @@
-"""The Python side of the fused MoE path (ops/moe.py: buffers, slices, parities, phases, shadow experts) run on the CPU:
-the device entry points are replaced by the functional model of tests/cpu_kernel_model.py and the symmetric heap lives
-in host memory.  The scenario and its checks are the ones of the GPU test, against the same fp32 oracle."""
+"""The Python side of the fused paths run on the CPU: the device entry points are replaced by the functional model of
+tests/cpu_kernel_model.py and the symmetric heap lives in host memory.  First the MoE step (ops/moe.py: buffers, slices,
+parities, phases, fp8 arm, shadow experts) with the ranks emulated in one process -- the scenario and the checks are the
+GPU test's own, against the same fp32 oracle -- then MoE, DLRM, striped transfers and a training loop between REAL
+processes that share the heap, where barriers and waits are real."""
 import pytest
 import torch
 
