@@ -199,6 +199,14 @@ class SymmetricHeap:
         a private stream).  For waits that may last long (a decoder waiting for a prefill): no kernel spins on the GPU
         meanwhile.  Returns False on timeout."""
         import time as _time
+        if self.device < 0:                        # host-memory heap (tests on the memfd backend): read the word itself
+            word = self.tensor(4 * slot, [1], torch.int32)
+            t0 = _time.monotonic()
+            while ((int(word[0]) - want) & 0xFFFFFFFF) >= 0x80000000:
+                if _time.monotonic() - t0 > timeout_s:
+                    return False
+                _time.sleep(poll_s)
+            return True
         if not hasattr(self, "_poll_stream"):
             self._poll_stream = torch.cuda.Stream(device=self.device)
             self._poll_host = torch.zeros(1, dtype=torch.int32).pin_memory()

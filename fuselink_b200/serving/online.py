@@ -26,6 +26,7 @@ import torch
 
 from .disagg import HDR_INTS, HDR_LENS, HDR_OUTS, KVLink, ServeParams
 from ..models.llama import LlamaShard
+from ..utils.timing import device_sync, timing_event
 
 MAX_BATCH = 20
 _LINE = re.compile(r"ts:\s*([0-9.eE+-]+)\s+prompt:\s*(\d+)\s+shared:\s*(\d+)\s+out:\s*(\d+)")
@@ -138,7 +139,7 @@ class OnlinePrefill:
         use = self.batches // len(self.links)
         heap = link.heap
         C = link.C
-        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0, e1, e2 = (timing_event(self.dev) for _ in range(3))
         e0.record()
         # prefill computes on the padded batch; the last real position of each request gives its first token
         last_pos = torch.tensor([l - 1 for l in lens], dtype=torch.long, device=self.dev)
@@ -156,7 +157,7 @@ class OnlinePrefill:
         link.send_layers(self.dst, self.k_pool, self.v_pool, B * cb, src_bt, dst_bt, torch.zeros_like(nblocks), 0, 1, hdr=hdr,
                          final=True, num_ctas=1)
         e2.record()
-        torch.cuda.synchronize()
+        device_sync(self.dev)
         kv_bytes = int(nblocks.sum().item()) * m.layers * link.page_elems * 2 * p.elem_bytes
         st = BatchStats(B, sum(lens), kv_bytes, HDR_INTS * 8, e1.elapsed_time(e2), e0.elapsed_time(e1))
         self.stats.append(st)
@@ -185,7 +186,7 @@ class OnlinePrefill:
         one = torch.zeros(1, 1, dtype=torch.int32, device=self.dev)
         link.send_layers(self.dst, self.k_pool, self.v_pool, 1, one, one, torch.zeros(1, dtype=torch.int32, device=self.dev), 0, 1,
                          hdr=hdr, final=True, num_ctas=1)
-        torch.cuda.synchronize()
+        device_sync(self.dev)
         self.batches += 1
 
 
@@ -207,7 +208,7 @@ class OnlineDecode:
         heap = link.heap
         link.seq += 1
         link.wait_final()
-        torch.cuda.synchronize()
+        device_sync(link.k_pool.local.device)
         heap.check_status("online decode wait")
         hdr = link.hdr.local.cpu()
         B, S, mb = int(hdr[0]), int(hdr[1]), int(hdr[2])
@@ -229,7 +230,7 @@ class OnlineDecode:
                 tokens = self.model.decode_step(tokens, pos, link.k_pool.local, link.v_pool.local, bt, link.pool_blocks)
                 pos = pos + 1
                 gen.append(tokens)
-        torch.cuda.synchronize()
+        device_sync(dev)
         # give the pool back: credit word on the SENDER's pad counts batches finished on this pool
         self.done_on[i] += 1
         link.C.put_chunks([(self.credit_pad.addr(), self.credit_pad.addr(self.src), 16,

@@ -8,6 +8,27 @@ from typing import Dict, List
 import torch
 
 
+class _HostEvent:
+    """Stand-in with the two methods of a CUDA timing event that the serving code uses, on the host clock."""
+
+    def record(self):
+        import time
+        self.t = time.perf_counter()
+
+    def elapsed_time(self, other: "_HostEvent") -> float:
+        return (other.t - self.t) * 1e3
+
+
+def timing_event(device):
+    """A CUDA timing event for a CUDA device; on the CPU (tests that model the kernels) the host clock."""
+    return torch.cuda.Event(enable_timing=True) if torch.device(device).type == "cuda" else _HostEvent()
+
+
+def device_sync(device) -> None:
+    if torch.device(device).type == "cuda":
+        torch.cuda.synchronize()
+
+
 class CudaTimer:
     """Named sections timed with CUDA events on the current stream; totals are read after a synchronize."""
 

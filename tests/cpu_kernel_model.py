@@ -1,7 +1,7 @@
 """A functional model, in plain PyTorch on host memory, of the device entry points the fused paths call: the MoE step
 (`moe_dispatch`, `moe_zero_tail`, `grouped_gemm` with its five epilogues, `moe_combine`, `moe_combine_dw`, the fp8 quantisers
-and the block-scaled fp8 grouped GEMM), the DLRM step (`embbag` forward and backward) and the transfers (`put_chunks`,
-`all_to_all`, `wait_flags`, `barrier`).
+and the block-scaled fp8 grouped GEMM), the DLRM step (`embbag` forward and backward), the KV hand-off of serving
+(`kv_pack_send`) and the transfers (`put_chunks`, `all_to_all`, `wait_flags`, `barrier`).
 
 It takes the same arguments as the bindings of the real extension, raw addresses of peers' buffers included, and does to
 the memory behind them what the kernels are specified to do.  With it the Python side of the fused paths -- buffer sizes,
@@ -110,6 +110,36 @@ class Model:
         self.put_chunks(segs, chunk_bytes, 0, use_bulk, num_ctas, threads, status_addr)
         for r, w in enumerate(want):
             self._wait_ge(pads[rank] + 4 * (slot0 + r), w, status_addr, 600 + r)
+
+    # ---------------------------------------------------------------------------------------- KV pack + send
+    def kv_pack_send(self, src_k, src_v, dst_k, dst_v, src_layout, dst_layout, src_blocks, dst_blocks, L, H, S, D, l0, l1,
+                     src_bt, dst_bt, nblocks, hdr, hdr_dst, done_flag, seq, cta_counter, num_ctas, status_addr):
+        """Pages named by the block tables go from the local pools into the peer's, layers [l0, l1), with the change of
+        layout (0 = [block][layer][head][slot][dim], 1 = [layer][block][slot][head][dim]; elements of 2 bytes); then the
+        header, then the flag."""
+        def pool(t_or_addr, nblk, layout):
+            n = nblk * L * H * S * D                                  # the pool may be larger than the pages this call names
+            flat = t_or_addr.view(torch.int16).view(-1)[:n] if torch.is_tensor(t_or_addr) else self._view(t_or_addr, [n], torch.int16)
+            return flat.view(nblk, L, H, S, D) if layout == 0 else flat.view(L, nblk, S, H, D)
+
+        def page(p, layout, blk, layer):                         # always as [head][slot][dim]
+            return p[blk, layer] if layout == 0 else p[layer, blk].transpose(0, 1)
+
+        for src, dst in ((src_k, dst_k), (src_v, dst_v)):
+            sp, dp = pool(src, src_blocks, src_layout), pool(dst, dst_blocks, dst_layout)
+            for b in range(src_bt.shape[0]):
+                for j in range(int(nblocks[b])):
+                    sb, db = int(src_bt[b, j]), int(dst_bt[b, j])
+                    if not (0 <= sb < src_blocks and 0 <= db < dst_blocks):
+                        self._status(status_addr, 6, 1000)
+                        continue
+                    for layer in range(l0, l1):
+                        page(dp, dst_layout, db, layer).copy_(page(sp, src_layout, sb, layer))
+        if hdr is not None and hdr_dst:
+            raw = hdr.contiguous().view(torch.uint8).view(-1)
+            self._view(hdr_dst, [raw.numel()], torch.uint8).copy_(raw)
+        if done_flag:
+            self._flag(done_flag)[0] = int(seq)
 
     # ---------------------------------------------------------------------------------------- embedding bag + all-to-all
     def embbag(self, backward, weights, indices, t_first, t_total, b_local, peers, lr, num_ctas, status_addr):
@@ -294,7 +324,8 @@ def installed(single_process=True, lock_path=None):
     model.lock_path = lock_path
     from fuselink_b200.models import dlrm
     from fuselink_b200.ops import fp8
-    saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8, dlrm)]
+    from fuselink_b200.serving import disagg
+    saved = [(m, m.require_native) for m in (comm, gemm, moe, fp8, dlrm, disagg)]
     for m, _ in saved:
         m.require_native = lambda model=model: model
     try:

@@ -258,3 +258,20 @@ def test_striped_transfer_over_relays_between_processes(tmp_path):
            "--master-port", str(port), os.path.join(here, "mp_relay_cpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.stdout.count("RELAY-MP-OK") == 4, out.stdout[-2000:] + out.stderr[-4000:]
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+def test_online_serving_between_processes(dtype):
+    """Trace -> scheduler -> prefill on one process, decode on another: paged KV, header, flags and pool credits over the
+    shared heap (two pools used in turn, the end-of-trace header last); every generated token checked against the dense
+    model.  fp32 also covers pools of 4-byte elements, which the KV entry point moves as heads twice as wide."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(here, "mp_online_cpu_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, FL_ONLINE_DTYPE=dtype))
+    assert out.stdout.count("ONLINE-MP-OK") == 2, out.stdout[-2000:] + out.stderr[-4000:]
