@@ -30,6 +30,8 @@ def main():
     ap.add_argument("--input-len", type=int, default=512)
     ap.add_argument("--decode-steps", type=int, default=8)
     ap.add_argument("--decode-sleep-ms", type=float, default=0.0, help="stand-in for decoding, 25 in the reference")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"], help="cpu: host tensors and a host-memory heap (only under a model of "
+                                                                              "the device entry points, as the tests run it)")
     ap.add_argument("--policy", default="fcfs", choices=["fcfs", "sjf", "aged"], help="order in which waiting requests are batched (fcfs: the reference)")
     ap.add_argument("--max-batch-tokens", type=int, default=0, help="limit on the active prompt tokens of one batch (0: none)")
     args = ap.parse_args()
@@ -48,7 +50,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
         return multi_process(args, cfg, p, reqs)
-    net = LlamaShard(cfg, device="cuda", max_positions=args.input_len + args.decode_steps)
+    net = LlamaShard(cfg, device=args.device, max_positions=args.input_len + args.decode_steps)
     pool = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
     heaps = SymmetricHeap.emulated(2, 2 * pool + (64 << 20))
     links = [[KVLink(h, p, net.kvh_local, name=f"kv{i}") for i in range(2)] for h in heaps]
@@ -83,9 +85,14 @@ def multi_process(args, cfg, p, reqs):
     from fuselink_b200.serving.online import MAX_BATCH, OnlineDecode, OnlinePrefill, TraceReader
     rank, local, world = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ["WORLD_SIZE"])
     assert world % 2 == 0, "half of the ranks prefill, half decode"
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist.init_process_group("nccl", device_id=dev)
+    cpu = args.device == "cpu"
+    if cpu:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+    else:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        dist.init_process_group("nccl", device_id=dev)
     tp = world // 2
     is_prefill = rank < tp
     groups = [dist.new_group(list(range(0, tp))), dist.new_group(list(range(tp, world)))]
@@ -93,7 +100,7 @@ def multi_process(args, cfg, p, reqs):
     p = ServeParams(cfg, MAX_BATCH, args.input_len, args.decode_steps, tp)
     net = LlamaShard(cfg, rank % tp, tp, group if tp > 1 else None, device=dev, max_positions=args.input_len + args.decode_steps)
     pool = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * 2
-    heap = SymmetricHeap.create(2 * pool + (64 << 20), device=local)
+    heap = SymmetricHeap.create(2 * pool + (64 << 20), device=-1 if cpu else local)
     links = [KVLink(heap, p, net.kvh_local, name=f"kv{i}") for i in range(2)]
     peer = rank + tp if is_prefill else rank - tp
     served = 0
@@ -137,7 +144,8 @@ def multi_process(args, cfg, p, reqs):
     wd = threading.Timer(60.0, lambda: os._exit(0))      # the report is out: never hang in teardown
     wd.daemon = True
     wd.start()
-    torch.cuda.synchronize()
+    if not cpu:
+        torch.cuda.synchronize()
     dist.barrier()
     heap.close()
     dist.destroy_process_group()

@@ -275,3 +275,33 @@ def test_online_serving_between_processes(dtype):
            "--master-port", str(port), os.path.join(here, "mp_online_cpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, FL_ONLINE_DTYPE=dtype))
     assert out.stdout.count("ONLINE-MP-OK") == 2, out.stdout[-2000:] + out.stderr[-4000:]
+
+
+def _run_script_on_model(script, args, nproc=1, env=None, timeout=600):
+    import os
+    import socket
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    root = os.path.dirname(here)
+    cmd = [os.path.join(here, "run_with_kernel_model.py"), os.path.join(root, script), *args]
+    if nproc > 1:
+        s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+        cmd = ["-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1", "--master-port", str(port)] + cmd
+    out = subprocess.run([sys.executable, *cmd], capture_output=True, text=True, timeout=timeout, env=dict(os.environ, **(env or {})))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    import json
+    return [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
+
+
+@pytest.mark.parametrize("nproc", [1, 4])
+def test_online_serving_experiment_script_end_to_end(nproc):
+    """experiments/run_online_serving.py itself: one process with both stages on an emulated heap, and four processes --
+    two tensor-parallel prefill ranks, two decode ranks, the batches shared inside the prefill group."""
+    rows = _run_script_on_model("experiments/run_online_serving.py", ["--device", "cpu", "--model", "tiny", "--requests", "12", "--rate", "300",
+                                                                      "--input-len", "96", "--decode-steps", "2", "--policy", "sjf"], nproc=nproc)
+    served = [r for r in rows if "served" in r]
+    assert served and served[0]["served"] == 12
+    assert sum(r["batch"] for r in rows if "batch" in r and "prompt_tokens" in r) == 12
+    if nproc > 1:
+        assert [r for r in rows if "decoded_requests" in r][0]["decoded_requests"] == 12
