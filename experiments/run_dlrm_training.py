@@ -33,6 +33,8 @@ def main():
     ap.add_argument("--log-every", type=int, default=10)
     ap.add_argument("--data-seeds", type=int, default=8, help="distinct synthetic batches, visited round robin")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"])
+    ap.add_argument("--host-heap", action="store_true", help="with --device cpu: build the symmetric heap in host memory and take the fused path "
+                                                             "(only under a model of the device entry points, as the tests run it)")
     ap.add_argument("--checkpoint", default="")
     ap.add_argument("--resume", default="")
     a = ap.parse_args()
@@ -50,9 +52,10 @@ def main():
         dev = torch.device("cuda", local)
         if world > 1:
             dist.init_process_group("nccl", device_id=dev)
+    if not cpu or a.host_heap:
         from fuselink_b200.parallel.symm import SymmetricHeap
         bl = cfg.global_batch // world
-        heap = SymmetricHeap.create(2 * bl * cfg.num_tables * cfg.dim * 4 + (16 << 20), device=local)
+        heap = SymmetricHeap.create(2 * bl * cfg.num_tables * cfg.dim * 4 + (16 << 20), device=-1 if cpu else local)
     model = DLRM(cfg, heap, rank, world, device=dev)
     opt = torch.optim.SGD(model.dense_parameters(), lr=cfg.lr)
     start = 0

@@ -38,6 +38,8 @@ def main():
     ap.add_argument("--reshadow-every", type=int, default=0, help="with --shadow: every K steps choose the shadowed experts of each layer "
                                                                   "again from the loads of the last batch")
     ap.add_argument("--reshadow-tolerance", type=float, default=0.15, help="copy slots stay empty once the busiest rank is within (1 + this) of the mean load")
+    ap.add_argument("--host-heap", action="store_true", help="with --device cpu: build the symmetric heap in host memory and take the fused path "
+                                                             "(only under a model of the device entry points, as the tests run it)")
     ap.add_argument("--checkpoint", default="", help="save the last state here (per rank: experts differ)")
     ap.add_argument("--resume", default="", help="load <path>.rank<r> written by --checkpoint (same world size) before training")
     a = ap.parse_args()
@@ -59,15 +61,17 @@ def main():
         dev = torch.device("cuda", local)
         if world > 1:
             dist.init_process_group("nccl", device_id=dev)
+    fused = not cpu or a.host_heap
+    if fused:
         from fuselink_b200.parallel.symm import SymmetricHeap
         T, k, H, F, E = a.batch * a.seq, cfg.topk, cfg.hidden, cfg.ffn, cfg.num_experts
         rows = (E // world + (a.shadow if world > 1 else 0)) * ((T * world + 127) // 128 * 128)
         per_layer = rows * H * 2 * 2 + 2 * T * k * H * 2 + rows * 4 + (1 << 20)        # the symmetric buffers of one MoE workspace
-        heap = SymmetricHeap.create(cfg.layers * per_layer + (64 << 20), device=local)
-    net = MoETransformer(cfg, a.batch * a.seq, heap, rank, world, device=dev, seed=0, fused_sgd_lr=0.0 if cpu else a.lr)
+        heap = SymmetricHeap.create(cfg.layers * per_layer + (64 << 20), device=-1 if cpu else local)
+    net = MoETransformer(cfg, a.batch * a.seq, heap, rank, world, device=dev, seed=0, fused_sgd_lr=a.lr if fused else 0.0)
     if a.resume:
         net.load_state_dict(torch.load(f"{a.resume}.rank{rank}", map_location=dev))
-    params = net.parameters() if cpu else net.dense_parameters()       # on CUDA the expert update is fused into the wgrad GEMM
+    params = net.dense_parameters() if fused else net.parameters()     # on the fused path the expert update is part of the wgrad GEMM
     opt = torch.optim.SGD(params, lr=a.lr)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
     t_mark, tok = time.perf_counter(), 0

@@ -305,3 +305,29 @@ def test_online_serving_experiment_script_end_to_end(nproc):
     assert sum(r["batch"] for r in rows if "batch" in r and "prompt_tokens" in r) == 12
     if nproc > 1:
         assert [r for r in rows if "decoded_requests" in r][0]["decoded_requests"] == 12
+
+
+def test_moe_training_script_on_the_fused_path_between_processes(tmp_path):
+    """experiments/run_moe_training.py itself, two processes, fused path on a host-memory heap: a shadowed expert per layer
+    chosen again every step, the experts' update fused into the modelled wgrad, checkpoint and resume."""
+    ck = str(tmp_path / "ck")
+    env = {"FL_MODEL_LOCK": str(tmp_path / "atomic.lock")}
+    base = ["--model", "tiny_moe", "--device", "cpu", "--host-heap", "--batch", "2", "--seq", "16", "--lr", "0.2", "--log-every", "1",
+            "--shadow", "1", "--reshadow-every", "1"]
+    rows = _run_script_on_model("experiments/run_moe_training.py", base + ["--steps", "3", "--checkpoint", ck], nproc=2, env=env)
+    assert [r["step"] for r in rows] == [1, 2, 3] and all(r["n_gpus"] == 2 and 0 < r["loss"] < 20 for r in rows)
+    import os
+    assert os.path.exists(ck + ".rank0") and os.path.exists(ck + ".rank1")
+    more = _run_script_on_model("experiments/run_moe_training.py", base + ["--steps", "1", "--resume", ck], nproc=2, env=env)
+    fresh = _run_script_on_model("experiments/run_moe_training.py", base + ["--steps", "1"], nproc=2, env=env)
+    assert fresh[0]["loss"] == rows[0]["loss"] and more[0]["loss"] != fresh[0]["loss"]      # the resumed run starts from trained weights
+
+
+def test_dlrm_training_script_on_the_fused_path_between_processes():
+    """experiments/run_dlrm_training.py, three processes (uneven table split), fused path on a host-memory heap: the losses
+    are the ones of the plain path from the same seed."""
+    args = ["--device", "cpu", "--tables", "5", "--rows", "300", "--global-batch", "96", "--pooling", "4", "--lr", "0.3", "--steps", "4", "--log-every", "1"]
+    fused = _run_script_on_model("experiments/run_dlrm_training.py", args + ["--host-heap"], nproc=3)
+    plain = _run_script_on_model("experiments/run_dlrm_training.py", args, nproc=3)
+    assert [r["step"] for r in fused] == [1, 2, 3, 4]
+    assert [r["loss"] for r in fused] == pytest.approx([r["loss"] for r in plain], abs=2e-5)
