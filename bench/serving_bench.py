@@ -32,14 +32,25 @@ def main():
     ap.add_argument("--model-path", default="dummy", help="'dummy' = random weights, else a Hugging Face state_dict file or directory")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--emulate", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"], help="cpu: host tensors and a host-memory heap (only under a model of "
+                                                                              "the device entry points, as the tests run it)")
     args = ap.parse_args()
     from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard, load_checkpoint_file
     from fuselink_b200.parallel.symm import SymmetricHeap
     from fuselink_b200.serving.disagg import DecodeStage, KVLink, PrefillStage, ServeParams, make_prompts
 
     rank = int(os.environ.get("RANK", 0)); local = int(os.environ.get("LOCAL_RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    cpu = args.device == "cpu"
+    if cpu:
+        dev, heap_dev = torch.device("cpu"), -1
+    else:
+        torch.cuda.set_device(local)
+        dev, heap_dev = torch.device("cuda", local), local
+
+    def sync():
+        if not cpu:
+            torch.cuda.synchronize()
+
     cfg = MODEL_ZOO[args.model]
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.precision]
     if args.emulate or world == 1:
@@ -48,14 +59,14 @@ def main():
         if args.model_path != "dummy":
             net.load_hf_state_dict(load_checkpoint_file(args.model_path))
         pool_bytes = 2 * p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim * p.elem_bytes
-        heaps = SymmetricHeap.emulated(2, pool_bytes + (64 << 20), device=local)
+        heaps = SymmetricHeap.emulated(2, pool_bytes + (64 << 20), device=max(heap_dev, 0))
         links = [KVLink(h, p, net.kvh_local) for h in heaps]
         pre = PrefillStage(p, net, links[0], 1, pipeline_layers=args.kv == "fuselink")
         dec = DecodeStage(p, net, links[1])
         prompts = make_prompts(p, dev)
         res = []
         for _ in range(args.iters):
-            torch.cuda.synchronize(); t0 = time.monotonic()
+            sync(); t0 = time.monotonic()
             rp = pre.run(prompts); rd = dec.run()
             res.append((rd.extra["t_first_token"] - t0, rp, rd))
         ttft, rp, rd = res[-1]
@@ -63,7 +74,11 @@ def main():
                           "kv_ms": rp.kv_ms, "kv_GB": rp.kv_bytes / 1e9, "decode_tok_s": rd.tokens / (rd.compute_ms / 1e3)}))
         return
     assert world % 2 == 0
-    dist.init_process_group("nccl", device_id=dev)
+    if cpu:
+        assert args.kv != "nccl", "the NCCL arm needs GPUs"
+        dist.init_process_group("gloo")
+    else:
+        dist.init_process_group("nccl", device_id=dev)
     tp = world // 2
     is_prefill = rank < tp
     groups = [dist.new_group(list(range(0, tp))), dist.new_group(list(range(tp, world)))]
@@ -74,7 +89,7 @@ def main():
     if args.model_path != "dummy":
         net.load_hf_state_dict(load_checkpoint_file(args.model_path))      # every shard cuts its part out of the full checkpoint
     pool_elems = p.batch_size * p.max_blocks_per_req * cfg.layers * net.kvh_local * cfg.block_size * cfg.head_dim
-    heap = SymmetricHeap.create(2 * pool_elems * p.elem_bytes + (64 << 20), device=local)
+    heap = SymmetricHeap.create(2 * pool_elems * p.elem_bytes + (64 << 20), device=heap_dev)
     link = KVLink(heap, p, net.kvh_local)
     peer = rank + tp if is_prefill else rank - tp            # the reference's pairing: rank <-> rank + world/2
     prompts = make_prompts(p, dev)
@@ -82,7 +97,7 @@ def main():
     dec = DecodeStage(p, net, link, use_graph=True) if not is_prefill else None
     out = None
     for it in range(args.iters):
-        dist.barrier(); torch.cuda.synchronize()
+        dist.barrier(); sync()
         t0 = time.monotonic()
         if args.kv == "nccl":
             out = _nccl_iteration(p, net, link, pre, dec, prompts, peer, is_prefill, t0)
@@ -113,7 +128,7 @@ def main():
     if dec is not None:
         dec.graph = None
         dec.g_out = None
-    torch.cuda.synchronize()
+    sync()
     dist.barrier()
     heap.close()
     dist.destroy_process_group()

@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--tp_size", type=int, default=0, help="0: world/2")
     ap.add_argument("--tracepath", default="")
     ap.add_argument("--kv", default="fuselink", choices=["fuselink", "fuselink-nopipe", "nccl"])
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"], help="cpu: only under a model of the device entry points (tests)")
     a = ap.parse_args()
     from fuselink_b200.models.llama import MODEL_ZOO
 
@@ -41,11 +42,11 @@ def main():
         raise SystemExit(f"--tp_size {a.tp_size} needs {2 * a.tp_size} ranks (got {world})")
     if a.tracepath:
         sys.argv = ["run_online_serving.py", "--trace", a.tracepath, "--model", a.model_name, "--input-len", str(a.input_len),
-                    "--decode-steps", str(a.num_decoding_step)]
+                    "--decode-steps", str(a.num_decoding_step), "--device", a.device]
         runpy.run_path(os.path.join(root, "experiments", "run_online_serving.py"), run_name="__main__")
     else:
         sys.argv = ["serving_bench.py", "--model", a.model_name, "--kv", a.kv, "--batch", str(a.batch_size), "--input-len",
-                    str(a.input_len), "--decode-steps", str(a.num_decoding_step), "--model-path", a.model_path, "--precision", a.precision] + (["--emulate"] if world == 1 else [])
+                    str(a.input_len), "--decode-steps", str(a.num_decoding_step), "--model-path", a.model_path, "--precision", a.precision, "--device", a.device] + (["--emulate"] if world == 1 else [])
         runpy.run_path(os.path.join(root, "bench", "serving_bench.py"), run_name="__main__")
 
 

@@ -25,6 +25,7 @@ import torch
 from .._ext import require_native
 from ..models.llama import KV_BLHSD, KV_LBSHD, LlamaConfig, LlamaShard
 from ..parallel.symm import SymmetricHeap
+from ..utils.timing import device_sync, timing_event
 
 HDR_MAX_BATCH = 32
 HDR_TOKENS, HDR_LENS, HDR_OUTS = 4, 4 + HDR_MAX_BATCH, 4 + 2 * HDR_MAX_BATCH
@@ -133,24 +134,31 @@ class PrefillStage:
         self.dst_bt = (torch.arange(B, dtype=torch.int32, device=dev).unsqueeze(1) * mb +
                        torch.arange(cb, dtype=torch.int32, device=dev).unsqueeze(0)).contiguous()
         self.nblocks = torch.full((B,), cb, dtype=torch.int32, device=dev)
-        self.side = torch.cuda.Stream(device=dev)
+        # the KV hand-off runs on a side stream beside the prefill; on host tensors (tests that model the kernels) in line
+        self.side = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        self.dev = dev
         self.hdr = torch.zeros(HDR_INTS, dtype=torch.int64, device=dev)
 
     def run(self, tokens: torch.Tensor) -> StageReport:
         p, link = self.p, self.link
         link.seq += 1
-        main = torch.cuda.current_stream()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cuda = self.side is not None
+        main = torch.cuda.current_stream() if cuda else None
+        e0, e1, k0, k1 = (timing_event(self.dev) for _ in range(4))
         first_kv = [True]
+
+        def after_main():
+            """The side stream continues from what the main stream has enqueued so far."""
+            if cuda:
+                ev = torch.cuda.Event()
+                ev.record(main)
+                self.side.wait_event(ev)
 
         def on_layer(l: int):
             if not self.pipeline:
                 return
-            ev = torch.cuda.Event()
-            ev.record(main)
             with torch.cuda.stream(self.side):
-                self.side.wait_event(ev)
+                after_main()
                 if first_kv[0]:
                     k0.record(self.side)
                     first_kv[0] = False
@@ -161,10 +169,8 @@ class PrefillStage:
         e1.record(main)
         self.hdr[0], self.hdr[1], self.hdr[2] = p.batch_size, p.input_len, p.max_blocks_per_req
         self.hdr[4:4 + p.batch_size] = first
-        ev = torch.cuda.Event()
-        ev.record(main)
         with torch.cuda.stream(self.side):
-            self.side.wait_event(ev)
+            after_main()
             if not self.pipeline:
                 k0.record(self.side)
                 link.send_layers(self.dst, self.k_pool, self.v_pool, self.ctx_blocks, self.src_bt, self.dst_bt, self.nblocks, 0,
@@ -173,8 +179,9 @@ class PrefillStage:
             link.send_layers(self.dst, self.k_pool, self.v_pool, self.ctx_blocks, self.src_bt, self.dst_bt,
                              torch.zeros_like(self.nblocks), 0, 1, hdr=self.hdr, final=True, num_ctas=1)
             k1.record(self.side)
-        main.wait_stream(self.side)
-        torch.cuda.synchronize()
+        if cuda:
+            main.wait_stream(self.side)
+        device_sync(self.dev)
         kv_bytes = 2 * self.ctx_blocks * p.model.layers * link.page_elems * p.elem_bytes
         return StageReport("prefill", elapsed_ms=e0.elapsed_time(k1), compute_ms=e0.elapsed_time(e1), kv_ms=k0.elapsed_time(k1),
                            kv_bytes=kv_bytes, tokens=p.batch_size * p.input_len)
@@ -190,7 +197,8 @@ class DecodeStage:
         B, mb = p.batch_size, p.max_blocks_per_req
         self.bt = (torch.arange(B, dtype=torch.int32, device=dev).unsqueeze(1) * mb +
                    torch.arange(mb, dtype=torch.int32, device=dev).unsqueeze(0)).contiguous()
-        self.use_graph = use_graph
+        self.dev = dev
+        self.use_graph = use_graph and dev.type == "cuda"
         self.graph = None
         self.g_tokens = torch.zeros(B, dtype=torch.long, device=dev)
         self.g_pos = torch.zeros(B, dtype=torch.long, device=dev)
@@ -223,7 +231,7 @@ class DecodeStage:
         """Generate num_decoding_step tokens after `tokens` ([B] first tokens).  Returns (generated [B, 1+steps],
         device ms of the loop)."""
         p = self.p
-        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0, d1 = timing_event(self.dev), timing_event(self.dev)
         out = [tokens]
         pos = torch.full((p.batch_size,), p.input_len, dtype=torch.long, device=tokens.device)
         if self.use_graph and self.graph is None:
@@ -242,18 +250,18 @@ class DecodeStage:
             out.append(tokens)
             pos = pos + 1
         d1.record()
-        torch.cuda.synchronize()
+        device_sync(self.dev)
         return torch.stack(out, 1), d0.elapsed_time(d1)
 
     def run(self) -> StageReport:
         p, link = self.p, self.link
         link.seq += 1
-        w0, w1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0, w1 = timing_event(self.dev), timing_event(self.dev)
         w0.record()
         link.wait_final()                       # header + every layer's pages have landed
         w1.record()
         tokens = link.hdr.local[4:4 + p.batch_size].clone()
-        torch.cuda.synchronize()
+        device_sync(self.dev)
         t_first = time.monotonic()              # first token is on the decode side: time-to-first-token ends here
         gen, ms = self.decode(tokens)
         rep = StageReport("decode", elapsed_ms=w0.elapsed_time(w1) + ms, compute_ms=ms, kv_ms=w0.elapsed_time(w1),

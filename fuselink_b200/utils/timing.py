@@ -11,7 +11,7 @@ import torch
 class _HostEvent:
     """Stand-in with the two methods of a CUDA timing event that the serving code uses, on the host clock."""
 
-    def record(self):
+    def record(self, stream=None):
         import time
         self.t = time.perf_counter()
 

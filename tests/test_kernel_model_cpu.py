@@ -331,3 +331,62 @@ def test_dlrm_training_script_on_the_fused_path_between_processes():
     plain = _run_script_on_model("experiments/run_dlrm_training.py", args, nproc=3)
     assert [r["step"] for r in fused] == [1, 2, 3, 4]
     assert [r["loss"] for r in fused] == pytest.approx([r["loss"] for r in plain], abs=2e-5)
+
+
+@pytest.mark.parametrize("pipeline", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_offline_prefill_to_decode_on_the_model(pipeline, dtype):
+    """The offline experiment's two stages as virtual ranks of one process: prefill with the per-layer (or one-shot) KV
+    hand-off, then paged greedy decoding on the other side, against the dense model token by token."""
+    import cpu_kernel_model
+    from fuselink_b200.models.llama import MODEL_ZOO, LlamaShard
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    from fuselink_b200.serving.disagg import DecodeStage, KVLink, PrefillStage, ServeParams, make_prompts
+    p = ServeParams(model=MODEL_ZOO["tiny"], batch_size=3, input_len=64, num_decoding_step=4, dtype=dtype)
+    heaps = SymmetricHeap.emulated(2, 32 << 20)
+    try:
+        with cpu_kernel_model.installed():
+            net = LlamaShard(p.model, device="cpu", seed=1, dtype=dtype)
+            links = [KVLink(h, p, net.kvh_local) for h in heaps]
+            pre = PrefillStage(p, net, links[0], dst_rank=1, pipeline_layers=pipeline)
+            dec = DecodeStage(p, net, links[1])
+            prompts = make_prompts(p, "cpu", seed=3)
+            rp = pre.run(prompts)
+            rd = dec.run()
+            for h in heaps:
+                h.check_status()
+        gen = rd.extra["generated"]
+        assert gen.shape == (p.batch_size, 1 + p.num_decoding_step) and rd.extra["graph"] is False
+        seq, agree = prompts.clone(), 0
+        for t in range(1 + p.num_decoding_step):
+            agree += int((net.forward_dense(seq).argmax(-1) == gen[:, t]).sum())
+            seq = torch.cat([seq, gen[:, t:t + 1]], 1)
+        total = p.batch_size * (1 + p.num_decoding_step)
+        assert agree == total if dtype == torch.float32 else agree >= 0.8 * total
+        assert rp.kv_bytes == 2 * p.batch_size * p.context_blocks_per_req * p.model.layers * links[0].page_elems * p.elem_bytes
+        assert rd.tokens == p.batch_size * p.num_decoding_step
+    finally:
+        for h in heaps:
+            h.close()
+
+
+@pytest.mark.parametrize("nproc", [1, 4])
+def test_serving_command_line_end_to_end(nproc):
+    """`python -m fuselink_b200.serving` with the reference's flags (experiments/serving/main.cc:45-107): both stages on an
+    emulated heap in one process, and 2 + 2 tensor-parallel ranks as four processes; fp32 pools."""
+    rows = _run_script_on_model("fuselink_b200/serving/__main__.py",
+                                ["--model_name", "tiny_opt", "--model_path", "dummy", "--precision", "fp32", "--input_len", "64", "--batch_size", "2",
+                                 "--block_size", "16", "--num_decoding_step", "3", "--device", "cpu"], nproc=nproc)
+    r = rows[-1]
+    assert r["ttft_ms"] > 0 and r["decode_tok_s"] > 0 and r["prefill_ms"] > 0
+    if nproc > 1:
+        assert r["tp"] == 2 and r["n_gpus"] == 4 and 0 < r["comm_over_elapsed"] <= 1.0
+
+
+def test_serving_command_line_replays_a_trace(tmp_path):
+    from fuselink_b200.serving.tracegen import generate
+    trace = tmp_path / "trace.txt"
+    trace.write_text("\n".join(generate(requests=9, rate=500.0, prompt_min=16, prompt_max=60, seed=1)) + "\n")
+    rows = _run_script_on_model("fuselink_b200/serving/__main__.py",
+                                ["--model_name", "tiny", "--input_len", "64", "--num_decoding_step", "2", "--tracepath", str(trace), "--device", "cpu"])
+    assert [r for r in rows if "served" in r][0]["served"] == 9
