@@ -100,6 +100,9 @@ def parse():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--zipf", type=float, default=1.2)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: host tensors and a host-memory heap; only meaningful under a model of the device entry points (the tests run "
+                         "the script that way to check its plumbing) and never a benchmark")
     ap.add_argument("--shadow", type=int, default=0,
                     help="replicate the N experts the router favours most on every rank: their rows are computed where they originate and "
                          "their weight gradients are summed over the ranks (fuselink arm, N GPUs > 1)")
@@ -122,11 +125,20 @@ def main():
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch multi-GPU runs with torch.distributed.run (one rank per GPU)")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    cpu = args.device == "cpu"
+    if cpu:
+        assert args.impl == "fuselink", "the host mode exists for the plumbing of the fuselink arm only"
+        dev = torch.device("cpu")
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("gloo", rank=rank, world_size=world)
+    else:
+        torch.cuda.set_device(local_rank)
+        dev = torch.device("cuda", local_rank)
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from fuselink_b200.utils.timing import timing_event      # a CUDA timing event on a GPU, the host clock in the host mode
 
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops.moe import MoEConfig
@@ -143,7 +155,7 @@ def main():
         shadow = args.shadow if W > 1 else 0
         rows = (cfg.num_experts // W + shadow) * cap
         heap_bytes = 2 * rows * H * 2 + rows * 4 + 2 * T * cfg.topk * H * 2 + (64 << 20)
-        heap = SymmetricHeap.create(heap_bytes, device=local_rank)
+        heap = SymmetricHeap.create(heap_bytes, device=-1 if cpu else local_rank)
         layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr, shadow_experts=shadow)
         expert_params = []          # updated inside the wgrad kernels' epilogue
     else:
@@ -170,7 +182,8 @@ def main():
     def sync_all():
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+        if not cpu:
+            torch.cuda.synchronize()
 
     def launches():
         return layer.ws.launches if getattr(layer, "ws", None) is not None else 0
@@ -187,7 +200,7 @@ def main():
         time.sleep(0.25)
     sync_all()
     l0 = launches()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = timing_event(dev), timing_event(dev)
     t_wall0 = time.time()
     e0.record()
     for i in range(args.steps):
@@ -257,37 +270,46 @@ def main():
     e2e = None
     if not args.no_e2e:
         try:
-            host = [torch.randn(T, H).to(torch.bfloat16).pin_memory() for _ in range(2)]
-            # Input pipeline of the public API: each step's activations are copied from pinned host memory on a copy
-            # stream into one of two device buffers while the previous step computes; the step waits for its own copy.
-            copy_stream = torch.cuda.Stream(device=dev)
-            dbufs = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-            ready = [torch.cuda.Event() for _ in range(2)]
-            consumed = [torch.cuda.Event() for _ in range(2)]
+            host = [torch.randn(T, H).to(torch.bfloat16) for _ in range(2)]
+            if cpu:
+                def run_e2e(n):                                      # host mode: the copies in line, no streams
+                    last, buf = 0.0, torch.empty(T, H, dtype=torch.bfloat16)
+                    for i in range(n):
+                        buf.copy_(host[i % 2])
+                        last = float(step(buf).item())
+                    return last
+            else:
+                host = [h.pin_memory() for h in host]
+                # Input pipeline of the public API: each step's activations are copied from pinned host memory on a copy
+                # stream into one of two device buffers while the previous step computes; the step waits for its own copy.
+                copy_stream = torch.cuda.Stream(device=dev)
+                dbufs = [torch.empty(T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+                ready = [torch.cuda.Event() for _ in range(2)]
+                consumed = [torch.cuda.Event() for _ in range(2)]
 
-            def prefetch(i):
-                b = i % 2
-                with torch.cuda.stream(copy_stream):
-                    copy_stream.wait_event(consumed[b])          # the step that last read this buffer has finished
-                    dbufs[b].copy_(host[i % 2], non_blocking=True)
-                    ready[b].record(copy_stream)
-
-            def run_e2e(n):
-                last = 0.0
-                prefetch(0)
-                for i in range(n):
+                def prefetch(i):
                     b = i % 2
-                    torch.cuda.current_stream().wait_event(ready[b])
-                    if i + 1 < n:
-                        prefetch(i + 1)                          # next step's host -> device copy overlaps this step
-                    loss = step(dbufs[b])
-                    consumed[b].record()
-                    last = float(loss.item())                    # this step's result, device -> host
-                return last
+                    with torch.cuda.stream(copy_stream):
+                        copy_stream.wait_event(consumed[b])          # the step that last read this buffer has finished
+                        dbufs[b].copy_(host[i % 2], non_blocking=True)
+                        ready[b].record(copy_stream)
+
+                def run_e2e(n):
+                    last = 0.0
+                    prefetch(0)
+                    for i in range(n):
+                        b = i % 2
+                        torch.cuda.current_stream().wait_event(ready[b])
+                        if i + 1 < n:
+                            prefetch(i + 1)                          # next step's host -> device copy overlaps this step
+                        loss = step(dbufs[b])
+                        consumed[b].record()
+                        last = float(loss.item())                    # this step's result, device -> host
+                    return last
 
             run_e2e(2)
             sync_all()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0, f1 = timing_event(dev), timing_event(dev)
             f0.record()
             loss_host = run_e2e(args.steps)
             f1.record()
@@ -302,7 +324,8 @@ def main():
         except Exception as e:  # noqa: BLE001 - the device-timed line above must still be reported
             e2e = {"error": repr(e)}
             try:
-                torch.cuda.synchronize()
+                if not cpu:
+                    torch.cuda.synchronize()
             except Exception:  # noqa: BLE001
                 pass
 

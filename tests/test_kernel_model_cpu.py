@@ -390,3 +390,25 @@ def test_serving_command_line_replays_a_trace(tmp_path):
     rows = _run_script_on_model("fuselink_b200/serving/__main__.py",
                                 ["--model_name", "tiny", "--input_len", "64", "--num_decoding_step", "2", "--tracepath", str(trace), "--device", "cpu"])
     assert [r for r in rows if "served" in r][0]["served"] == 9
+
+
+@pytest.mark.parametrize("nproc,extra", [(1, []), (2, ["--shadow", "1"]), (2, ["--dtype", "fp8"])])
+def test_headline_bench_script_plumbing(nproc, extra, tmp_path):
+    """bench.py itself in its host mode under the model (tiny shape; not a measurement): warm-up, timed region, the
+    end-to-end region, roofline block, one JSON line with every key the contract names, clean teardown -- on one process
+    and on two, with a shadowed expert and with the fp8 arm."""
+    rows = _run_script_on_model("bench.py", ["--device", "cpu", "--gpus", str(nproc), "--tokens", "64", "--hidden", "128", "--ffn", "256",
+                                             "--steps", "2", "--warmup", "1", *extra], nproc=nproc, env={"FL_MODEL_LOCK": str(tmp_path / "atomic.lock")})
+    assert len(rows) == 1
+    r = rows[0]
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling", "vs_baseline", "dtype", "data",
+                "config", "clocks", "e2e", "gpu_launches"):
+        assert key in r, key
+    assert r["n_gpus"] == nproc and r["steps"] == 2 and r["warmup"] == 1 and r["value"] > 0 and r["gpu_launches"] > 0
+    assert r["config"]["global_batch"] == 64 * nproc and r["config"]["parallelism"].startswith(f"ep{nproc}")
+    assert "error" not in r["e2e"] and r["e2e"]["value"] > 0 and r["e2e"]["h2d_bytes_per_step"] == 64 * 128 * 2
+    assert "error" not in (r["roofline"] or {}) and r["roofline"]["hot_rank_rows"] >= r["roofline"]["mean_rows"] * (0.5 if extra[:1] == ["--shadow"] else 1.0)
+    if extra[:1] == ["--shadow"]:
+        assert "shadow experts [0]" in r["config"]["parallelism"]
+    if extra[:1] == ["--dtype"]:
+        assert r["dtype"].startswith("fp8")
