@@ -240,6 +240,7 @@ def main():
                        "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
             "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
             "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roof,
+            **({"host_mode": "device entry points modelled on the host: plumbing check, not a measurement"} if cpu else {}),
         }
 
     # The device-timed number exists from here on.  Whatever happens in the end-to-end region (a rank that raises while
