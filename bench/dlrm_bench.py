@@ -27,19 +27,30 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--rows", type=int, default=1_000_000)
     ap.add_argument("--global-batch", type=int, default=65536)
+    ap.add_argument("--tables", type=int, default=26)
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"], help="cpu: plumbing check under a model of the device entry points (tests), "
+                                                                              "never a measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0)); local = int(os.environ.get("LOCAL_RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+    cpu = args.device == "cpu"
+    if cpu:
+        assert args.impl == "fuselink"
+        dev = torch.device("cpu")
+        if world > 1:
+            dist.init_process_group("gloo")
+    else:
+        torch.cuda.set_device(local)
+        dev = torch.device("cuda", local)
+        if world > 1:
+            dist.init_process_group("nccl", device_id=dev)
+    from fuselink_b200.utils.timing import timing_event
     from fuselink_b200.models.dlrm import DLRM, DLRMConfig, synthetic_batch
-    cfg = DLRMConfig(rows=args.rows, global_batch=args.global_batch)
+    cfg = DLRMConfig(num_tables=args.tables, rows=args.rows, global_batch=args.global_batch)
     heap = None
     if args.impl == "fuselink":
         from fuselink_b200.parallel.symm import SymmetricHeap
         bl = cfg.global_batch // world
-        heap = SymmetricHeap.create(2 * bl * cfg.num_tables * cfg.dim * 4 + (16 << 20), device=local)
+        heap = SymmetricHeap.create(2 * bl * cfg.num_tables * cfg.dim * 4 + (16 << 20), device=-1 if cpu else local)
         model = DLRM(cfg, heap, rank, world, device=dev)
         step_fn = model.train_step
     else:
@@ -52,12 +63,13 @@ def main():
     def sync():
         if world > 1:
             dist.barrier()
-        torch.cuda.synchronize()
+        if not cpu:
+            torch.cuda.synchronize()
 
     for i in range(args.warmup):
         step_fn(*batches[i % 4], opt)
     sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = timing_event(dev), timing_event(dev)
     e0.record()
     for i in range(args.steps):
         loss = step_fn(*batches[i % 4], opt)

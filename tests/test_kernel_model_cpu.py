@@ -412,3 +412,11 @@ def test_headline_bench_script_plumbing(nproc, extra, tmp_path):
         assert "shadow experts [0]" in r["config"]["parallelism"]
     if extra[:1] == ["--dtype"]:
         assert r["dtype"].startswith("fp8")
+
+
+@pytest.mark.parametrize("nproc", [1, 2])
+def test_dlrm_bench_script_plumbing(nproc):
+    rows = _run_script_on_model("bench/dlrm_bench.py", ["--device", "cpu", "--tables", "5", "--rows", "300", "--global-batch", "64", "--steps", "2",
+                                                        "--warmup", "1"], nproc=nproc)
+    r = rows[-1]
+    assert r["n_gpus"] == nproc and r["value"] > 0 and 0.3 < r["loss"] < 1.2 and r["gpu_launches_per_step"] > 0
