@@ -420,3 +420,43 @@ def test_dlrm_bench_script_plumbing(nproc):
                                                         "--warmup", "1"], nproc=nproc)
     r = rows[-1]
     assert r["n_gpus"] == nproc and r["value"] > 0 and 0.3 < r["loss"] < 1.2 and r["gpu_launches_per_step"] > 0
+
+
+def test_variable_all_to_all_and_put_many_on_the_model():
+    """ops/comm.py on four emulated ranks: a variable all-to-all with ragged blocks (one launch of up to 8 segments per
+    rank, arrival counters derived from byte counts on both sides), twice, so the running totals are exercised too."""
+    import cpu_kernel_model
+    from fuselink_b200.ops.comm import Channel, all_to_all_v, chunking
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    W = 4
+    heaps = SymmetricHeap.emulated(W, 32 << 20)
+    try:
+        with cpu_kernel_model.installed():
+            chans = [Channel(h, "v", engine="ldst") for h in heaps]
+            cap = 3 << 20
+            recvs = [h.alloc_tensor([W * cap], torch.uint8) for h in heaps]
+            g = torch.Generator().manual_seed(0)
+            for it in range(2):
+                sizes = torch.randint(0, cap, (W, W), generator=g).tolist()          # sizes[r][p]: bytes r sends to p
+                sizes[1][2] = 0                                                       # an empty block
+                sends, offs = [], []
+                for r in range(W):
+                    o, acc = [], 0
+                    for p in range(W):
+                        o.append(acc)
+                        acc += (sizes[r][p] + 15) // 16 * 16
+                    offs.append(o)
+                    sends.append(torch.randint(0, 255, (max(acc, 16),), dtype=torch.uint8, generator=g))
+                for r in range(W):                                                    # every rank's launch, then every rank's wait
+                    all_to_all_v(chans[r], sends[r], offs[r], sizes[r], recvs[r], [r * cap] * W, [sizes[p][r] for p in range(W)], wait=False)
+                for r in range(W):
+                    chans[r].wait()
+                    heaps[r].check_status(f"a2a-v {it}")
+                for r in range(W):
+                    for p in range(W):
+                        n = sizes[p][r]
+                        assert torch.equal(recvs[r].local[p * cap: p * cap + n], sends[p][offs[p][r]: offs[p][r] + n]), (it, r, p)
+            assert chunking(0)[1] == 0 and chunking(100)[1] == 1 and chunking(1 << 30)[0] == 512 * 1024
+    finally:
+        for h in heaps:
+            h.close()
