@@ -6,7 +6,7 @@
 #   make monitor   build/bin/fuselink-monitor
 #   make harness   build/bin/fl_net_harness
 #   make lib       build/lib/libfuselink.so               kernels + cuMem regions + monitor (include/fuselink.h); needs nvcc
-#   make all       everything above;  make clean
+#   make all       everything above;  make clean;  make test (CPU tier of the tests; needs Python)
 CXX      ?= g++
 NVCC     ?= /usr/local/cuda/bin/nvcc
 CUDA_HOME ?= /usr/local/cuda
@@ -26,7 +26,7 @@ CU_SRCS   := $(wildcard $(SRC)/kernels/*.cu)
 CU_OBJS   := $(patsubst $(SRC)/kernels/%.cu,$(OBJ)/%.o,$(CU_SRCS))
 HEADERS   := $(wildcard $(SRC)/*/*.h) $(wildcard $(SRC)/*/*.cuh)
 
-.PHONY: all fl monitor harness lib clean
+.PHONY: all fl monitor harness lib clean test
 all: fl monitor harness lib
 fl: $(BUILD)/lib/libnccl-net-fuselink.so
 monitor: $(BUILD)/bin/fuselink-monitor
@@ -55,6 +55,11 @@ $(BUILD)/bin/fl_net_harness: $(SRC)/net/harness_main.cc | $(BUILD)/bin
 	$(CXX) $(CXXFLAGS) -o $@ $< -ldl -lpthread
 $(BUILD)/lib/libfuselink.so: $(CU_OBJS) $(HOST_OBJS) | $(BUILD)/lib
 	$(CXX) -shared -o $@ $^ -L$(CUDA_HOME)/lib64 -Wl,-rpath,$(CUDA_HOME)/lib64 -lcudart -ldl -lrt -lpthread
+
+# the CPU tier of the tests (the reference declares a `test` target and gives it no rule, Makefile:16)
+test:
+	python -m fuselink_b200.build
+	python -m pytest tests -q -m "not gpu"
 
 clean:
 	rm -rf $(BUILD)
