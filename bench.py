@@ -86,6 +86,39 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "power_w_max": max(power) if power else None}
 
 
+class ResultLine:
+    """Prints the result line exactly once: from the main thread when the run completes, or from a timer when the part of
+    the run that follows the device-timed region (the end-to-end region: a rank may raise there while the others wait in
+    a collective) has not finished within its limit -- the line then carries an error in place of that part, and the
+    process ends with status 0 because the device-timed result is valid."""
+
+    def __init__(self, rank: int, make_line):
+        self.rank, self.make_line = rank, make_line
+        self.lock, self.printed, self.timer = threading.Lock(), False, None
+
+    def emit(self, e2e, roof) -> None:
+        with self.lock:
+            if self.printed:
+                return
+            self.printed = True
+            if self.rank == 0:
+                print(json.dumps(self.make_line(e2e, roof)))
+            sys.stdout.flush()
+
+    def arm(self, limit_s: float) -> None:
+        def give_up():
+            self.emit({"error": "the end-to-end region did not finish within its time limit"}, None)
+            os._exit(0)
+
+        self.timer = threading.Timer(limit_s, give_up)
+        self.timer.daemon = True
+        self.timer.start()
+
+    def disarm(self) -> None:
+        if self.timer is not None:
+            self.timer.cancel()
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -243,29 +276,9 @@ def main():
             **({"host_mode": "device entry points modelled on the host: plumbing check, not a measurement"} if cpu else {}),
         }
 
-    # The device-timed number exists from here on.  Whatever happens in the end-to-end region (a rank that raises while
-    # the others wait in a collective, for instance), the line is printed exactly once: by the main thread, or by this
-    # timer when the region has not finished within its limit, after which the process ends.
-    out_lock = threading.Lock()
-    printed = [False]
-
-    def emit(e2e, roof):
-        with out_lock:
-            if printed[0]:
-                return
-            printed[0] = True
-            if rank == 0:
-                print(json.dumps(make_line(e2e, roof)))
-            sys.stdout.flush()
-
-    def give_up():
-        emit({"error": "the end-to-end region did not finish within its time limit"}, None)
-        os._exit(0)
-
-    limit_s = max(240.0, 40.0 * ms / 1e3)
-    guard = threading.Timer(limit_s, give_up)
-    guard.daemon = True
-    guard.start()
+    # The device-timed number exists from here on: whatever happens next, the line is printed exactly once.
+    result = ResultLine(rank, make_line)
+    result.arm(max(240.0, 40.0 * ms / 1e3))
 
     # ---------------------------------------------------------------- end-to-end region (public API)
     e2e = None
@@ -347,8 +360,8 @@ def main():
     except Exception as e:  # noqa: BLE001 - reporting only
         roof = {"error": repr(e)}
 
-    guard.cancel()
-    emit(e2e, roof)
+    result.disarm()
+    result.emit(e2e, roof)
     # the result is out: teardown must never be able to hang the job (a watchdog ends the process after 60 s)
     sys.stdout.flush()
     wd = threading.Timer(60.0, lambda: os._exit(0))

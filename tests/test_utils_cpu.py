@@ -97,3 +97,28 @@ def test_every_environment_variable_read_by_the_sources_is_documented():
     names = {n for n in names if not n.startswith(("NCCL_PTR_", "NCCL_LOG_", "NCCL_NET_HANDLE", "NCCL_NET_MAX", "NCCL_ALL", "NCCL_INIT", "NCCL_NET_DEVICE"))}
     missing = sorted(names - documented)
     assert not missing, f"not in docs/environment.md: {missing}"
+
+
+def test_bench_result_line_is_printed_once_even_when_the_run_stalls():
+    """bench.py's ResultLine: a second emit prints nothing; an armed timer prints the line with an error in place of the
+    end-to-end part and ends the process with status 0 while the main thread is stuck."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys, time; sys.path.insert(0, %r); import bench\n"
+            "r = bench.ResultLine(0, lambda e2e, roof: {'value': 1.5, 'e2e': e2e, 'roofline': roof})\n"
+            "mode = sys.argv[1]\n"
+            "if mode == 'twice':\n"
+            "    r.arm(30.0); r.disarm(); r.emit({'value': 2}, {'x': 1}); r.emit({'value': 3}, None)\n"
+            "else:\n"
+            "    r.arm(0.3); time.sleep(20); print('never')\n") % root
+    twice = subprocess.run([sys.executable, "-c", code, "twice"], capture_output=True, text=True, timeout=60)
+    assert twice.returncode == 0 and twice.stdout.strip() == '{"value": 1.5, "e2e": {"value": 2}, "roofline": {"x": 1}}'
+    import time
+    t0 = time.time()
+    stuck = subprocess.run([sys.executable, "-c", code, "stuck"], capture_output=True, text=True, timeout=60)
+    assert stuck.returncode == 0 and time.time() - t0 < 10 and "never" not in stuck.stdout
+    import json
+    line = json.loads(stuck.stdout.strip())
+    assert line["value"] == 1.5 and "did not finish" in line["e2e"]["error"] and line["roofline"] is None
