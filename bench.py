@@ -136,6 +136,9 @@ def parse():
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: host tensors and a host-memory heap; only meaningful under a model of the device entry points (the tests run "
                          "the script that way to check its plumbing) and never a benchmark")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="which rank owns which expert (fuselink arm): balanced = evened out by the load the router's bias predicts "
+                         "(no effect with one GPU or one expert per GPU); contiguous = expert e on rank e // (E / N)")
     ap.add_argument("--shadow", type=int, default=0,
                     help="replicate the N experts the router favours most on every rank: their rows are computed where they originate and "
                          "their weight gradients are summed over the ranks (fuselink arm, N GPUs > 1)")
@@ -189,7 +192,8 @@ def main():
         rows = (cfg.num_experts // W + shadow) * cap
         heap_bytes = 2 * rows * H * 2 + rows * 4 + 2 * T * cfg.topk * H * 2 + (64 << 20)
         heap = SymmetricHeap.create(heap_bytes, device=-1 if cpu else local_rank)
-        layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr, shadow_experts=shadow)
+        layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr, shadow_experts=shadow,
+                         placement=args.placement)
         expert_params = []          # updated inside the wgrad kernels' epilogue
     else:
         from fuselink_b200.models.moe_baseline import BaselineMoELayer
@@ -255,6 +259,8 @@ def main():
 
     # ---------------------------------------------------------------- the result line
     shadowed = getattr(getattr(layer, "cfg", None), "shadow", ())
+    placed = getattr(getattr(layer, "cfg", None), "placement", ())
+    placed = list(placed) if placed and list(placed) != list(range(len(placed))) else None
 
     def make_line(e2e, roof):
         flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
@@ -268,7 +274,7 @@ def main():
                        if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else
                        f"MoE-EP layer h{args.hidden} f{args.ffn} e{args.experts} k{args.topk}",
                        "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T,
-                       "parallelism": f"ep{world}" + (f" + shadow experts {list(shadowed)}" if shadowed else ""),
+                       "parallelism": f"ep{world}" + (f", expert homes {placed}" if placed else "") + (f" + shadow experts {list(shadowed)}" if shadowed else ""),
                        "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
                        "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
             "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,

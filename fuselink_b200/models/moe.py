@@ -13,7 +13,7 @@ import torch
 import torch.nn as nn
 
 from ..ops import gemm, ref
-from ..ops.moe import MoEConfig, MoEFunction, MoEWorkspace
+from ..ops.moe import MoEConfig, MoEFunction, MoEWorkspace, balanced_placement, expert_home
 from ..parallel.symm import SymmetricHeap
 
 
@@ -62,9 +62,15 @@ class MoELayer(nn.Module):
     def __init__(self, cfg: MoEConfig, heap: Optional[SymmetricHeap] = None, rank: int = 0, world: int = 1,
                  device="cuda", zipf_s: Optional[float] = 1.2, seed: int = 0, fused_sgd_lr: float = 0.0,
                  name: str = "moe", capacity_factor: float = 0.0, drop_tokens: bool = False, min_capacity: int = 4,
-                 noisy_gate: Optional[str] = None, jitter_eps: float = 1e-2, shadow_experts=0):
+                 noisy_gate: Optional[str] = None, jitter_eps: float = 1e-2, shadow_experts=0, placement=None):
         super().__init__()
         bias = zipf_log_bias(cfg.num_experts, zipf_s) if zipf_s else torch.zeros(cfg.num_experts)
+        # which rank owns which expert: in order by default; "balanced" evens out the rows per rank the router's bias
+        # predicts (the same on every rank, since the bias is); or an explicit tuple of homes
+        if placement == "balanced":
+            placement = balanced_placement(bias.exp().tolist(), world)
+        if placement not in (None, "contiguous") and tuple(placement) != tuple(cfg.placement):
+            cfg = dataclasses.replace(cfg, placement=tuple(int(h) for h in placement))
         if isinstance(shadow_experts, int):
             # the n experts the router favours most (its bias is the same on every rank, so is the choice)
             shadow_experts = torch.argsort(bias, descending=True, stable=True)[:shadow_experts].tolist() if shadow_experts > 0 else []
@@ -86,7 +92,8 @@ class MoELayer(nn.Module):
         # this rank's experts, then its copies of the shadowed experts (ops.moe.slot_table); every expert's init depends on
         # (seed, global expert id), not on the layout, so a copy starts out equal to the owner's expert
         w13, w2 = [], []
-        for e in [rank * self.epr + le for le in range(self.epr)] + list(cfg.shadow):
+        self.local_experts = sorted((e for e in range(E) if self.home(e)[0] == rank), key=lambda e: self.home(e)[1])
+        for e in self.local_experts + list(cfg.shadow):
             ge = torch.Generator().manual_seed(seed * 1000 + 17 + max(e, 0))      # e < 0: an empty copy slot, contents unused
             wg = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
             wu = (torch.randn(F, H, generator=ge) * 0.02).to(torch.bfloat16)
@@ -120,14 +127,18 @@ class MoELayer(nn.Module):
             w = w * keep.to(w.dtype)
         return w, idx.int()
 
+    def home(self, e: int):
+        """(owner rank, local index) of expert e."""
+        return expert_home(self.cfg.num_experts, self.world, self.cfg.placement, e)
+
     @torch.no_grad()
     def sync_shadow_to_real(self) -> None:
         """Copy this rank's copy of every shadowed expert it owns into the expert's own slot (which receives no rows while
         the expert is shadowed and so goes stale): call before exporting the experts or changing the set of shadows."""
         for j, e in enumerate(self.cfg.shadow):
-            if e >= 0 and e // self.epr == self.rank:
-                self.w13[e % self.epr].copy_(self.w13[self.epr + j])
-                self.w2[e % self.epr].copy_(self.w2[self.epr + j])
+            if e >= 0 and self.home(e)[0] == self.rank:
+                self.w13[self.home(e)[1]].copy_(self.w13[self.epr + j])
+                self.w2[self.home(e)[1]].copy_(self.w2[self.epr + j])
 
     @torch.no_grad()
     def set_shadows(self, experts, group=None) -> None:
@@ -144,11 +155,11 @@ class MoELayer(nn.Module):
         for j, e in enumerate(experts):
             if e < 0:
                 continue
-            owner = e // self.epr
+            owner, local = self.home(e)
             for w in (self.w13, self.w2):
                 slot = w[self.epr + j]
                 if owner == self.rank:
-                    slot.copy_(w[e % self.epr])
+                    slot.copy_(w[local])
                 if self.world > 1:
                     import torch.distributed as dist
                     dist.broadcast(slot, src=owner if group is None else dist.get_global_rank(group, owner), group=group)
@@ -173,7 +184,7 @@ class MoELayer(nn.Module):
             import torch.distributed as dist
             dist.all_reduce(load, group=group)
         # with a tolerance: only as many copies as it takes to bring the busiest rank within (1 + tolerance) of the mean
-        chosen = choose_shadows(load, n) if tolerance is None else choose_shadows(load, n, self.world, tolerance)
+        chosen = choose_shadows(load, n) if tolerance is None else choose_shadows(load, n, self.world, tolerance, self.cfg.placement)
         self.set_shadows(chosen, group)
         return chosen
 
@@ -199,8 +210,9 @@ class MoELayer(nn.Module):
         dist.all_gather(xs, x.detach()); dist.all_gather(ws_, w.detach()); dist.all_gather(ids, idx)
         xs[self.rank], ws_[self.rank] = x, w    # keep the autograd edge of the local shard
         xa, wa, ia = torch.cat(xs), torch.cat(ws_), torch.cat(ids)
-        local = ia - self.rank * self.epr
-        local = torch.where((local >= 0) & (local < self.epr), local, torch.full_like(local, -1))
+        homes = torch.tensor(self.cfg.placement or range(self.cfg.num_experts), device=ia.device)[ia.long().clamp(0, self.cfg.num_experts - 1)]
+        local = (homes - self.rank * self.epr).to(ia.dtype)
+        local = torch.where((local >= 0) & (local < self.epr) & (ia >= 0), local, torch.full_like(local, -1))
         part = ref.moe_forward(xa, local, wa, wg, wu, self.w2)
         parts = list(part.split(T))
         out = torch.empty_like(parts[0])

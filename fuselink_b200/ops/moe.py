@@ -35,19 +35,46 @@ class MoEConfig:
     topk: int = 2
     tokens: int = 8192          # tokens per rank and step
     fp8: bool = False           # block-scaled e4m3 ("1 x 128") for the forward and dgrad GEMMs; wgrad stays bf16
+    placement: Tuple[int, ...] = ()  # home of every expert as rank * (E / W) + local index; () = in order (expert e on rank
+                                     # e // (E / W)); see balanced_placement()
     shadow: Tuple[int, ...] = ()  # experts replicated on every rank ("shadow" experts), see slot_table(); one entry per copy
                                   # slot, the slots in use first, -1 for a slot that is empty at the moment
 
 
-def slot_table(num_experts: int, world: int, shadow: Sequence[int], rank: int) -> torch.Tensor:
+def balanced_placement(expected_load: Sequence[float], world: int) -> Tuple[int, ...]:
+    """Homes for the experts that even out the expected rows per rank: experts in order of decreasing load, each to the
+    rank that carries the least so far and still has a free place (longest-processing-time-first).  With one expert per
+    rank, or one rank, this is the in-order placement.  Returns home[e] = rank * (E / W) + local index."""
+    E = len(expected_load)
+    assert E % world == 0
+    real = E // world
+    if real == 1 or world == 1:
+        return tuple(range(E))
+    load, used, home = [0.0] * world, [0] * world, [0] * E
+    for e in sorted(range(E), key=lambda e: (-float(expected_load[e]), e)):
+        r = min((r for r in range(world) if used[r] < real), key=lambda r: (load[r], r))
+        home[e] = r * real + used[r]
+        used[r] += 1
+        load[r] += float(expected_load[e])
+    return tuple(home)
+
+
+def expert_home(num_experts: int, world: int, placement: Sequence[int], e: int) -> Tuple[int, int]:
+    """(owner rank, local index) of expert e."""
+    h = placement[e] if placement else e
+    return divmod(h, num_experts // world)
+
+
+def slot_table(num_experts: int, world: int, shadow: Sequence[int], rank: int, placement: Sequence[int] = ()) -> torch.Tensor:
     """Where rank ``rank`` sends a row that chose expert e: the slot number ``dest_rank * slots_per_rank + local_slot``.
 
     Every rank has ``E / W`` slots for the experts it owns followed by one slot per shadowed expert.  A row for an
-    ordinary expert goes to the owner's slot.  A row for a shadowed expert stays on the rank it comes from, in that
-    rank's copy of the expert; the owner's own slot for it stays empty.  This is what removes the load imbalance of a
-    skewed router: a hot expert's rows are computed where they originate, spread over all ranks, at the price of
-    summing that expert's weight gradients over the ranks (FasterMoE calls such replicas shadow experts).  The kernels
-    see slots as "experts" and need no change: owner = slot // slots_per_rank.
+    ordinary expert goes to the owner's slot (``placement`` says who owns what; in order by default).  A row for a
+    shadowed expert stays on the rank it comes from, in that rank's copy of the expert; the owner's own slot for it stays
+    empty.  This is what removes the load imbalance of a skewed router: a hot expert's rows are computed where they
+    originate, spread over all ranks, at the price of summing that expert's weight gradients over the ranks (FasterMoE
+    calls such replicas shadow experts).  The kernels see slots as "experts" and need no change:
+    owner = slot // slots_per_rank.
 
     The table has E + 2 entries and is indexed with ``clamp(e, -1, E) + 1``, so an expert id out of range maps to -1,
     which the dispatch kernel reports through the status word like any other bad index."""
@@ -57,9 +84,11 @@ def slot_table(num_experts: int, world: int, shadow: Sequence[int], rank: int) -
     used = [e for e in shadow if e >= 0]
     assert len(set(used)) == len(used) and all(e < num_experts for e in used)
     assert list(shadow[:len(used)]) == used, "the copy slots in use come first"
+    assert not placement or sorted(placement) == list(range(num_experts)), "a placement gives every expert a home of its own"
     t = torch.full((num_experts + 2,), -1, dtype=torch.int32)
     for e in range(num_experts):
-        t[e + 1] = (e // real) * spr + e % real
+        owner, local = expert_home(num_experts, world, placement, e)
+        t[e + 1] = owner * spr + local
     for j, e in enumerate(used):
         t[e + 1] = rank * spr + real + j
     return t
@@ -96,7 +125,8 @@ class MoEWorkspace:
         self.dgu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
         self.local_count = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
         self.base = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
-        self.slots_of = slot_table(cfg.num_experts, W, cfg.shadow, heap.rank).to(dev) if self.nshadow else None
+        remap = self.nshadow or (cfg.placement and tuple(cfg.placement) != tuple(range(cfg.num_experts)))
+        self.slots_of = slot_table(cfg.num_experts, W, cfg.shadow, heap.rank, cfg.placement).to(dev) if remap else None
         # sums the shadow experts' weight gradients over the ranks, in place; replaced in tests that emulate ranks on one GPU
         self.reduce_shadow_grads = _allreduce_shadow_grads
         self.pos = torch.zeros(T, k, dtype=torch.int32, device=dev)
@@ -129,20 +159,24 @@ class MoEWorkspace:
         assert len(shadow) == self.nshadow and self.pending_shadow is None
         self.cfg = dataclasses.replace(self.cfg, shadow=tuple(int(e) for e in shadow))
         if self.nshadow:
-            self.slots_of = slot_table(self.cfg.num_experts, self.heap.world, self.cfg.shadow, self.heap.rank).to(self.slots_of.device)
+            self.slots_of = slot_table(self.cfg.num_experts, self.heap.world, self.cfg.shadow, self.heap.rank, self.cfg.placement).to(self.slots_of.device)
 
 
-def busiest_rank_load(expert_load: Sequence[float], world: int, shadow: Sequence[int]) -> float:
+def busiest_rank_load(expert_load: Sequence[float], world: int, shadow: Sequence[int], placement: Sequence[int] = ()) -> float:
     """Rows on the busiest rank when the experts in ``shadow`` are replicated: a rank computes the rows of the experts it
     owns that are not shadowed, plus its own share (taken as 1 / world) of every shadowed expert's rows."""
     E = len(expert_load)
-    real = E // world
     sh = {e for e in shadow if e >= 0}
     spread = sum(expert_load[e] for e in sh) / world
-    return max(sum(expert_load[e] for e in range(r * real, (r + 1) * real) if e not in sh) for r in range(world)) + spread
+    per_rank = [0.0] * world
+    for e in range(E):
+        if e not in sh:
+            per_rank[expert_home(E, world, placement, e)[0]] += expert_load[e]
+    return max(per_rank) + spread
 
 
-def choose_shadows(expert_load: torch.Tensor, slots: int, world: int = 0, tolerance: float = 0.0) -> Tuple[int, ...]:
+def choose_shadows(expert_load: torch.Tensor, slots: int, world: int = 0, tolerance: float = 0.0,
+                   placement: Sequence[int] = ()) -> Tuple[int, ...]:
     """Which experts to replicate, from the rows routed to each expert summed over all ranks: the busiest experts first
     (ties: the lower id), one per copy slot.  With ``world`` and ``tolerance`` given, experts are added only while the
     busiest rank would still carry more than (1 + tolerance) x the mean, so a router that has become balanced stops paying
@@ -153,7 +187,7 @@ def choose_shadows(expert_load: torch.Tensor, slots: int, world: int = 0, tolera
         return tuple(order[:slots])
     mean = sum(load) / world
     chosen: list = []
-    while len(chosen) < slots and busiest_rank_load(load, world, chosen) > (1.0 + tolerance) * mean:
+    while len(chosen) < slots and busiest_rank_load(load, world, chosen, placement) > (1.0 + tolerance) * mean:
         chosen.append(order[len(chosen)])
     return tuple(chosen) + (-1,) * (slots - len(chosen))
 

@@ -39,12 +39,14 @@ def main():
         model.wait_limit_s = 20.0
         heap = SymmetricHeap.create(48 << 20, device=-1)
         for sgd in (0.0, 0.05):
-            layer = MoELayer(cfg, heap, rank, world, device="cpu", zipf_s=1.2, seed=11, fused_sgd_lr=sgd, name=f"l{sgd}", shadow_experts=2)
+            layer = MoELayer(cfg, heap, rank, world, device="cpu", zipf_s=1.2, seed=11, fused_sgd_lr=sgd, name=f"l{sgd}", shadow_experts=2,
+                             placement=os.environ.get("FL_MOE_PLACEMENT") or None)
             shadow = layer.cfg.shadow
             assert shadow == (0, 1)
             # the experts themselves, once each, as fp32 leaves (every rank builds the same oracle)
             wg_, wu_ = gemm.deinterleave_gate_up(layer.w13.data[:epr])
-            wg, wu, w2 = (torch.cat(gather(t.float())).requires_grad_(True) for t in (wg_, wu_, layer.w2.data[:epr]))
+            order = [layer.home(e)[0] * epr + layer.home(e)[1] for e in range(E)]      # gathered in slot order, wanted by expert id
+            wg, wu, w2 = (torch.cat(gather(t.float()))[order].clone().requires_grad_(True) for t in (wg_, wu_, layer.w2.data[:epr]))
             for step in range(2):
                 g = torch.Generator().manual_seed(100 * step + rank)
                 x = torch.randn(T, H, generator=g).to(torch.bfloat16)
@@ -67,8 +69,8 @@ def main():
                 close(out, refs[rank], "out", 3e-2)
                 close(xa.grad, xr[rank].grad, "dx")
                 close(wa.grad, wr[rank].grad, "dw")
-                slot_of = lambda e: epr + shadow.index(e) if e in shadow else e - rank * epr
-                mine = [e for e in range(E) if e in shadow or e // epr == rank]
+                slot_of = lambda e: epr + shadow.index(e) if e in shadow else layer.home(e)[1]
+                mine = [e for e in range(E) if e in shadow or layer.home(e)[0] == rank]
                 if not sgd:
                     dg, du = gemm.deinterleave_gate_up(layer.w13.grad)
                     for e in mine:
@@ -88,13 +90,13 @@ def main():
                     assert all(torch.equal(c, copies[0]) for c in copies), "the copies must stay identical on every rank"
             if sgd:
                 # choose the shadows again from the last routing (same Zipf bias: same experts), then force another pair
-                assert layer.reshadow(tolerance=0.0)[:2] == (0, 1)
+                assert layer.reshadow()[:2] == (0, 1)                # no tolerance given: both copy slots are filled, hottest first
                 layer.set_shadows((5, 0))
                 assert layer.ws.cfg.shadow == (5, 0) and layer.cfg.shadow == (5, 0)
-                owner5 = gather(layer.w2.data[5 % epr].float())[5 // epr]
+                owner5 = gather(layer.w2.data[layer.home(5)[1]].float())[layer.home(5)[0]]
                 assert torch.equal(layer.w2.data[epr].float(), owner5), "expert 5 must have travelled from its owner into the copy slot"
-                if rank == 1 // epr:                                 # expert 1 is no longer shadowed: its owner took the trained copy back
-                    close(layer.w2.data[1 % epr], w2.detach()[1], "W2 of the expert that went home", 2e-2)
+                if rank == layer.home(1)[0]:                         # expert 1 is no longer shadowed: its owner took the trained copy back
+                    close(layer.w2.data[layer.home(1)[1]], w2.detach()[1], "W2 of the expert that went home", 2e-2)
                 x = torch.randn(T, H).to(torch.bfloat16)
                 with torch.no_grad():
                     w_, idx = layer.route(x)

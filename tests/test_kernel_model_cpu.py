@@ -195,8 +195,8 @@ def test_an_empty_copy_slot_costs_nothing_and_changes_nothing():
     _run_on_model(2, shadow=(-1, -1))
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_expert_parallel_step_between_processes(world, tmp_path):
+@pytest.mark.parametrize("world,placement", [(2, ""), (4, ""), (2, "balanced"), (4, "balanced")])
+def test_expert_parallel_step_between_processes(world, placement, tmp_path):
     """Real processes over a shared-memory heap: forward, backward, the all-reduce of the shadow experts' gradients, the
     fused update, and a change of the shadowed experts by broadcast -- all against an fp32 autograd oracle."""
     import os
@@ -205,7 +205,7 @@ def test_expert_parallel_step_between_processes(world, tmp_path):
     import sys
     here = os.path.dirname(os.path.abspath(__file__))
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
-    env = dict(os.environ, FL_MODEL_LOCK=str(tmp_path / "reserve.lock"))
+    env = dict(os.environ, FL_MODEL_LOCK=str(tmp_path / "reserve.lock"), FL_MOE_PLACEMENT=placement)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(here, "mp_moe_cpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
@@ -392,7 +392,7 @@ def test_serving_command_line_replays_a_trace(tmp_path):
     assert [r for r in rows if "served" in r][0]["served"] == 9
 
 
-@pytest.mark.parametrize("nproc,extra", [(1, []), (2, ["--shadow", "1"]), (2, ["--dtype", "fp8"])])
+@pytest.mark.parametrize("nproc,extra", [(1, []), (2, ["--shadow", "1"]), (2, ["--dtype", "fp8"]), (2, ["--placement", "contiguous"])])
 def test_headline_bench_script_plumbing(nproc, extra, tmp_path):
     """bench.py itself in its host mode under the model (tiny shape; not a measurement): warm-up, timed region, the
     end-to-end region, roofline block, one JSON line with every key the contract names, clean teardown -- on one process
@@ -410,6 +410,8 @@ def test_headline_bench_script_plumbing(nproc, extra, tmp_path):
     assert "error" not in (r["roofline"] or {}) and r["roofline"]["hot_rank_rows"] >= r["roofline"]["mean_rows"] * (0.5 if extra[:1] == ["--shadow"] else 1.0)
     if extra[:1] == ["--shadow"]:
         assert "shadow experts [0]" in r["config"]["parallelism"]
+    if nproc == 2:                                  # by default the experts' homes follow the load the router's bias predicts
+        assert ("expert homes" in r["config"]["parallelism"]) == (extra[:1] != ["--placement"])
     if extra[:1] == ["--dtype"]:
         assert r["dtype"].startswith("fp8")
 
@@ -460,3 +462,11 @@ def test_variable_all_to_all_and_put_many_on_the_model():
     finally:
         for h in heaps:
             h.close()
+
+
+@pytest.mark.parametrize("world,placement,shadow,sgd", [(2, "balanced", (), 0.0), (4, "balanced", (), 0.0), (2, "balanced", (0,), 0.05),
+                                                        (4, (7, 6, 5, 4, 3, 2, 1, 0), (), 0.05), (1, "balanced", (), 0.0)])
+def test_expert_placement_on_the_model(world, placement, shadow, sgd):
+    """Experts owned out of order (evened out by the router's bias, or any permutation): same outputs, gradients and updates
+    as the oracle, which knows experts by id."""
+    _run_on_model(world, placement=placement, shadow=shadow, sgd=sgd, steps=2 if sgd else 1)

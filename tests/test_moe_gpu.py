@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=(), device="cuda"):
+def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=(), device="cuda", placement=None):
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops import gemm, moe as M, ref
     from fuselink_b200.parallel.symm import SymmetricHeap
@@ -14,7 +14,7 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
     heaps = SymmetricHeap.emulated(world, 64 << 20)
     sync = torch.cuda.synchronize if device == "cuda" else (lambda: None)
     try:
-        layers = [MoELayer(cfg, heaps[r], r, world, device=device, seed=3, fused_sgd_lr=sgd, name="m", shadow_experts=list(shadow))
+        layers = [MoELayer(cfg, heaps[r], r, world, device=device, seed=3, fused_sgd_lr=sgd, name="m", shadow_experts=list(shadow), placement=placement)
                   for r in range(world)]
         epr = E // world
         for r in range(1, world):
@@ -23,7 +23,11 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
         for l in layers:
             g_, u_ = gemm.deinterleave_gate_up(l.w13.data[:epr])          # the experts themselves; copies of shadowed ones follow
             wg_all.append(g_.float()); wu_all.append(u_.float()); w2_all.append(l.w2.data[:epr].float())
-        wg, wu, w2 = (torch.cat(v).clone().requires_grad_(True) for v in (wg_all, wu_all, w2_all))
+        wg, wu, w2 = (torch.cat(v) for v in (wg_all, wu_all, w2_all))     # in slot order: rank 0's experts, rank 1's, ...
+        if placement is not None:                                         # the oracle wants them by expert id
+            order = [layers[0].home(e)[0] * epr + layers[0].home(e)[1] for e in range(E)]
+            wg, wu, w2 = wg[order], wu[order], w2[order]
+        wg, wu, w2 = (t.clone().requires_grad_(True) for t in (wg, wu, w2))
         for step in range(steps):
             gen = torch.Generator(device=device).manual_seed(100 + step)
             xs = [torch.randn(T, H, generator=gen, device=device).to(torch.bfloat16) for _ in range(world)]
@@ -73,15 +77,16 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
                 close(dxs[r], xr[r].grad, f"dx rank {r}")
                 close(dws[r], wr[r].grad, f"dw rank {r}")
             # slot -> expert: a rank's own experts, then its copies of the shadowed ones (whose own slots stay idle)
-            own = lambda r: [e for e in range(r * epr, (r + 1) * epr)]
+            own = lambda r: layers[r].local_experts                  # in slot order; r * epr ... in the default placement
             pick = lambda r: [i for i, e in enumerate(own(r)) if e not in shadow]
-            if not shadow and not sgd:
+            plain = not shadow and placement is None
+            if plain and not sgd:
                 for r in range(world):
                     dg, du = gemm.deinterleave_gate_up(grads[r][0])
                     close(dg, wg.grad[r * epr:(r + 1) * epr], f"dWgate rank {r}")
                     close(du, wu.grad[r * epr:(r + 1) * epr], f"dWup rank {r}")
                     close(grads[r][1], w2.grad[r * epr:(r + 1) * epr], f"dW2 rank {r}")
-            elif not shadow:
+            elif plain:
                 with torch.no_grad():
                     for t in (wg, wu, w2):
                         t -= sgd * t.grad
