@@ -27,7 +27,10 @@ for s in $SECTIONS; do
     moe)
       for impl in fuselink nccl; do run "moe $impl" launch bench.py --impl "$impl" --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP"; done ;;
     moe-shadow)   # not in the default list: the hottest experts replicated on every rank
-      if [ "$NGPU" -ge 2 ]; then for n in 1 2 3; do run "moe shadow=$n" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n"; done; fi ;;
+      if [ "$NGPU" -ge 2 ]; then
+        run "moe contiguous placement" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --placement contiguous
+        for n in 1 2 3; do run "moe shadow=$n" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n"; done
+      fi ;;
     gemm-sweep)   # not in the default list: tile order x kernel variant for every GEMM of the step
       for c in fwd1 fwd2 dact dx wgrad2 wgrad13; do run "gemm sweep $c" python bench/gemm_case.py --case "$c" --rows 16384 --iters 5 --sweep; done ;;
     p2p)
