@@ -199,7 +199,7 @@ def main():
         from fuselink_b200.models.moe_baseline import BaselineMoELayer
 
         heap = None
-        layer = BaselineMoELayer(cfg, rank, world, device=dev, zipf_s=args.zipf, seed=0)
+        layer = BaselineMoELayer(cfg, rank, world, device=dev, zipf_s=args.zipf, seed=0, placement=args.placement)
         expert_params = [layer.w13, layer.w2]
     opt = torch.optim.SGD([layer.router] + expert_params, lr=args.lr)
 
@@ -260,6 +260,8 @@ def main():
     # ---------------------------------------------------------------- the result line
     shadowed = getattr(getattr(layer, "cfg", None), "shadow", ())
     placed = getattr(getattr(layer, "cfg", None), "placement", ())
+    if args.impl == "nccl" and getattr(layer, "homes", None) is not None:
+        placed = layer.homes.tolist()
     placed = list(placed) if placed and list(placed) != list(range(len(placed))) else None
 
     def make_line(e2e, roof):

@@ -13,18 +13,27 @@ from .moe import zipf_log_bias
 
 
 class BaselineMoELayer(nn.Module):
-    def __init__(self, cfg: MoEConfig, rank: int = 0, world: int = 1, device="cuda", zipf_s=1.2, seed: int = 0):
+    def __init__(self, cfg: MoEConfig, rank: int = 0, world: int = 1, device="cuda", zipf_s=1.2, seed: int = 0, placement=None):
         super().__init__()
         self.cfg, self.rank, self.world = cfg, rank, world
         self.epr = cfg.num_experts // world
+        # which rank owns which expert: in order, or "balanced" by the router's bias like MoELayer (ops.moe.balanced_placement)
+        homes = list(range(cfg.num_experts))
+        if placement == "balanced":
+            from ..ops.moe import balanced_placement
+            homes = list(balanced_placement((zipf_log_bias(cfg.num_experts, zipf_s) if zipf_s else torch.zeros(cfg.num_experts)).exp().tolist(), world))
+        elif placement not in (None, "contiguous"):
+            homes = [int(h) for h in placement]
+        self.homes = None if homes == list(range(cfg.num_experts)) else torch.tensor(homes, device=device)
+        local = sorted((e for e in range(cfg.num_experts) if homes[e] // self.epr == rank), key=lambda e: homes[e])
         g = torch.Generator().manual_seed(seed)
         H, Fd, E = cfg.hidden, cfg.ffn, cfg.num_experts
         self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(torch.bfloat16).to(device))
         bias = zipf_log_bias(E, zipf_s) if zipf_s else torch.zeros(E)
         self.register_buffer("router_bias", bias.to(device))
         w13, w2 = [], []
-        for le in range(self.epr):
-            ge = torch.Generator().manual_seed(seed * 1000 + 17 + rank * self.epr + le)
+        for e in local:                                            # rank * epr + le in the in-order placement
+            ge = torch.Generator().manual_seed(seed * 1000 + 17 + e)
             wg = (torch.randn(Fd, H, generator=ge) * 0.02).to(torch.bfloat16)
             wu = (torch.randn(Fd, H, generator=ge) * 0.02).to(torch.bfloat16)
             wd = (torch.randn(H, Fd, generator=ge) * 0.02).to(torch.bfloat16)
@@ -41,6 +50,8 @@ class BaselineMoELayer(nn.Module):
         w, idx = torch.topk(probs, k, -1)
         w = w / w.sum(-1, keepdim=True)
         flat = idx.reshape(-1)
+        if self.homes is not None:
+            flat = self.homes[flat]                                # from here on "expert" means the expert's home slot
         order = torch.argsort(flat, stable=True)
         tok = order // k
         xp = x[tok]                                                # permute

@@ -276,3 +276,14 @@ def test_dlrm_training_script_two_ranks_checkpoint_and_resume(tmp_path):
     wrong = subprocess.run([sys.executable, script, "--device", "cpu", "--tables", "5", "--rows", "300", "--global-batch", "64", "--pooling", "4",
                             "--steps", "1", "--resume", ck], capture_output=True, text=True, timeout=300)
     assert wrong.returncode != 0 and "written by 2 ranks" in wrong.stderr
+
+
+def test_baseline_layer_gives_the_same_result_under_any_expert_placement():
+    from fuselink_b200.models.moe_baseline import BaselineMoELayer
+    from fuselink_b200.ops.moe import MoEConfig
+    cfg = MoEConfig(hidden=128, ffn=256, num_experts=8, topk=2, tokens=64)
+    a = BaselineMoELayer(cfg, 0, 1, device="cpu", seed=3)
+    b = BaselineMoELayer(cfg, 0, 1, device="cpu", seed=3, placement=(7, 6, 5, 4, 3, 2, 1, 0))
+    x = torch.randn(64, 128).to(torch.bfloat16)
+    assert torch.equal(a(x), b(x)) and torch.equal(a.w2[0], b.w2[7]) and a.homes is None
+    assert BaselineMoELayer(cfg, 0, 1, device="cpu", seed=3, placement="balanced").homes is None      # one rank: nothing to even out
