@@ -43,6 +43,22 @@ def main():
                 assert torch.equal(dst.local, want), f"transfer {it} arrived damaged"
             dist.barrier()                                            # the destination buffer and the staging are reused
         assert sel.relay_answers == 3
+        # a relay is declared dead (every rank hears of it on the host): the next plans leave it out and the transfer still arrives
+        sel.mark_dead(2)
+        for it in range(3, 5):
+            stripes = sel.plan(0, 1, nbytes)
+            paths = [p for p, _, _ in stripes]
+            assert paths[0] == 1 and 2 not in paths and sum(b for _, _, b in stripes) == nbytes, stripes
+            src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=torch.Generator().manual_seed(it)) if rank == 0 else None
+            striped.transfer(0, 1, src, dst, nbytes, stripes)
+            sel.complete(0, 1, nbytes, stripes)
+            heap.check_status(f"transfer {it} without relay 2")
+            if rank == 1:
+                want = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=torch.Generator().manual_seed(it))
+                assert torch.equal(dst.local, want), f"transfer {it} arrived damaged"
+            dist.barrier()
+        sel.mark_dead(3)
+        assert [p for p, _, _ in sel.plan(0, 1, nbytes)] == [1], "with no relay left the answer is the direct path"
         sel.close()
         print(f"RELAY-MP-OK rank {rank}", flush=True)
         heap.close()
