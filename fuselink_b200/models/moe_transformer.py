@@ -40,6 +40,7 @@ class MoEModelConfig:
     aux_loss_coef: float = 0.01
     capacity_factor: float = 0.0          # > 0 with drop_tokens: choices over an expert's capacity contribute nothing
     drop_tokens: bool = False
+    placement: Optional[str] = None       # "balanced": experts' homes evened out by the router's bias (MoELayer)
     shadow_experts: int = 0               # copies of the n experts the router favours most on every rank (CUDA path)
 
 
@@ -96,7 +97,7 @@ class MoETransformer(nn.Module):
         for l in range(cfg.layers):
             moe = MoELayer(mcfg, heap, rank, world, device=device, zipf_s=None, seed=seed * 100 + l, fused_sgd_lr=fused_sgd_lr,
                            name=f"moe{l}", capacity_factor=cfg.capacity_factor, drop_tokens=cfg.drop_tokens,
-                           shadow_experts=cfg.shadow_experts if world > 1 else 0)
+                           shadow_experts=cfg.shadow_experts if world > 1 else 0, placement=cfg.placement)
             blocks.append(_Block(cfg, moe, device, gen, dtype))
         self.blocks = nn.ModuleList(blocks)
 
