@@ -470,3 +470,22 @@ def test_expert_placement_on_the_model(world, placement, shadow, sgd):
     """Experts owned out of order (evened out by the router's bias, or any permutation): same outputs, gradients and updates
     as the oracle, which knows experts by id."""
     _run_on_model(world, placement=placement, shadow=shadow, sgd=sgd, steps=2 if sgd else 1)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_moe_configurations_on_the_model(seed):
+    """Ranks, experts, top-k, tokens, shadowed experts (with empty copy slots), placements (balanced or any permutation),
+    fused update and the fp8 arm drawn at random from fixed seeds: every combination equals the oracle."""
+    import random
+    rng = random.Random(700 + seed)
+    W = rng.choice([1, 2, 4])
+    E = rng.choice([e for e in (4, 8, 16) if e % W == 0])
+    nsh = rng.choice([0, 0, 1, 2])
+    shadow = tuple(rng.sample(range(E), nsh)) + ((-1,) if nsh and rng.random() < 0.3 else ())
+    placement = rng.choice([None, None, "balanced", tuple(rng.sample(range(E), E))])
+    sgd = rng.choice([0.0, 0.05])
+    import cpu_kernel_model
+    from test_moe_gpu import _run
+    with cpu_kernel_model.installed():
+        _run(W, T=rng.choice([16, 48, 130]), H=128, Fd=256, E=E, k=rng.choice([1, 2, 3]), sgd=sgd, steps=2 if sgd else 1,
+             fp8=rng.random() < 0.25, shadow=shadow, placement=placement, device="cpu")
