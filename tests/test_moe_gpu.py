@@ -151,6 +151,14 @@ def test_moe_shadow_experts(world, shadow):
 
 
 @_UNVERIFIED
+@pytest.mark.parametrize("world,placement", [(2, "balanced"), (4, "balanced"), (2, (7, 6, 5, 4, 3, 2, 1, 0))])
+def test_moe_expert_placement(world, placement):
+    """Experts owned out of order: one index gather in front of the dispatch kernel, everything else as in test_moe_fwd_bwd."""
+    _run(world, placement=placement)
+    _run(world, placement=placement, sgd=0.05, steps=2)
+
+
+@_UNVERIFIED
 def test_moe_shadow_experts_two_steps_fused_sgd():
     _run(2, sgd=0.05, steps=2, shadow=(1,))
 
