@@ -228,7 +228,7 @@ def test_moe_transformer_trains_between_processes(tmp_path):
     assert out.stdout.count("MOE-TRAIN-OK") == 2, out.stdout[-2000:] + out.stderr[-4000:]
 
 
-@pytest.mark.parametrize("world", [2, 3])
+@pytest.mark.parametrize("world", [3])
 def test_dlrm_fused_step_between_processes(world):
     """Real processes, shared-memory heap, modelled embedding-bag entry points: losses, tables and dense weights follow the
     plain-PyTorch path of the same model step by step."""
@@ -392,7 +392,7 @@ def test_serving_command_line_replays_a_trace(tmp_path):
     assert [r for r in rows if "served" in r][0]["served"] == 9
 
 
-@pytest.mark.parametrize("nproc,extra", [(1, []), (2, ["--shadow", "1"]), (2, ["--dtype", "fp8"]), (2, ["--placement", "contiguous"])])
+@pytest.mark.parametrize("nproc,extra", [(1, []), (2, ["--shadow", "1"]), (2, ["--placement", "contiguous", "--dtype", "fp8"])])
 def test_headline_bench_script_plumbing(nproc, extra, tmp_path):
     """bench.py itself in its host mode under the model (tiny shape; not a measurement): warm-up, timed region, the
     end-to-end region, roofline block, one JSON line with every key the contract names, clean teardown -- on one process
@@ -412,11 +412,11 @@ def test_headline_bench_script_plumbing(nproc, extra, tmp_path):
         assert "shadow experts [0]" in r["config"]["parallelism"]
     if nproc == 2:                                  # by default the experts' homes follow the load the router's bias predicts
         assert ("expert homes" in r["config"]["parallelism"]) == (extra[:1] != ["--placement"])
-    if extra[:1] == ["--dtype"]:
+    if "--dtype" in extra:
         assert r["dtype"].startswith("fp8")
 
 
-@pytest.mark.parametrize("nproc", [1, 2])
+@pytest.mark.parametrize("nproc", [2])
 def test_dlrm_bench_script_plumbing(nproc):
     rows = _run_script_on_model("bench/dlrm_bench.py", ["--device", "cpu", "--tables", "5", "--rows", "300", "--global-batch", "64", "--steps", "2",
                                                         "--warmup", "1"], nproc=nproc)
