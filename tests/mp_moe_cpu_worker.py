@@ -32,7 +32,7 @@ def main():
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops import gemm, moe as M, ref
     from fuselink_b200.parallel.symm import SymmetricHeap
-    E, T, k, H, F = 8, 32, 2, 128, 256
+    E, T, k, H, F = int(os.environ.get("FL_MOE_E", "8")), int(os.environ.get("FL_MOE_T", "32")), int(os.environ.get("FL_MOE_K", "2")), 128, 256
     epr = E // world
     cfg = M.MoEConfig(hidden=H, ffn=F, num_experts=E, topk=k, tokens=T)
     with cpu_kernel_model.installed(single_process=False, lock_path=os.environ["FL_MODEL_LOCK"]) as model:
