@@ -313,6 +313,42 @@ class Model:
                           gu, ldgu, dgu, row_info, peers, 0.0, zero_tail, group_m, max_ctas, status, _fp32_operands=True)
 
 
+def describe_call(args, bases, span=1 << 30):
+    """Arguments of a device call as data: tensors by shape / dtype / contiguity, addresses relative to the heap regions
+    they point into, everything else as it is.  Two runs that hand the kernels the same work give the same description."""
+    def one(a):
+        if torch.is_tensor(a):
+            return ["tensor", list(a.shape), str(a.dtype), a.is_contiguous()]
+        if isinstance(a, (list, tuple)):
+            return ["list", [one(x) for x in a]]
+        if isinstance(a, int) and a > (1 << 32):
+            for i, b in enumerate(bases):
+                if 0 <= a - b < span:
+                    return ["addr", i, a - b]
+            return ["addr", "outside the heap"]
+        return a
+    return [one(a) for a in args]
+
+
+@contextlib.contextmanager
+def recording(model, bases, names=("moe_dispatch", "moe_zero_tail", "grouped_gemm", "moe_combine", "moe_combine_dw", "barrier")):
+    """Inside the block every call of the named entry points is appended to the list this yields, as [name, description]."""
+    trace, cls, saved = [], type(model), {}
+    for name in names:
+        orig = getattr(cls, name)
+        saved[name] = orig
+
+        def wrap(self, *a, _n=name, _o=orig, **k):
+            trace.append([_n, describe_call(a, bases)])
+            return _o(self, *a, **k)
+        setattr(cls, name, wrap)
+    try:
+        yield trace
+    finally:
+        for name, orig in saved.items():
+            setattr(cls, name, orig)
+
+
 @contextlib.contextmanager
 def installed(single_process=True, lock_path=None):
     """Inside the block the MoE path's and the transfer path's modules get the model instead of the extension.  With

@@ -491,3 +491,55 @@ def test_random_moe_configurations_on_the_model(seed):
     with cpu_kernel_model.installed():
         _run(W, T=rng.choice([16, 48, 130]), H=128, Fd=256, E=E, k=rng.choice([1, 2, 3]), sgd=sgd, steps=2 if sgd else 1,
              fp8=rng.random() < 0.25, shadow=shadow, placement=placement, device="cpu")
+
+
+def _default_step_trace(world, sgd):
+    """Every device call of two default MoE steps (no placement, no shadows, bf16), ranks emulated in one process."""
+    import cpu_kernel_model
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops import moe as M
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    heaps = SymmetricHeap.emulated(world, 64 << 20)
+    try:
+        with cpu_kernel_model.installed() as model, cpu_kernel_model.recording(model, heaps[0].base, ) as trace:
+            cfg = M.MoEConfig(hidden=128, ffn=256, num_experts=8, topk=2, tokens=48)
+            layers = [MoELayer(cfg, heaps[r], r, world, device="cpu", seed=3, fused_sgd_lr=sgd, name="m") for r in range(world)]
+            for step in range(2):
+                g = torch.Generator().manual_seed(step)
+                xs = [torch.randn(48, 128, generator=g).to(torch.bfloat16) for _ in range(world)]
+                with torch.no_grad():
+                    routes = [layers[r].route(xs[r]) for r in range(world)]
+                wss = [l.ws for l in layers]
+                for r in range(world):
+                    M.moe_forward_dispatch(wss[r], xs[r], routes[r][1].contiguous())
+                for r in range(world):
+                    M.moe_forward_experts(wss[r], layers[r].w13.data, layers[r].w2.data)
+                for r in range(world):
+                    M.moe_forward_combine(wss[r], routes[r][0].contiguous())
+                for r in range(world):
+                    M.moe_backward_dispatch(wss[r], xs[r], routes[r][1].contiguous(), routes[r][0].contiguous())
+                for r in range(world):
+                    M.moe_backward_experts(wss[r], layers[r].w13.data, layers[r].w2.data, sgd, True)
+                for r in range(world):
+                    M.moe_backward_finish(wss[r], True)
+        return trace
+    finally:
+        for h in heaps:
+            h.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("sgd", [0.0, 0.05])
+def test_default_moe_step_hands_the_kernels_exactly_the_recorded_work(world, sgd):
+    """The default configuration of the fused MoE step is the one that was run and measured on B200.  Its device calls --
+    which entry point, in which order, with which scalars, tensor shapes, and addresses relative to the heap -- are pinned
+    to a recorded digest, so an edit of the Python side that changes what the kernels are given (new options must leave
+    the default alone) shows up here, on a machine without a GPU."""
+    import hashlib
+    import json
+    import os
+    golden = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "moe_default_step_calls.json")))
+    want = golden[f"world{world}_sgd{sgd}"]
+    trace = _default_step_trace(world, sgd)
+    assert len(trace) == want["calls"]
+    assert hashlib.sha256(json.dumps(trace).encode()).hexdigest() == want["sha256"], "the default MoE step no longer issues the recorded device calls"
