@@ -360,7 +360,7 @@ def main():
             if world > 1:
                 dist.all_reduce(rows, op=dist.ReduceOp.MAX)
             hot_rows = int(rows.item())
-            m = rl.moe_step_model(T, world, cfg.hidden, cfg.ffn, cfg.topk, hot_rows)
+            m = rl.moe_step_model(T, world, cfg.hidden, cfg.ffn, cfg.topk, hot_rows, shadows=sum(1 for e in shadowed if e >= 0))
             roof = {"hot_rank_rows": hot_rows, "mean_rows": T * cfg.topk, "flops_hot_rank": m["flops"],
                     "nvlink_bytes_hot_rank": m["nvlink_bytes"], "target_ms": m["target_ms"],
                     "achieved_fraction": m["target_ms"] / ms_per_step, "peaks": rl.peaks().source,

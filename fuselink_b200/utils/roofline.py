@@ -50,10 +50,12 @@ def fused_target_ms(flops: float, nvlink_bytes: float, sustained: bool = True) -
     return max(flops / peak, nvlink_bytes / (NVLINK_PEER_GBS * 1e9)) * 1e3
 
 
-def moe_step_model(tokens_per_gpu: int, world: int, hidden: int, ffn: int, topk: int, rows_on_rank: int) -> dict:
-    """FLOPs and NVLink bytes of one MoE fwd+bwd step on the rank that receives `rows_on_rank` routed rows."""
+def moe_step_model(tokens_per_gpu: int, world: int, hidden: int, ffn: int, topk: int, rows_on_rank: int, shadows: int = 0) -> dict:
+    """FLOPs and NVLink bytes of one MoE fwd+bwd step on the rank that receives `rows_on_rank` routed rows.  ``shadows``
+    experts are replicated on every rank: their bf16 weight gradients (3 * hidden * ffn elements each) cross the links in
+    one all-reduce per step, 2 (W - 1) / W of the bytes per rank."""
     flops = rows_on_rank * 3 * (2 * hidden * 2 * ffn + 2 * ffn * hidden)
     remote = (world - 1) / world if world > 1 else 0.0
     # per routed row: x in, y out (forward), dy in, dx out (backward); bf16
-    nvlink = rows_on_rank * hidden * 2 * 4 * remote
+    nvlink = rows_on_rank * hidden * 2 * 4 * remote + shadows * 3 * hidden * ffn * 2 * 2 * remote
     return {"flops": flops, "nvlink_bytes": nvlink, "target_ms": fused_target_ms(flops, nvlink)}
