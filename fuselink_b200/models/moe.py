@@ -148,6 +148,7 @@ class MoELayer(nn.Module):
         experts = tuple(int(e) for e in experts)
         experts = tuple(e for e in experts if e >= 0) + (-1,) * sum(1 for e in experts if e < 0)   # slots in use first
         assert len(experts) <= len(self.cfg.shadow), "more shadows than copy slots"
+        assert all(e < self.cfg.num_experts for e in experts) and len({e for e in experts if e >= 0}) == sum(e >= 0 for e in experts), experts
         experts += (-1,) * (len(self.cfg.shadow) - len(experts))
         if experts == tuple(self.cfg.shadow):
             return

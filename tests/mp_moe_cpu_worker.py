@@ -25,7 +25,7 @@ def close(a, b, what, tol=4e-2):
     assert err < tol * (b.float().abs().max().item() + 1e-4), f"rank {dist.get_rank()} {what}: err {err} vs max {b.float().abs().max().item()}"
 
 
-def main():
+def main():                      # the change of shadows below names expert 5: shapes with at least 6 experts
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=120))
     import cpu_kernel_model
