@@ -493,8 +493,8 @@ def test_random_moe_configurations_on_the_model(seed):
              fp8=rng.random() < 0.25, shadow=shadow, placement=placement, device="cpu")
 
 
-def _default_step_trace(world, sgd):
-    """Every device call of two default MoE steps (no placement, no shadows, bf16), ranks emulated in one process."""
+def _default_step_trace(world, sgd, placement=None):
+    """Every device call of two default MoE steps (no shadows, bf16), ranks emulated in one process."""
     import cpu_kernel_model
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops import moe as M
@@ -503,7 +503,7 @@ def _default_step_trace(world, sgd):
     try:
         with cpu_kernel_model.installed() as model, cpu_kernel_model.recording(model, heaps[0].base, ) as trace:
             cfg = M.MoEConfig(hidden=128, ffn=256, num_experts=8, topk=2, tokens=48)
-            layers = [MoELayer(cfg, heaps[r], r, world, device="cpu", seed=3, fused_sgd_lr=sgd, name="m") for r in range(world)]
+            layers = [MoELayer(cfg, heaps[r], r, world, device="cpu", seed=3, fused_sgd_lr=sgd, name="m", placement=placement) for r in range(world)]
             for step in range(2):
                 g = torch.Generator().manual_seed(step)
                 xs = [torch.randn(48, 128, generator=g).to(torch.bfloat16) for _ in range(world)]
@@ -543,3 +543,12 @@ def test_default_moe_step_hands_the_kernels_exactly_the_recorded_work(world, sgd
     trace = _default_step_trace(world, sgd)
     assert len(trace) == want["calls"]
     assert hashlib.sha256(json.dumps(trace).encode()).hexdigest() == want["sha256"], "the default MoE step no longer issues the recorded device calls"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_placement_changes_nothing_the_kernels_can_see_but_index_values(world):
+    """With the experts' homes evened out, a step issues the same device calls as in the recorded default -- same entry
+    points, order, scalars, shapes and addresses; what differs are the values inside the index tensor and which expert's
+    weights sit in which slot."""
+    assert _default_step_trace(world, 0.05, placement="balanced") == _default_step_trace(world, 0.05)
+    assert _default_step_trace(world, 0.05, placement=(7, 6, 5, 4, 3, 2, 1, 0)) == _default_step_trace(world, 0.05)
