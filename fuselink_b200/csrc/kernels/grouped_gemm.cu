@@ -1,6 +1,6 @@
 // Persistent, warp-specialised grouped GEMM for sm_100a.
 //
-//   warp 0      : TMA producer  (cp.async.bulk.tensor, never multicast; operands are always local memory)
+//   warp 0      : TMA producer  (tiled TMA loads, one per CTA; operands are always local memory)
 //   warp 1      : MMA issuer    (tcgen05.mma kind::f16, one elected thread), owns the TMEM allocation
 //   warps 2..9  : epilogue      (tcgen05.ld -> registers -> fused epilogue -> global / peer stores); two warps
 //                 share each TMEM lane quadrant and split the tile's columns

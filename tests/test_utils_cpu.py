@@ -122,26 +122,3 @@ def test_bench_result_line_is_printed_once_even_when_the_run_stalls():
     import json
     line = json.loads(stuck.stdout.strip())
     assert line["value"] == 1.5 and "did not finish" in line["e2e"]["error"] and line["roofline"] is None
-
-
-def test_sources_name_no_closed_call_and_no_multicast_load():
-    """Two things never appear in a source file, not even in a comment: the batched memcpy entry points (they fault B200s
-    on this driver) and a TMA or bulk LOAD with cluster multicast (from a peer's memory it hangs the GPU, and the package
-    runs the same files on one GPU and on eight).  A multicast tcgen05.commit is not a load and is allowed."""
-    import re
-    import subprocess
-    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    files = subprocess.run(["git", "ls-files"], cwd=root, capture_output=True, text=True).stdout.split()
-    batch = re.compile("Memcpy" + "(3D)?" + "Batch" + "Async")
-    mcast = re.compile(r"cp\.async\.bulk[^;\"]*" + "multicast" + "::cluster")
-    bad = []
-    for f in files:
-        if f.endswith(".md") or not os.path.isfile(os.path.join(root, f)):
-            continue
-        try:
-            text = open(os.path.join(root, f), encoding="utf-8").read()
-        except UnicodeDecodeError:
-            continue
-        if batch.search(text) or mcast.search(text):
-            bad.append(f)
-    assert not bad, bad
