@@ -96,13 +96,13 @@ class ResultLine:
         self.rank, self.make_line = rank, make_line
         self.lock, self.printed, self.timer = threading.Lock(), False, None
 
-    def emit(self, e2e, roof) -> None:
+    def emit(self, e2e, roof, *more) -> None:
         with self.lock:
             if self.printed:
                 return
             self.printed = True
             if self.rank == 0:
-                print(json.dumps(self.make_line(e2e, roof)))
+                print(json.dumps(self.make_line(e2e, roof, *more)))
             sys.stdout.flush()
 
     def arm(self, limit_s: float) -> None:
@@ -139,11 +139,63 @@ def parse():
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="which rank owns which expert (fuselink arm): balanced = evened out by the load the router's bias predicts "
                          "(no effect with one GPU or one expert per GPU); contiguous = expert e on rank e // (E / N)")
-    ap.add_argument("--shadow", type=int, default=0,
-                    help="replicate the N experts the router favours most on every rank: their rows are computed where they originate and "
-                         "their weight gradients are summed over the ranks (fuselink arm, N GPUs > 1)")
+    ap.add_argument("--shadow", default="auto",
+                    help="fuselink arm, N GPUs > 1.  auto (default): after the first warm-up step the layer looks at its own routing, "
+                         "replicates as few of the busiest experts as it takes for no rank's own experts to exceed the mean load by more "
+                         "than --tolerance, and splits the replicated experts' rows over the ranks so that every rank computes about the "
+                         "mean (MoELayer.rebalance); the copies' weight gradients are summed over the ranks.  An integer N: the N experts "
+                         "the router's bias favours most, their rows computed where they originate.  0: none")
+    ap.add_argument("--shadow-slots", type=int, default=4, help="copy slots every rank reserves with --shadow auto (unused ones cost nothing per step)")
+    ap.add_argument("--tolerance", type=float, default=0.05)
+    ap.add_argument("--no-baseline", action="store_true", help="skip the PyTorch + NCCL arm that follows the fuselink arm in the same process")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="fp8: block-scaled e4m3 (1x128) forward/dgrad GEMMs")
     return ap.parse_args()
+
+
+def stock_arm(args, cfg, rank, world, dev, xs, fuselink_value):
+    """The same step in its stock formulation (framework permute, NCCL all_to_all_single, library GEMMs, autograd,
+    torch.optim.SGD; models/moe_baseline.py), timed like the fuselink arm: same inputs, steps and warm-up, CUDA events,
+    max over ranks.  Experts sit where the in-order placement puts them: expert e on rank e // (E / N)."""
+    import torch
+    import torch.distributed as dist
+
+    from fuselink_b200.models.moe_baseline import BaselineMoELayer
+
+    import dataclasses
+    layer = BaselineMoELayer(dataclasses.replace(cfg, fp8=False, shadow=(), placement=()), rank, world, device=dev, zipf_s=args.zipf, seed=0)
+    opt = torch.optim.SGD([layer.router, layer.w13, layer.w2], lr=args.lr)
+
+    def step(x):
+        x = x.detach().requires_grad_(True)
+        loss = layer(x).float().pow(2).mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(xs[i % len(xs)])
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(xs[i % len(xs)])
+    e1.record()
+    sync_all()
+    tms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms = float(tms.item())
+    value = world * cfg.tokens * args.steps / (ms / 1e3)
+    gemm_used = layer.expert_gemm
+    del layer, opt
+    return {"impl": "pytorch+nccl: permute + all_to_all_single + library GEMMs + autograd + torch.optim.SGD, same process and inputs",
+            "expert_gemm": gemm_used, "value": value, "unit": "tokens/s",
+            "ms_per_step": ms / args.steps, "ratio": fuselink_value / value}
 
 
 def main():
@@ -188,14 +240,19 @@ def main():
 
         W = world
         cap = (T * W + 127) // 128 * 128
-        shadow = args.shadow if W > 1 else 0
-        rows = (cfg.num_experts // W + shadow) * cap
+        auto_shadow = args.shadow == "auto" and W > 1
+        if auto_shadow:
+            shadow = [-1] * min(args.shadow_slots, cfg.num_experts)     # empty copy slots, filled by rebalance() after warm-up step 1
+        else:
+            shadow = int(args.shadow) if (W > 1 and args.shadow != "auto") else 0
+        rows = (cfg.num_experts // W + (len(shadow) if auto_shadow else shadow)) * cap
         heap_bytes = 2 * rows * H * 2 + rows * 4 + 2 * T * cfg.topk * H * 2 + (64 << 20)
         heap = SymmetricHeap.create(heap_bytes, device=-1 if cpu else local_rank)
         layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr, shadow_experts=shadow,
                          placement=args.placement)
         expert_params = []          # updated inside the wgrad kernels' epilogue
     else:
+        auto_shadow = False
         from fuselink_b200.models.moe_baseline import BaselineMoELayer
 
         heap = None
@@ -228,6 +285,9 @@ def main():
     # ---------------------------------------------------------------- device-timed region
     for i in range(args.warmup):
         step(xs[i % n_inputs])
+        if i == 0 and auto_shadow:
+            sync_all()
+            layer.rebalance(tolerance=args.tolerance)     # from the routing of the step just done; fixed from here on
     sync_all()
     if heap is not None:
         heap.check_status("warmup")
@@ -264,19 +324,19 @@ def main():
         placed = layer.homes.tolist()
     placed = list(placed) if placed and list(placed) != list(range(len(placed))) else None
 
-    def make_line(e2e, roof):
+    def make_line(e2e, roof, base=None):
         flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
         return {
             "metric": "MoE-EP tokens/s (fwd+bwd+SGD)", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
+            "scaling": "weak", "vs_baseline": base,
             "dtype": "fp8 e4m3 1x128 block-scaled (fwd, dgrad) + bf16 (wgrad)" if cfg.fp8 else "bf16", "data": "synthetic",
             "impl": args.impl,
             "config": {"model": "MoE-EP layer: hidden 4096, 8 experts SwiGLU 4096-14336-4096, top-2, Zipf(1.2) router bias"
                        if (args.hidden, args.ffn, args.experts, args.topk) == (4096, 14336, 8, 2) else
                        f"MoE-EP layer h{args.hidden} f{args.ffn} e{args.experts} k{args.topk}",
                        "global_batch": world * T, "seq_len": T, "tokens_per_gpu": T,
-                       "parallelism": f"ep{world}" + (f", expert homes {placed}" if placed else "") + (f" + shadow experts {list(shadowed)}" if shadowed else ""),
+                       "parallelism": f"ep{world}" + (f", expert homes {placed}" if placed else "") + (f" + shadow experts {[e for e in shadowed if e >= 0]}" + (" chosen from the routing of warm-up step 1, their rows spread over the ranks' copies" if auto_shadow else "") if any(e >= 0 for e in shadowed) else ""),
                        "optimizer": "SGD lr %g (experts: fused into the wgrad epilogue)" % args.lr if args.impl == "fuselink" else "SGD lr %g" % args.lr,
                        "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
             "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
@@ -368,8 +428,16 @@ def main():
     except Exception as e:  # noqa: BLE001 - reporting only
         roof = {"error": repr(e)}
 
+    # ---------------------------------------------------------------- the stock arm, same process, same steps
+    base = None
+    if args.impl == "fuselink" and not args.no_baseline and not cpu:
+        try:
+            base = stock_arm(args, cfg, rank, world, dev, xs, value)
+        except Exception as e:  # noqa: BLE001 - the fuselink numbers above must still be reported
+            base = {"impl": "pytorch+nccl", "error": repr(e), "ratio": None}
+
     result.disarm()
-    result.emit(e2e, roof)
+    result.emit(e2e, roof, base)
     # the result is out: teardown must never be able to hang the job (a watchdog ends the process after 60 s)
     sys.stdout.flush()
     wd = threading.Timer(60.0, lambda: os._exit(0))

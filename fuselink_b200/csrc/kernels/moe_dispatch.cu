@@ -158,7 +158,8 @@ extern "C" int fl_moe_dispatch(const FlMoeDispatchArgs* a, cudaStream_t stream) 
   if (a->hidden % 8) return -1;
   if (a->num_experts < 1 || a->num_experts > 1024) return -2;
   if (a->world < 1 || a->world > 8 || a->experts_per_rank * a->world != a->num_experts) return -3;
-  if (a->rank < 0 || a->rank > 15 || (long long)a->tokens * a->topk >= (1ll << 28)) return -4;
+  if (a->rank < 0 || a->rank >= a->world || (long long)a->tokens * a->topk >= (1ll << 28)) return -4;
+  if (a->cap <= 0 || a->topk < 1 || a->tokens < 0) return -5;
   const int n = a->tokens * a->topk;
   if (n == 0) return 0;
   if (!a->reuse_slots) {

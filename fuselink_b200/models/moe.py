@@ -189,6 +189,33 @@ class MoELayer(nn.Module):
         self.set_shadows(chosen, group)
         return chosen
 
+    @torch.no_grad()
+    def rebalance(self, topk_idx: Optional[torch.Tensor] = None, group=None, tolerance: float = 0.05) -> tuple:
+        """Even out the rows per rank from the routing of a batch (by default the last one routed), between steps:
+        replicate as few of the busiest experts as it takes for no rank's OWN experts to exceed (1 + tolerance) x the mean
+        load (the other copy slots stay empty), then split the shadowed experts' rows over the ranks' copies so that every
+        rank computes about the mean (ops.moe.spread_plan).  Collective over the ranks of the layer.  Returns the experts
+        now shadowed."""
+        from ..ops.moe import choose_shadows, spread_pattern, spread_plan
+        n, E = len(self.cfg.shadow), self.cfg.num_experts
+        if topk_idx is None:
+            topk_idx = getattr(self, "last_topk_idx", None)
+        if n == 0 or topk_idx is None:
+            return tuple(self.cfg.shadow)
+        mine = torch.bincount(topk_idx.reshape(-1).long().clamp(0, E - 1), minlength=E).double()
+        loads = [mine]
+        if self.world > 1:
+            import torch.distributed as dist
+            loads = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(loads, mine, group=group)
+        loads = torch.stack(loads).cpu()
+        chosen = choose_shadows(loads.sum(0), n, self.world, tolerance, self.cfg.placement, spread=True)
+        self.set_shadows(chosen, group)
+        if self.ws is not None:
+            plan = spread_plan(loads.tolist(), self.world, chosen, self.cfg.placement)
+            self.ws.set_spread(spread_pattern(plan[self.rank], self.cfg.tokens, self.rank))
+        return chosen
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         w, idx = self.route(x)
         if x.is_cuda and self.ws is None:
@@ -240,6 +267,6 @@ def smoke_step(device: str = "cuda:0", tokens: int = 512, hidden: int = 512, ffn
         heap.check_status("smoke")
         assert x.grad is not None and torch.isfinite(x.grad.float()).all()
         assert layer.router.grad is not None
-        return float(loss)
+        return float(loss.detach())
     finally:
         heap.close()

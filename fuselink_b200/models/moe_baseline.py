@@ -1,7 +1,12 @@
 """The stock formulation of the MoE expert-parallel step, used as the measured baseline:
 framework permute (sort by expert) + ``all_to_all_single`` over NCCL + library GEMMs per expert + the mirror
 all-to-all, with autograd doing the backward and ``torch.optim.SGD`` the update.  None of this library's
-kernels run on this path."""
+kernels run on this path.
+
+The expert FFN is the library's grouped GEMM (``torch.nn.functional.grouped_mm``: one launch per projection over all
+local experts, group sizes read on the device) where this PyTorch build has it for the device, else one matmul per
+expert; the activation stays in bf16.  ``self.expert_gemm`` says which one runs.  The host reads the routing result only
+where the stock collective needs it: ``all_to_all_single`` takes its split sizes as Python lists."""
 from __future__ import annotations
 
 import torch
@@ -41,6 +46,39 @@ class BaselineMoELayer(nn.Module):
             w2.append(wd)
         self.w13 = nn.Parameter(torch.stack(w13).to(device))
         self.w2 = nn.Parameter(torch.stack(w2).to(device))
+        self.expert_gemm = "grouped_mm" if self._probe_grouped_mm(device) else "matmul per expert"
+
+    @staticmethod
+    def _probe_grouped_mm(device) -> bool:
+        """Whether the library grouped GEMM runs (forward and backward) on this device with bf16 operands."""
+        fn = getattr(F, "grouped_mm", None)
+        if fn is None or torch.device(device).type != "cuda":
+            return False
+        try:
+            a = torch.randn(32, 64, device=device, dtype=torch.bfloat16, requires_grad=True)
+            b = torch.randn(2, 64, 32, device=device, dtype=torch.bfloat16, requires_grad=True)
+            offs = torch.tensor([16, 32], device=device, dtype=torch.int32)
+            fn(a, b, offs=offs).float().sum().backward()
+            torch.cuda.synchronize()
+            return bool(torch.isfinite(a.grad.float()).all())
+        except Exception:  # noqa: BLE001 - not supported by this build / device: use the loop
+            return False
+
+    def _experts(self, xe, ecnt_dev, ecnt_host):
+        """SwiGLU FFN of every local expert over its rows (xe is sorted by expert; ecnt = rows per expert)."""
+        Fd = self.cfg.ffn
+        if self.expert_gemm == "grouped_mm":
+            offs = ecnt_dev.cumsum(0).to(torch.int32)
+            h = F.grouped_mm(xe, self.w13.transpose(1, 2), offs=offs)
+            return F.grouped_mm(F.silu(h[:, :Fd]) * h[:, Fd:], self.w2.transpose(1, 2), offs=offs)
+        ecnt = ecnt_host() if callable(ecnt_host) else ecnt_host
+        outs, o = [], 0
+        for e in range(self.epr):
+            xs = xe[o:o + ecnt[e]]
+            o += ecnt[e]
+            h = xs @ self.w13[e].t()
+            outs.append((F.silu(h[:, :Fd]) * h[:, Fd:]) @ self.w2[e].t())
+        return torch.cat(outs)
 
     def forward(self, x):
         cfg, W = self.cfg, self.world
@@ -71,17 +109,10 @@ class BaselineMoELayer(nn.Module):
             eid = torch.repeat_interleave(torch.arange(self.epr, device=x.device).repeat(W), rc.reshape(-1))
             eorder = torch.argsort(eid, stable=True)
             xe = xr[eorder]
-            ecnt = rc.sum(0).tolist()
+            ecnt_dev = rc.sum(0)
         else:
-            xe, ecnt = xp, cnt.tolist()
-        outs, o = [], 0
-        Fd = cfg.ffn
-        for e in range(self.epr):
-            xs = xe[o:o + ecnt[e]]
-            o += ecnt[e]
-            h = xs @ self.w13[e].t()
-            outs.append((F.silu(h[:, :Fd].float()) * h[:, Fd:].float()).to(x.dtype) @ self.w2[e].t())
-        ye = torch.cat(outs)
+            xe, ecnt_dev = xp, cnt
+        ye = self._experts(xe, ecnt_dev, ecnt_dev.tolist)
         if W > 1:
             inv = torch.empty_like(eorder)
             inv[eorder] = torch.arange(eorder.numel(), device=x.device)

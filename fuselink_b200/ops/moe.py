@@ -127,6 +127,8 @@ class MoEWorkspace:
         self.base = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
         remap = self.nshadow or (cfg.placement and tuple(cfg.placement) != tuple(range(cfg.num_experts)))
         self.slots_of = slot_table(cfg.num_experts, W, cfg.shadow, heap.rank, cfg.placement).to(dev) if remap else None
+        self.spread = None                                # [T, 1] int32: rank that computes a token's shadow rows, minus this rank
+        self.sh_stride = self._shadow_stride() if self.nshadow else None
         # sums the shadow experts' weight gradients over the ranks, in place; replaced in tests that emulate ranks on one GPU
         self.reduce_shadow_grads = _allreduce_shadow_grads
         self.pos = torch.zeros(T, k, dtype=torch.int32, device=dev)
@@ -153,6 +155,25 @@ class MoEWorkspace:
     def shadows_in_use(self) -> int:
         return sum(1 for e in self.cfg.shadow if e >= 0)
 
+    def _shadow_stride(self) -> torch.Tensor:
+        """[E + 2] int32, indexed like slots_of: slots per rank for a shadowed expert, 0 for every other entry, so that
+        slots_of[j] + sh_stride[j] * (dest - rank) is the expert's copy on rank ``dest``."""
+        t = torch.zeros(self.cfg.num_experts + 2, dtype=torch.int32)
+        for e in self.cfg.shadow:
+            if e >= 0:
+                t[e + 1] = self.epr
+        return t.to(self.local_count.device)
+
+    def set_spread(self, pattern: Optional[torch.Tensor]) -> None:
+        """Which rank computes the shadow rows of each token (spread_pattern), or None: they stay here.  Between steps
+        only: the backward dispatch must see the pattern of its forward."""
+        assert self.pending_shadow is None
+        if pattern is None or not self.nshadow or not bool((pattern != 0).any()):
+            self.spread = None
+        else:
+            assert pattern.numel() == self.cfg.tokens
+            self.spread = pattern.to(self.local_count.device, torch.int32).reshape(-1, 1)
+
     def set_shadow(self, shadow: Sequence[int]) -> None:
         """Other experts in the copy slots (as many slots as before: the buffers keep their size; -1 = empty, in-use slots
         first).  Between steps only."""
@@ -160,23 +181,82 @@ class MoEWorkspace:
         self.cfg = dataclasses.replace(self.cfg, shadow=tuple(int(e) for e in shadow))
         if self.nshadow:
             self.slots_of = slot_table(self.cfg.num_experts, self.heap.world, self.cfg.shadow, self.heap.rank, self.cfg.placement).to(self.slots_of.device)
+            self.sh_stride = self._shadow_stride()
+            self.spread = None                            # a plan belongs to the set of shadows it was made for
 
 
-def busiest_rank_load(expert_load: Sequence[float], world: int, shadow: Sequence[int], placement: Sequence[int] = ()) -> float:
-    """Rows on the busiest rank when the experts in ``shadow`` are replicated: a rank computes the rows of the experts it
-    owns that are not shadowed, plus its own share (taken as 1 / world) of every shadowed expert's rows."""
+def owned_rows(expert_load: Sequence[float], world: int, shadow: Sequence[int], placement: Sequence[int] = ()) -> list:
+    """Rows every rank computes for the experts it owns that are not shadowed."""
     E = len(expert_load)
     sh = {e for e in shadow if e >= 0}
-    spread = sum(expert_load[e] for e in sh) / world
     per_rank = [0.0] * world
     for e in range(E):
         if e not in sh:
             per_rank[expert_home(E, world, placement, e)[0]] += expert_load[e]
-    return max(per_rank) + spread
+    return per_rank
+
+
+def busiest_rank_load(expert_load: Sequence[float], world: int, shadow: Sequence[int], placement: Sequence[int] = (),
+                      spread: bool = False) -> float:
+    """Rows on the busiest rank when the experts in ``shadow`` are replicated: a rank computes the rows of the experts it
+    owns that are not shadowed, plus its own share (taken as 1 / world) of every shadowed expert's rows.  With ``spread``
+    the shadowed experts' rows go to whichever copies even out the ranks (spread_plan), so the busiest rank carries the
+    mean unless the experts it owns alone exceed it."""
+    per_rank = owned_rows(expert_load, world, shadow, placement)
+    if spread:
+        return max(max(per_rank), sum(expert_load) / world)
+    return max(per_rank) + sum(expert_load[e] for e in {e for e in shadow if e >= 0}) / world
+
+
+def spread_plan(load, world: int, shadow: Sequence[int], placement: Sequence[int] = ()) -> list:
+    """Where the rows of the shadowed experts are computed so that every rank ends up with the same number of rows.
+
+    ``load[r][e]`` = rows rank r routes to expert e.  Every rank holds a copy of every shadowed expert, so a row for one of
+    them may be computed anywhere; by default it stays where it originates.  That leaves the ranks that also own a busy
+    ordinary expert with more rows than the others.  The plan moves the surplus: a rank whose total (rows of its own experts
+    from everyone + its own shadow rows) is above the mean sends the excess shadow rows to the ranks below the mean, in
+    proportion to their deficit.  Returns share[r][d] = fraction of rank r's shadow rows that are computed on rank d (each row
+    sums to 1).  The gradients of the copies are summed over the ranks whatever the split, so only the dispatch changes."""
+    E = len(load[0])
+    sh = [e for e in shadow if e >= 0]
+    total = [sum(load[r][e] for r in range(world)) for e in range(E)]
+    own = owned_rows(total, world, sh, placement)
+    made = [sum(load[r][e] for e in sh) for r in range(world)]          # shadow rows that originate on rank r
+    share = [[1.0 if d == r else 0.0 for d in range(world)] for r in range(world)]
+    if not sh or sum(made) <= 0:
+        return share
+    mean = sum(total) / world
+    have = [own[r] + made[r] for r in range(world)]
+    surplus = [min(max(have[r] - mean, 0.0), made[r]) for r in range(world)]   # only shadow rows can move
+    deficit = [max(mean - have[r], 0.0) for r in range(world)]
+    moved = min(sum(surplus), sum(deficit))
+    if moved <= 0:
+        return share
+    fs, fd = moved / sum(surplus), moved / sum(deficit)
+    for r in range(world):
+        out = surplus[r] * fs
+        if out <= 0 or made[r] <= 0:
+            continue
+        share[r][r] = 1.0 - out / made[r]
+        for d in range(world):
+            if deficit[d] > 0:
+                share[r][d] += (out / made[r]) * (deficit[d] * fd / moved)
+    return share
+
+
+def spread_pattern(share_row: Sequence[float], tokens: int, rank: int) -> torch.Tensor:
+    """int32 [tokens]: the rank that computes the shadow rows of token t, minus ``rank`` (0 = stays here), such that the
+    fraction of tokens sent to rank d is share_row[d].  Token t is placed by the fractional part of t x the golden ratio, a
+    low-discrepancy sequence, so every stretch of the batch is split in the same proportions."""
+    edges = torch.tensor(list(share_row), dtype=torch.float64).cumsum(0)
+    edges = edges / edges[-1]
+    u = (torch.arange(tokens, dtype=torch.float64) * 0.6180339887498949) % 1.0
+    dest = torch.bucketize(u, edges[:-1].contiguous(), right=True)
+    return (dest - rank).to(torch.int32)
 
 
 def choose_shadows(expert_load: torch.Tensor, slots: int, world: int = 0, tolerance: float = 0.0,
-                   placement: Sequence[int] = ()) -> Tuple[int, ...]:
+                   placement: Sequence[int] = (), spread: bool = False) -> Tuple[int, ...]:
     """Which experts to replicate, from the rows routed to each expert summed over all ranks: the busiest experts first
     (ties: the lower id), one per copy slot.  With ``world`` and ``tolerance`` given, experts are added only while the
     busiest rank would still carry more than (1 + tolerance) x the mean, so a router that has become balanced stops paying
@@ -187,7 +267,7 @@ def choose_shadows(expert_load: torch.Tensor, slots: int, world: int = 0, tolera
         return tuple(order[:slots])
     mean = sum(load) / world
     chosen: list = []
-    while len(chosen) < slots and busiest_rank_load(load, world, chosen, placement) > (1.0 + tolerance) * mean:
+    while len(chosen) < slots and busiest_rank_load(load, world, chosen, placement, spread) > (1.0 + tolerance) * mean:
         chosen.append(order[len(chosen)])
     return tuple(chosen) + (-1,) * (slots - len(chosen))
 
@@ -204,7 +284,10 @@ def _dispatch(ws: MoEWorkspace, x: torch.Tensor, idx: torch.Tensor, scale: Optio
     C = require_native()
     h, cfg = ws.heap, ws.cfg
     if ws.slots_of is not None:
-        idx = ws.slots_of[(idx.clamp(-1, cfg.num_experts) + 1).long()]          # expert id -> slot (see slot_table)
+        j = (idx.clamp(-1, cfg.num_experts) + 1).long()
+        idx = ws.slots_of[j]                                                    # expert id -> slot (see slot_table)
+        if ws.spread is not None:
+            idx = idx + ws.sh_stride[j] * ws.spread                             # a shadowed expert's copy on another rank
     C.moe_dispatch(x, idx, scale, ws.num_slots, ws.epr, ws.cap, h.rank, h.world, ws.local_count, ws.base, ws.pos,
                    ws.slot, ws.counts.peers(), ws.step_parity, dst.peers(), ws.info.peers(), reuse, h.status_addr)
     ws.launches += 1 if reuse else 3

@@ -1,14 +1,9 @@
 """Block-scaled fp8 grouped GEMM: quantisers against their PyTorch restatement, and the GEMM against an fp32 matmul of
 the DEQUANTISED operands (so the check isolates the kernel from the quantisation error)."""
-import os
-
 import pytest
 import torch
 
-# The fp8 kernel has been compiled for sm_100a but not yet validated on hardware; until it has, its GPU tests run only on
-# request so that a defect in it cannot take the CUDA context (and every test after it) down with it.
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(os.environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1", reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")]
+pytestmark = pytest.mark.gpu
 
 
 def _mk(shape, scale=1.0, seed=0):

@@ -48,6 +48,17 @@ def test_shadow_experts_two_steps_fused_update_keeps_the_copies_identical():
     _run_on_model(2, sgd=0.05, steps=2, shadow=(1,))
 
 
+@pytest.mark.parametrize("world,shadow,spread", [
+    (2, (0,), [[0.5, 0.5], [0.25, 0.75]]),
+    (4, (0, 5), [[1, 0, 0, 0], [0.2, 0.3, 0.5, 0], [0, 0, 0.4, 0.6], [0.25, 0.25, 0.25, 0.25]]),
+    (2, (4, -1), [[0.0, 1.0], [1.0, 0.0]]),
+])
+def test_shadow_rows_spread_over_the_copies_on_the_model(world, shadow, spread):
+    """A shadowed expert's rows computed by other ranks' copies: outputs, input gradients and summed weight gradients as before."""
+    _run_on_model(world, shadow=shadow, spread=spread)
+    _run_on_model(world, shadow=shadow, spread=spread, sgd=0.05, steps=2)
+
+
 def test_shadowed_rows_do_not_cross_ranks():
     """With every expert shadowed nothing is sent: each rank's counters show exactly its own tokens."""
     import cpu_kernel_model

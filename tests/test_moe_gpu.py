@@ -5,7 +5,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=(), device="cuda", placement=None):
+def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, shadow=(), device="cuda", placement=None, spread=None):
     from fuselink_b200.models.moe import MoELayer
     from fuselink_b200.ops import gemm, moe as M, ref
     from fuselink_b200.parallel.symm import SymmetricHeap
@@ -19,6 +19,9 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
         epr = E // world
         for r in range(1, world):
             layers[r].router.data.copy_(layers[0].router.data)
+        if spread is not None:          # share[r][d]: fraction of rank r's shadow rows that rank d's copy computes
+            for r in range(world):
+                layers[r].ws.set_spread(M.spread_pattern(spread[r], T, r))
         wg_all, wu_all, w2_all = [], [], []
         for l in layers:
             g_, u_ = gemm.deinterleave_gate_up(l.w13.data[:epr])          # the experts themselves; copies of shadowed ones follow
@@ -133,24 +136,17 @@ def test_moe_fwd_bwd(world):
     _run(world)
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1", reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
 @pytest.mark.parametrize("world", [1, 2])
 def test_moe_fwd_bwd_fp8_block_scaled(world):
     _run(world, fp8=True)
 
 
-_UNVERIFIED = pytest.mark.skipif(__import__("os").environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1",
-                                 reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
-
-
-@_UNVERIFIED
 @pytest.mark.parametrize("world,shadow", [(2, (0,)), (4, (0, 5)), (1, (2,)), (2, (4, -1))])
 def test_moe_shadow_experts(world, shadow):
     """Hot experts replicated on every rank: same outputs and gradients as without, the copies' gradients summed."""
     _run(world, shadow=shadow)
 
 
-@_UNVERIFIED
 @pytest.mark.parametrize("world,placement", [(2, "balanced"), (4, "balanced"), (2, (7, 6, 5, 4, 3, 2, 1, 0))])
 def test_moe_expert_placement(world, placement):
     """Experts owned out of order: one index gather in front of the dispatch kernel, everything else as in test_moe_fwd_bwd."""
@@ -158,9 +154,19 @@ def test_moe_expert_placement(world, placement):
     _run(world, placement=placement, sgd=0.05, steps=2)
 
 
-@_UNVERIFIED
 def test_moe_shadow_experts_two_steps_fused_sgd():
     _run(2, sgd=0.05, steps=2, shadow=(1,))
+
+
+@pytest.mark.parametrize("world,shadow,spread", [
+    (2, (0,), [[0.5, 0.5], [0.25, 0.75]]),
+    (4, (0, 5), [[1, 0, 0, 0], [0.2, 0.3, 0.5, 0], [0, 0, 0.4, 0.6], [0.25, 0.25, 0.25, 0.25]]),
+    (2, (4, -1), [[0.0, 1.0], [1.0, 0.0]]),
+])
+def test_moe_shadow_rows_spread_over_the_copies(world, shadow, spread):
+    """A shadowed expert's rows may be computed by any rank's copy: same outputs and gradients whatever the split."""
+    _run(world, shadow=shadow, spread=spread)
+    _run(world, shadow=shadow, spread=spread, sgd=0.05, steps=2)
 
 
 def test_moe_two_steps_fused_sgd():

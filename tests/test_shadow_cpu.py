@@ -158,3 +158,29 @@ def test_empty_copy_slots_in_the_table_and_the_layer():
     assert l.cfg.shadow == (3, -1) and torch.equal(l.w2[4], l.w2[3])
     l.reshadow(torch.tensor([[0, 1], [2, 3], [0, 2], [1, 3]]), tolerance=0.5)     # one rank: always level
     assert l.cfg.shadow == (-1, -1)
+
+
+def test_spread_plan_levels_the_ranks_and_the_pattern_follows_it():
+    """Zipf-skewed loads on 2, 4 and 8 ranks: with as few shadows as the tolerance asks for and their rows split by the plan
+    every rank computes the mean within the tolerance; the per-token pattern realises the plan's shares."""
+    import torch
+    from fuselink_b200.ops import moe as M
+    L = [45754, 28357, 18115, 12716, 9339, 6862, 5565, 4364]
+    for W, want in ((2, 0), (4, 1), (8, 3)):
+        pl = M.balanced_placement(L, W)
+        load = [[x / W for x in L] for _ in range(W)]
+        ch = M.choose_shadows(torch.tensor(L, dtype=torch.float64), 4, W, 0.05, pl, spread=True)
+        assert sum(e >= 0 for e in ch) == want, (W, ch)
+        plan = M.spread_plan(load, W, ch, pl)
+        own = M.owned_rows(L, W, ch, pl)
+        made = [sum(load[r][e] for e in ch if e >= 0) for r in range(W)]
+        tot = [own[d] + sum(made[r] * plan[r][d] for r in range(W)) for d in range(W)]
+        mean = sum(L) / W
+        assert max(tot) <= 1.05 * mean + 1 and abs(sum(tot) - sum(L)) < 1e-6 * sum(L)
+        for r in range(W):
+            assert abs(sum(plan[r]) - 1.0) < 1e-9 and min(plan[r]) >= 0
+            pat = M.spread_pattern(plan[r], 8192, r)
+            for d in range(W):
+                assert abs(float((pat == d - r).double().mean()) - plan[r][d]) < 2e-3
+    # nothing shadowed, or nothing to move: rows stay where they are
+    assert M.spread_plan([[1.0] * 8] * 2, 2, (), ()) == [[1.0, 0.0], [0.0, 1.0]]

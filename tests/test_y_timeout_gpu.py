@@ -35,8 +35,6 @@ def test_flag_wait_runs_out_and_reports_status():
             hh.close()
 
 
-@pytest.mark.skipif(__import__("os").environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1",
-                    reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
 def test_put_kernel_feeds_monitor_counters():
     """The put kernel adds the bytes of every finished chunk to a pinned host counter that the monitor's sweeper folds
     into the path's completed bytes (device-side completion counters -> lock-free host thread)."""
