@@ -38,6 +38,7 @@ struct KParams {
   __nv_bfloat16* dgu;
   const int* row_info;
   FlPeerPtrs peers;
+  int num_peers; long long peer_rows;
   int zero_tail;
   int group_m;
   int* status;
@@ -377,9 +378,14 @@ fp8_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           dst = p.C + grow * p.ldc;
         } else if (valid) {
           const int info = p.row_info[grow];
-          dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[(info >> 28) & 0xF]) + (long long)(info & 0x0FFFFFFF) * p.ldc;
+          const int rk = (info >> 28) & 0xF;
+          const long long slot = info & 0x0FFFFFFF;
+          if (rk < p.num_peers && (p.peer_rows <= 0 || slot < p.peer_rows))
+            dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
+          else
+            report(p.status, kBadIndex, 2500);   // names no rank / no slot of the receive buffer: not stored
         }
-        if (valid || (zero_row && p.epilogue == FL_EPI_STORE)) {
+        if ((valid && dst != nullptr) || (zero_row && p.epilogue == FL_EPI_STORE)) {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             float v[32];
@@ -501,6 +507,13 @@ extern "C" int fl_fp8_grouped_gemm(const FlFp8GemmDesc* d, cudaStream_t stream) 
   p.a_scale = d->a_scale; p.b_scale = d->b_scale; p.b_mn = d->b_mn_major; p.epilogue = d->epilogue;
   p.C = (__nv_bfloat16*)d->C; p.ldc = d->ldc; p.gu = (__nv_bfloat16*)d->gu; p.ldgu = d->ldgu; p.dgu = (__nv_bfloat16*)d->dgu;
   p.row_info = d->row_info; p.peers = d->peers; p.zero_tail = d->zero_tail;
+  p.num_peers = d->num_peers; p.peer_rows = d->peer_rows;
+  if (d->epilogue == FL_EPI_SCATTER) {
+    if (d->num_peers < 1 || d->num_peers > FL_MAX_PEERS) return bad("SCATTER needs 1..8 receive buffers (num_peers)");
+    if (d->row_info == nullptr) return bad("SCATTER needs row_info");
+    for (int i = 0; i < d->num_peers; ++i)
+      if (d->peers.p[i] == nullptr) return bad("SCATTER: a receive buffer is null");
+  }
   p.group_m = d->group_m > 0 ? d->group_m : 16; p.status = d->status;
   CUtensorMap tmA, tmB;
   int rc = make_map(&tmA, d->A, d->K, d->cap, d->num_groups, 128, BM);
@@ -508,10 +521,12 @@ extern "C" int fl_fp8_grouped_gemm(const FlFp8GemmDesc* d, cudaStream_t stream) 
   rc = d->b_mn_major ? make_map(&tmB, d->B, d->N, d->K, d->num_groups, 128, 128)
                      : make_map(&tmB, d->B, d->K, d->N, d->num_groups, 128, BN);
   if (rc) return rc;
-  static int num_sms = 0;
+  static int sms_of[64];                       // per device: the shared-memory attribute belongs to the device's copy of the kernel
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return bad("device ordinal out of range");
+  int& num_sms = sms_of[dev];
   if (!num_sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaFuncSetAttribute(fp8_grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) { num_sms = 0; return (int)e; }

@@ -24,6 +24,8 @@ struct FlFp8GemmDesc {
   void* dgu;                        // DSWIGLU output
   const int* row_info;              // SCATTER
   FlPeerPtrs peers;
+  int num_peers;                    // SCATTER: entries of `peers` in use
+  long long peer_rows;              // SCATTER: rows of every receive buffer (0 = not checked)
   int zero_tail;
   int group_m;
   int max_ctas;

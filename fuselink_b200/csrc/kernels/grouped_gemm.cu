@@ -49,6 +49,7 @@ struct KParams {
   __nv_bfloat16* dgu;
   const int* row_info;
   FlPeerPtrs peers;
+  int num_peers; long long peer_rows;
   float sgd_lr;
   int zero_tail;
   int group_m;
@@ -183,7 +184,12 @@ __device__ __forceinline__ void epilogue_slab(const KParams& p, const EpiSlab& e
         const int info = p.row_info[(long long)e.g * p.cap + row];
         const int rk = (info >> 28) & 0xF;
         const long long slot = info & 0x0FFFFFFF;
-        dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
+        if (rk >= p.num_peers || (p.peer_rows > 0 && slot >= p.peer_rows)) {
+          report(p.status, kBadIndex, 500);      // a row that names no rank / no slot of the receive buffer: not stored
+          valid = false;
+        } else {
+          dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
+        }
       }
     } else {
       valid = row < p.M;
@@ -732,6 +738,13 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
   p.C = (__nv_bfloat16*)d->C; p.ldc = d->ldc; p.gsc = d->gsc;
   p.gu = (__nv_bfloat16*)d->gu; p.ldgu = d->ldgu; p.dgu = (__nv_bfloat16*)d->dgu;
   p.row_info = d->row_info; p.peers = d->peers; p.sgd_lr = d->sgd_lr; p.zero_tail = d->zero_tail;
+  p.num_peers = d->num_peers; p.peer_rows = d->peer_rows;
+  if (d->epilogue == FL_EPI_SCATTER) {
+    if (d->num_peers < 1 || d->num_peers > FL_MAX_PEERS) return bad("SCATTER needs 1..8 receive buffers (num_peers)");
+    if (d->row_info == nullptr) return bad("SCATTER needs row_info");
+    for (int i = 0; i < d->num_peers; ++i)
+      if (d->peers.p[i] == nullptr) return bad("SCATTER: a receive buffer is null");
+  }
   p.group_m = d->group_m > 0 ? d->group_m : 16;
   p.status = d->status;
 
@@ -759,11 +772,17 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
     if (rc) return rc;
   }
 
-  static int num_sms = 0, max_pairs = 0;
-  static bool attr_set = false;
+  // per device: a process may drive several GPUs, and the shared-memory attribute belongs to the device's copy of the kernel
+  constexpr int kMaxDev = 64;
+  static int sms_of[kMaxDev], pairs_of[kMaxDev];
+  static bool attr_set_of[kMaxDev];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDev) return bad("device ordinal out of range");
+  int& num_sms = sms_of[dev];
+  int& max_pairs = pairs_of[dev];
+  bool& attr_set = attr_set_of[dev];
   if (!attr_set) {
-    int dev = 0;
-    cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;

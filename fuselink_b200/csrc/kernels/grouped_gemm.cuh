@@ -45,6 +45,8 @@ struct FlGemmDesc {
   void* dgu;                                      // DSWIGLU output (same ld as gu)
   const int* row_info;                            // SCATTER: per grouped row  (rank << 28) | slot
   FlPeerPtrs peers;                               // SCATTER: base of each rank's receive buffer
+  int num_peers;                                  // SCATTER: entries of `peers` in use; a row naming another rank is skipped
+  long long peer_rows;                            // SCATTER: rows of every receive buffer (0 = not checked); a slot beyond it is skipped
   float sgd_lr;                                   // WGRAD: 0 => store dW
   int zero_tail;                                  // STORE/SWIGLU/DSWIGLU: write zeros to rows in [count, roundup(count,128))
   // fp8 block scaling (elem_bytes == 1): fp32 scales, A: [rows, K/128] per-row-per-128, B: [N/128, K/128]

@@ -428,6 +428,7 @@ FlVmmRegion* fl_vmm_adopt(void* ptr, size_t size, int owner_device) {
   r->size = round_up(size, gran);
   r->slab_bytes = r->size;
   r->owns_va = false;
+  r->owns_phys = false;     // the memory behind the address was allocated elsewhere: it is not in this layer's usage count
   r->access.push_back(owner_device);
   Slab s;
   if (g_drv->retain(ptr, &s.handle)) { delete r; return nullptr; }

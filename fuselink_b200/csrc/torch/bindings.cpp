@@ -43,7 +43,7 @@ static void grouped_gemm(int64_t group_mode, int64_t num_groups, int64_t cap, in
                          c10::optional<torch::Tensor> C, int64_t ldc, int64_t gsc, c10::optional<torch::Tensor> gu,
                          int64_t ldgu, c10::optional<torch::Tensor> dgu, c10::optional<torch::Tensor> row_info,
                          std::vector<int64_t> peers, double sgd_lr, bool zero_tail, int64_t group_m, int64_t max_ctas,
-                         c10::optional<torch::Tensor> status) {
+                         c10::optional<torch::Tensor> status, int64_t peer_rows) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "grouped_gemm needs CUDA tensors");
   TORCH_CHECK(A.scalar_type() == torch::kBFloat16 && B.scalar_type() == torch::kBFloat16, "bf16 operands expected");
   c10::cuda::CUDAGuard guard(A.device());
@@ -59,7 +59,7 @@ static void grouped_gemm(int64_t group_mode, int64_t num_groups, int64_t cap, in
   d.C = opt_ptr(C); d.ldc = ldc; d.gsc = gsc;
   d.gu = opt_ptr(gu); d.ldgu = ldgu; d.dgu = opt_ptr(dgu);
   d.row_info = row_info.has_value() ? row_info->data_ptr<int>() : nullptr;
-  d.peers = to_peers(peers);
+  d.peers = to_peers(peers); d.num_peers = (int)peers.size(); d.peer_rows = peer_rows;
   d.sgd_lr = (float)sgd_lr; d.zero_tail = zero_tail; d.group_m = (int)group_m; d.max_ctas = (int)max_ctas;
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
   check_rc(fl_grouped_gemm(&d, cur_stream()), "fl_grouped_gemm", fl_gemm_last_error());
@@ -237,7 +237,7 @@ static void fp8_grouped_gemm(int64_t num_groups, int64_t cap, int64_t N, int64_t
                              int64_t epilogue, c10::optional<torch::Tensor> C, int64_t ldc, c10::optional<torch::Tensor> gu,
                              int64_t ldgu, c10::optional<torch::Tensor> dgu, c10::optional<torch::Tensor> row_info,
                              std::vector<int64_t> peers, bool zero_tail, int64_t group_m, int64_t max_ctas,
-                             c10::optional<torch::Tensor> status) {
+                             c10::optional<torch::Tensor> status, int64_t peer_rows) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.element_size() == 1 && B.element_size() == 1, "fp8 operands expected");
   c10::cuda::CUDAGuard guard(A.device());
   FlFp8GemmDesc d;
@@ -248,7 +248,8 @@ static void fp8_grouped_gemm(int64_t num_groups, int64_t cap, int64_t N, int64_t
   d.B = B.data_ptr(); d.b_mn_major = b_mn; d.b_scale = b_scale.data_ptr<float>();
   d.epilogue = (int)epilogue; d.C = opt_ptr(C); d.ldc = ldc; d.gu = opt_ptr(gu); d.ldgu = ldgu; d.dgu = opt_ptr(dgu);
   d.row_info = row_info.has_value() ? row_info->data_ptr<int>() : nullptr;
-  d.peers = to_peers(peers); d.zero_tail = zero_tail; d.group_m = (int)group_m; d.max_ctas = (int)max_ctas;
+  d.peers = to_peers(peers); d.num_peers = (int)peers.size(); d.peer_rows = peer_rows;
+  d.zero_tail = zero_tail; d.group_m = (int)group_m; d.max_ctas = (int)max_ctas;
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
   check_rc(fl_fp8_grouped_gemm(&d, cur_stream()), "fl_fp8_grouped_gemm", fl_fp8_last_error());
 }

@@ -181,6 +181,12 @@ class StripedP2P:
     chunk), each relay forwards its stripe chunk by chunk as the flags appear, the destination waits for its
     arrival counter.  This is the reference's multi-path idea (a channel's buffer lives on a relay GPU,
     src/plugin.cc:1201, src/fuselink.cc:43-56) with explicit stripes instead of per-channel VA remaps.
+
+    Flow control: a relay's staging buffer has two halves used in turn (per relay: its k-th stripe goes to half
+    k % 2), and a relay counts the stripes it has finished forwarding in a word of its own signal pad.  Before a
+    source writes a relay's k-th stripe it waits (on its stream, reading the relay's word over NVLink) until the
+    relay has forwarded its first k - 1 stripes, i.e. until the half it is about to overwrite has been drained.
+    Transfers may therefore be issued back to back; a stripe must fit in half the staging buffer.
     """
 
     def __init__(self, heap: SymmetricHeap, name: str, staging_bytes: int, engine: Optional[str] = None):
@@ -188,12 +194,16 @@ class StripedP2P:
         self.C = require_native()
         self.engine = engine or knobs().copy_engine
         self.chunk = knobs().chunk_bytes
-        self.staging = heap.alloc_tensor([staging_bytes], torch.uint8)
-        self.max_chunks = (staging_bytes + self.chunk - 1) // self.chunk
-        self.chunk_flags = heap.signal_slots(f"relay:{name}:chunks", self.max_chunks)
+        self.half_chunks = max(1, staging_bytes // 2 // self.chunk)
+        self.half_bytes = self.half_chunks * self.chunk
+        self.staging = heap.alloc_tensor([2 * self.half_bytes], torch.uint8)
+        self.chunk_flags = heap.signal_slots(f"relay:{name}:chunks", 2 * self.half_chunks)
         self.arrive = heap.signal_slots(f"relay:{name}:arrive", 1)
+        self.forwarded = heap.signal_slots(f"relay:{name}:forwarded", 1)      # on the relay: stripes it has passed on
+        self.token = heap.alloc_tensor([32], torch.uint8)                     # 16 B payload + 16 B landing place of the count bump
         self.seq = 0
         self.arrived_expected = 0
+        self.relayed = [0] * heap.world                                       # stripes given to each relay so far (same on every rank)
 
     def transfer(self, src_rank: int, dst_rank: int, src: Optional[torch.Tensor], dst: SymTensor, nbytes: int,
                  stripes: Sequence[Tuple[int, int, int]]) -> None:
@@ -203,8 +213,11 @@ class StripedP2P:
         cb = self.chunk
         me = heap.rank
         total_chunks = sum((b + cb - 1) // cb for _, _, b in stripes if b > 0)
+        relays = [(path, off, b) for path, off, b in stripes if b > 0 and path != dst_rank]
+        assert len({p for p, _, _ in relays}) == len(relays), "one stripe per relay and transfer"
+        halves = {path: self.relayed[path] % 2 for path, _, _ in relays}
         if me == src_rank:
-            segs = []
+            segs, credits = [], []
             for path, off, b in stripes:
                 if b <= 0:
                     continue
@@ -212,18 +225,30 @@ class StripedP2P:
                     segs.append((src.data_ptr() + off, dst.addr(dst_rank) + off, b,
                                  heap.sig_addr(self.arrive, dst_rank), FLAG_COUNT, 0))
                 else:
-                    assert b <= self.staging.shape[0], "stripe larger than the relay staging buffer"
-                    segs.append((src.data_ptr() + off, self.staging.addr(path), b,
-                                 heap.sig_addr(self.chunk_flags, path), FLAG_SEQ_PER_CHUNK, 0))
+                    assert b <= self.half_bytes, "stripe larger than half the relay staging buffer"
+                    h = halves[path]
+                    if self.relayed[path] >= 2:       # the stripe that last used this half has left the relay
+                        credits.append((heap.sig_addr(self.forwarded, path), (self.relayed[path] - 1) & 0xFFFFFFFF))
+                    segs.append((src.data_ptr() + off, self.staging.addr(path) + h * self.half_bytes, b,
+                                 heap.sig_addr(self.chunk_flags + h * self.half_chunks, path), FLAG_SEQ_PER_CHUNK, 0))
+            if credits:
+                self.C.wait_flags(credits, heap.status_addr)
             ctas, threads = _launch_shape(total_chunks, self.engine)
             self.C.put_chunks(segs, cb, self.seq, self.engine == "bulk", ctas, threads, heap.status_addr)
-        for path, off, b in stripes:
-            if path == me and me != dst_rank and me != src_rank and b > 0:
-                seg = (self.staging.addr(), dst.addr(dst_rank) + off, b, heap.sig_addr(self.arrive, dst_rank),
-                       FLAG_COUNT, heap.sig_addr(self.chunk_flags))
+        for path, off, b in relays:
+            if path == me and me != src_rank:
+                h = halves[path]
+                seg = (self.staging.addr() + h * self.half_bytes, dst.addr(dst_rank) + off, b, heap.sig_addr(self.arrive, dst_rank),
+                       FLAG_COUNT, heap.sig_addr(self.chunk_flags + h * self.half_chunks))
                 n = (b + cb - 1) // cb
                 ctas, threads = _launch_shape(n, self.engine)
                 self.C.put_chunks([seg], cb, self.seq, self.engine == "bulk", ctas, threads, heap.status_addr)
+                # stream-ordered after the forward: one more stripe has left this relay (a 16-byte local put whose
+                # arrival count is the word the source waits on)
+                bump = (self.token.addr(), self.token.addr() + 16, 16, heap.sig_addr(self.forwarded), FLAG_COUNT, 0)
+                self.C.put_chunks([bump], 16, 0, False, 1, 32, heap.status_addr)
+        for path, _, _ in relays:
+            self.relayed[path] += 1
         if me == dst_rank:
             self.arrived_expected += total_chunks
             self.C.wait_flags([(heap.sig_addr(self.arrive), self.arrived_expected & 0xFFFFFFFF)], heap.status_addr)

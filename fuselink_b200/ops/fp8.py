@@ -38,7 +38,7 @@ def grouped_gemm_rows_fp8(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tenso
                           out: Optional[torch.Tensor] = None, gu: Optional[torch.Tensor] = None,
                           dgu: Optional[torch.Tensor] = None, row_info: Optional[torch.Tensor] = None,
                           peers: Optional[List[int]] = None, ldc: Optional[int] = None, zero_tail: bool = False,
-                          group_m: int = 16, max_ctas: int = 0, status: Optional[torch.Tensor] = None):
+                          group_m: int = 16, max_ctas: int = 0, status: Optional[torch.Tensor] = None, peer_rows: int = 0):
     """M-grouped fp8 GEMM: C_g = (A_g * a_s) @ (B_g * b_s)^T with fp32 accumulation.
     b_q: [G, N, K] (K-major) with b_s [G, N/128, K/128]; or with ``b_mn_major`` [G, K, N] with b_s [G, K/128, N/128]."""
     C = require_native()
@@ -53,7 +53,7 @@ def grouped_gemm_rows_fp8(a_q: torch.Tensor, a_s: torch.Tensor, b_q: torch.Tenso
     if ldc is None:
         ldc = out.shape[1] if out is not None else N
     C.fp8_grouped_gemm(G, cap, N, K, counts, a_q, a_s, b_q, b_mn_major, b_s, epilogue, out, ldc, gu,
-                       gu.shape[1] if gu is not None else 0, dgu, row_info, peers or [], zero_tail, group_m, max_ctas, status)
+                       gu.shape[1] if gu is not None else 0, dgu, row_info, peers or [], zero_tail, group_m, max_ctas, status, peer_rows)
     return out
 
 

@@ -15,8 +15,10 @@ def grouped_gemm_rows(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.T
                       gu: Optional[torch.Tensor] = None, dgu: Optional[torch.Tensor] = None,
                       row_info: Optional[torch.Tensor] = None, peers: Optional[List[int]] = None, ldc: Optional[int] = None,
                       zero_tail: bool = False, group_m: int = 16, max_ctas: int = 0,
-                      status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                      status: Optional[torch.Tensor] = None, peer_rows: int = 0) -> Optional[torch.Tensor]:
     """M-grouped GEMM: for each group g, ``C_g = A_g @ B_g^T`` over the first counts[g] rows of A_g.
+    With the SCATTER epilogue ``peer_rows`` is the number of rows of every receive buffer: a row whose return address
+    lies outside is not stored and the status word reports a bad index.
 
     a: [G*cap, K] bf16 token buffer (group g owns rows [g*cap, (g+1)*cap)).
     b: [G, N, K] (K-major, the nn.Linear layout) or, with ``b_mn_major``, [G, K, N].
@@ -37,7 +39,7 @@ def grouped_gemm_rows(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.T
     ldb = N if b_mn_major else K
     C.grouped_gemm(0, G, cap, 0, N, K, counts, a, False, K, cap * K, b, b_mn_major, ldb, b.shape[1] * b.shape[2],
                    epilogue, out, ldc, gsc, gu if gu is not None else None, gu.shape[1] if gu is not None else 0, dgu,
-                   row_info, peers or [], 0.0, zero_tail, group_m, max_ctas, status)
+                   row_info, peers or [], 0.0, zero_tail, group_m, max_ctas, status, peer_rows)
     return out
 
 
@@ -54,7 +56,7 @@ def grouped_gemm_wgrad(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.
         assert sgd_lr == 0.0
         out = torch.empty(G, M, N, dtype=torch.bfloat16, device=a.device)
     C.grouped_gemm(1, G, cap, M, N, 0, counts, a, True, M, cap * M, b, True, N, cap * N, EPI_WGRAD, out, N, M * N,
-                   None, 0, None, None, [], sgd_lr, False, group_m, max_ctas, status)
+                   None, 0, None, None, [], sgd_lr, False, group_m, max_ctas, status, 0)
     return out
 
 

@@ -327,13 +327,13 @@ def moe_forward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor) -
                                  gu=ws.gu, zero_tail=True, status=st)
         C.fp8_quantize_rows(ws.act, ws.q_act, ws.s_act, counts, ws.cap)
         f8.grouped_gemm_rows_fp8(ws.q_act, ws.s_act, *ws.wq["w2"], counts, ws.cap, epilogue=gemm.EPI_SCATTER,
-                                 row_info=ws.info.local, peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st)
+                                 row_info=ws.info.local, peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st, peer_rows=ws.comb.local.shape[0])
         ws.launches += 4
     else:
         gemm.grouped_gemm_rows(ws.xd.local, w13, counts, ws.cap, epilogue=gemm.EPI_SWIGLU, out=ws.act, gu=ws.gu,
                                zero_tail=True, status=st)
         gemm.grouped_gemm_rows(ws.act, w2, counts, ws.cap, epilogue=gemm.EPI_SCATTER, row_info=ws.info.local,
-                               peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st)
+                               peers=ws.comb.peers(), ldc=ws.cfg.hidden, status=st, peer_rows=ws.comb.local.shape[0])
     barrier(h, ws.name + ":c", signal=True, wait=False)
     ws.launches += 5
 
@@ -380,14 +380,15 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
             C.fp8_quantize_rows(ws.dgu, ws.q_dgu, ws.s_dgu, counts, ws.cap)
             f8.grouped_gemm_rows_fp8(ws.q_dgu, ws.s_dgu, *ws.wq["w13"], counts, ws.cap, b_mn_major=True,
                                      epilogue=gemm.EPI_SCATTER, row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden,
-                                     status=st)
+                                     status=st, peer_rows=ws.dxs.local.shape[0])
         ws.launches += 2
     else:
         gemm.grouped_gemm_rows(ws.dyd.local, w2, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=ws.gu,
                                dgu=ws.dgu, zero_tail=True, status=st)
         if need_dx:
             gemm.grouped_gemm_rows(ws.dgu, w13, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER,
-                                   row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st)
+                                   row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st,
+                                   peer_rows=ws.dxs.local.shape[0])
     shadow_grads = None
     if ws.nshadow:
         # Owned experts as below, on the leading slots.  The copies of the shadowed experts have seen this rank's rows

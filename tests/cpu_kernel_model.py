@@ -226,7 +226,7 @@ class Model:
 
     # ---------------------------------------------------------------------------------------- grouped GEMM
     def grouped_gemm(self, mode, G, cap, M, N, K, counts, A, a_mn, lda, gsa, B, b_mn, ldb, gsb, epilogue, out, ldc, gsc,
-                     gu, ldgu, dgu, row_info, peers, sgd_lr, zero_tail, group_m, max_ctas, status, _fp32_operands=False):
+                     gu, ldgu, dgu, row_info, peers, sgd_lr, zero_tail, group_m, max_ctas, status, peer_rows=0, _fp32_operands=False):
         assert _fp32_operands or (A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16)
         assert A.is_contiguous() and B.is_contiguous()
         assert counts is None or (counts.dtype == torch.int32 and counts.numel() >= G)
@@ -261,6 +261,7 @@ class Model:
                 info = row_info[rows]
                 for r in range(n):
                     home, i = (int(info[r]) >> 28) & 0xF, int(info[r]) & 0x0FFFFFFF
+                    assert home < len(peers) and (peer_rows <= 0 or i < peer_rows), "the kernel skips such a row and reports a bad index"
                     self._view(peers[home] + i * ldc * 2, [N], torch.bfloat16).copy_(c[r].to(torch.bfloat16))
             elif epilogue == EPI_DSWIGLU:                           # c = dAct [n, F]; saved gate/up -> dGate/dUp, interleaved
                 v = gu[rows].float().view(n, N // 128, 2, 128)
@@ -296,7 +297,7 @@ class Model:
         scale.copy_(s)
 
     def fp8_grouped_gemm(self, G, cap, N, K, counts, A, a_scale, B, b_mn, b_scale, epilogue, out, ldc, gu, ldgu, dgu, row_info,
-                         peers, zero_tail, group_m, max_ctas, status):
+                         peers, zero_tail, group_m, max_ctas, status, peer_rows=0):
         from fuselink_b200.ops import fp8 as f8
         assert A.element_size() == 1 and B.element_size() == 1 and A.shape == (G * cap, K)
         assert a_scale.shape == (G * cap, K // 128)
@@ -310,7 +311,7 @@ class Model:
         b = f8.dequantize_blocks(B, b_scale)
         # the same epilogues, on operands that carry exactly the information the e4m3 values and their scales hold
         self.grouped_gemm(0, G, cap, 0, N, K, counts, a.to(torch.float32), False, K, cap * K, b, b_mn, 0, 0, epilogue, out, ldc, 0,
-                          gu, ldgu, dgu, row_info, peers, 0.0, zero_tail, group_m, max_ctas, status, _fp32_operands=True)
+                          gu, ldgu, dgu, row_info, peers, 0.0, zero_tail, group_m, max_ctas, status, peer_rows, _fp32_operands=True)
 
 
 def describe_call(args, bases, span=1 << 30):

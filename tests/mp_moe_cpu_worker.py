@@ -103,6 +103,38 @@ def main():                      # the change of shadows below names expert 5: s
                     out = M.MoEFunction.apply(x, w_, idx, layer.w13, layer.w2, layer.ws, 0.0)
                 heap.check_status("after the change")
                 assert int(layer.ws.counts_now()[epr]) == int((idx == 5).sum()) and int(layer.ws.counts_now()[epr + 1]) == int((idx == 0).sum())
+                # the layer evens out the ranks by itself: shadows from the observed routing, their rows spread over the copies
+                chosen = layer.rebalance(tolerance=0.0)
+                assert layer.cfg.shadow == chosen == layer.ws.cfg.shadow
+                wg_, wu_ = gemm.deinterleave_gate_up(layer.w13.data[:epr])      # the owners hold the current weights again
+                wg, wu, w2 = (torch.cat(gather(t.float()))[order].clone().requires_grad_(True) for t in (wg_, wu_, layer.w2.data[:epr]))
+                g = torch.Generator().manual_seed(4242 + rank)
+                x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+                dout = torch.randn(T, H, generator=g).to(torch.bfloat16)
+                xa = x.clone().requires_grad_(True)
+                with torch.no_grad():
+                    w_, idx = layer.route(x)
+                wa = w_.clone().requires_grad_(True)
+                layer.zero_grad(set_to_none=True)
+                out = M.MoEFunction.apply(xa, wa, idx, layer.w13, layer.w2, layer.ws, 0.0)
+                (out.float() * dout.float()).sum().backward()
+                heap.check_status("after the rebalance")
+                xs, douts, ws_, idxs = gather(x), gather(dout), gather(w_), gather(idx)
+                xr = [t.float().requires_grad_(True) for t in xs]
+                wr = [t.float().requires_grad_(True) for t in ws_]
+                refs = [ref.moe_forward(xr[r], idxs[r], wr[r], wg, wu, w2) for r in range(world)]
+                sum((refs[r] * douts[r].float()).sum() for r in range(world)).backward()
+                close(out, refs[rank], "out after the rebalance", 3e-2)
+                close(xa.grad, xr[rank].grad, "dx after the rebalance")
+                close(wa.grad, wr[rank].grad, "dw after the rebalance")
+                dg, du = gemm.deinterleave_gate_up(layer.w13.grad)
+                for e in range(E):
+                    if e in chosen or layer.home(e)[0] == rank:
+                        sl = epr + chosen.index(e) if e in chosen else layer.home(e)[1]
+                        close(dg[sl], wg.grad[e], f"dWgate expert {e} after the rebalance")
+                        close(layer.w2.grad[sl], w2.grad[e], f"dW2 expert {e} after the rebalance")
+                rows = gather(layer.ws.counts_now().sum().reshape(1).to(torch.int64))
+                assert sum(int(r) for r in rows) == world * T * k
         dist.barrier()
         print(f"MOE-MP-OK rank {rank}", flush=True)
         heap.close()

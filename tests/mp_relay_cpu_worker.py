@@ -25,8 +25,22 @@ def main():
         heap = SymmetricHeap.create(64 << 20, device=-1)
         nbytes = (6 << 20) + 4096
         dst = heap.alloc_tensor([nbytes], torch.uint8)
+        dsts = [heap.alloc_tensor([nbytes], torch.uint8) for _ in range(4)]
         striped = StripedP2P(heap, "t", 8 << 20)
         sel = PathSelector(world)                                     # every rank plans on its own table: same inputs, same plan
+        # four transfers back to back, nothing between them: the relays' staging halves are reused, and what keeps the source
+        # from overwriting a stripe a relay is still forwarding is the credit it reads from the relay
+        plan = sel.plan(0, 1, nbytes)
+        for it in range(4):
+            src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=torch.Generator().manual_seed(100 + it)) if rank == 0 else None
+            striped.transfer(0, 1, src, dsts[it], nbytes, plan)
+        sel.complete(0, 1, nbytes, plan)
+        heap.check_status("back to back")
+        if rank == 1:
+            for it in range(4):
+                want = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=torch.Generator().manual_seed(100 + it))
+                assert torch.equal(dsts[it].local, want), f"back-to-back transfer {it} arrived damaged"
+        dist.barrier()
         for it in range(3):
             stripes = sel.plan(0, 1, nbytes)
             paths = [p for p, _, _ in stripes]
@@ -41,8 +55,8 @@ def main():
             if rank == 1:
                 want = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, generator=torch.Generator().manual_seed(it))
                 assert torch.equal(dst.local, want), f"transfer {it} arrived damaged"
-            dist.barrier()                                            # the destination buffer and the staging are reused
-        assert sel.relay_answers == 3
+            dist.barrier()                                            # the destination buffer is reused
+        assert sel.relay_answers == 4
         # a relay is declared dead (every rank hears of it on the host): the next plans leave it out and the transfer still arrives
         sel.mark_dead(2)
         for it in range(3, 5):

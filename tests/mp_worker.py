@@ -79,8 +79,8 @@ def main():
         for m in (fused, base):
             m.zero_grad(set_to_none=True)
 
-    # ---- MoE with the two hottest experts replicated on every rank (not run on a GPU yet: opt-in) ----------------
-    if os.environ.get("FUSELINK_TEST_UNVERIFIED", "0") == "1":
+    # ---- MoE with the two hottest experts replicated on every rank ---------------------------------------------
+    if True:
         from fuselink_b200.ops import gemm
         sh = MoELayer(cfg, heap, rank, world, device=dev, seed=4, fused_sgd_lr=0.0, name="moe_sh", shadow_experts=2)
         epr, F = cfg.num_experts // world, cfg.ffn
@@ -110,6 +110,47 @@ def main():
                 close(sh.w2.grad[slot], base.w2.grad[le], f"dW2 expert {e}")
             for m in (sh, base):
                 m.zero_grad(set_to_none=True)
+
+    # ---- experts placed by expected load, then the layer rebalances itself from its own routing -----------------
+    # (copy slots start empty; rebalance() picks the shadows and spreads their rows over the ranks' copies)
+    if world > 1 and cfg.num_experts // world > 1:
+        pl = MoELayer(cfg, heap, rank, world, device=dev, seed=4, fused_sgd_lr=0.0, name="moe_pl", placement="balanced",
+                      shadow_experts=[-1, -1])
+        bpl = BaselineMoELayer(cfg, rank, world, device=dev, seed=4, placement="balanced")
+        F = cfg.ffn
+        for step in range(3):
+            g = torch.Generator(device=dev).manual_seed(130 + step * 10 + rank)
+            x = torch.randn(cfg.tokens, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+            xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+            oa, ob = pl(xa), bpl(xb)
+            (oa.float().pow(2).mean()).backward()
+            (ob.float().pow(2).mean()).backward()
+            torch.cuda.synchronize()
+            heap.check_status("moe placement")
+
+            def close(a, b, what, tol=5e-2):
+                err = (a.float() - b.float()).abs().max().item()
+                den = b.float().abs().max().item() + 1e-6
+                assert err < tol * den, f"rank {rank} step {step} placement {what}: err {err} vs {den}"
+
+            close(oa, ob, "out")
+            close(xa.grad, xb.grad, "dx")
+            dg, du = gemm.deinterleave_gate_up(pl.w13.grad)
+            for le, e in enumerate(pl.local_experts):           # same homes in both arms: local index le holds expert e
+                slot = pl.epr + pl.cfg.shadow.index(e) if e in pl.cfg.shadow else le
+                close(dg[slot], bpl.w13.grad[le, :F], f"dWgate expert {e}")
+                close(du[slot], bpl.w13.grad[le, F:], f"dWup expert {e}")
+                close(pl.w2.grad[slot], bpl.w2.grad[le], f"dW2 expert {e}")
+            for m in (pl, bpl):
+                m.zero_grad(set_to_none=True)
+            if step == 0:
+                chosen = pl.rebalance(tolerance=0.0)            # tolerance 0: shadows are chosen whenever a rank is above the mean
+                rows = pl.ws.counts_now().sum().to(torch.float64).reshape(1)
+        # after the rebalance every rank computes about the mean number of rows
+        rows = pl.ws.counts_now().sum().to(torch.float64).reshape(1)
+        hi = rows.clone(); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        if any(e >= 0 for e in pl.cfg.shadow):
+            assert float(hi) <= 1.15 * cfg.tokens * cfg.topk, (rank, float(hi), pl.cfg.shadow)
 
     # ---- DLRM: fused embedding-bag + all-to-all vs EmbeddingBag + NCCL ------------------------------------
     dcfg = DLRMConfig(num_tables=10, rows=4000, dim=128, pooling=20, global_batch=64 * world, lr=0.05)

@@ -542,10 +542,10 @@ def _default_step_trace(world, sgd, placement=None):
 @pytest.mark.parametrize("world", [1, 2, 4])
 @pytest.mark.parametrize("sgd", [0.0, 0.05])
 def test_default_moe_step_hands_the_kernels_exactly_the_recorded_work(world, sgd):
-    """The default configuration of the fused MoE step is the one that was run and measured on B200.  Its device calls --
-    which entry point, in which order, with which scalars, tensor shapes, and addresses relative to the heap -- are pinned
-    to a recorded digest, so an edit of the Python side that changes what the kernels are given (new options must leave
-    the default alone) shows up here, on a machine without a GPU."""
+    """The device calls of the default fused MoE step -- which entry point, in which order, with which scalars, tensor
+    shapes, and addresses relative to the heap -- are pinned to a recorded digest, so an edit of the Python side that
+    changes what the kernels are given (new options must leave the default alone) shows up here, on a machine without a
+    GPU.  After a deliberate change of the default step the digests are recorded again."""
     import hashlib
     import json
     import os
