@@ -83,7 +83,7 @@ def main():
     if args.sweep:
         from fuselink_b200._ext import require_native
         C = require_native()
-        for pair in (0, 1):
+        for pair in (0, 1, 2):
             C.gemm_set_variant(pair)
             for gm in (4, 8, 16, 32):
                 sched["group_m"] = gm

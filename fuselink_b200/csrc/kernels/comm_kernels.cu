@@ -89,12 +89,14 @@ __global__ void __launch_bounds__(1024) put_chunks_kernel(const FlPutArgs a) {
   __syncthreads();
 
   unsigned long long chunks_before = 0;
-  for (int si = 0; si < a.nseg; ++si) {
+  bool live = true;
+  for (int si = 0; si < a.nseg && live; ++si) {
     const FlSeg& sg = a.seg[si];
     const unsigned long long nch = (sg.bytes + a.chunk_bytes - 1) / a.chunk_bytes;
+    unsigned long long done_here = 0;      // thread 0: bytes of this segment this CTA has finished
     // CTAs take chunks round-robin over the concatenation of all segments
     unsigned long long first = (blockIdx.x + gridDim.x - (chunks_before % gridDim.x)) % gridDim.x;
-    for (unsigned long long c = first; c < nch; c += gridDim.x) {
+    for (unsigned long long c = first; c < nch && live; c += gridDim.x) {
       const unsigned long long off = c * a.chunk_bytes;
       const unsigned long long len = (sg.bytes - off) < a.chunk_bytes ? (sg.bytes - off) : a.chunk_bytes;
       if (sg.wait_flags) {
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(1024) put_chunks_kernel(const FlPutArgs a) {
         __syncthreads();
         const int okv = wait_ok;
         __syncthreads();
-        if (!okv) return;
+        if (!okv) { live = false; break; }
       }
       const uint8_t* s = reinterpret_cast<const uint8_t*>(sg.src) + off;
       uint8_t* d = reinterpret_cast<uint8_t*>(sg.dst) + off;
@@ -116,17 +118,36 @@ __global__ void __launch_bounds__(1024) put_chunks_kernel(const FlPutArgs a) {
         copy_vec(s, d, len);
       }
       __syncthreads();
-      if (abort_flag) return;
+      if (abort_flag) { live = false; break; }
+      // The flag update is itself a release at system scope: it orders this thread's bulk stores (complete, see
+      // copy_bulk) and, through the barrier above, the other threads' stores before the flag becomes visible.
       if (threadIdx.x == 0 && sg.flag_mode != FL_FLAG_NONE) {
-        fence_sys();
         if (sg.flag_mode == FL_FLAG_SEQ_PER_CHUNK) st_release_sys(sg.flags + c, a.seq);
         else red_release_sys_add(sg.flags, 1u);
       }
       // device-side completion counter: the host monitor folds it into the path's completed bytes
-      if (threadIdx.x == 0 && sg.bytes_done != nullptr) atomicAdd_system(sg.bytes_done, (unsigned long long)len);
+      if (threadIdx.x == 0 && sg.bytes_done != nullptr) {
+        if (a.done_scratch != nullptr) done_here += len;
+        else atomicAdd_system(sg.bytes_done, (unsigned long long)len);
+      }
     }
+    if (threadIdx.x == 0 && done_here != 0) atomicAdd(a.done_scratch + si, done_here);
     chunks_before += nch;
   }
+  if (a.done_scratch != nullptr && threadIdx.x == 0) {
+    // every CTA takes a ticket, also one that gave up a wait; the last one forwards the totals and rearms the words
+    __threadfence();
+    const unsigned long long ticket = atomicAdd(a.done_scratch + FL_MAX_SEGS, 1ull);
+    if (ticket == (unsigned long long)gridDim.x - 1) {
+      __threadfence();
+      for (int si = 0; si < a.nseg; ++si) {
+        const unsigned long long total = atomicExch(a.done_scratch + si, 0ull);
+        if (total != 0 && a.seg[si].bytes_done != nullptr) atomicAdd_system(a.seg[si].bytes_done, total);
+      }
+      atomicExch(a.done_scratch + FL_MAX_SEGS, 0ull);
+    }
+  }
+  if (!live) return;
   if (blockIdx.x == 0 && (int)threadIdx.x < a.nwait)
     wait_flag_ge(a.wait_flag[threadIdx.x], a.wait_want[threadIdx.x], a.status, 650 + threadIdx.x);
 }

@@ -42,6 +42,11 @@ struct FlPutArgs {
   const uint32_t* wait_flag[8];
   unsigned int wait_want[8];
   int nwait;
+  // optional, with bytes_done: FL_MAX_SEGS + 1 zeroed 64-bit words of DEVICE memory owned by the caller's channel.  The
+  // CTAs add up their finished bytes there and the last CTA of the launch forwards one total per segment to bytes_done, so
+  // a launch costs one host-memory atomic per segment instead of one per chunk (each takes about a microsecond over PCIe
+  // and they serialise).  Launches that share the words must be stream-ordered.  Null: one host atomic per chunk.
+  unsigned long long* done_scratch;
 };
 
 struct FlWaitArgs {

@@ -64,7 +64,9 @@ extern "C" {
 // Returns 0 on success, a negative value for a rejected description, a positive cudaError otherwise.
 int fl_grouped_gemm(const FlGemmDesc* desc, cudaStream_t stream);
 const char* fl_gemm_last_error(void);
-// 0: one CTA per 128 x 256 tile; 1: CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2).  Default: FUSELINK_GEMM_PAIR or 1.
+// 0: one CTA per 128 x 256 tile; 1: CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2, two accumulators); 2: CTA pairs on
+// 256 x 512 tiles (one accumulator handed back in halves); 3: chosen per launch from the shape and the epilogue.
+// Default: FUSELINK_GEMM_PAIR or 3.
 void fl_gemm_set_variant(int pair);
 int fl_gemm_get_variant(void);
 #ifdef __cplusplus

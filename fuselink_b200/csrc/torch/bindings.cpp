@@ -69,7 +69,7 @@ static void grouped_gemm(int64_t group_mode, int64_t num_groups, int64_t cap, in
 // segs: list of (src_addr, dst_addr, bytes, flags_addr, flag_mode, wait_flags_addr)
 static void put_chunks(const std::vector<std::tuple<int64_t, int64_t, int64_t, int64_t, int64_t, int64_t>>& segs,
                        int64_t chunk_bytes, int64_t seq, bool use_bulk, int64_t num_ctas, int64_t threads,
-                       int64_t status_addr, const std::vector<int64_t>& counters) {
+                       int64_t status_addr, const std::vector<int64_t>& counters, int64_t counter_scratch) {
   FlPutArgs a;
   memset(&a, 0, sizeof a);
   TORCH_CHECK(segs.size() >= 1 && segs.size() <= FL_MAX_SEGS, "1..8 segments per launch");
@@ -85,6 +85,7 @@ static void put_chunks(const std::vector<std::tuple<int64_t, int64_t, int64_t, i
   }
   a.chunk_bytes = (unsigned)chunk_bytes; a.seq = (unsigned)seq; a.use_bulk = use_bulk;
   a.status = reinterpret_cast<int*>(status_addr);
+  a.done_scratch = reinterpret_cast<unsigned long long*>(counter_scratch);
   check_rc(fl_put_chunks(&a, (int)num_ctas, (int)threads, cur_stream()), "fl_put_chunks");
 }
 static void all_to_all(int64_t send_addr, const std::vector<int64_t>& recv_peers, int64_t bytes_per_peer, int64_t rank,
@@ -303,7 +304,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fp8_quantize_blocks", &fp8_quantize_blocks);
   m.def("fp8_grouped_gemm", &fp8_grouped_gemm);
   m.def("put_chunks", &put_chunks, py::arg("segs"), py::arg("chunk_bytes"), py::arg("seq"), py::arg("use_bulk"), py::arg("num_ctas"),
-        py::arg("threads"), py::arg("status_addr"), py::arg("counters") = std::vector<int64_t>());
+        py::arg("threads"), py::arg("status_addr"), py::arg("counters") = std::vector<int64_t>(), py::arg("counter_scratch") = 0);
   m.def("wait_flags", &wait_flags, py::arg("flags"), py::arg("status_addr"), py::arg("limit_ms") = 0);
   m.def("all_to_all", &all_to_all);
   m.def("barrier", &barrier);

@@ -34,13 +34,22 @@ def chunking(nbytes: int, chunk_bytes: Optional[int] = None) -> Tuple[int, int]:
     c = cfg
     # about one chunk per SM for mid sizes; a chunk is never cut below 64 KiB (a CTA streams it through a ring of
     # 16 KiB slots, and every chunk costs one remote flag update)
-    while c > 64 * 1024 and nbytes // c < _NUM_SMS:
+    while c > _chunk_min() and nbytes // c < _NUM_SMS:
         c //= 2
     c = max(16, (c + 15) // 16 * 16)
     return c, (nbytes + c - 1) // c
 
 
 _CHUNK_DEFAULT = None
+_CHUNK_MIN = None
+
+
+def _chunk_min() -> int:
+    global _CHUNK_MIN
+    if _CHUNK_MIN is None:
+        _CHUNK_MIN = max(16, knobs().chunk_min_bytes)
+    return _CHUNK_MIN
+
 
 
 def _chunk_default() -> int:
@@ -78,6 +87,9 @@ class Channel:
         kernel adds to (system-scope atomics) and the monitor's sweeper thread reads (`fl_monitor_attach_counters`)."""
         self.counters = torch.zeros(max(self.heap.world, 64), dtype=torch.int64).pin_memory()
         self.C.monitor_attach_counters(selector.mon, 0, self.counters.data_ptr())
+        # device words in which a launch adds up its finished bytes, so that it touches the host counter once (see FlPutArgs)
+        dev = self.heap.status().device
+        self.counter_scratch = torch.zeros(16, dtype=torch.int64, device=dev) if dev.type == "cuda" else None
         return self.counters
 
     # -- sender ------------------------------------------------------------------------------------
@@ -93,7 +105,8 @@ class Channel:
                self.heap.sig_addr(self.slot0 + self.heap.rank, dst_rank), FLAG_COUNT, 0)
         ctas, threads = _launch_shape(n, self.engine)
         ctr = [self.counters.data_ptr() + 8 * dst_rank] if self.counters is not None else []
-        self.C.put_chunks([seg], cb, 0, self.engine == "bulk", ctas, threads, self.heap.status_addr, ctr)
+        scratch = self.counter_scratch.data_ptr() if ctr and getattr(self, "counter_scratch", None) is not None else 0
+        self.C.put_chunks([seg], cb, 0, self.engine == "bulk", ctas, threads, self.heap.status_addr, ctr, scratch)
         return n
 
     def put_many(self, items: Sequence[Tuple[int, int, int, int]], chunk_bytes: int) -> None:

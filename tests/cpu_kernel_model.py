@@ -81,7 +81,7 @@ class Model:
             finally:
                 fcntl.flock(f, fcntl.LOCK_UN)
 
-    def put_chunks(self, segs, chunk_bytes, seq, use_bulk, num_ctas, threads, status_addr, counters=()):
+    def put_chunks(self, segs, chunk_bytes, seq, use_bulk, num_ctas, threads, status_addr, counters=(), counter_scratch=0):
         for i, (src, dst, nbytes, flags, mode, wait_flags) in enumerate(segs):
             nchunks = (nbytes + chunk_bytes - 1) // chunk_bytes
             for c in range(nchunks):

@@ -6,12 +6,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["single", "pair"])
+@pytest.fixture(autouse=True, params=["single", "pair", "wide"])
 def _variant(request):
-    """Every test runs on both kernels: one CTA per 128x256 tile, and CTA pairs on 256x256 tiles (cta_group::2)."""
+    """Every test runs on the three kernels: one CTA per 128x256 tile, CTA pairs on 256x256 tiles (cta_group::2, two
+    accumulators), and CTA pairs on 256x512 tiles (one accumulator handed back in halves)."""
     from fuselink_b200 import C
     before = C.gemm_get_variant()
-    C.gemm_set_variant(1 if request.param == "pair" else 0)
+    C.gemm_set_variant({"single": 0, "pair": 1, "wide": 2}[request.param])
     yield request.param
     C.gemm_set_variant(before)
 

@@ -166,13 +166,21 @@ def test_rehoming_onto_the_other_gpu_and_back(C):
     away = C.vmm_remap_slab(r, 0, 1, True, [0, 1])
     assert C.vmm_ptr(r) == ptr and C.vmm_slab_device(r, 0) == 1 and C.vmm_ptr2dev(ptr + 4096) == 1
     assert C.vmm_usage(1) - u1 == size and C.vmm_usage(0) == u0
-    v = _view(C, r, n)                                     # a GPU 0 kernel through the same address
-    assert torch.equal(v, _pattern(n, 41))
-    v.mul_(2)
-    torch.cuda.synchronize()
-    on1 = C.tensor_from_ptr(ptr, [n], torch.int32, 1)      # and GPU 1 sees what GPU 0 wrote: the memory is its own now
+    # GPU 0 kernels through the same address (this library's copy kernel, launched on GPU 0; PyTorch itself refuses to wrap
+    # the pointer as a cuda:0 tensor because the driver now reports GPU 1 as its home -- which is the point)
+    def gpu0_copy(dst_addr, src_addr, nbytes):
+        with torch.cuda.device(0):
+            C.put_chunks([(src_addr, dst_addr, nbytes, 0, 0, 0)], 1 << 20, 0, False, 64, 512, 0)
+            torch.cuda.synchronize()
+
+    got = torch.empty(n, dtype=torch.int32, device="cuda:0")
+    gpu0_copy(got.data_ptr(), ptr, size)
+    assert torch.equal(got, _pattern(n, 41))
+    twice = _pattern(n, 41) * 2
+    gpu0_copy(ptr, twice.data_ptr(), size)                 # GPU 0 writes through the pointer, over NVLink
+    on1 = C.tensor_from_ptr(ptr, [n], torch.int32, 1)      # and GPU 1 sees it in what is now its own memory
     with torch.cuda.device(1):
-        assert torch.equal(on1.to("cuda:0"), _pattern(n, 41) * 2)
+        assert torch.equal(on1.to("cuda:0"), twice)
         torch.cuda.synchronize()
     home = C.vmm_remap_slab(r, 0, 0, True, [0])
     assert C.vmm_slab_device(r, 0) == 0 and C.vmm_usage(1) == u1 and C.vmm_usage(0) - u0 == size
