@@ -87,27 +87,32 @@ class ClockSampler:
 
 
 class ResultLine:
-    """Prints the result line exactly once: from the main thread when the run completes, or from a timer when the part of
-    the run that follows the device-timed region (the end-to-end region: a rank may raise there while the others wait in
-    a collective) has not finished within its limit -- the line then carries an error in place of that part, and the
-    process ends with status 0 because the device-timed result is valid."""
+    """Prints the result line exactly once: from the main thread when the run completes, or from a timer when what
+    follows the device-timed region (the end-to-end region, the stock arm, the other metrics: a rank may raise there while
+    the others wait in a collective) has not finished within its limit -- the line then carries what was complete by
+    then plus a note, and the process ends with status 0 because the device-timed result is valid.  ``parts`` is filled
+    in by the caller as the sections complete; ``make_line(parts)`` builds the line."""
 
-    def __init__(self, rank: int, make_line):
+    def __init__(self, rank: int, make_line, parts=None):
         self.rank, self.make_line = rank, make_line
+        self.parts = parts if parts is not None else {}
         self.lock, self.printed, self.timer = threading.Lock(), False, None
 
-    def emit(self, e2e, roof, *more) -> None:
+    def emit(self) -> None:
         with self.lock:
             if self.printed:
                 return
             self.printed = True
             if self.rank == 0:
-                print(json.dumps(self.make_line(e2e, roof, *more)))
+                print(json.dumps(self.make_line(self.parts)))
             sys.stdout.flush()
 
     def arm(self, limit_s: float) -> None:
         def give_up():
-            self.emit({"error": "the end-to-end region did not finish within its time limit"}, None)
+            self.parts["unfinished"] = "a section after the device-timed region did not finish within its time limit"
+            if self.parts.get("e2e") is None:
+                self.parts["e2e"] = {"error": "the end-to-end region did not finish within its time limit"}
+            self.emit()
             os._exit(0)
 
         self.timer = threading.Timer(limit_s, give_up)
@@ -147,9 +152,112 @@ def parse():
                          "the router's bias favours most, their rows computed where they originate.  0: none")
     ap.add_argument("--shadow-slots", type=int, default=4, help="copy slots every rank reserves with --shadow auto (unused ones cost nothing per step)")
     ap.add_argument("--tolerance", type=float, default=0.05)
+    ap.add_argument("--no-other", action="store_true", help="skip the p2p / all-to-all / DLRM numbers that follow the MoE arms")
     ap.add_argument("--no-baseline", action="store_true", help="skip the PyTorch + NCCL arm that follows the fuselink arm in the same process")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="fp8: block-scaled e4m3 (1x128) forward/dgrad GEMMs")
     return ap.parse_args()
+
+
+def other_metrics(rank, world, local_rank, dev):
+    """The rest of the headline metric -- p2p GB/s (GPU 0 -> GPU 1, 16 MiB and 1 GiB), all-to-all bus GB/s (128 MiB per
+    pair) and DLRM samples/s (26 tables x 1M x 128 fp32, batch 65536, SGD) -- each beside its stock counterpart (NCCL
+    send/recv, NCCL all_to_all_single, EmbeddingBag + NCCL all-to-all), measured in this process on the same GPUs:
+    CUDA events, max over ranks, short loops.  The sweeps over every size are bench/p2p_sweep.py and bench/a2a_sweep.py."""
+    import torch
+    import torch.distributed as dist
+
+    from fuselink_b200.ops.comm import Channel, all_to_all
+    from fuselink_b200.parallel.symm import SymmetricHeap, SymTensor
+
+    def timed(fn, warmup, iters):
+        for _ in range(warmup):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    out = {}
+    if world >= 2:
+        big, per = 1 << 30, 128 << 20
+        heap = SymmetricHeap.create(big + world * per + (64 << 20), device=local_rank)
+        try:
+            dst = heap.alloc_tensor([big], torch.uint8)
+            src = torch.randint(0, 255, (big,), dtype=torch.uint8, device=dev)
+            ch = Channel(heap, "bench-p2p", engine="bulk")
+            p2p = {}
+            for nbytes in (16 << 20, 1 << 30):
+                def ours():
+                    if rank == 0:
+                        ch.put(src, 1, dst.offset, nbytes)
+                    elif rank == 1:
+                        ch.expect(0, nbytes)
+                        ch.wait([0])
+
+                def stock():
+                    if rank == 0:
+                        dist.send(src[:nbytes], 1)
+                    elif rank == 1:
+                        dist.recv(dst.local[:nbytes], 0)
+                iters = 50 if nbytes < (1 << 28) else 15
+                a, b = timed(ours, 5, iters), timed(stock, 5, iters)
+                p2p[str(nbytes)] = {"fuselink_GBs": nbytes / a / 1e6, "nccl_GBs": nbytes / b / 1e6, "ratio": b / a}
+            out["p2p_GBs"] = p2p
+            recv = heap.alloc_tensor([world, per], torch.uint8)
+            send = src[: world * per].view(world, per)
+            ref = torch.empty(world * per, dtype=torch.uint8, device=dev)
+            ca = Channel(heap, "bench-a2a", engine="bulk")
+            a = timed(lambda: all_to_all(ca, send, recv), 3, 10)
+            b = timed(lambda: dist.all_to_all_single(ref, send.view(-1)), 3, 10)
+            same = bool(torch.equal(recv.local.view(-1), ref))
+            out["a2a_busGBs"] = {"per_pair_bytes": per, "fuselink": per * (world - 1) / a / 1e6, "nccl": per * (world - 1) / b / 1e6,
+                                 "ratio": b / a, "equal_to_nccl": same}
+            heap.check_status("bench p2p / all-to-all")
+            del dst, src, recv, send, ref
+        finally:
+            heap.close()
+        torch.cuda.empty_cache()
+
+    # DLRM, both arms
+    from fuselink_b200.models.dlrm import DLRM, DLRMConfig, synthetic_batch
+    from fuselink_b200.models.dlrm_baseline import BaselineDLRM
+    torch.backends.cuda.matmul.allow_tf32 = True
+    cfg = DLRMConfig()
+    batches = [synthetic_batch(cfg, rank, world, dev, seed=s_) for s_ in range(2)]
+    res = {}
+    for arm in ("fuselink", "nccl"):
+        heap = None
+        if arm == "fuselink":
+            bl = cfg.global_batch // world
+            heap = SymmetricHeap.create(2 * bl * cfg.num_tables * cfg.dim * 4 + (16 << 20), device=local_rank)
+            model = DLRM(cfg, heap, rank, world, device=dev)
+        else:
+            model = BaselineDLRM(cfg, rank, world, device=dev)
+        opt = torch.optim.SGD(model.dense_parameters(), lr=cfg.lr)
+        i = [0]
+
+        def step():
+            model.train_step(*batches[i[0] % 2], opt)
+            i[0] += 1
+        ms = timed(step, 3, 8)
+        res[arm] = cfg.global_batch / (ms / 1e3)
+        if heap is not None:
+            heap.check_status("bench dlrm")
+            heap.close()
+        del model, opt
+        torch.cuda.empty_cache()
+    out["dlrm_samples_s"] = {"fuselink": res["fuselink"], "pytorch_nccl": res["nccl"], "ratio": res["fuselink"] / res["nccl"],
+                             "config": "26 tables x 1M x 128 fp32 table-wise, pooling 20, Zipf(1.05), global batch 65536, SGD 0.01"}
+    return out
 
 
 def stock_arm(args, cfg, rank, world, dev, xs, fuselink_value):
@@ -324,7 +432,8 @@ def main():
         placed = layer.homes.tolist()
     placed = list(placed) if placed and list(placed) != list(range(len(placed))) else None
 
-    def make_line(e2e, roof, base=None):
+    def make_line(parts):
+        e2e, roof, base = parts.get("e2e"), parts.get("roofline"), parts.get("vs_baseline")
         flops_per_token = cfg.topk * 3 * 2 * cfg.hidden * cfg.ffn * 3       # 3 GEMM-equivalents, fwd + 2x bwd
         return {
             "metric": "MoE-EP tokens/s (fwd+bwd+SGD)", "value": value, "unit": "tokens/s", "n_gpus": world,
@@ -341,12 +450,15 @@ def main():
                        "l2_policy": "per-step working set (expert weights + activations, > 1 GB) is larger than the 126 MB L2"},
             "tflops_per_gpu": flops_per_token * T * args.steps / (ms / 1e3) / 1e12,
             "clocks": clocks, "e2e": e2e, "gpu_launches": n_launch, "roofline": roof,
+            **({"other_metrics": parts["other_metrics"]} if parts.get("other_metrics") is not None else {}),
+            **({"unfinished": parts["unfinished"]} if "unfinished" in parts else {}),
             **({"host_mode": "device entry points modelled on the host: plumbing check, not a measurement"} if cpu else {}),
         }
 
     # The device-timed number exists from here on: whatever happens next, the line is printed exactly once.
-    result = ResultLine(rank, make_line)
-    result.arm(max(240.0, 40.0 * ms / 1e3))
+    parts = {}
+    result = ResultLine(rank, make_line, parts)
+    result.arm(max(300.0, 60.0 * ms / 1e3))
 
     # ---------------------------------------------------------------- end-to-end region (public API)
     e2e = None
@@ -399,12 +511,12 @@ def main():
             ems = torch.tensor([f0.elapsed_time(f1)], device=dev, dtype=torch.float64)
             if world > 1:
                 dist.all_reduce(ems, op=dist.ReduceOp.MAX)
-            e2e = {"value": world * T * args.steps / (float(ems.item()) / 1e3), "unit": "tokens/s",
+            parts["e2e"] = e2e = {"value": world * T * args.steps / (float(ems.item()) / 1e3), "unit": "tokens/s",
                    "h2d_bytes_per_step": T * H * 2, "d2h_bytes_per_step": 4, "last_loss": loss_host}
             if heap is not None:
                 heap.check_status("e2e region")
         except Exception as e:  # noqa: BLE001 - the device-timed line above must still be reported
-            e2e = {"error": repr(e)}
+            parts["e2e"] = e2e = {"error": repr(e)}
             try:
                 if not cpu:
                     torch.cuda.synchronize()
@@ -427,6 +539,7 @@ def main():
                     "definition": "max(FLOPs / measured sustained cuBLAS bf16, NVLink bytes / 770 GB/s) on the rank with most routed rows"}
     except Exception as e:  # noqa: BLE001 - reporting only
         roof = {"error": repr(e)}
+    parts["roofline"] = roof
 
     # ---------------------------------------------------------------- the stock arm, same process, same steps
     base = None
@@ -435,9 +548,22 @@ def main():
             base = stock_arm(args, cfg, rank, world, dev, xs, value)
         except Exception as e:  # noqa: BLE001 - the fuselink numbers above must still be reported
             base = {"impl": "pytorch+nccl", "error": repr(e), "ratio": None}
+    parts["vs_baseline"] = base
+
+    # ---------------------------------------------------------------- the rest of the headline metric
+    if args.impl == "fuselink" and not args.no_other and not cpu:
+        layer = opt = None                       # the MoE arm's memory is not needed any more
+        if heap is not None:
+            heap.close()
+            heap = None
+        torch.cuda.empty_cache()
+        try:
+            parts["other_metrics"] = other_metrics(rank, world, local_rank, dev)
+        except Exception as e:  # noqa: BLE001
+            parts["other_metrics"] = {"error": repr(e)}
 
     result.disarm()
-    result.emit(e2e, roof, base)
+    result.emit()
     # the result is out: teardown must never be able to hang the job (a watchdog ends the process after 60 s)
     sys.stdout.flush()
     wd = threading.Timer(60.0, lambda: os._exit(0))

@@ -107,10 +107,11 @@ def test_bench_result_line_is_printed_once_even_when_the_run_stalls():
     import sys
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     code = ("import sys, time; sys.path.insert(0, %r); import bench\n"
-            "r = bench.ResultLine(0, lambda e2e, roof: {'value': 1.5, 'e2e': e2e, 'roofline': roof})\n"
+            "parts = {}\n"
+            "r = bench.ResultLine(0, lambda p: {'value': 1.5, 'e2e': p.get('e2e'), 'roofline': p.get('roofline')}, parts)\n"
             "mode = sys.argv[1]\n"
             "if mode == 'twice':\n"
-            "    r.arm(30.0); r.disarm(); r.emit({'value': 2}, {'x': 1}); r.emit({'value': 3}, None)\n"
+            "    r.arm(30.0); r.disarm(); parts['e2e'] = {'value': 2}; parts['roofline'] = {'x': 1}; r.emit(); parts['e2e'] = {'value': 3}; r.emit()\n"
             "else:\n"
             "    r.arm(0.3); time.sleep(20); print('never')\n") % root
     twice = subprocess.run([sys.executable, "-c", code, "twice"], capture_output=True, text=True, timeout=60)
