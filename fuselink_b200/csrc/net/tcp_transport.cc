@@ -46,9 +46,16 @@ static void map_v4(const sockaddr_in* v4, sockaddr_in6* out) {
   memcpy(&out->sin6_addr.s6_addr[12], &v4->sin_addr, 4);
 }
 
+// Whether `a` (IPv4, mapped) lies in the subnet of the interface address `ifa` / `mask`.
+static bool same_subnet_v4(const sockaddr_in* ifa, const sockaddr_in* mask, const in_addr& a) {
+  return (ifa->sin_addr.s_addr & mask->sin_addr.s_addr) == (a.s_addr & mask->sin_addr.s_addr);
+}
+
 // Interface selection: NCCL_SOCKET_IFNAME is a comma list of prefixes ("^" excludes, "=" exact), as in the
-// reference's OOB code (src/extern/socket.cc:86-99,323-357).  Without it: first non-loopback interface
-// that is up, else loopback.
+// reference's OOB code (src/extern/socket.cc:86-99,323-357).  Without it the reference's order of preference
+// applies: an "ib*" interface, else the interface in the subnet of the address in NCCL_COMM_ID ("ip:port", the
+// rendezvous address some launchers export), else anything that is neither docker nor loopback, else docker,
+// else loopback.
 int pick_listen_addr(sockaddr_in6* out) {
   const Params& p = params();
   std::string spec = p.socket_ifname;
@@ -74,6 +81,19 @@ int pick_listen_addr(sockaddr_in6* out) {
   bool found = false;
   sockaddr_in6 loop;
   bool have_loop = false;
+  // the address NCCL_COMM_ID names, if it is an IPv4 "a.b.c.d:port"
+  in_addr comm_id_addr;
+  bool have_comm_id = false;
+  if (names.empty()) {
+    const char* cid = getenv("NCCL_COMM_ID");
+    if (cid && strlen(cid) > 1) {
+      std::string host(cid);
+      const size_t colon = host.rfind(':');
+      if (colon != std::string::npos && host.find(':') == colon) host = host.substr(0, colon);
+      have_comm_id = inet_pton(AF_INET, host.c_str(), &comm_id_addr) == 1;
+    }
+  }
+  int best_rank = 100;   // without NCCL_SOCKET_IFNAME: 0 ib*, 1 subnet of NCCL_COMM_ID, 2 other, 3 docker (loopback apart)
   if (getifaddrs(&ifs) == 0) {
     for (ifaddrs* i = ifs; i && !found; i = i->ifa_next) {
       if (!i->ifa_addr || !(i->ifa_flags & IFF_UP)) continue;
@@ -91,11 +111,18 @@ int pick_listen_addr(sockaddr_in6* out) {
       } else if (is_loop) {
         if (!have_loop && fam == AF_INET) { loop = a; have_loop = true; }
       } else if (fam == AF_INET || want6) {
-        *out = a; found = true;
+        int rank = 2;
+        if (strncmp(i->ifa_name, "ib", 2) == 0) rank = 0;
+        else if (have_comm_id && fam == AF_INET && i->ifa_netmask &&
+                 same_subnet_v4(reinterpret_cast<sockaddr_in*>(i->ifa_addr), reinterpret_cast<sockaddr_in*>(i->ifa_netmask), comm_id_addr))
+          rank = 1;
+        else if (strncmp(i->ifa_name, "docker", 6) == 0) rank = 3;
+        if (rank < best_rank) { best_rank = rank; *out = a; }
       }
     }
     freeifaddrs(ifs);
   }
+  if (best_rank < 100) found = true;
   if (!found) {
     if (have_loop) { *out = loop; return 0; }
     sockaddr_in v4;

@@ -1,4 +1,4 @@
-"""Roofline arithmetic against the MEASURED peaks of this pool's B200s.
+"""Roofline arithmetic against MEASURED peaks of the B200s the numbers were taken on.
 
 The denominators are a plain device copy and a cuBLAS bf16 GEMM measured on the same GPUs (file
 ``MEASURED_PEAKS.json`` at the repository root when present, otherwise the stated fallback), so a fraction a
@@ -11,7 +11,7 @@ from dataclasses import dataclass
 
 _ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-NVLINK_PEER_GBS = 770.0        # measured peer copy per direction on this pool (nominal 900)
+NVLINK_PEER_GBS = 770.0        # measured peer copy per direction over NVLink 5 / NVSwitch (nominal 900)
 NVLINK_ALLREDUCE_BUS_GBS = 725.0
 
 
