@@ -172,6 +172,16 @@ extern "C" int fl_moe_dispatch(const FlMoeDispatchArgs* a, cudaStream_t stream) 
   return (int)cudaGetLastError();
 }
 
+extern "C" int fl_moe_dispatch_preload(void) {
+  // makes the runtime load the three dispatch kernels on the current device now (module loading may allocate and
+  // synchronise) instead of at their first launch
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, fl::moe_count_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, fl::moe_reserve_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, fl::moe_scatter_kernel);
+  return (int)e;
+}
+
 extern "C" int fl_moe_zero_tail(void* buf, const int* counts, int experts_local, int cap, int width,
                                 cudaStream_t stream) {
   if (width % 8 || experts_local < 1) return -1;

@@ -32,6 +32,8 @@ extern "C" {
 #endif
 // forward: count -> reserve (one system-scope atomic per expert) -> scatter.  backward: scatter only.
 int fl_moe_dispatch(const FlMoeDispatchArgs* a, cudaStream_t stream);
+// load the dispatch kernels on the current device now rather than at their first launch; returns a cudaError
+int fl_moe_dispatch_preload(void);
 // zero rows [counts[e], roundup(counts[e], 128)) of a grouped [E_local * cap, width] bf16 buffer
 int fl_moe_zero_tail(void* buf, const int* counts, int experts_local, int cap, int width, cudaStream_t stream);
 // out[t] = sum_k w[t,k] * slots[t*topk + k]   (w == nullptr => plain sum)

@@ -50,12 +50,35 @@ int scratch_for_current_device(void** out) {
 
 extern "C" const char* fl_moe_dispatch_noalloc_error(void) { return g_err; }
 
+extern "C" int fl_moe_dispatch_noalloc_setup(void) {
+  g_err[0] = 0;
+  void* scratch = nullptr;
+  int rc = scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, clear_counters_kernel);
+  if (e == cudaSuccess) e = (cudaError_t)fl_moe_dispatch_preload();
+  if (e != cudaSuccess) {
+    snprintf(g_err, sizeof g_err, "loading the dispatch kernels failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
 extern "C" int fl_moe_dispatch_noalloc(const FlMoeDispatchNoAllocArgs* in, cudaStream_t stream) {
   g_err[0] = 0;
-  if (!in || in->tokens < 0 || in->topk < 1 || in->num_experts < 1) {
-    snprintf(g_err, sizeof g_err, "bad arguments");
-    return -1;
-  }
+  auto bad = [](int code, const char* why) {
+    snprintf(g_err, sizeof g_err, "%s", why);
+    return code;
+  };
+  // everything fl_moe_dispatch would refuse is refused here, before anything is enqueued
+  if (!in) return bad(FL_NOALLOC_E_ARGS, "null argument block");
+  if (in->tokens < 0 || in->topk < 1 || in->num_experts < 1) return bad(FL_NOALLOC_E_ARGS, "tokens >= 0, topk >= 1 and num_experts >= 1 are required");
+  if (in->hidden <= 0 || in->hidden % 8) return bad(FL_NOALLOC_E_ARGS, "hidden must be a positive multiple of 8 (16-byte rows pieces)");
+  if (in->world < 1 || in->world > 8 || in->rank < 0 || in->rank >= in->world) return bad(FL_NOALLOC_E_ARGS, "1 <= world <= 8 and 0 <= rank < world are required");
+  if (in->experts_per_rank < 1 || (long long)in->experts_per_rank * in->world != in->num_experts)
+    return bad(FL_NOALLOC_E_ARGS, "experts_per_rank * world must equal num_experts");
+  if (in->cap <= 0) return bad(FL_NOALLOC_E_ARGS, "cap must be positive");
   const long long assignments = (long long)in->tokens * in->topk;
   if (assignments > FL_NOALLOC_MAX_ASSIGNMENTS || in->num_experts > FL_NOALLOC_MAX_EXPERTS) {
     snprintf(g_err, sizeof g_err,
@@ -87,6 +110,12 @@ extern "C" int fl_moe_dispatch_noalloc(const FlMoeDispatchNoAllocArgs* in, cudaS
 
   clear_counters_kernel<<<1, 256, 0, stream>>>(FL_NOALLOC_MAX_EXPERTS);
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  return fl_moe_dispatch(&a, stream);
+  if (e != cudaSuccess) {
+    snprintf(g_err, sizeof g_err, "launch failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  rc = fl_moe_dispatch(&a, stream);
+  if (rc < 0) snprintf(g_err, sizeof g_err, "fl_moe_dispatch refused the arguments (code %d)", rc);
+  else if (rc > 0) snprintf(g_err, sizeof g_err, "launch failed: %s", cudaGetErrorString((cudaError_t)rc));
+  return rc < 0 ? FL_NOALLOC_E_ARGS : rc;
 }

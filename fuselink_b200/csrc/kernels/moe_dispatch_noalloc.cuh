@@ -16,8 +16,12 @@
 // (FL_NOALLOC_SCRATCH_BYTES, about 0.5 MiB) is held by every GPU that loads the library until the process
 // exits.
 //
-// Set-up: the first call on a device resolves the device address of the scratch array (with that device
-// current) and remembers it; make that first call outside any stream capture.
+// Set-up: fl_moe_dispatch_noalloc_setup(), once per device with that device current, from a thread that may
+// synchronise the device: it resolves the device address of the scratch array and makes the runtime load the
+// kernels (loading a module can allocate and synchronise -- exactly what the callers above cannot afford later).
+// Without it the first fl_moe_dispatch_noalloc call on a device does the same work itself; make that first
+// call, or the set-up call, outside any stream capture.  After set-up a call enqueues four kernels and
+// touches no allocator.
 //
 // Sharing: every call on a device uses the same scratch array.  The counters are cleared at the start of
 // each call, so calls may follow one another on one stream, or on several streams if the caller orders
@@ -33,6 +37,7 @@
 
 #define FL_NOALLOC_E_TOO_LARGE (-100)
 #define FL_NOALLOC_E_SETUP (-101)
+#define FL_NOALLOC_E_ARGS (-102)       // an argument is out of range; fl_moe_dispatch_noalloc_error() says which
 
 typedef struct {
   const void* x;              // [tokens, hidden] bf16
@@ -52,8 +57,10 @@ typedef struct {
 #ifdef __cplusplus
 extern "C" {
 #endif
-// Returns 0, a negative FL_NOALLOC_E_* / argument error, or a positive cudaError.
+// Returns 0, a negative FL_NOALLOC_E_*, or a positive cudaError.  Nothing is enqueued unless the arguments are accepted.
 int fl_moe_dispatch_noalloc(const FlMoeDispatchNoAllocArgs* args, cudaStream_t stream);
+// Optional, once per device (see "Set-up" above).  Returns 0, FL_NOALLOC_E_SETUP or a positive cudaError.
+int fl_moe_dispatch_noalloc_setup(void);
 const char* fl_moe_dispatch_noalloc_error(void);
 #ifdef __cplusplus
 }

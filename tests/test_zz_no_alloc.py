@@ -35,6 +35,7 @@ def _lib():
     lib.fl_moe_dispatch_noalloc.argtypes = [ctypes.POINTER(Args), ctypes.c_void_p]
     lib.fl_moe_dispatch_noalloc.restype = ctypes.c_int
     lib.fl_moe_dispatch_noalloc_error.restype = ctypes.c_char_p
+    lib.fl_moe_dispatch_noalloc_setup.restype = ctypes.c_int
     return lib
 
 
@@ -50,6 +51,7 @@ def test_noalloc_dispatch_matches_regular_entry_point():
     T, k, H, E = 1000, 2, 256, 8
     cap = 1024
     stream = torch.cuda.current_stream().cuda_stream
+    assert lib.fl_moe_dispatch_noalloc_setup() == 0, lib.fl_moe_dispatch_noalloc_error()
     for call in range(2):                       # two calls in a row share the built-in scratch
         g = torch.Generator(device="cuda").manual_seed(7 + call)
         x = torch.randn(T, H, generator=g, device="cuda").to(torch.bfloat16)
@@ -75,9 +77,12 @@ def test_noalloc_dispatch_matches_regular_entry_point():
         a.count_peers[0], a.x_peers[0], a.info_peers[0] = cnt_b.data_ptr(), xd_b.data_ptr(), info_b.data_ptr()
         a.parity = parity
         a.status = status.data_ptr()
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = lib.fl_moe_dispatch_noalloc(ctypes.byref(a), ctypes.c_void_p(stream))
         assert rc == 0, lib.fl_moe_dispatch_noalloc_error()
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call must not change the device's free memory"
         assert status[0].item() == 0
         # same per-expert counts; every (token, k) row landed intact in its expert's range; same return info
         assert torch.equal(cnt_a[parity], cnt_b[parity])
@@ -99,3 +104,6 @@ def test_noalloc_dispatch_rejects_oversized_problem():
     rc = lib.fl_moe_dispatch_noalloc(ctypes.byref(a), None)
     assert rc == -100
     assert b"too large" in lib.fl_moe_dispatch_noalloc_error()
+    a.tokens, a.rank = 64, 3                                  # a rank outside the world: refused before anything is enqueued
+    assert lib.fl_moe_dispatch_noalloc(ctypes.byref(a), None) == -102
+    assert b"rank" in lib.fl_moe_dispatch_noalloc_error()
