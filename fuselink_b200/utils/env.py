@@ -33,7 +33,7 @@ class Knobs:
     # framework knobs
     monitor_timeout_us: int = field(default_factory=lambda: _int("FUSELINK_MONITOR_TIMEOUT_US", 160))
     min_stripe_bytes: int = field(default_factory=lambda: _int("FUSELINK_MIN_STRIPE_BYTES", 4 * 1024 * 1024))
-    copy_engine: str = field(default_factory=lambda: os.environ.get("FUSELINK_COPY_ENGINE", "ldst"))  # ldst | bulk
+    copy_engine: str = field(default_factory=lambda: os.environ.get("FUSELINK_COPY_ENGINE", "bulk"))  # bulk | ldst
     copy_ctas: int = field(default_factory=lambda: _int("FUSELINK_COPY_CTAS", 0))
     chunk_min_bytes: int = field(default_factory=lambda: _int("FUSELINK_CHUNK_MIN", 64 * 1024))   # mid sizes are cut into about one chunk per SM, never below this
     steps_in_flight: int = 8  # FUSELINK_STEPS in the reference (src/fuselink.h:14)

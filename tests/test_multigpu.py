@@ -23,8 +23,6 @@ def test_two_or_more_gpus_against_nccl():
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
-@pytest.mark.skipif(os.environ.get("FUSELINK_TEST_UNVERIFIED", "0") != "1",
-                    reason="set FUSELINK_TEST_UNVERIFIED=1 to run tests of code that has not been validated on a GPU yet")
 def test_rank_leaving_between_steps_on_gpus():
     """A rank leaves between steps with nothing in flight; the others learn of it on the host (heartbeat) before their
     next launch and go on among themselves.  NVLS off, plain peer stores, no GPU fault involved."""
