@@ -11,7 +11,8 @@ N(0, 1) activations.  Weak scaling: tokens per GPU fixed, the 8 experts are spre
 
 Prints ONE JSON line on rank 0.  ``value`` is device-timed (CUDA events, max over ranks) with inputs resident
 on the device; ``e2e`` is the same step driven through ``MoELayer`` with the host->device copy of each step's
-activations from pinned memory and the device->host read of the loss inside the timed region.
+activations from pinned memory and the device->host copy of every step's loss (into pinned memory; the host reads it once
+the next step has been enqueued) inside the timed region.
 
 ``--impl reference`` reports that the reference cannot be run here; ``--impl nccl`` runs the stock
 PyTorch + NCCL formulation of the same step (framework permute, all_to_all_single, library GEMMs).
@@ -488,6 +489,11 @@ def main():
                         dbufs[b].copy_(host[i % 2], non_blocking=True)
                         ready[b].record(copy_stream)
 
+                # Device -> host: every step's loss is copied into pinned memory right behind the step and read by the host
+                # once the NEXT step has been enqueued, so the GPU is never left without work while the host reads a number.
+                loss_pinned = torch.zeros(2, dtype=torch.float32).pin_memory()
+                loss_ready = [torch.cuda.Event() for _ in range(2)]
+
                 def run_e2e(n):
                     last = 0.0
                     prefetch(0)
@@ -498,7 +504,14 @@ def main():
                             prefetch(i + 1)                          # next step's host -> device copy overlaps this step
                         loss = step(dbufs[b])
                         consumed[b].record()
-                        last = float(loss.item())                    # this step's result, device -> host
+                        loss_pinned[b:b + 1].copy_(loss.detach().reshape(1), non_blocking=True)   # this step's result, device -> host
+                        loss_ready[b].record()
+                        if i > 0:                                    # read the previous step's loss now that this step is queued
+                            loss_ready[1 - b].synchronize()
+                            last = float(loss_pinned[1 - b])
+                    if n > 0:
+                        loss_ready[(n - 1) % 2].synchronize()
+                        last = float(loss_pinned[(n - 1) % 2])
                     return last
 
             run_e2e(2)

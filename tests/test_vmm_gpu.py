@@ -185,8 +185,19 @@ def test_rehoming_onto_the_other_gpu_and_back(C):
     home = C.vmm_remap_slab(r, 0, 0, True, [0])
     assert C.vmm_slab_device(r, 0) == 0 and C.vmm_usage(1) == u1 and C.vmm_usage(0) - u0 == size
     assert torch.equal(_view(C, r, n), _pattern(n, 41) * 2)
-    bare = C.vmm_remap_slab(r, 0, 1, False, [0, 1])
+    # the reference's "Remap time": a few more round trips now that the driver has seen every call once
+    aways, homes, bares = [], [], []
+    for _ in range(5):
+        aways.append(C.vmm_remap_slab(r, 0, 1, True, [0, 1]))
+        homes.append(C.vmm_remap_slab(r, 0, 0, True, [0]))
+    assert torch.equal(_view(C, r, n), _pattern(n, 41) * 2)
+    for _ in range(5):
+        bares.append(C.vmm_remap_slab(r, 0, 1, False, [0, 1]))
+        bares.append(C.vmm_remap_slab(r, 0, 0, False, [0]))
     torch.cuda.synchronize()
-    print(f"re-homing {size >> 20} MiB: to GPU 1 {away} us, home {home} us (both carry the contents), to GPU 1 without the copy {bare} us")
+    med = lambda v: sorted(v)[len(v) // 2]
+    print(f"re-homing {size >> 20} MiB (median of 5 after the first): to GPU 1 {med(aways)} us, home {med(homes)} us (both carry the "
+          f"contents), without the copy {med(bares)} us; first calls {away} / {home} us")
+    C.vmm_remap_slab(r, 0, 1, False, [0, 1])
     C.vmm_destroy(r)
     assert C.vmm_usage(0) == u0 and C.vmm_usage(1) == u1
