@@ -74,6 +74,10 @@ struct CudaDriver : Driver {
   CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr) = nullptr;
   CUresult (*MemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr) = nullptr;
   CUresult (*MemGetHandleForAddressRange)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long) = nullptr;
+  CUresult (*StreamCreate)(CUstream*, unsigned int) = nullptr;
+  CUresult (*StreamSynchronize)(CUstream) = nullptr;
+  CUresult (*MemcpyAsync)(CUdeviceptr, CUdeviceptr, size_t, CUstream) = nullptr;
+  CUresult (*CtxGetCurrent)(CUcontext*) = nullptr;
 
   template <class F>
   bool sym(const char* name, F& fn) {
@@ -113,6 +117,10 @@ struct CudaDriver : Driver {
     (void)sym("cuPointerGetAttribute", PointerGetAttribute);
     (void)sym("cuMemGetAddressRange", MemGetAddressRange);
     (void)sym("cuMemGetHandleForAddressRange", MemGetHandleForAddressRange);
+    (void)sym("cuStreamCreate", StreamCreate);
+    (void)sym("cuStreamSynchronize", StreamSynchronize);
+    (void)sym("cuMemcpyAsync", MemcpyAsync);
+    (void)sym("cuCtxGetCurrent", CtxGetCurrent);
     g_err[0] = 0;
     return chk(Init(0), "cuInit") == 0;
   }
@@ -184,12 +192,37 @@ struct CudaDriver : Driver {
     *h = (uint64_t)hh;
     return rc;
   }
+  // Copies run on a stream of their own (non-blocking, one per thread and context) and only that stream is waited for.
+  // A synchronous cuMemcpy or a context-wide synchronise would also wait for every kernel on the default stream -- and a
+  // communication library's progress thread that calls into this layer must never wait for the kernels it is feeding.
+  CUstream private_stream() {
+    if (!StreamCreate || !StreamSynchronize || !MemcpyAsync || !CtxGetCurrent) return nullptr;
+    static thread_local std::map<CUcontext, CUstream> streams;
+    CUcontext ctx = nullptr;
+    if (CtxGetCurrent(&ctx) != CUDA_SUCCESS || !ctx) return nullptr;
+    auto it = streams.find(ctx);
+    if (it != streams.end()) return it->second;
+    CUstream st = nullptr;
+    if (StreamCreate(&st, CU_STREAM_NON_BLOCKING) != CUDA_SUCCESS) return nullptr;
+    streams[ctx] = st;
+    return st;
+  }
   int copy(uintptr_t dst, uintptr_t src, size_t n) override {
+    if (CUstream st = private_stream()) {
+      int rc = chk(MemcpyAsync((CUdeviceptr)dst, (CUdeviceptr)src, n, st), "cuMemcpyAsync");
+      if (rc) return rc;
+      return chk(StreamSynchronize(st), "cuStreamSynchronize");
+    }
     int rc = chk(MemcpyDtoD((CUdeviceptr)dst, (CUdeviceptr)src, n), "cuMemcpyDtoD");
     if (rc) return rc;
     return chk(CtxSynchronize(), "cuCtxSynchronize");
   }
   int any_copy(void* dst, const void* src, size_t n) override {
+    if (CUstream st = private_stream()) {
+      int rc = chk(MemcpyAsync((CUdeviceptr)(uintptr_t)dst, (CUdeviceptr)(uintptr_t)src, n, st), "cuMemcpyAsync");
+      if (rc) return rc;
+      return chk(StreamSynchronize(st), "cuStreamSynchronize");
+    }
     if (!Memcpy) { set_err("%s: cuMemcpy not available (%ld)", "vmm", 0); return 1; }
     return chk(Memcpy((CUdeviceptr)(uintptr_t)dst, (CUdeviceptr)(uintptr_t)src, n), "cuMemcpy");
   }

@@ -18,13 +18,18 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(extra_env, args, port):
+def _run(extra_env, args, port, limit_s=420):
     lib = os.path.join(ROOT, "fuselink_b200", "lib")
     env = dict(os.environ, NCCL_NET_PLUGIN="fuselink", LD_LIBRARY_PATH=lib + ":" + os.environ.get("LD_LIBRARY_PATH", ""),
                NCCL_DEBUG="INFO", NCCL_DEBUG_SUBSYS="INIT,NET", NCCL_NVLS_ENABLE="0", **extra_env)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
            "--master-port", str(port), os.path.join(ROOT, "bench", "nccl_plugin_sendrecv.py"), *args]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=limit_s, env=env)
+    except subprocess.TimeoutExpired as e:       # show how far the run got: NCCL's and the plugin's log lines
+        def tail(b):
+            return (b.decode(errors="replace") if isinstance(b, bytes) else (b or ""))[-6000:]
+        raise AssertionError(f"no result within {limit_s} s\n--- stdout\n{tail(e.stdout)}\n--- stderr\n{tail(e.stderr)}") from None
     text = out.stdout + out.stderr
     assert out.returncode == 0, text[-6000:]
     rows = [json.loads(l) for l in out.stdout.splitlines() if l.startswith("{")]
@@ -53,3 +58,4 @@ def test_striping_under_the_proxy_adds_the_virtual_nics_bandwidth():
                       ["--size-lo", "25", "--size-hi", "25", "--iters", "3", "--warmup", "1"], port)
         rates[degree] = res["results"][0]["GBps_per_direction"]
     assert rates[4] > 2.0 * rates[1], rates
+
