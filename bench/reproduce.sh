@@ -22,14 +22,14 @@ launch() { if [ "$NGPU" -gt 1 ]; then tr "$@"; else python "$@"; fi; }
 
 for s in $SECTIONS; do
   case $s in
-    gemm)    # isolated grouped GEMMs of the flagship shape, both kernel variants
-      for v in 0 1; do FUSELINK_GEMM_PAIR=$v run "gemm pair=$v" python bench/gemm_case.py --case fwd1 --rows 8192 --iters 10; done ;;
+    gemm)    # isolated grouped GEMMs of the flagship shape, the three tilings
+      for v in 0 1 2; do FUSELINK_GEMM_PAIR=$v run "gemm variant=$v" python bench/gemm_case.py --case fwd1 --rows 8192 --iters 10; done ;;
     moe)
       for impl in fuselink nccl; do run "moe $impl" launch bench.py --impl "$impl" --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP"; done ;;
-    moe-shadow)   # not in the default list: the hottest experts replicated on every rank
+    moe-shadow)   # not in the default list: what the default (--shadow auto: chosen and spread by rebalance()) is compared with
       if [ "$NGPU" -ge 2 ]; then
-        run "moe contiguous placement" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --placement contiguous
-        for n in 1 2 3; do run "moe shadow=$n" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n"; done
+        run "moe contiguous placement, no shadows" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --placement contiguous --shadow 0 --no-baseline --no-other
+        for n in 0 1 2 3; do run "moe shadow=$n (rows stay local)" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n" --no-baseline --no-other; done
       fi ;;
     gemm-sweep)   # not in the default list: tile order x kernel variant for every GEMM of the step
       for c in fwd1 fwd2 dact dx wgrad2 wgrad13; do run "gemm sweep $c" python bench/gemm_case.py --case "$c" --rows 16384 --iters 5 --sweep; done ;;

@@ -20,6 +20,9 @@ struct FlEmbBagArgs {
                               // backward: every rank's gradient buffer of the same shape
   float lr;                   // backward: SGD learning rate
   int* status;                // device int32[8]
+  int hot_rows;               // backward: updates of rows [0, hot_rows) of a table are summed in shared memory per CTA and applied
+                              // once at the end (tables whose ids are ordered by frequency, as Zipf-distributed ids are, have
+                              // their hot rows there); 0 = the library's default (FUSELINK_EMBBAG_HOT_ROWS or 64), < 0 = off
 };
 
 #ifdef __cplusplus
