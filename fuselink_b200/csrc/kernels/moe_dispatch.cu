@@ -26,18 +26,44 @@ __global__ void moe_count_kernel(const FlMoeDispatchArgs a) {
   a.pos[i] = atomicAdd(&a.local_count[e], 1);
 }
 
-__global__ void moe_reserve_kernel(const FlMoeDispatchArgs a) {
-  const int e = threadIdx.x;
-  if (e < a.num_experts) {
+// One contiguous range of rows per (rank, expert) on the expert's owner: one system-scope atomic each.
+__device__ __forceinline__ void reserve_rows(const FlMoeDispatchArgs& a) {
+  for (int e = threadIdx.x; e < a.num_experts; e += blockDim.x) {
     const int owner = e / a.experts_per_rank, le = e % a.experts_per_rank;
     int* cnt = reinterpret_cast<int*>(a.count_peers.p[owner]) + a.parity * a.experts_per_rank + le;
-    const int n = a.local_count[e];
+    const int n = __ldcg(a.local_count + e);      // other CTAs' atomics: read at L2
     a.base[e] = n > 0 ? atomicAdd_system(cnt, n) : 0;
     a.local_count[e] = 0;  // ready for the next step
   }
   // clear the other parity's counters of THIS rank; peers touch them only after the next inter-rank barrier
-  if (threadIdx.x < a.experts_per_rank)
-    reinterpret_cast<int*>(a.count_peers.p[a.rank])[(a.parity ^ 1) * a.experts_per_rank + threadIdx.x] = 0;
+  for (int i = threadIdx.x; i < a.experts_per_rank; i += blockDim.x)
+    reinterpret_cast<int*>(a.count_peers.p[a.rank])[(a.parity ^ 1) * a.experts_per_rank + i] = 0;
+}
+
+__global__ void moe_reserve_kernel(const FlMoeDispatchArgs a) { reserve_rows(a); }
+
+// Counting and reservation in one launch: every CTA counts its share, takes a ticket, and the CTA that draws the last
+// ticket -- by then every count is in -- reserves the rows and rearms the ticket.
+__global__ void __launch_bounds__(256) moe_count_reserve_kernel(const FlMoeDispatchArgs a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < a.tokens * a.topk) {
+    const int e = a.topk_idx[i];
+    if (e < 0 || e >= a.num_experts) {
+      report(a.status, kBadIndex, 1100);
+      a.pos[i] = -1;
+    } else {
+      a.pos[i] = atomicAdd(&a.local_count[e], 1);
+    }
+  }
+  __shared__ int last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(a.ticket, 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  reserve_rows(a);
+  if (threadIdx.x == 0) *a.ticket = 0;
 }
 
 // one warp per token: the row is read once and stored to each of its top-k destinations
@@ -163,8 +189,12 @@ extern "C" int fl_moe_dispatch(const FlMoeDispatchArgs* a, cudaStream_t stream) 
   const int n = a->tokens * a->topk;
   if (n == 0) return 0;
   if (!a->reuse_slots) {
-    fl::moe_count_kernel<<<(n + 255) / 256, 256, 0, stream>>>(*a);
-    fl::moe_reserve_kernel<<<1, 1024, 0, stream>>>(*a);
+    if (a->ticket != nullptr) {
+      fl::moe_count_reserve_kernel<<<(n + 255) / 256, 256, 0, stream>>>(*a);
+    } else {
+      fl::moe_count_kernel<<<(n + 255) / 256, 256, 0, stream>>>(*a);
+      fl::moe_reserve_kernel<<<1, 1024, 0, stream>>>(*a);
+    }
   }
   int ctas = (a->tokens + 7) / 8;
   if (ctas > 148 * 8) ctas = 148 * 8;
@@ -178,6 +208,7 @@ extern "C" int fl_moe_dispatch_preload(void) {
   cudaFuncAttributes attr;
   cudaError_t e = cudaFuncGetAttributes(&attr, fl::moe_count_kernel);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, fl::moe_reserve_kernel);
+  if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, fl::moe_count_reserve_kernel);
   if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, fl::moe_scatter_kernel);
   return (int)e;
 }

@@ -15,7 +15,9 @@ struct FlMoeDispatchArgs {
   int experts_per_rank;
   int cap;                    // rows reserved per expert in the destination buffers
   int rank, world;
-  int* local_count;           // [num_experts] scratch, zeroed by the count kernel's caller
+  int* local_count;           // [num_experts] scratch, zero before the first call (the kernels leave it zero)
+  int* ticket;                // optional: one more zeroed int of scratch.  With it counting and reservation are ONE launch
+                              // (the last CTA to finish counting reserves the rows); without it they are two
   int* base;                  // [num_experts] scratch: first row this rank owns in each expert buffer
   int* pos;                   // [tokens, topk] scratch: position inside (rank, expert)
   int* slot;                  // [tokens, topk] out (forward) / in (backward): row inside the owner's buffer
@@ -30,7 +32,8 @@ struct FlMoeDispatchArgs {
 #ifdef __cplusplus
 extern "C" {
 #endif
-// forward: count -> reserve (one system-scope atomic per expert) -> scatter.  backward: scatter only.
+// forward: count + reserve (one system-scope atomic per expert; one launch with `ticket`, else two) -> scatter.
+// backward: scatter only.
 int fl_moe_dispatch(const FlMoeDispatchArgs* a, cudaStream_t stream);
 // load the dispatch kernels on the current device now rather than at their first launch; returns a cudaError
 int fl_moe_dispatch_preload(void);

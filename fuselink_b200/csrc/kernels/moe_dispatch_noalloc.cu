@@ -101,6 +101,7 @@ extern "C" int fl_moe_dispatch_noalloc(const FlMoeDispatchNoAllocArgs* in, cudaS
   a.num_experts = in->num_experts; a.experts_per_rank = in->experts_per_rank; a.cap = in->cap;
   a.rank = in->rank; a.world = in->world;
   a.local_count = counters; a.base = base; a.pos = pos; a.slot = in->slot;
+  a.ticket = in->num_experts < FL_NOALLOC_MAX_EXPERTS ? counters + in->num_experts : nullptr;   // cleared with the counters
   for (int i = 0; i < 8; ++i) {
     a.count_peers.p[i] = in->count_peers[i];
     a.x_peers.p[i] = in->x_peers[i];

@@ -20,7 +20,7 @@
 // synchronise the device: it resolves the device address of the scratch array and makes the runtime load the
 // kernels (loading a module can allocate and synchronise -- exactly what the callers above cannot afford later).
 // Without it the first fl_moe_dispatch_noalloc call on a device does the same work itself; make that first
-// call, or the set-up call, outside any stream capture.  After set-up a call enqueues four kernels and
+// call, or the set-up call, outside any stream capture.  After set-up a call enqueues three kernels and
 // touches no allocator.
 //
 // Sharing: every call on a device uses the same scratch array.  The counters are cleared at the start of

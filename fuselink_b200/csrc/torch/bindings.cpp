@@ -197,6 +197,8 @@ static void moe_dispatch(torch::Tensor x, torch::Tensor topk_idx, c10::optional<
   a.num_experts = (int)num_experts; a.experts_per_rank = (int)experts_per_rank; a.cap = (int)cap;
   a.rank = (int)rank; a.world = (int)world;
   a.local_count = local_count.data_ptr<int>(); a.base = base.data_ptr<int>();
+  // a spare (zero) element behind the per-expert counters is the ticket that lets counting and reservation share a launch
+  a.ticket = local_count.numel() > num_experts ? local_count.data_ptr<int>() + num_experts : nullptr;
   a.pos = pos.data_ptr<int>(); a.slot = slot.data_ptr<int>();
   a.count_peers = to_peers(count_peers); a.parity = (int)parity;
   a.x_peers = to_peers(x_peers); a.info_peers = to_peers(info_peers);

@@ -123,7 +123,7 @@ class MoEWorkspace:
         self.act = torch.empty(rows, F, dtype=bf, device=dev)
         self.gu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
         self.dgu = torch.empty(rows, 2 * F, dtype=bf, device=dev)
-        self.local_count = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
+        self.local_count = torch.zeros(self.num_slots + 1, dtype=torch.int32, device=dev)   # + the ticket of the one-launch count/reserve
         self.base = torch.zeros(self.num_slots, dtype=torch.int32, device=dev)
         remap = self.nshadow or (cfg.placement and tuple(cfg.placement) != tuple(range(cfg.num_experts)))
         self.slots_of = slot_table(cfg.num_experts, W, cfg.shadow, heap.rank, cfg.placement).to(dev) if remap else None
@@ -290,7 +290,7 @@ def _dispatch(ws: MoEWorkspace, x: torch.Tensor, idx: torch.Tensor, scale: Optio
             idx = idx + ws.sh_stride[j] * ws.spread                             # a shadowed expert's copy on another rank
     C.moe_dispatch(x, idx, scale, ws.num_slots, ws.epr, ws.cap, h.rank, h.world, ws.local_count, ws.base, ws.pos,
                    ws.slot, ws.counts.peers(), ws.step_parity, dst.peers(), ws.info.peers(), reuse, h.status_addr)
-    ws.launches += 1 if reuse else 3
+    ws.launches += 1 if reuse else 2
 
 
 def _wq(ws: MoEWorkspace, name: str, w: torch.Tensor):
