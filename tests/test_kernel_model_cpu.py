@@ -545,13 +545,19 @@ def test_default_moe_step_hands_the_kernels_exactly_the_recorded_work(world, sgd
     """The device calls of the default fused MoE step -- which entry point, in which order, with which scalars, tensor
     shapes, and addresses relative to the heap -- are pinned to a recorded digest, so an edit of the Python side that
     changes what the kernels are given (new options must leave the default alone) shows up here, on a machine without a
-    GPU.  After a deliberate change of the default step the digests are recorded again."""
+    GPU.  After a deliberate change of the default step the digests are recorded again: run this test with
+    FUSELINK_RECORD_GOLDEN=1."""
     import hashlib
     import json
     import os
-    golden = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "moe_default_step_calls.json")))
-    want = golden[f"world{world}_sgd{sgd}"]
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "moe_default_step_calls.json")
+    golden = json.load(open(path))
     trace = _default_step_trace(world, sgd)
+    if os.environ.get("FUSELINK_RECORD_GOLDEN", "0") == "1":
+        golden[f"world{world}_sgd{sgd}"] = {"calls": len(trace), "sha256": hashlib.sha256(json.dumps(trace).encode()).hexdigest()}
+        json.dump(golden, open(path, "w"), indent=1)
+        return
+    want = golden[f"world{world}_sgd{sgd}"]
     assert len(trace) == want["calls"]
     assert hashlib.sha256(json.dumps(trace).encode()).hexdigest() == want["sha256"], "the default MoE step no longer issues the recorded device calls"
 
