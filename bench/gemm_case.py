@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--cublas", action="store_true", help="also time torch.matmul on the same shape")
     ap.add_argument("--group-m", type=int, default=16, help="row tiles that share a column of weight tiles in the tile order (L2 reuse)")
     ap.add_argument("--max-ctas", type=int, default=0, help="cap on the persistent grid (0: one CTA, or CTA pair, per SM)")
+    ap.add_argument("--sgd", action="store_true", help="wgrad cases: apply W -= lr * dW in the epilogue (reads and rewrites the weights) as the MoE step does")
     ap.add_argument("--sweep", action="store_true", help="time the case for group-m 4/8/16/32 x both kernel variants, one JSON line each")
     args = ap.parse_args()
     from fuselink_b200.ops import gemm
@@ -69,13 +70,13 @@ def main():
         M, N, K = G * cap, H, 2 * F
     elif args.case == "wgrad2":
         a, b = rnd(G * cap, H), rnd(G * cap, F)
-        out = torch.empty(G, H, F, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, status=st, **sched)
+        out = torch.zeros(G, H, F, dtype=bf, device=dev)
+        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, sgd_lr=1e-6 if args.sgd else 0.0, status=st, **sched)
         M, N, K = H * G, F, cap
     elif args.case == "wgrad13":
         a, b = rnd(G * cap, 2 * F), rnd(G * cap, H)
-        out = torch.empty(G, 2 * F, H, dtype=bf, device=dev)
-        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, status=st, **sched)
+        out = torch.zeros(G, 2 * F, H, dtype=bf, device=dev)
+        fn = lambda: gemm.grouped_gemm_wgrad(a, b, counts, cap, G, out=out, sgd_lr=1e-6 if args.sgd else 0.0, status=st, **sched)
         M, N, K = 2 * F * G, H, cap
     else:
         raise SystemExit("unknown case")

@@ -219,6 +219,14 @@ __device__ __forceinline__ void prefetch_saved_gate_up(const KParams& p, int g, 
   }
 }
 
+// WGRAD with the fused SGD update reads the weights it rewrites: one L2 request per weight row of the slab, made before the
+// wait on the accumulator, so that the epilogue's row-per-thread loads find them in L2.
+__device__ __forceinline__ void prefetch_weights(const KParams& p, int g, int row0, int n0, int cols, int r_in_tile) {
+  const int row = row0 + r_in_tile;
+  if (row < p.M && cols > 0)
+    bulk_prefetch_l2(p.C + (long long)g * p.gsc + (long long)row * p.ldc + n0, (uint32_t)(cols * 2));
+}
+
 // Fused epilogues, run by the 8 epilogue warps of a CTA: warp (q, half) owns TMEM lanes [32q, 32q+32) and half of
 // the columns; thread = one output row.
 __device__ __forceinline__ void epilogue_slab(const KParams& p, const EpiSlab& e, uint32_t acc_addr, int q, int half,
@@ -509,6 +517,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t acc_ph = (tile_i >> 1) & 1;
       if (p.epilogue == FL_EPI_DSWIGLU && half == 0)
         prefetch_saved_gate_up(p, t.g, t.m0, t.rows, t.n0, min(BN, p.N - t.n0), q * 32 + lane);
+      if (p.epilogue == FL_EPI_WGRAD && p.sgd_lr != 0.f && half == 0)
+        prefetch_weights(p, t.g, t.m0, t.n0, min(BN, p.N - t.n0), q * 32 + lane);
       ok = mbar_wait(&sh->tmem_full[acc], acc_ph, abort_flag, p.status, kTimeoutTmemFull, 400 + acc);
       if (!ok) break;
       tc_fence_after_sync();
@@ -693,6 +703,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (p.epilogue == FL_EPI_DSWIGLU && half == 0)
         prefetch_saved_gate_up(p, t.g, t.m0 + 128 * (int)rank, min(128, t.cnt - (t.m0 + 128 * (int)rank)), t.n0, min(BN, p.N - t.n0),
                                q * 32 + lane);
+      if (p.epilogue == FL_EPI_WGRAD && p.sgd_lr != 0.f && half == 0)
+        prefetch_weights(p, t.g, t.m0 + 128 * (int)rank, t.n0, min(BN, p.N - t.n0), q * 32 + lane);
       ok = mbar_wait(&sh->tmem_full[acc], acc_ph, abort_flag, p.status, kTimeoutTmemFull, 1400 + acc);
       if (!ok) break;
       tc_fence_after_sync();
@@ -925,6 +937,8 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (p.epilogue == FL_EPI_DSWIGLU && half == 0)
         prefetch_saved_gate_up(p, t.g, t.m0 + 128 * (int)rank, min(128, t.cnt - (t.m0 + 128 * (int)rank)), t.n0,
                                min(WIDE_N, p.N - t.n0), q * 32 + lane);
+      if (p.epilogue == FL_EPI_WGRAD && p.sgd_lr != 0.f && half == 0)
+        prefetch_weights(p, t.g, t.m0 + 128 * (int)rank, t.n0, min(WIDE_N, p.N - t.n0), q * 32 + lane);
       for (int h = 0; h < 2 && ok; ++h) {
         ok = mbar_wait(&sh->half_full[h], ph, abort_flag, p.status, kTimeoutTmemFull, 2400 + h);
         if (!ok) break;
