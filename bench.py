@@ -14,8 +14,15 @@ on the device; ``e2e`` is the same step driven through ``MoELayer`` with the hos
 activations from pinned memory and the device->host copy of every step's loss (into pinned memory; the host reads it once
 the next step has been enqueued) inside the timed region.
 
-``--impl reference`` reports that the reference cannot be run here; ``--impl nccl`` runs the stock
-PyTorch + NCCL formulation of the same step (framework permute, all_to_all_single, library GEMMs).
+On more than one GPU the layer evens out the skewed router's load by itself (``--shadow auto``): after the first warm-up
+step it replicates the busiest experts where that is needed and spreads their rows over the ranks (``MoELayer.rebalance``);
+the choice is fixed for the timed region and named in ``config.parallelism``.
+
+After the fuselink arm the same process runs the stock PyTorch + NCCL formulation of the step (framework permute,
+all_to_all_single, library grouped GEMM, autograd, torch.optim.SGD) with the same steps and warm-up -> ``vs_baseline``,
+and the other parts of the headline metric (p2p and all-to-all bandwidth, DLRM samples/s), each beside its NCCL
+counterpart -> ``other_metrics``.  ``--impl reference`` reports that the reference cannot be run here; ``--impl nccl``
+runs the stock arm alone.
 """
 from __future__ import annotations
 
