@@ -7,6 +7,7 @@ math runs as plain PyTorch with an all-gather of the tokens and a reduce-scatter
 from __future__ import annotations
 
 import dataclasses
+import os
 from typing import Optional
 
 import torch
@@ -103,6 +104,24 @@ class MoELayer(nn.Module):
         self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr + shadows, 2F, H], gate/up interleaved by 128
         self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr + shadows, H, F]
         self.ws = MoEWorkspace(heap, cfg, name) if heap is not None else None
+        if self.ws is not None and world > 1 and len(cfg.shadow) > 0:
+            self._own_reduce_group(world)
+
+    def _own_reduce_group(self, world: int) -> None:
+        """A NCCL communicator of this layer's own for the sum of the shadow experts' gradients, its kernels limited to a
+        few CTAs, so that the sum can run beside the backward GEMMs (which then leave those SMs free) instead of after
+        them.  Collective over the ranks; without NCCL (CPU runs, emulated ranks) nothing changes."""
+        try:
+            import torch.distributed as dist
+            if not (dist.is_available() and dist.is_initialized() and dist.get_backend() == "nccl" and dist.get_world_size() == world):
+                return
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = self.ws.reduce_ctas
+            opts.config.min_ctas = min(8, self.ws.reduce_ctas)
+            self.ws.reduce_group = dist.new_group(ranks=list(range(world)), pg_options=opts)
+            self.ws.overlap_reduce = os.environ.get("FUSELINK_OVERLAP_REDUCE", "1") != "0"
+        except Exception:  # noqa: BLE001 - an older PyTorch without the option: the default group, no overlap
+            self.ws.reduce_group, self.ws.overlap_reduce = None, False
 
     # -- routing ------------------------------------------------------------------------------------------
     def route(self, x: torch.Tensor):

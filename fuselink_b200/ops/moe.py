@@ -144,6 +144,13 @@ class MoEWorkspace:
             self.s_dgu = torch.empty(rows, 2 * F // 128, dtype=torch.float32, device=dev)
             self.wq = {}                                                     # per-weight (e4m3, scales), refreshed each step
         self.pending_shadow = None
+        # Overlap of the shadow experts' gradient all-reduce with the rest of the backward pass (set by MoELayer once it has
+        # a communicator of its own whose kernels are limited to `reduce_ctas` CTAs): the copies' weight gradients are then
+        # computed first and summed while dX and the owned experts' weight gradients run on the remaining SMs.
+        self.overlap_reduce = False
+        self.reduce_group = None
+        self.reduce_ctas = 16
+        self.started_shadow = None
         self.parity = 0
         self.step_parity = 0
         self.launches = 0   # kernels of this library launched through this workspace (bench accounting)
@@ -276,7 +283,7 @@ def _allreduce_shadow_grads(ws: MoEWorkspace, grads):
     """Starts the sums; the returned handles are waited for once the rest of the backward pass has been enqueued."""
     if ws.heap.world > 1:
         import torch.distributed as dist
-        return [dist.all_reduce(g, async_op=True) for g in grads]
+        return [dist.all_reduce(g, async_op=True, group=ws.reduce_group) for g in grads]
     return []
 
 
@@ -370,6 +377,10 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     st = h.status()
     # dAct = dY @ W2 ; the epilogue turns it into dGate/dUp using the saved gate/up.  dX rows go home next (needs the
     # pre-update W13), then the weight gradients.
+    overlap = bool(ws.overlap_reduce and ws.nshadow and ws.shadows_in_use and not cfg.fp8)
+    beside = 0                                                       # CTAs a GEMM may use while the reduction's kernels run beside it
+    if overlap:
+        beside = max(2, (torch.cuda.get_device_properties(ws.dgu.device).multi_processor_count - ws.reduce_ctas - 4) // 2 * 2)
     if cfg.fp8:
         from . import fp8 as f8
         # the quantised weights of the forward pass are reused: a 128 x 128 scale block is its own transpose
@@ -385,10 +396,18 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     else:
         gemm.grouped_gemm_rows(ws.dyd.local, w2, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_DSWIGLU, gu=ws.gu,
                                dgu=ws.dgu, zero_tail=True, status=st)
+        if overlap:
+            # the copies' weight gradients first: their sum over the ranks starts now and runs beside what follows
+            R, S, cut = ws.epr_real, ws.shadows_in_use, ws.epr_real * ws.cap
+            end = cut + S * ws.cap
+            early = (gemm.grouped_gemm_wgrad(ws.dgu[cut:end], ws.xd.local[cut:end], counts[R:R + S], ws.cap, S, status=st),
+                     gemm.grouped_gemm_wgrad(ws.dyd.local[cut:end], ws.act[cut:end], counts[R:R + S], ws.cap, S, status=st))
+            ws.launches += 2
+            works = ws.reduce_shadow_grads(ws, early) or []
         if need_dx:
             gemm.grouped_gemm_rows(ws.dgu, w13, counts, ws.cap, b_mn_major=True, epilogue=gemm.EPI_SCATTER,
                                    row_info=ws.info.local, peers=ws.dxs.peers(), ldc=cfg.hidden, status=st,
-                                   peer_rows=ws.dxs.local.shape[0])
+                                   peer_rows=ws.dxs.local.shape[0], max_ctas=beside)
     shadow_grads = None
     if ws.nshadow:
         # Owned experts as below, on the leading slots.  The copies of the shadowed experts have seen this rank's rows
@@ -397,17 +416,19 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
         R, S, cut = ws.epr_real, ws.shadows_in_use, ws.epr_real * ws.cap
         dyd, dgu, act, xd = ws.dyd.local, ws.dgu, ws.act, ws.xd.local
         if sgd_lr:
-            gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=w2[:R], sgd_lr=sgd_lr, status=st)
-            gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=w13[:R], sgd_lr=sgd_lr, status=st)
+            gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=w2[:R], sgd_lr=sgd_lr, status=st, max_ctas=beside)
+            gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=w13[:R], sgd_lr=sgd_lr, status=st, max_ctas=beside)
             dw2 = dw13 = None
         else:
             dw2 = torch.empty_like(w2)
             dw13 = torch.empty_like(w13)
-            gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=dw2[:R], status=st)
-            gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=dw13[:R], status=st)
+            gemm.grouped_gemm_wgrad(dyd[:cut], act[:cut], counts[:R], ws.cap, R, out=dw2[:R], status=st, max_ctas=beside)
+            gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=dw13[:R], status=st, max_ctas=beside)
             dw2[R:].zero_()                                          # copy slots: filled in once the sums are complete, empty
             dw13[R:].zero_()                                         # ones stay zero
-        if S:
+        if overlap:
+            shadow_grads = early                                     # computed, and their reduction started, before dX
+        elif S:
             end = cut + S * ws.cap                                   # empty copy slots at the end take no part
             shadow_grads = (gemm.grouped_gemm_wgrad(dgu[cut:end], xd[cut:end], counts[R:R + S], ws.cap, S, status=st),
                             gemm.grouped_gemm_wgrad(dyd[cut:end], act[cut:end], counts[R:R + S], ws.cap, S, status=st))
@@ -424,6 +445,7 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     ws.launches += 6 + (1 if need_dx else 0)
     # finished in moe_backward_finish: the sum over ranks runs while the other ranks complete their GEMMs
     ws.pending_shadow = None if shadow_grads is None else (shadow_grads, w13, w2, dw13, dw2, sgd_lr)
+    ws.started_shadow = works if (overlap and shadow_grads is not None) else None
     return dw13, dw2
 
 
@@ -432,7 +454,10 @@ def start_shadow_reduction(ws: MoEWorkspace):
     if ws.pending_shadow is None:
         return None
     pending, ws.pending_shadow = ws.pending_shadow, None
-    works = ws.reduce_shadow_grads(ws, pending[0]) or []
+    if ws.started_shadow is not None:                      # already running since the copies' gradients were computed
+        works, ws.started_shadow = ws.started_shadow, None
+    else:
+        works = ws.reduce_shadow_grads(ws, pending[0]) or []
     return pending, works
 
 
