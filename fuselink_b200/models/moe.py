@@ -113,12 +113,15 @@ class MoELayer(nn.Module):
         them.  Collective over the ranks; without NCCL (CPU runs, emulated ranks) nothing changes."""
         try:
             import torch.distributed as dist
-            if not (dist.is_available() and dist.is_initialized() and dist.get_backend() == "nccl" and dist.get_world_size() == world):
+            if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() == world):
                 return
-            opts = dist.ProcessGroupNCCL.Options()
-            opts.config.max_ctas = self.ws.reduce_ctas
-            opts.config.min_ctas = min(8, self.ws.reduce_ctas)
-            self.ws.reduce_group = dist.new_group(ranks=list(range(world)), pg_options=opts)
+            if dist.get_backend() == "nccl":
+                opts = dist.ProcessGroupNCCL.Options()
+                opts.config.max_ctas = self.ws.reduce_ctas
+                opts.config.min_ctas = min(8, self.ws.reduce_ctas)
+                self.ws.reduce_group = dist.new_group(ranks=list(range(world)), pg_options=opts)
+            else:                                    # host runs (gloo): same order of work, an ordinary group
+                self.ws.reduce_group = dist.new_group(ranks=list(range(world)))
             self.ws.overlap_reduce = os.environ.get("FUSELINK_OVERLAP_REDUCE", "1") != "0"
         except Exception:  # noqa: BLE001 - an older PyTorch without the option: the default group, no overlap
             self.ws.reduce_group, self.ws.overlap_reduce = None, False

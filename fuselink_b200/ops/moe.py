@@ -379,7 +379,7 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
     # pre-update W13), then the weight gradients.
     overlap = bool(ws.overlap_reduce and ws.nshadow and ws.shadows_in_use and not cfg.fp8)
     beside = 0                                                       # CTAs a GEMM may use while the reduction's kernels run beside it
-    if overlap:
+    if overlap and ws.dgu.device.type == "cuda":
         beside = max(2, (torch.cuda.get_device_properties(ws.dgu.device).multi_processor_count - ws.reduce_ctas - 4) // 2 * 2)
     if cfg.fp8:
         from . import fp8 as f8
