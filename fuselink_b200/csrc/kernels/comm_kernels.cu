@@ -177,11 +177,14 @@ extern "C" int fl_put_chunks(const FlPutArgs* args, int num_ctas, int threads, c
   if (num_ctas <= 0) num_ctas = 1;
   size_t smem = args->use_bulk ? fl::BULK_SLOTS * fl::BULK_SLOT_BYTES : 0;
   if (smem > 48 * 1024) {
-    static bool set = false;
-    if (!set) {
+    static bool set_on[64];                 // per device: a process may drive several GPUs
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return -3;
+    if (!set_on[dev]) {
       cudaError_t e = cudaFuncSetAttribute(fl::put_chunks_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return (int)e;
-      set = true;
+      set_on[dev] = true;
     }
   }
   fl::put_chunks_kernel<<<num_ctas, threads, smem, stream>>>(*args);

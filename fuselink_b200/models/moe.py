@@ -104,13 +104,16 @@ class MoELayer(nn.Module):
         self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr + shadows, 2F, H], gate/up interleaved by 128
         self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr + shadows, H, F]
         self.ws = MoEWorkspace(heap, cfg, name) if heap is not None else None
-        if self.ws is not None and world > 1 and len(cfg.shadow) > 0:
+        if self.ws is not None and world > 1 and len(cfg.shadow) > 0 and os.environ.get("FUSELINK_OVERLAP_REDUCE", "0") == "1":
             self._own_reduce_group(world)
 
     def _own_reduce_group(self, world: int) -> None:
-        """A NCCL communicator of this layer's own for the sum of the shadow experts' gradients, its kernels limited to a
-        few CTAs, so that the sum can run beside the backward GEMMs (which then leave those SMs free) instead of after
-        them.  Collective over the ranks; without NCCL (CPU runs, emulated ranks) nothing changes."""
+        """Optional (FUSELINK_OVERLAP_REDUCE=1): a NCCL communicator of this layer's own for the sum of the shadow experts'
+        gradients, its kernels limited to a few CTAs, so that the sum can run beside the backward GEMMs (which then leave
+        those SMs free) instead of after them.  Off by default: measured on 8 B200s with three shadowed experts the
+        CTA-limited all-reduce takes longer than the GEMMs it hides behind (19.7 ms per step against 18.7 ms with the
+        default communicator after the GEMMs); at 4 GPUs with one shadowed expert the two are equal.  Collective over the
+        ranks; on host runs (gloo) an ordinary group is made and only the order of the work changes."""
         try:
             import torch.distributed as dist
             if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() == world):
@@ -122,7 +125,7 @@ class MoELayer(nn.Module):
                 self.ws.reduce_group = dist.new_group(ranks=list(range(world)), pg_options=opts)
             else:                                    # host runs (gloo): same order of work, an ordinary group
                 self.ws.reduce_group = dist.new_group(ranks=list(range(world)))
-            self.ws.overlap_reduce = os.environ.get("FUSELINK_OVERLAP_REDUCE", "1") != "0"
+            self.ws.overlap_reduce = True
         except Exception:  # noqa: BLE001 - an older PyTorch without the option: the default group, no overlap
             self.ws.reduce_group, self.ws.overlap_reduce = None, False
 
