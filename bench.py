@@ -363,6 +363,9 @@ def main():
             shadow = int(args.shadow) if (W > 1 and args.shadow != "auto") else 0
         rows = (cfg.num_experts // W + (len(shadow) if auto_shadow else shadow)) * cap
         heap_bytes = 2 * rows * H * 2 + rows * 4 + 2 * T * cfg.topk * H * 2 + (64 << 20)
+        n_copy = len(shadow) if auto_shadow else shadow
+        if n_copy:      # the expert weights and the staging of the copies' gradient rows live on the heap as well (MoEWorkspace.enable_push_reduce)
+            heap_bytes += (cfg.num_experts // W + 2 * n_copy) * 3 * H * cfg.ffn * 2 + (1 << 20)
         heap = SymmetricHeap.create(heap_bytes, device=-1 if cpu else local_rank)
         layer = MoELayer(cfg, heap, rank, world, device=dev, zipf_s=args.zipf, seed=0, fused_sgd_lr=args.lr, shadow_experts=shadow,
                          placement=args.placement)

@@ -67,6 +67,8 @@ def main():
         T, k, H, F, E = a.batch * a.seq, cfg.topk, cfg.hidden, cfg.ffn, cfg.num_experts
         rows = (E // world + (a.shadow if world > 1 else 0)) * ((T * world + 127) // 128 * 128)
         per_layer = rows * H * 2 * 2 + 2 * T * k * H * 2 + rows * 4 + (1 << 20)        # the symmetric buffers of one MoE workspace
+        if a.shadow and world > 1:                                                     # + expert weights and gradient staging of the copies
+            per_layer += (E // world + 2 * a.shadow) * 3 * H * cfg.ffn * 2 + (1 << 20)
         heap = SymmetricHeap.create(cfg.layers * per_layer + (64 << 20), device=-1 if cpu else local)
     net = MoETransformer(cfg, a.batch * a.seq, heap, rank, world, device=dev, seed=0, fused_sgd_lr=a.lr if fused else 0.0)
     if a.resume:

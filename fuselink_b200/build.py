@@ -41,7 +41,7 @@ NVCC_FLAGS = [
 ]
 CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", "-pthread"]
 
-KERNELS = ["grouped_gemm", "comm_kernels", "embbag", "kv_pack", "moe_dispatch", "moe_dispatch_noalloc", "fp8_gemm"]
+KERNELS = ["grouped_gemm", "comm_kernels", "embbag", "kv_pack", "moe_dispatch", "moe_dispatch_noalloc", "fp8_gemm", "shadow_reduce"]
 NET_SRCS = ["plugin", "tcp_transport", "tcp_endpoints", "params", "conn_manager", "ib_transport", "nvl_channel", "logging", "rdma_transport", "soft_provider", "verbs_provider", "nic_rate"]
 
 

@@ -52,6 +52,7 @@ struct KParams {
   const int* row_info;
   FlPeerPtrs peers;
   int num_peers; long long peer_rows;
+  int push_world, push_rank, push_shift;   // WGRAD: rows dealt out to the ranks that sum them (FlGemmDesc::push_world)
   float sgd_lr;
   int zero_tail;
   int group_m;
@@ -255,6 +256,14 @@ __device__ __forceinline__ void epilogue_slab(const KParams& p, const EpiSlab& e
           dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[rk]) + slot * p.ldc;
         }
       }
+    } else if (p.push_world > 0) {
+      // the row goes to the rank that sums its block, into the part of that rank's buffer kept for this source
+      valid = row < p.M;
+      const int blk = row >> p.push_shift;
+      const long long lrow = ((long long)(blk / p.push_world) << p.push_shift) + (row & ((1 << p.push_shift) - 1));
+      const long long rows_own = p.M / p.push_world;
+      dst = reinterpret_cast<__nv_bfloat16*>(p.peers.p[blk % p.push_world]) +
+            (((long long)e.g * p.push_world + p.push_rank) * rows_own + lrow) * p.ldc;
     } else {
       valid = row < p.M;
       dst = p.C + (long long)e.g * p.gsc + (long long)row * p.ldc;
@@ -531,7 +540,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
     }
-    if (p.epilogue == FL_EPI_SCATTER) fence_sys();  // peer stores visible before the kernel's completion is signalled
+    if (p.epilogue == FL_EPI_SCATTER || p.push_world > 0) fence_sys();  // peer stores visible before the kernel's completion is signalled
   }
 
   tc_fence_before_sync();
@@ -717,7 +726,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->tmem_empty[acc]), 0));
     }
-    if (p.epilogue == FL_EPI_SCATTER) fence_sys();
+    if (p.epilogue == FL_EPI_SCATTER || p.push_world > 0) fence_sys();
   }
 
   tc_fence_before_sync();
@@ -954,7 +963,7 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&sh->half_empty[h]), 0));
       }
     }
-    if (p.epilogue == FL_EPI_SCATTER) fence_sys();
+    if (p.epilogue == FL_EPI_SCATTER || p.push_world > 0) fence_sys();
   }
 
   tc_fence_before_sync();
@@ -1059,6 +1068,16 @@ extern "C" int fl_grouped_gemm(const FlGemmDesc* d, cudaStream_t stream) {
     if (d->row_info == nullptr) return bad("SCATTER needs row_info");
     for (int i = 0; i < d->num_peers; ++i)
       if (d->peers.p[i] == nullptr) return bad("SCATTER: a receive buffer is null");
+  }
+  if (d->push_world > 0) {
+    if (d->epilogue != FL_EPI_WGRAD || d->group_mode != 1) return bad("push_world belongs to the K-grouped WGRAD epilogue");
+    if (d->sgd_lr != 0.f) return bad("push_world: the update is applied by the rank that sums the rows, sgd_lr must be 0");
+    if (d->push_world > FL_MAX_PEERS || d->push_rank < 0 || d->push_rank >= d->push_world) return bad("push_world / push_rank out of range");
+    if (d->push_block_log2 < 0 || d->push_block_log2 > 16 || d->M % (d->push_world << d->push_block_log2))
+      return bad("push_world: M must be a whole number of blocks per rank");
+    for (int i = 0; i < d->push_world; ++i)
+      if (d->peers.p[i] == nullptr) return bad("push_world: a receive buffer is null");
+    p.push_world = d->push_world; p.push_rank = d->push_rank; p.push_shift = d->push_block_log2;
   }
   p.group_m = d->group_m > 0 ? d->group_m : 16;
   p.status = d->status;

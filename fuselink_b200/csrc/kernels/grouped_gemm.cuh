@@ -24,7 +24,8 @@ enum FlGemmEpilogue : int {
   FL_EPI_SWIGLU = 1,   // B rows interleaved [128 gate | 128 up] per 256; writes act = silu(gate)*up and gate/up
   FL_EPI_SCATTER = 2,  // each output row goes to peers.p[rank(row)] + slot(row)*ldc   (combine / dX return)
   FL_EPI_DSWIGLU = 3,  // accumulator is dAct; reads saved gate/up, writes dgate/dup in the interleaved layout
-  FL_EPI_WGRAD = 4,    // K-grouped: store dW_g (bf16), or apply W_g -= lr * dW_g in place when sgd_lr != 0
+  FL_EPI_WGRAD = 4,    // K-grouped: store dW_g (bf16), or apply W_g -= lr * dW_g in place when sgd_lr != 0; with push_world
+                       // the rows of dW_g go to the ranks that sum them (see push_world below)
 };
 
 struct FlGemmDesc {
@@ -48,6 +49,12 @@ struct FlGemmDesc {
   int num_peers;                                  // SCATTER: entries of `peers` in use; a row naming another rank is skipped
   long long peer_rows;                            // SCATTER: rows of every receive buffer (0 = not checked); a slot beyond it is skipped
   float sgd_lr;                                   // WGRAD: 0 => store dW
+  // WGRAD, first half of a sum over ranks done by the GEMM itself: with push_world > 0 the rows of dW_g are dealt out in
+  // blocks of 2^push_block_log2 rows, block b to rank b % push_world, and stored (bf16) into that rank's buffer
+  // peers.p[b % push_world], laid out [num_groups][push_world sources][M / push_world rows][ldc], at source push_rank and
+  // row (b / push_world) * 2^push_block_log2 + (row inside the block).  M must be a multiple of push_world blocks; sgd_lr
+  // must be 0 and C is not written.  fl_shadow_update (shadow_reduce.cuh) sums the sources and applies the result.
+  int push_world, push_rank, push_block_log2;
   int zero_tail;                                  // STORE/SWIGLU/DSWIGLU: write zeros to rows in [count, roundup(count,128))
   // fp8 block scaling (elem_bytes == 1): fp32 scales, A: [rows, K/128] per-row-per-128, B: [N/128, K/128]
   const float* a_scale; long long lda_scale;

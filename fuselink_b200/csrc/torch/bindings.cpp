@@ -6,6 +6,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "../kernels/grouped_gemm.cuh"
+#include "../kernels/shadow_reduce.cuh"
 #include "../kernels/comm_kernels.cuh"
 #include "../kernels/embbag.cuh"
 #include "../kernels/kv_pack.cuh"
@@ -63,6 +64,47 @@ static void grouped_gemm(int64_t group_mode, int64_t num_groups, int64_t cap, in
   d.sgd_lr = (float)sgd_lr; d.zero_tail = zero_tail; d.group_m = (int)group_m; d.max_ctas = (int)max_ctas;
   d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
   check_rc(fl_grouped_gemm(&d, cur_stream()), "fl_grouped_gemm", fl_gemm_last_error());
+}
+
+// Weight-gradient GEMM whose result rows go straight to the ranks that sum them (FlGemmDesc::push_world): a: [G*cap, M],
+// b: [G*cap, N] token-major, peers: every rank's staging [G][world][M / world][N].
+static void grouped_gemm_wgrad_push(int64_t num_groups, int64_t cap, torch::Tensor counts, torch::Tensor A, torch::Tensor B,
+                                    std::vector<int64_t> peers, int64_t rank, int64_t block_log2, int64_t group_m,
+                                    int64_t max_ctas, c10::optional<torch::Tensor> status) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && counts.is_cuda(), "grouped_gemm_wgrad_push needs CUDA tensors");
+  TORCH_CHECK(A.scalar_type() == torch::kBFloat16 && B.scalar_type() == torch::kBFloat16, "bf16 operands expected");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(0) == num_groups * cap && B.size(0) == num_groups * cap &&
+              A.is_contiguous() && B.is_contiguous(), "a: [G*cap, M], b: [G*cap, N] contiguous");
+  c10::cuda::CUDAGuard guard(A.device());
+  const int64_t M = A.size(1), N = B.size(1);
+  FlGemmDesc d;
+  memset(&d, 0, sizeof d);
+  d.group_mode = 1; d.num_groups = (int)num_groups; d.cap = (int)cap; d.M = (int)M; d.N = (int)N;
+  d.counts = counts.data_ptr<int>(); d.elem_bytes = 2;
+  d.A = A.data_ptr(); d.a_mn_major = 1; d.lda = M; d.gsa = cap * M;
+  d.B = B.data_ptr(); d.b_mn_major = 1; d.ldb = N; d.gsb = cap * N;
+  d.epilogue = FL_EPI_WGRAD; d.ldc = N;
+  d.peers = to_peers(peers); d.num_peers = (int)peers.size();
+  d.push_world = (int)peers.size(); d.push_rank = (int)rank; d.push_block_log2 = (int)block_log2;
+  d.group_m = (int)group_m; d.max_ctas = (int)max_ctas;
+  d.status = status.has_value() ? status->data_ptr<int>() : nullptr;
+  check_rc(fl_grouped_gemm(&d, cur_stream()), "fl_grouped_gemm", fl_gemm_last_error());
+}
+
+// Sum of the staged partial rows over the sources, then w - lr * sum (lr != 0) or the sum itself into every rank's `out`.
+static void shadow_update(torch::Tensor part, c10::optional<torch::Tensor> w, std::vector<int64_t> out_peers, int64_t groups,
+                          int64_t rank, int64_t M, int64_t N, int64_t block_log2, int64_t group_stride, double lr,
+                          int64_t max_ctas) {
+  TORCH_CHECK(part.is_cuda() && part.scalar_type() == torch::kBFloat16 && part.is_contiguous(), "staging: contiguous bf16 on the GPU");
+  TORCH_CHECK(part.numel() >= groups * M * N, "staging smaller than groups x M x N");
+  TORCH_CHECK(lr == 0.0 || (w.has_value() && w->is_cuda() && w->scalar_type() == torch::kBFloat16), "weights: bf16 on the GPU");
+  c10::cuda::CUDAGuard guard(part.device());
+  FlShadowUpdateArgs a;
+  memset(&a, 0, sizeof a);
+  a.part = part.data_ptr(); a.w = opt_ptr(w); a.out_peers = to_peers(out_peers);
+  a.groups = (int)groups; a.world = (int)out_peers.size(); a.rank = (int)rank; a.M = (int)M; a.N = (int)N;
+  a.block_log2 = (int)block_log2; a.group_stride = group_stride; a.lr = (float)lr; a.max_ctas = (int)max_ctas;
+  check_rc(fl_shadow_update(&a, cur_stream()), "fl_shadow_update", fl_shadow_update_error());
 }
 
 // ------------------------------------------------------------------------------------------------ comm
@@ -300,6 +342,8 @@ static int64_t vmm_remap_slab(int64_t region, int64_t slab, int64_t target, bool
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &grouped_gemm);
+  m.def("grouped_gemm_wgrad_push", &grouped_gemm_wgrad_push);
+  m.def("shadow_update", &shadow_update);
   m.def("gemm_set_variant", [](int64_t v) { fl_gemm_set_variant((int)v); });
   m.def("gemm_get_variant", []() { return fl_gemm_get_variant(); });
   m.def("fp8_quantize_rows", &fp8_quantize_rows);

@@ -1,7 +1,7 @@
 """Python entry points of the tcgen05 grouped GEMM (csrc/kernels/grouped_gemm.cu)."""
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -58,6 +58,33 @@ def grouped_gemm_wgrad(a: torch.Tensor, b: torch.Tensor, counts: Optional[torch.
     C.grouped_gemm(1, G, cap, M, N, 0, counts, a, True, M, cap * M, b, True, N, cap * N, EPI_WGRAD, out, N, M * N,
                    None, 0, None, None, [], sgd_lr, False, group_m, max_ctas, status, 0)
     return out
+
+
+def push_block_log2(M: int, world: int, most: int = 8) -> int:
+    """Rows of a pushed weight gradient are dealt out to the ranks in blocks of 2^b rows: the largest b <= ``most`` that
+    gives every rank a whole number of blocks, or -1 when M is no multiple of the number of ranks."""
+    for b in range(most, -1, -1):
+        if M % (world << b) == 0:
+            return b
+    return -1
+
+
+def grouped_gemm_wgrad_push(a: torch.Tensor, b: torch.Tensor, counts: torch.Tensor, cap: int, G: int, peers: Sequence[int],
+                            rank: int, block_log2: int, *, group_m: int = 16, max_ctas: int = 0,
+                            status: Optional[torch.Tensor] = None) -> None:
+    """K-grouped GEMM as grouped_gemm_wgrad, but the rows of every ``C_g`` go from the epilogue straight to the ranks
+    that sum them: block i (2^block_log2 rows) of group g into ``peers[i % world]``, a buffer laid out
+    [G, world, M / world, N], at source ``rank`` and local block ``i // world``.  ``shadow_update`` is the other half."""
+    require_native().grouped_gemm_wgrad_push(G, cap, counts, a, b, list(peers), rank, block_log2, group_m, max_ctas, status)
+
+
+def shadow_update(part: torch.Tensor, w: Optional[torch.Tensor], out_peers: Sequence[int], groups: int, rank: int, M: int,
+                  N: int, block_log2: int, group_stride: int, lr: float, max_ctas: int = 0) -> None:
+    """For the blocks of rows this rank sums: the fp32 sum over the sources staged in ``part`` ([groups, world, M / world,
+    N], written by every rank's grouped_gemm_wgrad_push), then ``w - lr * sum`` (or the sum itself when ``lr`` is 0)
+    stored as bf16 into every rank's copy ``out_peers[d]`` ([groups] matrices of [M, N], ``group_stride`` elements
+    apart).  Run it once every rank's GEMM is known to be complete."""
+    require_native().shadow_update(part, w, list(out_peers), groups, rank, M, N, block_log2, group_stride, lr, max_ctas)
 
 
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 128) -> torch.Tensor:

@@ -16,6 +16,7 @@ every rank, its rows are computed where they originate, and the copies' weight g
 from __future__ import annotations
 
 import dataclasses
+import types
 from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
@@ -144,6 +145,10 @@ class MoEWorkspace:
             self.s_dgu = torch.empty(rows, 2 * F // 128, dtype=torch.float32, device=dev)
             self.wq = {}                                                     # per-weight (e4m3, scales), refreshed each step
         self.pending_shadow = None
+        # Sum of the copies' weight gradients done by this library instead of an all-reduce (enable_push_reduce): the
+        # copies' weight-gradient GEMMs store their result rows into the staging of the rank that sums them, and that rank
+        # writes the updated rows into every copy.
+        self.push = None
         # Overlap of the shadow experts' gradient all-reduce with the rest of the backward pass (set by MoELayer once it has
         # a communicator of its own whose kernels are limited to `reduce_ctas` CTAs): the copies' weight gradients are then
         # computed first and summed while dX and the owned experts' weight gradients run on the remaining SMs.
@@ -154,6 +159,28 @@ class MoEWorkspace:
         self.parity = 0
         self.step_parity = 0
         self.launches = 0   # kernels of this library launched through this workspace (bench accounting)
+
+    def enable_push_reduce(self, max_ctas: int = 0) -> bool:
+        """Moves the sum of the shadow experts' weight gradients from an all-reduce into this library's kernels.  Allocates,
+        on the symmetric heap, the expert weights themselves (``self.push.w13`` / ``.w2``: the layer must use these as its
+        parameters, since peers write the updated rows of the copies into them) and the staging the partial gradients are
+        pushed into.  Returns False, and changes nothing that matters, when the shapes do not divide over the ranks or
+        the heap has no room; call it on every rank or on none."""
+        cfg, W = self.cfg, self.heap.world
+        H, F = cfg.hidden, cfg.ffn
+        b13, b2 = gemm.push_block_log2(2 * F, W), gemm.push_block_log2(H, W)
+        if W < 2 or not self.nshadow or b13 < 0 or b2 < 0 or H % 8 or F % 8:
+            return False
+        try:
+            bf = torch.bfloat16
+            w13 = self.heap.alloc_tensor([self.epr, 2 * F, H], bf)
+            w2 = self.heap.alloc_tensor([self.epr, H, F], bf)
+            p13 = self.heap.alloc_tensor([self.nshadow, W, 2 * F // W, H], bf)
+            p2 = self.heap.alloc_tensor([self.nshadow, W, H // W, F], bf)
+        except MemoryError:
+            return False
+        self.push = types.SimpleNamespace(w13=w13, w2=w2, p13=p13, p2=p2, b13=b13, b2=b2, max_ctas=max_ctas)
+        return True
 
     def counts_now(self) -> torch.Tensor:
         return self.counts.local[self.step_parity]
@@ -426,8 +453,17 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
             gemm.grouped_gemm_wgrad(dgu[:cut], xd[:cut], counts[:R], ws.cap, R, out=dw13[:R], status=st, max_ctas=beside)
             dw2[R:].zero_()                                          # copy slots: filled in once the sums are complete, empty
             dw13[R:].zero_()                                         # ones stay zero
+        pk = ws.push
         if overlap:
             shadow_grads = early                                     # computed, and their reduction started, before dX
+        elif S and sgd_lr and pk is not None and w13.data_ptr() == pk.w13.addr() and w2.data_ptr() == pk.w2.addr():
+            # the copies' gradient rows go from the GEMMs' epilogues to the ranks that sum them; moe_backward_finish
+            # continues once every rank has signalled (shadow_update)
+            end = cut + S * ws.cap
+            gemm.grouped_gemm_wgrad_push(dgu[cut:end], xd[cut:end], counts[R:R + S], ws.cap, S, pk.p13.peers(), h.rank, pk.b13, status=st)
+            gemm.grouped_gemm_wgrad_push(dyd[cut:end], act[cut:end], counts[R:R + S], ws.cap, S, pk.p2.peers(), h.rank, pk.b2, status=st)
+            ws.launches += 2
+            shadow_grads = S
         elif S:
             end = cut + S * ws.cap                                   # empty copy slots at the end take no part
             shadow_grads = (gemm.grouped_gemm_wgrad(dgu[cut:end], xd[cut:end], counts[R:R + S], ws.cap, S, status=st),
@@ -456,6 +492,8 @@ def start_shadow_reduction(ws: MoEWorkspace):
     pending, ws.pending_shadow = ws.pending_shadow, None
     if ws.started_shadow is not None:                      # already running since the copies' gradients were computed
         works, ws.started_shadow = ws.started_shadow, None
+    elif isinstance(pending[0], int):                      # pushed by the GEMMs: nothing to start
+        works = []
     else:
         works = ws.reduce_shadow_grads(ws, pending[0]) or []
     return pending, works
@@ -466,7 +504,19 @@ def finish_shadow_grads(ws: MoEWorkspace, started) -> None:
     update, the trailing slots of the gradients moe_backward_experts returned."""
     if started is None:
         return
-    ((g13, g2), w13, w2, dw13, dw2, sgd_lr), works = started
+    (grads, w13, w2, dw13, dw2, sgd_lr), works = started
+    if isinstance(grads, int):
+        # pushed: every rank's partial rows are in the staging (the callers wait for the ranks' signal first); sum the rows
+        # this rank is responsible for, update them, and write them into every rank's copy
+        S, R, pk, cfg, h = grads, ws.epr_real, ws.push, ws.cfg, ws.heap
+        M13, N13, M2, N2 = 2 * cfg.ffn, cfg.hidden, cfg.hidden, cfg.ffn
+        gemm.shadow_update(pk.p13.local, w13[R:], [a + R * M13 * N13 * 2 for a in pk.w13.peers()], S, h.rank, M13, N13, pk.b13,
+                           M13 * N13, sgd_lr, pk.max_ctas)
+        gemm.shadow_update(pk.p2.local, w2[R:], [a + R * M2 * N2 * 2 for a in pk.w2.peers()], S, h.rank, M2, N2, pk.b2,
+                           M2 * N2, sgd_lr, pk.max_ctas)
+        ws.launches += 2
+        return
+    g13, g2 = grads
     for w in works:
         if hasattr(w, "wait"):
             w.wait()

@@ -277,6 +277,36 @@ class Model:
 
 
     # ---------------------------------------------------------------------------------------- fp8 arm
+    def grouped_gemm_wgrad_push(self, G, cap, counts, A, B, peers, rank, block_log2, group_m, max_ctas, status):
+        # dW_g = A_g^T @ B_g, its rows dealt out in blocks to the ranks that sum them: block b of group g lands in rank
+        # b % world's staging [G][world sources][M / world][N] at source `rank`
+        assert A.dtype == torch.bfloat16 and B.dtype == torch.bfloat16 and A.is_contiguous() and B.is_contiguous()
+        M, N, world, blk = A.shape[1], B.shape[1], len(peers), 1 << block_log2
+        assert A.shape[0] == G * cap and B.shape[0] == G * cap and M % (world * blk) == 0 and 0 <= rank < world
+        own = M // world
+        for g in range(G):
+            n = min(int(counts[g]), cap)
+            c = (A[g * cap: g * cap + n].float().t() @ B[g * cap: g * cap + n].float()).to(torch.bfloat16)
+            c = c.view(M // (world * blk), world, blk, N)                    # [round, owner, row in block, N]
+            for d in range(world):
+                dst = self._view(peers[d] + ((g * world + rank) * own) * N * 2, [own, N], torch.bfloat16)
+                dst.copy_(c[:, d].reshape(own, N))
+
+    def shadow_update(self, part, w, out_peers, groups, rank, M, N, block_log2, group_stride, lr, max_ctas):
+        world, blk = len(out_peers), 1 << block_log2
+        assert part.dtype == torch.bfloat16 and M % (world * blk) == 0 and N % 8 == 0 and group_stride % 8 == 0
+        own = M // world
+        total = part.reshape(-1)[: groups * M * N].view(groups, world, own, N).float().sum(1)       # [groups, own, N]
+        for g in range(groups):
+            # local block i, row j -> row (i * world + rank) * blk + j of the full matrix
+            rows = ((torch.arange(own // blk).view(-1, 1) * world + rank) * blk + torch.arange(blk).view(1, -1)).reshape(-1)
+            new = total[g]
+            if lr:
+                new = w.reshape(-1)[g * group_stride: g * group_stride + M * N].view(M, N)[rows].float() - lr * new
+            new = new.to(torch.bfloat16)
+            for d in range(world):
+                self._view(out_peers[d] + g * group_stride * 2, [M, N], torch.bfloat16)[rows] = new
+
     def fp8_quantize_rows(self, x, q, scale, counts, cap):
         from fuselink_b200.ops import fp8 as f8
         rows = x.shape[0]

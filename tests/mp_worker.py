@@ -111,6 +111,34 @@ def main():
             for m in (sh, base):
                 m.zero_grad(set_to_none=True)
 
+    # ---- shadowed experts with the fused update: the copies' gradient rows are pushed by the weight-gradient GEMMs to the
+    # rank that sums them, which writes the updated rows into every copy; against the all-reduce formulation ----------
+    if world > 1:
+        lr, arms = 0.01, {}
+        for push in ("1", "0"):
+            os.environ["FUSELINK_PUSH_REDUCE"] = push
+            arms[push] = MoELayer(cfg, heap, rank, world, device=dev, seed=4, fused_sgd_lr=lr, name="moe_push" + push, shadow_experts=2)
+        os.environ.pop("FUSELINK_PUSH_REDUCE")
+        assert arms["1"].ws.push is not None and arms["0"].ws.push is None
+        before = {n: getattr(arms["0"], n).detach().float().clone() for n in ("w13", "w2")}
+        for step in range(3):
+            g = torch.Generator(device=dev).manual_seed(170 + step * 10 + rank)
+            x = torch.randn(cfg.tokens, cfg.hidden, generator=g, device=dev).to(torch.bfloat16)
+            for m in arms.values():
+                m(x.clone().requires_grad_(True)).float().pow(2).sum().backward()
+            torch.cuda.synchronize()
+            heap.check_status("moe push")
+        epr = cfg.num_experts // world
+        for n in ("w13", "w2"):
+            a, b = getattr(arms["1"], n).detach().float(), getattr(arms["0"], n).detach().float()
+            moved = (b - before[n]).abs().max().item()
+            assert moved > 1e-3, f"{n}: the update must be visible ({moved})"
+            err = (a - b).abs().max().item()
+            assert err < 0.05 * moved + 3e-4, f"rank {rank} {n}: pushed sum {err} away from the all-reduce arm (weights moved {moved})"
+            copies = [torch.empty_like(a[epr:]) for _ in range(world)]
+            dist.all_gather(copies, a[epr:].contiguous())
+            assert all(torch.equal(c, copies[0]) for c in copies), f"{n}: the copies must stay identical on every rank"
+
     # ---- experts placed by expected load, then the layer rebalances itself from its own routing -----------------
     # (copy slots start empty; rebalance() picks the shadows and spreads their rows over the ranks' copies)
     if world > 1 and cfg.num_experts // world > 1:

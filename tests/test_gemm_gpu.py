@@ -208,3 +208,49 @@ def test_throughput_smoke():
     tf = 2.0 * cap * N * K / ms / 1e9
     print(f"\n[gemm smoke] 8192x4096x4096 bf16: {ms:.3f} ms  {tf:.0f} TFLOP/s")
     assert tf > 50, "tensor-core path is not being used"
+
+
+@pytest.mark.parametrize("world,M,lr", [(2, 512, 0.5), (4, 1024, 0.5), (2, 384, 0.0), (8, 2048, 0.25)])
+def test_wgrad_push_and_update_sum_the_ranks_partials(world, M, lr):
+    """The two halves of the sum of replicated experts' weight gradients, with the ranks emulated one after the other on
+    this GPU (neither kernel waits for another): every rank's GEMM deals its result rows out to the staging of the rank
+    that sums them, then every rank sums its blocks, updates them and writes them into every copy.  Against fp32:
+    w - lr * sum over ranks of A_r^T B_r (or the sum itself), identical in every copy."""
+    from fuselink_b200.ops import gemm
+    G, cap, N = 2, 512, 256
+    blk = gemm.push_block_log2(M, world)
+    assert blk >= 0
+    counts = [torch.tensor([300 - 17 * r, 37 * (r % 2)], dtype=torch.int32, device="cuda") for r in range(world)]
+    a = [_mk([G * cap, M], seed=10 + r) for r in range(world)]
+    b = [_mk([G * cap, N], seed=50 + r) for r in range(world)]
+    stage = [torch.full((G, world, M // world, N), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    w0 = _mk([G, M, N], 0.5, seed=99)
+    copies = [w0.clone() for _ in range(world)]
+    outs = copies if lr else [torch.full_like(w0, 5.0) for _ in range(world)]
+    st = _status()
+    for r in range(world):
+        gemm.grouped_gemm_wgrad_push(a[r], b[r], counts[r], cap, G, [s.data_ptr() for s in stage], r, blk, status=st)
+    for r in range(world):
+        gemm.shadow_update(stage[r], copies[r] if lr else None, [o.data_ptr() for o in outs], G, r, M, N, blk, M * N, lr)
+    torch.cuda.synchronize()
+    _check_status(st)
+    for g in range(G):
+        total = sum(a[r][g * cap:g * cap + int(counts[r][g])].float().t() @ b[r][g * cap:g * cap + int(counts[r][g])].float()
+                    for r in range(world))
+        ref = w0[g].float() - lr * total if lr else total
+        err = (outs[0][g].float() - ref).abs().max().item()
+        # every rank's partial is rounded to bf16 once, the result once
+        assert err < 2e-2 * (total.abs().max().item() * (lr or 1.0)) + 4e-3 * ref.abs().max().item(), (g, err)
+    for r in range(1, world):
+        assert torch.equal(outs[r], outs[0]), "every copy holds the same bits"
+
+
+def test_wgrad_push_rejects_rows_that_do_not_divide_over_the_ranks():
+    from fuselink_b200.ops import gemm
+    a, b = _mk([256, 384], seed=1), _mk([256, 256], seed=2)
+    counts = torch.tensor([100], dtype=torch.int32, device="cuda")
+    stage = torch.zeros(1, 2, 192, 256, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError):
+        gemm.grouped_gemm_wgrad_push(a, b, counts, 256, 1, [stage.data_ptr()] * 2, 0, 8)      # 384 rows: not 2 x 256
+    with pytest.raises(RuntimeError):
+        gemm.grouped_gemm_wgrad_push(a, b, counts, 256, 1, [stage.data_ptr()] * 2, 2, 6)      # rank 2 of 2

@@ -206,17 +206,20 @@ def test_an_empty_copy_slot_costs_nothing_and_changes_nothing():
     _run_on_model(2, shadow=(-1, -1))
 
 
-@pytest.mark.parametrize("world,placement,shape", [(2, "", ""), (4, "", ""), (2, "balanced", ""), (4, "balanced", ""), (3, "balanced", "12 3 20")])
-def test_expert_parallel_step_between_processes(world, placement, shape, tmp_path):
-    """Real processes over a shared-memory heap: forward, backward, the all-reduce of the shadow experts' gradients, the
-    fused update, and a change of the shadowed experts by broadcast -- all against an fp32 autograd oracle."""
+@pytest.mark.parametrize("world,placement,shape,push", [(2, "", "", "1"), (2, "", "", "0"), (4, "", "", "1"), (2, "balanced", "", "1"),
+                                                        (4, "balanced", "", "1"), (3, "balanced", "12 3 20", "1")])
+def test_expert_parallel_step_between_processes(world, placement, shape, push, tmp_path):
+    """Real processes over a shared-memory heap: forward, backward, the sum of the shadow experts' gradients over the ranks
+    (pushed by the weight-gradient GEMMs to the rank that sums and updates each block of rows; an all-reduce with
+    FUSELINK_PUSH_REDUCE=0, without the fused update, or when the rows do not divide over the ranks, as with 3 ranks here),
+    the fused update, and a change of the shadowed experts by broadcast -- all against an fp32 autograd oracle."""
     import os
     import socket
     import subprocess
     import sys
     here = os.path.dirname(os.path.abspath(__file__))
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
-    env = dict(os.environ, FL_MODEL_LOCK=str(tmp_path / "reserve.lock"), FL_MOE_PLACEMENT=placement)
+    env = dict(os.environ, FL_MODEL_LOCK=str(tmp_path / "reserve.lock"), FL_MOE_PLACEMENT=placement, FUSELINK_PUSH_REDUCE=push)
     if shape:                                                     # experts, top-k, tokens per rank (default 8, 2, 32)
         env.update(zip(("FL_MOE_E", "FL_MOE_K", "FL_MOE_T"), shape.split()))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",

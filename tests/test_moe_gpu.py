@@ -62,7 +62,8 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
             # backward
             dws = [M.moe_backward_dispatch(wss[r], douts[r], routes[r][1].contiguous(), routes[r][0].contiguous()) for r in range(world)]
             grads = [M.moe_backward_experts(wss[r], layers[r].w13.data, layers[r].w2.data, sgd, True) for r in range(world)]
-            if any(e >= 0 for e in shadow):
+            if any(e >= 0 for e in shadow) and not isinstance(wss[0].pending_shadow[0], int):
+                # (an int: the GEMMs have pushed the copies' gradient rows to the ranks that sum them -- fused update)
                 # the ranks are emulated on one GPU: the sum over ranks that NCCL would do is done here
                 totals = [sum(wss[r].pending_shadow[0][i] for r in range(world)) for i in range(2)]
                 for w_ in wss:
