@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(512) shadow_update_kernel(const Params p) {
       if (s < world) add8(acc, q[s]);
     if (p.lr != 0.f) {
       float wv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      add8(wv, __ldg(p.w + off));
+      add8(wv, p.w[off]);      // a plain load: this thread rewrites the same 16 bytes of the own copy below
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = fmaf(-p.lr, acc[i], wv[i]);
     }

@@ -223,6 +223,11 @@ def test_wgrad_push_and_update_sum_the_ranks_partials(world, M, lr):
     counts = [torch.tensor([300 - 17 * r, 37 * (r % 2)], dtype=torch.int32, device="cuda") for r in range(world)]
     a = [_mk([G * cap, M], seed=10 + r) for r in range(world)]
     b = [_mk([G * cap, N], seed=50 + r) for r in range(world)]
+    for r in range(world):          # the contraction runs over whole 64-row blocks: rows past the count are zero, as the MoE step leaves them
+        for g in range(G):
+            c = int(counts[r][g])
+            a[r][g * cap + c:g * cap + (c + 127) // 128 * 128] = 0
+            b[r][g * cap + c:g * cap + (c + 127) // 128 * 128] = 0
     stage = [torch.full((G, world, M // world, N), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
     w0 = _mk([G, M, N], 0.5, seed=99)
     copies = [w0.clone() for _ in range(world)]
