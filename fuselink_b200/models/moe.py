@@ -104,11 +104,11 @@ class MoELayer(nn.Module):
         self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr + shadows, 2F, H], gate/up interleaved by 128
         self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr + shadows, H, F]
         self.ws = MoEWorkspace(heap, cfg, name) if heap is not None else None
-        if (self.ws is not None and world > 1 and len(cfg.shadow) > 0 and fused_sgd_lr
-                and os.environ.get("FUSELINK_PUSH_REDUCE", "1") != "0" and self.ws.enable_push_reduce()):
+        if (self.ws is not None and world > 1 and len(cfg.shadow) > 0 and os.environ.get("FUSELINK_PUSH_REDUCE", "1") != "0"
+                and self.ws.enable_push_reduce(weights=bool(fused_sgd_lr)) and fused_sgd_lr):
             # The copies' gradients are summed by this library (rows pushed from the weight-gradient GEMMs to the rank that
-            # sums them, updated rows written into every copy), so the expert weights live on the symmetric heap.  Without
-            # room there, or with FUSELINK_PUSH_REDUCE=0, they stay ordinary tensors and the sum is an all-reduce.
+            # sums them; with the fused update the updated rows are written into every copy, so the expert weights live on
+            # the symmetric heap).  Without room there, or with FUSELINK_PUSH_REDUCE=0, the sum is an all-reduce.
             for name_, sym in (("w13", self.ws.push.w13), ("w2", self.ws.push.w2)):
                 t = sym.local
                 t.copy_(getattr(self, name_).detach())

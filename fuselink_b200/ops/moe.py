@@ -149,6 +149,7 @@ class MoEWorkspace:
         # copies' weight-gradient GEMMs store their result rows into the staging of the rank that sums them, and that rank
         # writes the updated rows into every copy.
         self.push = None
+        self.gathering_shadow = None
         # Overlap of the shadow experts' gradient all-reduce with the rest of the backward pass (set by MoELayer once it has
         # a communicator of its own whose kernels are limited to `reduce_ctas` CTAs): the copies' weight gradients are then
         # computed first and summed while dX and the owned experts' weight gradients run on the remaining SMs.
@@ -160,12 +161,14 @@ class MoEWorkspace:
         self.step_parity = 0
         self.launches = 0   # kernels of this library launched through this workspace (bench accounting)
 
-    def enable_push_reduce(self, max_ctas: int = 0) -> bool:
+    def enable_push_reduce(self, weights: bool = True, max_ctas: int = 0) -> bool:
         """Moves the sum of the shadow experts' weight gradients from an all-reduce into this library's kernels.  Allocates,
-        on the symmetric heap, the expert weights themselves (``self.push.w13`` / ``.w2``: the layer must use these as its
-        parameters, since peers write the updated rows of the copies into them) and the staging the partial gradients are
-        pushed into.  Returns False, and changes nothing that matters, when the shapes do not divide over the ranks or
-        the heap has no room; call it on every rank or on none."""
+        on the symmetric heap, the staging the partial gradients are pushed into and, with ``weights`` (the fused SGD
+        update), the expert weights themselves (``self.push.w13`` / ``.w2``: the layer must use these as its parameters,
+        since peers write the updated rows of the copies into them); without ``weights`` the buffers the summed gradients
+        of the copies are written into by the ranks that sum them (``self.push.g13`` / ``.g2``).  Returns False, and changes
+        nothing that matters, when the shapes do not divide over the ranks or the heap has no room; call it on every rank
+        or on none."""
         cfg, W = self.cfg, self.heap.world
         H, F = cfg.hidden, cfg.ffn
         b13, b2 = gemm.push_block_log2(2 * F, W), gemm.push_block_log2(H, W)
@@ -173,13 +176,15 @@ class MoEWorkspace:
             return False
         try:
             bf = torch.bfloat16
-            w13 = self.heap.alloc_tensor([self.epr, 2 * F, H], bf)
-            w2 = self.heap.alloc_tensor([self.epr, H, F], bf)
+            w13 = self.heap.alloc_tensor([self.epr, 2 * F, H], bf) if weights else None
+            w2 = self.heap.alloc_tensor([self.epr, H, F], bf) if weights else None
+            g13 = None if weights else self.heap.alloc_tensor([self.nshadow, 2 * F, H], bf)
+            g2 = None if weights else self.heap.alloc_tensor([self.nshadow, H, F], bf)
             p13 = self.heap.alloc_tensor([self.nshadow, W, 2 * F // W, H], bf)
             p2 = self.heap.alloc_tensor([self.nshadow, W, H // W, F], bf)
         except MemoryError:
             return False
-        self.push = types.SimpleNamespace(w13=w13, w2=w2, p13=p13, p2=p2, b13=b13, b2=b2, max_ctas=max_ctas)
+        self.push = types.SimpleNamespace(w13=w13, w2=w2, g13=g13, g2=g2, p13=p13, p2=p2, b13=b13, b2=b2, max_ctas=max_ctas)
         return True
 
     def counts_now(self) -> torch.Tensor:
@@ -456,7 +461,8 @@ def moe_backward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor, 
         pk = ws.push
         if overlap:
             shadow_grads = early                                     # computed, and their reduction started, before dX
-        elif S and sgd_lr and pk is not None and w13.data_ptr() == pk.w13.addr() and w2.data_ptr() == pk.w2.addr():
+        elif S and pk is not None and ((sgd_lr and pk.w13 is not None and w13.data_ptr() == pk.w13.addr() and w2.data_ptr() == pk.w2.addr())
+                                       or (not sgd_lr and pk.g13 is not None)):
             # the copies' gradient rows go from the GEMMs' epilogues to the ranks that sum them; moe_backward_finish
             # continues once every rank has signalled (shadow_update)
             end = cut + S * ws.cap
@@ -510,10 +516,19 @@ def finish_shadow_grads(ws: MoEWorkspace, started) -> None:
         # this rank is responsible for, update them, and write them into every rank's copy
         S, R, pk, cfg, h = grads, ws.epr_real, ws.push, ws.cfg, ws.heap
         M13, N13, M2, N2 = 2 * cfg.ffn, cfg.hidden, cfg.hidden, cfg.ffn
-        gemm.shadow_update(pk.p13.local, w13[R:], [a + R * M13 * N13 * 2 for a in pk.w13.peers()], S, h.rank, M13, N13, pk.b13,
-                           M13 * N13, sgd_lr, pk.max_ctas)
-        gemm.shadow_update(pk.p2.local, w2[R:], [a + R * M2 * N2 * 2 for a in pk.w2.peers()], S, h.rank, M2, N2, pk.b2,
-                           M2 * N2, sgd_lr, pk.max_ctas)
+        if sgd_lr:
+            gemm.shadow_update(pk.p13.local, w13[R:], [a + R * M13 * N13 * 2 for a in pk.w13.peers()], S, h.rank, M13, N13, pk.b13,
+                               M13 * N13, sgd_lr, pk.max_ctas)
+            gemm.shadow_update(pk.p2.local, w2[R:], [a + R * M2 * N2 * 2 for a in pk.w2.peers()], S, h.rank, M2, N2, pk.b2,
+                               M2 * N2, sgd_lr, pk.max_ctas)
+        else:
+            # the summed rows go into every rank's buffer; a rank's own buffer is complete once every rank has run this and
+            # signalled
+            gemm.shadow_update(pk.p13.local, None, pk.g13.peers(), S, h.rank, M13, N13, pk.b13, M13 * N13, 0.0, pk.max_ctas)
+            gemm.shadow_update(pk.p2.local, None, pk.g2.peers(), S, h.rank, M2, N2, pk.b2, M2 * N2, 0.0, pk.max_ctas)
+            barrier(h, ws.name + ":bg", signal=True, wait=False)
+            ws.gathering_shadow = (S, dw13, dw2)              # moe_backward_complete waits for the ranks and fills dw13 / dw2
+            ws.launches += 1
         ws.launches += 2
         return
     g13, g2 = grads
@@ -545,6 +560,22 @@ def moe_backward_finish(ws: MoEWorkspace, need_dx: bool = True) -> Optional[torc
     return dx
 
 
+def moe_backward_complete(ws: MoEWorkspace) -> None:
+    """Phase 4, only where the copies' summed gradients are handed out (no fused update) and were summed by this library:
+    once every rank has written the rows it summed into this rank's buffer, they are copied into the copy slots of the
+    gradients moe_backward_experts returned."""
+    pending = getattr(ws, "gathering_shadow", None)
+    if pending is None:
+        return
+    ws.gathering_shadow = None
+    S, dw13, dw2 = pending
+    R, pk = ws.epr_real, ws.push
+    barrier(ws.heap, ws.name + ":bg", signal=False, wait=True)
+    dw13[R:R + S].copy_(pk.g13.local[:S])
+    dw2[R:R + S].copy_(pk.g2.local[:S])
+    ws.launches += 1
+
+
 def moe_backward(ws: MoEWorkspace, dout: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor,
                  w13: torch.Tensor, w2: torch.Tensor, sgd_lr: float = 0.0, need_dx: bool = True):
     """Returns (dx, dtopk_w, dw13, dw2).  With ``sgd_lr`` the expert weights are updated in place by the wgrad
@@ -552,6 +583,7 @@ def moe_backward(ws: MoEWorkspace, dout: torch.Tensor, topk_idx: torch.Tensor, t
     dw = moe_backward_dispatch(ws, dout.contiguous(), topk_idx, topk_w)
     dw13, dw2 = moe_backward_experts(ws, w13, w2, sgd_lr, need_dx)
     dx = moe_backward_finish(ws, need_dx)
+    moe_backward_complete(ws)
     return dx, dw, dw13, dw2
 
 

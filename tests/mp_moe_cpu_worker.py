@@ -43,7 +43,7 @@ def main():                      # the change of shadows below names expert 5: s
                              placement=os.environ.get("FL_MOE_PLACEMENT") or None)
             shadow = layer.cfg.shadow
             assert shadow == (0, 1)
-            pushed = bool(sgd) and os.environ.get("FUSELINK_PUSH_REDUCE", "1") != "0" and (2 * F) % world == 0 and H % world == 0
+            pushed = os.environ.get("FUSELINK_PUSH_REDUCE", "1") != "0" and (2 * F) % world == 0 and H % world == 0
             assert (layer.ws.push is not None) == pushed, "the copies' gradients are summed by the library's own kernels when they can be"
             # the experts themselves, once each, as fp32 leaves (every rank builds the same oracle)
             wg_, wu_ = gemm.deinterleave_gate_up(layer.w13.data[:epr])

@@ -69,6 +69,8 @@ def _run(world, T=256, H=256, Fd=512, E=8, k=2, sgd=0.0, steps=1, fp8=False, sha
                 for w_ in wss:
                     w_.reduce_shadow_grads = lambda ws_, gs, totals=totals: [g.copy_(t) for g, t in zip(gs, totals)]
             dxs = [M.moe_backward_finish(wss[r], True) for r in range(world)]
+            for r in range(world):
+                M.moe_backward_complete(wss[r])
             sync()
             for h in heaps:
                 h.check_status("backward")
