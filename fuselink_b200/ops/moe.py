@@ -9,9 +9,13 @@ backward  dw = <dOut, y_k>; dispatch(w_k * dOut) to the slots chosen in forward 
           dAct GEMM (B MN-major, DSWIGLU epilogue) -> wgrad W2, wgrad W13 (K-grouped, both operands MN-major)
           -> dX GEMM (B MN-major, SCATTER epilogue) -> barrier -> sum over k
 
-There is no stand-alone all-to-all and no framework permute in either direction; NCCL is not called -- except for one
-all-reduce per step when experts are shadowed (``MoEConfig.shadow``, ``slot_table``): a hot expert is then replicated on
-every rank, its rows are computed where they originate, and the copies' weight gradients are summed over the ranks.
+There is no stand-alone all-to-all and no framework permute in either direction, and NCCL is not called.  When experts
+are shadowed (``MoEConfig.shadow``, ``slot_table``) a hot expert is replicated on every rank, its rows are computed on any
+rank's copy, and the copies' weight gradients are summed over the ranks by two more kernels of this library
+(``MoEWorkspace.enable_push_reduce``: the weight-gradient GEMM's epilogue stores each block of result rows into the
+staging of the rank that sums it; that rank writes the updated rows, or the summed gradient rows, into every copy).
+Where that is not possible (rows that do not divide over the ranks, no room on the heap, FUSELINK_PUSH_REDUCE=0) the sum
+is one all-reduce per step on the process group.
 """
 from __future__ import annotations
 
