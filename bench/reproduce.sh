@@ -6,7 +6,7 @@
 #   NGPU=1 bench/reproduce.sh            # kernels + flagship step on one GPU
 #   NGPU=8 bench/reproduce.sh            # adds p2p / all-to-all sweeps, DLRM, serving and the NCCL arms
 #   SECTIONS="moe dlrm" NGPU=8 bench/reproduce.sh
-#   SECTIONS="moe-shadow gemm-sweep" NGPU=8 bench/reproduce.sh     # optional sections
+#   SECTIONS="moe-shadow shadow-reduce gemm-sweep" NGPU=8 bench/reproduce.sh     # optional sections
 set -uo pipefail
 cd "$(dirname "$0")/.."
 NGPU=${NGPU:-1}; OUT=${OUT:-bench_results.jsonl}; STEPS=${STEPS:-20}; WARMUP=${WARMUP:-5}
@@ -31,11 +31,17 @@ for s in $SECTIONS; do
         run "moe contiguous placement, no shadows" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --placement contiguous --shadow 0 --no-baseline --no-other
         for n in 0 1 2 3; do run "moe shadow=$n (rows stay local)" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n" --no-baseline --no-other; done
       fi ;;
+    shadow-reduce)   # not in the default list: the sum of the copies' gradients, own kernels against the all-reduce, and the two kernels alone
+      run "push GEMM + update kernel, one GPU" python bench/shadow_reduce_case.py --world 8 --groups 1 --rows 4096 --iters 5
+      if [ "$NGPU" -ge 2 ]; then
+        for p in 1 0; do FUSELINK_PUSH_REDUCE=$p run "moe shadows forced, push=$p" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --tolerance 0 --no-baseline --no-other; done
+      fi ;;
     gemm-sweep)   # not in the default list: tile order x kernel variant for every GEMM of the step
       for c in fwd1 fwd2 dact dx wgrad2 wgrad13; do run "gemm sweep $c" python bench/gemm_case.py --case "$c" --rows 16384 --iters 5 --sweep; done ;;
     p2p)
       if [ "$NGPU" -ge 2 ]; then run "p2p" tr bench/p2p_sweep.py --pairs 1; fi
-      if [ "$NGPU" -ge 4 ]; then run "p2p 2 pairs" tr bench/p2p_sweep.py --pairs 2; run "p2p relays" tr bench/p2p_sweep.py --pairs 1 --relays 2; fi ;;
+      if [ "$NGPU" -ge 4 ]; then run "p2p 2 pairs" tr bench/p2p_sweep.py --pairs 2; run "p2p relays" tr bench/p2p_sweep.py --pairs 1 --relays 2; fi
+      if [ "$NGPU" -ge 8 ]; then run "p2p 4 pairs" tr bench/p2p_sweep.py --pairs 4; fi ;;
     a2a)
       if [ "$NGPU" -ge 2 ]; then run "a2a" tr bench/a2a_sweep.py; fi ;;
     dlrm)
