@@ -104,6 +104,7 @@ class MoELayer(nn.Module):
         self.w13 = nn.Parameter(torch.stack(w13).to(device))   # [epr + shadows, 2F, H], gate/up interleaved by 128
         self.w2 = nn.Parameter(torch.stack(w2).to(device))     # [epr + shadows, H, F]
         self.ws = MoEWorkspace(heap, cfg, name) if heap is not None else None
+        self.register_state_dict_pre_hook(lambda module, prefix, keep_vars: module.weights_ready())
         if (self.ws is not None and world > 1 and len(cfg.shadow) > 0 and os.environ.get("FUSELINK_PUSH_REDUCE", "1") != "0"
                 and self.ws.enable_push_reduce(weights=bool(fused_sgd_lr)) and fused_sgd_lr):
             # The copies' gradients are summed by this library (rows pushed from the weight-gradient GEMMs to the rank that
@@ -165,10 +166,20 @@ class MoELayer(nn.Module):
         """(owner rank, local index) of expert e."""
         return expert_home(self.cfg.num_experts, self.world, self.cfg.placement, e)
 
+    def weights_ready(self) -> None:
+        """Call before reading the expert weights outside a training step (export, comparison, a change of shadows) when
+        experts are shadowed and updated by the fused SGD: the rows of this rank's copies are written by the ranks that
+        summed them, and this waits, on the current stream, until all of them have.  The next forward pass needs no such
+        call.  Collective in the sense that every rank must have finished its step."""
+        if self.ws is not None:
+            from ..ops.moe import wait_for_copies
+            wait_for_copies(self.ws)
+
     @torch.no_grad()
     def sync_shadow_to_real(self) -> None:
         """Copy this rank's copy of every shadowed expert it owns into the expert's own slot (which receives no rows while
         the expert is shadowed and so goes stale): call before exporting the experts or changing the set of shadows."""
+        self.weights_ready()
         for j, e in enumerate(self.cfg.shadow):
             if e >= 0 and self.home(e)[0] == self.rank:
                 self.w13[self.home(e)[1]].copy_(self.w13[self.epr + j])

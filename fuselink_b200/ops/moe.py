@@ -154,6 +154,7 @@ class MoEWorkspace:
         # writes the updated rows into every copy.
         self.push = None
         self.gathering_shadow = None
+        self.copies_pending = False
         # Overlap of the shadow experts' gradient all-reduce with the rest of the backward pass (set by MoELayer once it has
         # a communicator of its own whose kernels are limited to `reduce_ctas` CTAs): the copies' weight gradients are then
         # computed first and summed while dX and the owned experts' weight gradients run on the remaining SMs.
@@ -358,6 +359,7 @@ def moe_forward_experts(ws: MoEWorkspace, w13: torch.Tensor, w2: torch.Tensor) -
     C = require_native()
     h = ws.heap
     barrier(h, ws.name + ":d", signal=False, wait=True)
+    ws.copies_pending = False      # every rank's dispatch signal follows its writes into the copies (finish_shadow_grads)
     counts = ws.counts_now()
     C.moe_zero_tail(ws.xd.addr(), counts.data_ptr(), ws.epr, ws.cap, ws.cfg.hidden)
     st = h.status()
@@ -525,6 +527,12 @@ def finish_shadow_grads(ws: MoEWorkspace, started) -> None:
                                M13 * N13, sgd_lr, pk.max_ctas)
             gemm.shadow_update(pk.p2.local, w2[R:], [a + R * M2 * N2 * 2 for a in pk.w2.peers()], S, h.rank, M2, N2, pk.b2,
                                M2 * N2, sgd_lr, pk.max_ctas)
+            # This rank's copies are complete once EVERY rank has run the two kernels above.  The next forward pass learns
+            # that from the ranks' dispatch signal, which each of them sends after this one; whatever else reads the copies
+            # first (a change of shadows, a checkpoint) calls wait_for_copies.
+            barrier(h, ws.name + ":bw", signal=True, wait=False)
+            ws.copies_pending = True
+            ws.launches += 1
         else:
             # the summed rows go into every rank's buffer; a rank's own buffer is complete once every rank has run this and
             # signalled
@@ -562,6 +570,15 @@ def moe_backward_finish(ws: MoEWorkspace, need_dx: bool = True) -> Optional[torc
         ws.launches += 1
     finish_shadow_grads(ws, started)
     return dx
+
+
+def wait_for_copies(ws: MoEWorkspace) -> None:
+    """After a step with the fused update of shadowed experts summed by this library: waits (on the current stream) until
+    every rank has written the rows it updated into this rank's copies.  A no-op when nothing is outstanding."""
+    if getattr(ws, "copies_pending", False):
+        ws.copies_pending = False
+        barrier(ws.heap, ws.name + ":bw", signal=False, wait=True)
+        ws.launches += 1
 
 
 def moe_backward_complete(ws: MoEWorkspace) -> None:

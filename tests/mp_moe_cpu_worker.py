@@ -81,6 +81,7 @@ def main():                      # the change of shadows below names expert 5: s
                         close(layer.w2.grad[slot_of(e)], w2.grad[e], f"dW2 expert {e}")
                     layer.zero_grad(set_to_none=True)
                 else:
+                    layer.weights_ready()       # pushed sums: the rows of this rank's copies are written by the ranks that summed them
                     with torch.no_grad():
                         for t in (wg, wu, w2):
                             t -= sgd * t.grad

@@ -128,6 +128,8 @@ def main():
                 m(x.clone().requires_grad_(True)).float().pow(2).sum().backward()
             torch.cuda.synchronize()
             heap.check_status("moe push")
+        arms["1"].weights_ready()           # the peers write the rows they updated into this rank's copies
+        torch.cuda.synchronize()
         epr = cfg.num_experts // world
         for n in ("w13", "w2"):
             a, b = getattr(arms["1"], n).detach().float(), getattr(arms["0"], n).detach().float()
