@@ -11,7 +11,7 @@ decode, and rank r hands its KV shard to rank r + world/2 -- the reference's lay
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 experiments/run_online_serving.py --model opt_6.7b
 
 The report is the reference's: communication volume per batch (KV bytes, header bytes), send window, prefill time.
-The multi-process mode has not been run on hardware yet (the single-process mode has)."""
+Both modes run on B200s: one process on one GPU, 1 + 1 processes on two GPUs, and 2 x TP 2 on four."""
 import argparse
 import json
 import os
