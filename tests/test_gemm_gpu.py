@@ -210,7 +210,7 @@ def test_throughput_smoke():
     assert tf > 50, "tensor-core path is not being used"
 
 
-@pytest.mark.parametrize("world,M,lr", [(2, 512, 0.5), (4, 1024, 0.5), (2, 384, 0.0), (8, 2048, 0.25)])
+@pytest.mark.parametrize("world,M,lr", [(2, 512, 0.5), (4, 1024, 0.5), (2, 384, 0.0), (8, 2048, 0.25), (3, 768, 0.5)])
 def test_wgrad_push_and_update_sum_the_ranks_partials(world, M, lr):
     """The two halves of the sum of replicated experts' weight gradients, with the ranks emulated one after the other on
     this GPU (neither kernel waits for another): every rank's GEMM deals its result rows out to the staging of the rank
