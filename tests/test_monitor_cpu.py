@@ -214,6 +214,23 @@ def test_daemon_sizes_its_table_from_the_machine():
     assert f"{want or 8} paths" in out.stdout, out.stdout
 
 
+def test_daemon_bench_mode_reports_the_decision_latency():
+    """`fuselink-monitor --bench` times a selector decision and the table's calls with the sweeper running; a decision is
+    a few atomics and two clock reads, far below the 160 us lease it has to fit into."""
+    import json
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "fuselink_b200", "lib", "fuselink-monitor")
+    if not os.path.exists(exe):
+        pytest.skip("daemon not built")
+    for threads in (1, 3):
+        out = subprocess.run([exe, "--bench", "100000", "--threads", str(threads)], capture_output=True, text=True, timeout=60)
+        assert out.returncode == 0, out.stderr
+        r = json.loads(out.stdout.strip().splitlines()[-1])
+        assert r["threads"] == threads and r["paths"] == 8
+        assert r["decisions"] >= 100000 * threads
+        for k in ("select_paths_ns", "borrow_release_ns", "mark_active_ns", "post_complete_bytes_ns"):
+            assert 0 < r[k] < 50_000, (k, r)               # generous: a shared CI core, not a latency claim
+
+
 def test_metrics_endpoint_serves_the_table():
     """The Prometheus endpoint reads the same table the selector writes: state, outstanding bytes and decisions."""
     import urllib.request
