@@ -1,7 +1,8 @@
 // C / C++ interface of fuselink_b200: everything exported by lib/libfuselink.so (no Python, no PyTorch needed).
 //
 //   kernels   grouped GEMM (bf16 and block-scaled fp8), chunked peer copies / all-to-all / flag waits,
-//             MoE dispatch + combine, embedding-bag + all-to-all, KV page pack + send      (launch on a cudaStream_t)
+//             MoE dispatch + combine, embedding-bag + all-to-all, KV page pack + send,
+//             sum + update of replicated experts' weight gradients                         (launch on a cudaStream_t)
 //   regions   cuMem regions that can be exported, imported, aliased and re-homed; slab pool  (vmm.h)
 //   monitor   lock-free idleness table and path selection                                    (monitor.h)
 //
@@ -15,5 +16,6 @@
 #include "../csrc/kernels/kv_pack.cuh"
 #include "../csrc/kernels/moe_dispatch.cuh"
 #include "../csrc/kernels/moe_dispatch_noalloc.cuh"
+#include "../csrc/kernels/shadow_reduce.cuh"
 #include "../csrc/mem/vmm.h"
 #include "../csrc/monitor/monitor.h"
