@@ -572,3 +572,49 @@ def test_placement_changes_nothing_the_kernels_can_see_but_index_values(world):
     weights sit in which slot."""
     assert _default_step_trace(world, 0.05, placement="balanced") == _default_step_trace(world, 0.05)
     assert _default_step_trace(world, 0.05, placement=(7, 6, 5, 4, 3, 2, 1, 0)) == _default_step_trace(world, 0.05)
+
+
+def test_push_reduce_falls_back_when_the_heap_has_no_room_or_the_rows_do_not_divide():
+    """enable_push_reduce answers False, and the layer keeps ordinary tensors for its experts (the all-reduce formulation),
+    when the symmetric heap cannot take the weights and the staging, and when the gradient rows do not divide over the
+    ranks; with room and divisible rows the experts move onto the heap."""
+    import os
+    import cpu_kernel_model
+    from fuselink_b200.models.moe import MoELayer
+    from fuselink_b200.ops import moe as M
+    from fuselink_b200.parallel.symm import SymmetricHeap
+    cfg = M.MoEConfig(hidden=128, ffn=256, num_experts=4, topk=2, tokens=16)
+
+    def on_heap(layer, heap):
+        return heap.addr(0) <= layer.w13.data_ptr() < heap.addr(0) + heap.size
+
+    with cpu_kernel_model.installed():
+        heaps = SymmetricHeap.emulated(2, 32 << 20)
+        three = SymmetricHeap.emulated(3, 32 << 20)
+        try:
+            # how much one workspace takes: push-reduce off
+            os.environ["FUSELINK_PUSH_REDUCE"] = "0"
+            try:
+                before = heaps[0]._state["bump"]
+                probe = MoELayer(cfg, heaps[0], 0, 2, device="cpu", seed=1, fused_sgd_lr=0.05, name="probe", shadow_experts=1)
+                need = heaps[0]._state["bump"] - before
+            finally:
+                os.environ.pop("FUSELINK_PUSH_REDUCE", None)
+            assert probe.ws.push is None and not on_heap(probe, heaps[0])
+            # with room: the experts move onto the heap
+            b = MoELayer(cfg, heaps[0], 0, 2, device="cpu", seed=1, fused_sgd_lr=0.05, name="b", shadow_experts=1)
+            assert b.ws.push is not None and on_heap(b, heaps[0])
+            assert b.w13.data_ptr() == b.ws.push.w13.addr() and b.w2.data_ptr() == b.ws.push.w2.addr()
+            assert torch.equal(b.w13.detach(), probe.w13.detach())                       # same weights, new home
+            # leave room for one more workspace and little else
+            left = heaps[0].size - heaps[0]._state["bump"]
+            heaps[0].alloc(left - need - (96 << 10))
+            a = MoELayer(cfg, heaps[0], 0, 2, device="cpu", seed=1, fused_sgd_lr=0.05, name="a", shadow_experts=1)
+            assert a.ws.push is None and not on_heap(a, heaps[0])
+            # rows that do not divide over the ranks: 512 and 128 rows over 3 ranks
+            odd = M.MoEConfig(hidden=128, ffn=256, num_experts=6, topk=2, tokens=16)
+            c = MoELayer(odd, three[0], 0, 3, device="cpu", seed=1, fused_sgd_lr=0.05, name="c", shadow_experts=1)
+            assert c.ws.push is None
+        finally:
+            for h in heaps + three:
+                h.close()
