@@ -6,7 +6,7 @@
 #   NGPU=1 bench/reproduce.sh            # kernels + flagship step on one GPU
 #   NGPU=8 bench/reproduce.sh            # adds p2p / all-to-all sweeps, DLRM, serving and the NCCL arms
 #   SECTIONS="moe dlrm" NGPU=8 bench/reproduce.sh
-#   SECTIONS="moe-shadow shadow-reduce gemm-sweep" NGPU=8 bench/reproduce.sh     # optional sections
+#   SECTIONS="moe-shadow shadow-reduce gemm-sweep monitor" NGPU=8 bench/reproduce.sh     # optional sections
 set -uo pipefail
 cd "$(dirname "$0")/.."
 NGPU=${NGPU:-1}; OUT=${OUT:-bench_results.jsonl}; STEPS=${STEPS:-20}; WARMUP=${WARMUP:-5}
@@ -31,6 +31,8 @@ for s in $SECTIONS; do
         run "moe contiguous placement, no shadows" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --placement contiguous --shadow 0 --no-baseline --no-other
         for n in 0 1 2 3; do run "moe shadow=$n (rows stay local)" tr bench.py --gpus "$NGPU" --steps "$STEPS" --warmup "$WARMUP" --shadow "$n" --no-baseline --no-other; done
       fi ;;
+    monitor)   # not in the default list (no GPU needed): latency of a selector decision and of the table's calls
+      for t in 1 4; do run "monitor decisions, $t thread(s)" fuselink_b200/lib/fuselink-monitor --bench 2000000 --threads "$t" --groups 8; done ;;
     shadow-reduce)   # not in the default list: the sum of the copies' gradients, own kernels against the all-reduce, and the two kernels alone
       run "push GEMM + update kernel, one GPU" python bench/shadow_reduce_case.py --world 8 --groups 1 --rows 4096 --iters 5
       if [ "$NGPU" -ge 2 ]; then
